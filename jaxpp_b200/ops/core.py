@@ -1,0 +1,545 @@
+"""The closed set of tensor ops that captured train steps are made of.
+
+Every op is a ``torch.library`` custom op in the ``b200`` namespace with
+
+* a shape function (``register_fake``) so a train step can be traced without data,
+* a reference implementation in plain PyTorch (runs on CPU, and on CUDA only when native
+  kernels are switched off with ``JAXPP_B200_NATIVE=0``),
+* a native sm_100a implementation (``jaxpp_b200.ops.native``) used for CUDA tensors, and
+* an explicit backward written in terms of other ``b200`` ops, with the input-gradient and
+  weight-gradient parts as *separate* ops so that the compiler can split a backward task into
+  its activation half and its weight half by dataflow (zero-bubble schedules).
+
+The reference framework has no op layer of its own: these computations are XLA fusions of the
+user's jnp code there (e.g. examples/basic.py:33-91 for dense/attention/LayerNorm/GELU).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+from torch import Tensor
+
+from ..utils import config
+
+_lib = torch.library.Library("b200", "DEF")
+
+_NATIVE = None
+
+
+def _native():
+    """The native kernel module; raises if it cannot be loaded (no silent fallback on CUDA)."""
+    global _NATIVE
+    if _NATIVE is None:
+        from . import native
+
+        native.load()
+        _NATIVE = native
+    return _NATIVE
+
+
+def _use_native(t: Tensor) -> bool:
+    return t.is_cuda and config.use_native_kernels.value
+
+
+def _define(schema: str, ref_impl, fake_impl, native_name: str | None = None):
+    """Register ``b200::<schema>`` with reference, fake and (optional) native implementations."""
+    name = schema.split("(")[0]
+    _lib.define(schema)
+    qual = f"b200::{name}"
+
+    if native_name is None:
+        impl = ref_impl
+    else:
+        def impl(*args, __ref=ref_impl, __nn=native_name):
+            first = next(a for a in args if isinstance(a, Tensor))
+            if _use_native(first):
+                return getattr(_native(), __nn)(*args)
+            return __ref(*args)
+
+    _lib.impl(name, impl, "CompositeExplicitAutograd")
+    torch.library.register_fake(qual, fake_impl)
+    return getattr(torch.ops.b200, name)
+
+
+def _autograd(name: str, backward, setup_context):
+    torch.library.register_autograd(f"b200::{name}", backward, setup_context=setup_context)
+
+
+def _f32(t: Tensor) -> Tensor:
+    return t.float()
+
+
+# ======================================================================================
+# linear:  y[..., N] = x[..., K] @ w[N, K]^T (+ bias[N])
+# ======================================================================================
+
+def _linear_ref(x, w, bias):
+    y = x @ w.t()
+    return y if bias is None else y + bias
+
+
+def _linear_fake(x, w, bias):
+    return x.new_empty(*x.shape[:-1], w.shape[0])
+
+
+linear = _define("linear(Tensor x, Tensor w, Tensor? bias) -> Tensor", _linear_ref, _linear_fake, "linear")
+
+
+def _linear_dgrad_ref(dy, w):
+    return dy @ w
+
+
+linear_dgrad = _define(
+    "linear_dgrad(Tensor dy, Tensor w) -> Tensor",
+    _linear_dgrad_ref,
+    lambda dy, w: dy.new_empty(*dy.shape[:-1], w.shape[1]),
+    "linear_dgrad",
+)
+
+
+def _linear_wgrad_ref(dy, x):
+    return dy.reshape(-1, dy.shape[-1]).t() @ x.reshape(-1, x.shape[-1])
+
+
+linear_wgrad = _define(
+    "linear_wgrad(Tensor dy, Tensor x) -> Tensor",
+    _linear_wgrad_ref,
+    lambda dy, x: dy.new_empty(dy.shape[-1], x.shape[-1]),
+    "linear_wgrad",
+)
+
+# column sums, used for bias gradients
+colsum = _define(
+    "colsum(Tensor dy) -> Tensor",
+    lambda dy: dy.reshape(-1, dy.shape[-1]).float().sum(0).to(dy.dtype),
+    lambda dy: dy.new_empty(dy.shape[-1]),
+    "colsum",
+)
+
+
+def _linear_setup(ctx, inputs, output):
+    x, w, bias = inputs
+    ctx.save_for_backward(x, w)
+    ctx.has_bias = bias is not None
+
+
+def _linear_bwd(ctx, dy):
+    x, w = ctx.saved_tensors
+    dx = linear_dgrad(dy, w) if ctx.needs_input_grad[0] else None
+    dw = linear_wgrad(dy, x) if ctx.needs_input_grad[1] else None
+    db = colsum(dy) if ctx.has_bias and ctx.needs_input_grad[2] else None
+    return dx, dw, db
+
+
+_autograd("linear", _linear_bwd, _linear_setup)
+
+
+# ======================================================================================
+# RMSNorm / LayerNorm (statistics in fp32)
+# ======================================================================================
+
+def _rmsnorm_ref(x, w, eps):
+    xf = _f32(x)
+    rstd = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return (xf * rstd * _f32(w)).to(x.dtype), rstd.squeeze(-1)
+
+
+rmsnorm = _define(
+    "rmsnorm(Tensor x, Tensor w, float eps) -> (Tensor, Tensor)",
+    _rmsnorm_ref,
+    lambda x, w, eps: (torch.empty_like(x), x.new_empty(x.shape[:-1], dtype=torch.float32)),
+    "rmsnorm",
+)
+
+
+def _rmsnorm_bwd_ref(dy, x, w, rstd):
+    xf, dyf, wf = _f32(x), _f32(dy), _f32(w)
+    xhat = xf * rstd.unsqueeze(-1)
+    g = dyf * wf
+    dx = (g - xhat * (g * xhat).mean(-1, keepdim=True)) * rstd.unsqueeze(-1)
+    dw = (dyf * xhat).reshape(-1, x.shape[-1]).sum(0)
+    return dx.to(x.dtype), dw.to(w.dtype)
+
+
+rmsnorm_bwd = _define(
+    "rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd) -> (Tensor, Tensor)",
+    _rmsnorm_bwd_ref,
+    lambda dy, x, w, rstd: (torch.empty_like(x), torch.empty_like(w)),
+    "rmsnorm_bwd",
+)
+
+
+def _rmsnorm_setup(ctx, inputs, output):
+    x, w, _ = inputs
+    ctx.save_for_backward(x, w, output[1])
+
+
+def _rmsnorm_autograd(ctx, dy, _drstd):
+    x, w, rstd = ctx.saved_tensors
+    dx, dw = rmsnorm_bwd(dy, x, w, rstd)
+    return dx, dw, None
+
+
+_autograd("rmsnorm", _rmsnorm_autograd, _rmsnorm_setup)
+
+
+def _layernorm_ref(x, w, b, eps):
+    xf = _f32(x)
+    mean = xf.mean(-1, keepdim=True)
+    var = (xf - mean).pow(2).mean(-1, keepdim=True)
+    rstd = torch.rsqrt(var + eps)
+    y = (xf - mean) * rstd * _f32(w) + _f32(b)
+    return y.to(x.dtype), mean.squeeze(-1), rstd.squeeze(-1)
+
+
+layernorm = _define(
+    "layernorm(Tensor x, Tensor w, Tensor b, float eps) -> (Tensor, Tensor, Tensor)",
+    _layernorm_ref,
+    lambda x, w, b, eps: (
+        torch.empty_like(x),
+        x.new_empty(x.shape[:-1], dtype=torch.float32),
+        x.new_empty(x.shape[:-1], dtype=torch.float32),
+    ),
+    "layernorm",
+)
+
+
+def _layernorm_bwd_ref(dy, x, w, mean, rstd):
+    xf, dyf, wf = _f32(x), _f32(dy), _f32(w)
+    xhat = (xf - mean.unsqueeze(-1)) * rstd.unsqueeze(-1)
+    g = dyf * wf
+    dx = (g - g.mean(-1, keepdim=True) - xhat * (g * xhat).mean(-1, keepdim=True)) * rstd.unsqueeze(-1)
+    dw = (dyf * xhat).reshape(-1, x.shape[-1]).sum(0)
+    db = dyf.reshape(-1, x.shape[-1]).sum(0)
+    return dx.to(x.dtype), dw.to(w.dtype), db.to(w.dtype)
+
+
+layernorm_bwd = _define(
+    "layernorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor mean, Tensor rstd) -> (Tensor, Tensor, Tensor)",
+    _layernorm_bwd_ref,
+    lambda dy, x, w, mean, rstd: (torch.empty_like(x), torch.empty_like(w), torch.empty_like(w)),
+    "layernorm_bwd",
+)
+
+
+def _layernorm_setup(ctx, inputs, output):
+    x, w, b, _ = inputs
+    ctx.save_for_backward(x, w, output[1], output[2])
+
+
+def _layernorm_autograd(ctx, dy, _dm, _dr):
+    x, w, mean, rstd = ctx.saved_tensors
+    dx, dw, db = layernorm_bwd(dy, x, w, mean, rstd)
+    return dx, dw, db, None
+
+
+_autograd("layernorm", _layernorm_autograd, _layernorm_setup)
+
+
+# ======================================================================================
+# Activations: GELU (tanh approximation) and SwiGLU on a fused [gate | up] tensor
+# ======================================================================================
+_K0 = math.sqrt(2.0 / math.pi)
+_K1 = 0.044715
+
+
+def _gelu_ref(x):
+    xf = _f32(x)
+    return (0.5 * xf * (1.0 + torch.tanh(_K0 * (xf + _K1 * xf.pow(3))))).to(x.dtype)
+
+
+def _gelu_bwd_ref(dy, x):
+    xf = _f32(x)
+    t = torch.tanh(_K0 * (xf + _K1 * xf.pow(3)))
+    dt = (1.0 - t * t) * _K0 * (1.0 + 3.0 * _K1 * xf * xf)
+    return (_f32(dy) * (0.5 * (1.0 + t) + 0.5 * xf * dt)).to(x.dtype)
+
+
+gelu = _define("gelu(Tensor x) -> Tensor", _gelu_ref, lambda x: torch.empty_like(x), "gelu")
+gelu_bwd = _define("gelu_bwd(Tensor dy, Tensor x) -> Tensor", _gelu_bwd_ref, lambda dy, x: torch.empty_like(x), "gelu_bwd")
+_autograd(
+    "gelu",
+    lambda ctx, dy: gelu_bwd(dy, ctx.saved_tensors[0]),
+    lambda ctx, inputs, output: ctx.save_for_backward(inputs[0]),
+)
+
+
+def _swiglu_ref(gu):
+    g, u = _f32(gu).chunk(2, dim=-1)
+    return (torch.nn.functional.silu(g) * u).to(gu.dtype)
+
+
+def _swiglu_bwd_ref(dy, gu):
+    g, u = _f32(gu).chunk(2, dim=-1)
+    s = torch.sigmoid(g)
+    dyf = _f32(dy)
+    dg = dyf * u * s * (1.0 + g * (1.0 - s))
+    du = dyf * g * s
+    return torch.cat([dg, du], dim=-1).to(gu.dtype)
+
+
+swiglu = _define(
+    "swiglu(Tensor gate_up) -> Tensor",
+    _swiglu_ref,
+    lambda gu: gu.new_empty(*gu.shape[:-1], gu.shape[-1] // 2),
+    "swiglu",
+)
+swiglu_bwd = _define(
+    "swiglu_bwd(Tensor dy, Tensor gate_up) -> Tensor", _swiglu_bwd_ref, lambda dy, gu: torch.empty_like(gu), "swiglu_bwd"
+)
+_autograd(
+    "swiglu",
+    lambda ctx, dy: swiglu_bwd(dy, ctx.saved_tensors[0]),
+    lambda ctx, inputs, output: ctx.save_for_backward(inputs[0]),
+)
+
+
+# ======================================================================================
+# RoPE on [B, S, H, D] with half-split rotation (Llama convention); cos/sin are [S, D/2] fp32
+# ======================================================================================
+
+def _rope_ref(x, cos, sin, inverse):
+    xf = _f32(x)
+    d2 = x.shape[-1] // 2
+    x1, x2 = xf[..., :d2], xf[..., d2:]
+    c = cos[None, :, None, :]
+    s = -sin[None, :, None, :] if inverse else sin[None, :, None, :]
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).to(x.dtype)
+
+
+rope = _define(
+    "rope(Tensor x, Tensor cos, Tensor sin, bool inverse) -> Tensor",
+    _rope_ref,
+    lambda x, cos, sin, inverse: torch.empty_like(x),
+    "rope",
+)
+
+
+def _rope_setup(ctx, inputs, output):
+    _, cos, sin, inverse = inputs
+    ctx.save_for_backward(cos, sin)
+    ctx.inverse = inverse
+
+
+def _rope_autograd(ctx, dy):
+    cos, sin = ctx.saved_tensors
+    return rope(dy, cos, sin, not ctx.inverse), None, None, None
+
+
+_autograd("rope", _rope_autograd, _rope_setup)
+
+
+# ======================================================================================
+# Attention on [B, S, H, D] (q) and [B, S, Hkv, D] (k, v); returns output and log-sum-exp
+# ======================================================================================
+
+def _attn_ref(q, k, v, causal, scale):
+    B, S, H, D = q.shape
+    Hkv = k.shape[2]
+    rep = H // Hkv
+    qf = _f32(q).permute(0, 2, 1, 3)
+    kf = _f32(k).permute(0, 2, 1, 3).repeat_interleave(rep, dim=1)
+    vf = _f32(v).permute(0, 2, 1, 3).repeat_interleave(rep, dim=1)
+    s = (qf @ kf.transpose(-1, -2)) * scale
+    if causal:
+        Sk = k.shape[1]
+        mask = torch.ones(S, Sk, dtype=torch.bool, device=q.device).tril(Sk - S)
+        s = s.masked_fill(~mask, float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.exp(s - lse.unsqueeze(-1))
+    o = (p @ vf).permute(0, 2, 1, 3)
+    return o.to(q.dtype).contiguous(), lse  # lse: [B, H, S] fp32
+
+
+attention = _define(
+    "attention(Tensor q, Tensor k, Tensor v, bool causal, float scale) -> (Tensor, Tensor)",
+    _attn_ref,
+    lambda q, k, v, causal, scale: (
+        torch.empty_like(q),
+        q.new_empty(q.shape[0], q.shape[2], q.shape[1], dtype=torch.float32),
+    ),
+    "attention",
+)
+
+
+def _attn_bwd_ref(do, q, k, v, o, lse, causal, scale):
+    B, S, H, D = q.shape
+    Hkv = k.shape[2]
+    rep = H // Hkv
+    qf = _f32(q).permute(0, 2, 1, 3)
+    kf = _f32(k).permute(0, 2, 1, 3).repeat_interleave(rep, dim=1)
+    vf = _f32(v).permute(0, 2, 1, 3).repeat_interleave(rep, dim=1)
+    dof = _f32(do).permute(0, 2, 1, 3)
+    of = _f32(o).permute(0, 2, 1, 3)
+    s = (qf @ kf.transpose(-1, -2)) * scale
+    if causal:
+        Sk = k.shape[1]
+        mask = torch.ones(S, Sk, dtype=torch.bool, device=q.device).tril(Sk - S)
+        s = s.masked_fill(~mask, float("-inf"))
+    p = torch.exp(s - lse.unsqueeze(-1))
+    dv = p.transpose(-1, -2) @ dof
+    dp = dof @ vf.transpose(-1, -2)
+    delta = (dof * of).sum(-1, keepdim=True)
+    ds = p * (dp - delta) * scale
+    dq = ds @ kf
+    dk = ds.transpose(-1, -2) @ qf
+    if rep > 1:
+        dk = dk.reshape(B, Hkv, rep, k.shape[1], D).sum(2)
+        dv = dv.reshape(B, Hkv, rep, k.shape[1], D).sum(2)
+    to = lambda t, like: t.permute(0, 2, 1, 3).to(like.dtype).contiguous()
+    return to(dq, q), to(dk, k), to(dv, v)
+
+
+attention_bwd = _define(
+    "attention_bwd(Tensor do, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, bool causal, float scale)"
+    " -> (Tensor, Tensor, Tensor)",
+    _attn_bwd_ref,
+    lambda do, q, k, v, o, lse, causal, scale: (torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)),
+    "attention_bwd",
+)
+
+
+def _attn_setup(ctx, inputs, output):
+    q, k, v, causal, scale = inputs
+    ctx.save_for_backward(q, k, v, output[0], output[1])
+    ctx.causal, ctx.scale = causal, scale
+
+
+def _attn_autograd(ctx, do, _dlse):
+    q, k, v, o, lse = ctx.saved_tensors
+    dq, dk, dv = attention_bwd(do, q, k, v, o, lse, ctx.causal, ctx.scale)
+    return dq, dk, dv, None, None
+
+
+_autograd("attention", _attn_autograd, _attn_setup)
+
+
+# ======================================================================================
+# Cross entropy over the last dim: returns per-row loss (fp32) and log-sum-exp (fp32)
+# ======================================================================================
+
+def _ce_ref(logits, labels):
+    lf = _f32(logits)
+    lse = torch.logsumexp(lf, dim=-1)
+    picked = lf.gather(-1, labels.unsqueeze(-1)).squeeze(-1)
+    return lse - picked, lse
+
+
+cross_entropy = _define(
+    "cross_entropy(Tensor logits, Tensor labels) -> (Tensor, Tensor)",
+    _ce_ref,
+    lambda logits, labels: (
+        logits.new_empty(logits.shape[:-1], dtype=torch.float32),
+        logits.new_empty(logits.shape[:-1], dtype=torch.float32),
+    ),
+    "cross_entropy",
+)
+
+
+def _ce_bwd_ref(dloss, logits, labels, lse):
+    p = torch.exp(_f32(logits) - lse.unsqueeze(-1))
+    p.scatter_add_(-1, labels.unsqueeze(-1), -torch.ones_like(p[..., :1]))
+    return (p * dloss.unsqueeze(-1)).to(logits.dtype)
+
+
+cross_entropy_bwd = _define(
+    "cross_entropy_bwd(Tensor dloss, Tensor logits, Tensor labels, Tensor lse) -> Tensor",
+    _ce_bwd_ref,
+    lambda dloss, logits, labels, lse: torch.empty_like(logits),
+    "cross_entropy_bwd",
+)
+
+
+def _ce_setup(ctx, inputs, output):
+    logits, labels = inputs
+    ctx.save_for_backward(logits, labels, output[1])
+
+
+def _ce_autograd(ctx, dloss, _dlse):
+    logits, labels, lse = ctx.saved_tensors
+    return cross_entropy_bwd(dloss.contiguous(), logits, labels, lse), None
+
+
+_autograd("cross_entropy", _ce_autograd, _ce_setup)
+
+
+# ======================================================================================
+# Embedding gather / scatter-add
+# ======================================================================================
+embedding = _define(
+    "embedding(Tensor ids, Tensor table) -> Tensor",
+    lambda ids, table: table[ids],
+    lambda ids, table: table.new_empty(*ids.shape, table.shape[1]),
+    "embedding",
+)
+
+
+def _emb_bwd_ref(dy, ids, vocab):
+    out = torch.zeros(vocab, dy.shape[-1], dtype=torch.float32, device=dy.device)
+    out.index_add_(0, ids.reshape(-1), _f32(dy).reshape(-1, dy.shape[-1]))
+    return out.to(dy.dtype)
+
+
+embedding_bwd = _define(
+    "embedding_bwd(Tensor dy, Tensor ids, int vocab) -> Tensor",
+    _emb_bwd_ref,
+    lambda dy, ids, vocab: dy.new_empty(vocab, dy.shape[-1]),
+    "embedding_bwd",
+)
+
+
+def _emb_setup(ctx, inputs, output):
+    ids, table = inputs
+    ctx.save_for_backward(ids)
+    ctx.vocab = table.shape[0]
+
+
+_autograd("embedding", lambda ctx, dy: (None, embedding_bwd(dy.contiguous(), ctx.saved_tensors[0], ctx.vocab)), _emb_setup)
+
+
+# ======================================================================================
+# Fused AdamW step (functional): returns new (master, m, v, low-precision copy)
+# ``master``/``m``/``v`` are fp32; ``grad`` may be bf16 or fp32; ``step`` is a 0-d tensor (1-based)
+# ======================================================================================
+
+def _adamw_ref(master, grad, m, v, step, lr, beta1, beta2, eps, weight_decay, grad_scale, out_dtype):
+    g = _f32(grad) * grad_scale
+    m2 = beta1 * m + (1.0 - beta1) * g
+    v2 = beta2 * v + (1.0 - beta2) * g * g
+    t = step.to(torch.float32)
+    bc1 = 1.0 - beta1 ** t
+    bc2 = 1.0 - beta2 ** t
+    upd = (m2 / bc1) / ((v2 / bc2).sqrt() + eps)
+    p2 = master * (1.0 - lr * weight_decay) - lr * upd
+    return p2, m2, v2, p2.to(out_dtype)
+
+
+adamw = _define(
+    "adamw(Tensor master, Tensor grad, Tensor m, Tensor v, Tensor step, float lr, float beta1, float beta2,"
+    " float eps, float weight_decay, float grad_scale, ScalarType out_dtype) -> (Tensor, Tensor, Tensor, Tensor)",
+    _adamw_ref,
+    lambda master, grad, m, v, step, lr, b1, b2, eps, wd, gs, out_dtype: (
+        torch.empty_like(master),
+        torch.empty_like(m),
+        torch.empty_like(v),
+        master.new_empty(master.shape, dtype=out_dtype),
+    ),
+    "adamw",
+)
+
+
+# ======================================================================================
+# Mean-squared-error helper used by the encoder example (kept as ATen: it is glue, not hot)
+# ======================================================================================
+
+def mse_loss(out: Tensor, target: Tensor) -> Tensor:
+    return (out.float() - target.float()).pow(2).mean()
+
+
+__all__ = [
+    "linear", "linear_dgrad", "linear_wgrad", "colsum", "rmsnorm", "rmsnorm_bwd", "layernorm", "layernorm_bwd",
+    "gelu", "gelu_bwd", "swiglu", "swiglu_bwd", "rope", "attention", "attention_bwd", "cross_entropy",
+    "cross_entropy_bwd", "embedding", "embedding_bwd", "adamw", "mse_loss",
+]

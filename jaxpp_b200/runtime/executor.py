@@ -1,0 +1,257 @@
+"""Interpreters for compiled programs.
+
+``RankState`` holds one pipeline rank's value environment and executes that rank's instructions;
+``run_single_controller`` drives all ranks of a program from one process in the program's global
+order (the oracle / CPU simulator, and the mode notebooks use; reference:
+``GlobalMpmdFunction.__call__``, src/jaxpp/core.py:3709-3793); ``run_multi_controller`` executes
+only this process's rank and talks to the others through a :class:`~.comm.Comm` (reference:
+``ScalarMpmdFunction.__call__``, :3401-3447, and the eager primitive implementations in
+src/jaxpp/jax_primitives.py:370-523, 776-859).
+"""
+from __future__ import annotations
+
+import contextlib
+import time
+from collections import defaultdict
+from typing import Any, Sequence
+
+import torch
+
+from ..compiler.program import (Accum, AllGather, AllReduce, Delete, Instr, LoopIndex, Program, RunTask, SendDone,
+                                Slice, Transfer)
+from ..utils import config
+
+# ---- task timing (reference: collect_task_times_ms, jax_primitives.py:742-773) -----------------
+_TIMES: list[dict] = []
+
+
+@contextlib.contextmanager
+def collect_task_times_ms(enabled: bool = True):
+    """Collect ``task name → [milliseconds…]`` for every task run inside the ``with``.
+
+    While active, the executor synchronises the device before and after each task, which serialises
+    the pipeline: use it to cost tasks, not to measure throughput.
+    """
+    if not enabled:
+        yield None
+        return
+    table: dict[str, list[float]] = defaultdict(list)
+    _TIMES.append(table)
+    try:
+        yield table
+    finally:
+        _TIMES.pop()
+
+
+class RankState:
+    """Environment and instruction semantics of one pipeline rank."""
+
+    def __init__(self, rank: int, device: torch.device, record_events: bool = False):
+        self.rank = rank
+        self.device = device
+        self.env: dict[int, torch.Tensor] = {}
+        self.index_cache: dict[int, torch.Tensor] = {}
+        self.record_events = record_events and device.type == "cuda"
+        self.events: list[tuple[str, Any, Any]] = []
+
+    # -- individual instructions --------------------------------------------------------------
+    def run_task(self, ins: RunTask):
+        env = self.env
+        args = []
+        for v, donate in zip(ins.ins, ins.donate):
+            args.append(env.pop(v) if donate else env[v])
+        fn = ins.code.bind(self.device)
+        timing = _TIMES[-1] if _TIMES else None
+        if timing is not None:
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)
+            t0 = time.perf_counter()
+        if self.record_events:
+            e0 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+        if self.device.type == "cuda" and config.nvtx_ranges.value:
+            torch.cuda.nvtx.range_push(ins.name)
+            try:
+                outs = fn(args)
+            finally:
+                torch.cuda.nvtx.range_pop()
+        else:
+            outs = fn(args)
+        if self.record_events:
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record()
+            self.events.append((ins.name, e0, e1))
+        if timing is not None:
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)
+            timing[f"{ins.name} ({id(ins.code)})"].append((time.perf_counter() - t0) * 1e3)
+        for v, o in zip(ins.outs, outs):
+            if v >= 0:
+                env[v] = o
+
+    def slice(self, ins: Slice):
+        self.env[ins.out] = self.env[ins.src].select(ins.axis, ins.index)
+
+    def loop_index(self, ins: LoopIndex):
+        t = self.index_cache.get(ins.index)
+        if t is None:
+            t = torch.tensor(ins.index, dtype=torch.int64, device=self.device)
+            self.index_cache[ins.index] = t
+        self.env[ins.out] = t
+
+    def accum(self, ins: Accum):
+        env = self.env
+        val = env[ins.val]
+        acc = env.get(ins.acc)
+        if ins.kind == 1:  # concat: write slot
+            if acc is None:
+                shape = list(val.shape)
+                shape.insert(ins.axis, ins.n)
+                acc = torch.empty(shape, dtype=val.dtype, device=val.device)
+                env[ins.acc] = acc
+            acc.select(ins.axis, ins.index).copy_(val)
+            return
+        if acc is None:
+            env[ins.acc] = val if (ins.steal and val.is_contiguous()) else val.clone()
+        elif ins.kind == 0:
+            acc.add_(val)
+        else:
+            torch.maximum(acc, val, out=acc)
+
+    def delete(self, ins: Delete):
+        for v in ins.vids:
+            self.env.pop(v, None)
+
+    def busy_ms(self) -> float:
+        """Sum of task durations recorded with CUDA events (call after a device synchronise)."""
+        return sum(e0.elapsed_time(e1) for _, e0, e1 in self.events)
+
+
+def _local_sum(state: RankState, ins: AllReduce, like_shape, like_dtype):
+    if ins.local:
+        buf = state.env[ins.local[0]].clone()
+        for v in ins.local[1:]:
+            buf.add_(state.env[v])
+        return buf
+    return torch.zeros(like_shape, dtype=like_dtype, device=state.device)
+
+
+def run_single_controller(prog: Program, inputs: Sequence[torch.Tensor | None], devices: Sequence[torch.device],
+                          record_events: bool = False) -> tuple[list[RankState], list]:
+    """Execute ``prog`` for all ranks in this process.  ``inputs[i]`` is the full flat input ``i`` (or
+    ``None`` if unused); returns the rank states and the flat outputs as ``{rank: tensor}`` dicts."""
+    states = [RankState(r, devices[r], record_events) for r in range(prog.n_ranks)]
+    for (vid, ranks), x in zip(prog.inputs, inputs):
+        for r in ranks:
+            states[r].env[vid] = x if x.device == devices[r] else x.to(devices[r])
+    pending_collectives: dict[int, list] = defaultdict(list)
+    for ins in prog.instrs:
+        st = states[ins.rank]
+        if isinstance(ins, RunTask):
+            st.run_task(ins)
+        elif isinstance(ins, Slice):
+            st.slice(ins)
+        elif isinstance(ins, LoopIndex):
+            st.loop_index(ins)
+        elif isinstance(ins, Accum):
+            st.accum(ins)
+        elif isinstance(ins, Transfer):
+            dst = states[ins.dst]
+            for v in ins.vids:
+                t = st.env[v]
+                dst.env[v] = t if t.device == dst.device else t.to(dst.device, non_blocking=True)
+        elif isinstance(ins, SendDone):
+            pass
+        elif isinstance(ins, Delete):
+            st.delete(ins)
+        elif isinstance(ins, (AllReduce, AllGather)):
+            group = pending_collectives[ins.cid]
+            group.append(ins)
+            if len(group) == len(ins.ranks):
+                _collective_single(prog, states, group)
+                del pending_collectives[ins.cid]
+        else:  # pragma: no cover
+            raise NotImplementedError(type(ins))
+    outs = []
+    for o in prog.outputs:
+        if o[0] == "c":
+            outs.append(o[1])
+        else:
+            _, vid, ranks = o
+            outs.append({r: states[r].env[vid] for r in ranks})
+    return states, outs
+
+
+def _collective_single(prog: Program, states, group):
+    first = group[0]
+    info = prog.values[first.out]
+    if isinstance(first, AllReduce):
+        total = None
+        for ins in sorted(group, key=lambda i: i.rank):
+            part = _local_sum(states[ins.rank], ins, info.shape, info.dtype)
+            part = part.to(states[first.ranks[0]].device)
+            total = part if total is None else total.add_(part)
+        for ins in group:
+            states[ins.rank].env[ins.out] = total.to(states[ins.rank].device).clone() if len(group) > 1 else total
+    else:
+        parts: dict[int, torch.Tensor] = {}
+        for ins in group:
+            for p, v in ins.local.items():
+                parts[p] = states[ins.rank].env[v]
+        for ins in group:
+            dev = states[ins.rank].device
+            states[ins.rank].env[ins.out] = torch.cat([parts[p].to(dev) for p in sorted(parts)], dim=ins.axis)
+
+
+def run_multi_controller(prog: Program, rank: int, inputs: Sequence[torch.Tensor | None], device: torch.device, comm,
+                         record_events: bool = False) -> tuple[RankState, list]:
+    """Execute this process's part of ``prog``.  ``inputs[i]`` is the local tensor of flat input ``i`` or
+    ``None`` when this rank does not hold it."""
+    st = RankState(rank, device, record_events)
+    for (vid, ranks), x in zip(prog.inputs, inputs):
+        if rank in ranks:
+            if x is None:
+                raise ValueError(f"input %{vid} is required on pipeline rank {rank} but no local data was given")
+            st.env[vid] = x
+    comm.begin_step(st)
+    for ins in prog.for_rank(rank):
+        if isinstance(ins, RunTask):
+            comm.before_use(st, ins.ins)
+            st.run_task(ins)
+        elif isinstance(ins, Slice):
+            st.slice(ins)
+        elif isinstance(ins, LoopIndex):
+            st.loop_index(ins)
+        elif isinstance(ins, Accum):
+            comm.before_use(st, (ins.val,))
+            st.accum(ins)
+        elif isinstance(ins, Transfer):
+            if ins.rank == rank:
+                comm.send(st, ins, prog)
+            else:
+                comm.recv(st, ins, prog)
+        elif isinstance(ins, SendDone):
+            comm.send_done(st, ins)
+        elif isinstance(ins, Delete):
+            st.delete(ins)
+        elif isinstance(ins, AllReduce):
+            comm.before_use(st, ins.local)
+            info = prog.values[ins.out]
+            buf = _local_sum(st, ins, info.shape, info.dtype)
+            st.env[ins.out] = comm.all_reduce(buf, ins.ranks)
+        elif isinstance(ins, AllGather):
+            comm.before_use(st, ins.local.values())
+            st.env[ins.out] = comm.all_gather(st, ins, prog)
+        else:  # pragma: no cover
+            raise NotImplementedError(type(ins))
+    comm.end_step(st)
+    outs = []
+    for o in prog.outputs:
+        if o[0] == "c":
+            outs.append(o[1])
+        else:
+            _, vid, ranks = o
+            if rank in ranks:
+                comm.before_use(st, (vid,))
+            outs.append({rank: st.env[vid]} if rank in ranks else {})
+    return st, outs

@@ -1,0 +1,133 @@
+"""Run-time configuration flags read from the environment.
+
+Behavioural counterpart of the reference's flag classes (src/jaxpp/utils.py:35-113) and its
+flag list (src/jaxpp/env_vars.py:3-22): a flag is parsed lazily from ``os.environ`` the first
+time ``.value`` is read, the parsed value is remembered, and code can override it for a
+dynamic extent with ``with flag.set(v):``.  Flag names keep the ``JAXPP_`` prefix so that
+launch scripts written for the reference keep working.
+"""
+from __future__ import annotations
+
+import contextlib
+import math
+import os
+from typing import Callable, Generic, Iterator, TypeVar
+
+T = TypeVar("T")
+_UNSET = object()
+
+
+class OverwriteableVar(Generic[T]):
+    """A value holder with a default and a scoped override."""
+
+    def __init__(self, default_value: T | None = None):
+        self.default_value = default_value
+        self._override = _UNSET
+
+    def __bool__(self):
+        # Guards against ``if flag:`` (always true for an object) instead of ``if flag.value:``.
+        raise ValueError("Variable used as truthy value")
+
+    @contextlib.contextmanager
+    def set(self, to: T) -> Iterator[None]:
+        saved = self._override
+        self._override = to
+        try:
+            yield
+        finally:
+            self._override = saved
+
+    @property
+    def value(self) -> T:
+        if self._override is not _UNSET:
+            return self._override  # type: ignore[return-value]
+        assert self.default_value is not None
+        return self.default_value
+
+
+class EnvVar(OverwriteableVar[T]):
+    """Flag backed by an environment variable; the environment is consulted once."""
+
+    def __init__(self, env_key: str, default_value: T | None = None):
+        super().__init__(default_value)
+        self.env_key = env_key
+        self._cached = _UNSET
+
+    def parse(self, text: str) -> T | None:  # pragma: no cover - overridden
+        raise NotImplementedError
+
+    @property
+    def value(self) -> T:
+        if self._override is not _UNSET:
+            return self._override  # type: ignore[return-value]
+        if self._cached is _UNSET:
+            raw = os.getenv(self.env_key)
+            if raw is None:
+                assert self.default_value is not None
+                self._cached = self.default_value
+            else:
+                parsed = self.parse(raw)
+                if parsed is None:
+                    raise ValueError(f"Unsupported value {self.env_key}={raw}")
+                self._cached = parsed
+        return self._cached  # type: ignore[return-value]
+
+
+_TRUE = {"true", "1", "t", "y", "yes"}
+_FALSE = {"false", "0", "f", "n", "no"}
+
+
+def parse_bool(s: str) -> bool | None:
+    low = s.lower()
+    if low in _TRUE:
+        return True
+    if low in _FALSE:
+        return False
+    return None
+
+
+class BoolEnvVar(EnvVar[bool]):
+    def parse(self, text: str) -> bool | None:
+        return parse_bool(text)
+
+
+class StrEnvVar(EnvVar[str]):
+    def parse(self, text: str) -> str | None:
+        return text
+
+
+class IntEnvVar(EnvVar[int]):
+    def parse(self, text: str) -> int | None:
+        try:
+            return int(text)
+        except ValueError:
+            return None
+
+
+# --- flags (same names and defaults as the reference, env_vars.py:3-22) -----------------
+share_donation = BoolEnvVar("JAXPP_SHARE_DONATION", True)
+enable_local_propagation = BoolEnvVar("JAXPP_ENABLE_LOCAL_PROPAGATION", False)
+enable_licm = BoolEnvVar("JAXPP_ENABLE_LICM", False)
+dump_dir = StrEnvVar("JAXPP_DUMP_DIR", "")
+# inf (the default) = sent buffers are only collected at the end of the step.
+transfer_done_delay = IntEnvVar("JAXPP_TRANSFER_DONE_DELAY", math.inf)  # type: ignore[arg-type]
+disable_schedule_task_fusion = BoolEnvVar("JAXPP_DISABLE_SCHEDULE_TASK_FUSION", False)
+disable_prevent_cse = BoolEnvVar("JAXPP_DISABLE_PREVENT_CSE", False)
+directional_communicators = BoolEnvVar("JAXPP_DIRECTIONAL_COMMUNICATORS", False)
+conservative_loop_clustering = BoolEnvVar("JAXPP_CONSERVATIVE_LOOP_CLUSTERING", True)
+debug_skip_propagation = BoolEnvVar("JAXPP_DEBUG_SKIP_PROPAGATION", False)
+debug_force_mpmdify = BoolEnvVar("JAXPP_DEBUG_FORCE_MPMDIFY", False)
+fast_infer_shardings = BoolEnvVar("JAXPP_FAST_INFER_SHARDINGS", False)
+enable_check_ir = BoolEnvVar("JAXPP_ENABLE_CHECK_JAXPR", False)
+
+# --- flags that only exist in this framework ----------------------------------------------
+# Use the hand-written sm_100a kernels (1) or the ATen reference implementations (0) on CUDA.
+use_native_kernels = BoolEnvVar("JAXPP_B200_NATIVE", True)
+# Use fused compute+collective kernels over peer memory (1) or the NCCL-only twins (0).
+use_fused_collectives = BoolEnvVar("JAXPP_B200_FUSED_COLLECTIVES", True)
+# Capture tasks into CUDA graphs after their first eager run.
+use_cuda_graphs = BoolEnvVar("JAXPP_B200_CUDA_GRAPHS", False)
+# Seconds a rank may go without a heartbeat before the watchdog reports it.
+heartbeat_timeout_s = IntEnvVar("JAXPP_B200_HEARTBEAT_TIMEOUT", 30)
+# Wrap every task in an NVTX range named like the task (fwd_3__5, …) for timeline profilers.
+nvtx_ranges = BoolEnvVar("JAXPP_B200_NVTX", False)
