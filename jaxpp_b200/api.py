@@ -15,7 +15,7 @@ from .primitives import current_trace
 from .runtime.executor import collect_task_times_ms
 from .schedules import (BaseSchedule, DualPipeV, Eager1F1B, GPipe, Interleaved1F1B, InterleavedGPipe, KimiK2, Std1F1B,
                         ZeroBubble)
-from .training import Add, Concat, Max, treduce, treduce_i
+from .training import Add, Concat, Max, take, treduce, treduce_i
 
 _to_global_jax_array = _to_global_array  # name under which the reference exports it
 
@@ -56,5 +56,5 @@ __all__ = [
     "pipeline_enter_stage", "MpmdMesh", "MpmdArray", "MpmdSharding", "BaseSchedule", "Std1F1B", "Eager1F1B",
     "Interleaved1F1B", "KimiK2", "ZeroBubble", "DualPipeV", "GPipe", "cross_mpmd_all_reduce", "cross_mpmd_stack",
     "place_with", "spmd_to_mpmd_reshard", "mpmd_to_spmd_reshard", "collect_task_times_ms", "_to_global_jax_array",
-    "value_and_grad", "Mesh", "Device", "NamedSharding", "PartitionSpec", "P", "DistArray", "ShapeDtypeStruct",
+    "value_and_grad", "take", "Mesh", "Device", "NamedSharding", "PartitionSpec", "P", "DistArray", "ShapeDtypeStruct",
 ]

@@ -165,10 +165,15 @@ def run_single_controller(prog: Program, inputs: Sequence[torch.Tensor | None], 
         elif isinstance(ins, Delete):
             st.delete(ins)
         elif isinstance(ins, (AllReduce, AllGather)):
+            # a rank's contribution is read when *its* instruction is reached (it may be deleted right after)
             group = pending_collectives[ins.cid]
-            group.append(ins)
+            if isinstance(ins, AllReduce):
+                info = prog.values[ins.out]
+                group.append((ins, _local_sum(st, ins, info.shape, info.dtype)))
+            else:
+                group.append((ins, {p: st.env[v] for p, v in ins.local.items()}))
             if len(group) == len(ins.ranks):
-                _collective_single(prog, states, group)
+                _collective_single(states, group)
                 del pending_collectives[ins.cid]
         else:  # pragma: no cover
             raise NotImplementedError(type(ins))
@@ -182,23 +187,21 @@ def run_single_controller(prog: Program, inputs: Sequence[torch.Tensor | None], 
     return states, outs
 
 
-def _collective_single(prog: Program, states, group):
-    first = group[0]
-    info = prog.values[first.out]
+def _collective_single(states, group):
+    first = group[0][0]
     if isinstance(first, AllReduce):
+        home = states[first.ranks[0]].device
         total = None
-        for ins in sorted(group, key=lambda i: i.rank):
-            part = _local_sum(states[ins.rank], ins, info.shape, info.dtype)
-            part = part.to(states[first.ranks[0]].device)
+        for ins, part in sorted(group, key=lambda g: g[0].rank):
+            part = part.to(home)
             total = part if total is None else total.add_(part)
-        for ins in group:
+        for ins, _ in group:
             states[ins.rank].env[ins.out] = total.to(states[ins.rank].device).clone() if len(group) > 1 else total
     else:
         parts: dict[int, torch.Tensor] = {}
-        for ins in group:
-            for p, v in ins.local.items():
-                parts[p] = states[ins.rank].env[v]
-        for ins in group:
+        for ins, local in group:
+            parts.update(local)
+        for ins, _ in group:
             dev = states[ins.rank].device
             states[ins.rank].env[ins.out] = torch.cat([parts[p].to(dev) for p in sorted(parts)], dim=ins.axis)
 

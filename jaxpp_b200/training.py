@@ -20,7 +20,15 @@ from torch.utils import _pytree as pytree
 from .primitives import OP_ADD, OP_CONCAT, OP_MAX, current_trace
 from .schedules import BaseSchedule
 
-__all__ = ["treduce", "treduce_i", "Add", "Max", "Concat", "AddT", "MaxT", "default_op"]
+__all__ = ["treduce", "treduce_i", "take", "Add", "Max", "Concat", "AddT", "MaxT", "default_op"]
+
+
+def take(x: torch.Tensor, i, axis: int = 0) -> torch.Tensor:
+    """``x`` sliced at index ``i`` along ``axis``; ``i`` may be a Python int or the 0-d index tensor
+    that :func:`treduce_i` passes to its body while a step is being captured."""
+    if isinstance(i, torch.Tensor):
+        return x.index_select(axis, i.reshape(1)).squeeze(axis)
+    return x.select(axis, i)
 
 
 @dataclasses.dataclass(frozen=True)

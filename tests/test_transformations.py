@@ -1,0 +1,235 @@
+"""Compiler equivalence: the scheduled multi-rank program, interpreted in one process, must give
+bit-identical results to the plain sequential step — for every schedule family."""
+import pytest
+import torch
+from torch.utils import _pytree as pytree
+
+import jaxpp_b200 as jp
+from jaxpp_b200.compiler.program import AllReduce, RunTask, Transfer
+from jaxpp_b200.compiler.verify import verify_program
+from jaxpp_b200.ops import core as ops
+from jaxpp_b200.utils import config
+
+from helpers import assert_trees_equal, local, make_mlp_step, mlp_forward, mlp_params
+
+CASES = [
+    # (mpmd_dim, schedule, n_mubatches)
+    (2, jp.Std1F1B(2), 4),
+    (4, jp.Std1F1B(4), 8),
+    (3, jp.Eager1F1B(3), 5),
+    (2, jp.GPipe(2), 3),
+    (2, jp.Interleaved1F1B(4, 2), 4),
+    (4, jp.Interleaved1F1B(8, 4), 8),
+    (2, jp.Interleaved1F1B(4, 2, fuse_steady_state=True), 4),
+    (2, jp.KimiK2(4, 2), 4),
+    (4, jp.ZeroBubble(4), 6),
+    (2, jp.DualPipeV(4, 2), 4),
+    (4, jp.DualPipeV(8, 4), 10),
+]
+
+
+def cpu_mesh(pp):
+    return jp.MpmdMesh.create({"mpmd": pp, "data": 1, "model": 1}, kind="cpu", multi_process=False)
+
+
+@pytest.mark.parametrize("pp,schedule,n_mb", CASES, ids=lambda c: str(c).replace(" ", ""))
+def test_scheduled_program_is_bit_exact(pp, schedule, n_mb):
+    n_layers = schedule.num_stages
+    params = mlp_params(n_layers, 16)
+    batch = torch.randn(n_mb, 4, 16, generator=torch.Generator().manual_seed(1))
+    step = make_mlp_step(schedule.num_stages, schedule, n_mb)
+    ref = step(params, batch)
+    f = jp.mpmd_jit_with_loop(step, cpu_mesh(pp))
+    got = f(params, batch)
+    assert_trees_equal(ref, got, exact=True)
+    compiled = f.lower(params, batch)
+    verify_program(compiled.program)
+    # losses live on the rank of the last stage, each layer's params where its stage runs
+    assert got[0].mpmd_idxs == (schedule.get_mpmd_idx(schedule.num_stages - 1),)
+    for layer, p in enumerate(got[1]):
+        assert p["w1"].mpmd_idxs == (schedule.get_mpmd_idx(layer),)
+
+
+@pytest.mark.parametrize("pp,schedule,n_mb", [(8, jp.Interleaved1F1B(48, 8), 64), (8, jp.DualPipeV(16, 8), 18)],
+                         ids=["interleaved48x64", "dualpipev16x18"])
+def test_big_shapes_compile(pp, schedule, n_mb):
+    params = mlp_params(schedule.num_stages, 8)
+    batch = torch.randn(n_mb, 2, 8)
+    step = make_mlp_step(schedule.num_stages, schedule, n_mb)
+    compiled = jp.mpmd_jit_with_loop(step, cpu_mesh(pp)).lower(params, batch)
+    stats = compiled.program.stats()
+    assert stats["n_tasks"] > schedule.num_stages * n_mb
+    verify_program(compiled.program)
+    # structurally identical stages share executables
+    assert stats["n_executables"] < 64
+
+
+def test_fusion_flag_unpacks_fused_tasks():
+    sched = jp.Interleaved1F1B(4, 2)
+    params, batch = mlp_params(4, 8), torch.randn(4, 2, 8)
+    step = make_mlp_step(4, sched, 4)
+    fused = jp.mpmd_jit_with_loop(step, cpu_mesh(2)).lower(params, batch).program
+    assert any(i.name.startswith("fused_") for i in fused.instrs if isinstance(i, RunTask))
+    with config.disable_schedule_task_fusion.set(True):
+        plain = jp.mpmd_jit_with_loop(step, cpu_mesh(2)).lower(params, batch).program
+    assert not any(i.name.startswith("fused_") for i in plain.instrs if isinstance(i, RunTask))
+    assert sum(isinstance(i, RunTask) for i in plain.instrs) > sum(isinstance(i, RunTask) for i in fused.instrs)
+
+
+def test_zero_bubble_split_separates_weight_grads():
+    sched = jp.ZeroBubble(2)
+    params, batch = mlp_params(2, 8), torch.randn(2, 2, 8)
+    prog = jp.mpmd_jit_with_loop(make_mlp_step(2, sched, 2), cpu_mesh(2)).lower(params, batch).program
+    by_name = {i.name.split("__")[0]: i for i in prog.instrs if isinstance(i, RunTask)}
+    assert "bwdA_1" in by_name and "bwdW_1" in by_name and "bwdW_0" not in by_name
+    ops_of = lambda name: " ".join(str(t) for t in by_name[name].code.targets)
+    assert "linear_wgrad" in ops_of("bwdW_1") and "linear_wgrad" not in ops_of("bwdA_1")
+    assert "linear_dgrad" in ops_of("bwdA_1") and "linear_dgrad" not in ops_of("bwdW_1")
+
+
+def test_shared_weight_gradients_use_cross_rank_all_reduce():
+    """A weight used by the first and the last stage: each rank accumulates its own partial gradient
+    and the partials are summed once after the loop."""
+    sched = jp.Std1F1B(2)
+    n_mb = 4
+    g = torch.Generator().manual_seed(3)
+    params = {"emb": torch.randn(8, 8, generator=g) * 0.3, "mid": torch.randn(8, 8, generator=g) * 0.3}
+    batch = torch.randn(n_mb, 4, 8, generator=g)
+
+    def step(params, batch):
+        def body(mb):
+            def loss_fn(p):
+                x = ops.linear(mb, p["emb"], None)
+                x = jp.mark_stage_end(ops.gelu(x))
+                x = ops.linear(x, p["mid"], None)
+                x = ops.linear(x, p["emb"], None)  # tied weight on the last stage
+                x = jp.mark_stage_end(x)
+                return (x ** 2).mean() / n_mb
+
+            return jp.value_and_grad(loss_fn)(params)
+
+        loss, grads = jp.treduce(body, batch, schedule=sched)
+        return loss, pytree.tree_map(lambda p, gr: p - 0.5 * gr, params, grads)
+
+    ref = step(params, batch)
+    f = jp.mpmd_jit_with_loop(step, cpu_mesh(2))
+    got = f(params, batch)
+    prog = f.lower(params, batch).program
+    assert sum(isinstance(i, AllReduce) for i in prog.instrs) == 2  # one instruction per participant
+    # no weight-sized transfer inside the loop: only the [4, 8] activations and their gradients move
+    assert all(prog.values[v].shape == (4, 8) for i in prog.instrs if isinstance(i, Transfer) for v in i.vids)
+    assert got[1]["emb"].mpmd_idxs == (0, 1) and got[1]["mid"].mpmd_idxs == (1,)
+    assert_trees_equal(ref, got, exact=False, rtol=1e-6, atol=1e-7)
+    verify_program(prog)
+
+
+def test_after_loop_requires_explicit_collective():
+    sched = jp.Std1F1B(2)
+    params, batch = mlp_params(2, 8), torch.randn(2, 2, 8)
+
+    def step(params, batch):
+        loss, grads = make_inner(params, batch)
+        norm = sum((g ** 2).sum() for g in pytree.tree_leaves(grads))  # mixes ranks without a collective
+        return loss, norm
+
+    def make_inner(params, batch):
+        def body(mb):
+            def loss_fn(p):
+                return ((mlp_forward(p, mb, 2) - mb) ** 2).mean()
+
+            return jp.value_and_grad(loss_fn)(params)
+
+        return jp.treduce(body, batch, schedule=sched)
+
+    with pytest.raises(AssertionError, match="After loop computation is not replicateable"):
+        jp.mpmd_jit_with_loop(step, cpu_mesh(2)).lower(params, batch)
+
+    def step_ok(params, batch):
+        loss, grads = make_inner(params, batch)
+        per_stage = [sum((g ** 2).sum() for g in pytree.tree_leaves(layer)) for layer in grads]
+        norm = jp.cross_mpmd_all_reduce(*per_stage).sqrt()
+        stacked = jp.cross_mpmd_stack(per_stage)
+        return loss, norm, stacked
+
+    ref = step_ok(params, batch)
+    got = jp.mpmd_jit_with_loop(step_ok, cpu_mesh(2))(params, batch)
+    assert got[1].mpmd_idxs == (0, 1) and got[2].mpmd_idxs == (0, 1)
+    assert_trees_equal(ref, got, exact=False)
+
+
+def test_replicated_scalars_and_passthrough():
+    """Values with no placement constraint (a step counter) are computed on every rank; inputs
+    returned unchanged stay exact."""
+    sched = jp.Std1F1B(2)
+    params, batch = mlp_params(2, 8), torch.randn(2, 2, 8)
+    inner = make_mlp_step(2, sched, 2)
+
+    def step(params, batch, count, extra):
+        loss, new = inner(params, batch)
+        return loss, new, count + 1, extra
+
+    count, extra = torch.tensor(7), torch.arange(3.0)
+    out = jp.mpmd_jit_with_loop(step, cpu_mesh(2))(params, batch, count, extra)
+    assert out[2].mpmd_idxs == (0, 1) and int(out[2]) == 8
+    assert torch.equal(local(out[3]), extra)
+
+
+def test_forward_only_pipeline_by_yield():
+    params = mlp_params(4, 8)
+    x = torch.randn(3, 8)
+
+    def infer(params, x):
+        return mlp_forward(params, x, 4).sum(-1)
+
+    ref = infer(params, x)
+    f = jp.mpmd_jit_by_yield(infer, cpu_mesh(2))
+    got = f(params, x)
+    assert torch.equal(local(got), ref)
+    prog = f.lower(params, x).program
+    ranks = [i.rank for i in prog.instrs if isinstance(i, RunTask)]
+    assert ranks == [0, 1, 0, 1]  # stage s runs on rank s % mpmd_dim
+    verify_program(prog)
+
+
+def test_treduce_i_and_ops():
+    sched = jp.Std1F1B(2)
+    params = mlp_params(2, 8)
+    batch = torch.randn(3, 2, 8)
+
+    def step(params, batch):
+        def body(i):
+            mb = jp.take(batch, i)
+
+            def loss_fn(p):
+                out = mlp_forward(p, mb, 2)
+                return ((out - mb) ** 2).mean(), out.detach().abs().amax()
+
+            (loss, peak), grads = jp.value_and_grad(loss_fn, has_aux=True)(params)
+            return loss, grads, peak
+
+        return jp.treduce_i(body, 3, schedule=sched, operation=(jp.Concat(), jp.Add, jp.Max))
+
+    ref_body = step(params, batch)
+    got = jp.mpmd_jit_with_loop(step, cpu_mesh(2))(params, batch)
+    assert_trees_equal(ref_body, got, exact=False, rtol=1e-6, atol=1e-7)
+
+
+def test_schedule_stage_mismatch_is_reported():
+    params, batch = mlp_params(4, 8), torch.randn(2, 2, 8)
+    step = make_mlp_step(4, jp.Std1F1B(2), 2)  # 4 markers, schedule for 2 stages
+    with pytest.raises(AssertionError, match="marks 4 stages but the schedule was built for 2"):
+        jp.mpmd_jit_with_loop(step, cpu_mesh(2)).lower(params, batch)
+
+
+def test_in_shardings_and_dump(tmp_path):
+    sched = jp.Std1F1B(2)
+    params, batch = mlp_params(2, 8), torch.randn(2, 2, 8)
+    with config.dump_dir.set(str(tmp_path)):
+        f = jp.mpmd_jit_with_loop(make_mlp_step(2, sched, 2), cpu_mesh(2), name="toy")
+        compiled = f.lower(params, batch)
+    (args, kwargs) = compiled.in_shardings
+    assert args[0][0]["w1"].mesh_ids == frozenset({0}) and args[0][1]["w1"].mesh_ids == frozenset({1})
+    assert args[1].mesh_ids == frozenset({0, 1})  # the batch feeds stage 0 and the loss on stage 1
+    text = (tmp_path / "toy.global.0.program.txt").read_text()
+    assert "task fwd_0__0" in text and "transfer#" in text
+    assert "send#" in (tmp_path / "toy.local.0.rank0.program.txt").read_text()

@@ -1,0 +1,82 @@
+"""Flag classes and small utilities (behaviour of the reference's tests/test_utils.py)."""
+import logging
+import os
+
+import pytest
+
+from jaxpp_b200.utils import (BoolEnvVar, IntEnvVar, OverwriteableVar, StrEnvVar, format_bytes, groupby, hbytes,
+                              log_elapsed_time, parse_bool, partition, unzip_multi)
+
+
+def test_unzip_multi():
+    assert unzip_multi([(1, "a"), (2, "b")]) == [[1, 2], ["a", "b"]]
+    assert unzip_multi([], arity=3) == [[], [], []]
+    assert unzip_multi([(1, 2, 3)], arity=3) == [[1], [2], [3]]
+    with pytest.raises(AssertionError):
+        unzip_multi([(1, 2), (3,)])
+
+
+def test_groupby_partition():
+    assert groupby([("a", 1), ("b", 2), ("a", 3)]) == {"a": [1, 3], "b": [2]}
+    assert partition(lambda x: x % 2 == 0, range(5)) == ([0, 2, 4], [1, 3])
+
+
+def test_log_elapsed_time(caplog):
+    log = logging.getLogger("t")
+    with caplog.at_level(logging.INFO, logger="t"):
+        with log_elapsed_time("evt", msg="hello", log=log):
+            pass
+        with log_elapsed_time("evt2", unit="ms", log=log):
+            pass
+    assert "[evt] hello took" in caplog.text and caplog.text.count("ms") >= 1
+    with pytest.raises(ValueError, match="Unknown unit"):
+        with log_elapsed_time("evt", unit="h"):
+            pass
+
+
+def test_overwriteable_var():
+    v = OverwriteableVar(3)
+    assert v.value == 3
+    with v.set(5):
+        assert v.value == 5
+        with v.set(7):
+            assert v.value == 7
+        assert v.value == 5
+    assert v.value == 3
+    with pytest.raises(ValueError, match="truthy"):
+        bool(v)
+
+
+def test_parse_bool():
+    for s in ["true", "1", "T", "y", "YES"]:
+        assert parse_bool(s) is True
+    for s in ["false", "0", "F", "n", "No"]:
+        assert parse_bool(s) is False
+    assert parse_bool("maybe") is None
+
+
+def test_env_vars(monkeypatch):
+    monkeypatch.setenv("X_BOOL", "yes")
+    monkeypatch.setenv("X_INT", "12")
+    monkeypatch.setenv("X_STR", "abc")
+    monkeypatch.setenv("X_BAD", "twelve")
+    assert BoolEnvVar("X_BOOL", False).value is True
+    assert IntEnvVar("X_INT", 1).value == 12
+    assert StrEnvVar("X_STR", "").value == "abc"
+    assert BoolEnvVar("X_MISSING", True).value is True
+    with pytest.raises(ValueError, match="Unsupported value X_BAD=twelve"):
+        IntEnvVar("X_BAD", 0).value
+    # the environment is read once
+    v = IntEnvVar("X_INT", 1)
+    assert v.value == 12
+    monkeypatch.setenv("X_INT", "13")
+    assert v.value == 12
+    with v.set(99):
+        assert v.value == 99
+    assert v.value == 12
+
+
+def test_bytes():
+    assert format_bytes(512) == "512B"
+    assert format_bytes(2048) == "2.00KiB"
+    assert hbytes([1024 * 1024, 1024 * 1024]) == "2.00MiB"
