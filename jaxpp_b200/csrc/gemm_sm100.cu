@@ -1,0 +1,348 @@
+// bf16 GEMM for sm_100a: D[M,N] = A[M,K] * B[N,K]^T with fp32 accumulation in tensor memory.
+//
+// One persistent CTA per SM walks 128x256 output tiles.  Warp 0 streams operand tiles into a 4-stage
+// shared-memory ring with TMA (128-byte swizzle), warp 1 issues tcgen05.mma (128x256x16 per instruction)
+// into one of two 256-column TMEM accumulators, warps 2-5 drain the other accumulator with tcgen05.ld
+// and write the result (optionally + bias, optionally accumulated onto an existing fp32 D), so the
+// epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Either operand can be K-major (reduction dimension contiguous in memory) or MN-major (row/column
+// dimension contiguous), which covers the three GEMMs of a linear layer without a transpose pass:
+//   forward  y  = x  * w^T : A = x  (K-major),  B = w (K-major)
+//   dgrad    dx = dy * w   : A = dy (K-major),  B = w (MN-major)
+//   wgrad    dw = dy^T * x : A = dy (MN-major), B = x (MN-major)
+// Every wait is bounded; on a time-out the kernel records a status, drains its own TMA copies, frees its
+// tensor memory and returns.
+#include "common.cuh"
+
+#include <mutex>
+#include <unordered_map>
+
+namespace jpb {
+
+constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int TMEM_COLS = 512;
+
+struct GemmParams {
+  int M, N, K;
+  int ldd;             // elements between rows of D
+  int out_fp32;        // D is fp32 (else bf16)
+  int accumulate;      // D += result (D must be fp32)
+  int bias_fp32;
+  const void* bias;    // per-column bias or nullptr
+  void* D;
+  int* status;
+  int tiles_m, tiles_n;
+};
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // operand stages need 1024-byte alignment for the 128-byte swizzle pattern
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full = bars;                  // [STAGES] TMA -> MMA
+  uint64_t* empty = bars + STAGES;        // [STAGES] MMA -> TMA
+  uint64_t* acc_full = bars + 2 * STAGES;   // [2] MMA -> epilogue
+  uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2] epilogue -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int k_blocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer --------------------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      uint32_t armed = 0;       // bit s set <=> a copy into stage s may still be in flight
+      uint32_t armed_phase = 0; // bit s = barrier phase of the latest copy issued into stage s
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % p.tiles_m) * BM;
+        const int n0 = (tile / p.tiles_m) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait_bounded(&empty[s], ph ^ 1, abort_flag, p.status)) { ok = false; break; }
+          uint8_t* sa = smem + s * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          mbar_expect_tx(&full[s], STAGE_BYTES);
+          armed |= 1u << s;
+          armed_phase = (armed_phase & ~(1u << s)) | (ph << s);
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_2d(sa, &map_a, &full[s], k0, m0);                 // box {64 k, 128 rows}
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &map_a, &full[s], m0 + j * 64, k0);
+          }
+          if (!B_MN) {
+            tma_load_2d(sb, &map_b, &full[s], k0, n0);                 // box {64 k, 256 rows}
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &map_b, &full[s], n0 + j * 64, k0);
+          }
+        }
+      }
+      if (!ok) {
+        // drain: wait (bounded) until every copy this thread issued has landed, so that no TMA write is
+        // still in flight when the CTA's shared memory is released
+        const uint64_t t0 = globaltimer_ns();
+        for (int s = 0; s < STAGES; ++s) {
+          if (!(armed & (1u << s))) continue;
+          const uint32_t ph = (armed_phase >> s) & 1;
+          while (!mbar_try_wait(&full[s], ph) && globaltimer_ns() - t0 < JPB_WAIT_BUDGET_NS) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer --------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      uint32_t it = 0;
+      uint32_t tile_i = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
+        const uint32_t acc = tile_i & 1;
+        const uint32_t acc_ph = (tile_i >> 1) & 1;
+        if (!mbar_wait_bounded(&acc_empty[acc], acc_ph ^ 1, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait_bounded(&full[s], ph, abort_flag, p.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = A_MN ? make_smem_desc(sa + k * 2048, 8192, 1024) : make_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, 8192, 1024) : make_smem_desc(sb + k * 32, 16, 1024);
+            umma_bf16_ss(d_tmem, da, db, idesc, (kb | k) != 0);
+          }
+          umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
+        }
+        if (ok) umma_commit(&acc_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------- epilogue (warps 2..5) ------------------------------------------
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are visible to this warp
+    uint32_t tile_i = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
+      const int m0 = (tile % p.tiles_m) * BM;
+      const int n0 = (tile / p.tiles_m) * BN;
+      const uint32_t acc = tile_i & 1;
+      const uint32_t acc_ph = (tile_i >> 1) & 1;
+      if (!mbar_wait_bounded(&acc_full[acc], acc_ph, abort_flag, p.status)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN + c * 32, r);
+        tc_wait_ld();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (p.bias) {
+          if (p.bias_fp32) {
+            const float* b = static_cast<const float*>(p.bias) + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (col0 + j < p.N) v[j] += __ldg(b + j);
+          } else {
+            const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(p.bias) + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (col0 + j < p.N) v[j] += __bfloat162float(b[j]);
+          }
+        }
+        if (!row_ok) continue;
+        const bool full_chunk = col0 + 32 <= p.N;
+        if (p.out_fp32) {
+          float* d = static_cast<float*>(p.D) + size_t(row) * p.ldd + col0;
+          if (full_chunk && (p.ldd & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              if (p.accumulate) {
+                const float4 old = *reinterpret_cast<const float4*>(d + j);
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              *reinterpret_cast<float4*>(d + j) = o;
+            }
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) d[j] = p.accumulate ? d[j] + v[j] : v[j];
+          }
+        } else {
+          __nv_bfloat16* d = static_cast<__nv_bfloat16*>(p.D) + size_t(row) * p.ldd + col0;
+          if (full_chunk && (p.ldd & 7) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 o;
+              o.x = pack_bf16(v[j], v[j + 1]);
+              o.y = pack_bf16(v[j + 2], v[j + 3]);
+              o.z = pack_bf16(v[j + 4], v[j + 5]);
+              o.w = pack_bf16(v[j + 6], v[j + 7]);
+              *reinterpret_cast<uint4*>(d + j) = o;
+            }
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) d[j] = __float2bfloat16_rn(v[j]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+    }
+  }
+
+  // ------------------------------- teardown -------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// -------------------------------------------------------------------------------------------------------------
+// host side: tensor-map cache + launcher
+// -------------------------------------------------------------------------------------------------------------
+struct MapKey {
+  const void* base;
+  uint64_t d0, d1, stride;
+  uint32_t b0, b1;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && d0 == o.d0 && d1 == o.d1 && stride == o.stride && b0 == o.b0 && b1 == o.b1;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.base);
+    h = h * 1000003u ^ k.d0;
+    h = h * 1000003u ^ k.d1;
+    h = h * 1000003u ^ k.stride;
+    h = h * 1000003u ^ (size_t(k.b0) << 16 | k.b1);
+    return h;
+  }
+};
+
+static std::mutex g_map_mutex;
+static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
+
+// 2-D bf16 map over a row-major matrix with `rows` rows of `cols` contiguous elements.
+static int get_map_2d(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint64_t ld_elems,
+                      uint32_t box_cols, uint32_t box_rows) {
+  MapKey key{base, cols, rows, ld_elems, box_cols, box_rows};
+  {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    auto it = g_map_cache.find(key);
+    if (it != g_map_cache.end()) {
+      *out = it->second;
+      return 0;
+    }
+  }
+  uint64_t dims[2] = {cols, rows};
+  uint64_t strides[1] = {ld_elems * 2};
+  uint32_t box[2] = {box_cols, box_rows};
+  int rc = jpb_make_tensor_map(out, base, 2, 2, dims, strides, box, 1);
+  if (rc != 0) return rc;
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  if (g_map_cache.size() > 4096) g_map_cache.clear();
+  g_map_cache.emplace(key, *out);
+  return 0;
+}
+
+static int g_num_sms = 0;
+
+template <bool A_MN, bool B_MN>
+static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
+  auto kernel = gemm_bf16_kernel<A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return int(e);
+    configured = true;
+  }
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < g_num_sms ? tiles : g_num_sms;
+  kernel<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ma, mb, p);
+  return int(cudaGetLastError());
+}
+
+}  // namespace jpb
+
+// A: [M,K] with lda (K-major) or stored as [K,M] with lda (MN-major); likewise B for [N,K] / [K,N].
+// All leading dimensions in elements; bf16 operands must be 16-byte aligned with lda/ldb multiples of 8.
+JPB_API int jpb_gemm_bf16(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int lda, int ldb,
+                          int ldd, int a_mn_major, int b_mn_major, int out_fp32, int accumulate, int bias_fp32,
+                          void* stream) {
+  using namespace jpb;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
+    return -JPB_ERR_BAD_ARGUMENT;
+  if (accumulate && !out_fp32) return -JPB_ERR_BAD_ARGUMENT;
+  CUtensorMap ma, mb;
+  int rc;
+  if (!a_mn_major) rc = get_map_2d(&ma, A, K, M, lda, BK, BM);
+  else rc = get_map_2d(&ma, A, M, K, lda, 64, BK);
+  if (rc) return rc;
+  if (!b_mn_major) rc = get_map_2d(&mb, B, K, N, ldb, BK, BN);
+  else rc = get_map_2d(&mb, B, N, K, ldb, 64, BK);
+  if (rc) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.out_fp32 = out_fp32; p.accumulate = accumulate;
+  p.bias = bias; p.bias_fp32 = bias_fp32; p.D = D; p.status = jpb_status_device_ptr();
+  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (!a_mn_major && !b_mn_major) return launch<false, false>(ma, mb, p, s);
+  if (!a_mn_major && b_mn_major) return launch<false, true>(ma, mb, p, s);
+  if (a_mn_major && b_mn_major) return launch<true, true>(ma, mb, p, s);
+  return launch<true, false>(ma, mb, p, s);
+}

@@ -1,0 +1,314 @@
+"""ctypes bindings for the native sm_100a library (``jaxpp_b200/_native/libjaxpp_b200.so``).
+
+Every function here takes and returns ``torch`` CUDA tensors, allocates outputs through torch's
+caching allocator and launches on the *current* CUDA stream.  ``load()`` raises if the library is
+missing: on a GPU machine the ops never silently fall back to a library or eager implementation.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+
+_LIB: ctypes.CDLL | None = None
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(os.path.dirname(_HERE), "_native", "libjaxpp_b200.so")
+
+_c_int, _c_ll, _c_f, _c_p = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
+
+
+def load() -> ctypes.CDLL:
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"native kernel library not found at {LIB_PATH}; build it with `python -m jaxpp_b200.csrc.build` "
+            "(or __graft_entry__.build())"
+        )
+    lib = ctypes.CDLL(LIB_PATH)
+    lib.jpb_gemm_bf16.argtypes = [_c_p, _c_p, _c_p, _c_p] + [_c_int] * 11 + [_c_p]
+    lib.jpb_norm_fwd.argtypes = [_c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_f, _c_p]
+    lib.jpb_norm_bwd.argtypes = [_c_int, _c_int] + [_c_p] * 9 + [_c_int, _c_int, _c_p]
+    lib.jpb_norm_bwd_scratch_elems.argtypes = [_c_int, _c_int]
+    lib.jpb_norm_bwd_scratch_elems.restype = _c_ll
+    lib.jpb_colsum_scratch_elems.argtypes = [_c_int, _c_int]
+    lib.jpb_colsum_scratch_elems.restype = _c_ll
+    lib.jpb_colsum.argtypes = [_c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p]
+    lib.jpb_gelu.argtypes = [_c_int, _c_int, _c_p, _c_p, _c_p, _c_ll, _c_p]
+    lib.jpb_swiglu.argtypes = [_c_int, _c_int, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_p]
+    lib.jpb_rope.argtypes = [_c_int, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p]
+    lib.jpb_embedding_fwd.argtypes = [_c_int, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_p]
+    lib.jpb_embedding_bwd.argtypes = [_c_int, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_p]
+    lib.jpb_ce_fwd.argtypes = [_c_int, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p]
+    lib.jpb_ce_bwd.argtypes = [_c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p]
+    lib.jpb_adamw.argtypes = [_c_int, _c_int] + [_c_p] * 9 + [_c_ll] + [_c_f] * 6 + [_c_p]
+    lib.jpb_read_status.argtypes = [_c_int]
+    lib.jpb_build_info.restype = ctypes.c_char_p
+    for name in ("jpb_attention_fwd", "jpb_attention_bwd"):
+        if hasattr(lib, name):
+            getattr(lib, name).restype = _c_int
+    _LIB = lib
+    return lib
+
+
+def is_available() -> bool:
+    return os.path.exists(LIB_PATH)
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        raise NativeError(f"{what} failed with code {rc}")
+
+
+def read_status(clear: bool = True) -> int:
+    """Status word of the current device: non-zero after a kernel gave up on a bounded wait (1), rejected an
+    argument (2) or timed out waiting for a peer GPU (3).  Synchronise the stream first."""
+    return load().jpb_read_status(1 if clear else 0)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise NativeError(f"native kernels support float32 and bfloat16, got {t.dtype}")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _rows(t: torch.Tensor) -> int:
+    return t.numel() // t.shape[-1]
+
+
+# ---- GEMM ---------------------------------------------------------------------------------------------
+def _as_2d_bf16(t: torch.Tensor) -> torch.Tensor:
+    t2 = t.reshape(-1, t.shape[-1])
+    if t2.dtype != torch.bfloat16:
+        raise NativeError(f"the tcgen05 GEMM takes bfloat16 operands, got {t2.dtype}")
+    if t2.stride(-1) != 1 or (t2.stride(0) % 8) or (t2.data_ptr() % 16):
+        t2 = t2.contiguous()
+    return t2
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, M: int, N: int, K: int, a_mn: bool, b_mn: bool, out: torch.Tensor,
+         bias: Optional[torch.Tensor] = None, accumulate: bool = False):
+    """``out[M,N] (+)= A * B^T``.  ``a`` is [M,K] (or [K,M] when ``a_mn``), ``b`` is [N,K] (or [K,N] when ``b_mn``)."""
+    lib = load()
+    rc = lib.jpb_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), _p(bias), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+        int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate),
+        int(bias is not None and bias.dtype == torch.float32), _stream(),
+    )
+    _check(rc, "jpb_gemm_bf16")
+    return out
+
+
+def linear(x, w, bias):
+    x2 = _as_2d_bf16(x)
+    w2 = _as_2d_bf16(w)
+    M, K = x2.shape
+    N = w2.shape[0]
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    gemm(x2, w2, M, N, K, False, False, out, bias.contiguous() if bias is not None else None)
+    return out.view(*x.shape[:-1], N)
+
+
+def linear_dgrad(dy, w):
+    dy2 = _as_2d_bf16(dy)
+    w2 = _as_2d_bf16(w)  # [N_out, K_in]: reduction over N_out, so w is the MN-major B operand
+    M, Nred = dy2.shape
+    Kout = w2.shape[1]
+    out = torch.empty(M, Kout, dtype=torch.bfloat16, device=dy.device)
+    gemm(dy2, w2, M, Kout, Nred, False, True, out)
+    return out.view(*dy.shape[:-1], Kout)
+
+
+def linear_wgrad(dy, x, out: Optional[torch.Tensor] = None, accumulate: bool = False):
+    dy2 = _as_2d_bf16(dy)
+    x2 = _as_2d_bf16(x)
+    tokens, Nout = dy2.shape
+    Kin = x2.shape[1]
+    if out is None:
+        out = torch.empty(Nout, Kin, dtype=torch.bfloat16, device=dy.device)
+    gemm(dy2, x2, Nout, Kin, tokens, True, True, out, accumulate=accumulate)
+    return out
+
+
+# ---- norms ----------------------------------------------------------------------------------------------
+def rmsnorm(x, w, eps):
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    rstd = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+    _check(load().jpb_norm_fwd(0, _dt(x), x.data_ptr(), w.contiguous().data_ptr(), None, y.data_ptr(), None,
+                               rstd.data_ptr(), _rows(x), x.shape[-1], float(eps), _stream()), "rmsnorm")
+    return y, rstd
+
+
+def norm_bwd_scratch(rows: int, H: int, device) -> torch.Tensor:
+    n = load().jpb_norm_bwd_scratch_elems(rows, H)
+    return torch.empty(n, dtype=torch.float32, device=device)
+
+
+def rmsnorm_bwd(dy, x, w, rstd):
+    dy, x, w = dy.contiguous(), x.contiguous(), w.contiguous()
+    dx, dw = torch.empty_like(x), torch.empty_like(w)
+    rows, H = _rows(x), x.shape[-1]
+    scratch = norm_bwd_scratch(rows, H, x.device)
+    _check(load().jpb_norm_bwd(0, _dt(x), dy.data_ptr(), x.data_ptr(), w.data_ptr(), None, rstd.data_ptr(), dx.data_ptr(),
+                               dw.data_ptr(), None, scratch.data_ptr(), rows, H, _stream()), "rmsnorm_bwd")
+    return dx, dw
+
+
+def layernorm(x, w, b, eps):
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    mean = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+    rstd = torch.empty_like(mean)
+    _check(load().jpb_norm_fwd(1, _dt(x), x.data_ptr(), w.contiguous().data_ptr(), b.contiguous().data_ptr(), y.data_ptr(),
+                               mean.data_ptr(), rstd.data_ptr(), _rows(x), x.shape[-1], float(eps), _stream()), "layernorm")
+    return y, mean, rstd
+
+
+def layernorm_bwd(dy, x, w, mean, rstd):
+    dy, x, w = dy.contiguous(), x.contiguous(), w.contiguous()
+    dx, dw, db = torch.empty_like(x), torch.empty_like(w), torch.empty_like(w)
+    rows, H = _rows(x), x.shape[-1]
+    scratch = norm_bwd_scratch(rows, H, x.device)
+    _check(load().jpb_norm_bwd(1, _dt(x), dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+                               dx.data_ptr(), dw.data_ptr(), db.data_ptr(), scratch.data_ptr(), rows, H, _stream()),
+           "layernorm_bwd")
+    return dx, dw, db
+
+
+def colsum(dy):
+    dy = dy.contiguous()
+    rows, cols = _rows(dy), dy.shape[-1]
+    out = torch.empty(cols, dtype=dy.dtype, device=dy.device)
+    scratch = torch.empty(load().jpb_colsum_scratch_elems(rows, cols), dtype=torch.float32, device=dy.device)
+    _check(load().jpb_colsum(_dt(dy), dy.data_ptr(), out.data_ptr(), scratch.data_ptr(), rows, cols, _stream()), "colsum")
+    return out
+
+
+# ---- activations ---------------------------------------------------------------------------------------
+def gelu(x):
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    _check(load().jpb_gelu(_dt(x), 0, x.data_ptr(), None, out.data_ptr(), x.numel(), _stream()), "gelu")
+    return out
+
+
+def gelu_bwd(dy, x):
+    x, dy = x.contiguous(), dy.contiguous()
+    out = torch.empty_like(x)
+    _check(load().jpb_gelu(_dt(x), 1, x.data_ptr(), dy.data_ptr(), out.data_ptr(), x.numel(), _stream()), "gelu_bwd")
+    return out
+
+
+def swiglu(gu):
+    gu = gu.contiguous()
+    F = gu.shape[-1] // 2
+    out = torch.empty(*gu.shape[:-1], F, dtype=gu.dtype, device=gu.device)
+    _check(load().jpb_swiglu(_dt(gu), 0, gu.data_ptr(), None, out.data_ptr(), _rows(gu), F, _stream()), "swiglu")
+    return out
+
+
+def swiglu_bwd(dy, gu):
+    gu, dy = gu.contiguous(), dy.contiguous()
+    F = gu.shape[-1] // 2
+    out = torch.empty_like(gu)
+    _check(load().jpb_swiglu(_dt(gu), 1, gu.data_ptr(), dy.data_ptr(), out.data_ptr(), _rows(gu), F, _stream()), "swiglu_bwd")
+    return out
+
+
+def rope(x, cos, sin, inverse):
+    x = x.contiguous()
+    B, S, H, D = x.shape
+    out = torch.empty_like(x)
+    _check(load().jpb_rope(_dt(x), x.data_ptr(), cos.contiguous().data_ptr(), sin.contiguous().data_ptr(), out.data_ptr(),
+                           B * S * H, S, H, D, int(inverse), _stream()), "rope")
+    return out
+
+
+# ---- embedding / loss / optimizer --------------------------------------------------------------------------
+def embedding(ids, table):
+    ids = ids.contiguous()
+    table = table.contiguous()
+    out = torch.empty(*ids.shape, table.shape[1], dtype=table.dtype, device=table.device)
+    _check(load().jpb_embedding_fwd(_dt(table), ids.data_ptr(), table.data_ptr(), out.data_ptr(), ids.numel(),
+                                    table.shape[1], table.shape[0], _stream()), "embedding")
+    return out
+
+
+def embedding_bwd(dy, ids, vocab):
+    dy, ids = dy.contiguous(), ids.contiguous()
+    d = dy.shape[-1]
+    acc = torch.empty(vocab, d, dtype=torch.float32, device=dy.device)
+    if dy.dtype == torch.float32:
+        _check(load().jpb_embedding_bwd(0, dy.data_ptr(), ids.data_ptr(), acc.data_ptr(), None, ids.numel(), d, vocab,
+                                        _stream()), "embedding_bwd")
+        return acc
+    out = torch.empty(vocab, d, dtype=dy.dtype, device=dy.device)
+    _check(load().jpb_embedding_bwd(_dt(dy), dy.data_ptr(), ids.data_ptr(), acc.data_ptr(), out.data_ptr(), ids.numel(), d,
+                                    vocab, _stream()), "embedding_bwd")
+    return out
+
+
+def cross_entropy(logits, labels):
+    logits, labels = logits.contiguous(), labels.contiguous()
+    rows, V = _rows(logits), logits.shape[-1]
+    loss = torch.empty(logits.shape[:-1], dtype=torch.float32, device=logits.device)
+    lse = torch.empty_like(loss)
+    _check(load().jpb_ce_fwd(_dt(logits), logits.data_ptr(), labels.data_ptr(), loss.data_ptr(), lse.data_ptr(), rows, V,
+                             _stream()), "cross_entropy")
+    return loss, lse
+
+
+def cross_entropy_bwd(dloss, logits, labels, lse):
+    logits, labels = logits.contiguous(), labels.contiguous()
+    dloss = dloss.contiguous().float()
+    rows, V = _rows(logits), logits.shape[-1]
+    out = torch.empty_like(logits)
+    _check(load().jpb_ce_bwd(_dt(logits), dloss.data_ptr(), logits.data_ptr(), labels.data_ptr(), lse.contiguous().data_ptr(),
+                             out.data_ptr(), rows, V, _stream()), "cross_entropy_bwd")
+    return out
+
+
+def adamw(master, grad, m, v, step, lr, beta1, beta2, eps, weight_decay, grad_scale, out_dtype):
+    master, grad, m, v = master.contiguous(), grad.contiguous(), m.contiguous(), v.contiguous()
+    p2, m2, v2 = torch.empty_like(master), torch.empty_like(m), torch.empty_like(v)
+    lp = torch.empty(master.shape, dtype=out_dtype, device=master.device)
+    step = step.to(device=master.device, dtype=torch.int64)
+    out_code = 0 if out_dtype == torch.float32 else 1
+    if out_dtype not in (torch.float32, torch.bfloat16):
+        raise NativeError(f"adamw low-precision copy must be float32 or bfloat16, got {out_dtype}")
+    _check(load().jpb_adamw(_dt(grad), out_code, master.data_ptr(), grad.data_ptr(), m.data_ptr(), v.data_ptr(),
+                            step.data_ptr(), p2.data_ptr(), m2.data_ptr(), v2.data_ptr(), lp.data_ptr(), master.numel(),
+                            float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), float(grad_scale),
+                            _stream()), "adamw")
+    return p2, m2, v2, lp
+
+
+# ---- attention: bound in attention.py once the kernel library provides it ----------------------------------
+def attention(q, k, v, causal, scale):
+    from . import attention as att
+
+    return att.attention_fwd(q, k, v, causal, scale)
+
+
+def attention_bwd(do, q, k, v, o, lse, causal, scale):
+    from . import attention as att
+
+    return att.attention_bwd(do, q, k, v, o, lse, causal, scale)

@@ -1,0 +1,166 @@
+"""Numerics of every native sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def native():
+    from jaxpp_b200.ops import native as n
+
+    n.load()  # fails loudly if the library was not built
+    yield n
+    torch.cuda.synchronize()
+    assert n.read_status() == 0, "a kernel reported a bounded-wait time-out or a bad argument"
+
+
+def rnd(*shape, dtype=torch.bfloat16, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g, device="cuda", dtype=torch.float32) * scale).to(dtype)
+
+
+def close(got, ref, rtol, atol):
+    torch.testing.assert_close(got.float(), ref.float(), rtol=rtol, atol=atol)
+
+
+GEMM_SHAPES = [
+    (128, 256, 64), (256, 512, 128), (384, 768, 192), (130, 264, 72),  # ragged M/N/K tails
+    (1024, 1600, 6400), (512, 11008, 4096), (2048, 4096, 5504), (64, 8, 8),
+]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_forward_layout(native, M, N, K):
+    x, w = rnd(M, K, scale=0.5), rnd(N, K, scale=0.5, seed=1)
+    bias = rnd(N, seed=2)
+    got = native.linear(x, w, bias)
+    ref = x.float() @ w.float().t() + bias.float()
+    close(got, ref, rtol=2e-2, atol=2e-2 * (K ** 0.5) * 0.25)
+    torch.cuda.synchronize()
+    assert native.read_status(clear=False) == 0
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES[:6])
+def test_gemm_dgrad_layout(native, M, N, K):
+    dy, w = rnd(M, N, scale=0.5), rnd(N, K, scale=0.5, seed=1)
+    got = native.linear_dgrad(dy, w)
+    ref = dy.float() @ w.float()
+    close(got, ref, rtol=2e-2, atol=2e-2 * (N ** 0.5) * 0.25)
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES[:6])
+def test_gemm_wgrad_layout_and_accumulate(native, M, N, K):
+    dy, x = rnd(M, N, scale=0.5), rnd(M, K, scale=0.5, seed=1)
+    got = native.linear_wgrad(dy, x)
+    ref = dy.float().t() @ x.float()
+    close(got, ref, rtol=2e-2, atol=2e-2 * (M ** 0.5) * 0.25)
+    acc = torch.ones(N, K, dtype=torch.float32, device="cuda")
+    native.linear_wgrad(dy, x, out=acc, accumulate=True)
+    native.linear_wgrad(dy, x, out=acc, accumulate=True)
+    close(acc, 1.0 + 2.0 * ref, rtol=2e-2, atol=4e-2 * (M ** 0.5) * 0.25)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,H", [(37, 256), (128, 1600), (64, 4096), (16, 8192)])
+def test_norms(native, dtype, rows, H):
+    from jaxpp_b200.ops import core as ops
+
+    tol = dict(rtol=1e-4, atol=1e-4) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    x, w, b, dy = rnd(rows, H, dtype=dtype), rnd(H, dtype=dtype, seed=1), rnd(H, dtype=dtype, seed=2), rnd(rows, H, dtype=dtype, seed=3)
+    y, rstd = native.rmsnorm(x, w, 1e-5)
+    ry, rr = ops._rmsnorm_ref(x.float(), w.float(), 1e-5)
+    close(y, ry, **tol)
+    close(rstd, rr, rtol=1e-4, atol=1e-4)
+    dx, dw = native.rmsnorm_bwd(dy, x, w, rstd)
+    rdx, rdw = ops._rmsnorm_bwd_ref(dy.float(), x.float(), w.float(), rr)
+    close(dx, rdx, **tol)
+    close(dw, rdw, rtol=tol["rtol"], atol=tol["atol"] * rows ** 0.5)
+    y, mean, rstd = native.layernorm(x, w, b, 1e-5)
+    ry, rm, rr = ops._layernorm_ref(x.float(), w.float(), b.float(), 1e-5)
+    close(y, ry, **tol)
+    close(mean, rm, rtol=1e-4, atol=1e-4)
+    dx, dw, db = native.layernorm_bwd(dy, x, w, mean, rstd)
+    rdx, rdw, rdb = ops._layernorm_bwd_ref(dy.float(), x.float(), w.float(), rm, rr)
+    close(dx, rdx, **tol)
+    close(dw, rdw, rtol=tol["rtol"], atol=tol["atol"] * rows ** 0.5)
+    close(db, rdb, rtol=tol["rtol"], atol=tol["atol"] * rows ** 0.5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_activations_rope_colsum(native, dtype):
+    from jaxpp_b200.ops import core as ops
+
+    tol = dict(rtol=1e-4, atol=1e-4) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    x, dy = rnd(33, 1024, dtype=dtype), rnd(33, 1024, dtype=dtype, seed=1)
+    close(native.gelu(x), ops._gelu_ref(x.float()), **tol)
+    close(native.gelu_bwd(dy, x), ops._gelu_bwd_ref(dy.float(), x.float()), **tol)
+    gu, d2 = rnd(33, 2048, dtype=dtype, seed=2), rnd(33, 1024, dtype=dtype, seed=3)
+    close(native.swiglu(gu), ops._swiglu_ref(gu.float()), **tol)
+    close(native.swiglu_bwd(d2, gu), ops._swiglu_bwd_ref(d2.float(), gu.float()), **tol)
+    close(native.colsum(x), x.float().sum(0), rtol=tol["rtol"], atol=tol["atol"] * 6)
+    q = rnd(2, 16, 4, 128, dtype=dtype, seed=4)
+    ang = torch.rand(16, 64, device="cuda") * 6.28
+    cos, sin = ang.cos(), ang.sin()
+    r = native.rope(q, cos, sin, False)
+    close(r, ops._rope_ref(q.float(), cos, sin, False), **tol)
+    close(native.rope(r, cos, sin, True), q, rtol=tol["rtol"] * 2, atol=tol["atol"] * 2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding_and_cross_entropy(native, dtype):
+    from jaxpp_b200.ops import core as ops
+
+    tol = dict(rtol=1e-4, atol=1e-4) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    vocab, d = 1000, 256
+    table = rnd(vocab, d, dtype=dtype)
+    ids = torch.randint(0, vocab, (4, 77), device="cuda")
+    assert torch.equal(native.embedding(ids, table), table[ids])
+    dy = rnd(4, 77, d, dtype=dtype, seed=1)
+    close(native.embedding_bwd(dy, ids, vocab), ops._emb_bwd_ref(dy.float(), ids, vocab), **tol)
+    for V in (32000, 50257, 1000):
+        logits = rnd(19, V, dtype=dtype, scale=3.0, seed=2)
+        labels = torch.randint(0, V, (19,), device="cuda")
+        loss, lse = native.cross_entropy(logits, labels)
+        rl, rlse = ops._ce_ref(logits.float(), labels)
+        close(loss, rl, rtol=1e-4, atol=1e-3)
+        close(lse, rlse, rtol=1e-4, atol=1e-3)
+        dl = torch.rand(19, device="cuda")
+        got = native.cross_entropy_bwd(dl, logits, labels, lse)
+        close(got, ops._ce_bwd_ref(dl, logits.float(), labels, rlse), rtol=tol["rtol"], atol=1e-3)
+
+
+@pytest.mark.parametrize("gdtype", [torch.float32, torch.bfloat16])
+def test_adamw(native, gdtype):
+    from jaxpp_b200.ops import core as ops
+
+    n = 100003
+    p, g = rnd(n, dtype=torch.float32), rnd(n, dtype=gdtype, seed=1)
+    m, v = rnd(n, dtype=torch.float32, scale=0.1, seed=2), rnd(n, dtype=torch.float32, scale=0.1, seed=3).abs()
+    step = torch.tensor(3, device="cuda")
+    args = (1e-3, 0.9, 0.95, 1e-8, 0.1, 0.5)
+    got = native.adamw(p, g, m, v, step, *args, torch.bfloat16)
+    ref = ops._adamw_ref(p, g, m, v, step, *args, torch.bfloat16)
+    for a, b in zip(got[:3], ref[:3]):
+        close(a, b, rtol=1e-5, atol=1e-6)
+    close(got[3], ref[3], rtol=1e-2, atol=1e-2)
+
+
+def test_ops_dispatch_to_native_and_autograd(native):
+    """The b200:: ops route CUDA tensors to the native kernels and differentiate through them."""
+    from jaxpp_b200.ops import core as ops
+
+    x = rnd(256, 512).requires_grad_()
+    w = rnd(1024, 512, scale=0.05, seed=1).requires_grad_()
+    g = rnd(512, seed=2).requires_grad_()
+    h = ops.rmsnorm(x, g, 1e-5)[0]
+    y = ops.swiglu(ops.linear(h, w, None))
+    y.float().pow(2).mean().backward()
+    xr, wr, gr = (t.detach().float().requires_grad_() for t in (x, w, g))
+    hr = ops._rmsnorm_ref(xr, gr, 1e-5)[0]
+    yr = ops._swiglu_ref(hr @ wr.t())
+    yr.pow(2).mean().backward()
+    close(y, yr, rtol=3e-2, atol=3e-2)
+    close(x.grad, xr.grad, rtol=5e-2, atol=2e-3)
+    close(w.grad, wr.grad, rtol=5e-2, atol=2e-3)
+    close(g.grad, gr.grad, rtol=5e-2, atol=5e-3)
