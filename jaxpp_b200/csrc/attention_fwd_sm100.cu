@@ -1,0 +1,335 @@
+// Flash attention forward for sm_100a (causal or full, MHA/GQA, head_dim 64 or 128, bf16 in/out).
+//
+// One CTA handles 128 query rows of one (batch, head).  Warp 0 streams Q once and K/V blocks of 128 rows
+// through a 2-stage shared-memory ring with TMA; warp 1 issues tcgen05.mma: S = Q K^T into one of two
+// 128-column TMEM buffers (so S of block j+1 is computed while block j is in softmax) and O += P V into a
+// third TMEM region; warps 2-5 own one query row per thread: they read S from TMEM, keep the running
+// (max, sum), write P as bf16 into shared memory in the swizzled K-major layout the tensor core reads,
+// rescale O in TMEM only when some row's maximum moved, and finally normalise and store O and the
+// log-sum-exp.  All waits are bounded and report through the status word.
+#include "common.cuh"
+
+namespace jpb {
+
+constexpr int ATT_BM = 128;   // query rows per CTA
+constexpr int ATT_BN = 128;   // kv rows per block
+constexpr int ATT_THREADS = 192;
+
+struct AttnParams {
+  int B, Sq, Sk, H, Hkv;
+  int causal;
+  float scale;
+  __nv_bfloat16* o;   // [B, Sq, H, D]
+  float* lse;         // [B, H, Sq]
+  int* status;
+};
+
+template <int D>
+struct AttnSmem {
+  static constexpr int TILE = 128 * 64 * 2;           // one [128 rows x 64 elements] swizzled block, 16 KiB
+  static constexpr int DB = D / 64;                   // 64-element blocks along head_dim
+  static constexpr int Q_BYTES = DB * TILE;
+  static constexpr int KV_BYTES = DB * TILE;
+  static constexpr int P_BYTES = 2 * TILE;            // [128 x 128] bf16
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + Q_BYTES;       // 2 stages
+  static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;  // 2 stages
+  static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
+  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+};
+
+enum { BAR_Q = 0, BAR_KF = 1, BAR_VF = 3, BAR_KE = 5, BAR_VE = 7, BAR_SF = 9, BAR_SE = 11, BAR_PF = 13, BAR_PV = 14, BAR_N = 15 };
+
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+  using L = AttnSmem<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bar = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + BAR_N);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_m = (p.Sq + ATT_BM - 1) / ATT_BM;
+  const int m_blk = num_m - 1 - blockIdx.x;  // heaviest (latest) causal tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.H / p.Hkv);
+  const int m0 = m_blk * ATT_BM;
+  int n_blocks = (p.Sk + ATT_BN - 1) / ATT_BN;
+  if (p.causal) {
+    const int last = (m0 + ATT_BM - 1 + (p.Sk - p.Sq)) / ATT_BN + 1;
+    n_blocks = last < n_blocks ? last : n_blocks;
+    if (n_blocks < 1) n_blocks = 1;
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar[BAR_Q], 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bar[BAR_KF + s], 1);
+      mbar_init(&bar[BAR_VF + s], 1);
+      mbar_init(&bar[BAR_KE + s], 1);
+      mbar_init(&bar[BAR_VE + s], 1);
+      mbar_init(&bar[BAR_SF + s], 1);
+      mbar_init(&bar[BAR_SE + s], 4);
+    }
+    mbar_init(&bar[BAR_PF], 4);
+    mbar_init(&bar[BAR_PV], 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_o = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------- TMA producer -------------------------------------------
+      uint32_t armed = 0, armed_phase = 0;  // indexed by barrier id, for draining after an abort
+      auto arm = [&](int id, uint32_t ph, uint32_t bytes) {
+        mbar_expect_tx(&bar[id], bytes);
+        armed |= 1u << id;
+        armed_phase = (armed_phase & ~(1u << id)) | (ph << id);
+      };
+      arm(BAR_Q, 0, L::Q_BYTES);
+#pragma unroll
+      for (int d = 0; d < L::DB; ++d) tma_load_4d(smem + L::OFF_Q + d * L::TILE, &map_q, &bar[BAR_Q], d * 64, h, m0, b);
+      bool ok = true;
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait_bounded(&bar[BAR_KE + s], ph ^ 1, abort_flag, p.status)) { ok = false; break; }
+        arm(BAR_KF + s, ph, L::KV_BYTES);
+#pragma unroll
+        for (int d = 0; d < L::DB; ++d)
+          tma_load_4d(smem + L::OFF_K + s * L::KV_BYTES + d * L::TILE, &map_k, &bar[BAR_KF + s], d * 64, hk, j * ATT_BN, b);
+        if (!mbar_wait_bounded(&bar[BAR_VE + s], ph ^ 1, abort_flag, p.status)) { ok = false; break; }
+        arm(BAR_VF + s, ph, L::KV_BYTES);
+#pragma unroll
+        for (int d = 0; d < L::DB; ++d)
+          tma_load_4d(smem + L::OFF_V + s * L::KV_BYTES + d * L::TILE, &map_v, &bar[BAR_VF + s], d * 64, hk, j * ATT_BN, b);
+      }
+      if (!ok) {
+        const uint64_t t0 = globaltimer_ns();
+        for (int id = 0; id < BAR_KE; ++id) {
+          if (!(armed & (1u << id))) continue;
+          while (!mbar_try_wait(&bar[id], (armed_phase >> id) & 1) && globaltimer_ns() - t0 < JPB_WAIT_BUDGET_NS) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------------- MMA issuer ------------------------------------------------
+      constexpr uint32_t idesc_s = make_idesc_bf16(ATT_BM, ATT_BN, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(ATT_BM, D, 0, 1);
+      const uint32_t sq = smem_u32(smem + L::OFF_Q);
+      const uint32_t sp = smem_u32(smem + L::OFF_P);
+      bool ok = mbar_wait_bounded(&bar[BAR_Q], 0, abort_flag, p.status);
+      auto issue_s = [&](int j) -> bool {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait_bounded(&bar[BAR_KF + s], ph, abort_flag, p.status)) return false;
+        if (!mbar_wait_bounded(&bar[BAR_SE + s], ph ^ 1, abort_flag, p.status)) return false;
+        tc_fence_after();
+        const uint32_t sk = smem_u32(smem + L::OFF_K + s * L::KV_BYTES);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * L::TILE + (k & 3) * 32;
+          umma_bf16_ss(tmem_base + s * ATT_BN, make_smem_desc(sq + off, 16, 1024), make_smem_desc(sk + off, 16, 1024),
+                       idesc_s, k != 0);
+        }
+        umma_commit(&bar[BAR_KE + s]);
+        umma_commit(&bar[BAR_SF + s]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        if (j + 1 < n_blocks && !issue_s(j + 1)) { ok = false; break; }
+        const int s = j & 1;
+        if (!mbar_wait_bounded(&bar[BAR_PF], j & 1, abort_flag, p.status)) { ok = false; break; }
+        if (!mbar_wait_bounded(&bar[BAR_VF + s], (j >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sv = smem_u32(smem + L::OFF_V + s * L::KV_BYTES);
+#pragma unroll
+        for (int k = 0; k < ATT_BN / 16; ++k) {
+          // A = P: K-major, two 64-wide kv blocks; B = V: MN-major, 16 kv rows per step, 64-wide d blocks
+          const uint64_t da = make_smem_desc(sp + (k >> 2) * L::TILE + (k & 3) * 32, 16, 1024);
+          const uint64_t db = make_smem_desc(sv + k * 2048, L::TILE, 1024);
+          umma_bf16_ss(tmem_o, da, db, idesc_pv, (j | k) != 0);
+        }
+        umma_commit(&bar[BAR_VE + s]);
+        umma_commit(&bar[BAR_PV]);
+      }
+    }
+  } else {
+    // ------------------------------------- softmax / correction / epilogue -----------------------------
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;          // row within the tile == TMEM lane
+    const int qi = m0 + r;                      // query index
+    const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
+    const float sl2 = p.scale * 1.4426950408889634f;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    uint8_t* sp = smem + L::OFF_P;
+    for (int j = 0; j < n_blocks && ok; ++j) {
+      const int s = j & 1;
+      if (!mbar_wait_bounded_warp(&bar[BAR_SF + s], (j >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+      tc_fence_after();
+      float sv[ATT_BN];
+#pragma unroll
+      for (int c = 0; c < ATT_BN / 32; ++c) {
+        uint32_t t[32];
+        tmem_ld_32x32(tmem_base + lane_addr + s * ATT_BN + c * 32, t);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sv[c * 32 + i] = __uint_as_float(t[i]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar[BAR_SE + s]);  // S buffer may be overwritten by block j+2
+      const int kv0 = j * ATT_BN;
+      const bool need_mask = (p.causal && kv0 + ATT_BN - 1 > m0 + (p.Sk - p.Sq)) || (kv0 + ATT_BN > p.Sk);
+      if (need_mask) {
+        const int limit = p.causal ? min(qi + (p.Sk - p.Sq), p.Sk - 1) : p.Sk - 1;  // last visible kv index
+#pragma unroll
+        for (int i = 0; i < ATT_BN; ++i)
+          if (kv0 + i > limit) sv[i] = -INFINITY;
+      }
+      float mx = sv[0];
+#pragma unroll
+      for (int i = 1; i < ATT_BN; ++i) mx = fmaxf(mx, sv[i]);
+      const float m_new = fmaxf(m_run, mx);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = exp2f((m_run - m_use) * sl2);  // 0 when m_run = -inf
+      const float neg = -m_use * sl2;
+      float rs = 0.f;
+#pragma unroll
+      for (int i = 0; i < ATT_BN; ++i) {
+        sv[i] = exp2f(fmaf(sv[i], sl2, neg));
+        rs += sv[i];
+      }
+      l_run = l_run * alpha + rs;
+      if (j > 0) {
+        // PV of the previous block must be complete before O is rescaled and P is overwritten
+        if (!mbar_wait_bounded_warp(&bar[BAR_PV], (j - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, m_new != m_run)) {
+#pragma unroll
+          for (int c = 0; c < D / 16; ++c) {
+            uint32_t t[16];
+            tmem_ld_32x16(tmem_o + lane_addr + c * 16, t);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * alpha);
+            tmem_st_32x16(tmem_o + lane_addr + c * 16, t);
+          }
+          tc_wait_st();
+        }
+      }
+      m_run = m_new;
+      // P -> shared memory, bf16, swizzled K-major: element (r, kv) lives in block kv/64 at
+      // r*128 + ((kv%64)/8 ^ (r%8))*16 + (kv%8)*2
+#pragma unroll
+      for (int c = 0; c < ATT_BN / 8; ++c) {
+        uint4 v;
+        v.x = pack_bf16(sv[c * 8 + 0], sv[c * 8 + 1]);
+        v.y = pack_bf16(sv[c * 8 + 2], sv[c * 8 + 3]);
+        v.z = pack_bf16(sv[c * 8 + 4], sv[c * 8 + 5]);
+        v.w = pack_bf16(sv[c * 8 + 6], sv[c * 8 + 7]);
+        const int blk = c >> 3, cc = c & 7;
+        *reinterpret_cast<uint4*>(sp + blk * L::TILE + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
+      }
+      fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's async proxy
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar[BAR_PF]);
+    }
+    if (ok && mbar_wait_bounded_warp(&bar[BAR_PV], (n_blocks - 1) & 1, abort_flag, p.status)) {
+      tc_fence_after();
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      const bool row_ok = qi < p.Sq;
+      __nv_bfloat16* orow = p.o + ((size_t(b) * p.Sq + qi) * p.H + h) * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t t[32];
+        tmem_ld_32x32(tmem_o + lane_addr + c * 32, t);
+        tc_wait_ld();
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(t[i]) * inv, __uint_as_float(t[i + 1]) * inv);
+            v.y = pack_bf16(__uint_as_float(t[i + 2]) * inv, __uint_as_float(t[i + 3]) * inv);
+            v.z = pack_bf16(__uint_as_float(t[i + 4]) * inv, __uint_as_float(t[i + 5]) * inv);
+            v.w = pack_bf16(__uint_as_float(t[i + 6]) * inv, __uint_as_float(t[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + i) = v;
+          }
+        }
+      }
+      if (row_ok) p.lse[(size_t(b) * p.H + h) * p.Sq + qi] = (l_run > 0.f) ? m_run * p.scale + logf(l_run) : -INFINITY;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// 4-D map over a [B, S, Hn, D] bf16 tensor with a box of [128 rows of S] x [64 elements of D]
+static int make_bshd_map(CUtensorMap* out, const void* base, int B, int S, int Hn, int D) {
+  uint64_t dims[4] = {uint64_t(D), uint64_t(Hn), uint64_t(S), uint64_t(B)};
+  uint64_t strides[3] = {uint64_t(D) * 2, uint64_t(Hn) * D * 2, uint64_t(S) * Hn * D * 2};
+  uint32_t box[4] = {64, 1, 128, 1};
+  return jpb_make_tensor_map(out, base, 2, 4, dims, strides, box, 1);
+}
+
+template <int D>
+static int launch_attn_fwd(const void* q, const void* k, const void* v, const AttnParams& p, cudaStream_t stream) {
+  using L = AttnSmem<D>;
+  CUtensorMap mq, mk, mv;
+  int rc = make_bshd_map(&mq, q, p.B, p.Sq, p.H, D);
+  if (rc) return rc;
+  rc = make_bshd_map(&mk, k, p.B, p.Sk, p.Hkv, D);
+  if (rc) return rc;
+  rc = make_bshd_map(&mv, v, p.B, p.Sk, p.Hkv, D);
+  if (rc) return rc;
+  auto kernel = attention_fwd_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return int(e);
+    configured = true;
+  }
+  dim3 grid((p.Sq + ATT_BM - 1) / ATT_BM, p.H, p.B);
+  kernel<<<grid, ATT_THREADS, L::TOTAL, stream>>>(mq, mk, mv, p);
+  return int(cudaGetLastError());
+}
+
+}  // namespace jpb
+
+// q: [B,Sq,H,D], k/v: [B,Sk,Hkv,D] contiguous bf16; o like q; lse: [B,H,Sq] fp32 (natural log).
+JPB_API int jpb_attention_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk, int H,
+                              int Hkv, int D, int causal, float scale, void* stream) {
+  using namespace jpb;
+  if (H % Hkv != 0 || (D != 64 && D != 128)) return -JPB_ERR_BAD_ARGUMENT;
+  AttnParams p;
+  p.B = B; p.Sq = Sq; p.Sk = Sk; p.H = H; p.Hkv = Hkv; p.causal = causal; p.scale = scale;
+  p.o = static_cast<__nv_bfloat16*>(o); p.lse = lse; p.status = jpb_status_device_ptr();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return D == 128 ? launch_attn_fwd<128>(q, k, v, p, s) : launch_attn_fwd<64>(q, k, v, p, s);
+}

@@ -85,6 +85,14 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   }
 }
 
+// Warp-uniform variant: every lane of the (converged) warp waits; the warp proceeds only if all lanes saw
+// the barrier flip, so that later warp-synchronous code is never entered by a partial warp.
+__device__ __forceinline__ bool mbar_wait_bounded_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                       int* status, int code = JPB_ERR_WAIT_TIMEOUT) {
+  const bool ok = mbar_wait_bounded(bar, parity, abort_flag, status, code);
+  return __all_sync(0xffffffffu, ok);
+}
+
 // ---- TMA ----------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
   asm volatile(

@@ -171,7 +171,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int n0 = (tile / p.tiles_m) * BN;
       const uint32_t acc = tile_i & 1;
       const uint32_t acc_ph = (tile_i >> 1) & 1;
-      if (!mbar_wait_bounded(&acc_full[acc], acc_ph, abort_flag, p.status)) { ok = false; break; }
+      if (!mbar_wait_bounded_warp(&acc_full[acc], acc_ph, abort_flag, p.status)) { ok = false; break; }
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
       const bool row_ok = row < p.M;
