@@ -1,0 +1,597 @@
+// Flash attention backward for sm_100a, as two tcgen05 kernels plus a small pre-pass:
+//
+//   delta[b,h,q]  = sum_d dO * O                                        (attn_delta_kernel)
+//   dK, dV        : one CTA per 128-row K/V block; loops over 64-row Q blocks (and, for GQA, over the
+//                   query heads sharing the K/V head).  Works on transposed tiles so that each thread owns
+//                   one K/V row: S^T = K Q^T, dP^T = V dO^T (TMEM), P^T and dS^T written to shared memory,
+//                   dV += P^T dO and dK += dS^T Q accumulated in TMEM over the whole loop.
+//   dQ            : one CTA per 128-row Q block; loops over 64-row K/V blocks: S = Q K^T, dP = dO V^T,
+//                   dS to shared memory, dQ += dS K accumulated in TMEM.
+//
+// Recomputing S and dP in the second kernel costs two extra MMAs per tile pair but needs no atomics and no
+// fp32 dQ staging buffer, and the result is deterministic.  The same shared-memory tile serves as a K-major
+// operand in one MMA and as an MN-major operand in another (only the descriptor differs), so nothing is
+// transposed in memory.  All waits are bounded.
+#include "common.cuh"
+
+namespace jpb {
+
+constexpr int BWD_THREADS = 192;
+
+struct AttnBwdParams {
+  int B, Sq, Sk, H, Hkv;
+  int causal;
+  float scale;
+  const float* lse;    // [B,H,Sq]
+  const float* delta;  // [B,H,Sq]
+  __nv_bfloat16 *dq, *dk, *dv;
+  int* status;
+};
+
+// swizzled K-major store of 8 consecutive bf16 (one 16-byte chunk `cc` of row `r`) into a [rows x 64] tile
+__device__ __forceinline__ void st_swz(uint8_t* tile, int r, int cc, uint4 v) {
+  *reinterpret_cast<uint4*>(tile + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
+                                  float* __restrict__ delta, int B, int S, int H, int D) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const long long total = (long long)B * S * H;
+  if (warp >= total) return;
+  const int h = warp % H;
+  const long long bs = warp / H;
+  const int s = int(bs % S), b = int(bs / S);
+  const __nv_bfloat16* a = dO + size_t(warp) * D;
+  const __nv_bfloat16* o = O + size_t(warp) * D;
+  float acc = 0.f;
+  for (int i = lane * 2; i < D; i += 64) {
+    const float2 x = unpack_bf16(*reinterpret_cast<const uint32_t*>(a + i));
+    const float2 y = unpack_bf16(*reinterpret_cast<const uint32_t*>(o + i));
+    acc += x.x * y.x + x.y * y.y;
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) delta[(size_t(b) * H + h) * S + s] = acc;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// dK / dV
+// ---------------------------------------------------------------------------------------------------------
+template <int D>
+struct DkvSmem {
+  static constexpr int DB = D / 64;
+  static constexpr int KV_TILE = 128 * 128;   // [128 kv x 64 d] bf16
+  static constexpr int Q_TILE = 64 * 128;     // [64 q x 64 d] bf16
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = OFF_K + DB * KV_TILE;
+  static constexpr int OFF_Q = OFF_V + DB * KV_TILE;      // 2 stages, each: Q (DB tiles) then dO (DB tiles)
+  static constexpr int STAGE = 2 * DB * Q_TILE;
+  static constexpr int OFF_P = OFF_Q + 2 * STAGE;         // P^T  [128 kv x 64 q]
+  static constexpr int OFF_DS = OFF_P + 128 * 128;        // dS^T [128 kv x 64 q]
+  static constexpr int OFF_BAR = OFF_DS + 128 * 128;
+  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+};
+
+enum { K1_KV = 0, K1_QF = 1, K1_QE = 3, K1_SF = 5, K1_SFREE = 6, K1_PF = 7, K1_PE = 8, K1_N = 9 };
+
+template <int D>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
+                     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                     const AttnBwdParams p) {
+  using L = DkvSmem<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bar = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + K1_N);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int jb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int G = p.H / p.Hkv;
+  const int kv0 = jb * 128;
+  const int nq = (p.Sq + 63) / 64;
+  int i_start = 0;
+  if (p.causal) {
+    const int first_q = kv0 - (p.Sk - p.Sq);  // first query row that sees kv0
+    i_start = first_q > 0 ? first_q / 64 : 0;
+  }
+  const int per_head = nq > i_start ? nq - i_start : 0;
+  const int n_iter = per_head * G;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar[K1_KV], 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&bar[K1_QF + s], 1); mbar_init(&bar[K1_QE + s], 1); }
+    mbar_init(&bar[K1_SF], 1);
+    mbar_init(&bar[K1_SFREE], 4);
+    mbar_init(&bar[K1_PF], 4);
+    mbar_init(&bar[K1_PE], 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t t_s = tmem_base, t_dp = tmem_base + 64, t_dv = tmem_base + 128, t_dk = tmem_base + 128 + D;
+
+  if (warp == 0) {
+    if (lane == 0 && n_iter > 0) {
+      uint32_t armed = 0, armed_phase = 0;
+      auto arm = [&](int id, uint32_t ph, uint32_t bytes) {
+        mbar_expect_tx(&bar[id], bytes);
+        armed |= 1u << id;
+        armed_phase = (armed_phase & ~(1u << id)) | (ph << id);
+      };
+      arm(K1_KV, 0, 2 * L::DB * L::KV_TILE);
+#pragma unroll
+      for (int d = 0; d < L::DB; ++d) {
+        tma_load_4d(smem + L::OFF_K + d * L::KV_TILE, &map_k, &bar[K1_KV], d * 64, hk, kv0, b);
+        tma_load_4d(smem + L::OFF_V + d * L::KV_TILE, &map_v, &bar[K1_KV], d * 64, hk, kv0, b);
+      }
+      bool ok = true;
+      for (int t = 0; t < n_iter && ok; ++t) {
+        const int s = t & 1;
+        const uint32_t ph = (t >> 1) & 1;
+        const int h = hk * G + t / per_head;
+        const int q0 = (i_start + t % per_head) * 64;
+        if (!mbar_wait_bounded(&bar[K1_QE + s], ph ^ 1, abort_flag, p.status)) { ok = false; break; }
+        arm(K1_QF + s, ph, L::STAGE);
+        uint8_t* st = smem + L::OFF_Q + s * L::STAGE;
+#pragma unroll
+        for (int d = 0; d < L::DB; ++d) {
+          tma_load_4d(st + d * L::Q_TILE, &map_q, &bar[K1_QF + s], d * 64, h, q0, b);
+          tma_load_4d(st + (L::DB + d) * L::Q_TILE, &map_do, &bar[K1_QF + s], d * 64, h, q0, b);
+        }
+      }
+      if (!ok) {
+        const uint64_t t0 = globaltimer_ns();
+        for (int id = 0; id < K1_QE; ++id) {
+          if (!(armed & (1u << id))) continue;
+          while (!mbar_try_wait(&bar[id], (armed_phase >> id) & 1) && globaltimer_ns() - t0 < JPB_WAIT_BUDGET_NS) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);   // [kv x q] = K-major x K-major
+      constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);  // [kv x d] = K-major(P^T) x MN-major(dO / Q)
+      const uint32_t sk = smem_u32(smem + L::OFF_K), sv = smem_u32(smem + L::OFF_V);
+      const uint32_t sp = smem_u32(smem + L::OFF_P), sds = smem_u32(smem + L::OFF_DS);
+      bool ok = n_iter > 0 && mbar_wait_bounded(&bar[K1_KV], 0, abort_flag, p.status);
+      auto issue_s = [&](int t) -> bool {
+        const int s = t & 1;
+        if (!mbar_wait_bounded(&bar[K1_QF + s], (t >> 1) & 1, abort_flag, p.status)) return false;
+        if (t > 0 && !mbar_wait_bounded(&bar[K1_SFREE], (t - 1) & 1, abort_flag, p.status)) return false;
+        tc_fence_after();
+        const uint32_t sq = smem_u32(smem + L::OFF_Q + s * L::STAGE);
+        const uint32_t sdo = sq + L::DB * L::Q_TILE;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t a_off = (k >> 2) * L::KV_TILE + (k & 3) * 32;
+          const uint32_t b_off = (k >> 2) * L::Q_TILE + (k & 3) * 32;
+          umma_bf16_ss(t_s, make_smem_desc(sk + a_off, 16, 1024), make_smem_desc(sq + b_off, 16, 1024), idesc_s, k != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t a_off = (k >> 2) * L::KV_TILE + (k & 3) * 32;
+          const uint32_t b_off = (k >> 2) * L::Q_TILE + (k & 3) * 32;
+          umma_bf16_ss(t_dp, make_smem_desc(sv + a_off, 16, 1024), make_smem_desc(sdo + b_off, 16, 1024), idesc_s, k != 0);
+        }
+        umma_commit(&bar[K1_SF]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int t = 0; t < n_iter && ok; ++t) {
+        if (t + 1 < n_iter && !issue_s(t + 1)) { ok = false; break; }
+        const int s = t & 1;
+        if (!mbar_wait_bounded(&bar[K1_PF], t & 1, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sq = smem_u32(smem + L::OFF_Q + s * L::STAGE);
+        const uint32_t sdo = sq + L::DB * L::Q_TILE;
+#pragma unroll
+        for (int k = 0; k < 64 / 16; ++k) {  // reduction over the 64 query rows
+          umma_bf16_ss(t_dv, make_smem_desc(sp + k * 32, 16, 1024), make_smem_desc(sdo + k * 2048, L::Q_TILE, 1024),
+                       idesc_acc, (t | k) != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < 64 / 16; ++k) {
+          umma_bf16_ss(t_dk, make_smem_desc(sds + k * 32, 16, 1024), make_smem_desc(sq + k * 2048, L::Q_TILE, 1024),
+                       idesc_acc, (t | k) != 0);
+        }
+        umma_commit(&bar[K1_QE + s]);
+        umma_commit(&bar[K1_PE]);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;  // kv row within the block == TMEM lane
+    const int kv = kv0 + r;
+    const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
+    const float sl2 = p.scale * 1.4426950408889634f;
+    bool ok = n_iter > 0;
+    for (int t = 0; t < n_iter && ok; ++t) {
+      const int h = hk * G + t / per_head;
+      const int q0 = (i_start + t % per_head) * 64;
+      if (!mbar_wait_bounded_warp(&bar[K1_SF], t & 1, abort_flag, p.status)) { ok = false; break; }
+      tc_fence_after();
+      float sv[64], dp[64];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t a[32], d2[32];
+        tmem_ld_32x32(t_s + lane_addr + c * 32, a);
+        tmem_ld_32x32(t_dp + lane_addr + c * 32, d2);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { sv[c * 32 + i] = __uint_as_float(a[i]); dp[c * 32 + i] = __uint_as_float(d2[i]); }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar[K1_SFREE]);
+      const float* lse_q = p.lse + (size_t(b) * p.H + h) * p.Sq;
+      const float* dl_q = p.delta + (size_t(b) * p.H + h) * p.Sq;
+      const int off = p.Sk - p.Sq;
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        const int q = q0 + i;
+        const bool visible = q < p.Sq && kv < p.Sk && (!p.causal || kv <= q + off);
+        float pv = 0.f, ds = 0.f;
+        if (visible) {
+          pv = exp2f(fmaf(sv[i], sl2, -__ldg(lse_q + q) * 1.4426950408889634f));
+          ds = pv * (dp[i] - __ldg(dl_q + q)) * p.scale;
+        }
+        sv[i] = pv;
+        dp[i] = ds;
+      }
+      if (t > 0) {
+        if (!mbar_wait_bounded_warp(&bar[K1_PE], (t - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+      }
+      uint8_t* tp = smem + L::OFF_P;
+      uint8_t* tds = smem + L::OFF_DS;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint4 v, w;
+        v.x = pack_bf16(sv[c * 8 + 0], sv[c * 8 + 1]); v.y = pack_bf16(sv[c * 8 + 2], sv[c * 8 + 3]);
+        v.z = pack_bf16(sv[c * 8 + 4], sv[c * 8 + 5]); v.w = pack_bf16(sv[c * 8 + 6], sv[c * 8 + 7]);
+        w.x = pack_bf16(dp[c * 8 + 0], dp[c * 8 + 1]); w.y = pack_bf16(dp[c * 8 + 2], dp[c * 8 + 3]);
+        w.z = pack_bf16(dp[c * 8 + 4], dp[c * 8 + 5]); w.w = pack_bf16(dp[c * 8 + 6], dp[c * 8 + 7]);
+        st_swz(tp, r, c, v);
+        st_swz(tds, r, c, w);
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar[K1_PF]);
+    }
+    const bool row_ok = kv < p.Sk;
+    __nv_bfloat16* dk_row = p.dk + ((size_t(b) * p.Sk + kv) * p.Hkv + hk) * D;
+    __nv_bfloat16* dv_row = p.dv + ((size_t(b) * p.Sk + kv) * p.Hkv + hk) * D;
+    if (n_iter == 0) {
+      if (row_ok) {
+        for (int i = 0; i < D; i += 8) {
+          *reinterpret_cast<uint4*>(dk_row + i) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(dv_row + i) = make_uint4(0, 0, 0, 0);
+        }
+      }
+    } else if (ok && mbar_wait_bounded_warp(&bar[K1_PE], (n_iter - 1) & 1, abort_flag, p.status)) {
+      tc_fence_after();
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t src = which ? t_dk : t_dv;
+        __nv_bfloat16* dst = which ? dk_row : dv_row;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t a[32];
+          tmem_ld_32x32(src + lane_addr + c * 32, a);
+          tc_wait_ld();
+          if (row_ok) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 v;
+              v.x = pack_bf16(__uint_as_float(a[i]), __uint_as_float(a[i + 1]));
+              v.y = pack_bf16(__uint_as_float(a[i + 2]), __uint_as_float(a[i + 3]));
+              v.z = pack_bf16(__uint_as_float(a[i + 4]), __uint_as_float(a[i + 5]));
+              v.w = pack_bf16(__uint_as_float(a[i + 6]), __uint_as_float(a[i + 7]));
+              *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// dQ
+// ---------------------------------------------------------------------------------------------------------
+template <int D>
+struct DqSmem {
+  static constexpr int DB = D / 64;
+  static constexpr int Q_TILE = 128 * 128;   // [128 q x 64 d]
+  static constexpr int KV_TILE = 64 * 128;   // [64 kv x 64 d]
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_DO = OFF_Q + DB * Q_TILE;
+  static constexpr int OFF_KV = OFF_DO + DB * Q_TILE;   // 2 stages, each: K (DB tiles) then V (DB tiles)
+  static constexpr int STAGE = 2 * DB * KV_TILE;
+  static constexpr int OFF_DS = OFF_KV + 2 * STAGE;     // dS [128 q x 64 kv]
+  static constexpr int OFF_BAR = OFF_DS + 128 * 128;
+  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+};
+
+enum { K2_Q = 0, K2_KF = 1, K2_KE = 3, K2_SF = 5, K2_SFREE = 6, K2_DF = 7, K2_DE = 8, K2_N = 9 };
+
+template <int D>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
+                   const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                   const AttnBwdParams p) {
+  using L = DqSmem<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bar = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + K2_N);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_m = (p.Sq + 127) / 128;
+  const int m_blk = num_m - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.H / p.Hkv);
+  const int m0 = m_blk * 128;
+  int n_iter = (p.Sk + 63) / 64;
+  if (p.causal) {
+    const int last = (m0 + 127 + (p.Sk - p.Sq)) / 64 + 1;
+    n_iter = last < n_iter ? last : n_iter;
+    if (n_iter < 1) n_iter = 1;
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar[K2_Q], 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&bar[K2_KF + s], 1); mbar_init(&bar[K2_KE + s], 1); }
+    mbar_init(&bar[K2_SF], 1);
+    mbar_init(&bar[K2_SFREE], 4);
+    mbar_init(&bar[K2_DF], 4);
+    mbar_init(&bar[K2_DE], 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 256); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t t_s = tmem_base, t_dp = tmem_base + 64, t_dq = tmem_base + 128;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t armed = 0, armed_phase = 0;
+      auto arm = [&](int id, uint32_t ph, uint32_t bytes) {
+        mbar_expect_tx(&bar[id], bytes);
+        armed |= 1u << id;
+        armed_phase = (armed_phase & ~(1u << id)) | (ph << id);
+      };
+      arm(K2_Q, 0, 2 * L::DB * L::Q_TILE);
+#pragma unroll
+      for (int d = 0; d < L::DB; ++d) {
+        tma_load_4d(smem + L::OFF_Q + d * L::Q_TILE, &map_q, &bar[K2_Q], d * 64, h, m0, b);
+        tma_load_4d(smem + L::OFF_DO + d * L::Q_TILE, &map_do, &bar[K2_Q], d * 64, h, m0, b);
+      }
+      bool ok = true;
+      for (int t = 0; t < n_iter && ok; ++t) {
+        const int s = t & 1;
+        const uint32_t ph = (t >> 1) & 1;
+        if (!mbar_wait_bounded(&bar[K2_KE + s], ph ^ 1, abort_flag, p.status)) { ok = false; break; }
+        arm(K2_KF + s, ph, L::STAGE);
+        uint8_t* st = smem + L::OFF_KV + s * L::STAGE;
+#pragma unroll
+        for (int d = 0; d < L::DB; ++d) {
+          tma_load_4d(st + d * L::KV_TILE, &map_k, &bar[K2_KF + s], d * 64, hk, t * 64, b);
+          tma_load_4d(st + (L::DB + d) * L::KV_TILE, &map_v, &bar[K2_KF + s], d * 64, hk, t * 64, b);
+        }
+      }
+      if (!ok) {
+        const uint64_t t0 = globaltimer_ns();
+        for (int id = 0; id < K2_KE; ++id) {
+          if (!(armed & (1u << id))) continue;
+          while (!mbar_try_wait(&bar[id], (armed_phase >> id) & 1) && globaltimer_ns() - t0 < JPB_WAIT_BUDGET_NS) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);   // [q x kv]
+      constexpr uint32_t idesc_dq = make_idesc_bf16(128, D, 0, 1);   // [q x d] = K-major(dS) x MN-major(K)
+      const uint32_t sq = smem_u32(smem + L::OFF_Q), sdo = smem_u32(smem + L::OFF_DO);
+      const uint32_t sds = smem_u32(smem + L::OFF_DS);
+      bool ok = mbar_wait_bounded(&bar[K2_Q], 0, abort_flag, p.status);
+      auto issue_s = [&](int t) -> bool {
+        const int s = t & 1;
+        if (!mbar_wait_bounded(&bar[K2_KF + s], (t >> 1) & 1, abort_flag, p.status)) return false;
+        if (t > 0 && !mbar_wait_bounded(&bar[K2_SFREE], (t - 1) & 1, abort_flag, p.status)) return false;
+        tc_fence_after();
+        const uint32_t sk = smem_u32(smem + L::OFF_KV + s * L::STAGE);
+        const uint32_t sv = sk + L::DB * L::KV_TILE;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t a_off = (k >> 2) * L::Q_TILE + (k & 3) * 32;
+          const uint32_t b_off = (k >> 2) * L::KV_TILE + (k & 3) * 32;
+          umma_bf16_ss(t_s, make_smem_desc(sq + a_off, 16, 1024), make_smem_desc(sk + b_off, 16, 1024), idesc_s, k != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t a_off = (k >> 2) * L::Q_TILE + (k & 3) * 32;
+          const uint32_t b_off = (k >> 2) * L::KV_TILE + (k & 3) * 32;
+          umma_bf16_ss(t_dp, make_smem_desc(sdo + a_off, 16, 1024), make_smem_desc(sv + b_off, 16, 1024), idesc_s, k != 0);
+        }
+        umma_commit(&bar[K2_SF]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int t = 0; t < n_iter && ok; ++t) {
+        if (t + 1 < n_iter && !issue_s(t + 1)) { ok = false; break; }
+        const int s = t & 1;
+        if (!mbar_wait_bounded(&bar[K2_DF], t & 1, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sk = smem_u32(smem + L::OFF_KV + s * L::STAGE);
+#pragma unroll
+        for (int k = 0; k < 64 / 16; ++k) {  // reduction over the 64 kv rows
+          umma_bf16_ss(t_dq, make_smem_desc(sds + k * 32, 16, 1024), make_smem_desc(sk + k * 2048, L::KV_TILE, 1024),
+                       idesc_dq, (t | k) != 0);
+        }
+        umma_commit(&bar[K2_KE + s]);
+        umma_commit(&bar[K2_DE]);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int qi = m0 + r;
+    const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
+    const float sl2 = p.scale * 1.4426950408889634f;
+    const bool row_ok = qi < p.Sq;
+    const float lse_r = row_ok ? p.lse[(size_t(b) * p.H + h) * p.Sq + qi] * 1.4426950408889634f : 0.f;
+    const float dl_r = row_ok ? p.delta[(size_t(b) * p.H + h) * p.Sq + qi] : 0.f;
+    const int off = p.Sk - p.Sq;
+    bool ok = true;
+    for (int t = 0; t < n_iter && ok; ++t) {
+      if (!mbar_wait_bounded_warp(&bar[K2_SF], t & 1, abort_flag, p.status)) { ok = false; break; }
+      tc_fence_after();
+      float sv[64], dp[64];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t a[32], d2[32];
+        tmem_ld_32x32(t_s + lane_addr + c * 32, a);
+        tmem_ld_32x32(t_dp + lane_addr + c * 32, d2);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { sv[c * 32 + i] = __uint_as_float(a[i]); dp[c * 32 + i] = __uint_as_float(d2[i]); }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar[K2_SFREE]);
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        const int kv = t * 64 + i;
+        const bool visible = row_ok && kv < p.Sk && (!p.causal || kv <= qi + off);
+        float ds = 0.f;
+        if (visible) {
+          const float pv = exp2f(fmaf(sv[i], sl2, -lse_r));
+          ds = pv * (dp[i] - dl_r) * p.scale;
+        }
+        dp[i] = ds;
+      }
+      if (t > 0) {
+        if (!mbar_wait_bounded_warp(&bar[K2_DE], (t - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+      }
+      uint8_t* tds = smem + L::OFF_DS;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint4 w;
+        w.x = pack_bf16(dp[c * 8 + 0], dp[c * 8 + 1]); w.y = pack_bf16(dp[c * 8 + 2], dp[c * 8 + 3]);
+        w.z = pack_bf16(dp[c * 8 + 4], dp[c * 8 + 5]); w.w = pack_bf16(dp[c * 8 + 6], dp[c * 8 + 7]);
+        st_swz(tds, r, c, w);
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar[K2_DF]);
+    }
+    if (ok && mbar_wait_bounded_warp(&bar[K2_DE], (n_iter - 1) & 1, abort_flag, p.status)) {
+      tc_fence_after();
+      __nv_bfloat16* dst = p.dq + ((size_t(b) * p.Sq + qi) * p.H + h) * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t a[32];
+        tmem_ld_32x32(t_dq + lane_addr + c * 32, a);
+        tc_wait_ld();
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(a[i]), __uint_as_float(a[i + 1]));
+            v.y = pack_bf16(__uint_as_float(a[i + 2]), __uint_as_float(a[i + 3]));
+            v.z = pack_bf16(__uint_as_float(a[i + 4]), __uint_as_float(a[i + 5]));
+            v.w = pack_bf16(__uint_as_float(a[i + 6]), __uint_as_float(a[i + 7]));
+            *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 256); }
+}
+
+// 4-D map over [B, S, Hn, D] bf16 with a box of [rows of S] x [64 elements of D]
+static int make_map_rows(CUtensorMap* out, const void* base, int B, int S, int Hn, int D, int rows) {
+  uint64_t dims[4] = {uint64_t(D), uint64_t(Hn), uint64_t(S), uint64_t(B)};
+  uint64_t strides[3] = {uint64_t(D) * 2, uint64_t(Hn) * D * 2, uint64_t(S) * Hn * D * 2};
+  uint32_t box[4] = {64, 1, uint32_t(rows), 1};
+  return jpb_make_tensor_map(out, base, 2, 4, dims, strides, box, 1);
+}
+
+template <int D>
+static int launch_bwd(const void* dO, const void* q, const void* k, const void* v, const AttnBwdParams& p, cudaStream_t stream) {
+  CUtensorMap mq64, mdo64, mk128, mv128, mq128, mdo128, mk64, mv64;
+  int rc = 0;
+  rc |= make_map_rows(&mq64, q, p.B, p.Sq, p.H, D, 64);
+  rc |= make_map_rows(&mdo64, dO, p.B, p.Sq, p.H, D, 64);
+  rc |= make_map_rows(&mk128, k, p.B, p.Sk, p.Hkv, D, 128);
+  rc |= make_map_rows(&mv128, v, p.B, p.Sk, p.Hkv, D, 128);
+  rc |= make_map_rows(&mq128, q, p.B, p.Sq, p.H, D, 128);
+  rc |= make_map_rows(&mdo128, dO, p.B, p.Sq, p.H, D, 128);
+  rc |= make_map_rows(&mk64, k, p.B, p.Sk, p.Hkv, D, 64);
+  rc |= make_map_rows(&mv64, v, p.B, p.Sk, p.Hkv, D, 64);
+  if (rc) return rc;
+  auto k1 = attn_bwd_dkdv_kernel<D>;
+  auto k2 = attn_bwd_dq_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvSmem<D>::TOTAL) != cudaSuccess) return -3;
+    if (cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, DqSmem<D>::TOTAL) != cudaSuccess) return -3;
+    configured = true;
+  }
+  dim3 g1((p.Sk + 127) / 128, p.Hkv, p.B);
+  k1<<<g1, BWD_THREADS, DkvSmem<D>::TOTAL, stream>>>(mq64, mdo64, mk128, mv128, p);
+  dim3 g2((p.Sq + 127) / 128, p.H, p.B);
+  k2<<<g2, BWD_THREADS, DqSmem<D>::TOTAL, stream>>>(mq128, mdo128, mk64, mv64, p);
+  return int(cudaGetLastError());
+}
+
+}  // namespace jpb
+
+// Scratch needed by jpb_attention_bwd: the fp32 `delta` vector [B,H,Sq].
+JPB_API long long jpb_attention_bwd_scratch_bytes(int B, int Sq, int Sk, int H, int Hkv, int D) {
+  (void)Sk; (void)Hkv; (void)D;
+  return (long long)B * H * Sq * 4;
+}
+
+// All tensors contiguous bf16: dO/q/o/dq [B,Sq,H,D], k/v/dk/dv [B,Sk,Hkv,D]; lse [B,H,Sq] fp32.
+// `scratch` must hold jpb_attention_bwd_scratch_bytes(); `reserved` is unused (pass NULL).
+JPB_API int jpb_attention_bwd(const void* dO, const void* q, const void* k, const void* v, const void* o, const float* lse,
+                              void* dq, void* dk, void* dv, void* scratch, void* reserved, int B, int Sq, int Sk, int H,
+                              int Hkv, int D, int causal, float scale, void* stream) {
+  using namespace jpb;
+  (void)reserved;
+  if (H % Hkv != 0 || (D != 64 && D != 128)) return -JPB_ERR_BAD_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* delta = static_cast<float*>(scratch);
+  const long long rows = (long long)B * Sq * H;
+  const int threads = 256;
+  const long long blocks = (rows * 32 + threads - 1) / threads;
+  attn_delta_kernel<<<(unsigned)blocks, threads, 0, s>>>(static_cast<const __nv_bfloat16*>(dO),
+                                                         static_cast<const __nv_bfloat16*>(o), delta, B, Sq, H, D);
+  AttnBwdParams p;
+  p.B = B; p.Sq = Sq; p.Sk = Sk; p.H = H; p.Hkv = Hkv; p.causal = causal; p.scale = scale;
+  p.lse = lse; p.delta = delta;
+  p.dq = static_cast<__nv_bfloat16*>(dq); p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
+  p.status = jpb_status_device_ptr();
+  return D == 128 ? launch_bwd<128>(dO, q, k, v, p, s) : launch_bwd<64>(dO, q, k, v, p, s);
+}

@@ -164,3 +164,34 @@ def test_ops_dispatch_to_native_and_autograd(native):
     close(x.grad, xr.grad, rtol=5e-2, atol=2e-3)
     close(w.grad, wr.grad, rtol=5e-2, atol=2e-3)
     close(g.grad, gr.grad, rtol=5e-2, atol=5e-3)
+
+
+ATTN_CASES = [
+    # B, S, H, Hkv, D, causal
+    (2, 256, 4, 4, 64, True),
+    (1, 512, 4, 2, 128, True),
+    (2, 384, 2, 2, 128, False),
+    (1, 200, 2, 1, 64, True),   # ragged sequence: masks past the end of K and padded query rows
+    (1, 1024, 8, 2, 128, True),
+]
+
+
+@pytest.mark.parametrize("B,S,H,Hkv,D,causal", ATTN_CASES)
+def test_flash_attention_forward_backward(native, B, S, H, Hkv, D, causal):
+    from jaxpp_b200.ops import attention as att
+    from jaxpp_b200.ops import core as ops
+
+    q, k, v = rnd(B, S, H, D, seed=1), rnd(B, S, Hkv, D, seed=2), rnd(B, S, Hkv, D, seed=3)
+    do = rnd(B, S, H, D, seed=4)
+    scale = D ** -0.5
+    o, lse = att.attention_fwd(q, k, v, causal, scale)
+    ro, rlse = ops._attn_ref(q.float(), k.float(), v.float(), causal, scale)
+    close(o, ro, rtol=2e-2, atol=2e-2)
+    close(lse, rlse, rtol=1e-3, atol=2e-3)
+    dq, dk, dv = att.attention_bwd(do, q, k, v, o, lse, causal, scale)
+    rdq, rdk, rdv = ops._attn_bwd_ref(do.float(), q.float(), k.float(), v.float(), ro, rlse, causal, scale)
+    close(dq, rdq, rtol=3e-2, atol=3e-2)
+    close(dk, rdk, rtol=3e-2, atol=3e-2 * (H // Hkv) ** 0.5)
+    close(dv, rdv, rtol=3e-2, atol=3e-2 * (H // Hkv) ** 0.5)
+    torch.cuda.synchronize()
+    assert native.read_status(clear=False) == 0
