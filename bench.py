@@ -1,0 +1,264 @@
+#!/usr/bin/env python
+"""Headline benchmark: training tokens/s of a Llama-2-7B-shape decoder, bf16, AdamW, synthetic data.
+
+    python bench.py --gpus 1 --steps K --warmup W
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+
+Weak scaling: every GPU contributes 16 sequences of 4096 tokens per step.  N=8 is the headline layout
+(PP=4 x TP=2, Interleaved1F1B with 2 virtual stages per rank, 32 microbatches of 4 sequences); smaller N
+keep the model and the per-GPU batch and shrink the mesh: N=4 PP2xTP2, N=2 TP2, N=1 a single device
+(16 microbatches of 1 sequence so that activations fit beside 7B of optimizer state).
+
+Prints ONE JSON line from rank 0.  ``value`` is device-timed (CUDA events around K steps, max over ranks);
+``e2e`` repeats the measurement through the public API with a host->device copy of the step's token ids
+from pinned memory and a device->host read of the loss in every step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="llama2_7b")
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only; invalid as a result)")
+    ap.add_argument("--seqs-per-gpu", type=int, default=16)
+    ap.add_argument("--nccl-only", action="store_true", help="baseline: NCCL collectives instead of fused kernels")
+    return ap.parse_args()
+
+
+LAYOUTS = {  # n_gpus -> (pp, tp, virtual stages per rank, microbatch size)
+    1: (1, 1, 1, 1),
+    2: (1, 2, 1, 4),
+    4: (2, 2, 2, 4),
+    8: (4, 2, 2, 4),
+}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.gpu)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_arm():
+    # The reference is JAX-based: its package installs from the offline wheelhouse only with --no-deps and
+    # cannot be imported because jax / jaxlib / cupy are neither installed nor in the wheelhouse.
+    print(json.dumps({"impl": "reference", "unavailable": "reference needs jax[cuda12]+cupy, absent from image and wheelhouse "
+                      "(pip --no-index: no matching distribution for jax); `import jaxpp` fails with ModuleNotFoundError: jax"}))
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return reference_arm()
+
+    import torch
+    import torch.distributed as dist
+
+    import jaxpp_b200 as jp
+    from jaxpp_b200.models import lm_trainer as lt
+    from jaxpp_b200.models import transformer as tf
+    from jaxpp_b200.ops import native
+    from jaxpp_b200.utils import config
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    n = args.gpus
+    if world != n:
+        raise SystemExit(f"--gpus {n} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {n}")
+    if n not in LAYOUTS:
+        raise SystemExit(f"supported GPU counts: {sorted(LAYOUTS)}")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    native.load()
+    if args.nccl_only:
+        config.use_fused_collectives._override = False
+
+    pp, tp, vstages, mb = LAYOUTS[n]
+    n_stages = pp * vstages
+    seqs = args.seqs_per_gpu * n
+    n_mb = seqs // mb
+    cfg = getattr(tf, args.model)(n_stages=n_stages, tp=tp)
+    if args.layers:
+        import dataclasses
+
+        cfg = dataclasses.replace(cfg, n_layers=args.layers)
+    schedule = jp.Interleaved1F1B(n_stages, pp) if vstages > 1 else jp.Std1F1B(pp)
+    mesh = jp.MpmdMesh.create({"mpmd": pp, "data": 1, "model": tp}, kind="cuda", multi_process=world > 1)
+    my_pp = mesh.my_mpmd_axis_index if world > 1 else None
+    tp_rank = mesh.axis_index("model") if world > 1 and tp > 1 else 0
+
+    hyper = lt.Hyper()
+    step_fn = lt.make_train_step(cfg, schedule, hyper)
+    jitted = jp.mpmd_jit_with_loop(step_fn, mesh, name="llama_train_step")
+    state = lt.init_state(cfg, schedule, device, my_rank=my_pp, tp_rank=tp_rank, seed=0)
+
+    g = torch.Generator().manual_seed(1234)
+    host_tokens = [torch.randint(0, cfg.vocab, (n_mb, mb, cfg.seq + 1), generator=g).pin_memory() for _ in range(2)]
+    tokens_per_step = seqs * cfg.seq
+    h2d_bytes = 2 * n_mb * mb * cfg.seq * 8
+
+    def load_batch(i):
+        t = host_tokens[i % 2].to(device, non_blocking=True)
+        return t[:, :, :-1].contiguous(), t[:, :, 1:].contiguous()
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def read_loss(losses):
+        t = losses.local_tensor()
+        return float(t.mean().item()) if t is not None else None
+
+    tok, lab = load_batch(0)
+    loss_val = None
+    for i in range(args.warmup):
+        state, losses = jitted(state, tok, lab)
+        loss_val = read_loss(losses)
+    sync_all()
+
+    # ---- device-timed region: K steps, inputs resident -------------------------------------------------------
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    native.LAUNCHES[0] = 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    e0.record()
+    for i in range(args.steps):
+        state, losses = jitted(state, tok, lab)
+    e1.record()
+    sync_all()
+    ms = e0.elapsed_time(e1) / args.steps
+    launches = native.LAUNCHES[0]
+    clocks = sampler.stop() if rank == 0 else None
+    status = native.read_status()
+
+    # ---- end-to-end region: H2D of the step's tokens + D2H of its loss, every step ----------------------------------
+    sync_all()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        tok, lab = load_batch(i)
+        state, losses = jitted(state, tok, lab)
+        lv = read_loss(losses)
+        loss_val = lv if lv is not None else loss_val
+    sync_all()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+
+    # ---- bubble: one extra step with per-task CUDA events ---------------------------------------------------------------
+    compiled = jitted.lower(state, tok, lab)
+    leaves, *_ = jitted._prepare((state, tok, lab), {})
+    sync_all()
+    b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    b0.record()
+    out = compiled(leaves, record_events=True)
+    b1.record()
+    torch.cuda.synchronize()
+    step_ms_b = b0.elapsed_time(b1)
+    busy = compiled.last_states[0].busy_ms() if world > 1 else sum(s.busy_ms() for s in compiled.last_states)
+    bubble = max(0.0, 1.0 - busy / step_ms_b)
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms, bubble, float(launches), float(status)], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms, bubble, launches, status = (float(x) for x in t.tolist())
+        lt_ = torch.tensor([loss_val if loss_val is not None else -1.0], device=device, dtype=torch.float64)
+        dist.all_reduce(lt_, op=dist.ReduceOp.MAX)
+        loss_val = float(lt_.item())
+
+    if rank == 0:
+        value = tokens_per_step / (ms / 1e3)
+        flops = cfg.flops_per_token() * tokens_per_step
+        peak = 1412.0e12
+        try:
+            peaks = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")))
+            peak = float(peaks.get("bf16_tflops_sustained", 1412.0)) * 1e12
+        except Exception:
+            pass
+        out = {
+            "metric": "train tokens/s, Llama-7B-shape PP4xTP2 on 8xB200 (max over ranks); bubble %",
+            "value": round(value, 1), "unit": "tokens/s", "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init weights)",
+            "config": {"model": f"{args.model} ({cfg.n_layers} layers, d_model {cfg.d_model}, seq {cfg.seq})",
+                       "global_batch": seqs, "seq_len": cfg.seq, "microbatches": n_mb, "microbatch_size": mb,
+                       "parallelism": f"pp{pp}tp{tp}" + (f" interleaved v={vstages}" if vstages > 1 else ""),
+                       "schedule": type(schedule).__name__, "optimizer": "AdamW fp32 master, fused kernel",
+                       "l2": "inputs exceed L2 (weights and activations are GBs per step)",
+                       "fused_collectives": bool(config.use_fused_collectives.value) and tp > 1},
+            "clocks": clocks,
+            "e2e": {"value": round(tokens_per_step / (e2e_ms / 1e3), 1), "unit": "tokens/s",
+                    "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4, "ms_per_step": round(e2e_ms, 3)},
+            "gpu_launches": int(launches),
+            "bubble_pct": round(100 * bubble, 2),
+            "ideal_bubble_pct": round(100 * schedule.ideal_bubble_fraction(n_mb), 2),
+            "mfu_of_measured_sustained_peak": round(flops / (ms / 1e3) / (peak * n), 4),
+            "final_loss": loss_val, "kernel_status": int(status),
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -101,9 +101,13 @@ class CompiledMpmd:
         return [sub.flat_devices[0].torch_device for sub in self.mesh.unstack]
 
     def __call__(self, leaves: list, record_events: bool = False):
+        with self.mesh:
+            return self._run(leaves, record_events)
+
+    def _run(self, leaves: list, record_events: bool = False):
         mesh = self.mesh
         prog = self.program
-        tensors = [leaves[p] for p in self.tensor_positions]
+        tensors = [None if isinstance(leaves[p], ShapeDtypeStruct) else leaves[p] for p in self.tensor_positions]
         if not mesh.jax_mesh.is_multi_process:
             if mesh.unstack[0].size != 1:
                 raise NotImplementedError(

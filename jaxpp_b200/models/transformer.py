@@ -1,0 +1,280 @@
+"""Transformer model families as pure functions over parameter pytrees.
+
+Three decoder/encoder families cover the benchmark configurations:
+
+* ``encoder`` — BERT-style post-LayerNorm encoder block (GELU FFN), the analogue of the reference's
+  example model (examples/basic.py:33-91);
+* ``gpt2``    — pre-LayerNorm decoder with learned positions and GELU FFN;
+* ``llama``   — pre-RMSNorm decoder with RoPE, SwiGLU FFN and grouped-query attention (Llama-2, and the
+  dense part of Mixtral).
+
+Models are written against the local shard a device sees.  With a ``model`` (tensor-parallel) axis of
+size ``tp`` the layers follow the Megatron sequence-parallel recipe: activations between blocks are sharded
+over tokens, column-parallel linears gather them (``ag_linear``), row-parallel linears reduce-scatter
+their output (``linear_rs``); parameters that are replicated across the axis (norm weights, embeddings,
+LM head) get their gradients summed with :func:`sync_replicated_grads`.  Stage boundaries are marked with
+``mark_stage_end`` every ``layers_per_stage`` layers.
+"""
+from __future__ import annotations
+
+import dataclasses
+import math
+from typing import Any
+
+import torch
+
+from ..ops import core as ops
+from ..parallel import tp as tpops
+from ..pipelining import mark_stage_end
+
+
+@dataclasses.dataclass(frozen=True)
+class ModelConfig:
+    family: str  # "encoder" | "gpt2" | "llama"
+    vocab: int
+    d_model: int
+    n_layers: int
+    n_heads: int
+    n_kv_heads: int
+    ffn: int
+    seq: int
+    n_stages: int = 1
+    tp: int = 1  # size of the tensor-parallel (model) axis
+    tp_axis: str = "model"
+    eps: float = 1e-5
+    rope_theta: float = 10000.0
+    dtype: torch.dtype = torch.bfloat16
+    causal: bool = True
+    tie_embeddings: bool = False
+    recompute: bool = False  # recompute each block's activations in backward
+
+    @property
+    def head_dim(self) -> int:
+        return self.d_model // self.n_heads
+
+    @property
+    def layers_per_stage(self) -> int:
+        assert self.n_layers % self.n_stages == 0
+        return self.n_layers // self.n_stages
+
+    @property
+    def padded_vocab(self) -> int:
+        return (self.vocab + 127) // 128 * 128
+
+    def n_params(self) -> int:
+        d, f = self.d_model, self.ffn
+        hd = self.head_dim
+        attn = d * (self.n_heads + 2 * self.n_kv_heads) * hd + self.n_heads * hd * d
+        mlp = (3 if self.family == "llama" else 2) * d * f
+        emb = self.padded_vocab * d * (1 if self.tie_embeddings or self.family == "encoder" else 2)
+        return self.n_layers * (attn + mlp) + emb
+
+    def flops_per_token(self) -> float:
+        """Training FLOPs per token: 6 per parameter in a matmul plus causal attention."""
+        d, f, hd = self.d_model, self.ffn, self.head_dim
+        attn_w = d * (self.n_heads + 2 * self.n_kv_heads) * hd + self.n_heads * hd * d
+        mlp_w = (3 if self.family == "llama" else 2) * d * f
+        head = self.padded_vocab * d if self.family != "encoder" else 0
+        matmul = 6.0 * (self.n_layers * (attn_w + mlp_w) + head)
+        attn = 12.0 * self.n_layers * self.n_heads * hd * self.seq * (0.5 if self.causal else 1.0)
+        return matmul + attn
+
+
+# presets named after the shapes in the benchmark configurations
+def llama2_7b(**kw) -> ModelConfig:
+    return ModelConfig("llama", 32000, 4096, 32, 32, 32, 11008, 4096, **kw)
+
+
+def llama2_70b(**kw) -> ModelConfig:
+    return ModelConfig("llama", 32000, 8192, 80, 64, 8, 28672, 4096, **kw)
+
+
+def gpt2_xl(**kw) -> ModelConfig:
+    return ModelConfig("gpt2", 50257, 1600, 48, 25, 25, 6400, 1024, **kw)
+
+
+def bert_example(**kw) -> ModelConfig:
+    kw.setdefault("dtype", torch.float32)
+    kw.setdefault("causal", False)
+    return ModelConfig("encoder", 0, 256, 4, 4, 4, 1024, 128, **kw)
+
+
+# =============================================================================================
+# parameters
+# =============================================================================================
+def _randn(gen, shape, std, dtype, device):
+    if str(device) == "meta":
+        return torch.empty(shape, dtype=dtype, device="meta")
+    return (torch.randn(shape, generator=gen, dtype=torch.float32, device=gen.device) * std).to(dtype=dtype, device=device)
+
+
+def init_layer(cfg: ModelConfig, layer: int, device="cpu", seed: int = 0, tp_rank: int = 0, dtype=None) -> dict:
+    """Parameters of one block (the ``tp_rank``-th shard of the tensor-parallel ones)."""
+    dtype = dtype or cfg.dtype
+    d, f, hd, tp = cfg.d_model, cfg.ffn, cfg.head_dim, cfg.tp
+    gen_dev = device if str(device).startswith("cuda") else "cpu"
+    gen = torch.Generator(device=gen_dev).manual_seed(seed * 100003 + layer * 131 + tp_rank)
+    std = 0.02
+    out_std = std / math.sqrt(2 * cfg.n_layers)
+    qkv_rows = (cfg.n_heads + 2 * cfg.n_kv_heads) * hd // tp
+    p = {
+        "wqkv": _randn(gen, (qkv_rows, d), std, dtype, device),
+        "wo": _randn(gen, (d, cfg.n_heads * hd // tp), out_std, dtype, device),
+        "w_down": _randn(gen, (d, f // tp), out_std, dtype, device),
+    }
+    ones = lambda: torch.ones(d, dtype=dtype, device=device)
+    zeros = lambda n=d: torch.zeros(n, dtype=dtype, device=device)
+    if cfg.family == "llama":
+        p["w_up"] = _randn(gen, (2 * f // tp, d), std, dtype, device)  # [gate | up]
+        p["attn_norm"], p["ffn_norm"] = ones(), ones()
+    else:
+        p["w_up"] = _randn(gen, (f // tp, d), std, dtype, device)
+        p["b_up"] = zeros(f // tp)
+        p["b_qkv"] = zeros(qkv_rows)
+        p["b_o"], p["b_down"] = zeros(), zeros()
+        p["ln1_w"], p["ln1_b"], p["ln2_w"], p["ln2_b"] = ones(), zeros(), ones(), zeros()
+    return p
+
+
+def init_params(cfg: ModelConfig, device="cpu", seed: int = 0, tp_rank: int = 0, layers=None, with_embed=True,
+                with_head=True, dtype=None) -> dict:
+    """Full parameter tree, or only the listed ``layers`` / embedding / head (for per-stage placement)."""
+    dtype = dtype or cfg.dtype
+    layers = range(cfg.n_layers) if layers is None else layers
+    gen_dev = device if str(device).startswith("cuda") else "cpu"
+    gen = torch.Generator(device=gen_dev).manual_seed(seed * 7919 + 17)
+    params: dict[str, Any] = {"layers": {f"{i:03d}": init_layer(cfg, i, device, seed, tp_rank, dtype) for i in layers}}
+    d = cfg.d_model
+    if cfg.family != "encoder":
+        if with_embed:
+            params["embed"] = _randn(gen, (cfg.padded_vocab, d), 0.02, dtype, device)
+            if cfg.family == "gpt2":
+                params["pos"] = _randn(gen, (cfg.seq, d), 0.01, dtype, device)
+        if with_head:
+            params["final_norm"] = torch.ones(d, dtype=dtype, device=device)
+            if cfg.family == "gpt2":
+                params["final_norm_b"] = torch.zeros(d, dtype=dtype, device=device)
+            if not cfg.tie_embeddings:
+                params["lm_head"] = _randn(gen, (cfg.padded_vocab, d), 0.02, dtype, device)
+    return params
+
+
+def rope_tables(cfg: ModelConfig, device="cpu") -> tuple[torch.Tensor, torch.Tensor]:
+    half = cfg.head_dim // 2
+    inv = cfg.rope_theta ** (-torch.arange(half, dtype=torch.float32, device=device) / half)
+    ang = torch.arange(cfg.seq, dtype=torch.float32, device=device)[:, None] * inv[None, :]
+    return ang.cos().contiguous(), ang.sin().contiguous()
+
+
+# =============================================================================================
+# blocks (x is [tokens_local, d]; tokens = batch * seq, batch-major)
+# =============================================================================================
+def _attention(cfg: ModelConfig, qkv: torch.Tensor, batch: int, rope) -> torch.Tensor:
+    hd, tp = cfg.head_dim, cfg.tp
+    hq, hkv = cfg.n_heads // tp, cfg.n_kv_heads // tp
+    qkv = qkv.view(batch, -1, hq + 2 * hkv, hd)
+    q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hkv], qkv[:, :, hq + hkv:]
+    if rope is not None:
+        cos, sin = rope
+        q = ops.rope(q.contiguous(), cos, sin, False)
+        k = ops.rope(k.contiguous(), cos, sin, False)
+    o, _ = ops.attention(q.contiguous(), k.contiguous(), v.contiguous(), cfg.causal, hd ** -0.5)
+    return o.view(-1, hq * hd)
+
+
+def llama_block(cfg: ModelConfig, p: dict, x: torch.Tensor, batch: int, rope) -> torch.Tensor:
+    h = ops.rmsnorm(x, p["attn_norm"], cfg.eps)[0]
+    qkv = tpops.column_linear(h, p["wqkv"], None, cfg)
+    a = _attention(cfg, qkv, batch, rope)
+    x = x + tpops.row_linear(a, p["wo"], None, cfg)
+    h = ops.rmsnorm(x, p["ffn_norm"], cfg.eps)[0]
+    gu = tpops.column_linear(h, p["w_up"], None, cfg)
+    x = x + tpops.row_linear(ops.swiglu(gu), p["w_down"], None, cfg)
+    return x
+
+
+def gpt2_block(cfg: ModelConfig, p: dict, x: torch.Tensor, batch: int, rope) -> torch.Tensor:
+    h = ops.layernorm(x, p["ln1_w"], p["ln1_b"], cfg.eps)[0]
+    qkv = tpops.column_linear(h, p["wqkv"], p["b_qkv"], cfg)
+    a = _attention(cfg, qkv, batch, None)
+    x = x + tpops.row_linear(a, p["wo"], p["b_o"], cfg)
+    h = ops.layernorm(x, p["ln2_w"], p["ln2_b"], cfg.eps)[0]
+    u = ops.gelu(tpops.column_linear(h, p["w_up"], p["b_up"], cfg))
+    x = x + tpops.row_linear(u, p["w_down"], p["b_down"], cfg)
+    return x
+
+
+def encoder_block(cfg: ModelConfig, p: dict, x: torch.Tensor, batch: int, rope) -> torch.Tensor:
+    """Post-LayerNorm block: x = LN(x + Attn(x)); x = LN(x + FFN(x))."""
+    qkv = tpops.column_linear(x, p["wqkv"], p["b_qkv"], cfg)
+    a = _attention(cfg, qkv, batch, None)
+    x = ops.layernorm(x + tpops.row_linear(a, p["wo"], p["b_o"], cfg), p["ln1_w"], p["ln1_b"], cfg.eps)[0]
+    u = ops.gelu(tpops.column_linear(x, p["w_up"], p["b_up"], cfg))
+    x = ops.layernorm(x + tpops.row_linear(u, p["w_down"], p["b_down"], cfg), p["ln2_w"], p["ln2_b"], cfg.eps)[0]
+    return x
+
+
+_BLOCKS = {"llama": llama_block, "gpt2": gpt2_block, "encoder": encoder_block}
+
+
+def run_layers(cfg: ModelConfig, params: dict, x: torch.Tensor, batch: int, rope=None) -> torch.Tensor:
+    """Apply every block in ``params['layers']`` with a stage marker after each ``layers_per_stage``."""
+    block = _BLOCKS[cfg.family]
+    per = cfg.layers_per_stage
+    for name in sorted(params["layers"]):
+        i = int(name)
+        x = block(cfg, params["layers"][name], x, batch, rope)
+        if (i + 1) % per == 0 and (i + 1) < cfg.n_layers:
+            x = mark_stage_end(x)
+    return x
+
+
+def encoder_forward(cfg: ModelConfig, params: dict, hidden: torch.Tensor) -> torch.Tensor:
+    """hidden: [batch, seq, d] → same shape; the last stage marker is placed by the caller after the loss
+    inputs are formed (a marker is required after the last stage)."""
+    b = hidden.shape[0]
+    x = run_layers(cfg, params, hidden.reshape(-1, cfg.d_model), b)
+    return mark_stage_end(x).view_as(hidden)
+
+
+def lm_loss(cfg: ModelConfig, params: dict, tokens: torch.Tensor, labels: torch.Tensor, rope=None) -> torch.Tensor:
+    """Sum over this device's tokens of the next-token cross entropy.  ``tokens``/``labels`` are
+    [batch, seq] int64; with tensor parallelism each device embeds and scores its own slice of the tokens
+    (sequence parallel), so the returned value is a partial sum."""
+    b = tokens.shape[0]
+    tp = cfg.tp
+    flat_tok, flat_lab = tokens.reshape(-1), labels.reshape(-1)
+    if tp > 1:
+        flat_tok, flat_lab = tpops.local_token_slice(flat_tok, cfg), tpops.local_token_slice(flat_lab, cfg)
+    x = ops.embedding(flat_tok, params["embed"])
+    if cfg.family == "gpt2":
+        pos = params["pos"]
+        n_local = flat_tok.shape[0]
+        pos_ids = tpops.local_positions(n_local, cfg, tokens.device)
+        x = x + ops.embedding(pos_ids, pos)
+    x = run_layers(cfg, params, x, b, rope)
+    if cfg.family == "gpt2":
+        x = ops.layernorm(x, params["final_norm"], params["final_norm_b"], cfg.eps)[0]
+    else:
+        x = ops.rmsnorm(x, params["final_norm"], cfg.eps)[0]
+    head = params["embed"] if cfg.tie_embeddings else params["lm_head"]
+    logits = ops.linear(x, head, None)
+    loss, _ = ops.cross_entropy(logits, flat_lab)
+    total = loss.sum()
+    return mark_stage_end(total)
+
+
+def sync_replicated_grads(cfg: ModelConfig, grads: dict) -> dict:
+    """Sum over the tensor-parallel axis the gradients of parameters that are replicated across it."""
+    if cfg.tp == 1:
+        return grads
+    rep_layer = {"attn_norm", "ffn_norm", "ln1_w", "ln1_b", "ln2_w", "ln2_b", "b_o", "b_down"}
+    out = dict(grads)
+    out["layers"] = {
+        name: {k: (tpops.all_reduce(g, cfg.tp_axis) if k in rep_layer else g) for k, g in layer.items()}
+        for name, layer in grads["layers"].items()
+    }
+    for k in ("embed", "pos", "final_norm", "final_norm_b", "lm_head"):
+        if k in grads:
+            out[k] = tpops.all_reduce(grads[k], cfg.tp_axis)
+    return out

@@ -54,5 +54,5 @@ def attention_bwd(do, q, k, v, o, lse, causal: bool, scale: float):
     rc = lib.jpb_attention_bwd(do.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
                                dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), scratch.data_ptr(), None, B, Sq, Sk, H, Hkv, D,
                                int(causal), float(scale), native._stream())
-    native._check(rc, "jpb_attention_bwd")
+    native._check(rc, "jpb_attention_bwd", 3)
     return dq, dk, dv

@@ -99,16 +99,35 @@ linear_dgrad = _define(
 )
 
 
-def _linear_wgrad_ref(dy, x):
-    return dy.reshape(-1, dy.shape[-1]).t() @ x.reshape(-1, x.shape[-1])
+# dtype of weight gradients produced by the backward of ``linear`` (None = same as the activations).
+# Set to torch.float32 to get fp32 main gradients straight out of the GEMM epilogue.
+WGRAD_DTYPE: list = [None]
 
 
-linear_wgrad = _define(
-    "linear_wgrad(Tensor dy, Tensor x) -> Tensor",
-    _linear_wgrad_ref,
-    lambda dy, x: dy.new_empty(dy.shape[-1], x.shape[-1]),
-    "linear_wgrad",
+def _linear_wgrad_ref(dy, x, out_dtype=None):
+    out = dy.reshape(-1, dy.shape[-1]).float().t() @ x.reshape(-1, x.shape[-1]).float()
+    return out.to(out_dtype if out_dtype is not None else dy.dtype)
+
+
+def _linear_wgrad_native_or_ref(dy, x, out_dtype=None):
+    if _use_native(dy):
+        nat = _native()
+        if out_dtype is None or out_dtype == dy.dtype:
+            return nat.linear_wgrad(dy, x)
+        if out_dtype != torch.float32:
+            raise RuntimeError(f"linear_wgrad writes bfloat16 or float32, not {out_dtype}")
+        out = torch.empty(dy.shape[-1], x.shape[-1], dtype=torch.float32, device=dy.device)
+        return nat.linear_wgrad(dy, x, out=out)
+    return _linear_wgrad_ref(dy, x, out_dtype)
+
+
+_lib.define("linear_wgrad(Tensor dy, Tensor x, ScalarType? out_dtype=None) -> Tensor")
+_lib.impl("linear_wgrad", _linear_wgrad_native_or_ref, "CompositeExplicitAutograd")
+torch.library.register_fake(
+    "b200::linear_wgrad",
+    lambda dy, x, out_dtype=None: dy.new_empty(dy.shape[-1], x.shape[-1], dtype=out_dtype or dy.dtype),
 )
+linear_wgrad = torch.ops.b200.linear_wgrad
 
 # column sums, used for bias gradients
 colsum = _define(
@@ -128,7 +147,7 @@ def _linear_setup(ctx, inputs, output):
 def _linear_bwd(ctx, dy):
     x, w = ctx.saved_tensors
     dx = linear_dgrad(dy, w) if ctx.needs_input_grad[0] else None
-    dw = linear_wgrad(dy, x) if ctx.needs_input_grad[1] else None
+    dw = linear_wgrad(dy, x, WGRAD_DTYPE[0]) if ctx.needs_input_grad[1] else None
     db = colsum(dy) if ctx.has_bias and ctx.needs_input_grad[2] else None
     return dx, dw, db
 
@@ -504,7 +523,8 @@ _autograd("embedding", lambda ctx, dy: (None, embedding_bwd(dy.contiguous(), ctx
 # ``master``/``m``/``v`` are fp32; ``grad`` may be bf16 or fp32; ``step`` is a 0-d tensor (1-based)
 # ======================================================================================
 
-def _adamw_ref(master, grad, m, v, step, lr, beta1, beta2, eps, weight_decay, grad_scale, out_dtype):
+def _adamw_ref(master, grad, m, v, step, lr, beta1, beta2, eps, weight_decay, grad_scale, out_dtype, lp_old=None,
+               inplace=False):
     g = _f32(grad) * grad_scale
     m2 = beta1 * m + (1.0 - beta1) * g
     v2 = beta2 * v + (1.0 - beta2) * g * g
@@ -513,14 +533,19 @@ def _adamw_ref(master, grad, m, v, step, lr, beta1, beta2, eps, weight_decay, gr
     bc2 = 1.0 - beta2 ** t
     upd = (m2 / bc1) / ((v2 / bc2).sqrt() + eps)
     p2 = master * (1.0 - lr * weight_decay) - lr * upd
+    if inplace:  # the caller gives up the old state: reuse its storage
+        master.copy_(p2), m.copy_(m2), v.copy_(v2)
+        lp = lp_old.copy_(p2) if lp_old is not None and lp_old.dtype == out_dtype else p2.to(out_dtype)
+        return master, m, v, lp
     return p2, m2, v2, p2.to(out_dtype)
 
 
 adamw = _define(
     "adamw(Tensor master, Tensor grad, Tensor m, Tensor v, Tensor step, float lr, float beta1, float beta2,"
-    " float eps, float weight_decay, float grad_scale, ScalarType out_dtype) -> (Tensor, Tensor, Tensor, Tensor)",
+    " float eps, float weight_decay, float grad_scale, ScalarType out_dtype, Tensor? lp_old=None, bool inplace=False)"
+    " -> (Tensor, Tensor, Tensor, Tensor)",
     _adamw_ref,
-    lambda master, grad, m, v, step, lr, b1, b2, eps, wd, gs, out_dtype: (
+    lambda master, grad, m, v, step, lr, b1, b2, eps, wd, gs, out_dtype, lp_old=None, inplace=False: (
         torch.empty_like(master),
         torch.empty_like(m),
         torch.empty_like(v),

@@ -62,9 +62,14 @@ class NativeError(RuntimeError):
     pass
 
 
-def _check(rc: int, what: str):
+# number of kernels of this library launched so far (benchmarks reset and read it)
+LAUNCHES = [0]
+
+
+def _check(rc: int, what: str, launches: int = 1):
     if rc != 0:
         raise NativeError(f"{what} failed with code {rc}")
+    LAUNCHES[0] += launches
 
 
 def read_status(clear: bool = True) -> int:
@@ -168,7 +173,7 @@ def rmsnorm_bwd(dy, x, w, rstd):
     rows, H = _rows(x), x.shape[-1]
     scratch = norm_bwd_scratch(rows, H, x.device)
     _check(load().jpb_norm_bwd(0, _dt(x), dy.data_ptr(), x.data_ptr(), w.data_ptr(), None, rstd.data_ptr(), dx.data_ptr(),
-                               dw.data_ptr(), None, scratch.data_ptr(), rows, H, _stream()), "rmsnorm_bwd")
+                               dw.data_ptr(), None, scratch.data_ptr(), rows, H, _stream()), "rmsnorm_bwd", 2)
     return dx, dw
 
 
@@ -189,7 +194,7 @@ def layernorm_bwd(dy, x, w, mean, rstd):
     scratch = norm_bwd_scratch(rows, H, x.device)
     _check(load().jpb_norm_bwd(1, _dt(x), dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
                                dx.data_ptr(), dw.data_ptr(), db.data_ptr(), scratch.data_ptr(), rows, H, _stream()),
-           "layernorm_bwd")
+           "layernorm_bwd", 3)
     return dx, dw, db
 
 
@@ -198,7 +203,7 @@ def colsum(dy):
     rows, cols = _rows(dy), dy.shape[-1]
     out = torch.empty(cols, dtype=dy.dtype, device=dy.device)
     scratch = torch.empty(load().jpb_colsum_scratch_elems(rows, cols), dtype=torch.float32, device=dy.device)
-    _check(load().jpb_colsum(_dt(dy), dy.data_ptr(), out.data_ptr(), scratch.data_ptr(), rows, cols, _stream()), "colsum")
+    _check(load().jpb_colsum(_dt(dy), dy.data_ptr(), out.data_ptr(), scratch.data_ptr(), rows, cols, _stream()), "colsum", 2)
     return out
 
 
@@ -258,11 +263,11 @@ def embedding_bwd(dy, ids, vocab):
     acc = torch.empty(vocab, d, dtype=torch.float32, device=dy.device)
     if dy.dtype == torch.float32:
         _check(load().jpb_embedding_bwd(0, dy.data_ptr(), ids.data_ptr(), acc.data_ptr(), None, ids.numel(), d, vocab,
-                                        _stream()), "embedding_bwd")
+                                        _stream()), "embedding_bwd", 1)
         return acc
     out = torch.empty(vocab, d, dtype=dy.dtype, device=dy.device)
     _check(load().jpb_embedding_bwd(_dt(dy), dy.data_ptr(), ids.data_ptr(), acc.data_ptr(), out.data_ptr(), ids.numel(), d,
-                                    vocab, _stream()), "embedding_bwd")
+                                    vocab, _stream()), "embedding_bwd", 2)
     return out
 
 
@@ -286,10 +291,19 @@ def cross_entropy_bwd(dloss, logits, labels, lse):
     return out
 
 
-def adamw(master, grad, m, v, step, lr, beta1, beta2, eps, weight_decay, grad_scale, out_dtype):
-    master, grad, m, v = master.contiguous(), grad.contiguous(), m.contiguous(), v.contiguous()
-    p2, m2, v2 = torch.empty_like(master), torch.empty_like(m), torch.empty_like(v)
-    lp = torch.empty(master.shape, dtype=out_dtype, device=master.device)
+def adamw(master, grad, m, v, step, lr, beta1, beta2, eps, weight_decay, grad_scale, out_dtype, lp_old=None,
+          inplace=False):
+    grad = grad.contiguous()
+    if inplace:
+        if not (master.is_contiguous() and m.is_contiguous() and v.is_contiguous()):
+            raise NativeError("in-place adamw needs contiguous state tensors")
+        p2, m2, v2 = master, m, v
+        reuse = lp_old is not None and lp_old.dtype == out_dtype and lp_old.is_contiguous()
+        lp = lp_old if reuse else torch.empty(master.shape, dtype=out_dtype, device=master.device)
+    else:
+        master, m, v = master.contiguous(), m.contiguous(), v.contiguous()
+        p2, m2, v2 = torch.empty_like(master), torch.empty_like(m), torch.empty_like(v)
+        lp = torch.empty(master.shape, dtype=out_dtype, device=master.device)
     step = step.to(device=master.device, dtype=torch.int64)
     out_code = 0 if out_dtype == torch.float32 else 1
     if out_dtype not in (torch.float32, torch.bfloat16):
