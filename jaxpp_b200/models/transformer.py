@@ -278,3 +278,42 @@ def sync_replicated_grads(cfg: ModelConfig, grads: dict) -> dict:
         if k in grads:
             out[k] = tpops.all_reduce(grads[k], cfg.tp_axis)
     return out
+
+
+# =============================================================================================
+# tensor-parallel sharding of a full (tp = 1) parameter tree
+# =============================================================================================
+def shard_layer_for_tp(cfg: ModelConfig, full: dict, tp: int, r: int) -> dict:
+    """The ``r``-th of ``tp`` shards of one block's parameters.  Column-parallel weights (``wqkv``,
+    ``w_up``) are split by output rows — per q/k/v section and per gate/up half so that every shard keeps
+    whole heads and matching gate/up columns — row-parallel ones (``wo``, ``w_down``) by input columns;
+    everything else is replicated."""
+    hd = cfg.head_dim
+    hq, hkv = cfg.n_heads * hd, cfg.n_kv_heads * hd
+    out = {}
+
+    def rows(t, sections):
+        parts, start = [], 0
+        for n in sections:
+            k = n // tp
+            parts.append(t[start + r * k:start + (r + 1) * k])
+            start += n
+        return torch.cat(parts, 0).contiguous()
+
+    for k, t in full.items():
+        if k in ("wqkv", "b_qkv"):
+            out[k] = rows(t, (hq, hkv, hkv))
+        elif k in ("w_up", "b_up"):
+            out[k] = rows(t, (cfg.ffn, cfg.ffn) if cfg.family == "llama" else (cfg.ffn,))
+        elif k in ("wo", "w_down"):
+            n = t.shape[1] // tp
+            out[k] = t[:, r * n:(r + 1) * n].contiguous()
+        else:
+            out[k] = t
+    return out
+
+
+def shard_params_for_tp(cfg: ModelConfig, full: dict, tp: int, r: int) -> dict:
+    out = {k: v for k, v in full.items() if k != "layers"}
+    out["layers"] = {name: shard_layer_for_tp(cfg, layer, tp, r) for name, layer in full["layers"].items()}
+    return out
