@@ -35,6 +35,10 @@ class DistComm:
             self.send_stream = torch.cuda.Stream(device)
             self.recv_stream = torch.cuda.Stream(device)
 
+    def _tag(self, tid: int, k: int) -> int:
+        """Message tag: gloo needs a distinct tag per message in flight between a pair; NCCL ignores tags."""
+        return 0 if self.cuda else (tid * 64 + k) % (1 << 30)
+
     def peer(self, mpmd_rank: int) -> int:
         """Global process rank of my positional counterpart in pipeline rank ``mpmd_rank``."""
         return self.mesh.unstack[mpmd_rank].flat_devices[self.pos_in_stage].process_index
@@ -59,7 +63,10 @@ class DistComm:
                 self.send_stream.wait_event(ready)
                 works = dist.batch_isend_irecv([dist.P2POp(dist.isend, t, peer) for t in tensors])
         else:
-            works = dist.batch_isend_irecv([dist.P2POp(dist.isend, t, peer) for t in tensors])
+            # gloo: one message per transfer (all arrays packed into one byte buffer)
+            packed = torch.cat([t.reshape(-1).view(torch.uint8) for t in tensors]) if len(tensors) > 1 else tensors[0]
+            tensors = [packed]
+            works = [dist.isend(packed, peer, tag=self._tag(ins.tid, 0))]
         self.inflight_send[ins.tid] = (tensors, works)
 
     def recv(self, st, ins: Transfer, prog: Program):
@@ -78,10 +85,20 @@ class DistComm:
                     w.wait()  # orders recv_stream after the NCCL stream; does not block the host
                 done = torch.cuda.Event()
                 done.record()
-            token = (works, done)
+            token = [works, done, False]
         else:
-            works = dist.batch_isend_irecv([dist.P2POp(dist.irecv, b, peer) for b in bufs])
-            token = (works, None)
+            if len(bufs) > 1:
+                sizes = [b.numel() * b.element_size() for b in bufs]
+                packed = torch.empty(sum(sizes), dtype=torch.uint8)
+                views, off = [], 0
+                for b, n in zip(bufs, sizes):
+                    views.append(packed[off:off + n].view(b.dtype).view(b.shape))
+                    off += n
+                bufs = views
+                works = [dist.irecv(packed, peer, tag=self._tag(ins.tid, 0))]
+            else:
+                works = [dist.irecv(bufs[0], peer, tag=self._tag(ins.tid, 0))]
+            token = [works, None, False]
         for v, b in zip(ins.vids, bufs):
             st.env[v] = b
             self.pending_recv[v] = token
@@ -92,7 +109,10 @@ class DistComm:
             token = self.pending_recv.pop(v, None)
             if token is None:
                 continue
-            works, done = token
+            works, done, waited = token
+            if waited:  # another array of the same transfer already waited (a gloo work must be waited once)
+                continue
+            token[2] = True
             if done is not None:
                 torch.cuda.current_stream(self.device).wait_event(done)
             else:

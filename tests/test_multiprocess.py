@@ -1,0 +1,34 @@
+"""Multi-process runs on one node over gloo (CPU ranks): the per-rank programs, the point-to-point backend,
+tensor-parallel ops and resharding, each against a locally computed oracle."""
+import os
+import sys
+
+import pytest
+
+from jaxpp_b200.launch import launch
+
+WORKER = os.path.join(os.path.dirname(os.path.abspath(__file__)), "mp_worker.py")
+
+
+def run(scenario, nproc):
+    rc = launch([WORKER, scenario], nproc, env={"CUDA_VISIBLE_DEVICES": "", "OMP_NUM_THREADS": "1"}, timeout_s=300)
+    assert rc == 0, f"scenario {scenario} failed with exit code {rc}"
+
+
+@pytest.mark.parametrize("scenario,nproc", [
+    ("pp_std1f1b", 2), ("pp_interleaved", 2), ("pp_zb", 3), ("pp_dualpipev", 2),
+])
+def test_pipeline_ranks_as_processes(scenario, nproc):
+    run(scenario, nproc)
+
+
+def test_tensor_parallel_two_ranks():
+    run("tp2", 2)
+
+
+def test_pipeline_times_tensor_parallel():
+    run("pp2_tp2", 4)
+
+
+def test_reshard_round_trip():
+    run("reshard", 4)
