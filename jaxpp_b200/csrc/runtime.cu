@@ -4,6 +4,7 @@
 #include "common.cuh"
 
 #include <cstdio>
+#include <cstring>
 #include <mutex>
 
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -83,3 +84,36 @@ JPB_API int jpb_num_sms() {
 }
 
 JPB_API const char* jpb_build_info() { return "jaxpp_b200 native kernels, sm_100a, CUDA " JPB_STR(CUDART_VERSION); }
+
+// ---- symmetric (peer-mapped) device memory through CUDA IPC ---------------------------------------------------
+// Every rank allocates the same number of bytes, publishes the 64-byte handle, and opens its peers' handles;
+// the kernels then address peers' buffers with plain pointers over NVLink.
+JPB_API int jpb_ipc_alloc(long long bytes, void** ptr, unsigned char* handle_out /* 64 bytes */) {
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, size_t(bytes));
+  if (e != cudaSuccess) return int(e);
+  e = cudaMemset(p, 0, size_t(bytes));
+  if (e != cudaSuccess) return int(e);
+  cudaIpcMemHandle_t h;
+  e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) return int(e);
+  static_assert(sizeof(h) == 64, "unexpected IPC handle size");
+  memcpy(handle_out, &h, 64);
+  *ptr = p;
+  return 0;
+}
+
+JPB_API int jpb_ipc_open(const unsigned char* handle, void** ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  return int(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+}
+
+JPB_API int jpb_ipc_close(void* ptr) { return int(cudaIpcCloseMemHandle(ptr)); }
+JPB_API int jpb_ipc_free(void* ptr) { return int(cudaFree(ptr)); }
+JPB_API int jpb_memset_async(void* ptr, int value, long long bytes, void* stream) {
+  return int(cudaMemsetAsync(ptr, value, size_t(bytes), static_cast<cudaStream_t>(stream)));
+}
+JPB_API int jpb_memcpy_async(void* dst, const void* src, long long bytes, void* stream) {
+  return int(cudaMemcpyAsync(dst, src, size_t(bytes), cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
+}

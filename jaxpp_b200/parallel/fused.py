@@ -1,0 +1,150 @@
+"""Fused tensor-parallel GEMMs: all-gather→GEMM and GEMM→reduce-scatter in one sm_100a kernel each.
+
+Python side of ``csrc/gemm_comm_sm100.cu``: picks the symmetric workspace of the mesh axis, stages this
+rank's shard into its own slot of the gather buffer, fills the call descriptor (epoch, buffer parity, peer
+pointers) and launches.  Shapes the kernel does not cover (token counts that are not a multiple of
+128 x ranks, feature counts that are not a multiple of 8) fall back to the NCCL twin in ``tp.py`` — loudly
+countable through ``FALLBACKS``.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ..ops import core as ops
+from ..ops import native
+from . import symm
+from . import tp as tpmod
+
+FALLBACKS = [0]
+_bound = False
+
+GATHER_ROWS, GATHER_RED = 1, 2
+
+
+def _lib():
+    global _bound
+    lib = native.load()
+    if not _bound:
+        p, i = ctypes.c_void_p, ctypes.c_int
+        lib.jpb_comm_gemm.argtypes = [p, p, p, p] + [i] * 11 + [ctypes.POINTER(symm.JpbCommDesc), p]
+        lib.jpb_memcpy_async.argtypes = [p, p, ctypes.c_longlong, p]
+        _bound = True
+    return lib
+
+
+def _bf16_2d(t: torch.Tensor) -> torch.Tensor:
+    t = t.reshape(-1, t.shape[-1])
+    if t.dtype != torch.bfloat16:
+        raise native.NativeError(f"fused tensor-parallel GEMMs take bfloat16, got {t.dtype}")
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _launch(a, b, out, bias, M, N, K, lda, ldb, a_mn, b_mn, accumulate, desc):
+    rc = _lib().jpb_comm_gemm(
+        None if a is None else a.data_ptr(), None if b is None else b.data_ptr(), out.data_ptr(),
+        None if bias is None else bias.data_ptr(), M, N, K, lda, ldb, out.stride(0), int(a_mn), int(b_mn),
+        int(out.dtype == torch.float32), int(accumulate), int(bias is not None and bias.dtype == torch.float32),
+        ctypes.byref(desc), native._stream())
+    native._check(rc, "jpb_comm_gemm")
+
+
+def _stage(ws: symm.CommWorkspace, desc, shard: torch.Tensor):
+    """Copy this rank's shard into its slot of G (device-to-device, on the current stream)."""
+    nbytes = shard.numel() * shard.element_size()
+    native._check(_lib().jpb_memcpy_async(ws.own_gather_slot(desc, nbytes), shard.data_ptr(), nbytes, native._stream()),
+                  "jpb_memcpy_async", 0)
+
+
+def _rows_ok(rows_total: int, n: int) -> bool:
+    return rows_total % (128 * n) == 0
+
+
+def ag_linear(x, w, bias, axis):
+    """y = all_gather_rows(x) @ w^T (+ bias)"""
+    n = tpmod.axis_size(axis)
+    x2, w2 = _bf16_2d(x), _bf16_2d(w)
+    Ml, K = x2.shape
+    M, N = Ml * n, w2.shape[0]
+    if not _rows_ok(M, n) or K % 8 or N % 8:
+        FALLBACKS[0] += 1
+        return ops.linear(tpmod._all_gather_rows(x, axis), w, bias)
+    ws = symm.workspace_for(axis, M * K * 2, 0)
+    desc = ws.next_call(GATHER_ROWS, False, False, (n - 1) * (Ml // 128))
+    _stage(ws, desc, x2)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    _launch(None, w2, out, bias.contiguous() if bias is not None else None, M, N, K, K, w2.stride(0), False, False, False, desc)
+    return out
+
+
+def ag_dgrad(dy_shard, w, axis):
+    """(dx, dy_full): dy_full = all_gather_rows(dy_shard), dx = dy_full @ w"""
+    n = tpmod.axis_size(axis)
+    dy2, w2 = _bf16_2d(dy_shard), _bf16_2d(w)  # w: [Nred, Kout]
+    Ml, Nred = dy2.shape
+    M, Kout = Ml * n, w2.shape[1]
+    if not _rows_ok(M, n) or Nred % 8 or Kout % 8:
+        FALLBACKS[0] += 1
+        full = tpmod._all_gather_rows(dy_shard, axis)
+        return ops.linear_dgrad(full, w), full
+    ws = symm.workspace_for(axis, M * Nred * 2, 0)
+    desc = ws.next_call(GATHER_ROWS, False, False, (n - 1) * (Ml // 128))
+    _stage(ws, desc, dy2)
+    dx = torch.empty(M, Kout, dtype=torch.bfloat16, device=dy_shard.device)
+    _launch(None, w2, dx, None, M, Kout, Nred, Nred, w2.stride(0), False, True, False, desc)
+    full = torch.empty(M, Nred, dtype=torch.bfloat16, device=dy_shard.device)
+    # every chunk has been pulled by the time the kernel ends: G now holds the gathered dy
+    native._check(_lib().jpb_memcpy_async(full.data_ptr(), desc.g[ws.rank], M * Nred * 2, native._stream()),
+                  "jpb_memcpy_async", 0)
+    return dx, full
+
+
+def ag_wgrad(dy, x_shard, axis, out_dtype=None):
+    """dW = dy^T @ all_gather_rows(x_shard); the gather runs along the reduction (token) dimension"""
+    n = tpmod.axis_size(axis)
+    dy2, x2 = _bf16_2d(dy), _bf16_2d(x_shard)
+    T, Nout = dy2.shape
+    Tl, Kin = x2.shape
+    out_dtype = out_dtype or torch.bfloat16
+    if T != Tl * n or T % (64 * n) or Nout % 8 or Kin % 8 or (n * (Tl // 64)) > 4096:
+        FALLBACKS[0] += 1
+        return ops.linear_wgrad(dy, tpmod._all_gather_rows(x_shard, axis), out_dtype)
+    ws = symm.workspace_for(axis, T * Kin * 2, 0)
+    desc = ws.next_call(GATHER_RED, True, False, (n - 1) * (Tl // 64))
+    _stage(ws, desc, x2)
+    out = torch.empty(Nout, Kin, dtype=out_dtype, device=dy.device)
+    _launch(dy2, None, out, None, Nout, Kin, T, Nout, Kin, True, True, False, desc)
+    return out
+
+
+def linear_rs(x, w, axis):
+    """y_shard = reduce_scatter_rows(x @ w^T)"""
+    n = tpmod.axis_size(axis)
+    x2, w2 = _bf16_2d(x), _bf16_2d(w)
+    M, K = x2.shape
+    N = w2.shape[0]
+    if not _rows_ok(M, n) or K % 8 or N % 8:
+        FALLBACKS[0] += 1
+        return tpmod._reduce_scatter_rows(ops.linear(x, w, None), axis)
+    ws = symm.workspace_for(axis, 0, M * N * 2)
+    desc = ws.next_call(0, False, True, 0)
+    out = torch.empty(M // n, N, dtype=torch.bfloat16, device=x.device)
+    _launch(x2, w2, out, None, M, N, K, x2.stride(0), w2.stride(0), False, False, False, desc)
+    return out
+
+
+def dgrad_rs(dy, w, axis):
+    """dx_shard = reduce_scatter_rows(dy @ w)"""
+    n = tpmod.axis_size(axis)
+    dy2, w2 = _bf16_2d(dy), _bf16_2d(w)  # w: [Nred, Kout]
+    M, Nred = dy2.shape
+    Kout = w2.shape[1]
+    if not _rows_ok(M, n) or Nred % 8 or Kout % 8:
+        FALLBACKS[0] += 1
+        return tpmod._reduce_scatter_rows(ops.linear_dgrad(dy, w), axis)
+    ws = symm.workspace_for(axis, 0, M * Kout * 2)
+    desc = ws.next_call(0, False, True, 0)
+    out = torch.empty(M // n, Kout, dtype=torch.bfloat16, device=dy.device)
+    _launch(dy2, w2, out, None, M, Kout, Nred, dy2.stride(0), w2.stride(0), False, True, False, desc)
+    return out

@@ -1,0 +1,125 @@
+"""Symmetric (peer-mapped) GPU memory for the fused compute+collective kernels.
+
+A :class:`SymmetricBuffer` is one ``cudaMalloc`` allocation of the same size on every rank of a process
+group whose CUDA IPC handles have been exchanged, so that each process holds a device pointer to every
+peer's copy (NVLink peer access).  A :class:`CommWorkspace` bundles what one family of fused GEMMs needs:
+a control block of flags, a double-buffered gather buffer and a double-buffered receive buffer, plus the
+host-side epoch / counter bookkeeping the kernels' flag protocol relies on.  Allocation and rendezvous
+happen once per (group, shape) and are reused by every layer.
+
+The reference has no counterpart (its collectives are XLA's); this is the layer the B200 design adds.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native
+
+
+class SymmetricBuffer:
+    def __init__(self, nbytes: int, group, group_ranks: list[int]):
+        lib = native.load()
+        lib.jpb_ipc_alloc.argtypes = [ctypes.c_longlong, ctypes.POINTER(ctypes.c_void_p), ctypes.c_char_p]
+        lib.jpb_ipc_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]
+        lib.jpb_ipc_close.argtypes = [ctypes.c_void_p]
+        lib.jpb_ipc_free.argtypes = [ctypes.c_void_p]
+        self.lib = lib
+        self.nbytes = nbytes
+        self.group = group
+        self.n = len(group_ranks)
+        self.rank = group_ranks.index(dist.get_rank())
+        ptr = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        native._check(lib.jpb_ipc_alloc(nbytes, ctypes.byref(ptr), handle), "jpb_ipc_alloc", 0)
+        self.local_ptr = ptr.value
+        handles: list[Any] = [None] * self.n
+        dist.all_gather_object(handles, handle.raw, group=group)
+        self.ptrs: list[int] = []
+        for q, h in enumerate(handles):
+            if q == self.rank:
+                self.ptrs.append(self.local_ptr)
+                continue
+            peer = ctypes.c_void_p()
+            native._check(lib.jpb_ipc_open(h, ctypes.byref(peer)), "jpb_ipc_open", 0)
+            self.ptrs.append(peer.value)
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+
+    def close(self):
+        for q, p in enumerate(self.ptrs):
+            if q != self.rank and p:
+                self.lib.jpb_ipc_close(p)
+        if self.local_ptr:
+            self.lib.jpb_ipc_free(self.local_ptr)
+        self.ptrs, self.local_ptr = [], None
+
+
+class JpbCommDesc(ctypes.Structure):
+    _fields_ = [
+        ("n_ranks", ctypes.c_int), ("rank", ctypes.c_int), ("epoch", ctypes.c_int), ("gather", ctypes.c_int),
+        ("gathered_is_b", ctypes.c_int), ("scatter", ctypes.c_int), ("counter_target", ctypes.c_longlong),
+        ("ctrl", ctypes.c_void_p * 8), ("g", ctypes.c_void_p * 8), ("r", ctypes.c_void_p * 8),
+    ]
+
+
+class CommWorkspace:
+    """Control block + double-buffered gather (G) and receive (R) buffers for one process group."""
+
+    def __init__(self, group, group_ranks: list[int], g_bytes: int, r_bytes: int):
+        lib = native.load()
+        lib.jpb_comm_ctrl_bytes.restype = ctypes.c_longlong
+        align = lambda x: (x + 1023) // 1024 * 1024
+        self.ctrl_bytes = align(lib.jpb_comm_ctrl_bytes())
+        self.g_bytes, self.r_bytes = align(max(g_bytes, 16)), align(max(r_bytes, 16))
+        total = self.ctrl_bytes + 2 * self.g_bytes + 2 * self.r_bytes
+        self.buf = SymmetricBuffer(total, group, group_ranks)
+        self.n, self.rank = self.buf.n, self.buf.rank
+        self.epoch = 0
+        self.pulled_total = 0  # cumulative number of chunks pulled by this rank (mirrors the device counter)
+
+    def next_call(self, gather: int, gathered_is_b: bool, scatter: bool, remote_chunks: int) -> JpbCommDesc:
+        self.epoch += 1
+        parity = self.epoch & 1
+        self.pulled_total += remote_chunks
+        d = JpbCommDesc()
+        d.n_ranks, d.rank, d.epoch = self.n, self.rank, self.epoch
+        d.gather, d.gathered_is_b, d.scatter = gather, int(gathered_is_b), int(scatter)
+        d.counter_target = self.pulled_total
+        for q in range(self.n):
+            base = self.buf.ptrs[q]
+            d.ctrl[q] = base
+            d.g[q] = base + self.ctrl_bytes + parity * self.g_bytes
+            d.r[q] = base + self.ctrl_bytes + 2 * self.g_bytes + parity * self.r_bytes
+        return d
+
+    def own_gather_slot(self, desc: JpbCommDesc, slot_bytes: int) -> int:
+        """Device address of this rank's slot inside its own G of the current parity."""
+        return desc.g[self.rank] + self.rank * slot_bytes
+
+
+_WORKSPACES: dict[Any, CommWorkspace] = {}
+
+
+def workspace_for(axis: str, g_bytes: int, r_bytes: int) -> CommWorkspace:
+    """One workspace per mesh axis, grown (re-allocated collectively) when a larger shape shows up.  All
+    ranks of the axis call this with the same arguments in the same order."""
+    from ..mesh import MpmdMesh
+
+    mesh = MpmdMesh.current()
+    group = mesh.axis_group(axis)
+    ranks = [d.process_index for d in mesh.peers_along(axis)]
+    key = (axis, tuple(ranks))
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.g_bytes < g_bytes or ws.r_bytes < r_bytes:
+        if ws is not None:
+            torch.cuda.synchronize()
+            dist.barrier(group=group)
+            g_bytes, r_bytes = max(g_bytes, ws.g_bytes), max(r_bytes, ws.r_bytes)
+            ws.buf.close()
+        ws = CommWorkspace(group, ranks, g_bytes, r_bytes)
+        _WORKSPACES[key] = ws
+    return ws

@@ -140,13 +140,13 @@ def _dgrad_rs_impl(dy, w, axis):
     return _reduce_scatter_rows(ops.linear_dgrad(dy, w), axis)
 
 
-def _ag_wgrad_impl(dy, x_shard, axis):
+def _ag_wgrad_impl(dy, x_shard, axis, out_dtype=None):
     """dW = dy^T @ all_gather(x_shard)"""
     if _fused(dy) and axis_size(axis) > 1:
         from . import fused
 
-        return fused.ag_wgrad(dy, x_shard, axis)
-    return ops.linear_wgrad(dy, _all_gather_rows(x_shard, axis))
+        return fused.ag_wgrad(dy, x_shard, axis, out_dtype)
+    return ops.linear_wgrad(dy, _all_gather_rows(x_shard, axis), out_dtype)
 
 
 def _ag_dgrad_impl(dy_shard, w, axis):
@@ -174,9 +174,11 @@ _lib.impl("dgrad_rs", _dgrad_rs_impl, "CompositeExplicitAutograd")
 torch.library.register_fake(
     "b200tp::dgrad_rs", lambda dy, w, axis: dy.new_empty(dy.shape[0] // axis_size(axis), w.shape[1])
 )
-_lib.define("ag_wgrad(Tensor dy, Tensor x_shard, str axis) -> Tensor")
+_lib.define("ag_wgrad(Tensor dy, Tensor x_shard, str axis, ScalarType? out_dtype=None) -> Tensor")
 _lib.impl("ag_wgrad", _ag_wgrad_impl, "CompositeExplicitAutograd")
-torch.library.register_fake("b200tp::ag_wgrad", lambda dy, x, axis: dy.new_empty(dy.shape[1], x.shape[1]))
+torch.library.register_fake(
+    "b200tp::ag_wgrad", lambda dy, x, axis, out_dtype=None: dy.new_empty(dy.shape[1], x.shape[1], dtype=out_dtype or dy.dtype)
+)
 _lib.define("ag_dgrad(Tensor dy_shard, Tensor w, str axis) -> (Tensor, Tensor)")
 _lib.impl("ag_dgrad", _ag_dgrad_impl, "CompositeExplicitAutograd")
 torch.library.register_fake(
@@ -196,7 +198,7 @@ def _ag_linear_bwd(ctx, dy):
     x, w = ctx.saved_tensors
     dy = dy.contiguous()
     dx = torch.ops.b200tp.dgrad_rs(dy, w, ctx.axis) if ctx.needs_input_grad[0] else None
-    dw = torch.ops.b200tp.ag_wgrad(dy, x, ctx.axis) if ctx.needs_input_grad[1] else None
+    dw = torch.ops.b200tp.ag_wgrad(dy, x, ctx.axis, ops.WGRAD_DTYPE[0]) if ctx.needs_input_grad[1] else None
     db = ops.colsum(dy) if ctx.has_bias and ctx.needs_input_grad[2] else None
     return dx, dw, db, None
 
@@ -213,7 +215,7 @@ def _linear_rs_setup(ctx, inputs, output):
 def _linear_rs_bwd(ctx, dy_shard):
     x, w = ctx.saved_tensors
     dx, dy_full = torch.ops.b200tp.ag_dgrad(dy_shard.contiguous(), w, ctx.axis)
-    dw = ops.linear_wgrad(dy_full, x) if ctx.needs_input_grad[1] else None
+    dw = ops.linear_wgrad(dy_full, x, ops.WGRAD_DTYPE[0]) if ctx.needs_input_grad[1] else None
     return (dx if ctx.needs_input_grad[0] else None), dw, None
 
 

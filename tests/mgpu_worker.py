@@ -1,0 +1,72 @@
+"""Multi-GPU worker (one process per GPU, NCCL): fused tensor-parallel kernels against their NCCL twins,
+and the pipelined language-model step across GPUs.  Run under ``jaxpp_b200.launch``."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import jaxpp_b200 as jp  # noqa: E402
+from jaxpp_b200.launch import distributed_main  # noqa: E402
+from jaxpp_b200.ops import native  # noqa: E402
+from jaxpp_b200.parallel import fused, tp  # noqa: E402
+from jaxpp_b200.utils import config  # noqa: E402
+
+
+def rnd(*shape, seed, scale=0.5):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, generator=g, device="cuda") * scale).to(torch.bfloat16)
+
+
+def close(a, b, atol, what):
+    torch.testing.assert_close(a.float(), b.float(), rtol=3e-2, atol=atol, msg=lambda m: f"{what}: {m}")
+
+
+def scenario_fused_tp():
+    n = dist.get_world_size()
+    r = dist.get_rank()
+    mesh = jp.MpmdMesh.create({"mpmd": 1, "data": 1, "model": n}, kind="cuda", multi_process=True)
+    with mesh:
+        for rep, (Ml, K, N) in enumerate([(256, 512, 768), (128 * 3, 1024, 264), (1024, 2048, 4096), (256, 512, 768)]):
+            M = Ml * n
+            x_shard, w = rnd(Ml, K, seed=10 + r + rep), rnd(N, K, seed=3 + rep, scale=0.1)
+            bias = rnd(N, seed=5)
+            with config.use_fused_collectives.set(False):
+                ref = torch.ops.b200tp.ag_linear(x_shard, w, bias, "model")
+            got = torch.ops.b200tp.ag_linear(x_shard, w, bias, "model")
+            close(got, ref, 0.05, f"ag_linear {Ml}x{K}x{N}")
+            # GEMM -> reduce-scatter
+            x_full, w_row = rnd(M, K, seed=20 + r + rep), rnd(N, K, seed=30 + r + rep, scale=0.1)
+            with config.use_fused_collectives.set(False):
+                ref = torch.ops.b200tp.linear_rs(x_full, w_row, "model")
+            got = torch.ops.b200tp.linear_rs(x_full, w_row, "model")
+            close(got, ref, 0.08, f"linear_rs {M}x{K}x{N}")
+            # backward ops
+            dy = rnd(M, N, seed=40 + r + rep)
+            with config.use_fused_collectives.set(False):
+                ref_dx = torch.ops.b200tp.dgrad_rs(dy, w, "model")
+                ref_dw = torch.ops.b200tp.ag_wgrad(dy, x_shard, "model", torch.float32)
+            close(torch.ops.b200tp.dgrad_rs(dy, w, "model"), ref_dx, 0.08, "dgrad_rs")
+            close(torch.ops.b200tp.ag_wgrad(dy, x_shard, "model", torch.float32), ref_dw, 0.05 * (M ** 0.5) / 8, "ag_wgrad")
+            dy_shard = rnd(Ml, N, seed=50 + r + rep)
+            with config.use_fused_collectives.set(False):
+                ref_dx2, ref_full = torch.ops.b200tp.ag_dgrad(dy_shard, w, "model")
+            got_dx2, got_full = torch.ops.b200tp.ag_dgrad(dy_shard, w, "model")
+            close(got_dx2, ref_dx2, 0.08, "ag_dgrad dx")
+            assert torch.equal(got_full, ref_full), "ag_dgrad gathered dy"
+        torch.cuda.synchronize()
+        assert native.read_status() == 0, "a fused kernel reported a time-out"
+        assert fused.FALLBACKS[0] == 0, f"{fused.FALLBACKS[0]} fused calls fell back to NCCL"
+    if r == 0:
+        print("fused tensor-parallel kernels match their NCCL twins", flush=True)
+
+
+SCENARIOS = {
+    "fused_tp": scenario_fused_tp,
+}
+
+if __name__ == "__main__":
+    distributed_main(SCENARIOS[sys.argv[1]], backend="nccl")
