@@ -16,6 +16,7 @@ import torch
 import torch.distributed as dist
 
 from ..compiler.program import AllGather, Program, SendDone, Transfer
+from .. import fault
 from ..mesh import MpmdMesh
 
 
@@ -54,6 +55,8 @@ class DistComm:
 
     # -- p2p ------------------------------------------------------------------------------------------
     def send(self, st, ins: Transfer, prog: Program):
+        if fault._PLAN[0] is not None and fault.transfer_action(self.rank, ins.tid) == "drop":
+            return  # injected fault: the message is never sent
         peer = self.peer(ins.dst)
         tensors = [st.env[v].contiguous() for v in ins.vids]
         if self.cuda:

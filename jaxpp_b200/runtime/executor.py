@@ -19,6 +19,7 @@ import torch
 
 from ..compiler.program import (Accum, AllGather, AllReduce, Delete, Instr, LoopIndex, Program, RunTask, SendDone,
                                 Slice, Transfer)
+from .. import fault
 from ..utils import config
 
 # ---- task timing (reference: collect_task_times_ms, jax_primitives.py:742-773) -----------------
@@ -219,6 +220,8 @@ def run_multi_controller(prog: Program, rank: int, inputs: Sequence[torch.Tensor
     comm.begin_step(st)
     for ins in prog.for_rank(rank):
         if isinstance(ins, RunTask):
+            if fault._PLAN[0] is not None:
+                fault.maybe_fail_task(rank, ins.name)
             comm.before_use(st, ins.ins)
             st.run_task(ins)
         elif isinstance(ins, Slice):
