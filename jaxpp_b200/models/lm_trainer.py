@@ -103,7 +103,7 @@ def make_train_step(cfg: tf.ModelConfig, schedule, hyper: Hyper = Hyper(), dp_ax
         n_mb, mb, seq = tokens.shape
         tokens_per_mb_local = mb * seq // cfg.tp
         total_tokens = n_mb * mb * seq * dp
-        rope = tf.rope_tables(cfg, tokens.device) if cfg.family == "llama" else None
+        rope = tf.rope_tables(cfg, tokens.device) if cfg.family in ("llama", "mixtral") else None
 
         def body(batch):
             tok, lab = batch
@@ -122,7 +122,7 @@ def make_train_step(cfg: tf.ModelConfig, schedule, hyper: Hyper = Hyper(), dp_ax
         losses, grads = jp.treduce(body, (tokens, labels), schedule=schedule)
         grads = tf.sync_replicated_grads(cfg, grads)
         if dp_axis is not None and dp > 1:
-            grads = pytree.tree_map(lambda g: tpops.all_reduce(g, dp_axis), grads)
+            grads = tf.sync_data_parallel_grads(cfg, grads, dp_axis)
         new_step = state["step"] + 1
 
         def update(p, master, g, m, v):

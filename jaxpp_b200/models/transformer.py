@@ -47,6 +47,13 @@ class ModelConfig:
     causal: bool = True
     tie_embeddings: bool = False
     recompute: bool = False  # recompute each block's activations in backward
+    # mixture of experts ("mixtral" family)
+    n_experts: int = 0
+    top_k: int = 2
+    capacity_factor: float = 1.25
+    ep: int = 1  # expert-parallel size (experts are sharded over ``ep_axis``; everything else is replicated there)
+    ep_axis: str = "data"
+    aux_coef: float = 0.01
 
     @property
     def head_dim(self) -> int:
@@ -65,7 +72,7 @@ class ModelConfig:
         d, f = self.d_model, self.ffn
         hd = self.head_dim
         attn = d * (self.n_heads + 2 * self.n_kv_heads) * hd + self.n_heads * hd * d
-        mlp = (3 if self.family == "llama" else 2) * d * f
+        mlp = (3 if self.family in ("llama", "mixtral") else 2) * d * f * max(1, self.n_experts)
         emb = self.padded_vocab * d * (1 if self.tie_embeddings or self.family == "encoder" else 2)
         return self.n_layers * (attn + mlp) + emb
 
@@ -73,7 +80,7 @@ class ModelConfig:
         """Training FLOPs per token: 6 per parameter in a matmul plus causal attention."""
         d, f, hd = self.d_model, self.ffn, self.head_dim
         attn_w = d * (self.n_heads + 2 * self.n_kv_heads) * hd + self.n_heads * hd * d
-        mlp_w = (3 if self.family == "llama" else 2) * d * f
+        mlp_w = (3 if self.family in ("llama", "mixtral") else 2) * d * f * (self.top_k if self.n_experts else 1)
         head = self.padded_vocab * d if self.family != "encoder" else 0
         matmul = 6.0 * (self.n_layers * (attn_w + mlp_w) + head)
         attn = 12.0 * self.n_layers * self.n_heads * hd * self.seq * (0.5 if self.causal else 1.0)
@@ -87,6 +94,10 @@ def llama2_7b(**kw) -> ModelConfig:
 
 def llama2_70b(**kw) -> ModelConfig:
     return ModelConfig("llama", 32000, 8192, 80, 64, 8, 28672, 4096, **kw)
+
+
+def mixtral_8x7b(**kw) -> ModelConfig:
+    return ModelConfig("mixtral", 32000, 4096, 32, 32, 8, 14336, 4096, n_experts=8, top_k=2, **kw)
 
 
 def gpt2_xl(**kw) -> ModelConfig:
@@ -126,6 +137,13 @@ def init_layer(cfg: ModelConfig, layer: int, device="cpu", seed: int = 0, tp_ran
     zeros = lambda n=d: torch.zeros(n, dtype=dtype, device=device)
     if cfg.family == "llama":
         p["w_up"] = _randn(gen, (2 * f // tp, d), std, dtype, device)  # [gate | up]
+        p["attn_norm"], p["ffn_norm"] = ones(), ones()
+    elif cfg.family == "mixtral":
+        del p["w_down"]
+        e_local = cfg.n_experts // cfg.ep
+        p["router"] = _randn(gen, (cfg.n_experts, d), std, dtype, device)
+        p["e_up"] = _randn(gen, (e_local, 2 * f, d), std, dtype, device)     # this rank's experts, [gate | up]
+        p["e_down"] = _randn(gen, (e_local, d, f), out_std, dtype, device)
         p["attn_norm"], p["ffn_norm"] = ones(), ones()
     else:
         p["w_up"] = _randn(gen, (f // tp, d), std, dtype, device)
@@ -193,6 +211,20 @@ def llama_block(cfg: ModelConfig, p: dict, x: torch.Tensor, batch: int, rope) ->
     return x
 
 
+def mixtral_block(cfg: ModelConfig, p: dict, x: torch.Tensor, batch: int, rope):
+    """Llama attention + top-k mixture-of-experts SwiGLU FFN; returns (x, load-balancing loss of this block)."""
+    from ..parallel import moe
+
+    h = ops.rmsnorm(x, p["attn_norm"], cfg.eps)[0]
+    qkv = tpops.column_linear(h, p["wqkv"], None, cfg)
+    a = _attention(cfg, qkv, batch, rope)
+    x = x + tpops.row_linear(a, p["wo"], None, cfg)
+    h = ops.rmsnorm(x, p["ffn_norm"], cfg.eps)[0]
+    y, aux = moe.moe_ffn(h, {"router": p["router"], "w_up": p["e_up"], "w_down": p["e_down"]}, cfg.n_experts, cfg.top_k,
+                         cfg.capacity_factor, cfg.ep, cfg.ep_axis)
+    return x + y, aux
+
+
 def gpt2_block(cfg: ModelConfig, p: dict, x: torch.Tensor, batch: int, rope) -> torch.Tensor:
     h = ops.layernorm(x, p["ln1_w"], p["ln1_b"], cfg.eps)[0]
     qkv = tpops.column_linear(h, p["wqkv"], p["b_qkv"], cfg)
@@ -219,8 +251,17 @@ _BLOCKS = {"llama": llama_block, "gpt2": gpt2_block, "encoder": encoder_block}
 
 def run_layers(cfg: ModelConfig, params: dict, x: torch.Tensor, batch: int, rope=None) -> torch.Tensor:
     """Apply every block in ``params['layers']`` with a stage marker after each ``layers_per_stage``."""
-    block = _BLOCKS[cfg.family]
     per = cfg.layers_per_stage
+    if cfg.family == "mixtral":
+        aux = torch.zeros((), dtype=torch.float32, device=x.device)
+        for name in sorted(params["layers"]):
+            i = int(name)
+            x, a = mixtral_block(cfg, params["layers"][name], x, batch, rope)
+            aux = aux + a
+            if (i + 1) % per == 0 and (i + 1) < cfg.n_layers:
+                x, aux = mark_stage_end((x, aux))
+        return x, aux
+    block = _BLOCKS[cfg.family]
     for name in sorted(params["layers"]):
         i = int(name)
         x = block(cfg, params["layers"][name], x, batch, rope)
@@ -253,6 +294,9 @@ def lm_loss(cfg: ModelConfig, params: dict, tokens: torch.Tensor, labels: torch.
         pos_ids = tpops.local_positions(n_local, cfg, tokens.device)
         x = x + ops.embedding(pos_ids, pos)
     x = run_layers(cfg, params, x, b, rope)
+    aux = None
+    if cfg.family == "mixtral":
+        x, aux = x
     if cfg.family == "gpt2":
         x = ops.layernorm(x, params["final_norm"], params["final_norm_b"], cfg.eps)[0]
     else:
@@ -261,6 +305,8 @@ def lm_loss(cfg: ModelConfig, params: dict, tokens: torch.Tensor, labels: torch.
     logits = ops.linear(x, head, None)
     loss, _ = ops.cross_entropy(logits, flat_lab)
     total = loss.sum()
+    if aux is not None:  # the load-balancing term is per token: scale it like the summed cross entropy
+        total = total + cfg.aux_coef * aux * flat_lab.shape[0]
     return mark_stage_end(total)
 
 
@@ -268,7 +314,7 @@ def sync_replicated_grads(cfg: ModelConfig, grads: dict) -> dict:
     """Sum over the tensor-parallel axis the gradients of parameters that are replicated across it."""
     if cfg.tp == 1:
         return grads
-    rep_layer = {"attn_norm", "ffn_norm", "ln1_w", "ln1_b", "ln2_w", "ln2_b", "b_o", "b_down"}
+    rep_layer = {"attn_norm", "ffn_norm", "ln1_w", "ln1_b", "ln2_w", "ln2_b", "b_o", "b_down", "router"}
     out = dict(grads)
     out["layers"] = {
         name: {k: (tpops.all_reduce(g, cfg.tp_axis) if k in rep_layer else g) for k, g in layer.items()}
@@ -277,6 +323,21 @@ def sync_replicated_grads(cfg: ModelConfig, grads: dict) -> dict:
     for k in ("embed", "pos", "final_norm", "final_norm_b", "lm_head"):
         if k in grads:
             out[k] = tpops.all_reduce(grads[k], cfg.tp_axis)
+    return out
+
+
+def sync_data_parallel_grads(cfg: ModelConfig, grads: dict, axis: str) -> dict:
+    """Sum gradients over the data-parallel axis.  Expert weights sharded over that axis (``e_up``/``e_down``)
+    are owned by one rank each and are left alone."""
+    sharded = {"e_up", "e_down"} if cfg.ep > 1 and cfg.ep_axis == axis else set()
+    out = dict(grads)
+    out["layers"] = {
+        name: {k: (g if k in sharded else tpops.all_reduce(g, axis)) for k, g in layer.items()}
+        for name, layer in grads["layers"].items()
+    }
+    for k, g in grads.items():
+        if k != "layers":
+            out[k] = tpops.all_reduce(g, axis)
     return out
 
 

@@ -93,3 +93,20 @@ def test_tied_embeddings_across_stages():
     got = jp.mpmd_jit_with_loop(step, cpu_mesh(2))(state, tokens, labels)
     assert got[0]["params"]["embed"].mpmd_idxs == (0, 1)  # the tied table lives on both ranks
     assert_trees_equal(ref, got, exact=False, rtol=1e-5, atol=1e-6)
+
+
+def test_mixtral_moe_pipelined_matches_unpipelined():
+    sched = jp.DualPipeV(4, 2)
+    cfg = tf.ModelConfig("mixtral", vocab=128, d_model=32, n_layers=4, n_heads=2, n_kv_heads=1, ffn=64, seq=16, n_stages=4,
+                         dtype=torch.float32, n_experts=4, top_k=2, capacity_factor=2.0)
+    step = lt.make_train_step(cfg, sched, lt.Hyper(lr=1e-2, inplace_update=False))
+    state = lt.init_state(cfg, sched, "cpu")
+    g = torch.Generator().manual_seed(2)
+    tokens = torch.randint(0, 128, (4, 2, 16), generator=g)
+    labels = torch.randint(0, 128, (4, 2, 16), generator=g)
+    ref = step(state, tokens, labels)
+    got = jp.mpmd_jit_with_loop(step, cpu_mesh(2))(state, tokens, labels)
+    assert_trees_equal(ref, got, exact=True)
+    assert got[0]["params"]["layers"]["003"]["e_up"].mpmd_idxs == (0,)  # V placement: stage 3 is back on rank 0
+    # the router gets a gradient from both the task loss and the load-balancing term
+    assert not torch.equal(local(got[0]["params"]["layers"]["000"]["router"]), state["params"]["layers"]["000"]["router"])
