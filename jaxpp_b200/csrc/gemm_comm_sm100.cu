@@ -106,17 +106,23 @@ __device__ __forceinline__ bool flag_wait_bounded(const int* flag, int want, boo
 struct TileOrder {
   int tiles_m, tiles_n, n_ranks, rank, tm_per_rank, mode;  // mode: 0 plain, 1 own-first, 2 own-last
   __device__ __forceinline__ void get(int idx, int& m_blk, int& n_blk) const {
+    // inside a row block tiles are walked in groups of 16 row tiles, column by column (L2-friendly)
+    const int rows_here = mode == 0 ? tiles_m : tm_per_rank;
+    const int per_block = rows_here * tiles_n;
+    const int blk = idx / per_block, in = idx % per_block;
+    const int per_group = 16 * tiles_n;
+    const int group = in / per_group, first_m = group * 16;
+    const int gm = (rows_here - first_m) < 16 ? (rows_here - first_m) : 16;
+    const int ing = in - group * per_group;
+    const int lm = first_m + ing % gm;
+    n_blk = ing / gm;
     if (mode == 0) {
-      m_blk = idx % tiles_m;
-      n_blk = idx / tiles_m;
+      m_blk = lm;
       return;
     }
-    const int per_block = tm_per_rank * tiles_n;
-    const int blk = idx / per_block, in = idx % per_block;
     const int shift = mode == 1 ? blk : blk + 1;
     const int slot = (rank + shift) % n_ranks;
-    m_blk = slot * tm_per_rank + in % tm_per_rank;
-    n_blk = in / tm_per_rank;
+    m_blk = slot * tm_per_rank + lm;
   }
 };
 
