@@ -16,7 +16,7 @@
 
 namespace jpb {
 
-constexpr int BWD_THREADS = 192;
+constexpr int BWD_THREADS = 320;  // TMA warp, MMA warp, 2 x 4 softmax warps (each group owns 32 of the 64 columns)
 
 struct AttnBwdParams {
   int B, Sq, Sk, H, Hkv;
@@ -103,8 +103,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     mbar_init(&bar[K1_KV], 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&bar[K1_QF + s], 1); mbar_init(&bar[K1_QE + s], 1); }
     mbar_init(&bar[K1_SF], 1);
-    mbar_init(&bar[K1_SFREE], 4);
-    mbar_init(&bar[K1_PF], 4);
+    mbar_init(&bar[K1_SFREE], 8);
+    mbar_init(&bar[K1_PF], 8);
     mbar_init(&bar[K1_PE], 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -211,36 +211,45 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const int kv = kv0 + r;
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
     const float sl2 = p.scale * 1.4426950408889634f;
+    const int grp = (warp - 2) >> 2;  // which half of the 64 query columns this warp group handles
+    const int cb = grp * 32;
     bool ok = n_iter > 0;
     for (int t = 0; t < n_iter && ok; ++t) {
       const int h = hk * G + t / per_head;
-      const int q0 = (i_start + t % per_head) * 64;
+      const int q0 = (i_start + t % per_head) * 64 + cb;
+      // per-column statistics of this block, fetched before the tensor core is done (same address in every lane)
+      const float* lse_q = p.lse + (size_t(b) * p.H + h) * p.Sq;
+      const float* dl_q = p.delta + (size_t(b) * p.H + h) * p.Sq;
+      float lq[32], dl[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const bool in = q0 + i < p.Sq;
+        lq[i] = in ? __ldg(lse_q + q0 + i) * 1.4426950408889634f : 0.f;
+        dl[i] = in ? __ldg(dl_q + q0 + i) : 0.f;
+      }
       if (!mbar_wait_bounded_warp(&bar[K1_SF], t & 1, abort_flag, p.status)) { ok = false; break; }
       tc_fence_after();
-      float sv[64], dp[64];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      float sv[32], dp[32];
+      {
         uint32_t a[32], d2[32];
-        tmem_ld_32x32(t_s + lane_addr + c * 32, a);
-        tmem_ld_32x32(t_dp + lane_addr + c * 32, d2);
+        tmem_ld_32x32(t_s + lane_addr + cb, a);
+        tmem_ld_32x32(t_dp + lane_addr + cb, d2);
         tc_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) { sv[c * 32 + i] = __uint_as_float(a[i]); dp[c * 32 + i] = __uint_as_float(d2[i]); }
+        for (int i = 0; i < 32; ++i) { sv[i] = __uint_as_float(a[i]); dp[i] = __uint_as_float(d2[i]); }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar[K1_SFREE]);
-      const float* lse_q = p.lse + (size_t(b) * p.H + h) * p.Sq;
-      const float* dl_q = p.delta + (size_t(b) * p.H + h) * p.Sq;
       const int off = p.Sk - p.Sq;
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
+      for (int i = 0; i < 32; ++i) {
         const int q = q0 + i;
         const bool visible = q < p.Sq && kv < p.Sk && (!p.causal || kv <= q + off);
         float pv = 0.f, ds = 0.f;
         if (visible) {
-          pv = exp2f(fmaf(sv[i], sl2, -__ldg(lse_q + q) * 1.4426950408889634f));
-          ds = pv * (dp[i] - __ldg(dl_q + q)) * p.scale;
+          pv = exp2f(fmaf(sv[i], sl2, -lq[i]));
+          ds = pv * (dp[i] - dl[i]) * p.scale;
         }
         sv[i] = pv;
         dp[i] = ds;
@@ -251,14 +260,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       uint8_t* tp = smem + L::OFF_P;
       uint8_t* tds = smem + L::OFF_DS;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint4 v, w;
         v.x = pack_bf16(sv[c * 8 + 0], sv[c * 8 + 1]); v.y = pack_bf16(sv[c * 8 + 2], sv[c * 8 + 3]);
         v.z = pack_bf16(sv[c * 8 + 4], sv[c * 8 + 5]); v.w = pack_bf16(sv[c * 8 + 6], sv[c * 8 + 7]);
         w.x = pack_bf16(dp[c * 8 + 0], dp[c * 8 + 1]); w.y = pack_bf16(dp[c * 8 + 2], dp[c * 8 + 3]);
         w.z = pack_bf16(dp[c * 8 + 4], dp[c * 8 + 5]); w.w = pack_bf16(dp[c * 8 + 6], dp[c * 8 + 7]);
-        st_swz(tp, r, c, v);
-        st_swz(tds, r, c, w);
+        st_swz(tp, r, grp * 4 + c, v);
+        st_swz(tds, r, grp * 4 + c, w);
       }
       fence_proxy_async();
       tc_fence_before();
@@ -270,7 +279,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     __nv_bfloat16* dv_row = p.dv + ((size_t(b) * p.Sk + kv) * p.Hkv + hk) * D;
     if (n_iter == 0) {
       if (row_ok) {
-        for (int i = 0; i < D; i += 8) {
+        for (int i = grp * (D / 2); i < (grp + 1) * (D / 2); i += 8) {
           *reinterpret_cast<uint4*>(dk_row + i) = make_uint4(0, 0, 0, 0);
           *reinterpret_cast<uint4*>(dv_row + i) = make_uint4(0, 0, 0, 0);
         }
@@ -282,7 +291,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const uint32_t src = which ? t_dk : t_dv;
         __nv_bfloat16* dst = which ? dk_row : dv_row;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = grp * (D / 64); c < (grp + 1) * (D / 64); ++c) {  // each warp group writes half of the columns
           uint32_t a[32];
           tmem_ld_32x32(src + lane_addr + c * 32, a);
           tc_wait_ld();
@@ -354,8 +363,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     mbar_init(&bar[K2_Q], 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&bar[K2_KF + s], 1); mbar_init(&bar[K2_KE + s], 1); }
     mbar_init(&bar[K2_SF], 1);
-    mbar_init(&bar[K2_SFREE], 4);
-    mbar_init(&bar[K2_DF], 4);
+    mbar_init(&bar[K2_SFREE], 8);
+    mbar_init(&bar[K2_DF], 8);
     mbar_init(&bar[K2_DE], 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -458,26 +467,27 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const float lse_r = row_ok ? p.lse[(size_t(b) * p.H + h) * p.Sq + qi] * 1.4426950408889634f : 0.f;
     const float dl_r = row_ok ? p.delta[(size_t(b) * p.H + h) * p.Sq + qi] : 0.f;
     const int off = p.Sk - p.Sq;
+    const int grp = (warp - 2) >> 2;  // which half of the 64 kv columns this warp group handles
+    const int cb = grp * 32;
     bool ok = true;
     for (int t = 0; t < n_iter && ok; ++t) {
       if (!mbar_wait_bounded_warp(&bar[K2_SF], t & 1, abort_flag, p.status)) { ok = false; break; }
       tc_fence_after();
-      float sv[64], dp[64];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      float sv[32], dp[32];
+      {
         uint32_t a[32], d2[32];
-        tmem_ld_32x32(t_s + lane_addr + c * 32, a);
-        tmem_ld_32x32(t_dp + lane_addr + c * 32, d2);
+        tmem_ld_32x32(t_s + lane_addr + cb, a);
+        tmem_ld_32x32(t_dp + lane_addr + cb, d2);
         tc_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) { sv[c * 32 + i] = __uint_as_float(a[i]); dp[c * 32 + i] = __uint_as_float(d2[i]); }
+        for (int i = 0; i < 32; ++i) { sv[i] = __uint_as_float(a[i]); dp[i] = __uint_as_float(d2[i]); }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar[K2_SFREE]);
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const int kv = t * 64 + i;
+      for (int i = 0; i < 32; ++i) {
+        const int kv = t * 64 + cb + i;
         const bool visible = row_ok && kv < p.Sk && (!p.causal || kv <= qi + off);
         float ds = 0.f;
         if (visible) {
@@ -491,11 +501,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       }
       uint8_t* tds = smem + L::OFF_DS;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint4 w;
         w.x = pack_bf16(dp[c * 8 + 0], dp[c * 8 + 1]); w.y = pack_bf16(dp[c * 8 + 2], dp[c * 8 + 3]);
         w.z = pack_bf16(dp[c * 8 + 4], dp[c * 8 + 5]); w.w = pack_bf16(dp[c * 8 + 6], dp[c * 8 + 7]);
-        st_swz(tds, r, c, w);
+        st_swz(tds, r, grp * 4 + c, w);
       }
       fence_proxy_async();
       tc_fence_before();
@@ -506,7 +516,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       tc_fence_after();
       __nv_bfloat16* dst = p.dq + ((size_t(b) * p.Sq + qi) * p.H + h) * D;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = grp * (D / 64); c < (grp + 1) * (D / 64); ++c) {
         uint32_t a[32];
         tmem_ld_32x32(t_dq + lane_addr + c * 32, a);
         tc_wait_ld();
