@@ -233,3 +233,36 @@ def test_in_shardings_and_dump(tmp_path):
     text = (tmp_path / "toy.global.0.program.txt").read_text()
     assert "task fwd_0__0" in text and "transfer#" in text
     assert "send#" in (tmp_path / "toy.local.0.rank0.program.txt").read_text()
+
+
+def test_licm_hoists_loop_invariant_casts():
+    """With JAXPP_ENABLE_LICM a cast of the parameters written inside the loop body runs once before the loop
+    (on each consumer rank) instead of once per microbatch; results are unchanged."""
+    sched = jp.Std1F1B(2)
+    params, batch = mlp_params(2, 8), torch.randn(4, 2, 8)
+
+    def step(params, batch):
+        def body(mb):
+            def loss_fn(p):
+                p = pytree.tree_map(lambda t: t.to(torch.float64), p)   # loop-invariant work
+                return ((mlp_forward(p, mb.to(torch.float64), 2) - mb) ** 2).mean().float()
+
+            return jp.value_and_grad(loss_fn)(params)
+
+        return jp.treduce(body, batch, schedule=sched)
+
+    ref = step(params, batch)
+    plain = jp.mpmd_jit_with_loop(step, cpu_mesh(2)).lower(params, batch).program
+    with config.enable_licm.set(True):
+        f = jp.mpmd_jit_with_loop(step, cpu_mesh(2))
+        hoisted = f.lower(params, batch).program
+        got = f(params, batch)
+    assert_trees_equal(ref, got, exact=True)
+
+    def casts_in(prog, name):
+        task = next(i for i in prog.instrs if isinstance(i, RunTask) and i.name == name)
+        return task.code.src.count("T[%d]" % next(k for k, t in enumerate(task.code.targets) if "_to_copy" in str(t))) \
+            if any("_to_copy" in str(t) for t in task.code.targets) else 0
+
+    assert casts_in(hoisted, "before_loop_r0") >= 5 and casts_in(plain, "fwd_0__0") >= 6
+    assert casts_in(hoisted, "fwd_0__0") == 1  # only the microbatch itself is still cast inside the loop
