@@ -1,0 +1,179 @@
+// All-reduce over NVLink peer memory in one kernel: reduce-scatter (each rank sums its slice of every peer's
+// buffer with direct peer loads, applies a scale, accumulates in fp32) followed by an all-gather of the reduced
+// slices, for gradient synchronisation across data-/tensor-parallel replicas (sum + scale + cast fused).
+//
+// Layout: every rank has a symmetric buffer X of `n` elements (its contribution, staged before the launch).
+//   phase 1  rank r reduces elements [r*S, (r+1)*S) over all ranks' X and writes the result back into its own X
+//            (other ranks read only *their* slices of this X, so the in-place write does not race);
+//   barrier  the last CTA to finish phase 1 raises this rank's "slice ready" flag in every peer;
+//   phase 2  every rank copies the reduced slices out of the owners' X into its output tensor.
+// NVSwitch gives every pair full bandwidth, so the one-shot direct pattern (no ring) is used.  All waits on peer
+// flags are bounded; flags carry an increasing epoch; X is double-buffered by call parity by the caller.
+#include "common.cuh"
+
+namespace jpb {
+
+constexpr int AR_MAX_RANKS = 8;
+
+struct AllReduceParams {
+  int n_ranks, rank, epoch;
+  long long n;                // elements
+  float scale;
+  void* x[AR_MAX_RANKS];      // symmetric buffers (x[rank] is local)
+  int* ready_peer[AR_MAX_RANKS];   // [n_ranks] ints in each rank's control block: ready_peer[q][r] = epoch when r staged X
+  int* slice_peer[AR_MAX_RANKS];   // [n_ranks] ints: slice_peer[q][r] = epoch when r finished reducing its slice
+  int* ready_local;
+  int* slice_local;
+  unsigned int* cta_counter;  // local, monotonically increasing
+  unsigned int counter_target;
+  void* out;                  // [n] result
+  int* status;
+};
+
+__device__ __forceinline__ int ar_ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void ar_st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ar_ld_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+// One thread of the CTA waits (bounded) for all peers' flags; the CTA learns the outcome through shared memory.
+__device__ __forceinline__ bool ar_wait_all(const int* flags, int n_ranks, int rank, int epoch, int* status, int* smem_ok) {
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    const uint64_t t0 = globaltimer_ns();
+    for (int q = 0; q < n_ranks && ok; ++q) {
+      if (q == rank) continue;
+      uint32_t spins = 0;
+      while (ar_ld_acquire_sys(flags + q) < epoch) {
+        if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > JPB_WAIT_BUDGET_NS) {
+          if (status) atomicCAS(status, JPB_OK, JPB_ERR_PEER_TIMEOUT);
+          ok = 0;
+          break;
+        }
+      }
+    }
+    *smem_ok = ok;
+  }
+  __syncthreads();
+  return *smem_ok != 0;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512) allreduce_kernel(const AllReduceParams p) {
+  __shared__ int ok_flag;
+  constexpr int VN = 16 / sizeof(T);
+  const long long nvec = p.n / VN;                       // n is a multiple of VN * n_ranks (checked on the host)
+  const long long slice = nvec / p.n_ranks;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    for (int q = 0; q < p.n_ranks; ++q)
+      if (q != p.rank) ar_st_release_sys(p.ready_peer[q] + p.rank, p.epoch);  // my X is staged (stream order)
+  }
+  if (!ar_wait_all(p.ready_local, p.n_ranks, p.rank, p.epoch, p.status, &ok_flag)) return;
+
+  // ---- phase 1: reduce my slice -----------------------------------------------------------------------
+  const long long base = slice * p.rank;
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < slice; v += (long long)gridDim.x * blockDim.x) {
+    float acc[VN];
+#pragma unroll
+    for (int j = 0; j < VN; ++j) acc[j] = 0.f;
+    for (int q = 0; q < p.n_ranks; ++q) {
+      const uint4 in = ar_ld_v4(static_cast<const uint8_t*>(p.x[q]) + (base + v) * 16);
+      if constexpr (sizeof(T) == 4) {
+        acc[0] += __uint_as_float(in.x); acc[1] += __uint_as_float(in.y);
+        acc[2] += __uint_as_float(in.z); acc[3] += __uint_as_float(in.w);
+      } else {
+        const float2 a = unpack_bf16(in.x), b = unpack_bf16(in.y), c = unpack_bf16(in.z), d = unpack_bf16(in.w);
+        acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+      }
+    }
+    uint4 o;
+    if constexpr (sizeof(T) == 4) {
+      o.x = __float_as_uint(acc[0] * p.scale); o.y = __float_as_uint(acc[1] * p.scale);
+      o.z = __float_as_uint(acc[2] * p.scale); o.w = __float_as_uint(acc[3] * p.scale);
+    } else {
+      o.x = pack_bf16(acc[0] * p.scale, acc[1] * p.scale); o.y = pack_bf16(acc[2] * p.scale, acc[3] * p.scale);
+      o.z = pack_bf16(acc[4] * p.scale, acc[5] * p.scale); o.w = pack_bf16(acc[6] * p.scale, acc[7] * p.scale);
+    }
+    *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.x[p.rank]) + (base + v) * 16) = o;
+    *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out) + (base + v) * 16) = o;
+  }
+  // ---- barrier: the last CTA of this rank publishes the slice to the peers ---------------------------------
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int done = atomicAdd(p.cta_counter, 1u) + 1u;
+    if (done == p.counter_target) {
+      for (int q = 0; q < p.n_ranks; ++q)
+        if (q != p.rank) ar_st_release_sys(p.slice_peer[q] + p.rank, p.epoch);
+    }
+  }
+  if (!ar_wait_all(p.slice_local, p.n_ranks, p.rank, p.epoch, p.status, &ok_flag)) return;
+
+  // ---- phase 2: gather the other ranks' reduced slices --------------------------------------------------------
+  for (int s = 1; s < p.n_ranks; ++s) {
+    const int q = (p.rank + s) % p.n_ranks;
+    const long long qbase = slice * q;
+    for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < slice; v += (long long)gridDim.x * blockDim.x)
+      *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out) + (qbase + v) * 16) =
+          ar_ld_v4(static_cast<const uint8_t*>(p.x[q]) + (qbase + v) * 16);
+  }
+}
+
+}  // namespace jpb
+
+struct JpbAllReduceDesc {
+  int n_ranks, rank, epoch, dtype;   // dtype: 0 fp32, 1 bf16
+  long long n;
+  float scale;
+  unsigned int counter_target;       // cumulative CTA count expected after this call
+  void* x[8];
+  void* ctrl[8];                     // control blocks: ints [0..7] ready, [8..15] slice, [16] CTA counter
+  void* out;
+  int grid;
+};
+
+JPB_API int jpb_allreduce_grid(long long n_elems, int elem_bytes) {
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long nvec = n_elems * elem_bytes / 16;
+  long long blocks = (nvec + 511) / 512;
+  if (blocks < 1) blocks = 1;
+  return int(blocks < sms ? blocks : sms);  // one resident CTA per SM at most: all CTAs must be co-resident
+}
+
+// In-place semantics on the staged symmetric buffers; `out` receives scale * sum over ranks.
+// n must be a multiple of (16 / elem_bytes) * n_ranks.
+JPB_API int jpb_allreduce(const JpbAllReduceDesc* d, void* stream) {
+  using namespace jpb;
+  if (!d || d->n_ranks < 2 || d->n_ranks > AR_MAX_RANKS) return -JPB_ERR_BAD_ARGUMENT;
+  const int vn = d->dtype == 0 ? 4 : 8;
+  if (d->n <= 0 || d->n % (vn * d->n_ranks) != 0) return -JPB_ERR_BAD_ARGUMENT;
+  AllReduceParams p;
+  p.n_ranks = d->n_ranks; p.rank = d->rank; p.epoch = d->epoch; p.n = d->n; p.scale = d->scale;
+  for (int q = 0; q < d->n_ranks; ++q) {
+    p.x[q] = d->x[q];
+    int* c = static_cast<int*>(d->ctrl[q]);
+    p.ready_peer[q] = c;
+    p.slice_peer[q] = c + 8;
+  }
+  int* mine = static_cast<int*>(d->ctrl[d->rank]);
+  p.ready_local = mine;
+  p.slice_local = mine + 8;
+  p.cta_counter = reinterpret_cast<unsigned int*>(mine + 16);
+  p.counter_target = d->counter_target;
+  p.out = d->out;
+  p.status = jpb_status_device_ptr();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (d->dtype == 0) allreduce_kernel<float><<<d->grid, 512, 0, s>>>(p);
+  else allreduce_kernel<__nv_bfloat16><<<d->grid, 512, 0, s>>>(p);
+  return int(cudaGetLastError());
+}

@@ -148,3 +148,73 @@ def dgrad_rs(dy, w, axis):
     out = torch.empty(M // n, Kout, dtype=torch.bfloat16, device=dy.device)
     _launch(dy2, w2, out, None, M, Kout, Nred, dy2.stride(0), w2.stride(0), False, True, False, desc)
     return out
+
+
+# ---- all-reduce over peer memory (gradient sync) -----------------------------------------------------------------
+class _AllReduceDesc(ctypes.Structure):
+    _fields_ = [("n_ranks", ctypes.c_int), ("rank", ctypes.c_int), ("epoch", ctypes.c_int), ("dtype", ctypes.c_int),
+                ("n", ctypes.c_longlong), ("scale", ctypes.c_float), ("counter_target", ctypes.c_uint),
+                ("x", ctypes.c_void_p * 8), ("ctrl", ctypes.c_void_p * 8), ("out", ctypes.c_void_p), ("grid", ctypes.c_int)]
+
+
+class _AllReduceWorkspace:
+    CTRL = 1024
+
+    def __init__(self, axis: str, nbytes: int):
+        from ..mesh import MpmdMesh
+
+        mesh = MpmdMesh.current()
+        ranks = [d.process_index for d in mesh.peers_along(axis)]
+        self.slot = (nbytes + 1023) // 1024 * 1024
+        self.buf = symm.SymmetricBuffer(self.CTRL + 2 * self.slot, mesh.axis_group(axis), ranks)
+        self.epoch = 0
+        self.ctas = 0
+
+
+_AR_WS: dict = {}
+AR_MIN_BYTES = 1 << 20  # smaller tensors are latency-bound: leave them to NCCL
+
+
+def all_reduce(x: torch.Tensor, axis: str, scale: float = 1.0) -> torch.Tensor:
+    """scale * sum over the ranks of ``axis``; fp32 or bf16, any shape (padded internally)."""
+    lib = _lib()
+    lib.jpb_allreduce.argtypes = [ctypes.POINTER(_AllReduceDesc), ctypes.c_void_p]
+    lib.jpb_allreduce_grid.argtypes = [ctypes.c_longlong, ctypes.c_int]
+    n_ranks = tpmod.axis_size(axis)
+    if x.dtype not in (torch.float32, torch.bfloat16):
+        raise native.NativeError(f"fused all_reduce takes float32 or bfloat16, got {x.dtype}")
+    flat = x.contiguous().view(-1)
+    vn = 16 // flat.element_size()
+    quantum = vn * n_ranks
+    n = (flat.numel() + quantum - 1) // quantum * quantum
+    nbytes = n * flat.element_size()
+    ws = _AR_WS.get(axis)
+    if ws is None or ws.slot < nbytes:
+        if ws is not None:
+            torch.cuda.synchronize()
+            ws.buf.close()
+        ws = _AllReduceWorkspace(axis, max(nbytes, 64 << 20))
+        _AR_WS[axis] = ws
+    ws.epoch += 1
+    parity = ws.epoch & 1
+    d = _AllReduceDesc()
+    d.n_ranks, d.rank, d.epoch = ws.buf.n, ws.buf.rank, ws.epoch
+    d.dtype = 0 if flat.dtype == torch.float32 else 1
+    d.n, d.scale = n, float(scale)
+    d.grid = lib.jpb_allreduce_grid(n, flat.element_size())
+    ws.ctas += d.grid
+    d.counter_target = ws.ctas & 0xFFFFFFFF
+    for q in range(ws.buf.n):
+        d.ctrl[q] = ws.buf.ptrs[q]
+        d.x[q] = ws.buf.ptrs[q] + ws.CTRL + parity * ws.slot
+    out = torch.empty(n, dtype=flat.dtype, device=x.device)
+    d.out = out.data_ptr()
+    stream = native._stream()
+    mine = d.x[ws.buf.rank]
+    native._check(lib.jpb_memcpy_async(mine, flat.data_ptr(), flat.numel() * flat.element_size(), stream), "stage", 0)
+    if n > flat.numel():
+        lib.jpb_memset_async.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p]
+        native._check(lib.jpb_memset_async(mine + flat.numel() * flat.element_size(), 0,
+                                           (n - flat.numel()) * flat.element_size(), stream), "pad", 0)
+    native._check(lib.jpb_allreduce(ctypes.byref(d), stream), "jpb_allreduce")
+    return out[:flat.numel()].view(x.shape)

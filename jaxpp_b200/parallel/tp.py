@@ -75,6 +75,11 @@ def _reduce_scatter_rows(x: Tensor, axis: str) -> Tensor:
 def _all_reduce_impl(x: Tensor, axis: str) -> Tensor:
     if axis_size(axis) == 1:
         return x
+    if _fused(x) and x.dtype in (torch.float32, torch.bfloat16):
+        from . import fused
+
+        if x.numel() * x.element_size() >= fused.AR_MIN_BYTES:
+            return fused.all_reduce(x, axis)
     out = x.contiguous().clone()
     dist.all_reduce(out, group=_group(axis))
     return out

@@ -57,6 +57,15 @@ def scenario_fused_tp():
             got_dx2, got_full = torch.ops.b200tp.ag_dgrad(dy_shard, w, "model")
             close(got_dx2, ref_dx2, 0.08, "ag_dgrad dx")
             assert torch.equal(got_full, ref_full), "ag_dgrad gathered dy"
+        # all-reduce over peer memory (three calls: both buffer parities and a reuse)
+        for rep, (numel, dt) in enumerate([(3 * 1024 * 1024 + 5, torch.float32), (2 * 1024 * 1024, torch.bfloat16),
+                                           (1024 * 1024 + 3, torch.float32)]):
+            g = torch.Generator(device="cuda").manual_seed(70 + r + rep)
+            t = torch.randn(numel, generator=g, device="cuda").to(dt)
+            ref = t.clone()
+            dist.all_reduce(ref)
+            got = fused.all_reduce(t, "model", 1.0)
+            close(got, ref, 1e-5 if dt == torch.float32 else 0.05, f"all_reduce {numel} {dt}")
         torch.cuda.synchronize()
         assert native.read_status() == 0, "a fused kernel reported a time-out"
         assert fused.FALLBACKS[0] == 0, f"{fused.FALLBACKS[0]} fused calls fell back to NCCL"
