@@ -698,3 +698,53 @@ JPB_API int jpb_adamw(int grad_dt, int out_dt, const float* p, const void* g, co
 #undef ADAMW
   return LAST_ERR;
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// RMSNorm backward without a caller-provided scratch buffer (see jaxpp_b200_noalloc.h)
+// ---------------------------------------------------------------------------------------------------------
+#include "jaxpp_b200_noalloc.h"
+
+// Partial dW sums of the no-allocation entry point: [JPB_NOALLOC_MAX_PARTS][2][JPB_NOALLOC_MAX_H] floats.
+static __device__ __align__(256) float g_noalloc_scratch[JPB_NOALLOC_MAX_PARTS * 2 * JPB_NOALLOC_MAX_H];
+// Device address of the array above, per device; the symbol itself is only a host-side handle.
+static float* g_noalloc_scratch_ptr[64] = {nullptr};
+
+JPB_API const char* jpb_noalloc_strerror(int code) {
+  switch (code) {
+    case JPB_NOALLOC_OK: return "ok";
+    case JPB_NOALLOC_ERR_TOO_LARGE: return "row length exceeds JPB_NOALLOC_MAX_H (8192): the built-in scratch array is too small";
+    case JPB_NOALLOC_ERR_BAD_SHAPE: return "rows and H must be positive and H a multiple of 4 (float32) or 8 (bfloat16)";
+    case JPB_NOALLOC_ERR_BAD_DTYPE: return "dtype must be 0 (float32) or 1 (bfloat16)";
+    case JPB_NOALLOC_ERR_SETUP: return "cudaGetSymbolAddress failed for the built-in scratch array";
+    default: return code > 0 ? "CUDA launch error (cudaError_t)" : "unknown error";
+  }
+}
+
+JPB_API int jpb_rmsnorm_bwd_noalloc(int dtype, const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                                    void* dw, int rows, int H, void* stream) {
+  if (dtype != 0 && dtype != 1) return JPB_NOALLOC_ERR_BAD_DTYPE;
+  const int vn = dtype == 0 ? 4 : 8;
+  if (rows <= 0 || H <= 0 || H % vn != 0) return JPB_NOALLOC_ERR_BAD_SHAPE;
+  if (H > JPB_NOALLOC_MAX_H) return JPB_NOALLOC_ERR_TOO_LARGE;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return JPB_NOALLOC_ERR_SETUP;
+  if (g_noalloc_scratch_ptr[dev] == nullptr) {
+    // once per device, with that device current: turn the symbol into a device pointer
+    float* ptr = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch) != cudaSuccess || ptr == nullptr)
+      return JPB_NOALLOC_ERR_SETUP;
+    g_noalloc_scratch_ptr[dev] = ptr;
+  }
+  float* scratch = g_noalloc_scratch_ptr[dev];
+  const int grid = rows < JPB_NOALLOC_MAX_PARTS ? rows : JPB_NOALLOC_MAX_PARTS;
+  return dispatch_dtype(dtype, [&](auto tag) {
+    using T = decltype(tag);
+    constexpr int VN = Vec<T>::N;
+    const int threads = norm_threads(H, VN, NORM_BWD_VECS);
+    // every CTA writes its whole partial row before the reduction reads it: nothing has to be cleared
+    norm_bwd_kernel<T, false><<<grid, threads, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)w, nullptr, rstd, (T*)dx,
+                                                            scratch, rows, H);
+    reduce_partials_kernel<T><<<(H + 255) / 256, 256, 0, STREAM>>>(scratch, (T*)dw, grid, H, size_t(2) * H);
+    return LAST_ERR;
+  });
+}
