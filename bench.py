@@ -130,6 +130,7 @@ def main():
     native.load()
     if args.nccl_only:
         config.use_fused_collectives._override = False
+    config.transfer_done_delay._override = 2  # release sent activations two sends later instead of at step end
 
     pp, tp, vstages, mb = LAYOUTS[n]
     n_stages = pp * vstages
@@ -142,6 +143,8 @@ def main():
         cfg = dataclasses.replace(cfg, n_layers=args.layers)
     schedule = jp.Interleaved1F1B(n_stages, pp) if vstages > 1 else jp.Std1F1B(pp)
     mesh = jp.MpmdMesh.create({"mpmd": pp, "data": 1, "model": tp}, kind="cuda", multi_process=world > 1)
+    if world > 1 and tp > 1:
+        mesh.axis_group("model")  # created collectively, up front
     my_pp = mesh.my_mpmd_axis_index if world > 1 else None
     tp_rank = mesh.axis_index("model") if world > 1 and tp > 1 else 0
 
