@@ -132,6 +132,82 @@ def scenario_pp_tp(pp, tp, schedule):
         pass
 
 
+def scenario_dp_ep(family):
+    """2 pipeline ranks x 2 data-parallel ranks.  ``gpt2``: plain data parallelism (gradients all-reduced over
+    the data axis); ``mixtral``: the data axis doubles as the expert-parallel axis (experts sharded, tokens
+    exchanged with all-to-all).  Oracle: the un-sharded step on the concatenated batch."""
+    pp, dp = 2, 2
+    mesh = jp.MpmdMesh.create({"mpmd": pp, "data": dp, "model": 1}, kind=device().type, multi_process=True)
+    dev = device()
+    sched = jp.Std1F1B(2)
+    base = dict(vocab=250, d_model=32, n_layers=2, n_heads=2, n_kv_heads=2, ffn=64, seq=16, dtype=torch.float32, n_stages=2)
+    # aux_coef 0: the load-balancing statistics are per rank by design, so only the task loss is comparable
+    moe = dict(n_experts=4, top_k=2, capacity_factor=8.0, aux_coef=0.0) if family == "mixtral" else {}
+    cfg1 = tf.ModelConfig(family, **base, **moe)
+    cfgd = tf.ModelConfig(family, **base, **moe, ep=dp if family == "mixtral" else 1)
+    hyper = lt.Hyper(lr=1e-2, inplace_update=False)
+    n_mb, mb = 2, 4
+    g = torch.Generator().manual_seed(9)
+    tokens = torch.randint(0, 250, (n_mb, mb, 16), generator=g)
+    labels = torch.randint(0, 250, (n_mb, mb, 16), generator=g)
+    state1 = lt.init_state(cfg1, sched, "cpu")
+    ref_state, ref_losses = lt.make_train_step(cfg1, sched, hyper)(state1, tokens, labels)
+    me_pp, me_dp = mesh.my_mpmd_axis_index, mesh.axis_index("data")
+    owners = lt.owner_ranks(cfgd, sched)
+    e_local = cfgd.n_experts // cfgd.ep if family == "mixtral" else 0
+
+    def shard_experts(k, v):
+        if family == "mixtral" and k in ("e_up", "e_down"):
+            return v[me_dp * e_local:(me_dp + 1) * e_local]
+        return v
+
+    def local_view(tree):
+        out = {}
+        for key in ("params", "master", "m", "v"):
+            full = tree[key]
+            sel = {"layers": {}}
+            for name, layer in full["layers"].items():
+                mine = owners[int(name)] == me_pp
+                sel["layers"][name] = {}
+                for k, v in layer.items():
+                    v = shard_experts(k, v)
+                    sel["layers"][name][k] = v.to(dev) if mine else jp.ShapeDtypeStruct(tuple(v.shape), v.dtype)
+            for k, v in full.items():
+                if k == "layers":
+                    continue
+                grp = "embed" if k in ("embed", "pos") else "head"
+                sel[k] = v.to(dev) if owners[grp] == me_pp else jp.ShapeDtypeStruct(tuple(v.shape), v.dtype)
+            out[key] = sel
+        out["step"] = tree["step"].to(dev)
+        return out
+
+    step = lt.make_train_step(cfgd, sched, hyper, dp_axis="data", dp=dp)
+    f = jp.mpmd_jit_with_loop(step, mesh)
+    half = mb // dp  # this data-parallel rank's sequences of every microbatch
+    tok_l = tokens[:, me_dp * half:(me_dp + 1) * half].contiguous().to(dev)
+    lab_l = labels[:, me_dp * half:(me_dp + 1) * half].contiguous().to(dev)
+    got_state, got_losses = f(local_view(state1), tok_l, lab_l)
+    ref_local = local_view(ref_state)
+    # with capacity-based routing the per-rank capacity differs from the single-rank run only if tokens are dropped;
+    # the generous capacity factor above keeps every token, so results agree up to reassociation
+    n = 0
+    for key in ("params", "m"):
+        a = pytree.tree_leaves(ref_local[key], is_leaf=lambda x: isinstance(x, jp.ShapeDtypeStruct))
+        b = pytree.tree_leaves(got_state[key], is_leaf=lambda x: isinstance(x, jp.MpmdArray))
+        for x, y in zip(a, b):
+            t = y.local_tensor()
+            if isinstance(x, jp.ShapeDtypeStruct):
+                assert t is None
+                continue
+            if key == "m":  # first moment = (1 - beta1) * gradient: linear in the gradient
+                torch.testing.assert_close(t.cpu(), x.cpu(), rtol=1e-3, atol=1e-7)
+            else:  # Adam's first step is +-lr per element: reassociation noise flips the sign where g ~ 0
+                bad = ((t.cpu() - x.cpu()).abs() > 5e-4).float().mean().item()
+                assert bad < 0.01, f"{bad:.3%} of a parameter tensor differs"
+            n += 1
+    assert n > 0
+
+
 def scenario_reshard():
     """SPMD -> MPMD -> SPMD round trip of arrays with several partition specs."""
     from jaxpp_b200.array import DistArray, MpmdSharding, mpmd_to_spmd_reshard, spmd_to_mpmd_reshard
@@ -171,6 +247,8 @@ SCENARIOS = {
     "pp2_tp2": lambda: scenario_pp_tp(2, 2, jp.Interleaved1F1B(4, 2)),
     "tp2": lambda: scenario_pp_tp(1, 2, jp.Std1F1B(1)),
     "reshard": scenario_reshard,
+    "pp2_dp2_gpt2": lambda: scenario_dp_ep("gpt2"),
+    "pp2_ep2_mixtral": lambda: scenario_dp_ep("mixtral"),
 }
 
 if __name__ == "__main__":

@@ -32,3 +32,11 @@ def test_pipeline_times_tensor_parallel():
 
 def test_reshard_round_trip():
     run("reshard", 4)
+
+
+def test_pipeline_times_data_parallel():
+    run("pp2_dp2_gpt2", 4)
+
+
+def test_pipeline_times_expert_parallel_moe():
+    run("pp2_ep2_mixtral", 4)
