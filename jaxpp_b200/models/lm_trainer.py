@@ -140,3 +140,27 @@ def make_train_step(cfg: tf.ModelConfig, schedule, hyper: Hyper = Hyper(), dp_ax
         return new_state, losses
 
     return step
+
+
+def param_specs(cfg: tf.ModelConfig, params_like: dict) -> dict:
+    """PartitionSpec of every parameter (global view = concatenation of the shards along the sharded dim).
+
+    Note that the global row order of ``wqkv`` / ``w_up`` is shard-major ([q_r | k_r | v_r] per rank): restoring a
+    checkpoint with a different tensor-parallel size needs the rows regrouped (``transformer.shard_layer_for_tp``
+    defines the canonical-to-shard mapping)."""
+    P = jp.PartitionSpec
+    tp, ep = cfg.tp_axis if cfg.tp > 1 else None, cfg.ep_axis if cfg.ep > 1 else None
+    col = {"wqkv": P(tp, None), "w_up": P(tp, None), "b_qkv": P(tp), "b_up": P(tp)}
+    row = {"wo": P(None, tp), "w_down": P(None, tp)}
+    exp = {"e_up": P(ep, None, None), "e_down": P(ep, None, None)}
+
+    def layer(ld):
+        return {k: col.get(k) or row.get(k) or exp.get(k) or P() for k in ld}
+
+    # same key order as the parameter tree (pytrees flatten dicts in insertion order)
+    return {k: ({name: layer(ld) for name, ld in v.items()} if k == "layers" else P()) for k, v in params_like.items()}
+
+
+def state_specs(cfg: tf.ModelConfig, state_like: dict) -> dict:
+    ps = param_specs(cfg, state_like["params"])
+    return {k: (jp.PartitionSpec() if k == "step" else ps) for k in state_like}

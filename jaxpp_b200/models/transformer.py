@@ -249,6 +249,54 @@ def encoder_block(cfg: ModelConfig, p: dict, x: torch.Tensor, batch: int, rope) 
 _BLOCKS = {"llama": llama_block, "gpt2": gpt2_block, "encoder": encoder_block}
 
 
+class _Recompute(torch.autograd.Function):
+    """Run ``fn`` without keeping its activations; re-run it in backward (full activation recompute of a block).
+    Captured steps see the re-run as ordinary ops inside the backward task of the stage."""
+
+    @staticmethod
+    def forward(ctx, fn, *args):
+        ctx.fn = fn
+        with torch.no_grad():
+            out = fn(*args)
+        ctx.save_for_backward(*[a for a in args if isinstance(a, torch.Tensor)])
+        ctx.is_tensor = [isinstance(a, torch.Tensor) for a in args]
+        ctx.others = [a for a in args if not isinstance(a, torch.Tensor)]
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        saved, others = list(ctx.saved_tensors), list(ctx.others)
+        args = []
+        for is_t in ctx.is_tensor:
+            if is_t:
+                a = saved.pop(0)
+                args.append(a.detach().requires_grad_(a.is_floating_point()))
+            else:
+                args.append(others.pop(0))
+        with torch.enable_grad():
+            out = ctx.fn(*args)
+            diff = [a for a in args if isinstance(a, torch.Tensor) and a.requires_grad]
+            grads = list(torch.autograd.grad(out, diff, g, allow_unused=True))
+        res = [None]
+        for a in args:
+            res.append(grads.pop(0) if isinstance(a, torch.Tensor) and a.requires_grad else None)
+        return tuple(res)
+
+
+def _maybe_recompute(cfg: ModelConfig, block, p: dict, x: torch.Tensor, batch: int, rope):
+    if not cfg.recompute:
+        return block(cfg, p, x, batch, rope)
+    keys = sorted(p)
+    rope_t = list(rope) if rope is not None else []
+
+    def fn(x_, *flat):
+        params = dict(zip(keys, flat[:len(keys)]))
+        r = tuple(flat[len(keys):]) if rope is not None else None
+        return block(cfg, params, x_, batch, r)
+
+    return _Recompute.apply(fn, x, *[p[k] for k in keys], *rope_t)
+
+
 def run_layers(cfg: ModelConfig, params: dict, x: torch.Tensor, batch: int, rope=None) -> torch.Tensor:
     """Apply every block in ``params['layers']`` with a stage marker after each ``layers_per_stage``."""
     per = cfg.layers_per_stage
@@ -264,7 +312,7 @@ def run_layers(cfg: ModelConfig, params: dict, x: torch.Tensor, batch: int, rope
     block = _BLOCKS[cfg.family]
     for name in sorted(params["layers"]):
         i = int(name)
-        x = block(cfg, params["layers"][name], x, batch, rope)
+        x = _maybe_recompute(cfg, block, params["layers"][name], x, batch, rope)
         if (i + 1) % per == 0 and (i + 1) < cfg.n_layers:
             x = mark_stage_end(x)
     return x

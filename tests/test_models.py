@@ -110,3 +110,31 @@ def test_mixtral_moe_pipelined_matches_unpipelined():
     assert got[0]["params"]["layers"]["003"]["e_up"].mpmd_idxs == (0,)  # V placement: stage 3 is back on rank 0
     # the router gets a gradient from both the task loss and the load-balancing term
     assert not torch.equal(local(got[0]["params"]["layers"]["000"]["router"]), state["params"]["layers"]["000"]["router"])
+
+
+def test_activation_recompute_matches_and_moves_forward_ops_into_backward():
+    from jaxpp_b200.compiler.program import RunTask
+
+    sched = jp.ZeroBubble(2)
+    kw = dict(vocab=128, d_model=32, n_layers=2, n_heads=2, n_kv_heads=2, ffn=64, seq=16, n_stages=2, dtype=torch.float32)
+    g = torch.Generator().manual_seed(2)
+    tokens = torch.randint(0, 128, (2, 2, 16), generator=g)
+    labels = torch.randint(0, 128, (2, 2, 16), generator=g)
+    outs, progs = [], []
+    for rec in (False, True):
+        cfg = tf.ModelConfig("llama", recompute=rec, **kw)
+        step = lt.make_train_step(cfg, sched, lt.Hyper(lr=1e-2, inplace_update=False))
+        state = lt.init_state(cfg, sched, "cpu")
+        f = jp.mpmd_jit_with_loop(step, cpu_mesh(2))
+        outs.append(f(state, tokens, labels))
+        progs.append(f.lower(state, tokens, labels).program)
+    assert_trees_equal(pytree.tree_map(local, outs[0], is_leaf=lambda x: isinstance(x, jp.MpmdArray)), outs[1], exact=True)
+
+    def n_attn(prog, name):
+        t = next(i for i in prog.instrs if isinstance(i, RunTask) and i.name == name)
+        return sum("b200.attention.default" in str(x) for x in t.code.targets)
+
+    assert n_attn(progs[0], "bwdA_1__0") == 0 and n_attn(progs[1], "bwdA_1__0") == 1  # forward re-run inside backward
+    # and the forward task hands fewer activations to the backward task
+    fwd = lambda prog: next(i for i in prog.instrs if isinstance(i, RunTask) and i.name == "fwd_1__0")
+    assert len(fwd(progs[1]).outs) < len(fwd(progs[0]).outs)

@@ -1,0 +1,24 @@
+"""The training driver end to end on CPU ranks: run, checkpoint, resume, metrics file."""
+import json
+import os
+import sys
+
+from jaxpp_b200.launch import launch
+
+
+def test_train_driver_checkpoint_and_resume(tmp_path):
+    ck, mt = str(tmp_path / "ckpt"), str(tmp_path / "m.jsonl")
+    base = ["-m", "jaxpp_b200.train", "--config", "llama7b_pp2tp2", "--tiny", "--device", "cpu", "--ckpt-dir", ck,
+            "--ckpt-every", "2", "--metrics", mt, "--lr", "0.01"]
+    env = {"CUDA_VISIBLE_DEVICES": "", "OMP_NUM_THREADS": "1",
+           "PYTHONPATH": os.path.dirname(os.path.dirname(os.path.abspath(__file__)))}
+    assert launch(base + ["--steps", "2"], 4, env=env, timeout_s=300) == 0
+    assert os.path.exists(os.path.join(ck, "step_00000002", "manifest.json"))
+    manifest = json.load(open(os.path.join(ck, "step_00000002", "manifest.json")))["entries"]
+    wq = manifest["params/layers/000/wqkv"]
+    assert wq["spec"] == ["model", None] and len(wq["shards"]) == 2          # one file per tensor-parallel shard
+    assert len(manifest["params/layers/000/attn_norm"]["shards"]) == 1      # replicated: written once
+    assert launch(base + ["--steps", "2", "--resume"], 4, env=env, timeout_s=300) == 0
+    recs = [json.loads(l) for l in open(mt)]
+    assert [r["step"] for r in recs] == [0, 1, 2, 3] and all(r["tokens_per_s"] > 0 for r in recs)
+    assert os.path.exists(os.path.join(ck, "step_00000004", "manifest.json"))
