@@ -31,8 +31,33 @@ def _nccl_paths():
         return None, None
 
 
+STAMP = os.path.join(OUT_DIR, "libjaxpp_b200.stamp")
+
+
 def sources():
     return sorted(f for f in os.listdir(HERE) if f.endswith((".cu", ".cpp")))
+
+
+def source_hash() -> str:
+    """Hash of everything the library is built from; written next to the library after a successful link so
+    that a loader can tell a stale binary from a current one."""
+    import hashlib
+
+    h = hashlib.sha256()
+    for f in sorted(os.listdir(HERE)):
+        if f.endswith((".cu", ".cpp", ".cuh", ".h", ".hpp")):
+            h.update(f.encode())
+            with open(os.path.join(HERE, f), "rb") as fh:
+                h.update(fh.read())
+    return h.hexdigest()
+
+
+def is_current() -> bool:
+    try:
+        with open(STAMP) as f:
+            return os.path.exists(LIB) and f.read().strip() == source_hash()
+    except OSError:
+        return False
 
 
 def build(verbose: bool = False, force: bool = False) -> str:
@@ -70,6 +95,25 @@ def build(verbose: bool = False, force: bool = False) -> str:
         if res.returncode != 0:
             sys.stderr.write(res.stdout + res.stderr)
             raise RuntimeError("link failed")
+    with open(STAMP, "w") as f:
+        f.write(source_hash())
+    return LIB
+
+
+def ensure_current() -> str:
+    """Build if the library is missing or older than its sources; safe to call from several processes."""
+    import fcntl
+
+    if is_current():
+        return LIB
+    os.makedirs(OUT_DIR, exist_ok=True)
+    with open(os.path.join(OUT_DIR, ".build.lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not is_current():
+                build()
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return LIB
 
 

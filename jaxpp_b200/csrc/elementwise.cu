@@ -148,6 +148,19 @@ __global__ void norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
     const int v = threadIdx.x + i * blockDim.x;
     if (v < nvec) { Vec<T> wv; wv.load(w + v * VN); wv.to_float(wf[i]); }
   }
+  // the next row's x and dy are requested before this row's block reduction, so that loads stay in flight
+  // across the barrier
+  Vec<T> xv[NORM_BWD_VECS], dv[NORM_BWD_VECS];
+  if (blockIdx.x < rows) {
+#pragma unroll
+    for (int i = 0; i < NORM_BWD_VECS; ++i) {
+      const int v = threadIdx.x + i * blockDim.x;
+      if (v < nvec) {
+        xv[i].load(x + size_t(blockIdx.x) * H + v * VN);
+        dv[i].load(dy + size_t(blockIdx.x) * H + v * VN);
+      }
+    }
+  }
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const float rstd = rstd_in[row];
     const float mean = LAYER ? mean_in[row] : 0.f;
@@ -157,11 +170,8 @@ __global__ void norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
     for (int i = 0; i < NORM_BWD_VECS; ++i) {
       const int v = threadIdx.x + i * blockDim.x;
       if (v < nvec) {
-        Vec<T> xv, dv;
-        xv.load(x + size_t(row) * H + v * VN);
-        dv.load(dy + size_t(row) * H + v * VN);
         float xf[VN], df[VN];
-        xv.to_float(xf); dv.to_float(df);
+        xv[i].to_float(xf); dv[i].to_float(df);
 #pragma unroll
         for (int j = 0; j < VN; ++j) {
           xh[i][j] = (xf[j] - mean) * rstd;
@@ -170,6 +180,17 @@ __global__ void norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
           s[1] += g[i][j] * xh[i][j];
           dw_acc[i][j] += df[j] * xh[i][j];
           db_acc[i][j] += df[j];
+        }
+      }
+    }
+    const int next = row + gridDim.x;
+    if (next < rows) {
+#pragma unroll
+      for (int i = 0; i < NORM_BWD_VECS; ++i) {
+        const int v = threadIdx.x + i * blockDim.x;
+        if (v < nvec) {
+          xv[i].load(x + size_t(next) * H + v * VN);
+          dv[i].load(dy + size_t(next) * H + v * VN);
         }
       }
     }

@@ -1,15 +1,19 @@
 // Tensor-parallel GEMMs fused with their collective over NVLink peer memory (sm_100a).
 //
 // One persistent kernel per op; the tcgen05 main loop is the one of gemm_sm100.cu (TMA ring -> tcgen05.mma
-// -> double-buffered TMEM accumulators -> epilogue warps) plus a seventh "comm" warp per CTA.
+// -> double-buffered TMEM accumulators -> epilogue warps) plus four "comm" warps per CTA.
 //
-//  all-gather -> GEMM   The gathered operand lives in a symmetric buffer G[n_ranks][rows_per_rank, width]
-//                       that exists on every rank; a rank's own slot is filled before the launch.  Comm
-//                       warps pull the peers' slots over NVLink (plain 16-byte peer loads, each byte crosses
-//                       the link once) into the local copy of G chunk by chunk and publish a flag per chunk;
-//                       the TMA producer runs the tiles (or k-blocks) that depend only on the local slot
-//                       first and waits on the chunk flag before it touches a pulled chunk.  The gather can
-//                       be along the rows of A (forward / dgrad) or along the reduction dimension (wgrad).
+//  all-gather -> GEMM   Every rank owns a symmetric buffer G[n_ranks][rows_per_rank, width].  The comm warps
+//                       of rank r PUSH r's shard straight from the tensor it lives in into slot r of every
+//                       peer's G (coalesced 16-byte peer stores, posted writes, each byte crosses the link
+//                       once, no staging copy), in 16 KiB pieces spread over all comm warps of the grid; the
+//                       warp that completes a chunk raises the chunk's flag in the receiver's memory.  The
+//                       TMA producer reads the tiles (or k-blocks) of the own shard directly from the shard
+//                       (its own tensor map) and runs them first; it waits on the chunk flag before it
+//                       touches a chunk a peer pushes.  The gather can be along the rows of A (forward /
+//                       dgrad) or along the reduction dimension (wgrad).  Optionally the comm warps also
+//                       assemble the complete gathered operand in an ordinary local tensor (own shard +
+//                       received chunks) while the tensor cores work, for a later local GEMM.
 //  GEMM -> reduce-scatter
 //                       Output row block p belongs to rank p.  Tiles of the peers' blocks are computed first;
 //                       their epilogue stores the bf16 partial tile straight into the owner's receive buffer
@@ -28,9 +32,12 @@ constexpr int CSTAGES = 4;
 constexpr int CA_BYTES = CBM * CBK * 2;
 constexpr int CB_BYTES = CBN * CBK * 2;
 constexpr int CSTAGE_BYTES = CA_BYTES + CB_BYTES;
-constexpr int COMM_THREADS = 224;  // TMA, MMA, 4 epilogue warps, comm warp
-constexpr int CSMEM_BYTES = CSTAGES * CSTAGE_BYTES + 1024 + 256;
+constexpr int COMM_WARPS = 4;
+constexpr int COMM_THREADS = 32 * (6 + COMM_WARPS);  // TMA, MMA, 4 epilogue warps, comm warps
+constexpr int EPI_STAGE_BYTES = 4 * 32 * 128;        // per epilogue warp: 32 rows x 64 bf16, swizzled
+constexpr int CSMEM_BYTES = CSTAGES * CSTAGE_BYTES + EPI_STAGE_BYTES + 1024 + 256;
 constexpr int MAX_RANKS = 8;
+constexpr int PIECE_BYTES = 16384;
 
 enum GatherMode : int { GATHER_NONE = 0, GATHER_ROWS = 1, GATHER_RED = 2 };
 
@@ -41,18 +48,25 @@ struct CommGemmParams {
   void* D;
   int* status;
   int tiles_m, tiles_n;
+  int a_blocked, b_blocked;          // MN-major operand through a 3-D map {64, K, MN/64}: one copy per stage
   // --- collective ---
   int n_ranks, rank;
   int epoch;                         // > 0, increases with every call on this workspace
   // all-gather
   int gather;                        // GatherMode
+  int gathered_is_b;                 // GATHER_RED: which operand is the gathered one
   int chunks_per_rank;               // m-tiles (GATHER_ROWS) or k-blocks (GATHER_RED) per rank slot
+  int rows_per_slot;                 // rows of G per rank slot
+  int pieces;                        // pieces per chunk
   long long chunk_bytes;             // contiguous bytes of one chunk inside G
+  long long piece_bytes;
+  const uint8_t* own_src;            // this rank's shard [rows_per_slot, width], contiguous
+  uint8_t* gather_out;               // optional: complete gathered operand, assembled locally
   uint8_t* g_local;                  // this rank's G
-  const uint8_t* g_peer[MAX_RANKS];  // every rank's G as mapped here (g_peer[rank] == g_local)
-  int* chunk_flags;                  // local, [n_ranks * chunks_per_rank]
-  int* ready_local;                  // local, [n_ranks]: ready_local[p] == epoch  <=> peer p's own slot is valid
-  int* ready_peer[MAX_RANKS];        // the same array in every peer's memory
+  uint8_t* g_peer[MAX_RANKS];        // every rank's G as mapped here (g_peer[rank] == g_local)
+  int* chunk_flags;                  // local, [n_ranks * chunks_per_rank], slot q is written by rank q
+  int* chunk_flags_peer[MAX_RANKS];  // the same array in every peer's memory
+  int* piece_count;                  // local scratch, [n_ranks * chunks_per_rank], zero between calls
   // reduce-scatter
   int scatter;                       // 0/1
   __nv_bfloat16* r_local;            // receive buffer [n_ranks][rows_per_rank, N] (slot = source rank)
@@ -132,13 +146,28 @@ __device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
   return v;
 }
 
+// One warp copies `len` bytes (a multiple of 16, both pointers 16-byte aligned) with 16 loads in flight per lane.
+__device__ __forceinline__ void copy_piece(uint8_t* dst, const uint8_t* src, long long len, int lane) {
+  const long long nvec = len / 16;
+  long long v = lane;
+  for (; v + 15 * 32 < nvec; v += 16 * 32) {
+    uint4 r[16];
+#pragma unroll
+    for (int u = 0; u < 16; ++u) r[u] = ld_volatile_v4(src + (v + u * 32) * 16);
+#pragma unroll
+    for (int u = 0; u < 16; ++u) *reinterpret_cast<uint4*>(dst + (v + u * 32) * 16) = r[u];
+  }
+  for (; v < nvec; v += 32) *reinterpret_cast<uint4*>(dst + v * 16) = ld_volatile_v4(src + v * 16);
+}
+
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(COMM_THREADS, 1)
 comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 const CommGemmParams p, int* done_counter, long long counter_target) {
+                 const __grid_constant__ CUtensorMap map_own, const CommGemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + CSTAGES * CSTAGE_BYTES);
+  uint8_t* epi_stage = smem + CSTAGES * CSTAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + CSTAGES * CSTAGE_BYTES + EPI_STAGE_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + CSTAGES;
   uint64_t* acc_full = bars + 2 * CSTAGES;
@@ -164,11 +193,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     fence_barrier_init();
     tma_prefetch_desc(&map_a);
     tma_prefetch_desc(&map_b);
-    if (blockIdx.x == 0 && p.gather != GATHER_NONE) {
-      // this rank's own slot of G was filled before the launch: tell every peer it may be pulled
-      for (int q = 0; q < p.n_ranks; ++q)
-        if (q != p.rank) st_release_sys(p.ready_peer[q] + p.rank, p.epoch);
-    }
+    if (p.gather != GATHER_NONE) tma_prefetch_desc(&map_own);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
@@ -181,23 +206,32 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (lane == 0) {
       uint32_t it = 0, armed = 0, armed_phase = 0;
       bool ok = true;
-      bool all_pulled = p.gather == GATHER_NONE;
+      // Chunk flags only grow, so a chunk seen once stays valid: in reduction-gather mode every tile walks
+      // the same chunks in the same order and only the first tile of this CTA polls.
+      int red_verified = 0;
       auto chunk_ready = [&](int chunk) -> bool {
-        if (all_pulled) return true;
-        if (chunk / p.chunks_per_rank == p.rank) return true;
-        if (!flag_wait_bounded(p.chunk_flags + chunk, p.epoch, false, abort_flag, p.status, JPB_ERR_PEER_TIMEOUT)) return false;
-        if ((long long)ld_acquire_gpu(done_counter) >= counter_target) all_pulled = true;
+        if (!flag_wait_bounded(p.chunk_flags + chunk, p.epoch, true, abort_flag, p.status, JPB_ERR_PEER_TIMEOUT)) return false;
         fence_proxy_async_global();
         return true;
       };
+      // own ranges, so that the k loop below needs no division
+      const int own_row0 = p.rank * p.rows_per_slot;
+      const int own_lo = p.rank * p.chunks_per_rank, own_hi = own_lo + p.chunks_per_rank;
+      const bool rows_mode = p.gather == GATHER_ROWS, red_mode = p.gather == GATHER_RED;
+      const bool gathered_a = red_mode && !p.gathered_is_b, gathered_b = red_mode && p.gathered_is_b;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int m_blk, n_blk;
         order.get(tile, m_blk, n_blk);
         const int m0 = m_blk * CBM, n0 = n_blk * CBN;
-        if (p.gather == GATHER_ROWS && !chunk_ready(m_blk)) { ok = false; break; }
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int kbe = (kb + k_rot) % k_blocks;
-          if (p.gather == GATHER_RED && !chunk_ready(kbe)) { ok = false; break; }
+        const bool own_rows = rows_mode && m_blk >= own_lo && m_blk < own_hi;
+        if (rows_mode && !own_rows && !chunk_ready(m_blk)) { ok = false; break; }
+        int kbe = k_rot;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it, kbe = (kbe + 1 == k_blocks ? 0 : kbe + 1)) {
+          const bool own_k = red_mode && kbe >= own_lo && kbe < own_hi;
+          if (red_mode && !own_k && kb >= red_verified) {
+            if (!chunk_ready(kbe)) { ok = false; break; }
+            red_verified = kb + 1;
+          }
           const int s = it % CSTAGES;
           const uint32_t ph = (it / CSTAGES) & 1;
           if (!mbar_wait_bounded(&empty[s], ph ^ 1, abort_flag, p.status)) { ok = false; break; }
@@ -208,16 +242,31 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           armed_phase = (armed_phase & ~(1u << s)) | (ph << s);
           const int k0 = kbe * CBK;
           if (!A_MN) {
-            tma_load_2d(sa, &map_a, &full[s], k0, m0);
+            if (own_rows) tma_load_2d(sa, &map_own, &full[s], k0, m0 - own_row0);
+            else tma_load_2d(sa, &map_a, &full[s], k0, m0);
           } else {
+            const bool a_own = own_k && gathered_a;
+            const CUtensorMap* ma = a_own ? &map_own : &map_a;
+            const int ka = a_own ? k0 - own_row0 : k0;
+            if (p.a_blocked) {
+              tma_load_3d(sa, ma, &full[s], 0, ka, m0 >> 6);
+            } else {
 #pragma unroll
-            for (int j = 0; j < CBM / 64; ++j) tma_load_2d(sa + j * 8192, &map_a, &full[s], m0 + j * 64, k0);
+              for (int j = 0; j < CBM / 64; ++j) tma_load_2d(sa + j * 8192, ma, &full[s], m0 + j * 64, ka);
+            }
           }
           if (!B_MN) {
             tma_load_2d(sb, &map_b, &full[s], k0, n0);
           } else {
+            const bool b_own = own_k && gathered_b;
+            const CUtensorMap* mb = b_own ? &map_own : &map_b;
+            const int kbk = b_own ? k0 - own_row0 : k0;
+            if (p.b_blocked) {
+              tma_load_3d(sb, mb, &full[s], 0, kbk, n0 >> 6);
+            } else {
 #pragma unroll
-            for (int j = 0; j < CBN / 64; ++j) tma_load_2d(sb + j * 8192, &map_b, &full[s], n0 + j * 64, k0);
+              for (int j = 0; j < CBN / 64; ++j) tma_load_2d(sb + j * 8192, mb, &full[s], n0 + j * 64, kbk);
+            }
           }
         }
       }
@@ -257,39 +306,57 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (ok) umma_commit(&acc_full[acc]);
       }
     }
-  } else if (warp == 6) {
-    // ------------------------------------------ comm warp: pull peers' slots ----------------------------
+  } else if (warp >= 6) {
+    // ------------------------------------------ comm warps: push the own shard to every peer ------------
     if (p.gather != GATHER_NONE) {
-      const int remote_chunks = (p.n_ranks - 1) * p.chunks_per_rank;
-      int ready_seen = 0;  // bit q set once peer q announced its slot
-      bool ok = true;
-      for (int idx = blockIdx.x; idx < remote_chunks && ok; idx += gridDim.x) {
-        const int slot = (p.rank + 1 + idx / p.chunks_per_rank) % p.n_ranks;
-        const int chunk = slot * p.chunks_per_rank + idx % p.chunks_per_rank;
-        if (!(ready_seen & (1 << slot))) {
-          bool w = flag_wait_bounded(p.ready_local + slot, p.epoch, true, abort_flag, p.status, JPB_ERR_PEER_TIMEOUT);
-          w = __all_sync(0xffffffffu, w);
-          if (!w) { ok = false; break; }
-          ready_seen |= 1 << slot;
-        }
-        const uint8_t* src = p.g_peer[slot] + (long long)chunk * p.chunk_bytes;
-        uint8_t* dst = p.g_local + (long long)chunk * p.chunk_bytes;
-        const long long nvec = p.chunk_bytes / 16;
-        long long v = lane;
-        for (; v + 7 * 32 < nvec; v += 8 * 32) {
-          uint4 r[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u) r[u] = ld_volatile_v4(src + (v + u * 32) * 16);
-#pragma unroll
-          for (int u = 0; u < 8; ++u) *reinterpret_cast<uint4*>(dst + (v + u * 32) * 16) = r[u];
-        }
-        for (; v < nvec; v += 32) *reinterpret_cast<uint4*>(dst + v * 16) = ld_volatile_v4(src + v * 16);
-        __threadfence();
-        fence_proxy_async_global();
+      const int n_comm = gridDim.x * COMM_WARPS;
+      const int wid = (warp - 6) * gridDim.x + blockIdx.x;
+      const int per_chunk = (p.n_ranks - 1) * p.pieces;
+      const long long total = (long long)p.chunks_per_rank * per_chunk;
+      for (long long g = wid; g < total; g += n_comm) {
+        const int c = int(g / per_chunk), rem = int(g % per_chunk);
+        const int pi = rem / p.pieces, piece = rem % p.pieces;
+        const int q = (p.rank + p.n_ranks - 1 - pi) % p.n_ranks;  // the peer that consumes this shard first goes first
+        const long long off = (long long)c * p.chunk_bytes + (long long)piece * p.piece_bytes;
+        const long long left = p.chunk_bytes - (long long)piece * p.piece_bytes;
+        const long long len = left < p.piece_bytes ? left : p.piece_bytes;
+        copy_piece(p.g_peer[q] + (long long)p.rank * p.chunks_per_rank * p.chunk_bytes + off, p.own_src + off, len, lane);
+        __threadfence_system();  // the stores of every lane are performed at the peer before the count below
         __syncwarp();
         if (lane == 0) {
-          st_release_gpu(p.chunk_flags + chunk, p.epoch);
-          atomicAdd(done_counter, 1);
+          int* cnt = p.piece_count + pi * p.chunks_per_rank + c;
+          if (atomicAdd(cnt, 1) == p.pieces - 1) {
+            *cnt = 0;  // ready for the next call; nobody else touches it before
+            __threadfence_system();
+            st_release_sys(p.chunk_flags_peer[q] + p.rank * p.chunks_per_rank + c, p.epoch);
+          }
+        }
+      }
+      if (p.gather_out != nullptr) {
+        // assemble the complete gathered operand locally: own shard first, then the chunks peers pushed
+        const long long own_total = (long long)p.chunks_per_rank * p.pieces;
+        const long long all_total = own_total * p.n_ranks;
+        bool ok = true;
+        for (long long g = wid; g < all_total && ok; g += n_comm) {
+          const int blk = int(g / own_total);           // 0: own slot, then in consumption order
+          const int slot = (p.rank + blk) % p.n_ranks;
+          const long long in = g % own_total;
+          const int c = int(in / p.pieces), piece = int(in % p.pieces);
+          const long long off = (long long)c * p.chunk_bytes + (long long)piece * p.piece_bytes;
+          const long long left = p.chunk_bytes - (long long)piece * p.piece_bytes;
+          const long long len = left < p.piece_bytes ? left : p.piece_bytes;
+          const long long slot_off = (long long)slot * p.chunks_per_rank * p.chunk_bytes;
+          const uint8_t* src = p.own_src + off;
+          if (blk != 0) {
+            int w = 1;
+            if (lane == 0)
+              w = flag_wait_bounded(p.chunk_flags + slot * p.chunks_per_rank + c, p.epoch, true, abort_flag, p.status,
+                                    JPB_ERR_PEER_TIMEOUT);
+            w = __shfl_sync(0xffffffffu, w, 0);
+            if (!w) { ok = false; break; }
+            src = p.g_local + slot_off + off;
+          }
+          copy_piece(p.gather_out + slot_off + off, src, len, lane);
         }
       }
     }
@@ -324,6 +391,42 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         w = __all_sync(0xffffffffu, w);
         if (!w) { ok = false; break; }
       }
+      if (remote) {
+        // Partial tile for a peer: transpose through shared memory so that every store instruction of the
+        // warp writes four complete 128-byte row segments into the owner's receive buffer.
+        uint8_t* stg = epi_stage + (warp - 2) * (32 * 128);
+        __nv_bfloat16* dst_rows = p.r_peer[owner] + (size_t(p.rank) * p.rows_per_rank + lm * CBM + quarter * 32) * p.N;
+#pragma unroll 1
+        for (int c2 = 0; c2 < CBN / 64; ++c2) {
+          const int col0 = n0 + c2 * 64;
+          if (col0 >= p.N) break;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + acc * CBN + c2 * 64 + half * 32, r);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 o;
+              o.x = pack_bf16(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
+              o.y = pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+              o.z = pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+              o.w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+              *reinterpret_cast<uint4*>(stg + lane * 128 + (((half * 4 + j) ^ (lane & 7)) * 16)) = o;
+            }
+          }
+          __syncwarp();
+          const int vec = lane & 7;
+          const int col = col0 + vec * 8;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = i * 4 + (lane >> 3);
+            const uint4 o = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((vec ^ (rr & 7)) * 16));
+            if (col < p.N) *reinterpret_cast<uint4*>(dst_rows + size_t(rr) * p.N + col) = o;
+          }
+          __syncwarp();
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < CBN / 32; ++c) {
         const int col0 = n0 + c * 32;
@@ -336,19 +439,6 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
         if (!row_ok) continue;
         const int ncols = (p.N - col0) < 32 ? (p.N - col0) : 32;  // N is a multiple of 8
-        if (remote) {
-          __nv_bfloat16* d = p.r_peer[owner] + (size_t(p.rank) * p.rows_per_rank + local_row) * p.N + col0;
-#pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            if (j < ncols) {
-              uint4 o;
-              o.x = pack_bf16(v[j], v[j + 1]); o.y = pack_bf16(v[j + 2], v[j + 3]);
-              o.z = pack_bf16(v[j + 4], v[j + 5]); o.w = pack_bf16(v[j + 6], v[j + 7]);
-              *reinterpret_cast<uint4*>(d + j) = o;
-            }
-          }
-          continue;
-        }
         if (p.scatter) {
           for (int q = 0; q < p.n_ranks; ++q) {
             if (q == p.rank) continue;
@@ -401,6 +491,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
         }
       }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
@@ -422,6 +513,14 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
+// 3-D bf16 map over an MN-major operand stored as [k_rows, mn contiguous], mn a multiple of 64 (see gemm_sm100.cu)
+static int comm_map_mn_blocked(CUtensorMap* out, const void* base, uint64_t mn, uint64_t k_rows, uint64_t ld_elems, uint32_t blocks) {
+  uint64_t dims[3] = {64, k_rows, mn / 64};
+  uint64_t strides[2] = {ld_elems * 2, 128};
+  uint32_t box[3] = {64, 64, blocks};
+  return jpb_make_tensor_map(out, base, 2, 3, dims, strides, box, 1);
+}
+
 // 2-D bf16 tensor map (row-major, `cols` contiguous)
 static int comm_map_2d(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint64_t ld_elems, uint32_t box_cols,
                        uint32_t box_rows) {
@@ -432,8 +531,8 @@ static int comm_map_2d(CUtensorMap* out, const void* base, uint64_t cols, uint64
 }
 
 template <bool A_MN, bool B_MN>
-static int comm_launch(const CUtensorMap& ma, const CUtensorMap& mb, const CommGemmParams& p, int* counter, long long target,
-                       cudaStream_t stream) {
+static int comm_launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CommGemmParams& p,
+                       int max_ctas, cudaStream_t stream) {
   auto kernel = comm_gemm_kernel<A_MN, B_MN>;
   static bool configured = false;
   if (!configured) {
@@ -443,21 +542,24 @@ static int comm_launch(const CUtensorMap& ma, const CUtensorMap& mb, const CommG
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  // The grid must be fully co-resident: comm warps of every CTA make progress while producers wait on them.
+  // At most one CTA per SM, so the whole grid is co-resident: the comm warps of every CTA push while the
+  // producers of the peer wait for what they push.
+  // A cap below the SM count keeps SMs free for kernels this one does not know about (point-to-point
+  // transfers of a pipeline on other streams), which must be able to run while CTAs here wait for a peer.
   const int tiles = p.tiles_m * p.tiles_n;
-  const int grid = tiles < sms ? tiles : sms;
-  kernel<<<grid, COMM_THREADS, CSMEM_BYTES, stream>>>(ma, mb, p, counter, target);
+  int grid = tiles < sms ? tiles : sms;
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  kernel<<<grid, COMM_THREADS, CSMEM_BYTES, stream>>>(ma, mb, mo, p);
   return int(cudaGetLastError());
 }
 
 }  // namespace jpb
 
 // Layout of the per-rank control block (ints) inside the symmetric workspace.
-#define JPB_CTRL_READY 0          /* [8]  */
-#define JPB_CTRL_COUNTER 8        /* [1]  */
-#define JPB_CTRL_CHUNK_FLAGS 16   /* [JPB_MAX_CHUNKS] */
 #define JPB_MAX_CHUNKS 4096
-#define JPB_CTRL_TILE_FLAGS (16 + JPB_MAX_CHUNKS) /* [8 * JPB_MAX_TILES_PER_RANK] */
+#define JPB_CTRL_CHUNK_FLAGS 16                        /* [JPB_MAX_CHUNKS] written by peers */
+#define JPB_CTRL_PIECE_COUNT (16 + JPB_MAX_CHUNKS)     /* [JPB_MAX_CHUNKS] local scratch, zero between calls */
+#define JPB_CTRL_TILE_FLAGS (16 + 2 * JPB_MAX_CHUNKS)  /* [8 * JPB_MAX_TILES_PER_RANK] written by peers */
 #define JPB_MAX_TILES_PER_RANK 8192
 #define JPB_CTRL_INTS (JPB_CTRL_TILE_FLAGS + 8 * JPB_MAX_TILES_PER_RANK)
 
@@ -466,21 +568,24 @@ struct JpbCommDesc {
   int gather;            // 0 none, 1 rows of A, 2 reduction dimension
   int gathered_is_b;     // which operand is read from G (its pointer argument is ignored)
   int scatter;
-  long long counter_target;
+  int max_ctas;          // > 0: cap on the grid (leaves SMs free for kernels of other streams), 0: one CTA per SM
   void* ctrl[8];         // control block of every rank as mapped in this process
   void* g[8];            // gather buffer (current parity) of every rank
   void* r[8];            // receive buffer (current parity) of every rank
 };
 
 JPB_API long long jpb_comm_ctrl_bytes() { return (long long)JPB_CTRL_INTS * 4; }
+JPB_API int jpb_comm_desc_bytes() { return int(sizeof(JpbCommDesc)); }  // lets a binding check its struct layout
 
 // D = A * B^T with a fused all-gather of one operand and/or reduce-scatter of the output (see file header).
-// For gather != 0 the gathered operand is G of shape [n_ranks * rows_per_rank, width] (bf16, contiguous):
+// For gather != 0 the gathered operand's pointer argument (A or B) is this rank's SHARD [rows / n_ranks, width]
+// (bf16, contiguous); the complete operand G is [n_ranks * rows_per_rank, width]:
 //   gather == 1: A = G is [M, K] K-major;  gather == 2: the gathered operand is MN-major, G is [K, M] or [K, N].
+// gather_out (optional, gather != 0): receives the complete gathered operand.
 // For scatter != 0, D is this rank's [M / n_ranks, N] block.
 JPB_API int jpb_comm_gemm(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int lda, int ldb,
                           int ldd, int a_mn_major, int b_mn_major, int out_fp32, int accumulate, int bias_fp32,
-                          const JpbCommDesc* desc, void* stream) {
+                          const JpbCommDesc* desc, void* gather_out, void* stream) {
   using namespace jpb;
   if (!desc || desc->n_ranks < 2 || desc->n_ranks > MAX_RANKS) return -JPB_ERR_BAD_ARGUMENT;
   const int n = desc->n_ranks;
@@ -495,14 +600,15 @@ JPB_API int jpb_comm_gemm(const void* A, const void* B, void* D, const void* bia
   p.n_ranks = n; p.rank = desc->rank; p.epoch = desc->epoch;
   p.gather = desc->gather; p.scatter = desc->scatter;
   int* my_ctrl = static_cast<int*>(desc->ctrl[desc->rank]);
-  p.ready_local = my_ctrl + JPB_CTRL_READY;
   p.chunk_flags = my_ctrl + JPB_CTRL_CHUNK_FLAGS;
+  p.piece_count = my_ctrl + JPB_CTRL_PIECE_COUNT;
+  p.gathered_is_b = desc->gathered_is_b;
   p.tile_flags_local = my_ctrl + JPB_CTRL_TILE_FLAGS;
   for (int q = 0; q < n; ++q) {
     int* c = static_cast<int*>(desc->ctrl[q]);
-    p.ready_peer[q] = c + JPB_CTRL_READY;
+    p.chunk_flags_peer[q] = c + JPB_CTRL_CHUNK_FLAGS;
     p.tile_flags_peer[q] = c + JPB_CTRL_TILE_FLAGS;
-    p.g_peer[q] = static_cast<const uint8_t*>(desc->g[q]);
+    p.g_peer[q] = static_cast<uint8_t*>(desc->g[q]);
     p.r_peer[q] = static_cast<__nv_bfloat16*>(desc->r[q]);
   }
   p.g_local = static_cast<uint8_t*>(desc->g[desc->rank]);
@@ -511,31 +617,61 @@ JPB_API int jpb_comm_gemm(const void* A, const void* B, void* D, const void* bia
   if (desc->scatter && (p.tiles_m / n) * p.tiles_n > JPB_MAX_TILES_PER_RANK) return -JPB_ERR_BAD_ARGUMENT;
   const void* a_ptr = A;
   const void* b_ptr = B;
+  const void* own = nullptr;
+  int own_width = 0;
   if (desc->gather == GATHER_ROWS) {
-    if (a_mn_major || desc->gathered_is_b) return -JPB_ERR_BAD_ARGUMENT;
+    if (a_mn_major || desc->gathered_is_b || !A) return -JPB_ERR_BAD_ARGUMENT;
+    own = A;
+    own_width = K;
     a_ptr = p.g_local;
     lda = K;
     p.chunks_per_rank = p.tiles_m / n;
+    p.rows_per_slot = M / n;
     p.chunk_bytes = (long long)CBM * K * 2;
   } else if (desc->gather == GATHER_RED) {
-    const int width = desc->gathered_is_b ? N : M;
-    if (desc->gathered_is_b) { if (!b_mn_major) return -JPB_ERR_BAD_ARGUMENT; b_ptr = p.g_local; ldb = N; }
-    else { if (!a_mn_major) return -JPB_ERR_BAD_ARGUMENT; a_ptr = p.g_local; lda = M; }
+    own_width = desc->gathered_is_b ? N : M;
+    if (desc->gathered_is_b) { if (!b_mn_major || !B) return -JPB_ERR_BAD_ARGUMENT; own = B; b_ptr = p.g_local; ldb = N; }
+    else { if (!a_mn_major || !A) return -JPB_ERR_BAD_ARGUMENT; own = A; a_ptr = p.g_local; lda = M; }
     p.chunks_per_rank = (K / CBK) / n;
-    p.chunk_bytes = (long long)CBK * width * 2;
+    p.rows_per_slot = K / n;
+    p.chunk_bytes = (long long)CBK * own_width * 2;
   }
-  if (desc->gather && n * p.chunks_per_rank > JPB_MAX_CHUNKS) return -JPB_ERR_BAD_ARGUMENT;
+  if (desc->gather) {
+    if (n * p.chunks_per_rank > JPB_MAX_CHUNKS || (own_width & 7)) return -JPB_ERR_BAD_ARGUMENT;
+    p.piece_bytes = p.chunk_bytes < PIECE_BYTES ? p.chunk_bytes : PIECE_BYTES;
+    p.pieces = int((p.chunk_bytes + p.piece_bytes - 1) / p.piece_bytes);
+    p.own_src = static_cast<const uint8_t*>(own);
+    p.gather_out = static_cast<uint8_t*>(gather_out);
+    if ((reinterpret_cast<uintptr_t>(own) & 15) || (reinterpret_cast<uintptr_t>(gather_out) & 15)) return -JPB_ERR_BAD_ARGUMENT;
+  }
   if ((reinterpret_cast<uintptr_t>(a_ptr) & 15) || (reinterpret_cast<uintptr_t>(b_ptr) & 15) || (lda & 7) || (ldb & 7))
     return -JPB_ERR_BAD_ARGUMENT;
-  CUtensorMap ma, mb;
-  int rc = a_mn_major ? comm_map_2d(&ma, a_ptr, M, K, lda, 64, CBK) : comm_map_2d(&ma, a_ptr, K, M, lda, CBK, CBM);
+  CUtensorMap ma, mb, mo;
+  p.a_blocked = a_mn_major && M % 64 == 0;
+  p.b_blocked = b_mn_major && N % 64 == 0;
+  int rc;
+  if (!a_mn_major) rc = comm_map_2d(&ma, a_ptr, K, M, lda, CBK, CBM);
+  else if (p.a_blocked) rc = comm_map_mn_blocked(&ma, a_ptr, M, K, lda, CBM / 64);
+  else rc = comm_map_2d(&ma, a_ptr, M, K, lda, 64, CBK);
   if (rc) return rc;
-  rc = b_mn_major ? comm_map_2d(&mb, b_ptr, N, K, ldb, 64, CBK) : comm_map_2d(&mb, b_ptr, K, N, ldb, CBK, CBN);
+  if (!b_mn_major) rc = comm_map_2d(&mb, b_ptr, K, N, ldb, CBK, CBN);
+  else if (p.b_blocked) rc = comm_map_mn_blocked(&mb, b_ptr, N, K, ldb, CBN / 64);
+  else rc = comm_map_2d(&mb, b_ptr, N, K, ldb, 64, CBK);
   if (rc) return rc;
-  int* counter = my_ctrl + JPB_CTRL_COUNTER;
+  if (desc->gather == GATHER_ROWS) {
+    rc = comm_map_2d(&mo, own, K, p.rows_per_slot, K, CBK, CBM);
+  } else if (desc->gather == GATHER_RED) {
+    const bool blocked = desc->gathered_is_b ? p.b_blocked : p.a_blocked;
+    const uint32_t blocks = desc->gathered_is_b ? CBN / 64 : CBM / 64;
+    rc = blocked ? comm_map_mn_blocked(&mo, own, own_width, p.rows_per_slot, own_width, blocks)
+                 : comm_map_2d(&mo, own, own_width, p.rows_per_slot, own_width, 64, CBK);
+  } else {
+    mo = ma;
+  }
+  if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (!a_mn_major && !b_mn_major) return comm_launch<false, false>(ma, mb, p, counter, desc->counter_target, s);
-  if (!a_mn_major && b_mn_major) return comm_launch<false, true>(ma, mb, p, counter, desc->counter_target, s);
-  if (a_mn_major && b_mn_major) return comm_launch<true, true>(ma, mb, p, counter, desc->counter_target, s);
-  return comm_launch<true, false>(ma, mb, p, counter, desc->counter_target, s);
+  if (!a_mn_major && !b_mn_major) return comm_launch<false, false>(ma, mb, mo, p, desc->max_ctas, s);
+  if (!a_mn_major && b_mn_major) return comm_launch<false, true>(ma, mb, mo, p, desc->max_ctas, s);
+  if (a_mn_major && b_mn_major) return comm_launch<true, true>(ma, mb, mo, p, desc->max_ctas, s);
+  return comm_launch<true, false>(ma, mb, mo, p, desc->max_ctas, s);
 }

@@ -39,6 +39,7 @@ struct GemmParams {
   void* D;
   int* status;
   int tiles_m, tiles_n;
+  int a_blocked, b_blocked;  // MN-major operand addressed through a 3-D map {64, K, MN/64}: one copy per stage
 };
 
 // Tile rasterisation: groups of GROUP_M row blocks are walked column by column, so that the ~148 tiles in
@@ -121,12 +122,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const int k0 = kb * BK;
           if (!A_MN) {
             tma_load_2d(sa, &map_a, &full[s], k0, m0);                 // box {64 k, 128 rows}
+          } else if (p.a_blocked) {
+            tma_load_3d(sa, &map_a, &full[s], 0, k0, m0 >> 6);         // box {64 m, 64 k, 2 blocks}
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &map_a, &full[s], m0 + j * 64, k0);
           }
           if (!B_MN) {
             tma_load_2d(sb, &map_b, &full[s], k0, n0);                 // box {64 k, 256 rows}
+          } else if (p.b_blocked) {
+            tma_load_3d(sb, &map_b, &full[s], 0, k0, n0 >> 6);         // box {64 n, 64 k, 4 blocks}
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &map_b, &full[s], n0 + j * 64, k0);
@@ -309,6 +314,31 @@ static int get_map_2d(CUtensorMap* out, const void* base, uint64_t cols, uint64_
   return 0;
 }
 
+// 3-D bf16 map over an MN-major operand stored as [K rows, mn contiguous] (mn a multiple of 64): dimensions
+// {64 within a block, K, mn / 64 blocks}; one copy of box {64, 64, blocks} lands as `blocks` consecutive
+// 64x64 swizzled blocks, the layout the MN-major shared-memory descriptors expect.
+static int get_map_mn_blocked(CUtensorMap* out, const void* base, uint64_t mn, uint64_t k_rows, uint64_t ld_elems,
+                              uint32_t blocks) {
+  MapKey key{base, mn, k_rows, ld_elems, 0xB10Cu, blocks};
+  {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    auto it = g_map_cache.find(key);
+    if (it != g_map_cache.end()) {
+      *out = it->second;
+      return 0;
+    }
+  }
+  uint64_t dims[3] = {64, k_rows, mn / 64};
+  uint64_t strides[2] = {ld_elems * 2, 128};
+  uint32_t box[3] = {64, 64, blocks};
+  int rc = jpb_make_tensor_map(out, base, 2, 3, dims, strides, box, 1);
+  if (rc != 0) return rc;
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  if (g_map_cache.size() > 4096) g_map_cache.clear();
+  g_map_cache.emplace(key, *out);
+  return 0;
+}
+
 static int g_num_sms = 0;
 
 template <bool A_MN, bool B_MN>
@@ -345,13 +375,17 @@ JPB_API int jpb_gemm_bf16(const void* A, const void* B, void* D, const void* bia
   if (accumulate && !out_fp32) return -JPB_ERR_BAD_ARGUMENT;
   CUtensorMap ma, mb;
   int rc;
+  const int a_blocked = a_mn_major && M % 64 == 0, b_blocked = b_mn_major && N % 64 == 0;
   if (!a_mn_major) rc = get_map_2d(&ma, A, K, M, lda, BK, BM);
+  else if (a_blocked) rc = get_map_mn_blocked(&ma, A, M, K, lda, BM / 64);
   else rc = get_map_2d(&ma, A, M, K, lda, 64, BK);
   if (rc) return rc;
   if (!b_mn_major) rc = get_map_2d(&mb, B, K, N, ldb, BK, BN);
+  else if (b_blocked) rc = get_map_mn_blocked(&mb, B, N, K, ldb, BN / 64);
   else rc = get_map_2d(&mb, B, N, K, ldb, 64, BK);
   if (rc) return rc;
   GemmParams p;
+  p.a_blocked = a_blocked; p.b_blocked = b_blocked;
   p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.out_fp32 = out_fp32; p.accumulate = accumulate;
   p.bias = bias; p.bias_fp32 = bias_fp32; p.D = D; p.status = jpb_status_device_ptr();
   p.tiles_m = (M + BM - 1) / BM;

@@ -100,12 +100,23 @@ def launch(argv: Sequence[str], nproc: int, env: dict | None = None, timeout_s: 
     return rc
 
 
-if __name__ == "__main__":
-    import argparse
+def _main(args: list[str]) -> int:
+    """``launch.py --nproc N [--timeout S] (script.py | -m module) [args of the script ...]``: everything after
+    the script or module name goes to the workers untouched."""
+    nproc, timeout_s, i = None, 600.0, 0
+    while i < len(args):
+        if args[i] == "--nproc":
+            nproc, i = int(args[i + 1]), i + 2
+        elif args[i] == "--timeout":
+            timeout_s, i = float(args[i + 1]), i + 2
+        else:
+            break
+    rest = args[i:]
+    if nproc is None or not rest or (rest[0] == "-m" and len(rest) < 2):
+        sys.stderr.write("usage: python -m jaxpp_b200.launch --nproc N [--timeout S] (script.py | -m module) [args ...]\n")
+        return 2
+    return launch(rest, nproc, timeout_s=timeout_s)
 
-    ap = argparse.ArgumentParser(description="run a script as N ranks on this node")
-    ap.add_argument("--nproc", type=int, required=True)
-    ap.add_argument("--timeout", type=float, default=600.0)
-    ap.add_argument("script", nargs=argparse.REMAINDER)
-    a = ap.parse_args()
-    sys.exit(launch(a.script, a.nproc, timeout_s=a.timeout))
+
+if __name__ == "__main__":
+    sys.exit(_main(sys.argv[1:]))

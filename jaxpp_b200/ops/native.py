@@ -23,11 +23,19 @@ def load() -> ctypes.CDLL:
     global _LIB
     if _LIB is not None:
         return _LIB
-    if not os.path.exists(LIB_PATH):
-        raise RuntimeError(
-            f"native kernel library not found at {LIB_PATH}; build it with `python -m jaxpp_b200.csrc.build` "
-            "(or __graft_entry__.build())"
-        )
+    from ..csrc import build as _build
+
+    if not _build.is_current():
+        # a binary that does not match its sources has a different ABI than the bindings below: never load it
+        import shutil
+
+        if shutil.which("nvcc") or os.path.exists("/usr/local/cuda/bin/nvcc"):
+            _build.ensure_current()
+        else:
+            raise RuntimeError(
+                f"native kernel library at {LIB_PATH} is missing or older than its sources and nvcc is not available; "
+                "build it with `python -m jaxpp_b200.csrc.build` (or __graft_entry__.build())"
+            )
     lib = ctypes.CDLL(LIB_PATH)
     lib.jpb_gemm_bf16.argtypes = [_c_p, _c_p, _c_p, _c_p] + [_c_int] * 11 + [_c_p]
     lib.jpb_norm_fwd.argtypes = [_c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_f, _c_p]

@@ -1,8 +1,8 @@
 """Fused tensor-parallel GEMMs: all-gather→GEMM and GEMM→reduce-scatter in one sm_100a kernel each.
 
-Python side of ``csrc/gemm_comm_sm100.cu``: picks the symmetric workspace of the mesh axis, stages this
-rank's shard into its own slot of the gather buffer, fills the call descriptor (epoch, buffer parity, peer
-pointers) and launches.  Shapes the kernel does not cover (token counts that are not a multiple of
+Python side of ``csrc/gemm_comm_sm100.cu``: picks the symmetric workspace of the mesh axis, fills the call
+descriptor (epoch, buffer parity, peer pointers) and launches; the kernel itself pushes this rank's shard to
+the peers, so no staging copy runs around it.  Shapes the kernel does not cover (token counts that are not a multiple of
 128 x ranks, feature counts that are not a multiple of 8) fall back to the NCCL twin in ``tp.py`` — loudly
 countable through ``FALLBACKS``.
 """
@@ -28,7 +28,7 @@ def _lib():
     lib = native.load()
     if not _bound:
         p, i = ctypes.c_void_p, ctypes.c_int
-        lib.jpb_comm_gemm.argtypes = [p, p, p, p] + [i] * 11 + [ctypes.POINTER(symm.JpbCommDesc), p]
+        lib.jpb_comm_gemm.argtypes = [p, p, p, p] + [i] * 11 + [ctypes.POINTER(symm.JpbCommDesc), p, p]
         lib.jpb_memcpy_async.argtypes = [p, p, ctypes.c_longlong, p]
         _bound = True
     return lib
@@ -41,20 +41,13 @@ def _bf16_2d(t: torch.Tensor) -> torch.Tensor:
     return t if t.is_contiguous() else t.contiguous()
 
 
-def _launch(a, b, out, bias, M, N, K, lda, ldb, a_mn, b_mn, accumulate, desc):
+def _launch(a, b, out, bias, M, N, K, lda, ldb, a_mn, b_mn, accumulate, desc, gather_out=None):
     rc = _lib().jpb_comm_gemm(
         None if a is None else a.data_ptr(), None if b is None else b.data_ptr(), out.data_ptr(),
         None if bias is None else bias.data_ptr(), M, N, K, lda, ldb, out.stride(0), int(a_mn), int(b_mn),
         int(out.dtype == torch.float32), int(accumulate), int(bias is not None and bias.dtype == torch.float32),
-        ctypes.byref(desc), native._stream())
+        ctypes.byref(desc), None if gather_out is None else gather_out.data_ptr(), native._stream())
     native._check(rc, "jpb_comm_gemm")
-
-
-def _stage(ws: symm.CommWorkspace, desc, shard: torch.Tensor):
-    """Copy this rank's shard into its slot of G (device-to-device, on the current stream)."""
-    nbytes = shard.numel() * shard.element_size()
-    native._check(_lib().jpb_memcpy_async(ws.own_gather_slot(desc, nbytes), shard.data_ptr(), nbytes, native._stream()),
-                  "jpb_memcpy_async", 0)
 
 
 def _rows_ok(rows_total: int, n: int) -> bool:
@@ -71,10 +64,9 @@ def ag_linear(x, w, bias, axis):
         FALLBACKS[0] += 1
         return ops.linear(tpmod._all_gather_rows(x, axis), w, bias)
     ws = symm.workspace_for(axis, M * K * 2, 0)
-    desc = ws.next_call(GATHER_ROWS, False, False, (n - 1) * (Ml // 128))
-    _stage(ws, desc, x2)
+    desc = ws.next_call(GATHER_ROWS, False, False)
     out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
-    _launch(None, w2, out, bias.contiguous() if bias is not None else None, M, N, K, K, w2.stride(0), False, False, False, desc)
+    _launch(x2, w2, out, bias.contiguous() if bias is not None else None, M, N, K, K, w2.stride(0), False, False, False, desc)
     return out
 
 
@@ -89,14 +81,11 @@ def ag_dgrad(dy_shard, w, axis):
         full = tpmod._all_gather_rows(dy_shard, axis)
         return ops.linear_dgrad(full, w), full
     ws = symm.workspace_for(axis, M * Nred * 2, 0)
-    desc = ws.next_call(GATHER_ROWS, False, False, (n - 1) * (Ml // 128))
-    _stage(ws, desc, dy2)
+    desc = ws.next_call(GATHER_ROWS, False, False)
     dx = torch.empty(M, Kout, dtype=torch.bfloat16, device=dy_shard.device)
-    _launch(None, w2, dx, None, M, Kout, Nred, Nred, w2.stride(0), False, True, False, desc)
+    # the comm warps also assemble the gathered dy (the weight gradient needs it) while the tensor cores work
     full = torch.empty(M, Nred, dtype=torch.bfloat16, device=dy_shard.device)
-    # every chunk has been pulled by the time the kernel ends: G now holds the gathered dy
-    native._check(_lib().jpb_memcpy_async(full.data_ptr(), desc.g[ws.rank], M * Nred * 2, native._stream()),
-                  "jpb_memcpy_async", 0)
+    _launch(dy2, w2, dx, None, M, Kout, Nred, Nred, w2.stride(0), False, True, False, desc, gather_out=full)
     return dx, full
 
 
@@ -111,10 +100,9 @@ def ag_wgrad(dy, x_shard, axis, out_dtype=None):
         FALLBACKS[0] += 1
         return ops.linear_wgrad(dy, tpmod._all_gather_rows(x_shard, axis), out_dtype)
     ws = symm.workspace_for(axis, T * Kin * 2, 0)
-    desc = ws.next_call(GATHER_RED, True, False, (n - 1) * (Tl // 64))
-    _stage(ws, desc, x2)
+    desc = ws.next_call(GATHER_RED, True, False)
     out = torch.empty(Nout, Kin, dtype=out_dtype, device=dy.device)
-    _launch(dy2, None, out, None, Nout, Kin, T, Nout, Kin, True, True, False, desc)
+    _launch(dy2, x2, out, None, Nout, Kin, T, Nout, Kin, True, True, False, desc)
     return out
 
 
@@ -128,7 +116,7 @@ def linear_rs(x, w, axis):
         FALLBACKS[0] += 1
         return tpmod._reduce_scatter_rows(ops.linear(x, w, None), axis)
     ws = symm.workspace_for(axis, 0, M * N * 2)
-    desc = ws.next_call(0, False, True, 0)
+    desc = ws.next_call(0, False, True)
     out = torch.empty(M // n, N, dtype=torch.bfloat16, device=x.device)
     _launch(x2, w2, out, None, M, N, K, x2.stride(0), w2.stride(0), False, False, False, desc)
     return out
@@ -144,7 +132,7 @@ def dgrad_rs(dy, w, axis):
         FALLBACKS[0] += 1
         return tpmod._reduce_scatter_rows(ops.linear_dgrad(dy, w), axis)
     ws = symm.workspace_for(axis, 0, M * Kout * 2)
-    desc = ws.next_call(0, False, True, 0)
+    desc = ws.next_call(0, False, True)
     out = torch.empty(M // n, Kout, dtype=torch.bfloat16, device=dy.device)
     _launch(dy2, w2, out, None, M, Kout, Nred, dy2.stride(0), w2.stride(0), False, True, False, desc)
     return out

@@ -11,9 +11,11 @@ Routing here is capacity based so that every shape in the captured step is stati
     expert FFN (SwiGLU) per local expert — equal-sized groups, one tcgen05 GEMM per expert and projection
     all-to-all back, combine: y_t = Σ_k w_{t,k} · out[e_{t,k}, slot_{t,k}]
 
-``b200tp::all_to_all`` is the collective (its transpose is itself); the permutations are index ops whose
-autograd gives the matching scatter/gather in backward.  On GPUs with fused collectives enabled, dispatch and
-combine run as peer-memory kernels (``jaxpp_b200.parallel.fused_moe``).
+With expert parallelism the two exchanges are the ops ``b200moe::dispatch_a2a`` (permutation into slots +
+all-to-all) and ``b200moe::combine_a2a`` (all-to-all back + weighted gather-sum); each is the other's
+transpose, which is how their backward is written.  On GPUs with fused collectives enabled they run as one
+peer-memory kernel each (``jaxpp_b200.parallel.fused_moe``), otherwise as index ops around
+``b200moe::all_to_all`` (NCCL / gloo).
 """
 from __future__ import annotations
 
@@ -46,6 +48,125 @@ torch.library.register_autograd(
     lambda ctx, g: (torch.ops.b200moe.all_to_all(g.contiguous(), ctx.axis), None),
     setup_context=lambda ctx, inputs, output: setattr(ctx, "axis", inputs[1]),
 )
+
+
+# ---- dispatch / combine fused with the expert-parallel exchange ------------------------------------------------------
+def _use_fused(x: Tensor) -> bool:
+    from ..utils import config
+
+    if not (x.is_cuda and config.use_fused_collectives.value and config.use_native_kernels.value):
+        return False
+    from . import fused_moe
+
+    return fused_moe.supported(x)
+
+
+def _dispatch_a2a_impl(x, dest, scale, n_experts: int, capacity: int, top_k: int, axis: str):
+    """x [T, d]; dest [T*k] slot (expert * C + position, E*C = dropped); scale [T*k] or None.
+    Returns [E_l, ep*C, d]: for every local expert, the slots of rank 0's tokens, then rank 1's, ..."""
+    ep = tpmod.axis_size(axis)
+    d = x.shape[-1]
+    e_local = n_experts // ep
+    if ep > 1 and _use_fused(x):
+        from . import fused_moe
+
+        n_slots = n_experts * capacity
+        picks = torch.arange(dest.numel(), device=x.device, dtype=torch.int32)
+        inv = torch.full((n_slots + 1,), -1, dtype=torch.int32, device=x.device)
+        inv[dest] = picks // top_k
+        slot_scale = None
+        if scale is not None:
+            slot_scale = torch.zeros(n_slots + 1, dtype=torch.float32, device=x.device)
+            slot_scale[dest] = scale.float()
+        return fused_moe.dispatch(x, inv, slot_scale, n_experts, capacity, axis)
+    src = x.repeat_interleave(top_k, dim=0)
+    if scale is not None:
+        src = (src.float() * scale.float().unsqueeze(-1)).to(x.dtype)
+    buf = torch.zeros(n_experts * capacity + 1, d, dtype=x.dtype, device=x.device)
+    buf = buf.index_add(0, dest, src)[:-1]
+    if ep == 1:
+        return buf.view(n_experts, capacity, d)
+    buf = _all_to_all_impl(buf.view(ep, e_local * capacity, d), axis)   # block q from rank q
+    return buf.view(ep, e_local, capacity, d).transpose(0, 1).reshape(e_local, ep * capacity, d)
+
+
+def _combine_a2a_impl(y, dest, weights, n_experts: int, capacity: int, top_k: int, axis: str, want_picked: bool):
+    """y [E_l, ep*C, d] -> (out [T, d], picked [T*k, d] or an empty tensor)."""
+    ep = tpmod.axis_size(axis)
+    d = y.shape[-1]
+    e_local = n_experts // ep
+    T = dest.numel() // top_k
+    if ep > 1 and _use_fused(y):
+        from . import fused_moe
+
+        out, picked = fused_moe.combine(y, dest.to(torch.int32), None if weights is None else weights.float().contiguous(),
+                                        n_experts, capacity, top_k, axis, want_picked)
+        return out, picked if picked is not None else y.new_empty(0)
+    if ep > 1:
+        y = y.view(e_local, ep, capacity, d).transpose(0, 1).reshape(ep, e_local * capacity, d)
+        y = _all_to_all_impl(y.contiguous(), axis)
+    flat = torch.cat([y.reshape(n_experts * capacity, d), torch.zeros(1, d, dtype=y.dtype, device=y.device)], 0)
+    picked = flat.index_select(0, dest)
+    w = weights.float() if weights is not None else torch.ones(dest.numel(), dtype=torch.float32, device=y.device)
+    out = (picked.view(T, top_k, d).float() * w.view(T, top_k, 1)).sum(1).to(y.dtype)
+    return out, picked if want_picked else y.new_empty(0)
+
+
+_lib.define("dispatch_a2a(Tensor x, Tensor dest, Tensor? scale, int n_experts, int capacity, int top_k, str axis) -> Tensor")
+_lib.impl("dispatch_a2a", _dispatch_a2a_impl, "CompositeExplicitAutograd")
+_lib.define("combine_a2a(Tensor y, Tensor dest, Tensor? weights, int n_experts, int capacity, int top_k, str axis, "
+            "bool want_picked) -> (Tensor, Tensor)")
+_lib.impl("combine_a2a", _combine_a2a_impl, "CompositeExplicitAutograd")
+
+
+def _dispatch_fake(x, dest, scale, n_experts, capacity, top_k, axis):
+    ep = tpmod.axis_size(axis)
+    return x.new_empty(n_experts // ep, ep * capacity, x.shape[-1])
+
+
+def _combine_fake(y, dest, weights, n_experts, capacity, top_k, axis, want_picked):
+    T = dest.numel() // top_k
+    return y.new_empty(T, y.shape[-1]), y.new_empty((dest.numel(), y.shape[-1]) if want_picked else (0,))
+
+
+torch.library.register_fake("b200moe::dispatch_a2a", _dispatch_fake)
+torch.library.register_fake("b200moe::combine_a2a", _combine_fake)
+
+
+def _dispatch_setup(ctx, inputs, output):
+    _, dest, scale, ctx.n_experts, ctx.capacity, ctx.top_k, ctx.axis = inputs
+    ctx.save_for_backward(dest, scale)
+
+
+def _dispatch_bwd(ctx, g):
+    # the transpose of "scatter rows into slots, scaled" is "gather-sum the slots of each token, scaled";
+    # no gradient flows to the scale (it is only used inside the backward of combine)
+    dest, scale = ctx.saved_tensors
+    dx, _ = torch.ops.b200moe.combine_a2a(g.contiguous(), dest, scale, ctx.n_experts, ctx.capacity, ctx.top_k, ctx.axis, False)
+    return dx, None, None, None, None, None, None
+
+
+def _combine_setup(ctx, inputs, output):
+    _, dest, weights, ctx.n_experts, ctx.capacity, ctx.top_k, ctx.axis, ctx.want_picked = inputs
+    ctx.has_weights = weights is not None
+    ctx.save_for_backward(dest, weights, output[1])
+
+
+def _combine_bwd(ctx, g_out, g_picked):
+    dest, weights, picked = ctx.saved_tensors
+    g_out = g_out.contiguous()
+    dy = torch.ops.b200moe.dispatch_a2a(g_out, dest, weights, ctx.n_experts, ctx.capacity, ctx.top_k, ctx.axis)
+    dw = None
+    if ctx.has_weights and ctx.needs_input_grad[2]:
+        if not ctx.want_picked:
+            raise RuntimeError("combine_a2a needs want_picked=True to differentiate with respect to the weights")
+        T = g_out.shape[0]
+        dw = (picked.view(T, ctx.top_k, -1).float() * g_out.float().unsqueeze(1)).sum(-1).reshape(-1).to(weights.dtype)
+    return dy, None, dw, None, None, None, None, None
+
+
+torch.library.register_autograd("b200moe::dispatch_a2a", _dispatch_bwd, setup_context=_dispatch_setup)
+torch.library.register_autograd("b200moe::combine_a2a", _combine_bwd, setup_context=_combine_setup)
 
 
 def route(x: Tensor, w_router: Tensor, top_k: int):
@@ -106,14 +227,11 @@ def moe_ffn(x: Tensor, p: dict, n_experts: int, top_k: int, capacity_factor: flo
     capacity = (capacity + 7) // 8 * 8
     top_i, weights, aux = route(x, p["router"], top_k)
     dest, _ = slots_for(top_i, n_experts, capacity)
+    if ep > 1:
+        buf = torch.ops.b200moe.dispatch_a2a(x, dest, None, n_experts, capacity, top_k, ep_axis)   # [E_l, ep*C, d]
+        y = expert_ffn(buf, p["w_up"], p["w_down"])
+        out, _ = torch.ops.b200moe.combine_a2a(y, dest, weights.reshape(-1), n_experts, capacity, top_k, ep_axis, True)
+        return out, aux
     buf = dispatch(x, dest, n_experts, capacity, top_k)                        # [E, C, d]
-    e_local = n_experts // ep
-    if ep > 1:
-        buf = torch.ops.b200moe.all_to_all(buf.view(ep, e_local * capacity, d), ep_axis)   # block q from rank q
-        buf = buf.view(ep, e_local, capacity, d).transpose(0, 1).reshape(e_local, ep * capacity, d)
-    y = expert_ffn(buf, p["w_up"], p["w_down"])                                # [E_l, ep*C, d]
-    if ep > 1:
-        y = y.view(e_local, ep, capacity, d).transpose(0, 1).reshape(ep, e_local * capacity, d)
-        y = torch.ops.b200moe.all_to_all(y.contiguous(), ep_axis)
-    y = y.reshape(n_experts, capacity, d)
-    return combine(y, dest, weights, top_k), aux
+    y = expert_ffn(buf, p["w_up"], p["w_down"])
+    return combine(y.reshape(n_experts, capacity, d), dest, weights, top_k), aux

@@ -61,7 +61,7 @@ class SymmetricBuffer:
 class JpbCommDesc(ctypes.Structure):
     _fields_ = [
         ("n_ranks", ctypes.c_int), ("rank", ctypes.c_int), ("epoch", ctypes.c_int), ("gather", ctypes.c_int),
-        ("gathered_is_b", ctypes.c_int), ("scatter", ctypes.c_int), ("counter_target", ctypes.c_longlong),
+        ("gathered_is_b", ctypes.c_int), ("scatter", ctypes.c_int), ("max_ctas", ctypes.c_int),
         ("ctrl", ctypes.c_void_p * 8), ("g", ctypes.c_void_p * 8), ("r", ctypes.c_void_p * 8),
     ]
 
@@ -72,6 +72,8 @@ class CommWorkspace:
     def __init__(self, group, group_ranks: list[int], g_bytes: int, r_bytes: int):
         lib = native.load()
         lib.jpb_comm_ctrl_bytes.restype = ctypes.c_longlong
+        if lib.jpb_comm_desc_bytes() != ctypes.sizeof(JpbCommDesc):
+            raise native.NativeError("call descriptor layout of the native library differs from the Python binding")
         align = lambda x: (x + 1023) // 1024 * 1024
         self.ctrl_bytes = align(lib.jpb_comm_ctrl_bytes())
         self.g_bytes, self.r_bytes = align(max(g_bytes, 16)), align(max(r_bytes, 16))
@@ -79,26 +81,32 @@ class CommWorkspace:
         self.buf = SymmetricBuffer(total, group, group_ranks)
         self.n, self.rank = self.buf.n, self.buf.rank
         self.epoch = 0
-        self.pulled_total = 0  # cumulative number of chunks pulled by this rank (mirrors the device counter)
+        # With pipeline stages on other GPUs, point-to-point kernels on side streams must be able to start
+        # while a fused kernel waits for its tensor-parallel peer: keep a few SMs out of the persistent grid.
+        from ..mesh import MpmdMesh
+        from ..utils import config
 
-    def next_call(self, gather: int, gathered_is_b: bool, scatter: bool, remote_chunks: int) -> JpbCommDesc:
+        mesh = MpmdMesh.current()
+        sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        reserve = config.comm_reserved_sms.value if mesh.mpmd_dim > 1 else 0
+        self.max_ctas = max(1, sms - reserve) if reserve > 0 else 0
+
+    def next_call(self, gather: int, gathered_is_b: bool, scatter: bool) -> JpbCommDesc:
+        """Descriptor of the next fused call.  Every call both sends to and receives from every peer, and a
+        rank's calls run in stream order; together that keeps a peer at most one call ahead, which is what the
+        double buffering by call parity and the ever-growing epoch in the flags rely on."""
         self.epoch += 1
         parity = self.epoch & 1
-        self.pulled_total += remote_chunks
         d = JpbCommDesc()
         d.n_ranks, d.rank, d.epoch = self.n, self.rank, self.epoch
         d.gather, d.gathered_is_b, d.scatter = gather, int(gathered_is_b), int(scatter)
-        d.counter_target = self.pulled_total
+        d.max_ctas = self.max_ctas
         for q in range(self.n):
             base = self.buf.ptrs[q]
             d.ctrl[q] = base
             d.g[q] = base + self.ctrl_bytes + parity * self.g_bytes
             d.r[q] = base + self.ctrl_bytes + 2 * self.g_bytes + parity * self.r_bytes
         return d
-
-    def own_gather_slot(self, desc: JpbCommDesc, slot_bytes: int) -> int:
-        """Device address of this rank's slot inside its own G of the current parity."""
-        return desc.g[self.rank] + self.rank * slot_bytes
 
 
 _WORKSPACES: dict[Any, CommWorkspace] = {}

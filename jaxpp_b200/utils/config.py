@@ -125,6 +125,9 @@ enable_check_ir = BoolEnvVar("JAXPP_ENABLE_CHECK_JAXPR", False)
 use_native_kernels = BoolEnvVar("JAXPP_B200_NATIVE", True)
 # Use fused compute+collective kernels over peer memory (1) or the NCCL-only twins (0).
 use_fused_collectives = BoolEnvVar("JAXPP_B200_FUSED_COLLECTIVES", True)
+# SMs the fused compute+collective kernels leave free when pipeline stages run on other GPUs, so that the
+# point-to-point kernels of side streams can start while a fused kernel waits for its tensor-parallel peer.
+comm_reserved_sms = IntEnvVar("JAXPP_B200_COMM_RESERVED_SMS", 4)
 # Capture tasks into CUDA graphs after their first eager run.
 use_cuda_graphs = BoolEnvVar("JAXPP_B200_CUDA_GRAPHS", False)
 # Seconds a rank may go without a heartbeat before the watchdog reports it.

@@ -106,8 +106,57 @@ def scenario_pp_gpu(schedule_name):
         print(f"pipeline over NCCL p2p ({schedule_name}) matches the eager step", flush=True)
 
 
+def scenario_pp_tp_gpu(pp, tp, schedule_name):
+    """Pipeline x tensor parallel Llama-style step on pp*tp GPUs (bf16, native kernels): the fused
+    compute+collective kernels against the same step with NCCL collectives, two steps each."""
+    from torch.utils import _pytree as pytree
+
+    from jaxpp_b200.models import lm_trainer as lt
+    from jaxpp_b200.models import transformer as tf
+
+    n_stages = {"std": pp, "interleaved": 2 * pp}[schedule_name]
+    sched = jp.Std1F1B(pp) if schedule_name == "std" else jp.Interleaved1F1B(n_stages, pp)
+    mesh = jp.MpmdMesh.create({"mpmd": pp, "data": 1, "model": tp}, kind="cuda", multi_process=True)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    cfg = tf.ModelConfig("llama", vocab=512, d_model=256, n_layers=n_stages, n_heads=4, n_kv_heads=2, ffn=512, seq=128,
+                         n_stages=n_stages, tp=tp, dtype=torch.bfloat16)
+    hyper = lt.Hyper(lr=1e-3, inplace_update=False)
+    n_mb = 2 * n_stages
+    g = torch.Generator().manual_seed(5)
+    tokens = torch.randint(0, 512, (n_mb, 2 * tp, 128), generator=g).to(dev)
+    labels = torch.randint(0, 512, (n_mb, 2 * tp, 128), generator=g).to(dev)
+    me_pp, me_tp = mesh.my_mpmd_axis_index, mesh.axis_index("model")
+    results = {}
+    for fused_on in (False, True):
+        with config.use_fused_collectives.set(fused_on):
+            state = lt.init_state(cfg, sched, dev, my_rank=me_pp, tp_rank=me_tp, seed=0)
+            f = jp.mpmd_jit_with_loop(lt.make_train_step(cfg, sched, hyper), mesh)
+            state, losses1 = f(state, tokens, labels)
+            state, losses2 = f(state, tokens, labels)
+            torch.cuda.synchronize()
+            results[fused_on] = (state, losses1, losses2)
+    assert native.read_status() == 0, "a fused kernel reported a time-out"
+    assert fused.FALLBACKS[0] == 0, f"{fused.FALLBACKS[0]} fused calls fell back to NCCL"
+    is_arr = lambda a: isinstance(a, jp.MpmdArray)
+    checked = 0
+    for a, b in zip(pytree.tree_leaves(results[False], is_leaf=is_arr), pytree.tree_leaves(results[True], is_leaf=is_arr)):
+        ta, tb = a.local_tensor(), b.local_tensor()
+        if ta is None:
+            continue
+        if ta.dtype in (torch.int32, torch.int64):
+            assert torch.equal(ta, tb)
+        else:
+            torch.testing.assert_close(tb.float(), ta.float(), rtol=5e-2, atol=5e-3)
+        checked += 1
+    assert checked > 0
+    if dist.get_rank() == 0:
+        print(f"pp{pp} x tp{tp} ({schedule_name}): fused collectives match NCCL through two steps", flush=True)
+
+
 SCENARIOS = {
     "fused_tp": scenario_fused_tp,
+    "pp2_tp2_std": lambda: scenario_pp_tp_gpu(2, 2, "std"),
+    "pp2_tp2_interleaved": lambda: scenario_pp_tp_gpu(2, 2, "interleaved"),
     "pp_std": lambda: scenario_pp_gpu("std"),
     "pp_interleaved": lambda: scenario_pp_gpu("interleaved"),
     "pp_zb": lambda: scenario_pp_gpu("zb"),

@@ -21,3 +21,10 @@ def test_fused_tensor_parallel_kernels_two_gpus():
 def test_pipeline_over_nccl_p2p_two_gpus(scenario):
     rc = launch([WORKER, scenario], 2, env={"NCCL_NVLS_ENABLE": "0"}, timeout_s=300)
     assert rc == 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs at least 4 GPUs")
+@pytest.mark.parametrize("scenario", ["pp2_tp2_std", "pp2_tp2_interleaved"])
+def test_pipeline_times_tensor_parallel_four_gpus(scenario):
+    rc = launch([WORKER, scenario], 4, env={"NCCL_NVLS_ENABLE": "0"}, timeout_s=420)
+    assert rc == 0
