@@ -115,6 +115,30 @@ __device__ __forceinline__ bool flag_wait_bounded(const int* flag, int want, boo
   }
 }
 
+// Four consecutive flags (16-byte aligned) with one load per poll; an acquire fence orders what follows.
+__device__ __forceinline__ bool flag_wait4_bounded(const int* flags, int want, volatile int* abort_flag, int* status, int code) {
+  uint32_t spins = 0;
+  uint64_t t0 = 0;
+  while (true) {
+    int4 v;
+    asm volatile("ld.volatile.global.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(flags) : "memory");
+    if (v.x >= want && v.y >= want && v.z >= want && v.w >= want) {
+      asm volatile("fence.acq_rel.sys;" ::: "memory");
+      return true;
+    }
+    if ((++spins & 0xff) == 0) {
+      if (*abort_flag) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > JPB_WAIT_BUDGET_NS) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, JPB_OK, code);
+        return false;
+      }
+    }
+  }
+}
+
 // Tile order: with a scatter, the row blocks of the peers come first (starting with the next rank) and the
 // own block last; with a row gather, the own block comes first.  Inside a row block tiles are m-fastest.
 struct TileOrder {
@@ -229,8 +253,15 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         for (int kb = 0; kb < k_blocks; ++kb, ++it, kbe = (kbe + 1 == k_blocks ? 0 : kbe + 1)) {
           const bool own_k = red_mode && kbe >= own_lo && kbe < own_hi;
           if (red_mode && !own_k && kb >= red_verified) {
-            if (!chunk_ready(kbe)) { ok = false; break; }
-            red_verified = kb + 1;
+            // four chunks per poll where the flags are aligned and none of the four is an own chunk
+            if ((kbe & 3) == 0 && kbe + 3 < k_blocks && !(kbe < own_lo && kbe + 3 >= own_lo)) {
+              if (!flag_wait4_bounded(p.chunk_flags + kbe, p.epoch, abort_flag, p.status, JPB_ERR_PEER_TIMEOUT)) { ok = false; break; }
+              fence_proxy_async_global();
+              red_verified = kb + 4;
+            } else {
+              if (!chunk_ready(kbe)) { ok = false; break; }
+              red_verified = kb + 1;
+            }
           }
           const int s = it % CSTAGES;
           const uint32_t ph = (it / CSTAGES) & 1;

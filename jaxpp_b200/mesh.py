@@ -235,7 +235,10 @@ class MpmdMesh:
             kind = "cuda" if torch.cuda.is_available() else "cpu"
         per_node = int(os.environ.get("LOCAL_WORLD_SIZE", "8")) if multi_process else max(1, torch.cuda.device_count() or 8)
         devs = make_devices(n, kind, multi_process, per_node)
-        return cls(Mesh(np.array(devs, dtype=object).reshape(tuple(shape.values())), tuple(shape.keys())), mpmd_axis_name)
+        mesh = cls(Mesh(np.array(devs, dtype=object).reshape(tuple(shape.values())), tuple(shape.keys())), mpmd_axis_name)
+        if multi_process and dist.is_available() and dist.is_initialized() and dist.get_world_size() == n:
+            mesh.create_process_groups()  # collectively, while every process is at the same point
+        return mesh
 
     def __enter__(self):
         MpmdMesh.mesh_stack.append(self)
@@ -362,6 +365,17 @@ class MpmdMesh:
                     mine = g
             cache[axis] = mine
         return cache[axis]
+
+    def create_process_groups(self) -> None:
+        """Create the process groups of every axis (and of the stages) now.  ``new_group`` is a collective over
+        all processes, so creating a group lazily inside a pipeline task would make the ranks of one stage wait
+        for ranks of another stage that cannot reach the same point before they receive data: every process
+        calls this at the same place instead (mesh creation, start of a multi-controller run)."""
+        if not self.jax_mesh.is_multi_process:
+            return
+        for axis in self.jax_mesh.axis_names:
+            self.axis_group(axis)
+        self.stage_group()
 
     def stage_group(self):
         """Process group of all processes in this process's pipeline rank."""

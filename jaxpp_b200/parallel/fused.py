@@ -179,8 +179,7 @@ def all_reduce(x: torch.Tensor, axis: str, scale: float = 1.0) -> torch.Tensor:
     ws = _AR_WS.get(axis)
     if ws is None or ws.slot < nbytes:
         if ws is not None:
-            torch.cuda.synchronize()
-            ws.buf.close()
+            symm._RETIRED.append(ws)  # freed between steps, see symm.release_retired
         ws = _AllReduceWorkspace(axis, max(nbytes, 64 << 20))
         _AR_WS[axis] = ws
     ws.epoch += 1

@@ -61,14 +61,10 @@ def _lib():
 
 
 def _workspace(axis: str, nbytes: int) -> _Workspace:
-    import torch.distributed as dist
-
     ws = _WS.get(axis)
     if ws is None or ws.slot < nbytes:
         if ws is not None:
-            torch.cuda.synchronize()
-            dist.barrier(group=ws.buf.group)
-            ws.buf.close()
+            symm._RETIRED.append(ws)  # freed between steps, see symm.release_retired
         ws = _Workspace(axis, nbytes)
         _WS[axis] = ws
     return ws

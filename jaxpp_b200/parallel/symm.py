@@ -46,7 +46,10 @@ class SymmetricBuffer:
             peer = ctypes.c_void_p()
             native._check(lib.jpb_ipc_open(h, ctypes.byref(peer)), "jpb_ipc_open", 0)
             self.ptrs.append(peer.value)
-        torch.cuda.synchronize()
+        # peers may write into this buffer as soon as they leave the barrier; only the current stream is
+        # synchronised (a device-wide synchronisation would also wait for receives of a pipeline that are
+        # posted ahead of time on side streams and cannot complete before this rank moves on)
+        torch.cuda.current_stream().synchronize()
         dist.barrier(group=group)
 
     def close(self):
@@ -124,10 +127,30 @@ def workspace_for(axis: str, g_bytes: int, r_bytes: int) -> CommWorkspace:
     ws = _WORKSPACES.get(key)
     if ws is None or ws.g_bytes < g_bytes or ws.r_bytes < r_bytes:
         if ws is not None:
-            torch.cuda.synchronize()
-            dist.barrier(group=group)
+            # The outgrown workspace is retired, not freed: cudaFree and closing IPC mappings synchronise the
+            # device, which must not happen while receives of a pipeline step are pending on side streams.
             g_bytes, r_bytes = max(g_bytes, ws.g_bytes), max(r_bytes, ws.r_bytes)
-            ws.buf.close()
+            _RETIRED.append(ws)
         ws = CommWorkspace(group, ranks, g_bytes, r_bytes)
         _WORKSPACES[key] = ws
     return ws
+
+
+_RETIRED: list = []
+
+
+def release_retired() -> None:
+    """Free the workspaces that were outgrown.  Collective over every group that retired one: call it between
+    steps with nothing in flight (outgrown buffers are small next to HBM, so never calling it is fine too)."""
+    if not _RETIRED:
+        return
+    torch.cuda.synchronize()
+    for ws in _RETIRED:
+        dist.barrier(group=ws.buf.group)   # every importer is done with the mapping ...
+        for q, ptr in enumerate(ws.buf.ptrs):
+            if q != ws.buf.rank and ptr:
+                ws.buf.lib.jpb_ipc_close(ptr)
+        dist.barrier(group=ws.buf.group)   # ... and has closed it before the owner frees the memory
+        ws.buf.lib.jpb_ipc_free(ws.buf.local_ptr)
+        ws.buf.ptrs, ws.buf.local_ptr = [], None
+    _RETIRED.clear()

@@ -32,6 +32,8 @@ class DistComm:
         self.pending_recv: dict[int, tuple] = {}  # vid → (work list, event)
         self.inflight_send: dict[int, tuple] = {}  # tid → (tensors, works)
         self.groups: dict[tuple, object] = {}
+        if dist.is_available() and dist.is_initialized():
+            mesh.create_process_groups()  # no-op when the mesh was made by MpmdMesh.create
         if self.cuda:
             self.send_stream = torch.cuda.Stream(device)
             self.recv_stream = torch.cuda.Stream(device)
@@ -52,6 +54,7 @@ class DistComm:
         for tid in list(self.inflight_send):
             self._finish_send(tid)
         self.before_use(st, list(self.pending_recv))
+
 
     # -- p2p ------------------------------------------------------------------------------------------
     def send(self, st, ins: Transfer, prog: Program):

@@ -106,6 +106,46 @@ def scenario_pp_gpu(schedule_name):
         print(f"pipeline over NCCL p2p ({schedule_name}) matches the eager step", flush=True)
 
 
+def scenario_fused_moe():
+    """Expert-parallel dispatch / combine as peer-memory kernels against the index-op + NCCL all-to-all path,
+    forward and backward, several calls in a row (both buffer parities)."""
+    from jaxpp_b200.parallel import moe
+
+    n, r = dist.get_world_size(), dist.get_rank()
+    mesh = jp.MpmdMesh.create({"mpmd": 1, "data": n, "model": 1}, kind="cuda", multi_process=True)
+    E, k, d = 4 * n, 2, 512
+    with mesh:
+        for rep, T in enumerate([256, 384, 256]):
+            capacity = (int(-(-T * k * 1.0 // E)) + 7) // 8 * 8
+            g = torch.Generator(device="cuda").manual_seed(100 + r + 7 * rep)
+            x0 = (torch.randn(T, d, generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+            top_i = torch.stack([torch.randperm(E, generator=g, device="cuda")[:k] for _ in range(T)])
+            w0 = torch.rand(T * k, generator=g, device="cuda")
+            dest, keep = moe.slots_for(top_i, E, capacity)
+            res = {}
+            for fused_on in (False, True):
+                with config.use_fused_collectives.set(fused_on):
+                    x = x0.clone().requires_grad_(True)
+                    w = w0.clone().requires_grad_(True)
+                    buf = torch.ops.b200moe.dispatch_a2a(x, dest, None, E, capacity, k, "data")
+                    y = (buf.float() * 1.5 + 0.25).to(torch.bfloat16)
+                    out, picked = torch.ops.b200moe.combine_a2a(y, dest, w, E, capacity, k, "data", True)
+                    loss = (out.float() * torch.linspace(-1, 1, d, device="cuda")).sum()
+                    gx, gw = torch.autograd.grad(loss, [x, w])
+                    scaled = torch.ops.b200moe.dispatch_a2a(x0, dest, w0, E, capacity, k, "data")
+                    res[fused_on] = (buf.detach(), out.detach(), picked.detach(), gx, gw, scaled)
+            names = ["dispatch", "combine out", "picked", "grad x", "grad weights", "scaled dispatch"]
+            for name, a, b in zip(names, res[False], res[True]):
+                if name in ("dispatch", "picked", "scaled dispatch"):
+                    assert torch.equal(a, b), f"{name}: fused differs from the all-to-all path (T={T})"
+                else:
+                    close(b, a, 0.05, f"{name} (T={T})")
+        torch.cuda.synchronize()
+        assert native.read_status() == 0, "a fused kernel reported a time-out"
+    if r == 0:
+        print("fused MoE dispatch / combine match the NCCL all-to-all path", flush=True)
+
+
 def scenario_pp_tp_gpu(pp, tp, schedule_name):
     """Pipeline x tensor parallel Llama-style step on pp*tp GPUs (bf16, native kernels): the fused
     compute+collective kernels against the same step with NCCL collectives, two steps each."""
@@ -155,6 +195,7 @@ def scenario_pp_tp_gpu(pp, tp, schedule_name):
 
 SCENARIOS = {
     "fused_tp": scenario_fused_tp,
+    "fused_moe": scenario_fused_moe,
     "pp2_tp2_std": lambda: scenario_pp_tp_gpu(2, 2, "std"),
     "pp2_tp2_interleaved": lambda: scenario_pp_tp_gpu(2, 2, "interleaved"),
     "pp_std": lambda: scenario_pp_gpu("std"),
