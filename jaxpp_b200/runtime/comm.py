@@ -32,6 +32,7 @@ class DistComm:
         self.pending_recv: dict[int, tuple] = {}  # vid → (work list, event)
         self.inflight_send: dict[int, tuple] = {}  # tid → (tensors, works)
         self.groups: dict[tuple, object] = {}
+        self.p2p_groups: dict[tuple, object] = {}  # (src pipeline rank, dst pipeline rank) → 2-process group
         if dist.is_available() and dist.is_initialized():
             mesh.create_process_groups()  # no-op when the mesh was made by MpmdMesh.create
         if self.cuda:
@@ -67,7 +68,8 @@ class DistComm:
             ready.record()
             with torch.cuda.stream(self.send_stream):
                 self.send_stream.wait_event(ready)
-                works = dist.batch_isend_irecv([dist.P2POp(dist.isend, t, peer) for t in tensors])
+                g = self.p2p_groups.get((self.rank, ins.dst))
+                works = dist.batch_isend_irecv([dist.P2POp(dist.isend, t, peer, group=g) for t in tensors])
         else:
             # gloo: one message per transfer (all arrays packed into one byte buffer)
             packed = torch.cat([t.reshape(-1).view(torch.uint8) for t in tensors]) if len(tensors) > 1 else tensors[0]
@@ -86,7 +88,8 @@ class DistComm:
             ready.record()
             with torch.cuda.stream(self.recv_stream):
                 self.recv_stream.wait_event(ready)
-                works = dist.batch_isend_irecv([dist.P2POp(dist.irecv, b, peer) for b in bufs])
+                g = self.p2p_groups.get((ins.rank, self.rank))
+                works = dist.batch_isend_irecv([dist.P2POp(dist.irecv, b, peer, group=g) for b in bufs])
                 for w in works:
                     w.wait()  # orders recv_stream after the NCCL stream; does not block the host
                 done = torch.cuda.Event()
@@ -185,8 +188,40 @@ class DistComm:
         return torch.cat(parts, dim=ins.axis)
 
 
+_P2P_GROUPS: dict[tuple, object] = {}
+
+
+def ensure_p2p_groups(prog: Program, comm: DistComm):
+    """One 2-process NCCL group per *directed* pair of pipeline ranks (and position in the stage) that the
+    program transfers between.  All point-to-point operations of one communicator run in issue order on one
+    stream, so with a single communicator a receive posted ahead of time (say, of a gradient that arrives much
+    later) would hold back every send issued after it; with a communicator per direction the only operations
+    that queue behind each other are those that are ordered anyway.  Collective: same order on every process."""
+    if not comm.cuda:
+        return
+    pairs = sorted({(ins.rank, ins.dst) for ins in prog.instrs if isinstance(ins, Transfer)})
+    n_pos = comm.mesh.unstack[0].size
+    mesh_key = comm.mesh._key()
+    for src, dst in pairs:
+        if (src, dst) in comm.p2p_groups:
+            continue
+        if (mesh_key, src, dst) in _P2P_GROUPS:  # made for another compiled function on the same mesh
+            comm.p2p_groups[(src, dst)] = _P2P_GROUPS[(mesh_key, src, dst)]
+            continue
+        mine = None
+        for pos in range(n_pos):
+            procs = [comm.mesh.unstack[src].flat_devices[pos].process_index,
+                     comm.mesh.unstack[dst].flat_devices[pos].process_index]
+            g = dist.new_group(ranks=procs)
+            if pos == comm.pos_in_stage and comm.rank in (src, dst):
+                mine = g
+        comm.p2p_groups[(src, dst)] = mine
+        _P2P_GROUPS[(mesh_key, src, dst)] = mine
+
+
 def ensure_groups(prog: Program, comm: DistComm):
     """Create, in program order and on every process, all process groups the program needs."""
+    ensure_p2p_groups(prog, comm)
     seen = set()
     for ins in prog.instrs:
         ranks = getattr(ins, "ranks", None)

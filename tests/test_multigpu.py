@@ -32,5 +32,5 @@ def test_pipeline_over_nccl_p2p_two_gpus(scenario):
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs at least 4 GPUs")
 @pytest.mark.parametrize("scenario", ["pp2_tp2_std", "pp2_tp2_interleaved"])
 def test_pipeline_times_tensor_parallel_four_gpus(scenario):
-    rc = launch([WORKER, scenario], 4, env={"NCCL_NVLS_ENABLE": "0"}, timeout_s=420)
+    rc = launch([WORKER, scenario], 4, env={"NCCL_NVLS_ENABLE": "0"}, timeout_s=180)
     assert rc == 0
