@@ -301,9 +301,14 @@ def mpmd_jit_by_yield(fun: Callable, mpmd_mesh: MpmdMesh, *, in_shardings=None, 
 
 
 # ---------------------------------------------------------------------------------------------------
-def value_and_grad(fun: Callable, argnums: int | Sequence[int] = 0, has_aux: bool = False) -> Callable:
+def value_and_grad(fun: Callable, argnums: int | Sequence[int] = 0, has_aux: bool = False,
+                   grad_dtype: torch.dtype | None = None) -> Callable:
     """``jax.value_and_grad`` for pytrees of tensors, built on ``torch.autograd.grad`` so that it can
-    be captured: the differentiated arguments are detached copies that require grad."""
+    be captured: the differentiated arguments are detached copies that require grad.
+
+    ``grad_dtype``: dtype the gradients are delivered in (default: each argument's own dtype).  With
+    ``torch.float32`` a weight gradient that a GEMM epilogue wrote in fp32 reaches the caller, and the
+    accumulation over microbatches, without a round trip through the parameter's bf16."""
     nums = (argnums,) if isinstance(argnums, int) else tuple(argnums)
 
     def wrapped(*args, **kwargs):
@@ -312,6 +317,10 @@ def value_and_grad(fun: Callable, argnums: int | Sequence[int] = 0, has_aux: boo
         for n in nums:
             leaves, spec = pytree.tree_flatten(args[n])
             leaves = [l.detach().requires_grad_(True) if l.is_floating_point() else l for l in leaves]
+            if grad_dtype is not None:
+                for l in leaves:
+                    if l.requires_grad:
+                        l.grad_dtype = grad_dtype
             args[n] = pytree.tree_unflatten(leaves, spec)
             flat_all.append(leaves)
             specs.append(spec)
@@ -327,7 +336,7 @@ def value_and_grad(fun: Callable, argnums: int | Sequence[int] = 0, has_aux: boo
             for l in leaves:
                 if l.requires_grad:
                     g = next(it)
-                    gl.append(g if g is not None else torch.zeros_like(l))
+                    gl.append(g if g is not None else torch.zeros_like(l, dtype=grad_dtype or l.dtype))
                 else:
                     gl.append(None)
             trees.append(pytree.tree_unflatten(gl, spec))

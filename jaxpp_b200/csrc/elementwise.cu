@@ -371,6 +371,55 @@ __global__ void rope_kernel(const T* __restrict__ x, const float* __restrict__ c
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// Fused split of a packed projection [rows, Hq + 2*Hkv, D] into contiguous q / k / v with RoPE applied to q
+// and k on the way (cs == nullptr: plain split), and its transpose: merge dq / dk / dv into the packed
+// gradient with the inverse rotation.  One pass over the data instead of three strided copies and two
+// rotations (forward) or three zero fills, three copies, two adds and two rotations (backward).
+// ---------------------------------------------------------------------------------------------------------
+template <typename T, bool MERGE>
+__global__ void qkv_rope_kernel(T* __restrict__ packed, T* __restrict__ q, T* __restrict__ k, T* __restrict__ v,
+                                const float* __restrict__ cs, const float* __restrict__ sn, size_t rows, int S, int Hq,
+                                int Hkv, int D) {
+  constexpr int VN = Vec<T>::N;
+  const int hv = (D / 2) / VN;
+  const int Ht = Hq + 2 * Hkv;
+  const size_t total = rows * Ht * hv;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+    const size_t head = i / hv;
+    const int c = int(i % hv) * VN;
+    const size_t row = head / Ht;
+    const int h = int(head % Ht);
+    const int s = int(row % S);
+    T* pp = packed + head * D;
+    T* sp;
+    bool rot = cs != nullptr;
+    if (h < Hq) sp = q + (row * Hq + h) * D;
+    else if (h < Hq + Hkv) sp = k + (row * Hkv + (h - Hq)) * D;
+    else { sp = v + (row * Hkv + (h - Hq - Hkv)) * D; rot = false; }
+    const T* src = MERGE ? sp : pp;
+    T* dst = MERGE ? pp : sp;
+    Vec<T> a, b;
+    a.load(src + c);
+    b.load(src + D / 2 + c);
+    if (rot) {
+      float af[VN], bf[VN], o1[VN], o2[VN];
+      a.to_float(af); b.to_float(bf);
+#pragma unroll
+      for (int j = 0; j < VN; ++j) {
+        const float cc = cs[size_t(s) * (D / 2) + c + j];
+        float ss = sn[size_t(s) * (D / 2) + c + j];
+        if (MERGE) ss = -ss;
+        o1[j] = af[j] * cc - bf[j] * ss;
+        o2[j] = bf[j] * cc + af[j] * ss;
+      }
+      a.from_float(o1); b.from_float(o2);
+    }
+    a.store(dst + c);
+    b.store(dst + D / 2 + c);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
 // Embedding
 // ---------------------------------------------------------------------------------------------------------
 template <typename T>
@@ -648,6 +697,22 @@ JPB_API int jpb_rope(int dt, const void* x, const float* cs, const float* sn, vo
     if ((D / 2) % VN) return -int(JPB_ERR_BAD_ARGUMENT);
     const size_t work = size_t(bsh) * ((D / 2) / VN);
     rope_kernel<T><<<ew_grid(work, 256), 256, 0, STREAM>>>((const T*)x, cs, sn, (T*)out, bsh, S, H, D, inverse);
+    return LAST_ERR;
+  });
+}
+
+// merge == 0: packed -> q, k, v (RoPE on q and k unless cs is null); merge == 1: q, k, v -> packed, inverse rotation.
+JPB_API int jpb_qkv_rope(int dt, int merge, void* packed, void* q, void* k, void* v, const float* cs, const float* sn,
+                         long long rows, int S, int Hq, int Hkv, int D, void* stream) {
+  return dispatch_dtype(dt, [&](auto tag) {
+    using T = decltype(tag);
+    constexpr int VN = Vec<T>::N;
+    if ((D / 2) % VN) return -int(JPB_ERR_BAD_ARGUMENT);
+    const size_t work = size_t(rows) * (Hq + 2 * Hkv) * ((D / 2) / VN);
+    if (merge)
+      qkv_rope_kernel<T, true><<<ew_grid(work, 256), 256, 0, STREAM>>>((T*)packed, (T*)q, (T*)k, (T*)v, cs, sn, rows, S, Hq, Hkv, D);
+    else
+      qkv_rope_kernel<T, false><<<ew_grid(work, 256), 256, 0, STREAM>>>((T*)packed, (T*)q, (T*)k, (T*)v, cs, sn, rows, S, Hq, Hkv, D);
     return LAST_ERR;
   });
 }

@@ -114,7 +114,7 @@ def make_train_step(cfg: tf.ModelConfig, schedule, hyper: Hyper = Hyper(), dp_ax
             prev = ops.WGRAD_DTYPE[0]
             ops.WGRAD_DTYPE[0] = torch.float32 if hyper.fp32_wgrad else None
             try:
-                loss, grads = jp.value_and_grad(loss_fn)(params)
+                loss, grads = jp.value_and_grad(loss_fn, grad_dtype=torch.float32 if hyper.fp32_wgrad else None)(params)
             finally:
                 ops.WGRAD_DTYPE[0] = prev
             return loss / tokens_per_mb_local, grads

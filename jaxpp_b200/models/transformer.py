@@ -191,12 +191,9 @@ def _attention(cfg: ModelConfig, qkv: torch.Tensor, batch: int, rope) -> torch.T
     hd, tp = cfg.head_dim, cfg.tp
     hq, hkv = cfg.n_heads // tp, cfg.n_kv_heads // tp
     qkv = qkv.view(batch, -1, hq + 2 * hkv, hd)
-    q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hkv], qkv[:, :, hq + hkv:]
-    if rope is not None:
-        cos, sin = rope
-        q = ops.rope(q.contiguous(), cos, sin, False)
-        k = ops.rope(k.contiguous(), cos, sin, False)
-    o, _ = ops.attention(q.contiguous(), k.contiguous(), v.contiguous(), cfg.causal, hd ** -0.5)
+    cos, sin = rope if rope is not None else (None, None)
+    q, k, v = ops.qkv_split(qkv, cos, sin, hq, hkv)  # one pass: split into contiguous q/k/v + RoPE on q, k
+    o, _ = ops.attention(q, k, v, cfg.causal, hd ** -0.5)
     return o.view(-1, hq * hd)
 
 

@@ -351,6 +351,71 @@ _autograd("rope", _rope_autograd, _rope_setup)
 
 
 # ======================================================================================
+# qkv_split: packed projection [B, S, Hq + 2*Hkv, D] -> contiguous q [B,S,Hq,D], k, v [B,S,Hkv,D] with RoPE on
+# q and k (cos/sin None: plain split); qkv_merge is its transpose (inverse rotation) and its backward
+# ======================================================================================
+
+def _qkv_split_ref(qkv, cos, sin, hq, hkv):
+    q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hkv], qkv[:, :, hq + hkv:]
+    if cos is not None:
+        q, k = _rope_ref(q, cos, sin, False), _rope_ref(k, cos, sin, False)
+    return q.contiguous(), k.contiguous(), v.contiguous()
+
+
+def _qkv_merge_ref(dq, dk, dv, cos, sin):
+    if cos is not None:
+        dq, dk = _rope_ref(dq, cos, sin, True), _rope_ref(dk, cos, sin, True)
+    return torch.cat([dq, dk, dv], dim=2)
+
+
+def _qkv_split_fake(qkv, cos, sin, hq, hkv):
+    B, S, _, D = qkv.shape
+    return qkv.new_empty(B, S, hq, D), qkv.new_empty(B, S, hkv, D), qkv.new_empty(B, S, hkv, D)
+
+
+qkv_split = _define(
+    "qkv_split(Tensor qkv, Tensor? cos, Tensor? sin, int hq, int hkv) -> (Tensor, Tensor, Tensor)",
+    _qkv_split_ref, _qkv_split_fake, "qkv_split",
+)
+qkv_merge = _define(
+    "qkv_merge(Tensor dq, Tensor dk, Tensor dv, Tensor? cos, Tensor? sin) -> Tensor",
+    _qkv_merge_ref,
+    lambda dq, dk, dv, cos, sin: dq.new_empty(dq.shape[0], dq.shape[1], dq.shape[2] + 2 * dk.shape[2], dq.shape[3]),
+    "qkv_merge",
+)
+
+
+def _qkv_split_setup(ctx, inputs, output):
+    _, cos, sin, ctx.hq, ctx.hkv = inputs
+    ctx.has_rope = cos is not None
+    if ctx.has_rope:
+        ctx.save_for_backward(cos, sin)
+
+
+def _qkv_split_bwd(ctx, dq, dk, dv):
+    cos, sin = ctx.saved_tensors if ctx.has_rope else (None, None)
+    return qkv_merge(dq.contiguous(), dk.contiguous(), dv.contiguous(), cos, sin), None, None, None, None
+
+
+def _qkv_merge_setup(ctx, inputs, output):
+    dq, dk, _, cos, sin = inputs
+    ctx.hq, ctx.hkv = dq.shape[2], dk.shape[2]
+    ctx.has_rope = cos is not None
+    if ctx.has_rope:
+        ctx.save_for_backward(cos, sin)
+
+
+def _qkv_merge_bwd(ctx, g):
+    cos, sin = ctx.saved_tensors if ctx.has_rope else (None, None)
+    q, k, v = qkv_split(g.contiguous(), cos, sin, ctx.hq, ctx.hkv)
+    return q, k, v, None, None
+
+
+_autograd("qkv_split", _qkv_split_bwd, _qkv_split_setup)
+_autograd("qkv_merge", _qkv_merge_bwd, _qkv_merge_setup)
+
+
+# ======================================================================================
 # Attention on [B, S, H, D] (q) and [B, S, Hkv, D] (k, v); returns output and log-sum-exp
 # ======================================================================================
 

@@ -255,6 +255,34 @@ def rope(x, cos, sin, inverse):
     return out
 
 
+def _qkv_rope(merge, packed, q, k, v, cos, sin):
+    B, S, Hq, D = q.shape
+    lib = load()
+    lib.jpb_qkv_rope.argtypes = [_c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p]
+    cs = None if cos is None else cos.contiguous().data_ptr()
+    sn = None if sin is None else sin.contiguous().data_ptr()
+    _check(lib.jpb_qkv_rope(_dt(packed), merge, packed.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), cs, sn,
+                            B * S, S, Hq, k.shape[2], D, _stream()), "qkv_rope")
+
+
+def qkv_split(qkv, cos, sin, hq, hkv):
+    qkv = qkv.contiguous()
+    B, S, _, D = qkv.shape
+    q = torch.empty(B, S, hq, D, dtype=qkv.dtype, device=qkv.device)
+    k = torch.empty(B, S, hkv, D, dtype=qkv.dtype, device=qkv.device)
+    v = torch.empty(B, S, hkv, D, dtype=qkv.dtype, device=qkv.device)
+    _qkv_rope(0, qkv, q, k, v, cos, sin)
+    return q, k, v
+
+
+def qkv_merge(dq, dk, dv, cos, sin):
+    dq, dk, dv = dq.contiguous(), dk.contiguous(), dv.contiguous()
+    B, S, Hq, D = dq.shape
+    out = torch.empty(B, S, Hq + 2 * dk.shape[2], D, dtype=dq.dtype, device=dq.device)
+    _qkv_rope(1, out, dq, dk, dv, cos, sin)
+    return out
+
+
 # ---- embedding / loss / optimizer --------------------------------------------------------------------------
 def embedding(ids, table):
     ids = ids.contiguous()

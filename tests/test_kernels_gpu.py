@@ -105,6 +105,18 @@ def test_activations_rope_colsum(native, dtype):
     r = native.rope(q, cos, sin, False)
     close(r, ops._rope_ref(q.float(), cos, sin, False), **tol)
     close(native.rope(r, cos, sin, True), q, rtol=tol["rtol"] * 2, atol=tol["atol"] * 2)
+    # fused split of a packed qkv projection (+ RoPE on q, k) and its transpose
+    for hq, hkv, rope_on in ((4, 2, True), (3, 3, False)):
+        packed = rnd(2, 16, hq + 2 * hkv, 128, dtype=dtype, seed=5)
+        c, s_ = (cos, sin) if rope_on else (None, None)
+        got = native.qkv_split(packed, c, s_, hq, hkv)
+        ref = ops._qkv_split_ref(packed.float(), c, s_, hq, hkv)
+        for g, r_ in zip(got, ref):
+            assert g.is_contiguous()
+            close(g, r_, **tol)
+        merged = native.qkv_merge(*got, c, s_)
+        close(merged, packed, rtol=tol["rtol"] * 2, atol=tol["atol"] * 2)  # merge inverts split
+        close(merged, ops._qkv_merge_ref(*[g.float() for g in got], c, s_), **tol)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
