@@ -22,8 +22,8 @@ struct AttnBwdParams {
   int B, Sq, Sk, H, Hkv;
   int causal;
   float scale;
-  const float* lse;    // [B,H,Sq]
-  const float* delta;  // [B,H,Sq]
+  const float* lse;    // [B,H,Sq], already multiplied by log2(e)
+  const float* delta;  // [B,H,Sq], already multiplied by the softmax scale
   __nv_bfloat16 *dq, *dk, *dv;
   int* status;
 };
@@ -34,8 +34,11 @@ __device__ __forceinline__ void st_swz(uint8_t* tile, int r, int cc, uint4 v) {
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// Writes delta * scale and lse * log2(e): the forms the two main kernels consume, so that their inner loops are
+// one fma + ex2 for P and one fma + mul for dS per element.
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
-                                  float* __restrict__ delta, int B, int S, int H, int D) {
+                                  const float* __restrict__ lse, float* __restrict__ delta_s, float* __restrict__ lse2,
+                                  float scale, int B, int S, int H, int D) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const long long total = (long long)B * S * H;
   if (warp >= total) return;
@@ -51,7 +54,11 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __
     acc += x.x * y.x + x.y * y.y;
   }
   acc = warp_sum(acc);
-  if (lane == 0) delta[(size_t(b) * H + h) * S + s] = acc;
+  if (lane == 0) {
+    const size_t idx = (size_t(b) * H + h) * S + s;
+    delta_s[idx] = acc * scale;
+    lse2[idx] = lse[idx] * 1.4426950408889634f;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -64,15 +71,20 @@ struct DkvSmem {
   static constexpr int Q_TILE = 64 * 128;     // [64 q x 64 d] bf16
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = OFF_K + DB * KV_TILE;
-  static constexpr int OFF_Q = OFF_V + DB * KV_TILE;      // 2 stages, each: Q (DB tiles) then dO (DB tiles)
+  // NS stages, each: Q (DB tiles) then dO (DB tiles).  A stage is reloaded only after the MMAs that read it have
+  // completed, and a TMA load takes about as long as an iteration: with two stages the loop
+  // "MMA done -> load -> S -> softmax -> MMA" spanned two iterations and set the pace; more stages hide it.
+  static constexpr int NS = 4;
+  static constexpr int OFF_Q = OFF_V + DB * KV_TILE;
   static constexpr int STAGE = 2 * DB * Q_TILE;
-  static constexpr int OFF_P = OFF_Q + 2 * STAGE;         // P^T  [128 kv x 64 q]
+  static constexpr int OFF_P = OFF_Q + NS * STAGE;        // P^T  [128 kv x 64 q]
   static constexpr int OFF_DS = OFF_P + 128 * 128;        // dS^T [128 kv x 64 q]
   static constexpr int OFF_BAR = OFF_DS + 128 * 128;
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
 };
 
-enum { K1_KV = 0, K1_QF = 1, K1_QE = 3, K1_SF = 5, K1_SFREE = 6, K1_PF = 7, K1_PE = 8, K1_N = 9 };
+constexpr int BWD_NS = 4;  // stages of the streamed operand in both kernels
+enum { K1_KV = 0, K1_QF = 1, K1_QE = K1_QF + BWD_NS, K1_SF = K1_QE + BWD_NS, K1_SFREE, K1_PF, K1_PE, K1_N };
 
 template <int D>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
@@ -101,7 +113,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
   if (threadIdx.x == 0) {
     mbar_init(&bar[K1_KV], 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&bar[K1_QF + s], 1); mbar_init(&bar[K1_QE + s], 1); }
+    for (int s = 0; s < BWD_NS; ++s) { mbar_init(&bar[K1_QF + s], 1); mbar_init(&bar[K1_QE + s], 1); }
     mbar_init(&bar[K1_SF], 1);
     mbar_init(&bar[K1_SFREE], 8);
     mbar_init(&bar[K1_PF], 8);
@@ -132,8 +144,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       }
       bool ok = true;
       for (int t = 0; t < n_iter && ok; ++t) {
-        const int s = t & 1;
-        const uint32_t ph = (t >> 1) & 1;
+        const int s = t % BWD_NS;
+        const uint32_t ph = (t / BWD_NS) & 1;
         const int h = hk * G + t / per_head;
         const int q0 = (i_start + t % per_head) * 64;
         if (!mbar_wait_bounded(&bar[K1_QE + s], ph ^ 1, abort_flag, p.status)) { ok = false; break; }
@@ -162,8 +174,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       const uint32_t sp = smem_u32(smem + L::OFF_P), sds = smem_u32(smem + L::OFF_DS);
       bool ok = n_iter > 0 && mbar_wait_bounded(&bar[K1_KV], 0, abort_flag, p.status);
       auto issue_s = [&](int t) -> bool {
-        const int s = t & 1;
-        if (!mbar_wait_bounded(&bar[K1_QF + s], (t >> 1) & 1, abort_flag, p.status)) return false;
+        const int s = t % BWD_NS;
+        if (!mbar_wait_bounded(&bar[K1_QF + s], (t / BWD_NS) & 1, abort_flag, p.status)) return false;
         if (t > 0 && !mbar_wait_bounded(&bar[K1_SFREE], (t - 1) & 1, abort_flag, p.status)) return false;
         tc_fence_after();
         const uint32_t sq = smem_u32(smem + L::OFF_Q + s * L::STAGE);
@@ -186,7 +198,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       if (ok) ok = issue_s(0);
       for (int t = 0; t < n_iter && ok; ++t) {
         if (t + 1 < n_iter && !issue_s(t + 1)) { ok = false; break; }
-        const int s = t & 1;
+        const int s = t % BWD_NS;
         if (!mbar_wait_bounded(&bar[K1_PF], t & 1, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sq = smem_u32(smem + L::OFF_Q + s * L::STAGE);
@@ -220,12 +232,26 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       // per-column statistics of this block, fetched before the tensor core is done (same address in every lane)
       const float* lse_q = p.lse + (size_t(b) * p.H + h) * p.Sq;
       const float* dl_q = p.delta + (size_t(b) * p.H + h) * p.Sq;
+      // tile-level test (warp-uniform): is every (kv row, query column) of this warp group's 128 x 32 block visible?
+      const int off = p.Sk - p.Sq;
+      const bool full = q0 + 31 < p.Sq && kv0 + 127 < p.Sk && (!p.causal || kv0 + 127 <= q0 + off) && (p.Sq & 3) == 0;
       float lq[32], dl[32];
+      if (full) {
+        const float4* l4 = reinterpret_cast<const float4*>(lse_q + q0);
+        const float4* d4 = reinterpret_cast<const float4*>(dl_q + q0);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const bool in = q0 + i < p.Sq;
-        lq[i] = in ? __ldg(lse_q + q0 + i) * 1.4426950408889634f : 0.f;
-        dl[i] = in ? __ldg(dl_q + q0 + i) : 0.f;
+        for (int i = 0; i < 8; ++i) {
+          const float4 a = __ldg(l4 + i), c = __ldg(d4 + i);
+          lq[4 * i] = a.x; lq[4 * i + 1] = a.y; lq[4 * i + 2] = a.z; lq[4 * i + 3] = a.w;
+          dl[4 * i] = c.x; dl[4 * i + 1] = c.y; dl[4 * i + 2] = c.z; dl[4 * i + 3] = c.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const bool in = q0 + i < p.Sq;
+          lq[i] = in ? __ldg(lse_q + q0 + i) : 0.f;
+          dl[i] = in ? __ldg(dl_q + q0 + i) : 0.f;
+        }
       }
       if (!mbar_wait_bounded_warp(&bar[K1_SF], t & 1, abort_flag, p.status)) { ok = false; break; }
       tc_fence_after();
@@ -241,18 +267,26 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar[K1_SFREE]);
-      const int off = p.Sk - p.Sq;
+      if (full) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int q = q0 + i;
-        const bool visible = q < p.Sq && kv < p.Sk && (!p.causal || kv <= q + off);
-        float pv = 0.f, ds = 0.f;
-        if (visible) {
-          pv = exp2f(fmaf(sv[i], sl2, -lq[i]));
-          ds = pv * (dp[i] - dl[i]) * p.scale;
+        for (int i = 0; i < 32; ++i) {
+          const float pv = exp2f(fmaf(sv[i], sl2, -lq[i]));
+          dp[i] = pv * fmaf(dp[i], p.scale, -dl[i]);
+          sv[i] = pv;
         }
-        sv[i] = pv;
-        dp[i] = ds;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int q = q0 + i;
+          const bool visible = q < p.Sq && kv < p.Sk && (!p.causal || kv <= q + off);
+          float pv = 0.f, ds = 0.f;
+          if (visible) {
+            pv = exp2f(fmaf(sv[i], sl2, -lq[i]));
+            ds = pv * fmaf(dp[i], p.scale, -dl[i]);
+          }
+          sv[i] = pv;
+          dp[i] = ds;
+        }
       }
       if (t > 0) {
         if (!mbar_wait_bounded_warp(&bar[K1_PE], (t - 1) & 1, abort_flag, p.status)) { ok = false; break; }
@@ -325,14 +359,14 @@ struct DqSmem {
   static constexpr int KV_TILE = 64 * 128;   // [64 kv x 64 d]
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_DO = OFF_Q + DB * Q_TILE;
-  static constexpr int OFF_KV = OFF_DO + DB * Q_TILE;   // 2 stages, each: K (DB tiles) then V (DB tiles)
+  static constexpr int OFF_KV = OFF_DO + DB * Q_TILE;   // BWD_NS stages, each: K (DB tiles) then V (DB tiles)
   static constexpr int STAGE = 2 * DB * KV_TILE;
-  static constexpr int OFF_DS = OFF_KV + 2 * STAGE;     // dS [128 q x 64 kv]
+  static constexpr int OFF_DS = OFF_KV + 4 * STAGE;     // dS [128 q x 64 kv]
   static constexpr int OFF_BAR = OFF_DS + 128 * 128;
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
 };
 
-enum { K2_Q = 0, K2_KF = 1, K2_KE = 3, K2_SF = 5, K2_SFREE = 6, K2_DF = 7, K2_DE = 8, K2_N = 9 };
+enum { K2_Q = 0, K2_KF = 1, K2_KE = K2_KF + BWD_NS, K2_SF = K2_KE + BWD_NS, K2_SFREE, K2_DF, K2_DE, K2_N };
 
 template <int D>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
@@ -361,7 +395,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(&bar[K2_Q], 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&bar[K2_KF + s], 1); mbar_init(&bar[K2_KE + s], 1); }
+    for (int s = 0; s < BWD_NS; ++s) { mbar_init(&bar[K2_KF + s], 1); mbar_init(&bar[K2_KE + s], 1); }
     mbar_init(&bar[K2_SF], 1);
     mbar_init(&bar[K2_SFREE], 8);
     mbar_init(&bar[K2_DF], 8);
@@ -392,8 +426,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       }
       bool ok = true;
       for (int t = 0; t < n_iter && ok; ++t) {
-        const int s = t & 1;
-        const uint32_t ph = (t >> 1) & 1;
+        const int s = t % BWD_NS;
+        const uint32_t ph = (t / BWD_NS) & 1;
         if (!mbar_wait_bounded(&bar[K2_KE + s], ph ^ 1, abort_flag, p.status)) { ok = false; break; }
         arm(K2_KF + s, ph, L::STAGE);
         uint8_t* st = smem + L::OFF_KV + s * L::STAGE;
@@ -420,8 +454,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const uint32_t sds = smem_u32(smem + L::OFF_DS);
       bool ok = mbar_wait_bounded(&bar[K2_Q], 0, abort_flag, p.status);
       auto issue_s = [&](int t) -> bool {
-        const int s = t & 1;
-        if (!mbar_wait_bounded(&bar[K2_KF + s], (t >> 1) & 1, abort_flag, p.status)) return false;
+        const int s = t % BWD_NS;
+        if (!mbar_wait_bounded(&bar[K2_KF + s], (t / BWD_NS) & 1, abort_flag, p.status)) return false;
         if (t > 0 && !mbar_wait_bounded(&bar[K2_SFREE], (t - 1) & 1, abort_flag, p.status)) return false;
         tc_fence_after();
         const uint32_t sk = smem_u32(smem + L::OFF_KV + s * L::STAGE);
@@ -444,7 +478,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       if (ok) ok = issue_s(0);
       for (int t = 0; t < n_iter && ok; ++t) {
         if (t + 1 < n_iter && !issue_s(t + 1)) { ok = false; break; }
-        const int s = t & 1;
+        const int s = t % BWD_NS;
         if (!mbar_wait_bounded(&bar[K2_DF], t & 1, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sk = smem_u32(smem + L::OFF_KV + s * L::STAGE);
@@ -464,7 +498,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
     const float sl2 = p.scale * 1.4426950408889634f;
     const bool row_ok = qi < p.Sq;
-    const float lse_r = row_ok ? p.lse[(size_t(b) * p.H + h) * p.Sq + qi] * 1.4426950408889634f : 0.f;
+    const float lse_r = row_ok ? p.lse[(size_t(b) * p.H + h) * p.Sq + qi] : 0.f;
     const float dl_r = row_ok ? p.delta[(size_t(b) * p.H + h) * p.Sq + qi] : 0.f;
     const int off = p.Sk - p.Sq;
     const int grp = (warp - 2) >> 2;  // which half of the 64 kv columns this warp group handles
@@ -485,16 +519,27 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar[K2_SFREE]);
+      // warp-uniform: every (query row, kv column) of this warp group's 128 x 32 block visible?
+      const int kv_first = t * 64 + cb;
+      const bool full = m0 + 127 < p.Sq && kv_first + 31 < p.Sk && (!p.causal || kv_first + 31 <= m0 + off);
+      if (full) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int kv = t * 64 + cb + i;
-        const bool visible = row_ok && kv < p.Sk && (!p.causal || kv <= qi + off);
-        float ds = 0.f;
-        if (visible) {
+        for (int i = 0; i < 32; ++i) {
           const float pv = exp2f(fmaf(sv[i], sl2, -lse_r));
-          ds = pv * (dp[i] - dl_r) * p.scale;
+          dp[i] = pv * fmaf(dp[i], p.scale, -dl_r);
         }
-        dp[i] = ds;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int kv = kv_first + i;
+          const bool visible = row_ok && kv < p.Sk && (!p.causal || kv <= qi + off);
+          float ds = 0.f;
+          if (visible) {
+            const float pv = exp2f(fmaf(sv[i], sl2, -lse_r));
+            ds = pv * fmaf(dp[i], p.scale, -dl_r);
+          }
+          dp[i] = ds;
+        }
       }
       if (t > 0) {
         if (!mbar_wait_bounded_warp(&bar[K2_DE], (t - 1) & 1, abort_flag, p.status)) { ok = false; break; }
@@ -577,10 +622,10 @@ static int launch_bwd(const void* dO, const void* q, const void* k, const void* 
 
 }  // namespace jpb
 
-// Scratch needed by jpb_attention_bwd: the fp32 `delta` vector [B,H,Sq].
+// Scratch needed by jpb_attention_bwd: two fp32 vectors [B,H,Sq] (delta * scale, lse * log2 e).
 JPB_API long long jpb_attention_bwd_scratch_bytes(int B, int Sq, int Sk, int H, int Hkv, int D) {
   (void)Sk; (void)Hkv; (void)D;
-  return (long long)B * H * Sq * 4;
+  return (long long)B * H * Sq * 4 * 2;
 }
 
 // All tensors contiguous bf16: dO/q/o/dq [B,Sq,H,D], k/v/dk/dv [B,Sk,Hkv,D]; lse [B,H,Sq] fp32.
@@ -593,14 +638,16 @@ JPB_API int jpb_attention_bwd(const void* dO, const void* q, const void* k, cons
   if (H % Hkv != 0 || (D != 64 && D != 128)) return -JPB_ERR_BAD_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   float* delta = static_cast<float*>(scratch);
+  float* lse2 = delta + (size_t)B * H * Sq;
   const long long rows = (long long)B * Sq * H;
   const int threads = 256;
   const long long blocks = (rows * 32 + threads - 1) / threads;
   attn_delta_kernel<<<(unsigned)blocks, threads, 0, s>>>(static_cast<const __nv_bfloat16*>(dO),
-                                                         static_cast<const __nv_bfloat16*>(o), delta, B, Sq, H, D);
+                                                         static_cast<const __nv_bfloat16*>(o), lse, delta, lse2, scale,
+                                                         B, Sq, H, D);
   AttnBwdParams p;
   p.B = B; p.Sq = Sq; p.Sk = Sk; p.H = H; p.Hkv = Hkv; p.causal = causal; p.scale = scale;
-  p.lse = lse; p.delta = delta;
+  p.lse = lse2; p.delta = delta;
   p.dq = static_cast<__nv_bfloat16*>(dq); p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
   p.status = jpb_status_device_ptr();
   return D == 128 ? launch_bwd<128>(dO, q, k, v, p, s) : launch_bwd<64>(dO, q, k, v, p, s);

@@ -3,17 +3,20 @@
 // One CTA handles 128 query rows of one (batch, head).  Warp 0 streams Q once and K/V blocks of 128 rows
 // through a 2-stage shared-memory ring with TMA; warp 1 issues tcgen05.mma: S = Q K^T into one of two
 // 128-column TMEM buffers (so S of block j+1 is computed while block j is in softmax) and O += P V into a
-// third TMEM region; warps 2-5 own one query row per thread: they read S from TMEM, keep the running
-// (max, sum), write P as bf16 into shared memory in the swizzled K-major layout the tensor core reads,
-// rescale O in TMEM only when some row's maximum moved, and finally normalise and store O and the
-// log-sum-exp.  All waits are bounded and report through the status word.
+// third TMEM region; warps 2-9 are two softmax groups that split the 128 kv columns of a block: thread
+// (row r, half g) reads its 64 columns of S from TMEM, the two halves of a row agree on the running maximum
+// through shared memory (one named barrier per block), each keeps a partial sum, writes its half of P as
+// bf16 into shared memory in the swizzled K-major layout the tensor core reads, rescales its half of O in
+// TMEM only when some row's maximum moved, and finally normalises and stores its half of O (and the
+// log-sum-exp).  The exponentials are MUFU-bound either way; two groups double the issue slots for the rest
+// and halve the live registers.  All waits are bounded and report through the status word.
 #include "common.cuh"
 
 namespace jpb {
 
 constexpr int ATT_BM = 128;   // query rows per CTA
 constexpr int ATT_BN = 128;   // kv rows per block
-constexpr int ATT_THREADS = 192;
+constexpr int ATT_THREADS = 320;  // TMA warp, MMA warp, 2 softmax groups of 4 warps
 
 struct AttnParams {
   int B, Sq, Sk, H, Hkv;
@@ -35,11 +38,13 @@ struct AttnSmem {
   static constexpr int OFF_K = OFF_Q + Q_BYTES;       // 2 stages
   static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;  // 2 stages
   static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
-  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int OFF_MAX = OFF_P + P_BYTES;       // [2 block parities][2 halves][128 rows] fp32 row maxima
+  static constexpr int OFF_SUM = OFF_MAX + 2048;      // [2 halves][128 rows] fp32 partial row sums
+  static constexpr int OFF_BAR = OFF_SUM + 1024;
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
 };
 
-enum { BAR_Q = 0, BAR_KF = 1, BAR_VF = 3, BAR_KE = 5, BAR_VE = 7, BAR_SF = 9, BAR_SE = 11, BAR_PF = 13, BAR_PV = 14, BAR_N = 15 };
+enum { BAR_Q = 0, BAR_KF = 1, BAR_VF = 3, BAR_KE = 5, BAR_VE = 7, BAR_SF = 9, BAR_SE = 11, BAR_PF = 13, BAR_PV = 14, BAR_MX = 15, BAR_N = 16 };
 
 template <int D>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
@@ -73,10 +78,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       mbar_init(&bar[BAR_KE + s], 1);
       mbar_init(&bar[BAR_VE + s], 1);
       mbar_init(&bar[BAR_SF + s], 1);
-      mbar_init(&bar[BAR_SE + s], 4);
+      mbar_init(&bar[BAR_SE + s], 8);
     }
-    mbar_init(&bar[BAR_PF], 4);
+    mbar_init(&bar[BAR_PF], 8);
     mbar_init(&bar[BAR_PV], 1);
+    mbar_init(&bar[BAR_MX], 8);   // the eight softmax warps meet here once per block (and once at the end)
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&map_q);
@@ -106,19 +112,33 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #pragma unroll
       for (int d = 0; d < L::DB; ++d) tma_load_4d(smem + L::OFF_Q + d * L::TILE, &map_q, &bar[BAR_Q], d * 64, h, m0, b);
       bool ok = true;
-      for (int j = 0; j < n_blocks && ok; ++j) {
+      // K runs one block ahead of V: a K stage is free as soon as S of its block has been computed (early), a V
+      // stage only after P V of its block (late).  Issued in the order K(0) K(1) V(0) K(2) V(1) ... the wait for
+      // a V stage never holds back the K block that the next S needs.
+      auto load_k = [&](int j) -> bool {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait_bounded(&bar[BAR_KE + s], ph ^ 1, abort_flag, p.status)) { ok = false; break; }
+        if (!mbar_wait_bounded(&bar[BAR_KE + s], ph ^ 1, abort_flag, p.status)) return false;
         arm(BAR_KF + s, ph, L::KV_BYTES);
 #pragma unroll
         for (int d = 0; d < L::DB; ++d)
           tma_load_4d(smem + L::OFF_K + s * L::KV_BYTES + d * L::TILE, &map_k, &bar[BAR_KF + s], d * 64, hk, j * ATT_BN, b);
-        if (!mbar_wait_bounded(&bar[BAR_VE + s], ph ^ 1, abort_flag, p.status)) { ok = false; break; }
+        return true;
+      };
+      auto load_v = [&](int j) -> bool {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait_bounded(&bar[BAR_VE + s], ph ^ 1, abort_flag, p.status)) return false;
         arm(BAR_VF + s, ph, L::KV_BYTES);
 #pragma unroll
         for (int d = 0; d < L::DB; ++d)
           tma_load_4d(smem + L::OFF_V + s * L::KV_BYTES + d * L::TILE, &map_v, &bar[BAR_VF + s], d * 64, hk, j * ATT_BN, b);
+        return true;
+      };
+      ok = load_k(0);
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        if (j + 1 < n_blocks && !load_k(j + 1)) { ok = false; break; }
+        if (!load_v(j)) { ok = false; break; }
       }
       if (!ok) {
         const uint64_t t0 = globaltimer_ns();
@@ -175,23 +195,26 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     }
   } else {
     // ------------------------------------- softmax / correction / epilogue -----------------------------
+    constexpr int HALF = ATT_BN / 2;
     const int quarter = warp & 3;
+    const int grp = (warp - 2) >> 2;            // which half of the kv columns (and of the O columns)
     const int r = quarter * 32 + lane;          // row within the tile == TMEM lane
     const int qi = m0 + r;                      // query index
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
     const float sl2 = p.scale * 1.4426950408889634f;
-    float m_run = -INFINITY, l_run = 0.f;
+    float* smax = reinterpret_cast<float*>(smem + L::OFF_MAX);
+    float m_run = -INFINITY, l_run = 0.f;       // l_run: this thread's half of the row sum
     bool ok = true;
     uint8_t* sp = smem + L::OFF_P;
     for (int j = 0; j < n_blocks && ok; ++j) {
       const int s = j & 1;
       if (!mbar_wait_bounded_warp(&bar[BAR_SF + s], (j >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
       tc_fence_after();
-      float sv[ATT_BN];
+      float sv[HALF];
 #pragma unroll
-      for (int c = 0; c < ATT_BN / 32; ++c) {
+      for (int c = 0; c < HALF / 32; ++c) {
         uint32_t t[32];
-        tmem_ld_32x32(tmem_base + lane_addr + s * ATT_BN + c * 32, t);
+        tmem_ld_32x32(tmem_base + lane_addr + s * ATT_BN + grp * HALF + c * 32, t);
         tc_wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; ++i) sv[c * 32 + i] = __uint_as_float(t[i]);
@@ -199,24 +222,37 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar[BAR_SE + s]);  // S buffer may be overwritten by block j+2
-      const int kv0 = j * ATT_BN;
-      const bool need_mask = (p.causal && kv0 + ATT_BN - 1 > m0 + (p.Sk - p.Sq)) || (kv0 + ATT_BN > p.Sk);
+      const int kv0 = j * ATT_BN + grp * HALF;
+      const bool need_mask = (p.causal && kv0 + HALF - 1 > m0 + (p.Sk - p.Sq)) || (kv0 + HALF > p.Sk);
       if (need_mask) {
         const int limit = p.causal ? min(qi + (p.Sk - p.Sq), p.Sk - 1) : p.Sk - 1;  // last visible kv index
 #pragma unroll
-        for (int i = 0; i < ATT_BN; ++i)
+        for (int i = 0; i < HALF; ++i)
           if (kv0 + i > limit) sv[i] = -INFINITY;
       }
       float mx = sv[0];
 #pragma unroll
-      for (int i = 1; i < ATT_BN; ++i) mx = fmaxf(mx, sv[i]);
-      const float m_new = fmaxf(m_run, mx);
+      for (int i = 1; i < HALF; ++i) mx = fmaxf(mx, sv[i]);
+      // the two halves of the row agree on the block maximum (double-buffered by block parity, so the next
+      // block's write cannot overtake a slow reader of this one)
+      smax[(s * 2 + grp) * ATT_BM + r] = mx;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar[BAR_MX]);
+      if (!mbar_wait_bounded_warp(&bar[BAR_MX], j & 1, abort_flag, p.status)) { ok = false; break; }
+      mx = fmaxf(mx, smax[(s * 2 + (grp ^ 1)) * ATT_BM + r]);
+      // Lazy rescaling: the reference maximum of a row only moves when the new maximum exceeds it by more than
+      // 8 in log2 units (P then stays below 2^8, harmless in fp32 sums and bf16 P), so the read-scale-write
+      // pass over O in TMEM, a chain of TMEM round trips, runs in a few blocks instead of nearly all of them.
+      // Both halves of a row see the same maxima and therefore take the same decision.
+      const float m_cand = fmaxf(m_run, mx);
+      const bool bump = (m_cand - m_run) * sl2 > 8.f;   // also true for the first finite maximum (m_run = -inf)
+      const float m_new = bump ? m_cand : m_run;
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = exp2f((m_run - m_use) * sl2);  // 0 when m_run = -inf
+      const float alpha = bump ? exp2f((m_run - m_use) * sl2) : 1.f;  // 0 when m_run = -inf
       const float neg = -m_use * sl2;
       float rs = 0.f;
 #pragma unroll
-      for (int i = 0; i < ATT_BN; ++i) {
+      for (int i = 0; i < HALF; ++i) {
         sv[i] = exp2f(fmaf(sv[i], sl2, neg));
         rs += sv[i];
       }
@@ -225,31 +261,30 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         // PV of the previous block must be complete before O is rescaled and P is overwritten
         if (!mbar_wait_bounded_warp(&bar[BAR_PV], (j - 1) & 1, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
-        if (__any_sync(0xffffffffu, m_new != m_run)) {
+        if (__any_sync(0xffffffffu, bump)) {
 #pragma unroll
-          for (int c = 0; c < D / 16; ++c) {
-            uint32_t t[16];
-            tmem_ld_32x16(tmem_o + lane_addr + c * 16, t);
+          for (int c = 0; c < D / 64; ++c) {   // this group's half of the O columns, 32 at a time
+            uint32_t t[32];
+            tmem_ld_32x32(tmem_o + lane_addr + grp * (D / 2) + c * 32, t);
             tc_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * alpha);
-            tmem_st_32x16(tmem_o + lane_addr + c * 16, t);
+            for (int i = 0; i < 32; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * alpha);
+            tmem_st_32x32(tmem_o + lane_addr + grp * (D / 2) + c * 32, t);
           }
           tc_wait_st();
         }
       }
       m_run = m_new;
       // P -> shared memory, bf16, swizzled K-major: element (r, kv) lives in block kv/64 at
-      // r*128 + ((kv%64)/8 ^ (r%8))*16 + (kv%8)*2
+      // r*128 + ((kv%64)/8 ^ (r%8))*16 + (kv%8)*2; this group's 64 columns are exactly block `grp`
 #pragma unroll
-      for (int c = 0; c < ATT_BN / 8; ++c) {
+      for (int c = 0; c < HALF / 8; ++c) {
         uint4 v;
         v.x = pack_bf16(sv[c * 8 + 0], sv[c * 8 + 1]);
         v.y = pack_bf16(sv[c * 8 + 2], sv[c * 8 + 3]);
         v.z = pack_bf16(sv[c * 8 + 4], sv[c * 8 + 5]);
         v.w = pack_bf16(sv[c * 8 + 6], sv[c * 8 + 7]);
-        const int blk = c >> 3, cc = c & 7;
-        *reinterpret_cast<uint4*>(sp + blk * L::TILE + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
+        *reinterpret_cast<uint4*>(sp + grp * L::TILE + r * 128 + ((c ^ (r & 7)) << 4)) = v;
       }
       fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's async proxy
       tc_fence_before();
@@ -258,13 +293,20 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     }
     if (ok && mbar_wait_bounded_warp(&bar[BAR_PV], (n_blocks - 1) & 1, abort_flag, p.status)) {
       tc_fence_after();
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      const bool row_ok = qi < p.Sq;
-      __nv_bfloat16* orow = p.o + ((size_t(b) * p.Sq + qi) * p.H + h) * D;
+      // combine the two partial row sums
+      float* ssum = reinterpret_cast<float*>(smem + L::OFF_SUM);
+      ssum[grp * ATT_BM + r] = l_run;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar[BAR_MX]);
+      if (!mbar_wait_bounded_warp(&bar[BAR_MX], n_blocks & 1, abort_flag, p.status)) ok = false;
+      const float l_all = ok ? l_run + ssum[(grp ^ 1) * ATT_BM + r] : 0.f;
+      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+      const bool row_ok = ok && qi < p.Sq;
+      __nv_bfloat16* orow = p.o + ((size_t(b) * p.Sq + qi) * p.H + h) * D + grp * (D / 2);
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
         uint32_t t[32];
-        tmem_ld_32x32(tmem_o + lane_addr + c * 32, t);
+        tmem_ld_32x32(tmem_o + lane_addr + grp * (D / 2) + c * 32, t);
         tc_wait_ld();
         if (row_ok) {
 #pragma unroll
@@ -278,7 +320,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           }
         }
       }
-      if (row_ok) p.lse[(size_t(b) * p.H + h) * p.Sq + qi] = (l_run > 0.f) ? m_run * p.scale + logf(l_run) : -INFINITY;
+      if (row_ok && grp == 0)
+        p.lse[(size_t(b) * p.H + h) * p.Sq + qi] = (l_all > 0.f) ? m_run * p.scale + logf(l_all) : -INFINITY;
     }
   }
 

@@ -130,8 +130,10 @@ __global__ void norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w
 // sums of dw (and db) in registers; partials go to `partial[gridDim.x][2][H]` (scratch) and a second kernel
 // reduces them.
 // ---------------------------------------------------------------------------------------------------------
-template <typename T, bool LAYER>
-__global__ void norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+// MAXT = largest block the instantiation is launched with: 512 leaves room (128 registers per thread) for the
+// next-row prefetch; the 1024-thread variant (very long rows) reloads each row after the barrier instead.
+template <typename T, bool LAYER, int MAXT = 512>
+__global__ void __launch_bounds__(MAXT) norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
                                 const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                                 T* __restrict__ dx, float* __restrict__ partial, int rows, int H) {
   constexpr int VN = Vec<T>::N;
@@ -150,8 +152,9 @@ __global__ void norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
   }
   // the next row's x and dy are requested before this row's block reduction, so that loads stay in flight
   // across the barrier
+  constexpr bool PREFETCH = MAXT <= 512;
   Vec<T> xv[NORM_BWD_VECS], dv[NORM_BWD_VECS];
-  if (blockIdx.x < rows) {
+  if (PREFETCH && blockIdx.x < rows) {
 #pragma unroll
     for (int i = 0; i < NORM_BWD_VECS; ++i) {
       const int v = threadIdx.x + i * blockDim.x;
@@ -170,6 +173,10 @@ __global__ void norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
     for (int i = 0; i < NORM_BWD_VECS; ++i) {
       const int v = threadIdx.x + i * blockDim.x;
       if (v < nvec) {
+        if (!PREFETCH) {
+          xv[i].load(x + size_t(row) * H + v * VN);
+          dv[i].load(dy + size_t(row) * H + v * VN);
+        }
         float xf[VN], df[VN];
         xv[i].to_float(xf); dv[i].to_float(df);
 #pragma unroll
@@ -184,7 +191,7 @@ __global__ void norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
       }
     }
     const int next = row + gridDim.x;
-    if (next < rows) {
+    if (PREFETCH && next < rows) {
 #pragma unroll
       for (int i = 0; i < NORM_BWD_VECS; ++i) {
         const int v = threadIdx.x + i * blockDim.x;
@@ -420,6 +427,40 @@ __global__ void qkv_rope_kernel(T* __restrict__ packed, T* __restrict__ q, T* __
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// Dropout with a counter-based generator (Philox4x32-10): element i uses word (i % 4) of the block keyed by
+// `seed` at counter (i / 4, offset).  The mask is a pure function of (seed, offset, i), so the backward pass
+// regenerates it instead of storing it, and a pipelined run draws the same numbers as a sequential one.
+// ---------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0, uint32_t k1) {
+#pragma unroll
+  for (int round = 0; round < 10; ++round) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    const uint32_t n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
+    c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+  }
+  return make_uint4(c0, c1, c2, c3);
+}
+
+template <typename T>
+__global__ void dropout_kernel(const T* __restrict__ x, T* __restrict__ out, const long long* __restrict__ seed_ptr,
+                               long long offset, uint32_t threshold, float scale, size_t n) {
+  const unsigned long long seed = (unsigned long long)(*seed_ptr);
+  const uint32_t k0 = uint32_t(seed), k1 = uint32_t(seed >> 32);
+  const size_t n4 = (n + 3) / 4;
+  for (size_t q = size_t(blockIdx.x) * blockDim.x + threadIdx.x; q < n4; q += size_t(gridDim.x) * blockDim.x) {
+    const uint4 r = philox4x32_10(uint32_t(q), uint32_t(q >> 32), uint32_t(offset), uint32_t((unsigned long long)offset >> 32), k0, k1);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const size_t i = q * 4 + j;
+      if (i < n) out[i] = T(w[j] >= threshold ? float(x[i]) * scale : 0.f);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
 // Embedding
 // ---------------------------------------------------------------------------------------------------------
 template <typename T>
@@ -629,10 +670,16 @@ JPB_API int jpb_norm_bwd(int layer, int dt, const void* dy, const void* x, const
     if (H % VN || H / VN > NORM_BWD_VECS * 1024) return -int(JPB_ERR_BAD_ARGUMENT);
     const int threads = norm_threads(H, VN, NORM_BWD_VECS);
     const int grid = rows < sm_count() * 2 ? rows : sm_count() * 2;
-    if (layer)
+    if (threads > 512) {
+      if (layer)
+        norm_bwd_kernel<T, true, 1024><<<grid, threads, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)w, mean, rstd, (T*)dx, scratch, rows, H);
+      else
+        norm_bwd_kernel<T, false, 1024><<<grid, threads, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)w, nullptr, rstd, (T*)dx, scratch, rows, H);
+    } else if (layer) {
       norm_bwd_kernel<T, true><<<grid, threads, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)w, mean, rstd, (T*)dx, scratch, rows, H);
-    else
+    } else {
       norm_bwd_kernel<T, false><<<grid, threads, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)w, nullptr, rstd, (T*)dx, scratch, rows, H);
+    }
     const int rt = 256;
     reduce_partials_kernel<T><<<(H + rt - 1) / rt, rt, 0, STREAM>>>(scratch, (T*)dw, grid, H, size_t(2) * H);
     if (layer) reduce_partials_kernel<T><<<(H + rt - 1) / rt, rt, 0, STREAM>>>(scratch + H, (T*)db, grid, H, size_t(2) * H);
@@ -663,6 +710,20 @@ static int ew_grid(size_t work, int threads) {
   size_t blocks = (work + threads - 1) / threads;
   const size_t cap = size_t(sm_count()) * 16;
   return int(blocks < cap ? (blocks ? blocks : 1) : cap);
+}
+
+// out = x * keep / (1 - p) with keep drawn from Philox keyed by *seed (an int64 on the device) at `offset`.
+JPB_API int jpb_dropout(int dt, const void* x, void* out, const long long* seed, long long offset, float p, long long n,
+                        void* stream) {
+  if (!(p >= 0.f && p < 1.f)) return -int(JPB_ERR_BAD_ARGUMENT);
+  return dispatch_dtype(dt, [&](auto tag) {
+    using T = decltype(tag);
+    const double t = double(p) * 4294967296.0;
+    const uint32_t threshold = t >= 4294967295.0 ? 0xFFFFFFFFu : uint32_t(t);
+    dropout_kernel<T><<<ew_grid(size_t(n + 3) / 4, 256), 256, 0, STREAM>>>((const T*)x, (T*)out, seed, offset, threshold,
+                                                                         1.f / (1.f - p), size_t(n));
+    return LAST_ERR;
+  });
 }
 
 JPB_API int jpb_gelu(int dt, int bwd, const void* x, const void* dy, void* out, long long n, void* stream) {
@@ -828,8 +889,12 @@ JPB_API int jpb_rmsnorm_bwd_noalloc(int dtype, const void* dy, const void* x, co
     constexpr int VN = Vec<T>::N;
     const int threads = norm_threads(H, VN, NORM_BWD_VECS);
     // every CTA writes its whole partial row before the reduction reads it: nothing has to be cleared
-    norm_bwd_kernel<T, false><<<grid, threads, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)w, nullptr, rstd, (T*)dx,
-                                                            scratch, rows, H);
+    if (threads > 512)
+      norm_bwd_kernel<T, false, 1024><<<grid, threads, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)w, nullptr, rstd,
+                                                                    (T*)dx, scratch, rows, H);
+    else
+      norm_bwd_kernel<T, false><<<grid, threads, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)w, nullptr, rstd, (T*)dx,
+                                                              scratch, rows, H);
     reduce_partials_kernel<T><<<(H + 255) / 256, 256, 0, STREAM>>>(scratch, (T*)dw, grid, H, size_t(2) * H);
     return LAST_ERR;
   });

@@ -285,6 +285,61 @@ _autograd(
 )
 
 
+# ======================================================================================
+# dropout with a counter-based generator: the mask is a function of (seed, offset, element index), so backward
+# regenerates it and a pipelined run draws the same numbers as the sequential one (the reference keeps
+# threefry keys with the same property, tests/functional_testing/test_dropout_enabled.py:55)
+# ======================================================================================
+_M32 = 0xFFFFFFFF
+
+
+def _mul32(a: int, b: Tensor):
+    """(hi, lo) 32-bit halves of a * b for a 32-bit constant ``a`` and int64 ``b`` holding 32-bit values."""
+    t, u = a * (b & 0xFFFF), a * (b >> 16)
+    low = ((u & 0xFFFF) << 16) + (t & _M32)
+    return ((u >> 16) + (t >> 32) + (low >> 32)) & _M32, low & _M32
+
+
+def philox_u32(n_blocks: int, seed: Tensor, offset: int, device) -> Tensor:
+    """[n_blocks, 4] int64 tensor of the 32-bit outputs of Philox4x32-10 at counters (block, offset), key ``seed``."""
+    q = torch.arange(n_blocks, dtype=torch.int64, device=device)
+    c0, c1 = q & _M32, (q >> 32) & _M32
+    c2 = torch.full_like(q, offset & _M32)
+    c3 = torch.full_like(q, (offset >> 32) & _M32)
+    seed = seed.to(device=device, dtype=torch.int64)
+    k0, k1 = (seed & _M32).expand_as(q).clone(), ((seed >> 32) & _M32).expand_as(q).clone()
+    for _ in range(10):
+        hi0, lo0 = _mul32(0xD2511F53, c0)
+        hi1, lo1 = _mul32(0xCD9E8D57, c2)
+        c0, c1, c2, c3 = hi1 ^ c1 ^ k0, lo1, hi0 ^ c3 ^ k1, lo0
+        k0, k1 = (k0 + 0x9E3779B9) & _M32, (k1 + 0xBB67AE85) & _M32
+    return torch.stack([c0, c1, c2, c3], dim=1)
+
+
+def _dropout_ref(x, p, seed, offset):
+    n = x.numel()
+    words = philox_u32((n + 3) // 4, seed, offset, x.device).reshape(-1)[:n].view(x.shape)
+    t = p * 4294967296.0
+    threshold = 0xFFFFFFFF if t >= 4294967295.0 else int(t)
+    keep = words >= threshold
+    return torch.where(keep, _f32(x) * (1.0 / (1.0 - p)), torch.zeros((), device=x.device)).to(x.dtype)
+
+
+dropout = _define(
+    "dropout(Tensor x, float p, Tensor seed, int offset) -> Tensor",
+    _dropout_ref, lambda x, p, seed, offset: torch.empty_like(x), "dropout",
+)
+
+
+def _dropout_setup(ctx, inputs, output):
+    _, ctx.p, seed, ctx.offset = inputs
+    ctx.save_for_backward(seed)
+
+
+_autograd("dropout", lambda ctx, dy: (dropout(dy.contiguous(), ctx.p, ctx.saved_tensors[0], ctx.offset), None, None, None),
+          _dropout_setup)
+
+
 def _swiglu_ref(gu):
     g, u = _f32(gu).chunk(2, dim=-1)
     return (torch.nn.functional.silu(g) * u).to(gu.dtype)

@@ -255,6 +255,17 @@ def rope(x, cos, sin, inverse):
     return out
 
 
+def dropout(x, p, seed, offset):
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    lib = load()
+    lib.jpb_dropout.argtypes = [_c_int, _c_p, _c_p, _c_p, _c_ll, _c_f, _c_ll, _c_p]
+    seed = seed.to(device=x.device, dtype=torch.int64).contiguous()
+    _check(lib.jpb_dropout(_dt(x), x.data_ptr(), out.data_ptr(), seed.data_ptr(), int(offset), float(p), x.numel(), _stream()),
+           "dropout")
+    return out
+
+
 def _qkv_rope(merge, packed, q, k, v, cos, sin):
     B, S, Hq, D = q.shape
     lib = load()

@@ -120,6 +120,21 @@ def test_activations_rope_colsum(native, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_dropout_matches_counter_based_reference(native, dtype):
+    from jaxpp_b200.ops import core as ops
+
+    x = rnd(37, 129, dtype=dtype, seed=11)   # odd element count: the last Philox block is partial
+    seed = torch.tensor(0x1234567812345, dtype=torch.int64, device="cuda")
+    for p_drop, offset in ((0.1, 0), (0.5, 3), (0.0, 9)):
+        got = native.dropout(x, p_drop, seed, offset)
+        ref = ops._dropout_ref(x, p_drop, seed, offset)
+        assert torch.equal(got == 0, ref == 0), "mask differs from the Philox reference"
+        close(got, ref.float(), rtol=1e-2 if dtype == torch.bfloat16 else 1e-6, atol=1e-6)
+    drop = (native.dropout(torch.ones(1 << 20, device="cuda"), 0.3, seed, 1) == 0).float().mean().item()
+    assert abs(drop - 0.3) < 5e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_embedding_and_cross_entropy(native, dtype):
     from jaxpp_b200.ops import core as ops
 

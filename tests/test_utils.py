@@ -80,3 +80,23 @@ def test_bytes():
     assert format_bytes(512) == "512B"
     assert format_bytes(2048) == "2.00KiB"
     assert hbytes([1024 * 1024, 1024 * 1024]) == "2.00MiB"
+
+
+def test_dropout_is_a_pure_function_of_seed_offset_and_index():
+    import torch
+
+    from jaxpp_b200.ops import core as ops
+
+    # known answer of Philox4x32-10 for the all-zero counter and key (Random123 test vectors)
+    w = ops.philox_u32(1, torch.tensor(0), 0, "cpu")[0]
+    assert [int(v) for v in w] == [0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8]
+    x = torch.ones(3, 1001)
+    seed = torch.tensor(99, dtype=torch.int64)
+    y = ops.dropout(x, 0.25, seed, 5)
+    assert torch.equal(y, ops.dropout(x, 0.25, seed, 5))
+    assert not torch.equal(y, ops.dropout(x, 0.25, seed, 6))
+    assert not torch.equal(y, ops.dropout(x, 0.25, seed + 1, 5))
+    assert abs((y == 0).float().mean().item() - 0.25) < 0.03 and torch.allclose(y[y != 0], torch.tensor(1 / 0.75))
+    xr = x.clone().requires_grad_(True)
+    (g,) = torch.autograd.grad(ops.dropout(xr, 0.25, seed, 5).sum(), [xr])
+    assert torch.equal(g, y)  # backward regenerates the same mask
