@@ -55,6 +55,7 @@ struct CommGemmParams {
   // all-gather
   int gather;                        // GatherMode
   int gathered_is_b;                 // GATHER_RED: which operand is the gathered one
+  int phases;                        // GATHER_RED with fp32 output: one pass over all tiles per rank slot (see kernel)
   int chunks_per_rank;               // m-tiles (GATHER_ROWS) or k-blocks (GATHER_RED) per rank slot
   int rows_per_slot;                 // rows of G per rank slot
   int pieces;                        // pieces per chunk
@@ -94,14 +95,20 @@ __device__ __forceinline__ void st_release_sys(int* p, int v) {
 }
 __device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
-// Spin until *flag >= want (flags only grow), at most JPB_WAIT_BUDGET_NS.  `sys` selects the scope of the load.
+// Spin until *flag >= want (flags only grow), at most JPB_WAIT_BUDGET_NS.  The poll is a relaxed load and one
+// acquire fence follows the successful one: an acquire load at system scope per poll measured about 2 us each
+// on this hardware, which added up to tens of microseconds per CTA in the reduction-gather.
 __device__ __forceinline__ bool flag_wait_bounded(const int* flag, int want, bool sys, volatile int* abort_flag, int* status,
                                                   int code) {
   uint32_t spins = 0;
   uint64_t t0 = 0;
   while (true) {
-    const int v = sys ? ld_acquire_sys(flag) : ld_acquire_gpu(flag);
-    if (v >= want) return true;
+    const int v = *reinterpret_cast<const volatile int*>(flag);
+    if (v >= want) {
+      if (sys) asm volatile("fence.acq_rel.sys;" ::: "memory");
+      else asm volatile("fence.acq_rel.gpu;" ::: "memory");
+      return true;
+    }
     if ((++spins & 0xff) == 0) {
       if (*abort_flag) return false;
       const uint64_t now = globaltimer_ns();
@@ -139,12 +146,72 @@ __device__ __forceinline__ bool flag_wait4_bounded(const int* flags, int want, v
   }
 }
 
-// Tile order: with a scatter, the row blocks of the peers come first (starting with the next rank) and the
-// own block last; with a row gather, the own block comes first.  Inside a row block tiles are m-fastest.
+// Wait until `count` consecutive flags are all >= want, with relaxed loads (several in flight) and a single
+// acquire fence at the end: a pass of the reduction-gather needs a whole slot, and one fence is much cheaper
+// than an acquire per chunk.
+__device__ __forceinline__ bool flags_wait_all_bounded(const int* flags, int count, int want, volatile int* abort_flag,
+                                                       int* status, int code) {
+  uint32_t spins = 0;
+  uint64_t t0 = 0;
+  int done = 0;  // flags [0, done) have been seen
+  while (done < count) {
+    bool all = true;
+    int i = done;
+    for (; i + 4 <= count && all; i += 4) {
+      int a, b, c, d;
+      if (((reinterpret_cast<uintptr_t>(flags + i)) & 15) == 0) {
+        asm volatile("ld.volatile.global.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "l"(flags + i) : "memory");
+      } else {
+        a = *reinterpret_cast<const volatile int*>(flags + i);     b = *reinterpret_cast<const volatile int*>(flags + i + 1);
+        c = *reinterpret_cast<const volatile int*>(flags + i + 2); d = *reinterpret_cast<const volatile int*>(flags + i + 3);
+      }
+      all = a >= want && b >= want && c >= want && d >= want;
+      if (all) done = i + 4;
+    }
+    for (; i < count && all; ++i) {
+      all = *reinterpret_cast<const volatile int*>(flags + i) >= want;
+      if (all) done = i + 1;
+    }
+    if (done >= count) break;
+    if ((++spins & 0x3f) == 0) {
+      if (*abort_flag) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > JPB_WAIT_BUDGET_NS) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, JPB_OK, code);
+        return false;
+      }
+    }
+  }
+  asm volatile("fence.acq_rel.sys;" ::: "memory");
+  return true;
+}
+
+// Tile order.  Plain: groups of 16 row tiles walked column by column (L2-friendly).  Row gather: the own row
+// block first, then the peers' blocks in the order their chunks arrive.  Scatter: the row blocks of all ranks
+// are interleaved in groups of 16 row tiles -- group g of the next rank's block, of the one after, ..., of the
+// own block last, then group g+1 -- so that the NVLink traffic is spread over the kernel instead of being
+// crammed into its first (n-1)/n, while an own tile still runs a group (more than a wave of the grid) after
+// the peers computed its partials.  (Interleaving column by column put both in the same wave and every own
+// tile waited for the link: measured 30 % slower on the K = 2048 projection.)
 struct TileOrder {
-  int tiles_m, tiles_n, n_ranks, rank, tm_per_rank, mode;  // mode: 0 plain, 1 own-first, 2 own-last
+  int tiles_m, tiles_n, n_ranks, rank, tm_per_rank, mode;  // mode: 0 plain, 1 own-first, 2 scatter (interleaved)
   __device__ __forceinline__ void get(int idx, int& m_blk, int& n_blk) const {
-    // inside a row block tiles are walked in groups of 16 row tiles, column by column (L2-friendly)
+    if (mode == 2) {
+      const int per_group = 16 * tiles_n * n_ranks;
+      const int group = idx / per_group, first_m = group * 16;
+      const int gm = (tm_per_rank - first_m) < 16 ? (tm_per_rank - first_m) : 16;
+      const int ing = idx - group * per_group;            // [n_ranks][tiles_n][gm]
+      const int per_blk = tiles_n * gm;
+      const int blk = ing / per_blk;
+      const int rem = ing - blk * per_blk;
+      n_blk = rem / gm;
+      const int l = rem - n_blk * gm;
+      const int slot = (rank + 1 + blk) % n_ranks;        // blk == n_ranks - 1 is the own block
+      m_blk = slot * tm_per_rank + first_m + l;
+      return;
+    }
     const int rows_here = mode == 0 ? tiles_m : tm_per_rank;
     const int per_block = rows_here * tiles_n;
     const int blk = idx / per_block, in = idx % per_block;
@@ -158,8 +225,7 @@ struct TileOrder {
       m_blk = lm;
       return;
     }
-    const int shift = mode == 1 ? blk : blk + 1;
-    const int slot = (rank + shift) % n_ranks;
+    const int slot = (rank + blk) % n_ranks;
     m_blk = slot * tm_per_rank + lm;
   }
 };
@@ -208,6 +274,13 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   order.tm_per_rank = p.tiles_m / p.n_ranks;
   order.mode = p.scatter ? 2 : (p.gather == GATHER_ROWS ? 1 : 0);
   const int k_rot = p.gather == GATHER_RED ? p.rank * p.chunks_per_rank : 0;
+  // Reduction-gather with an fp32 output runs in `phases` passes over this CTA's tiles: pass 0 multiplies the own
+  // rank's slice of the reduction dimension, pass q the slice pushed by rank (rank + q) % n, each adding into D
+  // through the accumulate epilogue.  No tile ever waits in the middle of its k loop for data still in flight:
+  // by the time pass q starts, the tensor cores have spent a whole pass on data that was already here.  The
+  // same CTA (and the same thread) owns a tile in every pass, so the read-modify-write of D needs no fence.
+  const int phases = p.phases;
+  const int kb_per_pass = phases > 1 ? p.chunks_per_rank : k_blocks;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < CSTAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -243,14 +316,25 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int own_lo = p.rank * p.chunks_per_rank, own_hi = own_lo + p.chunks_per_rank;
       const bool rows_mode = p.gather == GATHER_ROWS, red_mode = p.gather == GATHER_RED;
       const bool gathered_a = red_mode && !p.gathered_is_b, gathered_b = red_mode && p.gathered_is_b;
+      for (int pass = 0; pass < phases && ok; ++pass) {
+      const int pass_slot = (p.rank + pass) % p.n_ranks;
+      if (phases > 1) {
+        // a new slice: all of its chunks must have landed (they had a whole pass of tensor-core time to do so)
+        if (pass > 0) {
+          if (!flags_wait_all_bounded(p.chunk_flags + pass_slot * p.chunks_per_rank, p.chunks_per_rank, p.epoch, abort_flag,
+                                      p.status, JPB_ERR_PEER_TIMEOUT)) { ok = false; break; }
+          fence_proxy_async_global();
+        }
+        red_verified = kb_per_pass;
+      }
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int m_blk, n_blk;
         order.get(tile, m_blk, n_blk);
         const int m0 = m_blk * CBM, n0 = n_blk * CBN;
         const bool own_rows = rows_mode && m_blk >= own_lo && m_blk < own_hi;
         if (rows_mode && !own_rows && !chunk_ready(m_blk)) { ok = false; break; }
-        int kbe = k_rot;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it, kbe = (kbe + 1 == k_blocks ? 0 : kbe + 1)) {
+        int kbe = phases > 1 ? pass_slot * p.chunks_per_rank : k_rot;
+        for (int kb = 0; kb < kb_per_pass; ++kb, ++it, kbe = (kbe + 1 == k_blocks ? 0 : kbe + 1)) {
           const bool own_k = red_mode && kbe >= own_lo && kbe < own_hi;
           if (red_mode && !own_k && kb >= red_verified) {
             // four chunks per poll where the flags are aligned and none of the four is an own chunk
@@ -301,6 +385,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
         }
       }
+      }
       if (!ok) {
         const uint64_t t0 = globaltimer_ns();
         for (int s = 0; s < CSTAGES; ++s) {
@@ -316,12 +401,13 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       constexpr uint32_t idesc = make_idesc_bf16(CBM, CBN, A_MN, B_MN);
       uint32_t it = 0, tile_i = 0;
       bool ok = true;
+      for (int pass = 0; pass < phases && ok; ++pass)
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
         const uint32_t acc = tile_i & 1, acc_ph = (tile_i >> 1) & 1;
         if (!mbar_wait_bounded(&acc_empty[acc], acc_ph ^ 1, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * CBN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = 0; kb < kb_per_pass; ++kb, ++it) {
           const int s = it % CSTAGES;
           if (!mbar_wait_bounded(&full[s], (it / CSTAGES) & 1, abort_flag, p.status)) { ok = false; break; }
           tc_fence_after();
@@ -398,10 +484,12 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int tiles_per_rank = tm_per_rank * p.tiles_n;
     uint32_t tile_i = 0, epi_uses = 0;
     bool ok = true;
+    for (int pass = 0; pass < phases && ok; ++pass)
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
       int m_blk, n_blk;
       order.get(tile, m_blk, n_blk);
       const int m0 = m_blk * CBM, n0 = n_blk * CBN;
+      const bool accumulate = p.accumulate || pass > 0;
       const uint32_t acc = tile_i & 1, acc_ph = (tile_i >> 1) & 1;
       if (!mbar_wait_bounded_warp(&acc_full[acc], acc_ph, abort_flag, p.status)) { ok = false; break; }
       tc_fence_after();
@@ -413,13 +501,15 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const bool remote = p.scatter && owner != p.rank;
       if (p.scatter && !remote) {
         // own block: the peers' partials for this tile must have landed
-        bool w = true;
-        for (int q = 0; q < p.n_ranks && w; ++q) {
-          if (q == p.rank) continue;
-          w = flag_wait_bounded(p.tile_flags_local + q * tiles_per_rank + lm * p.tiles_n + n_blk, p.epoch, true, abort_flag,
-                                p.status, JPB_ERR_PEER_TIMEOUT);
+        int w = 1;
+        if (lane == 0) {  // one lane polls and fences; the shuffle below orders the other lanes after it
+          for (int q = 0; q < p.n_ranks && w; ++q) {
+            if (q == p.rank) continue;
+            w = flag_wait_bounded(p.tile_flags_local + q * tiles_per_rank + lm * p.tiles_n + n_blk, p.epoch, true, abort_flag,
+                                  p.status, JPB_ERR_PEER_TIMEOUT);
+          }
         }
-        w = __all_sync(0xffffffffu, w);
+        w = __shfl_sync(0xffffffffu, w, 0);
         if (!w) { ok = false; break; }
       }
       if (remote) {
@@ -485,7 +575,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
           }
         }
-        if (p.bias) {
+        if (p.bias && pass == 0) {
           if (p.bias_fp32) {
             const float* b = static_cast<const float*>(p.bias) + col0;
 #pragma unroll
@@ -502,7 +592,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           for (int j = 0; j < 32; j += 4) {
             if (j < ncols) {
               float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-              if (p.accumulate) {
+              if (accumulate) {
                 const float4 old = *reinterpret_cast<const float4*>(d + j);
                 o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
               }
@@ -629,6 +719,7 @@ JPB_API int jpb_comm_gemm(const void* A, const void* B, void* D, const void* bia
   p.tiles_m = (M + CBM - 1) / CBM;
   p.tiles_n = (N + CBN - 1) / CBN;
   p.n_ranks = n; p.rank = desc->rank; p.epoch = desc->epoch;
+  p.phases = 1;
   p.gather = desc->gather; p.scatter = desc->scatter;
   int* my_ctrl = static_cast<int*>(desc->ctrl[desc->rank]);
   p.chunk_flags = my_ctrl + JPB_CTRL_CHUNK_FLAGS;
@@ -666,6 +757,7 @@ JPB_API int jpb_comm_gemm(const void* A, const void* B, void* D, const void* bia
     p.chunks_per_rank = (K / CBK) / n;
     p.rows_per_slot = K / n;
     p.chunk_bytes = (long long)CBK * own_width * 2;
+    if (out_fp32 && !desc->scatter) p.phases = n;
   }
   if (desc->gather) {
     if (n * p.chunks_per_rank > JPB_MAX_CHUNKS || (own_width & 7)) return -JPB_ERR_BAD_ARGUMENT;

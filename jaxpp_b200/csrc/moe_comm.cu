@@ -250,3 +250,79 @@ JPB_API int jpb_moe_combine(const void* y, const int* dest, const float* weights
   jpb::moe_combine_kernel<<<moe_grid(), jpb::MOE_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return int(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Router: softmax over the expert logits, top-k pick, weights renormalised over the picks, and the two
+// per-expert statistics of the load-balancing loss (sum of probabilities, number of picks) in one pass.
+// One thread per token, at most 64 experts.
+// ---------------------------------------------------------------------------------------------------------
+namespace jpb {
+
+constexpr int ROUTER_MAX_E = 64;
+
+template <typename T>
+__global__ void router_kernel(const T* __restrict__ logits, float* __restrict__ probs, long long* __restrict__ top_i,
+                              float* __restrict__ weights, float* __restrict__ prob_sum, float* __restrict__ hits, int n_tok,
+                              int E, int k) {
+  __shared__ float s_prob[ROUTER_MAX_E];
+  __shared__ float s_hits[ROUTER_MAX_E];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) { s_prob[e] = 0.f; s_hits[e] = 0.f; }
+  __syncthreads();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < n_tok) {
+    float p[ROUTER_MAX_E];
+    float mx = -INFINITY;
+    for (int e = 0; e < E; ++e) { p[e] = float(logits[size_t(t) * E + e]); mx = fmaxf(mx, p[e]); }
+    float sum = 0.f;
+    for (int e = 0; e < E; ++e) { p[e] = __expf(p[e] - mx); sum += p[e]; }
+    const float inv = 1.f / sum;
+    for (int e = 0; e < E; ++e) {
+      p[e] *= inv;
+      probs[size_t(t) * E + e] = p[e];
+      atomicAdd(&s_prob[e], p[e]);
+    }
+    unsigned long long taken = 0ull;
+    float picked = 0.f;
+    int idx[8];
+    float val[8];
+    for (int j = 0; j < k; ++j) {
+      int best = -1;
+      float bv = -1.f;
+      for (int e = 0; e < E; ++e)
+        if (!((taken >> e) & 1ull) && p[e] > bv) { bv = p[e]; best = e; }   // ties: lowest index, like torch.topk
+      taken |= 1ull << best;
+      idx[j] = best; val[j] = bv; picked += bv;
+      atomicAdd(&s_hits[best], 1.f);
+    }
+    const float pinv = 1.f / picked;
+    for (int j = 0; j < k; ++j) {
+      top_i[size_t(t) * k + j] = idx[j];
+      weights[size_t(t) * k + j] = val[j] * pinv;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    atomicAdd(prob_sum + e, s_prob[e]);
+    atomicAdd(hits + e, s_hits[e]);
+  }
+}
+
+}  // namespace jpb
+
+// logits [n_tok, E] (fp32 dtype 0 or bf16 dtype 1) -> probs [n_tok, E] fp32, top_i [n_tok, k] int64, weights [n_tok, k]
+// fp32, prob_sum [E] and hits [E] fp32 (both zeroed here).  E <= 64, k <= 8.
+JPB_API int jpb_router(int dtype, const void* logits, float* probs, long long* top_i, float* weights, float* prob_sum,
+                       float* hits, int n_tok, int E, int k, void* stream) {
+  using namespace jpb;
+  if (E < 1 || E > ROUTER_MAX_E || k < 1 || k > 8 || k > E) return -JPB_ERR_BAD_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaMemsetAsync(prob_sum, 0, sizeof(float) * E, s);
+  cudaMemsetAsync(hits, 0, sizeof(float) * E, s);
+  const int threads = 128, blocks = (n_tok + threads - 1) / threads;
+  if (dtype == 0)
+    router_kernel<float><<<blocks, threads, 0, s>>>(static_cast<const float*>(logits), probs, top_i, weights, prob_sum, hits, n_tok, E, k);
+  else
+    router_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>(static_cast<const __nv_bfloat16*>(logits), probs, top_i, weights,
+                                                            prob_sum, hits, n_tok, E, k);
+  return int(cudaGetLastError());
+}

@@ -148,13 +148,9 @@ class _AllReduceDesc(ctypes.Structure):
 class _AllReduceWorkspace:
     CTRL = 1024
 
-    def __init__(self, axis: str, nbytes: int):
-        from ..mesh import MpmdMesh
-
-        mesh = MpmdMesh.current()
-        ranks = [d.process_index for d in mesh.peers_along(axis)]
+    def __init__(self, group, ranks: list, nbytes: int):
         self.slot = (nbytes + 1023) // 1024 * 1024
-        self.buf = symm.SymmetricBuffer(self.CTRL + 2 * self.slot, mesh.axis_group(axis), ranks)
+        self.buf = symm.SymmetricBuffer(self.CTRL + 2 * self.slot, group, ranks)
         self.epoch = 0
         self.ctas = 0
 
@@ -164,11 +160,22 @@ AR_MIN_BYTES = 1 << 20  # smaller tensors are latency-bound: leave them to NCCL
 
 
 def all_reduce(x: torch.Tensor, axis: str, scale: float = 1.0) -> torch.Tensor:
-    """scale * sum over the ranks of ``axis``; fp32 or bf16, any shape (padded internally)."""
+    """scale * sum over the ranks of mesh axis ``axis``; fp32 or bf16, any shape (padded internally)."""
+    from ..mesh import MpmdMesh
+
+    mesh = MpmdMesh.current()
+    ranks = [d.process_index for d in mesh.peers_along(axis)]
+    return all_reduce_group(x, mesh.axis_group(axis), ranks, scale)
+
+
+def all_reduce_group(x: torch.Tensor, group, ranks: list, scale: float = 1.0) -> torch.Tensor:
+    """scale * sum over the processes ``ranks`` (global ranks, same order everywhere) of process group ``group``:
+    one kernel over NVLink peer memory (reduce-scatter + all-gather with direct peer loads).  Used for the
+    gradient sync over a mesh axis and for cross-stage all-reduces (tied weights, global norms)."""
     lib = _lib()
     lib.jpb_allreduce.argtypes = [ctypes.POINTER(_AllReduceDesc), ctypes.c_void_p]
     lib.jpb_allreduce_grid.argtypes = [ctypes.c_longlong, ctypes.c_int]
-    n_ranks = tpmod.axis_size(axis)
+    n_ranks = len(ranks)
     if x.dtype not in (torch.float32, torch.bfloat16):
         raise native.NativeError(f"fused all_reduce takes float32 or bfloat16, got {x.dtype}")
     flat = x.contiguous().view(-1)
@@ -176,12 +183,13 @@ def all_reduce(x: torch.Tensor, axis: str, scale: float = 1.0) -> torch.Tensor:
     quantum = vn * n_ranks
     n = (flat.numel() + quantum - 1) // quantum * quantum
     nbytes = n * flat.element_size()
-    ws = _AR_WS.get(axis)
+    key = tuple(ranks)
+    ws = _AR_WS.get(key)
     if ws is None or ws.slot < nbytes:
         if ws is not None:
             symm._RETIRED.append(ws)  # freed between steps, see symm.release_retired
-        ws = _AllReduceWorkspace(axis, max(nbytes, 64 << 20))
-        _AR_WS[axis] = ws
+        ws = _AllReduceWorkspace(group, list(ranks), max(nbytes, 64 << 20))
+        _AR_WS[key] = ws
     ws.epoch += 1
     parity = ws.epoch & 1
     d = _AllReduceDesc()

@@ -169,15 +169,84 @@ torch.library.register_autograd("b200moe::dispatch_a2a", _dispatch_bwd, setup_co
 torch.library.register_autograd("b200moe::combine_a2a", _combine_bwd, setup_context=_combine_setup)
 
 
-def route(x: Tensor, w_router: Tensor, top_k: int):
-    """Returns (expert ids [T,k] int64, weights [T,k] fp32, aux loss scalar fp32)."""
-    logits = ops.linear(x, w_router, None).float()
-    probs = torch.softmax(logits, dim=-1)
+def _route_ref(logits: Tensor, top_k: int):
+    """(expert ids [T,k] int64, weights [T,k] fp32, probabilities [T,E] fp32, picks per expert [E] fp32)"""
+    probs = torch.softmax(logits.float(), dim=-1)
     top_v, top_i = probs.topk(top_k, dim=-1)
     weights = top_v / top_v.sum(-1, keepdim=True)
+    hits = torch.nn.functional.one_hot(top_i, logits.shape[-1]).sum((0, 1)).to(torch.float32)
+    return top_i, weights, probs, hits
+
+
+def _router_impl(logits: Tensor, top_k: int):
+    from ..ops import core as _core
+
+    if _core._use_native(logits) and logits.dtype in (torch.float32, torch.bfloat16) and logits.shape[-1] <= 64 and top_k <= 8:
+        import ctypes
+
+        from ..ops import native
+
+        lib = native.load()
+        p, i = ctypes.c_void_p, ctypes.c_int
+        lib.jpb_router.argtypes = [i, p, p, p, p, p, p, i, i, i, p]
+        lg = logits.contiguous()
+        T, E = lg.shape
+        dev = lg.device
+        probs = torch.empty(T, E, dtype=torch.float32, device=dev)
+        top_i = torch.empty(T, top_k, dtype=torch.int64, device=dev)
+        weights = torch.empty(T, top_k, dtype=torch.float32, device=dev)
+        stats = torch.empty(2, E, dtype=torch.float32, device=dev)
+        native._check(lib.jpb_router(0 if lg.dtype == torch.float32 else 1, lg.data_ptr(), probs.data_ptr(), top_i.data_ptr(),
+                                     weights.data_ptr(), stats[0].data_ptr(), stats[1].data_ptr(), T, E, top_k,
+                                     native._stream()), "jpb_router")
+        native.LAUNCHES[0] += 1
+        return top_i, weights, probs, stats[1]
+    return _route_ref(logits, top_k)
+
+
+_lib.define("router(Tensor logits, int top_k) -> (Tensor, Tensor, Tensor, Tensor)")
+_lib.impl("router", _router_impl, "CompositeExplicitAutograd")
+
+
+def _router_fake(logits, top_k):
+    T, E = logits.shape
+    f32 = dict(dtype=torch.float32, device=logits.device)
+    return (torch.empty(T, top_k, dtype=torch.int64, device=logits.device), torch.empty(T, top_k, **f32),
+            torch.empty(T, E, **f32), torch.empty(E, **f32))
+
+
+torch.library.register_fake("b200moe::router", _router_fake)
+
+
+def _router_setup(ctx, inputs, output):
+    ctx.save_for_backward(output[0], output[2])
+    ctx.in_dtype = inputs[0].dtype
+
+
+def _router_bwd(ctx, g_idx, g_w, g_probs, g_hits):
+    """weights_j = p_{i_j} / S with S the sum of the picked probabilities; probs = softmax(logits)."""
+    top_i, probs = ctx.saved_tensors
+    dp = g_probs.float() if g_probs is not None else torch.zeros_like(probs)
+    if g_w is not None:
+        pv = probs.gather(1, top_i)
+        s = pv.sum(-1, keepdim=True)
+        gw = g_w.float()
+        d_pv = gw / s - (gw * pv).sum(-1, keepdim=True) / (s * s)
+        dp = dp.scatter_add(1, top_i, d_pv)
+    dlogits = probs * (dp - (dp * probs).sum(-1, keepdim=True))
+    return dlogits.to(ctx.in_dtype), None
+
+
+torch.library.register_autograd("b200moe::router", _router_bwd, setup_context=_router_setup)
+
+
+def route(x: Tensor, w_router: Tensor, top_k: int):
+    """Returns (expert ids [T,k] int64, weights [T,k] fp32, aux loss scalar fp32).  Softmax, top-k, renormalised
+    weights and the load-balancing statistics come from one kernel on the GPU (``b200moe::router``)."""
+    logits = ops.linear(x, w_router, None)
+    top_i, weights, probs, hits = torch.ops.b200moe.router(logits, top_k)
     E = w_router.shape[0]
-    hits = torch.nn.functional.one_hot(top_i, E).sum(1).to(torch.float32)  # [T, E]
-    frac = hits.mean(0) / top_k
+    frac = hits / (top_i.shape[0] * top_k)
     aux = E * (frac.detach() * probs.mean(0)).sum()
     return top_i, weights, aux
 

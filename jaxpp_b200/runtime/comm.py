@@ -163,7 +163,18 @@ class DistComm:
         return self.groups[key]
 
     def all_reduce(self, buf: torch.Tensor, ranks):
-        dist.all_reduce(buf, group=self._group(ranks))
+        """Sum over my positional counterparts in pipeline ranks ``ranks``.  Large CUDA tensors (tied-weight
+        gradients) go through the one-kernel all-reduce over NVLink peer memory, the rest through NCCL / gloo."""
+        group = self._group(ranks)
+        if self.cuda and buf.dtype in (torch.float32, torch.bfloat16):
+            from ..parallel import fused
+            from ..utils import config
+
+            if (buf.numel() * buf.element_size() >= fused.AR_MIN_BYTES and config.use_fused_collectives.value
+                    and config.use_native_kernels.value):
+                procs = [self.mesh.unstack[r].flat_devices[self.pos_in_stage].process_index for r in ranks]
+                return fused.all_reduce_group(buf, group, procs)
+        dist.all_reduce(buf, group=group)
         return buf
 
     def all_gather(self, st, ins: AllGather, prog: Program):

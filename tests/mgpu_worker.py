@@ -146,6 +146,47 @@ def scenario_fused_moe():
         print("fused MoE dispatch / combine match the NCCL all-to-all path", flush=True)
 
 
+def scenario_pp_tied_gpu():
+    """Tied input / output embeddings on two pipeline GPUs: the two ranks' gradient contributions are summed by a
+    cross-stage all-reduce, which for a tensor this large runs as the one-kernel all-reduce over peer memory;
+    the same step with NCCL collectives is the oracle."""
+    from torch.utils import _pytree as pytree
+
+    from jaxpp_b200.models import lm_trainer as lt
+    from jaxpp_b200.models import transformer as tf
+
+    sched = jp.Std1F1B(2)
+    mesh = jp.MpmdMesh.create({"mpmd": 2, "data": 1, "model": 1}, kind="cuda", multi_process=True)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    cfg = tf.ModelConfig("llama", vocab=2048, d_model=256, n_layers=2, n_heads=4, n_kv_heads=2, ffn=512, seq=128,
+                         n_stages=2, tp=1, dtype=torch.bfloat16, tie_embeddings=True)
+    hyper = lt.Hyper(lr=1e-3, inplace_update=False)
+    g = torch.Generator().manual_seed(5)
+    tokens = torch.randint(0, 2048, (4, 2, 128), generator=g).to(dev)
+    labels = torch.randint(0, 2048, (4, 2, 128), generator=g).to(dev)
+    results = {}
+    for fused_on in (False, True):
+        with config.use_fused_collectives.set(fused_on):
+            state = lt.init_state(cfg, sched, dev, my_rank=mesh.my_mpmd_axis_index, tp_rank=0, seed=0)
+            f = jp.mpmd_jit_with_loop(lt.make_train_step(cfg, sched, hyper), mesh)
+            state, losses = f(state, tokens, labels)
+            torch.cuda.synchronize()
+            results[fused_on] = (state, losses)
+    assert native.read_status() == 0
+    assert fused._AR_WS, "the cross-stage all-reduce did not go through the peer-memory kernel"
+    is_arr = lambda a: isinstance(a, jp.MpmdArray)
+    checked = 0
+    for a, b in zip(pytree.tree_leaves(results[False], is_leaf=is_arr), pytree.tree_leaves(results[True], is_leaf=is_arr)):
+        ta, tb = a.local_tensor(), b.local_tensor()
+        if ta is None or not ta.is_floating_point():
+            continue
+        torch.testing.assert_close(tb.float(), ta.float(), rtol=2e-2, atol=2e-3)
+        checked += 1
+    assert checked > 0
+    if dist.get_rank() == 0:
+        print("tied embeddings: cross-stage all-reduce over peer memory matches NCCL", flush=True)
+
+
 def scenario_pp_tp_gpu(pp, tp, schedule_name):
     """Pipeline x tensor parallel Llama-style step on pp*tp GPUs (bf16, native kernels): the fused
     compute+collective kernels against the same step with NCCL collectives, two steps each."""
@@ -196,6 +237,7 @@ def scenario_pp_tp_gpu(pp, tp, schedule_name):
 SCENARIOS = {
     "fused_tp": scenario_fused_tp,
     "fused_moe": scenario_fused_moe,
+    "pp_tied": scenario_pp_tied_gpu,
     "pp2_tp2_std": lambda: scenario_pp_tp_gpu(2, 2, "std"),
     "pp2_tp2_interleaved": lambda: scenario_pp_tp_gpu(2, 2, "interleaved"),
     "pp_std": lambda: scenario_pp_gpu("std"),

@@ -120,6 +120,22 @@ def test_activations_rope_colsum(native, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_router_kernel(native, dtype):
+    from jaxpp_b200.parallel import moe
+    import jaxpp_b200 as jp
+
+    for T, E, k in ((1000, 8, 2), (77, 16, 4)):
+        logits = rnd(T, E, dtype=dtype, seed=21)
+        with jp.MpmdMesh.create({"mpmd": 1, "data": 1, "model": 1}, kind="cuda", multi_process=False):
+            top_i, w, probs, hits = torch.ops.b200moe.router(logits, k)
+        r_i, r_w, r_p, r_h = moe._route_ref(logits, k)
+        close(probs, r_p, rtol=1e-4, atol=1e-6)
+        assert torch.equal(top_i.sort(-1).values, r_i.sort(-1).values)
+        close(w.sort(-1).values, r_w.sort(-1).values, rtol=1e-4, atol=1e-6)
+        assert torch.equal(hits, r_h)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_dropout_matches_counter_based_reference(native, dtype):
     from jaxpp_b200.ops import core as ops
 

@@ -85,3 +85,23 @@ def test_moe_ffn_drops_and_aux_loss():
         assert aux.item() > 0
         y_small, _ = moe.moe_ffn(x, p, E, k, 0.25, 1, "data")  # tight capacity: some picks are dropped
         assert not torch.allclose(y_small, ref)
+
+
+def test_router_op_backward_matches_autograd_of_the_composition():
+    torch.manual_seed(3)
+    T, E, k = 50, 8, 2
+    logits = torch.randn(T, E, dtype=torch.float64)
+    gw, gp = torch.randn(T, k, dtype=torch.float64), torch.randn(T, E, dtype=torch.float64)
+
+    def loss(fn, lg):
+        top_i, w, probs, hits = fn(lg, k)
+        return (w.double() * gw).sum() + (probs.double() * gp).sum(), top_i, hits
+
+    a = logits.clone().requires_grad_(True)
+    la, ia, ha = loss(moe._route_ref, a)
+    (ga,) = torch.autograd.grad(la, [a])
+    b = logits.clone().requires_grad_(True)
+    lb, ib, hb = loss(torch.ops.b200moe.router, b)
+    (gb,) = torch.autograd.grad(lb, [b])
+    assert torch.equal(ia, ib) and torch.equal(ha, hb) and hb.sum().item() == T * k
+    torch.testing.assert_close(gb, ga, rtol=1e-5, atol=1e-6)

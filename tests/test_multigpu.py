@@ -23,7 +23,7 @@ def test_fused_moe_dispatch_combine_two_gpus():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
-@pytest.mark.parametrize("scenario", ["pp_std", "pp_interleaved", "pp_zb"])
+@pytest.mark.parametrize("scenario", ["pp_std", "pp_interleaved", "pp_zb", "pp_tied"])
 def test_pipeline_over_nccl_p2p_two_gpus(scenario):
     rc = launch([WORKER, scenario], 2, env={"NCCL_NVLS_ENABLE": "0"}, timeout_s=300)
     assert rc == 0
