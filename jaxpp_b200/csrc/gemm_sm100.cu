@@ -40,6 +40,11 @@ struct GemmParams {
   int* status;
   int tiles_m, tiles_n;
   int a_blocked, b_blocked;  // MN-major operand addressed through a 3-D map {64, K, MN/64}: one copy per stage
+  // Batched (grouped, equal-sized groups): `batch` problems stacked along the rows of each operand's storage --
+  // A [batch*M, K] or [batch*K, M], B [batch*N, K] or [batch*K, N], D [batch*M, N].  Tiles that straddle the
+  // end of a problem read rows of the next one; the epilogue masks them (and K must be a multiple of 64).
+  int batch;
+  int a_off, b_off;          // storage rows per problem of A and B
 };
 
 // Tile rasterisation: groups of GROUP_M row blocks are walked column by column, so that the ~148 tiles in
@@ -73,7 +78,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int tiles_per_problem = p.tiles_m * p.tiles_n;
+  const int num_tiles = tiles_per_problem * p.batch;
   const int k_blocks = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -108,8 +114,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int m_blk, n_blk;
-        tile_coords(tile, p.tiles_m, p.tiles_n, m_blk, n_blk);
+        const int prob = tile / tiles_per_problem;
+        tile_coords(tile - prob * tiles_per_problem, p.tiles_m, p.tiles_n, m_blk, n_blk);
         const int m0 = m_blk * BM, n0 = n_blk * BN;
+        const int a_row = prob * p.a_off, b_row = prob * p.b_off;  // storage-row offsets of this problem
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -121,20 +129,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           armed_phase = (armed_phase & ~(1u << s)) | (ph << s);
           const int k0 = kb * BK;
           if (!A_MN) {
-            tma_load_2d(sa, &map_a, &full[s], k0, m0);                 // box {64 k, 128 rows}
+            tma_load_2d(sa, &map_a, &full[s], k0, a_row + m0);         // box {64 k, 128 rows}
           } else if (p.a_blocked) {
-            tma_load_3d(sa, &map_a, &full[s], 0, k0, m0 >> 6);         // box {64 m, 64 k, 2 blocks}
+            tma_load_3d(sa, &map_a, &full[s], 0, a_row + k0, m0 >> 6); // box {64 m, 64 k, 2 blocks}
           } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &map_a, &full[s], m0 + j * 64, k0);
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &map_a, &full[s], m0 + j * 64, a_row + k0);
           }
           if (!B_MN) {
-            tma_load_2d(sb, &map_b, &full[s], k0, n0);                 // box {64 k, 256 rows}
+            tma_load_2d(sb, &map_b, &full[s], k0, b_row + n0);         // box {64 k, 256 rows}
           } else if (p.b_blocked) {
-            tma_load_3d(sb, &map_b, &full[s], 0, k0, n0 >> 6);         // box {64 n, 64 k, 4 blocks}
+            tma_load_3d(sb, &map_b, &full[s], 0, b_row + k0, n0 >> 6); // box {64 n, 64 k, 4 blocks}
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &map_b, &full[s], n0 + j * 64, k0);
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &map_b, &full[s], n0 + j * 64, b_row + k0);
           }
         }
       }
@@ -188,14 +196,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
       int m_blk, n_blk;
-      tile_coords(tile, p.tiles_m, p.tiles_n, m_blk, n_blk);
+      const int prob = tile / tiles_per_problem;
+      tile_coords(tile - prob * tiles_per_problem, p.tiles_m, p.tiles_n, m_blk, n_blk);
       const int m0 = m_blk * BM, n0 = n_blk * BN;
       const uint32_t acc = tile_i & 1;
       const uint32_t acc_ph = (tile_i >> 1) & 1;
       if (!mbar_wait_bounded_warp(&acc_full[acc], acc_ph, abort_flag, p.status)) { ok = false; break; }
       tc_fence_after();
-      const int row = m0 + quarter * 32 + lane;
-      const bool row_ok = row < p.M;
+      const int row_in = m0 + quarter * 32 + lane;        // row within this problem
+      const bool row_ok = row_in < p.M;
+      const size_t row = size_t(prob) * p.M + row_in;     // row of the stacked output
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int col0 = n0 + c * 32;
@@ -220,7 +230,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (!row_ok) continue;
         const bool full_chunk = col0 + 32 <= p.N;
         if (p.out_fp32) {
-          float* d = static_cast<float*>(p.D) + size_t(row) * p.ldd + col0;
+          float* d = static_cast<float*>(p.D) + row * p.ldd + col0;
           if (full_chunk && (p.ldd & 3) == 0) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
@@ -235,7 +245,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int j = 0; j < 32 && col0 + j < p.N; ++j) d[j] = p.accumulate ? d[j] + v[j] : v[j];
           }
         } else {
-          __nv_bfloat16* d = static_cast<__nv_bfloat16*>(p.D) + size_t(row) * p.ldd + col0;
+          __nv_bfloat16* d = static_cast<__nv_bfloat16*>(p.D) + row * p.ldd + col0;
           if (full_chunk && (p.ldd & 7) == 0) {
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
@@ -355,7 +365,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  const int tiles = p.tiles_m * p.tiles_n;
+  const int tiles = p.tiles_m * p.tiles_n * p.batch;
   const int grid = tiles < g_num_sms ? tiles : g_num_sms;
   kernel<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ma, mb, p);
   return int(cudaGetLastError());
@@ -363,29 +373,32 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams
 
 }  // namespace jpb
 
-// A: [M,K] with lda (K-major) or stored as [K,M] with lda (MN-major); likewise B for [N,K] / [K,N].
-// All leading dimensions in elements; bf16 operands must be 16-byte aligned with lda/ldb multiples of 8.
-JPB_API int jpb_gemm_bf16(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int lda, int ldb,
-                          int ldd, int a_mn_major, int b_mn_major, int out_fp32, int accumulate, int bias_fp32,
-                          void* stream) {
+// Common entry: `batch` equal-sized problems stacked along the storage rows of A, B and D (batch == 1: one GEMM).
+static int gemm_entry(const void* A, const void* B, void* D, const void* bias, int batch, int M, int N, int K, int lda, int ldb,
+                      int ldd, int a_mn_major, int b_mn_major, int out_fp32, int accumulate, int bias_fp32, void* stream) {
   using namespace jpb;
-  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
     return -JPB_ERR_BAD_ARGUMENT;
   if (accumulate && !out_fp32) return -JPB_ERR_BAD_ARGUMENT;
+  if (batch > 1 && (K % BK != 0 || bias != nullptr)) return -JPB_ERR_BAD_ARGUMENT;
   CUtensorMap ma, mb;
   int rc;
+  const uint64_t nb = uint64_t(batch);
   const int a_blocked = a_mn_major && M % 64 == 0, b_blocked = b_mn_major && N % 64 == 0;
-  if (!a_mn_major) rc = get_map_2d(&ma, A, K, M, lda, BK, BM);
-  else if (a_blocked) rc = get_map_mn_blocked(&ma, A, M, K, lda, BM / 64);
-  else rc = get_map_2d(&ma, A, M, K, lda, 64, BK);
+  if (!a_mn_major) rc = get_map_2d(&ma, A, K, nb * M, lda, BK, BM);
+  else if (a_blocked) rc = get_map_mn_blocked(&ma, A, M, nb * K, lda, BM / 64);
+  else rc = get_map_2d(&ma, A, M, nb * K, lda, 64, BK);
   if (rc) return rc;
-  if (!b_mn_major) rc = get_map_2d(&mb, B, K, N, ldb, BK, BN);
-  else if (b_blocked) rc = get_map_mn_blocked(&mb, B, N, K, ldb, BN / 64);
-  else rc = get_map_2d(&mb, B, N, K, ldb, 64, BK);
+  if (!b_mn_major) rc = get_map_2d(&mb, B, K, nb * N, ldb, BK, BN);
+  else if (b_blocked) rc = get_map_mn_blocked(&mb, B, N, nb * K, ldb, BN / 64);
+  else rc = get_map_2d(&mb, B, N, nb * K, ldb, 64, BK);
   if (rc) return rc;
   GemmParams p;
   p.a_blocked = a_blocked; p.b_blocked = b_blocked;
+  p.batch = batch;
+  p.a_off = a_mn_major ? K : M;
+  p.b_off = b_mn_major ? K : N;
   p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.out_fp32 = out_fp32; p.accumulate = accumulate;
   p.bias = bias; p.bias_fp32 = bias_fp32; p.D = D; p.status = jpb_status_device_ptr();
   p.tiles_m = (M + BM - 1) / BM;
@@ -395,4 +408,20 @@ JPB_API int jpb_gemm_bf16(const void* A, const void* B, void* D, const void* bia
   if (!a_mn_major && b_mn_major) return launch<false, true>(ma, mb, p, s);
   if (a_mn_major && b_mn_major) return launch<true, true>(ma, mb, p, s);
   return launch<true, false>(ma, mb, p, s);
+}
+
+// A: [M,K] with lda (K-major) or stored as [K,M] with lda (MN-major); likewise B for [N,K] / [K,N].
+// All leading dimensions in elements; bf16 operands must be 16-byte aligned with lda/ldb multiples of 8.
+JPB_API int jpb_gemm_bf16(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int lda, int ldb,
+                          int ldd, int a_mn_major, int b_mn_major, int out_fp32, int accumulate, int bias_fp32,
+                          void* stream) {
+  return gemm_entry(A, B, D, bias, 1, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, out_fp32, accumulate, bias_fp32, stream);
+}
+
+// Grouped GEMM with equal-sized groups (the local experts of a mixture-of-experts layer): problem b uses rows
+// [b*M, (b+1)*M) of a K-major A (or rows [b*K, (b+1)*K) of an MN-major one), likewise B, and writes rows
+// [b*M, (b+1)*M) of D.  One launch, one persistent grid over all problems' tiles.  K must be a multiple of 64.
+JPB_API int jpb_gemm_bf16_batched(const void* A, const void* B, void* D, int batch, int M, int N, int K, int lda, int ldb,
+                                  int ldd, int a_mn_major, int b_mn_major, int out_fp32, int accumulate, void* stream) {
+  return gemm_entry(A, B, D, nullptr, batch, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, out_fp32, accumulate, 0, stream);
 }

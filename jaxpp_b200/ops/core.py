@@ -156,6 +156,46 @@ _autograd("linear", _linear_bwd, _linear_setup)
 
 
 # ======================================================================================
+# grouped linear (equal-sized groups: the local experts of a mixture-of-experts layer)
+#   y[e] = x[e] @ w[e]^T   x [E, M, K], w [E, N, K] -> [E, M, N]; one launch on the GPU
+# ======================================================================================
+
+def _wg_dtype(dy, out_dtype):
+    return out_dtype if out_dtype is not None else dy.dtype
+
+
+linear_batched = _define(
+    "linear_batched(Tensor x, Tensor w) -> Tensor",
+    lambda x, w: torch.bmm(x, w.transpose(1, 2)),
+    lambda x, w: x.new_empty(x.shape[0], x.shape[1], w.shape[1]),
+    "linear_batched",
+)
+linear_dgrad_batched = _define(
+    "linear_dgrad_batched(Tensor dy, Tensor w) -> Tensor",
+    lambda dy, w: torch.bmm(dy, w),
+    lambda dy, w: dy.new_empty(dy.shape[0], dy.shape[1], w.shape[2]),
+    "linear_dgrad_batched",
+)
+linear_wgrad_batched = _define(
+    "linear_wgrad_batched(Tensor dy, Tensor x, ScalarType? out_dtype=None) -> Tensor",
+    lambda dy, x, out_dtype=None: torch.bmm(_f32(dy).transpose(1, 2), _f32(x)).to(_wg_dtype(dy, out_dtype)),
+    lambda dy, x, out_dtype=None: dy.new_empty(dy.shape[0], dy.shape[2], x.shape[2], dtype=_wg_dtype(dy, out_dtype)),
+    "linear_wgrad_batched",
+)
+
+
+def _linear_batched_bwd(ctx, dy):
+    x, w = ctx.saved_tensors
+    dy = dy.contiguous()
+    dx = linear_dgrad_batched(dy, w) if ctx.needs_input_grad[0] else None
+    dw = linear_wgrad_batched(dy, x, WGRAD_DTYPE[0]) if ctx.needs_input_grad[1] else None
+    return dx, dw
+
+
+_autograd("linear_batched", _linear_batched_bwd, lambda ctx, inputs, output: ctx.save_for_backward(*inputs))
+
+
+# ======================================================================================
 # RMSNorm / LayerNorm (statistics in fp32)
 # ======================================================================================
 

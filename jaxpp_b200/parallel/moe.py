@@ -281,12 +281,11 @@ def combine(y_buf: Tensor, dest: Tensor, weights: Tensor, top_k: int) -> Tensor:
 
 
 def expert_ffn(x: Tensor, w_up: Tensor, w_down: Tensor) -> Tensor:
-    """x: [E_l, M, d]; w_up: [E_l, 2F, d] ([gate | up]); w_down: [E_l, d, F]"""
-    outs = []
-    for e in range(x.shape[0]):
-        h = ops.swiglu(ops.linear(x[e], w_up[e], None))
-        outs.append(ops.linear(h, w_down[e], None))
-    return torch.stack(outs, 0)
+    """x: [E_l, M, d]; w_up: [E_l, 2F, d] ([gate | up]); w_down: [E_l, d, F].  Every local expert sees the same
+    number of slots, so each projection is one grouped tcgen05 GEMM over all local experts."""
+    E_l, M, d = x.shape
+    h = ops.swiglu(ops.linear_batched(x, w_up).view(E_l * M, -1))
+    return ops.linear_batched(h.view(E_l, M, -1), w_down)
 
 
 def moe_ffn(x: Tensor, p: dict, n_experts: int, top_k: int, capacity_factor: float, ep: int, ep_axis: str):

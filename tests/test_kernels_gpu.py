@@ -119,6 +119,22 @@ def test_activations_rope_colsum(native, dtype):
         close(merged, ops._qkv_merge_ref(*[g.float() for g in got], c, s_), **tol)
 
 
+@pytest.mark.parametrize("E,M,N,K", [(3, 192, 320, 256), (2, 200, 264, 128), (4, 64, 128, 64)])
+def test_grouped_gemm_equal_groups(native, E, M, N, K):
+    """One launch over all groups against per-group fp32 matmuls, in the three linear-layer layouts.  Group sizes
+    that are not multiples of the tile make tiles straddle two groups: the masked rows / columns must not leak."""
+    x, w = rnd(E, M, K, seed=31), rnd(E, N, K, scale=0.2, seed=32)
+    dy = rnd(E, M, N, seed=33)
+    close(native.linear_batched(x, w), torch.bmm(x.float(), w.float().transpose(1, 2)), rtol=2e-2, atol=2e-2 * K ** 0.5 * 0.2)
+    if N % 64 == 0:
+        close(native.linear_dgrad_batched(dy, w), torch.bmm(dy.float(), w.float()), rtol=2e-2, atol=2e-2 * N ** 0.5 * 0.2)
+    else:
+        close(native.linear_dgrad_batched(dy, w), torch.bmm(dy.float(), w.float()), rtol=2e-2, atol=2e-2 * N ** 0.5 * 0.2)
+    ref_w = torch.bmm(dy.float().transpose(1, 2), x.float())
+    close(native.linear_wgrad_batched(dy, x, torch.float32), ref_w, rtol=2e-2, atol=2e-2 * M ** 0.5)
+    close(native.linear_wgrad_batched(dy, x), ref_w, rtol=2e-2, atol=3e-2 * M ** 0.5)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_router_kernel(native, dtype):
     from jaxpp_b200.parallel import moe
