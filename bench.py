@@ -220,7 +220,11 @@ def main():
     busy = compiled.last_states[0].busy_ms() if world > 1 else sum(s.busy_ms() for s in compiled.last_states)
     bubble = max(0.0, 1.0 - busy / step_ms_b)
 
+    bubbles = [bubble]
     if world > 1:
+        allb = [torch.zeros(1, device=device, dtype=torch.float64) for _ in range(world)]
+        dist.all_gather(allb, torch.tensor([bubble], device=device, dtype=torch.float64))
+        bubbles = [float(x.item()) for x in allb]
         t = torch.tensor([ms, e2e_ms, bubble, float(launches), float(status)], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms, bubble, launches, status = (float(x) for x in t.tolist())
@@ -255,6 +259,7 @@ def main():
             "bubble_pct": round(100 * bubble, 2),
             "ideal_bubble_pct": round(100 * schedule.ideal_bubble_fraction(n_mb), 2),
             "mfu_of_measured_sustained_peak": round(flops / (ms / 1e3) / (peak * n), 4),
+            "bubble_pct_per_rank": [round(100 * b, 2) for b in bubbles],
             "final_loss": loss_val, "kernel_status": int(status),
         }
         print(json.dumps(out))

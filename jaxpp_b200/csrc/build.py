@@ -90,7 +90,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
             if res.returncode != 0:
                 raise RuntimeError(f"nvcc failed for {src}")
     if jobs or not os.path.exists(LIB):
-        link = [nvcc, "-shared", "-o", LIB, *objs, "-lcudart"]
+        link = [nvcc, "-shared", "-o", LIB, *objs, "-lcudart", "-ldl"]
         res = subprocess.run(link, capture_output=True, text=True)
         if res.returncode != 0:
             sys.stderr.write(res.stdout + res.stderr)

@@ -33,6 +33,7 @@ class DistComm:
         self.inflight_send: dict[int, tuple] = {}  # tid → (tensors, works)
         self.groups: dict[tuple, object] = {}
         self.p2p_groups: dict[tuple, object] = {}  # (src pipeline rank, dst pipeline rank) → 2-process group
+        self.native_p2p = None                     # NcclP2P when JAXPP_B200_P2P=native
         if dist.is_available() and dist.is_initialized():
             mesh.create_process_groups()  # no-op when the mesh was made by MpmdMesh.create
         if self.cuda:
@@ -63,7 +64,11 @@ class DistComm:
             return  # injected fault: the message is never sent
         peer = self.peer(ins.dst)
         tensors = [st.env[v].contiguous() for v in ins.vids]
-        if self.cuda:
+        if self.cuda and self.native_p2p is not None:
+            ready = torch.cuda.Event()
+            ready.record()
+            works = [self.native_p2p.send(peer, tensors, ready)]  # an event: the transfer's completion
+        elif self.cuda:
             ready = torch.cuda.Event()
             ready.record()
             with torch.cuda.stream(self.send_stream):
@@ -83,7 +88,12 @@ class DistComm:
         for v in ins.vids:
             info = prog.values[v]
             bufs.append(torch.empty(info.shape, dtype=info.dtype, device=self.device))
-        if self.cuda:
+        if self.cuda and self.native_p2p is not None:
+            ready = torch.cuda.Event()
+            ready.record()  # the buffers' allocation point on the compute stream
+            done = self.native_p2p.recv(peer, bufs, ready)
+            token = [[], done, False]
+        elif self.cuda:
             ready = torch.cuda.Event()
             ready.record()
             with torch.cuda.stream(self.recv_stream):
@@ -136,6 +146,8 @@ class DistComm:
         if item is None:
             return
         tensors, works = item
+        if self.cuda and self.native_p2p is not None:
+            return  # the payloads were recorded on the pair's stream when the send was enqueued
         if self.cuda:
             with torch.cuda.stream(self.send_stream):
                 for w in works:
@@ -200,6 +212,7 @@ class DistComm:
 
 
 _P2P_GROUPS: dict[tuple, object] = {}
+_NATIVE_P2P: dict[tuple, object] = {}
 
 
 def ensure_p2p_groups(prog: Program, comm: DistComm):
@@ -212,6 +225,20 @@ def ensure_p2p_groups(prog: Program, comm: DistComm):
         return
     pairs = sorted({(ins.rank, ins.dst) for ins in prog.instrs if isinstance(ins, Transfer)})
     n_pos = comm.mesh.unstack[0].size
+    from ..utils import config
+
+    if config.p2p_backend.value == "native":
+        from .p2p_native import NcclP2P
+
+        procs = [(comm.mesh.unstack[src].flat_devices[pos].process_index, comm.mesh.unstack[dst].flat_devices[pos].process_index)
+                 for src, dst in pairs for pos in range(n_pos)]
+        key = comm.mesh._key()
+        if key not in _NATIVE_P2P:
+            _NATIVE_P2P[key] = NcclP2P(procs, comm.device)
+        else:
+            _NATIVE_P2P[key].add_pairs(procs)
+        comm.native_p2p = _NATIVE_P2P[key]
+        return
     mesh_key = comm.mesh._key()
     for src, dst in pairs:
         if (src, dst) in comm.p2p_groups:

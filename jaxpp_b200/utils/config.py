@@ -128,6 +128,9 @@ use_fused_collectives = BoolEnvVar("JAXPP_B200_FUSED_COLLECTIVES", True)
 # SMs the fused compute+collective kernels leave free when pipeline stages run on other GPUs, so that the
 # point-to-point kernels of side streams can start while a fused kernel waits for its tensor-parallel peer.
 comm_reserved_sms = IntEnvVar("JAXPP_B200_COMM_RESERVED_SMS", 4)
+# Point-to-point backend of the multi-controller runtime on GPUs: "torch" (torch.distributed batch_isend_irecv) or
+# "native" (2-rank NCCL communicators driven through the C ABI of the native library).
+p2p_backend = StrEnvVar("JAXPP_B200_P2P", "torch")
 # Capture tasks into CUDA graphs after their first eager run.
 use_cuda_graphs = BoolEnvVar("JAXPP_B200_CUDA_GRAPHS", False)
 # Seconds a rank may go without a heartbeat before the watchdog reports it.

@@ -146,6 +146,38 @@ def scenario_fused_moe():
         print("fused MoE dispatch / combine match the NCCL all-to-all path", flush=True)
 
 
+def scenario_p2p_native():
+    """The C-ABI NCCL point-to-point backend on its own: several dtypes (fp8 included) in one grouped transfer, both
+    directions, twice (the second transfer reuses the communicators and streams)."""
+    from jaxpp_b200.runtime.p2p_native import NcclP2P
+
+    r = dist.get_rank()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    p2p = NcclP2P([(0, 1), (1, 0)], dev)
+
+    def payload(seed):
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        base = torch.randn(3, 1000, generator=g, device="cuda")
+        return [base.clone(), base.to(torch.bfloat16), base.to(torch.float8_e4m3fn), (base * 100).to(torch.int64),
+                torch.empty(0, device="cuda"), base[:, :7].contiguous()]
+
+    for rep in range(2):
+        mine, theirs = payload(10 * rep + r), payload(10 * rep + (1 - r))
+        bufs = [torch.empty_like(t) for t in theirs]
+        ready = torch.cuda.Event()
+        ready.record()
+        done_r = p2p.recv(1 - r, bufs, ready)
+        done_s = p2p.send(1 - r, mine, ready)
+        torch.cuda.current_stream().wait_event(done_r)
+        torch.cuda.current_stream().wait_event(done_s)
+        torch.cuda.synchronize()
+        for got, want in zip(bufs, theirs):
+            assert got.dtype == want.dtype and torch.equal(got.view(torch.uint8), want.view(torch.uint8)), want.dtype
+    p2p.close()
+    if r == 0:
+        print("native NCCL p2p backend: fp32 / bf16 / fp8 / int64 payloads round-trip", flush=True)
+
+
 def scenario_pp_tied_gpu():
     """Tied input / output embeddings on two pipeline GPUs: the two ranks' gradient contributions are summed by a
     cross-stage all-reduce, which for a tensor this large runs as the one-kernel all-reduce over peer memory;
@@ -238,6 +270,7 @@ SCENARIOS = {
     "fused_tp": scenario_fused_tp,
     "fused_moe": scenario_fused_moe,
     "pp_tied": scenario_pp_tied_gpu,
+    "p2p_native": scenario_p2p_native,
     "pp2_tp2_std": lambda: scenario_pp_tp_gpu(2, 2, "std"),
     "pp2_tp2_interleaved": lambda: scenario_pp_tp_gpu(2, 2, "interleaved"),
     "pp_std": lambda: scenario_pp_gpu("std"),

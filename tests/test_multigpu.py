@@ -34,3 +34,10 @@ def test_pipeline_over_nccl_p2p_two_gpus(scenario):
 def test_pipeline_times_tensor_parallel_four_gpus(scenario):
     rc = launch([WORKER, scenario], 4, env={"NCCL_NVLS_ENABLE": "0"}, timeout_s=180)
     assert rc == 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+@pytest.mark.parametrize("scenario", ["p2p_native", "pp_std", "pp_interleaved"])
+def test_native_nccl_p2p_backend_two_gpus(scenario):
+    rc = launch([WORKER, scenario], 2, env={"NCCL_NVLS_ENABLE": "0", "JAXPP_B200_P2P": "native"}, timeout_s=90)
+    assert rc == 0
