@@ -10,7 +10,7 @@ from jaxpp_b200.compiler.verify import verify_program
 from jaxpp_b200.ops import core as ops
 from jaxpp_b200.utils import config
 
-from helpers import assert_trees_equal, local, make_mlp_step, mlp_forward, mlp_params
+from helpers import assert_trees_equal, leaves, local, make_mlp_step, mlp_forward, mlp_params
 
 CASES = [
     # (mpmd_dim, schedule, n_mubatches)
@@ -266,3 +266,43 @@ def test_licm_hoists_loop_invariant_casts():
 
     assert casts_in(hoisted, "before_loop_r0") >= 5 and casts_in(plain, "fwd_0__0") >= 6
     assert casts_in(hoisted, "fwd_0__0") == 1  # only the microbatch itself is still cast inside the loop
+
+
+@pytest.mark.parametrize("schedule", [jp.Std1F1B(2), jp.Interleaved1F1B(4, 2), jp.ZeroBubble(2)], ids=["1f1b", "interleaved", "zb"])
+def test_dropout_inside_the_pipelined_loop_draws_the_same_numbers(schedule):
+    """Random numbers inside the microbatch loop (the reference's tests/functional_testing/test_dropout_enabled.py):
+    the mask is a function of (seed, microbatch, layer), so the scheduled program -- stages on different ranks,
+    backward tasks regenerating their masks, ZeroBubble's split backward -- must reproduce the sequential step
+    bit for bit, and a different seed must change the result."""
+    n_stages, n_mb = schedule.num_stages, 4
+    params = mlp_params(n_stages, 8)
+    batch = torch.randn(n_mb, 3, 8, generator=torch.Generator().manual_seed(3))
+
+    def make_step(seed):
+        def step(params, batch, base_seed):
+            def body(i):
+                mb = jp.take(batch, i)
+                seed_i = base_seed + i                       # a fresh stream per microbatch
+
+                def loss_fn(p):
+                    x = mb
+                    for layer, q in enumerate(p):
+                        h = ops.gelu(ops.linear(x, q["w1"], q["b1"]))
+                        h = ops.dropout(h, 0.25, seed_i, layer)
+                        x = ops.layernorm(x + ops.linear(h, q["w2"], None), q["g"], q["b"], 1e-5)[0]
+                        x = jp.mark_stage_end(x)
+                    return ((x - mb) ** 2).mean()
+
+                return jp.value_and_grad(loss_fn)(params)
+
+            return jp.treduce_i(body, n_mb, schedule=schedule)
+
+        return step
+
+    seed = torch.tensor(1234, dtype=torch.int64)
+    step = make_step(seed)
+    ref = step(params, batch, seed)
+    got = jp.mpmd_jit_with_loop(step, cpu_mesh(2))(params, batch, seed)
+    assert_trees_equal(ref, got, exact=True)
+    other = step(params, batch, seed + 1)
+    assert not torch.equal(leaves(other)[0], leaves(ref)[0])
