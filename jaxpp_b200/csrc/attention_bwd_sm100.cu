@@ -84,7 +84,31 @@ struct DkvSmem {
 };
 
 constexpr int BWD_NS = 4;  // stages of the streamed operand in both kernels
-enum { K1_KV = 0, K1_QF = 1, K1_QE = K1_QF + BWD_NS, K1_SF = K1_QE + BWD_NS, K1_SFREE, K1_PF, K1_PE, K1_N };
+enum { K1_KV = 0, K1_KVE = 1, K1_QF = 2, K1_QE = K1_QF + BWD_NS, K1_SF = K1_QE + BWD_NS, K1_SFREE, K1_PF, K1_PE, K1_N };
+
+// Work distribution of the persistent dK/dV kernel.  A work item is a pair of kv blocks (j, n_kvb-1-j) of one
+// (batch, kv head): under a causal mask the two together see the same number of query blocks whatever j is, so
+// items have equal cost and a round-robin over the CTAs is balanced; consecutive items belong to the same head
+// (their Q / dO stream stays in L2).  Tile k of a CTA is half (k & 1) of its item number (k >> 1).
+struct DkvTiles {
+  int n_kvb, n_pairs, n_items, G, nq, causal, Sq, Sk, Hkv;
+  __device__ __forceinline__ bool get(int k, int& jb, int& hk, int& b, int& i_start, int& per_head) const {
+    const int item = blockIdx.x + (k >> 1) * gridDim.x;
+    if (item >= n_items) return false;
+    const int hb = item / n_pairs, pi = item - hb * n_pairs;
+    jb = (k & 1) ? n_kvb - 1 - pi : pi;
+    hk = hb % Hkv;
+    b = hb / Hkv;
+    i_start = 0;
+    if (causal) {
+      const int first_q = jb * 128 - (Sk - Sq);  // first query row that sees this kv block
+      i_start = first_q > 0 ? first_q / 64 : 0;
+    }
+    per_head = nq > i_start ? nq - i_start : 0;
+    if ((k & 1) && n_kvb - 1 - pi == pi) per_head = -1;  // odd block count: the middle block is its item's only tile
+    return true;
+  }
+};
 
 template <int D>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
@@ -99,20 +123,16 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int jb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int G = p.H / p.Hkv;
-  const int kv0 = jb * 128;
-  const int nq = (p.Sq + 63) / 64;
-  int i_start = 0;
-  if (p.causal) {
-    const int first_q = kv0 - (p.Sk - p.Sq);  // first query row that sees kv0
-    i_start = first_q > 0 ? first_q / 64 : 0;
-  }
-  const int per_head = nq > i_start ? nq - i_start : 0;
-  const int n_iter = per_head * G;
+  DkvTiles tiles;
+  tiles.n_kvb = (p.Sk + 127) / 128;
+  tiles.n_pairs = (tiles.n_kvb + 1) / 2;
+  tiles.n_items = tiles.n_pairs * p.Hkv * p.B;
+  tiles.G = G; tiles.nq = (p.Sq + 63) / 64; tiles.causal = p.causal; tiles.Sq = p.Sq; tiles.Sk = p.Sk; tiles.Hkv = p.Hkv;
 
   if (threadIdx.x == 0) {
     mbar_init(&bar[K1_KV], 1);
+    mbar_init(&bar[K1_KVE], 1);
     for (int s = 0; s < BWD_NS; ++s) { mbar_init(&bar[K1_QF + s], 1); mbar_init(&bar[K1_QE + s], 1); }
     mbar_init(&bar[K1_SF], 1);
     mbar_init(&bar[K1_SFREE], 8);
@@ -120,6 +140,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     mbar_init(&bar[K1_PE], 1);
     *abort_flag = 0;
     fence_barrier_init();
+    tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_do); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
@@ -128,39 +149,51 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t t_s = tmem_base, t_dp = tmem_base + 64, t_dv = tmem_base + 128, t_dk = tmem_base + 128 + D;
 
+  // Every role walks the same tiles in the same order.  `g` counts the (kv block, q block) iterations of this
+  // CTA over all its tiles and `tile_i` its non-empty tiles: the barrier phases follow these two counters, so the
+  // operand ring, the S / P hand-offs and the K/V buffer carry over from one tile to the next without a drain.
   if (warp == 0) {
-    if (lane == 0 && n_iter > 0) {
+    if (lane == 0) {
       uint32_t armed = 0, armed_phase = 0;
       auto arm = [&](int id, uint32_t ph, uint32_t bytes) {
         mbar_expect_tx(&bar[id], bytes);
         armed |= 1u << id;
         armed_phase = (armed_phase & ~(1u << id)) | (ph << id);
       };
-      arm(K1_KV, 0, 2 * L::DB * L::KV_TILE);
-#pragma unroll
-      for (int d = 0; d < L::DB; ++d) {
-        tma_load_4d(smem + L::OFF_K + d * L::KV_TILE, &map_k, &bar[K1_KV], d * 64, hk, kv0, b);
-        tma_load_4d(smem + L::OFF_V + d * L::KV_TILE, &map_v, &bar[K1_KV], d * 64, hk, kv0, b);
-      }
       bool ok = true;
-      for (int t = 0; t < n_iter && ok; ++t) {
-        const int s = t % BWD_NS;
-        const uint32_t ph = (t / BWD_NS) & 1;
-        const int h = hk * G + t / per_head;
-        const int q0 = (i_start + t % per_head) * 64;
-        if (!mbar_wait_bounded(&bar[K1_QE + s], ph ^ 1, abort_flag, p.status)) { ok = false; break; }
-        arm(K1_QF + s, ph, L::STAGE);
-        uint8_t* st = smem + L::OFF_Q + s * L::STAGE;
+      uint32_t g = 0, tile_i = 0;
+      int jb, hk, b, i_start, per_head;
+      for (int k = 0; ok && tiles.get(k, jb, hk, b, i_start, per_head); ++k) {
+        const int n_iter = per_head * G;
+        if (n_iter <= 0) continue;
+        // K / V of the previous tile are read by its S and dP MMAs only: free once the last of them is done
+        if (tile_i > 0 && !mbar_wait_bounded(&bar[K1_KVE], (tile_i - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+        arm(K1_KV, tile_i & 1, 2 * L::DB * L::KV_TILE);
 #pragma unroll
         for (int d = 0; d < L::DB; ++d) {
-          tma_load_4d(st + d * L::Q_TILE, &map_q, &bar[K1_QF + s], d * 64, h, q0, b);
-          tma_load_4d(st + (L::DB + d) * L::Q_TILE, &map_do, &bar[K1_QF + s], d * 64, h, q0, b);
+          tma_load_4d(smem + L::OFF_K + d * L::KV_TILE, &map_k, &bar[K1_KV], d * 64, hk, jb * 128, b);
+          tma_load_4d(smem + L::OFF_V + d * L::KV_TILE, &map_v, &bar[K1_KV], d * 64, hk, jb * 128, b);
         }
+        for (int t = 0; t < n_iter && ok; ++t, ++g) {
+          const int s = g % BWD_NS;
+          const uint32_t ph = (g / BWD_NS) & 1;
+          const int h = hk * G + t / per_head;
+          const int q0 = (i_start + t % per_head) * 64;
+          if (!mbar_wait_bounded(&bar[K1_QE + s], ph ^ 1, abort_flag, p.status)) { ok = false; break; }
+          arm(K1_QF + s, ph, L::STAGE);
+          uint8_t* st = smem + L::OFF_Q + s * L::STAGE;
+#pragma unroll
+          for (int d = 0; d < L::DB; ++d) {
+            tma_load_4d(st + d * L::Q_TILE, &map_q, &bar[K1_QF + s], d * 64, h, q0, b);
+            tma_load_4d(st + (L::DB + d) * L::Q_TILE, &map_do, &bar[K1_QF + s], d * 64, h, q0, b);
+          }
+        }
+        ++tile_i;
       }
       if (!ok) {
         const uint64_t t0 = globaltimer_ns();
         for (int id = 0; id < K1_QE; ++id) {
-          if (!(armed & (1u << id))) continue;
+          if (id == K1_KVE || !(armed & (1u << id))) continue;
           while (!mbar_try_wait(&bar[id], (armed_phase >> id) & 1) && globaltimer_ns() - t0 < JPB_WAIT_BUDGET_NS) {
           }
         }
@@ -172,11 +205,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);  // [kv x d] = K-major(P^T) x MN-major(dO / Q)
       const uint32_t sk = smem_u32(smem + L::OFF_K), sv = smem_u32(smem + L::OFF_V);
       const uint32_t sp = smem_u32(smem + L::OFF_P), sds = smem_u32(smem + L::OFF_DS);
-      bool ok = n_iter > 0 && mbar_wait_bounded(&bar[K1_KV], 0, abort_flag, p.status);
-      auto issue_s = [&](int t) -> bool {
-        const int s = t % BWD_NS;
-        if (!mbar_wait_bounded(&bar[K1_QF + s], (t / BWD_NS) & 1, abort_flag, p.status)) return false;
-        if (t > 0 && !mbar_wait_bounded(&bar[K1_SFREE], (t - 1) & 1, abort_flag, p.status)) return false;
+      bool ok = true;
+      auto issue_s = [&](uint32_t gg) -> bool {
+        const int s = gg % BWD_NS;
+        if (!mbar_wait_bounded(&bar[K1_QF + s], (gg / BWD_NS) & 1, abort_flag, p.status)) return false;
+        if (gg > 0 && !mbar_wait_bounded(&bar[K1_SFREE], (gg - 1) & 1, abort_flag, p.status)) return false;
         tc_fence_after();
         const uint32_t sq = smem_u32(smem + L::OFF_Q + s * L::STAGE);
         const uint32_t sdo = sq + L::DB * L::Q_TILE;
@@ -195,130 +228,153 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         umma_commit(&bar[K1_SF]);
         return true;
       };
-      if (ok) ok = issue_s(0);
-      for (int t = 0; t < n_iter && ok; ++t) {
-        if (t + 1 < n_iter && !issue_s(t + 1)) { ok = false; break; }
-        const int s = t % BWD_NS;
-        if (!mbar_wait_bounded(&bar[K1_PF], t & 1, abort_flag, p.status)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t sq = smem_u32(smem + L::OFF_Q + s * L::STAGE);
-        const uint32_t sdo = sq + L::DB * L::Q_TILE;
+      uint32_t g = 0, tile_i = 0;
+      int jb, hk, b, i_start, per_head;
+      for (int k = 0; ok && tiles.get(k, jb, hk, b, i_start, per_head); ++k) {
+        const int n_iter = per_head * G;
+        if (n_iter <= 0) continue;
+        if (!mbar_wait_bounded(&bar[K1_KV], tile_i & 1, abort_flag, p.status)) { ok = false; break; }
+        if (!issue_s(g)) { ok = false; break; }
+        if (n_iter == 1) umma_commit(&bar[K1_KVE]);
+        for (int t = 0; t < n_iter && ok; ++t, ++g) {
+          if (t + 1 < n_iter) {
+            if (!issue_s(g + 1)) { ok = false; break; }
+            if (t + 2 == n_iter) umma_commit(&bar[K1_KVE]);  // the last S / dP of this tile: K and V may be replaced
+          }
+          const int s = g % BWD_NS;
+          if (!mbar_wait_bounded(&bar[K1_PF], g & 1, abort_flag, p.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sq = smem_u32(smem + L::OFF_Q + s * L::STAGE);
+          const uint32_t sdo = sq + L::DB * L::Q_TILE;
 #pragma unroll
-        for (int k = 0; k < 64 / 16; ++k) {  // reduction over the 64 query rows
-          umma_bf16_ss(t_dv, make_smem_desc(sp + k * 32, 16, 1024), make_smem_desc(sdo + k * 2048, L::Q_TILE, 1024),
-                       idesc_acc, (t | k) != 0);
-        }
+          for (int kk = 0; kk < 64 / 16; ++kk) {  // reduction over the 64 query rows
+            umma_bf16_ss(t_dv, make_smem_desc(sp + kk * 32, 16, 1024), make_smem_desc(sdo + kk * 2048, L::Q_TILE, 1024),
+                         idesc_acc, (t | kk) != 0);
+          }
 #pragma unroll
-        for (int k = 0; k < 64 / 16; ++k) {
-          umma_bf16_ss(t_dk, make_smem_desc(sds + k * 32, 16, 1024), make_smem_desc(sq + k * 2048, L::Q_TILE, 1024),
-                       idesc_acc, (t | k) != 0);
+          for (int kk = 0; kk < 64 / 16; ++kk) {
+            umma_bf16_ss(t_dk, make_smem_desc(sds + kk * 32, 16, 1024), make_smem_desc(sq + kk * 2048, L::Q_TILE, 1024),
+                         idesc_acc, (t | kk) != 0);
+          }
+          umma_commit(&bar[K1_QE + s]);
+          umma_commit(&bar[K1_PE]);
         }
-        umma_commit(&bar[K1_QE + s]);
-        umma_commit(&bar[K1_PE]);
+        ++tile_i;
       }
     }
   } else {
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;  // kv row within the block == TMEM lane
-    const int kv = kv0 + r;
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
     const float sl2 = p.scale * 1.4426950408889634f;
     const int grp = (warp - 2) >> 2;  // which half of the 64 query columns this warp group handles
     const int cb = grp * 32;
-    bool ok = n_iter > 0;
-    for (int t = 0; t < n_iter && ok; ++t) {
-      const int h = hk * G + t / per_head;
-      const int q0 = (i_start + t % per_head) * 64 + cb;
-      // per-column statistics of this block, fetched before the tensor core is done (same address in every lane)
-      const float* lse_q = p.lse + (size_t(b) * p.H + h) * p.Sq;
-      const float* dl_q = p.delta + (size_t(b) * p.H + h) * p.Sq;
-      // tile-level test (warp-uniform): is every (kv row, query column) of this warp group's 128 x 32 block visible?
-      const int off = p.Sk - p.Sq;
-      const bool full = q0 + 31 < p.Sq && kv0 + 127 < p.Sk && (!p.causal || kv0 + 127 <= q0 + off) && (p.Sq & 3) == 0;
-      float lq[32], dl[32];
-      if (full) {
-        const float4* l4 = reinterpret_cast<const float4*>(lse_q + q0);
-        const float4* d4 = reinterpret_cast<const float4*>(dl_q + q0);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float4 a = __ldg(l4 + i), c = __ldg(d4 + i);
-          lq[4 * i] = a.x; lq[4 * i + 1] = a.y; lq[4 * i + 2] = a.z; lq[4 * i + 3] = a.w;
-          dl[4 * i] = c.x; dl[4 * i + 1] = c.y; dl[4 * i + 2] = c.z; dl[4 * i + 3] = c.w;
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const bool in = q0 + i < p.Sq;
-          lq[i] = in ? __ldg(lse_q + q0 + i) : 0.f;
-          dl[i] = in ? __ldg(dl_q + q0 + i) : 0.f;
-        }
-      }
-      if (!mbar_wait_bounded_warp(&bar[K1_SF], t & 1, abort_flag, p.status)) { ok = false; break; }
-      tc_fence_after();
-      float sv[32], dp[32];
-      {
-        uint32_t a[32], d2[32];
-        tmem_ld_32x32(t_s + lane_addr + cb, a);
-        tmem_ld_32x32(t_dp + lane_addr + cb, d2);
-        tc_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) { sv[i] = __uint_as_float(a[i]); dp[i] = __uint_as_float(d2[i]); }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bar[K1_SFREE]);
-      if (full) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float pv = exp2f(fmaf(sv[i], sl2, -lq[i]));
-          dp[i] = pv * fmaf(dp[i], p.scale, -dl[i]);
-          sv[i] = pv;
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int q = q0 + i;
-          const bool visible = q < p.Sq && kv < p.Sk && (!p.causal || kv <= q + off);
-          float pv = 0.f, ds = 0.f;
-          if (visible) {
-            pv = exp2f(fmaf(sv[i], sl2, -lq[i]));
-            ds = pv * fmaf(dp[i], p.scale, -dl[i]);
+    const int off = p.Sk - p.Sq;
+    bool ok = true;
+    uint32_t g = 0;
+    int jb, hk, b, i_start, per_head;
+    for (int k = 0; ok && tiles.get(k, jb, hk, b, i_start, per_head); ++k) {
+      if (per_head < 0) continue;  // not a tile (middle block already done)
+      const int n_iter = per_head * G;
+      const int kv0 = jb * 128;
+      const int kv = kv0 + r;
+      const bool row_ok = kv < p.Sk;
+      __nv_bfloat16* dk_row = p.dk + ((size_t(b) * p.Sk + kv) * p.Hkv + hk) * D;
+      __nv_bfloat16* dv_row = p.dv + ((size_t(b) * p.Sk + kv) * p.Hkv + hk) * D;
+      if (n_iter == 0) {
+        if (row_ok) {
+          for (int i = grp * (D / 2); i < (grp + 1) * (D / 2); i += 8) {
+            *reinterpret_cast<uint4*>(dk_row + i) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(dv_row + i) = make_uint4(0, 0, 0, 0);
           }
-          sv[i] = pv;
-          dp[i] = ds;
         }
+        continue;
       }
-      if (t > 0) {
-        if (!mbar_wait_bounded_warp(&bar[K1_PE], (t - 1) & 1, abort_flag, p.status)) { ok = false; break; }
-      }
-      uint8_t* tp = smem + L::OFF_P;
-      uint8_t* tds = smem + L::OFF_DS;
+      for (int t = 0; t < n_iter && ok; ++t, ++g) {
+        const int h = hk * G + t / per_head;
+        const int q0 = (i_start + t % per_head) * 64 + cb;
+        // per-column statistics of this block, fetched before the tensor core is done (same address in every lane)
+        const float* lse_q = p.lse + (size_t(b) * p.H + h) * p.Sq;
+        const float* dl_q = p.delta + (size_t(b) * p.H + h) * p.Sq;
+        // tile-level test (warp-uniform): is every (kv row, query column) of this warp group's 128 x 32 block visible?
+        const bool full = q0 + 31 < p.Sq && kv0 + 127 < p.Sk && (!p.causal || kv0 + 127 <= q0 + off) && (p.Sq & 3) == 0;
+        float lq[32], dl[32];
+        if (full) {
+          const float4* l4 = reinterpret_cast<const float4*>(lse_q + q0);
+          const float4* d4 = reinterpret_cast<const float4*>(dl_q + q0);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint4 v, w;
-        v.x = pack_bf16(sv[c * 8 + 0], sv[c * 8 + 1]); v.y = pack_bf16(sv[c * 8 + 2], sv[c * 8 + 3]);
-        v.z = pack_bf16(sv[c * 8 + 4], sv[c * 8 + 5]); v.w = pack_bf16(sv[c * 8 + 6], sv[c * 8 + 7]);
-        w.x = pack_bf16(dp[c * 8 + 0], dp[c * 8 + 1]); w.y = pack_bf16(dp[c * 8 + 2], dp[c * 8 + 3]);
-        w.z = pack_bf16(dp[c * 8 + 4], dp[c * 8 + 5]); w.w = pack_bf16(dp[c * 8 + 6], dp[c * 8 + 7]);
-        st_swz(tp, r, grp * 4 + c, v);
-        st_swz(tds, r, grp * 4 + c, w);
-      }
-      fence_proxy_async();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bar[K1_PF]);
-    }
-    const bool row_ok = kv < p.Sk;
-    __nv_bfloat16* dk_row = p.dk + ((size_t(b) * p.Sk + kv) * p.Hkv + hk) * D;
-    __nv_bfloat16* dv_row = p.dv + ((size_t(b) * p.Sk + kv) * p.Hkv + hk) * D;
-    if (n_iter == 0) {
-      if (row_ok) {
-        for (int i = grp * (D / 2); i < (grp + 1) * (D / 2); i += 8) {
-          *reinterpret_cast<uint4*>(dk_row + i) = make_uint4(0, 0, 0, 0);
-          *reinterpret_cast<uint4*>(dv_row + i) = make_uint4(0, 0, 0, 0);
+          for (int i = 0; i < 8; ++i) {
+            const float4 a = __ldg(l4 + i), c = __ldg(d4 + i);
+            lq[4 * i] = a.x; lq[4 * i + 1] = a.y; lq[4 * i + 2] = a.z; lq[4 * i + 3] = a.w;
+            dl[4 * i] = c.x; dl[4 * i + 1] = c.y; dl[4 * i + 2] = c.z; dl[4 * i + 3] = c.w;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const bool in = q0 + i < p.Sq;
+            lq[i] = in ? __ldg(lse_q + q0 + i) : 0.f;
+            dl[i] = in ? __ldg(dl_q + q0 + i) : 0.f;
+          }
         }
+        if (!mbar_wait_bounded_warp(&bar[K1_SF], g & 1, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        float sv[32], dp[32];
+        {
+          uint32_t a[32], d2[32];
+          tmem_ld_32x32(t_s + lane_addr + cb, a);
+          tmem_ld_32x32(t_dp + lane_addr + cb, d2);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) { sv[i] = __uint_as_float(a[i]); dp[i] = __uint_as_float(d2[i]); }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar[K1_SFREE]);
+        if (full) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float pv = exp2f(fmaf(sv[i], sl2, -lq[i]));
+            dp[i] = pv * fmaf(dp[i], p.scale, -dl[i]);
+            sv[i] = pv;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int q = q0 + i;
+            const bool visible = q < p.Sq && kv < p.Sk && (!p.causal || kv <= q + off);
+            float pv = 0.f, ds = 0.f;
+            if (visible) {
+              pv = exp2f(fmaf(sv[i], sl2, -lq[i]));
+              ds = pv * fmaf(dp[i], p.scale, -dl[i]);
+            }
+            sv[i] = pv;
+            dp[i] = ds;
+          }
+        }
+        if (g > 0) {  // P^T / dS^T of the previous iteration (possibly of the previous tile) have been consumed
+          if (!mbar_wait_bounded_warp(&bar[K1_PE], (g - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+        }
+        uint8_t* tp = smem + L::OFF_P;
+        uint8_t* tds = smem + L::OFF_DS;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint4 v, w;
+          v.x = pack_bf16(sv[c * 8 + 0], sv[c * 8 + 1]); v.y = pack_bf16(sv[c * 8 + 2], sv[c * 8 + 3]);
+          v.z = pack_bf16(sv[c * 8 + 4], sv[c * 8 + 5]); v.w = pack_bf16(sv[c * 8 + 6], sv[c * 8 + 7]);
+          w.x = pack_bf16(dp[c * 8 + 0], dp[c * 8 + 1]); w.y = pack_bf16(dp[c * 8 + 2], dp[c * 8 + 3]);
+          w.z = pack_bf16(dp[c * 8 + 4], dp[c * 8 + 5]); w.w = pack_bf16(dp[c * 8 + 6], dp[c * 8 + 7]);
+          st_swz(tp, r, grp * 4 + c, v);
+          st_swz(tds, r, grp * 4 + c, w);
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar[K1_PF]);
       }
-    } else if (ok && mbar_wait_bounded_warp(&bar[K1_PE], (n_iter - 1) & 1, abort_flag, p.status)) {
+      if (!ok) break;
+      // dK / dV of this tile: the accumulators are complete when the last iteration's MMAs are.  The next tile's
+      // first accumulating MMA is issued only after these warps hand over its P^T / dS^T, i.e. after this read.
+      if (!mbar_wait_bounded_warp(&bar[K1_PE], (g - 1) & 1, abort_flag, p.status)) { ok = false; break; }
       tc_fence_after();
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
@@ -342,6 +398,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           }
         }
       }
+      tc_fence_before();
     }
   }
   tc_fence_before();
@@ -613,7 +670,12 @@ static int launch_bwd(const void* dO, const void* q, const void* k, const void* 
     if (cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, DqSmem<D>::TOTAL) != cudaSuccess) return -3;
     configured = true;
   }
-  dim3 g1((p.Sk + 127) / 128, p.Hkv, p.B);
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int n_kvb = (p.Sk + 127) / 128;
+  const int items = ((n_kvb + 1) / 2) * p.Hkv * p.B;  // pairs of kv blocks, see DkvTiles
+  const int g1 = items < sms ? items : sms;
   k1<<<g1, BWD_THREADS, DkvSmem<D>::TOTAL, stream>>>(mq64, mdo64, mk128, mv128, p);
   dim3 g2((p.Sq + 127) / 128, p.H, p.B);
   k2<<<g2, BWD_THREADS, DqSmem<D>::TOTAL, stream>>>(mq128, mdo128, mk64, mv64, p);
