@@ -44,8 +44,11 @@ _SIMPLE = (int, float, bool, str, type(None))
 class TaskCode:
     """Source text plus the tables it refers to; ``bind(device)`` gives the callable."""
 
-    def __init__(self, name: str, src: str, targets: list, consts: list, n_in: int, n_out: int):
+    def __init__(self, name: str, src: str, targets: list, consts: list, n_in: int, n_out: int, sink_outputs=()):
         self.name, self.src, self.targets, self.consts, self.n_in, self.n_out = name, src, targets, consts, n_in, n_out
+        # output positions produced by a weight-gradient op and by nothing else: ``run(args, sink)`` accepts an
+        # accumulator for them (see ops/sink.py)
+        self.sink_outputs = tuple(sink_outputs)
         self._bound: dict[Any, Callable] = {}
 
     def key(self):
@@ -55,7 +58,9 @@ class TaskCode:
         fn = self._bound.get(device)
         if fn is None:
             consts = [device if isinstance(c, torch.device) else c for c in self.consts]
-            scope = {"T": self.targets, "C": consts, "DEV": device}
+            from ..ops import sink as _sink
+
+            scope = {"T": self.targets, "C": consts, "DEV": device, "WG": _sink.call}
             exec(compile(self.src, f"<task {self.name}>", "exec"), scope)
             fn = scope["run"]
             self._bound[device] = fn
@@ -119,6 +124,14 @@ def generate(name: str, nodes: Sequence[fx.Node], inputs: Sequence[Any], outputs
             return f"slice({aref(a.start, m)}, {aref(a.stop, m)}, {aref(a.step, m)})"
         return consts.ref(a)
 
+    from ..ops import sink as _sink
+
+    sinkable = _sink.sink_targets()
+    out_index = {}
+    for j, k in enumerate(outputs):
+        out_index.setdefault(k, []).append(j)
+    sink_outputs: list[int] = []
+
     pre_free = [names[k] for k in inputs if last_use.get(k) == -1]
     if pre_free:
         lines.append(f"    {' = '.join(pre_free)} = None")
@@ -140,7 +153,13 @@ def generate(name: str, nodes: Sequence[fx.Node], inputs: Sequence[Any], outputs
             else:
                 parts = [aref(a, m) for a in n.args]
                 parts += [f"{kw}={aref(v, m)}" for kw, v in n.kwargs.items()]
-                lines.append(f"    {var} = {tref(n.target)}({', '.join(parts)})")
+                if n.target in sinkable and k not in last_use and len(out_index.get(k, ())) == 1:
+                    # a weight gradient that only leaves the task: the caller may supply its accumulator
+                    j = out_index[k][0]
+                    sink_outputs.append(j)
+                    lines.append(f"    {var} = WG({tref(n.target)}, sink, {j}, {', '.join(parts)})")
+                else:
+                    lines.append(f"    {var} = {tref(n.target)}({', '.join(parts)})")
         else:  # pragma: no cover
             raise NotImplementedError(f"cannot generate code for node {n.op}")
         dead = [kk for kk in {key_of(i, m) for i in n.all_input_nodes} if last_use.get(kk) == pos and kk not in out_set]
@@ -150,8 +169,8 @@ def generate(name: str, nodes: Sequence[fx.Node], inputs: Sequence[Any], outputs
             lines.append(f"    {' = '.join(sorted(names[d] for d in dead))} = None")
 
     lines.append(f"    return [{', '.join(names[k] for k in outputs)}]")
-    src = "def run(args):\n" + "\n".join(lines) + "\n"
-    return TaskCode(name, src, targets, consts.items, len(inputs), len(outputs))
+    src = "def run(args, sink=None):\n" + "\n".join(lines) + "\n"
+    return TaskCode(name, src, targets, consts.items, len(inputs), len(outputs), sink_outputs)
 
 
 class CodeCache:

@@ -432,9 +432,13 @@ class Lowering:
                                            u.members[0][0].cluster.stage_id, None, mbs[0], u.start, u.end))
             # accumulate loop outputs, queue transfers
             by_dst: dict[int, list] = defaultdict(list)
+            task = self.instrs[-1]
             for (o, mb), v in zip(keys_out, vids_out):
                 for k in out_positions.get(o, ()):
                     steal = o in single_use_outputs and len(out_positions[o]) == 1
+                    if (steal and loop.out_kinds[k] == 0 and config.wgrad_sinks.value and not remote_users.get(o)
+                            and v in task.outs and task.outs.index(v) in task.code.sink_outputs):
+                        task.sinks.append((task.outs.index(v), acc_vid[k]))
                     self.instrs.append(Accum(rank, acc_vid[k], v, loop.out_kinds[k], loop.out_axes[k], mb, n_mb, steal))
                 for dst in sorted(remote_users.get(o, ())):
                     by_dst[dst].append(((o, mb), v))

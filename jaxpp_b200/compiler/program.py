@@ -54,6 +54,9 @@ class RunTask(Instr):
     mubatch: int | None = None
     start: int = 0  # list-scheduling clock (integer latencies)
     end: int = 0
+    # (output position, accumulator value id): outputs that only feed the loop's Add accumulation and that the
+    # task can add into the accumulator itself (weight gradients, see ops/sink.py)
+    sinks: list = dataclasses.field(default_factory=list)
 
 
 @dataclasses.dataclass

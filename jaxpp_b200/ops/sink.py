@@ -1,0 +1,68 @@
+"""Weight-gradient sinks: let a wgrad GEMM add into the loop's accumulator instead of producing a fresh tensor.
+
+A ``treduce`` loop sums every microbatch's weight gradient into an accumulator.  Done literally that is a GEMM
+that writes a parameter-sized fp32 tensor followed by an add kernel that reads two of them and writes one, per
+weight and microbatch.  When a task output is (a) produced by a weight-gradient op and (b) consumed by nothing but
+the loop's ``Add`` accumulation, the executor hands the accumulator to the task and the op's GEMM epilogue does
+``acc += dy^T x`` in place (the accumulate epilogue of the tcgen05 kernels; ``add_`` on the reference path) and
+returns the accumulator itself, which makes the accumulation step a no-op.  The reference reaches the same effect
+through XLA's fusion of the add into the loop body; this is the explicit form of row N16 of the design inventory.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import core as ops
+
+
+def sink_targets() -> tuple:
+    """Op overloads whose result may be redirected into an accumulator."""
+    out = [torch.ops.b200.linear_wgrad.default]
+    try:
+        from ..parallel import tp  # noqa: F401  (registers the b200tp ops)
+
+        out.append(torch.ops.b200tp.ag_wgrad.default)
+    except Exception:  # pragma: no cover - the tensor-parallel ops are always importable
+        pass
+    return tuple(out)
+
+
+def _fits(acc: torch.Tensor, rows: int, cols: int, out_dtype) -> bool:
+    return acc.dim() == 2 and acc.shape[0] == rows and acc.shape[1] == cols and (out_dtype is None or acc.dtype == out_dtype)
+
+
+def accumulate(op, acc: torch.Tensor, *args, **kwargs) -> torch.Tensor:
+    """``acc += op(*args)`` with the addition done by the op where it can; returns ``acc``."""
+    if op is torch.ops.b200.linear_wgrad.default:
+        dy, x = args[0], args[1]
+        out_dtype = args[2] if len(args) > 2 else kwargs.get("out_dtype")
+        if (ops._use_native(dy) and acc.dtype == torch.float32 and acc.is_contiguous()
+                and _fits(acc, dy.shape[-1], x.shape[-1], out_dtype) and dy.dtype == torch.bfloat16):
+            ops._native().linear_wgrad(dy, x, out=acc, accumulate=True)
+            return acc
+    elif op is torch.ops.b200tp.ag_wgrad.default:
+        dy, x_shard, axis = args[0], args[1], args[2]
+        out_dtype = args[3] if len(args) > 3 else kwargs.get("out_dtype")
+        from ..parallel import tp
+
+        if (tp._fused(dy) and tp.axis_size(axis) > 1 and acc.dtype == torch.float32 and acc.is_contiguous()
+                and _fits(acc, dy.shape[-1], x_shard.shape[-1], out_dtype)):
+            from ..parallel import fused
+
+            got = fused.ag_wgrad(dy, x_shard, axis, out_dtype, acc=acc)
+            if got is acc:
+                return acc
+            return acc.add_(got)
+        if (ops._use_native(dy) and acc.dtype == torch.float32 and acc.is_contiguous() and dy.dtype == torch.bfloat16
+                and _fits(acc, dy.shape[-1], x_shard.shape[-1], out_dtype)):
+            ops._native().linear_wgrad(dy, tp._all_gather_rows(x_shard, axis), out=acc, accumulate=True)
+            return acc
+    return acc.add_(op(*args, **kwargs))
+
+
+def call(op, sink, index: int, *args, **kwargs):
+    """What generated task code calls for a sinkable op: ``sink`` maps output positions to accumulators."""
+    acc = sink.get(index) if sink else None
+    if acc is None:
+        return op(*args, **kwargs)
+    return accumulate(op, acc, *args, **kwargs)

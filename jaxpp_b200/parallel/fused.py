@@ -89,8 +89,9 @@ def ag_dgrad(dy_shard, w, axis):
     return dx, full
 
 
-def ag_wgrad(dy, x_shard, axis, out_dtype=None):
-    """dW = dy^T @ all_gather_rows(x_shard); the gather runs along the reduction (token) dimension"""
+def ag_wgrad(dy, x_shard, axis, out_dtype=None, acc=None):
+    """dW = dy^T @ all_gather_rows(x_shard); the gather runs along the reduction (token) dimension.  With ``acc``
+    (fp32, same shape) the product is added into it by the kernel's accumulate epilogue and ``acc`` is returned."""
     n = tpmod.axis_size(axis)
     dy2, x2 = _bf16_2d(dy), _bf16_2d(x_shard)
     T, Nout = dy2.shape
@@ -101,8 +102,9 @@ def ag_wgrad(dy, x_shard, axis, out_dtype=None):
         return ops.linear_wgrad(dy, tpmod._all_gather_rows(x_shard, axis), out_dtype)
     ws = symm.workspace_for(axis, T * Kin * 2, 0)
     desc = ws.next_call(GATHER_RED, True, False)
-    out = torch.empty(Nout, Kin, dtype=out_dtype, device=dy.device)
-    _launch(dy2, x2, out, None, Nout, Kin, T, Nout, Kin, True, True, False, desc)
+    accumulate = acc is not None and acc.dtype == torch.float32 and out_dtype == torch.float32
+    out = acc if accumulate else torch.empty(Nout, Kin, dtype=out_dtype, device=dy.device)
+    _launch(dy2, x2, out, None, Nout, Kin, T, Nout, Kin, True, True, accumulate, desc)
     return out
 
 

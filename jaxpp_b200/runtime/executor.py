@@ -62,6 +62,9 @@ class RankState:
         for v, donate in zip(ins.ins, ins.donate):
             args.append(env.pop(v) if donate else env[v])
         fn = ins.code.bind(self.device)
+        sink = None
+        if ins.sinks:
+            sink = {j: env[acc] for j, acc in ins.sinks if acc in env}
         timing = _TIMES[-1] if _TIMES else None
         if timing is not None:
             if self.device.type == "cuda":
@@ -73,11 +76,11 @@ class RankState:
         if self.device.type == "cuda" and config.nvtx_ranges.value:
             torch.cuda.nvtx.range_push(ins.name)
             try:
-                outs = fn(args)
+                outs = fn(args, sink) if sink else fn(args)
             finally:
                 torch.cuda.nvtx.range_pop()
         else:
-            outs = fn(args)
+            outs = fn(args, sink) if sink else fn(args)
         if self.record_events:
             e1 = torch.cuda.Event(enable_timing=True)
             e1.record()
@@ -114,6 +117,8 @@ class RankState:
             return
         if acc is None:
             env[ins.acc] = val if (ins.steal and val.is_contiguous()) else val.clone()
+        elif acc is val:
+            pass  # the task already added this microbatch's contribution into the accumulator (a sink)
         elif ins.kind == 0:
             acc.add_(val)
         else:

@@ -306,3 +306,30 @@ def test_dropout_inside_the_pipelined_loop_draws_the_same_numbers(schedule):
     assert_trees_equal(ref, got, exact=True)
     other = step(params, batch, seed + 1)
     assert not torch.equal(leaves(other)[0], leaves(ref)[0])
+
+
+def test_weight_gradients_sink_into_the_loop_accumulators():
+    """Weight gradients that only feed the loop's Add accumulation are added into the accumulator by the producing
+    op; the scheduled program marks those outputs, the accumulation step becomes a no-op for them, and the result
+    is identical to the literal produce-then-add form."""
+    sched = jp.Std1F1B(2)
+    params = mlp_params(2, 8)
+    batch = torch.randn(4, 3, 8, generator=torch.Generator().manual_seed(7))
+    step = make_mlp_step(2, sched, 4)
+    f = jp.mpmd_jit_with_loop(step, cpu_mesh(2))
+    compiled = f.lower(params, batch)
+    tasks = [i for i in compiled.program.instrs if isinstance(i, RunTask)]
+    sunk = [i for i in tasks if i.sinks]
+    assert sunk, "no task output was recognised as a weight-gradient sink"
+    assert all(t.task_type is None or "bwd" in str(t.task_type).lower() or "BWD" in str(t.task_type) for t in sunk)
+    n_w = sum(1 for p in params for k in p if k in ("w1", "w2"))
+    assert max(len(t.sinks) for t in sunk) <= n_w
+    got = f(params, batch)
+    with config.wgrad_sinks.set(False):
+        g = jp.mpmd_jit_with_loop(make_mlp_step(2, sched, 4), cpu_mesh(2))
+        plain = g.lower(params, batch)
+        assert not any(i.sinks for i in plain.program.instrs if isinstance(i, RunTask))
+        ref = g(params, batch)
+    eager = step(params, batch)
+    assert_trees_equal(eager, got, exact=True)
+    assert_trees_equal(eager, ref, exact=True)
