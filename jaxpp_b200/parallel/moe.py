@@ -199,7 +199,6 @@ def _router_impl(logits: Tensor, top_k: int):
         native._check(lib.jpb_router(0 if lg.dtype == torch.float32 else 1, lg.data_ptr(), probs.data_ptr(), top_i.data_ptr(),
                                      weights.data_ptr(), stats[0].data_ptr(), stats[1].data_ptr(), T, E, top_k,
                                      native._stream()), "jpb_router")
-        native.LAUNCHES[0] += 1
         return top_i, weights, probs, stats[1]
     return _route_ref(logits, top_k)
 

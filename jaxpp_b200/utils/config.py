@@ -133,8 +133,6 @@ comm_reserved_sms = IntEnvVar("JAXPP_B200_COMM_RESERVED_SMS", 4)
 p2p_backend = StrEnvVar("JAXPP_B200_P2P", "torch")
 # Let weight-gradient GEMMs add straight into the microbatch loop's accumulators (ops/sink.py).
 wgrad_sinks = BoolEnvVar("JAXPP_B200_WGRAD_SINKS", True)
-# Capture tasks into CUDA graphs after their first eager run.
-use_cuda_graphs = BoolEnvVar("JAXPP_B200_CUDA_GRAPHS", False)
 # Seconds a rank may go without a heartbeat before the watchdog reports it.
 heartbeat_timeout_s = IntEnvVar("JAXPP_B200_HEARTBEAT_TIMEOUT", 30)
 # Wrap every task in an NVTX range named like the task (fwd_3__5, …) for timeline profilers.
