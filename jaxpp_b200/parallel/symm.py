@@ -21,12 +21,22 @@ from ..ops import native
 
 
 class SymmetricBuffer:
+    """``nbytes`` usable bytes on every rank of ``group``, each rank's copy mapped into every other rank's
+    address space.  The allocation carries a guard band of ``GUARD`` bytes on either side of the usable range,
+    filled with a pattern: ``check_canaries()`` reads them back, so a kernel that wrote outside its buffer (here
+    or from a peer) is caught on the host without any tool that instruments the GPU."""
+
+    GUARD = 256
+    PATTERN = 0xA5
+
     def __init__(self, nbytes: int, group, group_ranks: list[int]):
         lib = native.load()
         lib.jpb_ipc_alloc.argtypes = [ctypes.c_longlong, ctypes.POINTER(ctypes.c_void_p), ctypes.c_char_p]
         lib.jpb_ipc_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]
         lib.jpb_ipc_close.argtypes = [ctypes.c_void_p]
         lib.jpb_ipc_free.argtypes = [ctypes.c_void_p]
+        lib.jpb_memset_async.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p]
+        lib.jpb_memcpy_async.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p]
         self.lib = lib
         self.nbytes = nbytes
         self.group = group
@@ -34,31 +44,50 @@ class SymmetricBuffer:
         self.rank = group_ranks.index(dist.get_rank())
         ptr = ctypes.c_void_p()
         handle = ctypes.create_string_buffer(64)
-        native._check(lib.jpb_ipc_alloc(nbytes, ctypes.byref(ptr), handle), "jpb_ipc_alloc", 0)
-        self.local_ptr = ptr.value
+        native._check(lib.jpb_ipc_alloc(nbytes + 2 * self.GUARD, ctypes.byref(ptr), handle), "jpb_ipc_alloc", 0)  # zero-filled
+        self.local_base = ptr.value
+        stream = native._stream()
+        native._check(lib.jpb_memset_async(self.local_base, self.PATTERN, self.GUARD, stream), "guard", 0)
+        native._check(lib.jpb_memset_async(self.local_base + self.GUARD + nbytes, self.PATTERN, self.GUARD, stream), "guard", 0)
         handles: list[Any] = [None] * self.n
         dist.all_gather_object(handles, handle.raw, group=group)
-        self.ptrs: list[int] = []
+        self.bases: list[int] = []
         for q, h in enumerate(handles):
             if q == self.rank:
-                self.ptrs.append(self.local_ptr)
+                self.bases.append(self.local_base)
                 continue
             peer = ctypes.c_void_p()
             native._check(lib.jpb_ipc_open(h, ctypes.byref(peer)), "jpb_ipc_open", 0)
-            self.ptrs.append(peer.value)
+            self.bases.append(peer.value)
+        self.ptrs: list[int] = [b + self.GUARD for b in self.bases]   # usable range of every rank's copy
+        self.local_ptr = self.ptrs[self.rank]
         # peers may write into this buffer as soon as they leave the barrier; only the current stream is
         # synchronised (a device-wide synchronisation would also wait for receives of a pipeline that are
         # posted ahead of time on side streams and cannot complete before this rank moves on)
         torch.cuda.current_stream().synchronize()
         dist.barrier(group=group)
 
+    def check_canaries(self) -> bool:
+        """True iff both guard bands of the local copy still hold the pattern (synchronises the current stream)."""
+        host = torch.empty(2 * self.GUARD, dtype=torch.uint8, device="cuda")
+        stream = native._stream()
+        self.lib.jpb_memcpy_async(host.data_ptr(), self.local_base, self.GUARD, stream)
+        self.lib.jpb_memcpy_async(host.data_ptr() + self.GUARD, self.local_base + self.GUARD + self.nbytes, self.GUARD, stream)
+        return bool((host.cpu() == self.PATTERN).all())
+
     def close(self):
-        for q, p in enumerate(self.ptrs):
-            if q != self.rank and p:
-                self.lib.jpb_ipc_close(p)
-        if self.local_ptr:
-            self.lib.jpb_ipc_free(self.local_ptr)
-        self.ptrs, self.local_ptr = [], None
+        for q, b in enumerate(self.bases):
+            if q != self.rank and b:
+                self.lib.jpb_ipc_close(b)
+        if self.local_base:
+            self.lib.jpb_ipc_free(self.local_base)
+        self.bases, self.ptrs, self.local_base, self.local_ptr = [], [], None, None
+
+
+def check_all_canaries() -> bool:
+    """Guard bands of every live symmetric buffer of this process (fused GEMM workspaces; all-reduce and MoE
+    workspaces register theirs through the same class)."""
+    return all(ws.buf.check_canaries() for ws in _WORKSPACES.values())
 
 
 class JpbCommDesc(ctypes.Structure):
@@ -147,10 +176,10 @@ def release_retired() -> None:
     torch.cuda.synchronize()
     for ws in _RETIRED:
         dist.barrier(group=ws.buf.group)   # every importer is done with the mapping ...
-        for q, ptr in enumerate(ws.buf.ptrs):
-            if q != ws.buf.rank and ptr:
-                ws.buf.lib.jpb_ipc_close(ptr)
+        for q, base in enumerate(ws.buf.bases):
+            if q != ws.buf.rank and base:
+                ws.buf.lib.jpb_ipc_close(base)
         dist.barrier(group=ws.buf.group)   # ... and has closed it before the owner frees the memory
-        ws.buf.lib.jpb_ipc_free(ws.buf.local_ptr)
-        ws.buf.ptrs, ws.buf.local_ptr = [], None
+        ws.buf.lib.jpb_ipc_free(ws.buf.local_base)
+        ws.buf.bases, ws.buf.ptrs, ws.buf.local_base, ws.buf.local_ptr = [], [], None, None
     _RETIRED.clear()

@@ -69,6 +69,11 @@ def scenario_fused_tp():
         torch.cuda.synchronize()
         assert native.read_status() == 0, "a fused kernel reported a time-out"
         assert fused.FALLBACKS[0] == 0, f"{fused.FALLBACKS[0]} fused calls fell back to NCCL"
+        from jaxpp_b200.parallel import symm
+
+        dist.barrier()
+        assert symm.check_all_canaries(), "a kernel wrote outside a symmetric workspace"
+        assert all(ws.buf.check_canaries() for ws in fused._AR_WS.values()), "all-reduce wrote outside its workspace"
     if r == 0:
         print("fused tensor-parallel kernels match their NCCL twins", flush=True)
 
@@ -142,6 +147,10 @@ def scenario_fused_moe():
                     close(b, a, 0.05, f"{name} (T={T})")
         torch.cuda.synchronize()
         assert native.read_status() == 0, "a fused kernel reported a time-out"
+        from jaxpp_b200.parallel import fused_moe
+
+        dist.barrier()
+        assert all(ws.buf.check_canaries() for ws in fused_moe._WS.values()), "dispatch / combine wrote outside the buffer"
     if r == 0:
         print("fused MoE dispatch / combine match the NCCL all-to-all path", flush=True)
 
