@@ -108,7 +108,11 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_dispatch_kernel(const MoePara
     const int in_owner = g % per_owner;
     const int el = in_owner / C, pos = in_owner % C;
     const int slot = (owner * p.e_local + el) * C + pos;
-    const int tok = p.index[slot];
+    int tok = p.index[slot];
+    if (tok >= p.n_tokens) {  // an index outside the token range: record it and treat the slot as empty
+      if (lane == 0 && p.status) atomicCAS(p.status, JPB_OK, JPB_ERR_BAD_ARGUMENT);
+      tok = -1;
+    }
     const float s = (p.scale != nullptr && tok >= 0) ? p.scale[slot] : 1.f;
     __nv_bfloat16* base = owner == p.rank ? p.out : p.recv_peer[owner];
     __nv_bfloat16* dst = base + ((long long)el * row_stride_out + (long long)p.rank * C + pos) * p.d;
@@ -171,7 +175,9 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_combine_kernel(const MoeParam
       for (int j = 0; j < p.top_k; ++j) {
         const int slot = p.index[t * p.top_k + j];
         uint4 val = make_uint4(0u, 0u, 0u, 0u);
-        if (slot < dump) {
+        if (slot < 0 || slot > dump) {  // not a slot and not the "dropped" marker: record it, contribute nothing
+          if (lane == 0 && v == lane && p.status) atomicCAS(p.status, JPB_OK, JPB_ERR_BAD_ARGUMENT);
+        } else if (slot < dump) {
           const int e = slot / C, pos = slot % C;
           const int owner = e / p.e_local, el = e % p.e_local;
           const __nv_bfloat16* src = owner == p.rank
@@ -229,10 +235,10 @@ static int moe_grid() {
   return sms * 4;
 }
 
-JPB_API int jpb_moe_dispatch(const void* x, const int* src_of_slot, const float* slot_scale, void* out, int n_experts,
-                             int capacity, int d, const JpbMoeDesc* desc, void* stream) {
+JPB_API int jpb_moe_dispatch(const void* x, const int* src_of_slot, const float* slot_scale, void* out, int n_tokens,
+                             int n_experts, int capacity, int d, const JpbMoeDesc* desc, void* stream) {
   jpb::MoeParams p = {};
-  const int rc = moe_fill(p, desc, n_experts, capacity, d, 0, 0);
+  const int rc = moe_fill(p, desc, n_experts, capacity, d, 0, n_tokens);
   if (rc) return rc;
   p.in = static_cast<const __nv_bfloat16*>(x); p.index = src_of_slot; p.scale = slot_scale;
   p.out = static_cast<__nv_bfloat16*>(out);

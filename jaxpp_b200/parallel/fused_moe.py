@@ -52,7 +52,7 @@ def _lib():
     lib = native.load()
     if not _bound:
         p, i = ctypes.c_void_p, ctypes.c_int
-        lib.jpb_moe_dispatch.argtypes = [p, p, p, p, i, i, i, ctypes.POINTER(JpbMoeDesc), p]
+        lib.jpb_moe_dispatch.argtypes = [p, p, p, p, i, i, i, i, ctypes.POINTER(JpbMoeDesc), p]
         lib.jpb_moe_combine.argtypes = [p, p, p, p, p, i, i, i, i, i, ctypes.POINTER(JpbMoeDesc), p]
         if lib.jpb_moe_desc_bytes() != ctypes.sizeof(JpbMoeDesc):
             raise native.NativeError("MoE call descriptor layout of the native library differs from the Python binding")
@@ -83,7 +83,7 @@ def dispatch(x: torch.Tensor, src_of_slot: torch.Tensor, slot_scale, n_experts: 
     desc = ws.next_call()
     out = torch.empty(n_experts // n, n * capacity, d, dtype=torch.bfloat16, device=x.device)
     rc = _lib().jpb_moe_dispatch(x.data_ptr(), src_of_slot.data_ptr(), None if slot_scale is None else slot_scale.data_ptr(),
-                                 out.data_ptr(), n_experts, capacity, d, ctypes.byref(desc), native._stream())
+                                 out.data_ptr(), x.shape[0], n_experts, capacity, d, ctypes.byref(desc), native._stream())
     native._check(rc, "jpb_moe_dispatch")
     return out
 
