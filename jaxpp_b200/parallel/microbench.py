@@ -40,6 +40,9 @@ def _time(fn, iters, flush):
     for _ in range(iters):
         flush.add_(1.0)
         dist.barrier()
+        # keep the GPU busy for ~0.5 ms while the host prepares the launch (descriptor set-up, tensor maps), so that
+        # the events bracket device time only, as they do inside a training step where the host runs ahead
+        torch.cuda._sleep(1_000_000)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         fn()
