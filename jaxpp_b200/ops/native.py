@@ -111,6 +111,13 @@ def _as_2d_bf16(t: torch.Tensor) -> torch.Tensor:
     t2 = t.reshape(-1, t.shape[-1])
     if t2.dtype != torch.bfloat16:
         raise NativeError(f"the tcgen05 GEMM takes bfloat16 operands, got {t2.dtype}")
+    if t2.shape[-1] % 8:
+        # TMA wants rows that start on 16-byte boundaries: give a narrow operand (a router's [tokens, n_experts]
+        # logits gradient, say) a row pitch that is a multiple of 8 elements; the extra columns are never addressed
+        width = t2.shape[-1]
+        padded = torch.zeros(t2.shape[0], (width + 7) // 8 * 8, dtype=t2.dtype, device=t2.device)
+        padded[:, :width].copy_(t2)
+        return padded[:, :width]
     if t2.stride(-1) != 1 or (t2.stride(0) % 8) or (t2.data_ptr() % 16):
         t2 = t2.contiguous()
     return t2

@@ -119,6 +119,17 @@ def test_activations_rope_colsum(native, dtype):
         close(merged, ops._qkv_merge_ref(*[g.float() for g in got], c, s_), **tol)
 
 
+def test_narrow_linear_like_a_router(native):
+    """A linear layer with 4 outputs (a small router): the narrow operands of its backward GEMMs are re-pitched."""
+    x, w, dy = rnd(300, 256, seed=41), rnd(4, 256, scale=0.2, seed=42), rnd(300, 4, seed=43)
+    close(native.linear(x, w, None), x.float() @ w.float().t(), rtol=2e-2, atol=0.1)
+    close(native.linear_dgrad(dy, w), dy.float() @ w.float(), rtol=2e-2, atol=0.05)
+    close(native.linear_wgrad(dy, x), dy.float().t() @ x.float(), rtol=2e-2, atol=0.5)
+    acc = torch.ones(4, 256, dtype=torch.float32, device="cuda")
+    native.linear_wgrad(dy, x, out=acc, accumulate=True)
+    close(acc, 1 + dy.float().t() @ x.float(), rtol=2e-2, atol=0.5)
+
+
 @pytest.mark.parametrize("E,M,N,K", [(3, 192, 320, 256), (2, 200, 264, 128), (4, 64, 128, 64)])
 def test_grouped_gemm_equal_groups(native, E, M, N, K):
     """One launch over all groups against per-group fp32 matmuls, in the three linear-layer layouts.  Group sizes
