@@ -15,11 +15,14 @@
 //                       assemble the complete gathered operand in an ordinary local tensor (own shard +
 //                       received chunks) while the tensor cores work, for a later local GEMM.
 //  GEMM -> reduce-scatter
-//                       Output row block p belongs to rank p.  Tiles of the peers' blocks are computed first;
-//                       their epilogue stores the bf16 partial tile straight into the owner's receive buffer
-//                       (peer stores) and then raises a per-tile flag in the owner's memory.  Tiles of the own
-//                       block run last; their epilogue waits for the peers' flags, adds the received partials
-//                       in fp32 and writes the final tile.
+//                       Output row block p belongs to rank p.  The epilogue of a tile of a peer's block
+//                       stores the bf16 partial tile straight into the owner's receive buffer (128-byte row
+//                       segments through a shared-memory transpose) and then raises a per-tile flag in the
+//                       owner's memory; the epilogue of an own tile waits for the peers' flags, adds the
+//                       received partials in fp32 and writes the final tile.  Peer and own tiles alternate in
+//                       groups of 16 row tiles (peers first), which spreads the link traffic over the kernel.
+//  reduction gather with an fp32 output (wgrad) runs one pass over the tiles per rank slot, the own slot
+//                       first, accumulating into D, so that no tile waits mid-k-loop for data in flight.
 //
 // Buffers are double-buffered by call parity, flags carry a monotonically increasing epoch and are never
 // reset.  No multicast load is used anywhere.  Every wait (mbarrier, chunk flag, peer flag) is bounded.
@@ -77,19 +80,6 @@ struct CommGemmParams {
   int rows_per_rank;                 // M / n_ranks for scatter
 };
 
-__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ int ld_acquire_sys(const int* p) {
-  int v;
-  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_gpu(int* p, int v) {
-  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 __device__ __forceinline__ void st_release_sys(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
