@@ -423,7 +423,29 @@ struct DqSmem {
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
 };
 
-enum { K2_Q = 0, K2_KF = 1, K2_KE = K2_KF + BWD_NS, K2_SF = K2_KE + BWD_NS, K2_SFREE, K2_DF, K2_DE, K2_N };
+enum { K2_Q = 0, K2_QFREE = 1, K2_KF = 2, K2_KE = K2_KF + BWD_NS, K2_SF = K2_KE + BWD_NS, K2_SFREE, K2_DF, K2_DE, K2_N };
+
+// Work distribution of the persistent dQ kernel: an item is a pair of query blocks (i, num_m-1-i) of one
+// (batch, head); under a causal mask the two together see the same number of kv blocks whatever i is.
+struct DqTiles {
+  int num_m, n_pairs, n_items, H, causal, Sq, Sk;
+  __device__ __forceinline__ bool get(int k, int& m_blk, int& h, int& b, int& n_iter) const {
+    const int item = blockIdx.x + (k >> 1) * gridDim.x;
+    if (item >= n_items) return false;
+    const int hb = item / n_pairs, pi = item - hb * n_pairs;
+    m_blk = (k & 1) ? pi : num_m - 1 - pi;   // the heavier block of the pair first
+    h = hb % H;
+    b = hb / H;
+    n_iter = (Sk + 63) / 64;
+    if (causal) {
+      const int last = (m_blk * 128 + 127 + (Sk - Sq)) / 64 + 1;
+      n_iter = last < n_iter ? last : n_iter;
+      if (n_iter < 1) n_iter = 1;
+    }
+    if ((k & 1) && num_m - 1 - pi == pi) n_iter = 0;  // odd block count: the middle block is its item's only tile
+    return true;
+  }
+};
 
 template <int D>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
@@ -438,20 +460,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_m = (p.Sq + 127) / 128;
-  const int m_blk = num_m - 1 - blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int hk = h / (p.H / p.Hkv);
-  const int m0 = m_blk * 128;
-  int n_iter = (p.Sk + 63) / 64;
-  if (p.causal) {
-    const int last = (m0 + 127 + (p.Sk - p.Sq)) / 64 + 1;
-    n_iter = last < n_iter ? last : n_iter;
-    if (n_iter < 1) n_iter = 1;
-  }
+  const int Gq = p.H / p.Hkv;
+  DqTiles tiles;
+  tiles.num_m = (p.Sq + 127) / 128;
+  tiles.n_pairs = (tiles.num_m + 1) / 2;
+  tiles.n_items = tiles.n_pairs * p.H * p.B;
+  tiles.H = p.H; tiles.causal = p.causal; tiles.Sq = p.Sq; tiles.Sk = p.Sk;
 
   if (threadIdx.x == 0) {
     mbar_init(&bar[K2_Q], 1);
+    mbar_init(&bar[K2_QFREE], 1);
     for (int s = 0; s < BWD_NS; ++s) { mbar_init(&bar[K2_KF + s], 1); mbar_init(&bar[K2_KE + s], 1); }
     mbar_init(&bar[K2_SF], 1);
     mbar_init(&bar[K2_SFREE], 8);
@@ -459,6 +477,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     mbar_init(&bar[K2_DE], 1);
     *abort_flag = 0;
     fence_barrier_init();
+    tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_do); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 256); tmem_relinquish(); }
   tc_fence_before();
@@ -467,6 +486,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t t_s = tmem_base, t_dp = tmem_base + 64, t_dq = tmem_base + 128;
 
+  // As in the dK/dV kernel: every role walks the same tiles; `g` counts this CTA's (q block, kv block) iterations
+  // over all its tiles and `tile_i` its tiles, and the barrier phases follow those two counters.
   if (warp == 0) {
     if (lane == 0) {
       uint32_t armed = 0, armed_phase = 0;
@@ -475,29 +496,38 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         armed |= 1u << id;
         armed_phase = (armed_phase & ~(1u << id)) | (ph << id);
       };
-      arm(K2_Q, 0, 2 * L::DB * L::Q_TILE);
-#pragma unroll
-      for (int d = 0; d < L::DB; ++d) {
-        tma_load_4d(smem + L::OFF_Q + d * L::Q_TILE, &map_q, &bar[K2_Q], d * 64, h, m0, b);
-        tma_load_4d(smem + L::OFF_DO + d * L::Q_TILE, &map_do, &bar[K2_Q], d * 64, h, m0, b);
-      }
       bool ok = true;
-      for (int t = 0; t < n_iter && ok; ++t) {
-        const int s = t % BWD_NS;
-        const uint32_t ph = (t / BWD_NS) & 1;
-        if (!mbar_wait_bounded(&bar[K2_KE + s], ph ^ 1, abort_flag, p.status)) { ok = false; break; }
-        arm(K2_KF + s, ph, L::STAGE);
-        uint8_t* st = smem + L::OFF_KV + s * L::STAGE;
+      uint32_t g = 0, tile_i = 0;
+      int m_blk, h, b, n_iter;
+      for (int k = 0; ok && tiles.get(k, m_blk, h, b, n_iter); ++k) {
+        if (n_iter <= 0) continue;
+        const int hk = h / Gq;
+        // Q / dO of the previous tile are read by its S and dP MMAs only
+        if (tile_i > 0 && !mbar_wait_bounded(&bar[K2_QFREE], (tile_i - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+        arm(K2_Q, tile_i & 1, 2 * L::DB * L::Q_TILE);
 #pragma unroll
         for (int d = 0; d < L::DB; ++d) {
-          tma_load_4d(st + d * L::KV_TILE, &map_k, &bar[K2_KF + s], d * 64, hk, t * 64, b);
-          tma_load_4d(st + (L::DB + d) * L::KV_TILE, &map_v, &bar[K2_KF + s], d * 64, hk, t * 64, b);
+          tma_load_4d(smem + L::OFF_Q + d * L::Q_TILE, &map_q, &bar[K2_Q], d * 64, h, m_blk * 128, b);
+          tma_load_4d(smem + L::OFF_DO + d * L::Q_TILE, &map_do, &bar[K2_Q], d * 64, h, m_blk * 128, b);
         }
+        for (int t = 0; t < n_iter && ok; ++t, ++g) {
+          const int s = g % BWD_NS;
+          const uint32_t ph = (g / BWD_NS) & 1;
+          if (!mbar_wait_bounded(&bar[K2_KE + s], ph ^ 1, abort_flag, p.status)) { ok = false; break; }
+          arm(K2_KF + s, ph, L::STAGE);
+          uint8_t* st = smem + L::OFF_KV + s * L::STAGE;
+#pragma unroll
+          for (int d = 0; d < L::DB; ++d) {
+            tma_load_4d(st + d * L::KV_TILE, &map_k, &bar[K2_KF + s], d * 64, hk, t * 64, b);
+            tma_load_4d(st + (L::DB + d) * L::KV_TILE, &map_v, &bar[K2_KF + s], d * 64, hk, t * 64, b);
+          }
+        }
+        ++tile_i;
       }
       if (!ok) {
         const uint64_t t0 = globaltimer_ns();
         for (int id = 0; id < K2_KE; ++id) {
-          if (!(armed & (1u << id))) continue;
+          if (id == K2_QFREE || !(armed & (1u << id))) continue;
           while (!mbar_try_wait(&bar[id], (armed_phase >> id) & 1) && globaltimer_ns() - t0 < JPB_WAIT_BUDGET_NS) {
           }
         }
@@ -509,11 +539,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       constexpr uint32_t idesc_dq = make_idesc_bf16(128, D, 0, 1);   // [q x d] = K-major(dS) x MN-major(K)
       const uint32_t sq = smem_u32(smem + L::OFF_Q), sdo = smem_u32(smem + L::OFF_DO);
       const uint32_t sds = smem_u32(smem + L::OFF_DS);
-      bool ok = mbar_wait_bounded(&bar[K2_Q], 0, abort_flag, p.status);
-      auto issue_s = [&](int t) -> bool {
-        const int s = t % BWD_NS;
-        if (!mbar_wait_bounded(&bar[K2_KF + s], (t / BWD_NS) & 1, abort_flag, p.status)) return false;
-        if (t > 0 && !mbar_wait_bounded(&bar[K2_SFREE], (t - 1) & 1, abort_flag, p.status)) return false;
+      bool ok = true;
+      auto issue_s = [&](uint32_t gg) -> bool {
+        const int s = gg % BWD_NS;
+        if (!mbar_wait_bounded(&bar[K2_KF + s], (gg / BWD_NS) & 1, abort_flag, p.status)) return false;
+        if (gg > 0 && !mbar_wait_bounded(&bar[K2_SFREE], (gg - 1) & 1, abort_flag, p.status)) return false;
         tc_fence_after();
         const uint32_t sk = smem_u32(smem + L::OFF_KV + s * L::STAGE);
         const uint32_t sv = sk + L::DB * L::KV_TILE;
@@ -532,89 +562,108 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         umma_commit(&bar[K2_SF]);
         return true;
       };
-      if (ok) ok = issue_s(0);
-      for (int t = 0; t < n_iter && ok; ++t) {
-        if (t + 1 < n_iter && !issue_s(t + 1)) { ok = false; break; }
-        const int s = t % BWD_NS;
-        if (!mbar_wait_bounded(&bar[K2_DF], t & 1, abort_flag, p.status)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t sk = smem_u32(smem + L::OFF_KV + s * L::STAGE);
+      uint32_t g = 0, tile_i = 0;
+      int m_blk, h, b, n_iter;
+      for (int k = 0; ok && tiles.get(k, m_blk, h, b, n_iter); ++k) {
+        if (n_iter <= 0) continue;
+        if (!mbar_wait_bounded(&bar[K2_Q], tile_i & 1, abort_flag, p.status)) { ok = false; break; }
+        if (!issue_s(g)) { ok = false; break; }
+        if (n_iter == 1) umma_commit(&bar[K2_QFREE]);
+        for (int t = 0; t < n_iter && ok; ++t, ++g) {
+          if (t + 1 < n_iter) {
+            if (!issue_s(g + 1)) { ok = false; break; }
+            if (t + 2 == n_iter) umma_commit(&bar[K2_QFREE]);  // the last S / dP of this tile: Q and dO may be replaced
+          }
+          const int s = g % BWD_NS;
+          if (!mbar_wait_bounded(&bar[K2_DF], g & 1, abort_flag, p.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sk = smem_u32(smem + L::OFF_KV + s * L::STAGE);
 #pragma unroll
-        for (int k = 0; k < 64 / 16; ++k) {  // reduction over the 64 kv rows
-          umma_bf16_ss(t_dq, make_smem_desc(sds + k * 32, 16, 1024), make_smem_desc(sk + k * 2048, L::KV_TILE, 1024),
-                       idesc_dq, (t | k) != 0);
+          for (int kk = 0; kk < 64 / 16; ++kk) {  // reduction over the 64 kv rows
+            umma_bf16_ss(t_dq, make_smem_desc(sds + kk * 32, 16, 1024), make_smem_desc(sk + kk * 2048, L::KV_TILE, 1024),
+                         idesc_dq, (t | kk) != 0);
+          }
+          umma_commit(&bar[K2_KE + s]);
+          umma_commit(&bar[K2_DE]);
         }
-        umma_commit(&bar[K2_KE + s]);
-        umma_commit(&bar[K2_DE]);
+        ++tile_i;
       }
     }
   } else {
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
-    const int qi = m0 + r;
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
     const float sl2 = p.scale * 1.4426950408889634f;
-    const bool row_ok = qi < p.Sq;
-    const float lse_r = row_ok ? p.lse[(size_t(b) * p.H + h) * p.Sq + qi] : 0.f;
-    const float dl_r = row_ok ? p.delta[(size_t(b) * p.H + h) * p.Sq + qi] : 0.f;
     const int off = p.Sk - p.Sq;
     const int grp = (warp - 2) >> 2;  // which half of the 64 kv columns this warp group handles
     const int cb = grp * 32;
     bool ok = true;
-    for (int t = 0; t < n_iter && ok; ++t) {
-      if (!mbar_wait_bounded_warp(&bar[K2_SF], t & 1, abort_flag, p.status)) { ok = false; break; }
-      tc_fence_after();
-      float sv[32], dp[32];
-      {
-        uint32_t a[32], d2[32];
-        tmem_ld_32x32(t_s + lane_addr + cb, a);
-        tmem_ld_32x32(t_dp + lane_addr + cb, d2);
-        tc_wait_ld();
+    uint32_t g = 0;
+    int m_blk, h, b, n_iter;
+    for (int k = 0; ok && tiles.get(k, m_blk, h, b, n_iter); ++k) {
+      if (n_iter <= 0) continue;
+      const int m0 = m_blk * 128;
+      const int qi = m0 + r;
+      const bool row_ok = qi < p.Sq;
+      const float lse_r = row_ok ? p.lse[(size_t(b) * p.H + h) * p.Sq + qi] : 0.f;
+      const float dl_r = row_ok ? p.delta[(size_t(b) * p.H + h) * p.Sq + qi] : 0.f;
+      for (int t = 0; t < n_iter && ok; ++t, ++g) {
+        if (!mbar_wait_bounded_warp(&bar[K2_SF], g & 1, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        float sv[32], dp[32];
+        {
+          uint32_t a[32], d2[32];
+          tmem_ld_32x32(t_s + lane_addr + cb, a);
+          tmem_ld_32x32(t_dp + lane_addr + cb, d2);
+          tc_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) { sv[i] = __uint_as_float(a[i]); dp[i] = __uint_as_float(d2[i]); }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bar[K2_SFREE]);
-      // warp-uniform: every (query row, kv column) of this warp group's 128 x 32 block visible?
-      const int kv_first = t * 64 + cb;
-      const bool full = m0 + 127 < p.Sq && kv_first + 31 < p.Sk && (!p.causal || kv_first + 31 <= m0 + off);
-      if (full) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float pv = exp2f(fmaf(sv[i], sl2, -lse_r));
-          dp[i] = pv * fmaf(dp[i], p.scale, -dl_r);
+          for (int i = 0; i < 32; ++i) { sv[i] = __uint_as_float(a[i]); dp[i] = __uint_as_float(d2[i]); }
         }
-      } else {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar[K2_SFREE]);
+        // warp-uniform: every (query row, kv column) of this warp group's 128 x 32 block visible?
+        const int kv_first = t * 64 + cb;
+        const bool full = m0 + 127 < p.Sq && kv_first + 31 < p.Sk && (!p.causal || kv_first + 31 <= m0 + off);
+        if (full) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kv = kv_first + i;
-          const bool visible = row_ok && kv < p.Sk && (!p.causal || kv <= qi + off);
-          float ds = 0.f;
-          if (visible) {
+          for (int i = 0; i < 32; ++i) {
             const float pv = exp2f(fmaf(sv[i], sl2, -lse_r));
-            ds = pv * fmaf(dp[i], p.scale, -dl_r);
+            dp[i] = pv * fmaf(dp[i], p.scale, -dl_r);
           }
-          dp[i] = ds;
-        }
-      }
-      if (t > 0) {
-        if (!mbar_wait_bounded_warp(&bar[K2_DE], (t - 1) & 1, abort_flag, p.status)) { ok = false; break; }
-      }
-      uint8_t* tds = smem + L::OFF_DS;
+        } else {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint4 w;
-        w.x = pack_bf16(dp[c * 8 + 0], dp[c * 8 + 1]); w.y = pack_bf16(dp[c * 8 + 2], dp[c * 8 + 3]);
-        w.z = pack_bf16(dp[c * 8 + 4], dp[c * 8 + 5]); w.w = pack_bf16(dp[c * 8 + 6], dp[c * 8 + 7]);
-        st_swz(tds, r, grp * 4 + c, w);
+          for (int i = 0; i < 32; ++i) {
+            const int kv = kv_first + i;
+            const bool visible = row_ok && kv < p.Sk && (!p.causal || kv <= qi + off);
+            float ds = 0.f;
+            if (visible) {
+              const float pv = exp2f(fmaf(sv[i], sl2, -lse_r));
+              ds = pv * fmaf(dp[i], p.scale, -dl_r);
+            }
+            dp[i] = ds;
+          }
+        }
+        if (g > 0) {  // dS of the previous iteration (possibly of the previous tile) has been consumed
+          if (!mbar_wait_bounded_warp(&bar[K2_DE], (g - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+        }
+        uint8_t* tds = smem + L::OFF_DS;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint4 w;
+          w.x = pack_bf16(dp[c * 8 + 0], dp[c * 8 + 1]); w.y = pack_bf16(dp[c * 8 + 2], dp[c * 8 + 3]);
+          w.z = pack_bf16(dp[c * 8 + 4], dp[c * 8 + 5]); w.w = pack_bf16(dp[c * 8 + 6], dp[c * 8 + 7]);
+          st_swz(tds, r, grp * 4 + c, w);
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar[K2_DF]);
       }
-      fence_proxy_async();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bar[K2_DF]);
-    }
-    if (ok && mbar_wait_bounded_warp(&bar[K2_DE], (n_iter - 1) & 1, abort_flag, p.status)) {
+      if (!ok) break;
+      // dQ of this tile; the next tile's first accumulating MMA needs a dS hand-over from these warps, which comes
+      // after this read of the accumulator
+      if (!mbar_wait_bounded_warp(&bar[K2_DE], (g - 1) & 1, abort_flag, p.status)) { ok = false; break; }
       tc_fence_after();
       __nv_bfloat16* dst = p.dq + ((size_t(b) * p.Sq + qi) * p.H + h) * D;
 #pragma unroll
@@ -634,6 +683,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           }
         }
       }
+      tc_fence_before();
     }
   }
   tc_fence_before();
@@ -677,7 +727,9 @@ static int launch_bwd(const void* dO, const void* q, const void* k, const void* 
   const int items = ((n_kvb + 1) / 2) * p.Hkv * p.B;  // pairs of kv blocks, see DkvTiles
   const int g1 = items < sms ? items : sms;
   k1<<<g1, BWD_THREADS, DkvSmem<D>::TOTAL, stream>>>(mq64, mdo64, mk128, mv128, p);
-  dim3 g2((p.Sq + 127) / 128, p.H, p.B);
+  const int num_m = (p.Sq + 127) / 128;
+  const int items2 = ((num_m + 1) / 2) * p.H * p.B;  // pairs of query blocks, see DqTiles
+  const int g2 = items2 < sms ? items2 : sms;
   k2<<<g2, BWD_THREADS, DqSmem<D>::TOTAL, stream>>>(mq128, mdo128, mk64, mv64, p);
   return int(cudaGetLastError());
 }
