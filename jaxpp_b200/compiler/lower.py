@@ -132,6 +132,10 @@ class Lowering:
     def run(self, schedule: BaseSchedule | None) -> Program:
         cap, graph = self.cap, self.graph
         cl.dce(graph)
+        if config.fuse_norm_backward_adds.value:
+            from .peephole import fuse_norm_backward_adds
+
+            fuse_norm_backward_adds(graph)
         loop = cl.find_loop(graph)
         nodes = list(graph.nodes)
         self.pos = {n: i for i, n in enumerate(nodes)}

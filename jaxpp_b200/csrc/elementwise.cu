@@ -135,7 +135,10 @@ __global__ void norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w
 template <typename T, bool LAYER, int MAXT = 512>
 __global__ void __launch_bounds__(MAXT) norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
                                 const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
-                                T* __restrict__ dx, float* __restrict__ partial, int rows, int H) {
+                                T* __restrict__ dx, float* __restrict__ partial, int rows, int H,
+                                const T* __restrict__ add = nullptr) {
+  // `add` (optional, same shape as dx): the gradient arriving over the residual connection; dx_out = dx + add
+  // with dx rounded to the storage type first, i.e. exactly what a separate add kernel would have produced.
   constexpr int VN = Vec<T>::N;
   __shared__ float scratch[64];
   const int nvec = H / VN;
@@ -211,7 +214,16 @@ __global__ void __launch_bounds__(MAXT) norm_bwd_kernel(const T* __restrict__ dy
         float o[VN];
 #pragma unroll
         for (int j = 0; j < VN; ++j) o[j] = (g[i][j] - m_g - xh[i][j] * m_gx) * rstd;
-        Vec<T> ov; ov.from_float(o); ov.store(dx + size_t(row) * H + v * VN);
+        Vec<T> ov; ov.from_float(o);
+        if (add != nullptr) {
+          Vec<T> av; av.load(add + size_t(row) * H + v * VN);
+          float r[VN], a[VN];
+          ov.to_float(r); av.to_float(a);
+#pragma unroll
+          for (int j = 0; j < VN; ++j) r[j] += a[j];
+          ov.from_float(r);
+        }
+        ov.store(dx + size_t(row) * H + v * VN);
       }
     }
   }
@@ -662,8 +674,9 @@ JPB_API long long jpb_norm_bwd_scratch_elems(int rows, int H) {
   return (long long)grid * 2 * H;
 }
 
-JPB_API int jpb_norm_bwd(int layer, int dt, const void* dy, const void* x, const void* w, const float* mean,
-                         const float* rstd, void* dx, void* dw, void* db, float* scratch, int rows, int H, void* stream) {
+static int norm_bwd_impl(int layer, int dt, const void* dy, const void* x, const void* w, const float* mean,
+                         const float* rstd, void* dx, void* dw, void* db, float* scratch, int rows, int H, const void* add,
+                         void* stream) {
   return dispatch_dtype(dt, [&](auto tag) {
     using T = decltype(tag);
     constexpr int VN = Vec<T>::N;
@@ -672,19 +685,31 @@ JPB_API int jpb_norm_bwd(int layer, int dt, const void* dy, const void* x, const
     const int grid = rows < sm_count() * 2 ? rows : sm_count() * 2;
     if (threads > 512) {
       if (layer)
-        norm_bwd_kernel<T, true, 1024><<<grid, threads, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)w, mean, rstd, (T*)dx, scratch, rows, H);
+        norm_bwd_kernel<T, true, 1024><<<grid, threads, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)w, mean, rstd, (T*)dx, scratch, rows, H, (const T*)add);
       else
-        norm_bwd_kernel<T, false, 1024><<<grid, threads, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)w, nullptr, rstd, (T*)dx, scratch, rows, H);
+        norm_bwd_kernel<T, false, 1024><<<grid, threads, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)w, nullptr, rstd, (T*)dx, scratch, rows, H, (const T*)add);
     } else if (layer) {
-      norm_bwd_kernel<T, true><<<grid, threads, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)w, mean, rstd, (T*)dx, scratch, rows, H);
+      norm_bwd_kernel<T, true><<<grid, threads, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)w, mean, rstd, (T*)dx, scratch, rows, H, (const T*)add);
     } else {
-      norm_bwd_kernel<T, false><<<grid, threads, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)w, nullptr, rstd, (T*)dx, scratch, rows, H);
+      norm_bwd_kernel<T, false><<<grid, threads, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)w, nullptr, rstd, (T*)dx, scratch, rows, H, (const T*)add);
     }
     const int rt = 256;
     reduce_partials_kernel<T><<<(H + rt - 1) / rt, rt, 0, STREAM>>>(scratch, (T*)dw, grid, H, size_t(2) * H);
     if (layer) reduce_partials_kernel<T><<<(H + rt - 1) / rt, rt, 0, STREAM>>>(scratch + H, (T*)db, grid, H, size_t(2) * H);
     return LAST_ERR;
   });
+}
+
+JPB_API int jpb_norm_bwd(int layer, int dt, const void* dy, const void* x, const void* w, const float* mean,
+                         const float* rstd, void* dx, void* dw, void* db, float* scratch, int rows, int H, void* stream) {
+  return norm_bwd_impl(layer, dt, dy, x, w, mean, rstd, dx, dw, db, scratch, rows, H, nullptr, stream);
+}
+
+// Same, with the residual-path gradient `add` (shape of dx) summed into dx in the same pass.
+JPB_API int jpb_norm_bwd_add(int layer, int dt, const void* dy, const void* x, const void* w, const float* mean,
+                             const float* rstd, void* dx, void* dw, void* db, float* scratch, int rows, int H,
+                             const void* add, void* stream) {
+  return norm_bwd_impl(layer, dt, dy, x, w, mean, rstd, dx, dw, db, scratch, rows, H, add, stream);
 }
 
 JPB_API long long jpb_colsum_scratch_elems(int rows, int cols) {

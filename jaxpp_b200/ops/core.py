@@ -230,6 +230,21 @@ rmsnorm_bwd = _define(
 )
 
 
+def _rmsnorm_bwd_add_ref(dy, x, w, rstd, add):
+    dx, dw = _rmsnorm_bwd_ref(dy, x, w, rstd)
+    return dx + add, dw
+
+
+# dx + (gradient arriving over the residual connection) in the pass that produces dx; the graph rewrite in
+# compiler/peephole.py puts it in place of ``rmsnorm_bwd`` followed by ``add``
+rmsnorm_bwd_add = _define(
+    "rmsnorm_bwd_add(Tensor dy, Tensor x, Tensor w, Tensor rstd, Tensor add) -> (Tensor, Tensor)",
+    _rmsnorm_bwd_add_ref,
+    lambda dy, x, w, rstd, add: (torch.empty_like(x), torch.empty_like(w)),
+    "rmsnorm_bwd_add",
+)
+
+
 def _rmsnorm_setup(ctx, inputs, output):
     x, w, _ = inputs
     ctx.save_for_backward(x, w, output[1])
@@ -280,6 +295,19 @@ layernorm_bwd = _define(
     _layernorm_bwd_ref,
     lambda dy, x, w, mean, rstd: (torch.empty_like(x), torch.empty_like(w), torch.empty_like(w)),
     "layernorm_bwd",
+)
+
+
+def _layernorm_bwd_add_ref(dy, x, w, mean, rstd, add):
+    dx, dw, db = _layernorm_bwd_ref(dy, x, w, mean, rstd)
+    return dx + add, dw, db
+
+
+layernorm_bwd_add = _define(
+    "layernorm_bwd_add(Tensor dy, Tensor x, Tensor w, Tensor mean, Tensor rstd, Tensor add) -> (Tensor, Tensor, Tensor)",
+    _layernorm_bwd_add_ref,
+    lambda dy, x, w, mean, rstd, add: (torch.empty_like(x), torch.empty_like(w), torch.empty_like(w)),
+    "layernorm_bwd_add",
 )
 
 

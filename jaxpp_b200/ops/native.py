@@ -245,6 +245,28 @@ def rmsnorm_bwd(dy, x, w, rstd):
     return dx, dw
 
 
+def _norm_bwd_add(layer, dy, x, w, mean, rstd, add):
+    dy, x, w, add = dy.contiguous(), x.contiguous(), w.contiguous(), add.contiguous()
+    lib = load()
+    lib.jpb_norm_bwd_add.argtypes = [_c_int, _c_int] + [_c_p] * 9 + [_c_int, _c_int, _c_p, _c_p]
+    dx, dw = torch.empty_like(x), torch.empty_like(w)
+    db = torch.empty_like(w) if layer else None
+    rows, H = _rows(x), x.shape[-1]
+    scratch = norm_bwd_scratch(rows, H, x.device)
+    _check(lib.jpb_norm_bwd_add(layer, _dt(x), dy.data_ptr(), x.data_ptr(), w.data_ptr(), _p(mean), rstd.data_ptr(),
+                                dx.data_ptr(), dw.data_ptr(), _p(db), scratch.data_ptr(), rows, H, add.data_ptr(), _stream()),
+           "norm_bwd_add", 3 if layer else 2)
+    return (dx, dw, db) if layer else (dx, dw)
+
+
+def rmsnorm_bwd_add(dy, x, w, rstd, add):
+    return _norm_bwd_add(0, dy, x, w, None, rstd, add)
+
+
+def layernorm_bwd_add(dy, x, w, mean, rstd, add):
+    return _norm_bwd_add(1, dy, x, w, mean, rstd, add)
+
+
 def layernorm(x, w, b, eps):
     x = x.contiguous()
     y = torch.empty_like(x)

@@ -131,6 +131,8 @@ comm_reserved_sms = IntEnvVar("JAXPP_B200_COMM_RESERVED_SMS", 4)
 # Point-to-point backend of the multi-controller runtime on GPUs: "torch" (torch.distributed batch_isend_irecv) or
 # "native" (2-rank NCCL communicators driven through the C ABI of the native library).
 p2p_backend = StrEnvVar("JAXPP_B200_P2P", "torch")
+# Rewrite "norm backward, then add the residual-path gradient" into one kernel (compiler/peephole.py).
+fuse_norm_backward_adds = BoolEnvVar("JAXPP_B200_FUSE_NORM_BWD_ADD", True)
 # Let weight-gradient GEMMs add straight into the microbatch loop's accumulators (ops/sink.py).
 wgrad_sinks = BoolEnvVar("JAXPP_B200_WGRAD_SINKS", True)
 # Seconds a rank may go without a heartbeat before the watchdog reports it.

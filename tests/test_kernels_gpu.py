@@ -119,6 +119,22 @@ def test_activations_rope_colsum(native, dtype):
         close(merged, ops._qkv_merge_ref(*[g.float() for g in got], c, s_), **tol)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_backward_with_residual_add_rounds_like_two_kernels(native, dtype):
+    """dx + add from one kernel must equal norm_bwd followed by a separate add bit for bit."""
+    rows, H = 77, 1024
+    x, dy, add = rnd(rows, H, dtype=dtype, seed=51), rnd(rows, H, dtype=dtype, seed=52), rnd(rows, H, dtype=dtype, seed=53)
+    w, b = rnd(H, dtype=dtype, seed=54), rnd(H, dtype=dtype, seed=55)
+    _, rstd = native.rmsnorm(x, w, 1e-5)
+    dx, dw = native.rmsnorm_bwd(dy, x, w, rstd)
+    dx2, dw2 = native.rmsnorm_bwd_add(dy, x, w, rstd, add)
+    assert torch.equal(dx2, dx + add) and torch.equal(dw2, dw)
+    _, mean, rstd = native.layernorm(x, w, b, 1e-5)
+    dx, dw, db = native.layernorm_bwd(dy, x, w, mean, rstd)
+    dx2, dw2, db2 = native.layernorm_bwd_add(dy, x, w, mean, rstd, add)
+    assert torch.equal(dx2, dx + add) and torch.equal(dw2, dw) and torch.equal(db2, db)
+
+
 def test_narrow_linear_like_a_router(native):
     """A linear layer with 4 outputs (a small router): the narrow operands of its backward GEMMs are re-pitched."""
     x, w, dy = rnd(300, 256, seed=41), rnd(4, 256, scale=0.2, seed=42), rnd(300, 4, seed=43)

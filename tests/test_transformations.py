@@ -333,3 +333,33 @@ def test_weight_gradients_sink_into_the_loop_accumulators():
     eager = step(params, batch)
     assert_trees_equal(eager, got, exact=True)
     assert_trees_equal(eager, ref, exact=True)
+
+
+def test_norm_backward_absorbs_the_residual_gradient_add():
+    """Pre-norm residual blocks: ``norm_bwd`` + ``add`` is rewritten into one op; the program still matches the eager
+    step bit for bit (the fused op rounds like the two separate kernels)."""
+    from jaxpp_b200.models import lm_trainer as lt
+    from jaxpp_b200.models import transformer as tf
+
+    cfg = tf.ModelConfig("llama", vocab=128, d_model=32, n_layers=2, n_heads=2, n_kv_heads=2, ffn=64, seq=16, n_stages=2,
+                         tp=1, dtype=torch.float32)
+    sched = jp.Std1F1B(2)
+    state = lt.init_state(cfg, sched, "cpu")
+    g = torch.Generator().manual_seed(0)
+    tok, lab = torch.randint(0, 128, (2, 2, 16), generator=g), torch.randint(0, 128, (2, 2, 16), generator=g)
+    step = lt.make_train_step(cfg, sched, lt.Hyper(inplace_update=False))
+    f = jp.mpmd_jit_with_loop(step, cpu_mesh(2))
+    compiled = f.lower(state, tok, lab)
+    used = set()
+    for ins in compiled.program.instrs:
+        if isinstance(ins, RunTask):
+            used |= {str(t) for t in ins.code.targets}
+    assert "b200.rmsnorm_bwd_add.default" in used
+    assert_trees_equal(step(state, tok, lab), f(state, tok, lab), exact=True)
+    with config.fuse_norm_backward_adds.set(False):
+        plain = jp.mpmd_jit_with_loop(lt.make_train_step(cfg, sched, lt.Hyper(inplace_update=False)), cpu_mesh(2))
+        used2 = set()
+        for ins in plain.lower(state, tok, lab).program.instrs:
+            if isinstance(ins, RunTask):
+                used2 |= {str(t) for t in ins.code.targets}
+        assert "b200.rmsnorm_bwd_add.default" not in used2
