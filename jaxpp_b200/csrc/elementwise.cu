@@ -220,7 +220,7 @@ __global__ void __launch_bounds__(MAXT) norm_bwd_kernel(const T* __restrict__ dy
           float r[VN], a[VN];
           ov.to_float(r); av.to_float(a);
 #pragma unroll
-          for (int j = 0; j < VN; ++j) r[j] += a[j];
+          for (int j = 0; j < VN; ++j) r[j] = __fadd_rn(r[j], a[j]);  // never contracted into the multiply above
           ov.from_float(r);
         }
         ov.store(dx + size_t(row) * H + v * VN);
