@@ -100,3 +100,26 @@ def test_dropout_is_a_pure_function_of_seed_offset_and_index():
     xr = x.clone().requires_grad_(True)
     (g,) = torch.autograd.grad(ops.dropout(xr, 0.25, seed, 5).sum(), [xr])
     assert torch.equal(g, y)  # backward regenerates the same mask
+
+
+def test_launcher_cli_runs_modules_and_passes_arguments_through(tmp_path):
+    """``python -m jaxpp_b200.launch --nproc N (script | -m module) args...``: everything after the script or module
+    name reaches the workers untouched, every rank gets its rendezvous environment, a failing rank fails the launch."""
+    import subprocess
+    import sys
+
+    script = tmp_path / "worker.py"
+    script.write_text(
+        "import os, sys\n"
+        "out = os.path.join(sys.argv[2], 'rank%s.txt' % os.environ['RANK'])\n"
+        "open(out, 'w').write(' '.join(sys.argv[1:]) + ' ' + os.environ['WORLD_SIZE'] + ' ' + os.environ['MASTER_ADDR'])\n"
+        "sys.exit(3 if sys.argv[1] == '--fail' and os.environ['RANK'] == '1' else 0)\n")
+    cmd = [sys.executable, "-m", "jaxpp_b200.launch", "--nproc", "2", "--timeout", "60", str(script)]
+    ok = subprocess.run(cmd + ["--iters", str(tmp_path), "--flag"], capture_output=True, text=True)
+    assert ok.returncode == 0, ok.stderr
+    for r in (0, 1):
+        assert (tmp_path / f"rank{r}.txt").read_text() == f"--iters {tmp_path} --flag 2 127.0.0.1"
+    bad = subprocess.run(cmd + ["--fail", str(tmp_path)], capture_output=True, text=True)
+    assert bad.returncode == 3 and "rank 1 exited with 3" in bad.stderr
+    usage = subprocess.run([sys.executable, "-m", "jaxpp_b200.launch", "--nproc", "2"], capture_output=True, text=True)
+    assert usage.returncode == 2 and "usage" in usage.stderr
