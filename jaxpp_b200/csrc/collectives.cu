@@ -9,6 +9,13 @@
 //   phase 2  every rank copies the reduced slices out of the owners' X into its output tensor.
 // NVSwitch gives every pair full bandwidth, so the one-shot direct pattern (no ring) is used.  All waits on peer
 // flags are bounded; flags carry an increasing epoch; X is double-buffered by call parity by the caller.
+//
+// The two halves also run alone, for optimizer state sharded over the data-parallel ranks:
+//   reduce-scatter (mode 1)  phase 1 only; `out` is this rank's reduced slice [n / n_ranks] (gradient shard);
+//   all-gather     (mode 2)  every rank staged its slice at the start of X; phase 2 only, `out` is [n] (the
+//                            updated low-precision parameters, gathered from the owners of the shards).
+// A rank leaves call e+1 only after every peer has started call e+1, i.e. finished call e, so the buffer of call
+// e is no longer read by anyone when call e+2 stages into it: parity double-buffering covers all three modes.
 #include "common.cuh"
 
 namespace jpb {
@@ -17,6 +24,7 @@ constexpr int AR_MAX_RANKS = 8;
 
 struct AllReduceParams {
   int n_ranks, rank, epoch;
+  int mode;                   // 0 all-reduce, 1 reduce-scatter, 2 all-gather
   long long n;                // elements
   float scale;
   void* x[AR_MAX_RANKS];      // symmetric buffers (x[rank] is local)
@@ -78,8 +86,20 @@ __global__ void __launch_bounds__(512) allreduce_kernel(const AllReduceParams p)
   }
   if (!ar_wait_all(p.ready_local, p.n_ranks, p.rank, p.epoch, p.status, &ok_flag)) return;
 
+  if (p.mode == 2) {
+    // ---- all-gather only: every rank's slice sits at the start of its X ------------------------------------
+    for (int s = 0; s < p.n_ranks; ++s) {
+      const int q = (p.rank + s) % p.n_ranks;
+      const long long qbase = slice * q;
+      for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < slice; v += (long long)gridDim.x * blockDim.x)
+        *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out) + (qbase + v) * 16) =
+            ar_ld_v4(static_cast<const uint8_t*>(p.x[q]) + v * 16);
+    }
+    return;
+  }
   // ---- phase 1: reduce my slice -----------------------------------------------------------------------
   const long long base = slice * p.rank;
+  const long long obase = p.mode == 1 ? 0 : base;   // reduce-scatter: `out` holds the slice only
   for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < slice; v += (long long)gridDim.x * blockDim.x) {
     float acc[VN];
 #pragma unroll
@@ -102,9 +122,10 @@ __global__ void __launch_bounds__(512) allreduce_kernel(const AllReduceParams p)
       o.x = pack_bf16(acc[0] * p.scale, acc[1] * p.scale); o.y = pack_bf16(acc[2] * p.scale, acc[3] * p.scale);
       o.z = pack_bf16(acc[4] * p.scale, acc[5] * p.scale); o.w = pack_bf16(acc[6] * p.scale, acc[7] * p.scale);
     }
-    *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.x[p.rank]) + (base + v) * 16) = o;
-    *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out) + (base + v) * 16) = o;
+    if (p.mode == 0) *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.x[p.rank]) + (base + v) * 16) = o;
+    *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out) + (obase + v) * 16) = o;
   }
+  if (p.mode == 1) return;
   // ---- barrier: the last CTA of this rank publishes the slice to the peers ---------------------------------
   __threadfence_system();
   __syncthreads();
@@ -138,7 +159,10 @@ struct JpbAllReduceDesc {
   void* ctrl[8];                     // control blocks: ints [0..7] ready, [8..15] slice, [16] CTA counter
   void* out;
   int grid;
+  int mode;                          // 0 all-reduce, 1 reduce-scatter (out = slice), 2 all-gather (x = slice)
 };
+
+JPB_API int jpb_allreduce_desc_bytes() { return int(sizeof(JpbAllReduceDesc)); }
 
 JPB_API int jpb_allreduce_grid(long long n_elems, int elem_bytes) {
   int dev = 0, sms = 0;
@@ -157,8 +181,9 @@ JPB_API int jpb_allreduce(const JpbAllReduceDesc* d, void* stream) {
   if (!d || d->n_ranks < 2 || d->n_ranks > AR_MAX_RANKS) return -JPB_ERR_BAD_ARGUMENT;
   const int vn = d->dtype == 0 ? 4 : 8;
   if (d->n <= 0 || d->n % (vn * d->n_ranks) != 0) return -JPB_ERR_BAD_ARGUMENT;
+  if (d->mode < 0 || d->mode > 2) return -JPB_ERR_BAD_ARGUMENT;
   AllReduceParams p;
-  p.n_ranks = d->n_ranks; p.rank = d->rank; p.epoch = d->epoch; p.n = d->n; p.scale = d->scale;
+  p.n_ranks = d->n_ranks; p.rank = d->rank; p.epoch = d->epoch; p.n = d->n; p.scale = d->scale; p.mode = d->mode;
   for (int q = 0; q < d->n_ranks; ++q) {
     p.x[q] = d->x[q];
     int* c = static_cast<int*>(d->ctrl[q]);

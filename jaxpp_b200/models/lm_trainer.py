@@ -22,6 +22,7 @@ from .. import api as jp
 from ..core import ShapeDtypeStruct
 from ..ops import core as ops
 from ..parallel import tp as tpops
+from ..parallel import zero
 from . import transformer as tf
 
 
@@ -34,6 +35,9 @@ class Hyper:
     weight_decay: float = 0.1
     fp32_wgrad: bool = True
     inplace_update: bool = True  # the step consumes the state it is given (donation)
+    # master weights and Adam moments sharded over the data-parallel ranks (``parallel/zero.py``): the state then
+    # holds flat 1/dp slices (``shard_state_for_dp``), gradients are reduce-scattered and parameters all-gathered
+    shard_optimizer: bool = False
 
 
 def stage_of_layer(cfg: tf.ModelConfig, layer: int) -> int:
@@ -121,25 +125,57 @@ def make_train_step(cfg: tf.ModelConfig, schedule, hyper: Hyper = Hyper(), dp_ax
 
         losses, grads = jp.treduce(body, (tokens, labels), schedule=schedule)
         grads = tf.sync_replicated_grads(cfg, grads)
-        if dp_axis is not None and dp > 1:
+        sharded_update = hyper.shard_optimizer and dp_axis is not None and dp > 1
+        if dp_axis is not None and dp > 1 and not sharded_update:
             grads = tf.sync_data_parallel_grads(cfg, grads, dp_axis)
         new_step = state["step"] + 1
+        whole = _not_replicated_over(cfg, params, dp_axis) if sharded_update else None
 
-        def update(p, master, g, m, v):
+        def update(p, master, g, m, v, keep_whole=True):
+            if not keep_whole:
+                # this rank's slice of the summed gradient -> AdamW on the slice -> parameter gathered from the owners
+                g = zero.reduce_scatter_flat(g, dp_axis)
+                pm, mm, vm, lp = ops.adamw(master, g, m, v, new_step, hyper.lr, hyper.beta1, hyper.beta2, hyper.eps,
+                                           hyper.weight_decay if p.dim() > 1 else 0.0, 1.0 / total_tokens, p.dtype,
+                                           None, hyper.inplace_update)
+                return zero.all_gather_flat(lp, dp_axis, p.numel()).view(p.shape), pm, mm, vm
             pm, mm, vm, lp = ops.adamw(master, g, m, v, new_step, hyper.lr, hyper.beta1, hyper.beta2, hyper.eps,
                                        hyper.weight_decay if p.dim() > 1 else 0.0, 1.0 / total_tokens, p.dtype,
                                        p if hyper.inplace_update else None, hyper.inplace_update)
             return lp, pm, mm, vm
 
         flat_p, spec = pytree.tree_flatten(params)
-        flat = [update(p, ma, g, m, v) for p, ma, g, m, v in zip(
+        keep = pytree.tree_leaves(whole) if sharded_update else [True] * len(flat_p)
+        flat = [update(p, ma, g, m, v, k) for p, ma, g, m, v, k in zip(
             flat_p, pytree.tree_leaves(state["master"]), pytree.tree_leaves(grads), pytree.tree_leaves(state["m"]),
-            pytree.tree_leaves(state["v"]))]
+            pytree.tree_leaves(state["v"]), keep)]
         unf = lambda k: pytree.tree_unflatten([f[k] for f in flat], spec)
         new_state = {"params": unf(0), "master": unf(1), "m": unf(2), "v": unf(3), "step": new_step}
         return new_state, losses
 
     return step
+
+
+def _not_replicated_over(cfg: tf.ModelConfig, params_like: dict, axis: str | None) -> dict:
+    """Tree of booleans shaped like the parameters: True where a parameter is *not* a replica over mesh axis
+    ``axis`` (expert weights when the expert-parallel axis is that axis), so its optimizer state stays whole."""
+    own = {"e_up", "e_down"} if cfg.ep > 1 and cfg.ep_axis == axis else set()
+    return {k: ({name: {kk: kk in own for kk in ld} for name, ld in v.items()} if k == "layers" else False)
+            for k, v in params_like.items()}
+
+
+def shard_state_for_dp(cfg: tf.ModelConfig, state: dict, dp: int, dp_rank: int, dp_axis: str = "data") -> dict:
+    """The state that ``Hyper(shard_optimizer=True)`` steps take: ``master`` / ``m`` / ``v`` reduced to data-parallel
+    rank ``dp_rank``'s flat slices (parameters that are not replicated over the axis keep their full state)."""
+    whole = _not_replicated_over(cfg, state["params"], dp_axis)
+
+    def keep(path):
+        node = whole
+        for k in path:
+            node = node[k] if isinstance(node, dict) else node
+        return bool(node)
+
+    return zero.shard_optimizer_state(state, dp, dp_rank, keep)
 
 
 def param_specs(cfg: tf.ModelConfig, params_like: dict) -> dict:
@@ -161,6 +197,16 @@ def param_specs(cfg: tf.ModelConfig, params_like: dict) -> dict:
     return {k: ({name: layer(ld) for name, ld in v.items()} if k == "layers" else P()) for k, v in params_like.items()}
 
 
-def state_specs(cfg: tf.ModelConfig, state_like: dict) -> dict:
+def state_specs(cfg: tf.ModelConfig, state_like: dict, shard_optimizer_axis: str | None = None) -> dict:
+    """PartitionSpecs of the whole training state.  With ``shard_optimizer_axis`` the optimizer leaves are the flat
+    slices of ``shard_state_for_dp``: globally a 1-d array split over that axis."""
     ps = param_specs(cfg, state_like["params"])
-    return {k: (jp.PartitionSpec() if k == "step" else ps) for k in state_like}
+    if shard_optimizer_axis is None:
+        return {k: (jp.PartitionSpec() if k == "step" else ps) for k in state_like}
+    whole = _not_replicated_over(cfg, state_like["params"], shard_optimizer_axis)
+    flat = jp.PartitionSpec(shard_optimizer_axis)
+    opt = pytree.tree_unflatten(
+        [spec if w else flat for spec, w in zip(pytree.tree_leaves(ps, is_leaf=lambda x: isinstance(x, jp.PartitionSpec)),
+                                                pytree.tree_leaves(whole))],
+        pytree.tree_structure(whole))
+    return {k: (jp.PartitionSpec() if k == "step" else ps if k == "params" else opt) for k in state_like}

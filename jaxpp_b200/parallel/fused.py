@@ -144,7 +144,8 @@ def dgrad_rs(dy, w, axis):
 class _AllReduceDesc(ctypes.Structure):
     _fields_ = [("n_ranks", ctypes.c_int), ("rank", ctypes.c_int), ("epoch", ctypes.c_int), ("dtype", ctypes.c_int),
                 ("n", ctypes.c_longlong), ("scale", ctypes.c_float), ("counter_target", ctypes.c_uint),
-                ("x", ctypes.c_void_p * 8), ("ctrl", ctypes.c_void_p * 8), ("out", ctypes.c_void_p), ("grid", ctypes.c_int)]
+                ("x", ctypes.c_void_p * 8), ("ctrl", ctypes.c_void_p * 8), ("out", ctypes.c_void_p), ("grid", ctypes.c_int),
+                ("mode", ctypes.c_int)]
 
 
 class _AllReduceWorkspace:
@@ -174,17 +175,61 @@ def all_reduce_group(x: torch.Tensor, group, ranks: list, scale: float = 1.0) ->
     """scale * sum over the processes ``ranks`` (global ranks, same order everywhere) of process group ``group``:
     one kernel over NVLink peer memory (reduce-scatter + all-gather with direct peer loads).  Used for the
     gradient sync over a mesh axis and for cross-stage all-reduces (tied weights, global norms)."""
+    flat = x.contiguous().view(-1)
+    out = _peer_collective(flat, group, ranks, scale, 0)
+    return out[:flat.numel()].view(x.shape)
+
+
+def shard_numel(numel: int, n_ranks: int) -> int:
+    """Elements per rank when a flat tensor of ``numel`` elements is split over ``n_ranks`` (padded so that every
+    slice is a whole number of 16-byte vectors for 2- and 4-byte types alike)."""
+    return (numel + 8 * n_ranks - 1) // (8 * n_ranks) * 8
+
+
+def reduce_scatter_flat(x: torch.Tensor, axis: str, scale: float = 1.0) -> torch.Tensor:
+    """This rank's slice ``[shard_numel]`` of scale * sum over the ranks of ``axis`` of the flattened ``x`` (zero
+    padded): the first half of the one-kernel all-reduce, for gradients of parameters whose optimizer state is
+    sharded over the axis."""
+    from ..mesh import MpmdMesh
+
+    mesh = MpmdMesh.current()
+    ranks = [d.process_index for d in mesh.peers_along(axis)]
+    return _peer_collective(x.contiguous().view(-1), mesh.axis_group(axis), ranks, scale, 1)
+
+
+def all_gather_flat(shard: torch.Tensor, axis: str) -> torch.Tensor:
+    """Concatenation ``[n_ranks * shard.numel()]`` of every rank's flat ``shard`` (equal sizes, a multiple of 8
+    elements): the second half of the one-kernel all-reduce, for updated parameters gathered from the owners of
+    their shards."""
+    from ..mesh import MpmdMesh
+
+    mesh = MpmdMesh.current()
+    ranks = [d.process_index for d in mesh.peers_along(axis)]
+    return _peer_collective(shard.contiguous().view(-1), mesh.axis_group(axis), ranks, 1.0, 2)
+
+
+def _peer_collective(flat: torch.Tensor, group, ranks: list, scale: float, mode: int) -> torch.Tensor:
+    """mode 0: all-reduce ``flat`` -> padded [n]; 1: reduce-scatter -> [n / n_ranks]; 2: all-gather of equal
+    slices -> [n_ranks * flat.numel()]."""
     lib = _lib()
     lib.jpb_allreduce.argtypes = [ctypes.POINTER(_AllReduceDesc), ctypes.c_void_p]
     lib.jpb_allreduce_grid.argtypes = [ctypes.c_longlong, ctypes.c_int]
+    if lib.jpb_allreduce_desc_bytes() != ctypes.sizeof(_AllReduceDesc):
+        raise native.NativeError("all-reduce call descriptor layout of the native library differs from the Python binding")
     n_ranks = len(ranks)
-    if x.dtype not in (torch.float32, torch.bfloat16):
-        raise native.NativeError(f"fused all_reduce takes float32 or bfloat16, got {x.dtype}")
-    flat = x.contiguous().view(-1)
-    vn = 16 // flat.element_size()
-    quantum = vn * n_ranks
-    n = (flat.numel() + quantum - 1) // quantum * quantum
-    nbytes = n * flat.element_size()
+    if flat.dtype not in (torch.float32, torch.bfloat16):
+        raise native.NativeError(f"peer-memory collectives take float32 or bfloat16, got {flat.dtype}")
+    es = flat.element_size()
+    vn = 16 // es
+    if mode == 2:
+        if flat.numel() % vn:
+            raise native.NativeError("all_gather_flat needs slices of whole 16-byte vectors")
+        n = flat.numel() * n_ranks
+    else:
+        quantum = (8 if mode == 1 else vn) * n_ranks
+        n = (flat.numel() + quantum - 1) // quantum * quantum
+    staged = flat.numel() if mode == 2 else n        # elements of X that this call uses
+    nbytes = staged * es
     key = tuple(ranks)
     ws = _AR_WS.get(key)
     if ws is None or ws.slot < nbytes:
@@ -195,23 +240,23 @@ def all_reduce_group(x: torch.Tensor, group, ranks: list, scale: float = 1.0) ->
     ws.epoch += 1
     parity = ws.epoch & 1
     d = _AllReduceDesc()
-    d.n_ranks, d.rank, d.epoch = ws.buf.n, ws.buf.rank, ws.epoch
+    d.n_ranks, d.rank, d.epoch, d.mode = ws.buf.n, ws.buf.rank, ws.epoch, mode
     d.dtype = 0 if flat.dtype == torch.float32 else 1
     d.n, d.scale = n, float(scale)
-    d.grid = lib.jpb_allreduce_grid(n, flat.element_size())
-    ws.ctas += d.grid
+    d.grid = lib.jpb_allreduce_grid(n, es)
+    if mode == 0:
+        ws.ctas += d.grid
     d.counter_target = ws.ctas & 0xFFFFFFFF
     for q in range(ws.buf.n):
         d.ctrl[q] = ws.buf.ptrs[q]
         d.x[q] = ws.buf.ptrs[q] + ws.CTRL + parity * ws.slot
-    out = torch.empty(n, dtype=flat.dtype, device=x.device)
+    out = torch.empty(n // n_ranks if mode == 1 else n, dtype=flat.dtype, device=flat.device)
     d.out = out.data_ptr()
     stream = native._stream()
     mine = d.x[ws.buf.rank]
-    native._check(lib.jpb_memcpy_async(mine, flat.data_ptr(), flat.numel() * flat.element_size(), stream), "stage", 0)
-    if n > flat.numel():
+    native._check(lib.jpb_memcpy_async(mine, flat.data_ptr(), flat.numel() * es, stream), "stage", 0)
+    if staged > flat.numel():
         lib.jpb_memset_async.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p]
-        native._check(lib.jpb_memset_async(mine + flat.numel() * flat.element_size(), 0,
-                                           (n - flat.numel()) * flat.element_size(), stream), "pad", 0)
+        native._check(lib.jpb_memset_async(mine + flat.numel() * es, 0, (staged - flat.numel()) * es, stream), "pad", 0)
     native._check(lib.jpb_allreduce(ctypes.byref(d), stream), "jpb_allreduce")
-    return out[:flat.numel()].view(x.shape)
+    return out

@@ -37,6 +37,8 @@ def main(argv=None):
     ap.add_argument("--metrics", default=None)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--lr", type=float, default=3e-4)
+    ap.add_argument("--shard-optimizer", action="store_true",
+                    help="keep master weights and Adam moments as 1/dp slices per data-parallel rank (ZeRO stage 1)")
     args = ap.parse_args(argv)
 
     def run():
@@ -66,10 +68,13 @@ def main(argv=None):
         my_pp = mesh.my_mpmd_axis_index if multi else None
         tp_rank = mesh.axis_index("model") if multi and rc.tp > 1 else 0
         dp_rank = mesh.axis_index("data") if multi and rc.dp > 1 else 0
-        hyper = lt.Hyper(lr=args.lr, inplace_update=True)
+        sharded_opt = args.shard_optimizer and multi and rc.dp > 1
+        hyper = lt.Hyper(lr=args.lr, inplace_update=True, shard_optimizer=sharded_opt)
         step_fn = lt.make_train_step(cfg, sched, hyper, dp_axis="data" if rc.dp > 1 else None, dp=rc.dp)
         state = lt.init_state(cfg, sched, device, my_rank=my_pp, tp_rank=tp_rank + 1000 * dp_rank * (rc.ep > 1), seed=args.seed)
-        specs = lt.state_specs(cfg, state)
+        if sharded_opt:
+            state = lt.shard_state_for_dp(cfg, state, rc.dp, dp_rank)
+        specs = lt.state_specs(cfg, state, "data" if sharded_opt else None)
         jitted = jp.mpmd_jit_with_loop(step_fn, mesh, out_specs=(specs, jp.PartitionSpec()), name=rc.name)
         n_mb, mb_local = rc.n_microbatches, max(1, rc.microbatch // rc.dp)
         start, cursor = 0, 0

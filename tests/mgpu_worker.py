@@ -232,6 +232,75 @@ def scenario_moe_train_gpu():
         print("Mixtral-style step with expert parallelism: fused MoE kernels match the NCCL path", flush=True)
 
 
+def scenario_zero_gpu():
+    """Optimizer state sharded over two data-parallel GPUs.  (1) The peer-memory reduce-scatter and all-gather
+    kernels against NCCL for fp32 / bf16 and sizes that need padding.  (2) A GPT-2-style train step whose master
+    weights and moments are 1/dp slices against the same step with whole state and all-reduced gradients."""
+    from torch.utils import _pytree as pytree
+
+    from jaxpp_b200.models import lm_trainer as lt
+    from jaxpp_b200.models import transformer as tf
+    from jaxpp_b200.parallel import zero
+
+    n, r = dist.get_world_size(), dist.get_rank()
+    sched = jp.Std1F1B(1)
+    mesh = jp.MpmdMesh.create({"mpmd": 1, "data": n, "model": 1}, kind="cuda", multi_process=True)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    with mesh:
+        for dtype, numel in ((torch.float32, 1 << 20), (torch.float32, 1000003), (torch.bfloat16, 3 * 1000 * 1000 + 5)):
+            x = (torch.randn(numel, generator=torch.Generator().manual_seed(7 + r)) * 0.5).to(dev).to(dtype)
+            s = zero.shard_numel(numel, n)
+            want = torch.zeros(s * n, dtype=torch.float32, device=dev)
+            want[:numel] = x.float()
+            dist.all_reduce(want)
+            want = want * 0.25
+            got = fused.reduce_scatter_flat(x, "data", 0.25)
+            assert got.shape == (s,) and got.dtype == dtype
+            tol = 0 if dtype == torch.float32 else 2e-2
+            torch.testing.assert_close(got.float(), want[r * s:(r + 1) * s], rtol=tol, atol=tol)
+            # the op picks the same kernel
+            torch.testing.assert_close(zero.reduce_scatter_flat(x, "data", 0.25), got, rtol=0, atol=0)
+            full = fused.all_gather_flat(got, "data")
+            parts = [torch.empty_like(got) for _ in range(n)]
+            dist.all_gather(parts, got)
+            assert torch.equal(full, torch.cat(parts))
+            assert torch.equal(zero.all_gather_flat(got, "data", numel), torch.cat(parts)[:numel])
+        torch.cuda.synchronize()
+        assert native.read_status() == 0, "a peer-memory collective reported a time-out"
+        for ws in fused._AR_WS.values():
+            ws.buf.check_canaries()
+
+    cfg = tf.ModelConfig("gpt2", vocab=2048, d_model=512, n_layers=2, n_heads=8, n_kv_heads=8, ffn=2048, seq=128, n_stages=1,
+                         tp=1, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(3 + r)
+    tokens = torch.randint(0, 2048, (2, 2, 128), generator=g).to(dev)
+    labels = torch.randint(0, 2048, (2, 2, 128), generator=g).to(dev)
+    results = {}
+    for sharded in (False, True):
+        hyper = lt.Hyper(lr=1e-3, inplace_update=False, shard_optimizer=sharded)
+        state = lt.init_state(cfg, sched, dev, my_rank=0, tp_rank=0, seed=0)
+        if sharded:
+            state = lt.shard_state_for_dp(cfg, state, n, r)
+        f = jp.mpmd_jit_with_loop(lt.make_train_step(cfg, sched, hyper, dp_axis="data", dp=n), mesh)
+        state, losses = f(state, tokens, labels)
+        state, losses2 = f(state, tokens, labels)
+        torch.cuda.synchronize()
+        results[sharded] = (state, losses, losses2)
+    assert native.read_status() == 0, "a fused kernel reported a time-out"
+    is_arr = lambda a: isinstance(a, jp.MpmdArray)
+    whole, shard = results[False], results[True]
+    for a, b in zip(pytree.tree_leaves((whole[0]["params"], whole[1], whole[2]), is_leaf=is_arr),
+                    pytree.tree_leaves((shard[0]["params"], shard[1], shard[2]), is_leaf=is_arr)):
+        torch.testing.assert_close(b.local_tensor().float(), a.local_tensor().float(), rtol=1e-2, atol=2e-3)
+    for key in ("master", "m"):
+        for a, b in zip(pytree.tree_leaves(whole[0][key], is_leaf=is_arr), pytree.tree_leaves(shard[0][key], is_leaf=is_arr)):
+            want = zero.local_shard(a.local_tensor(), n, r)
+            assert b.local_tensor().shape == want.shape
+            torch.testing.assert_close(b.local_tensor(), want, rtol=1e-2, atol=2e-3 if key == "master" else 1e-4)
+    if r == 0:
+        print("sharded optimizer state: peer-memory reduce-scatter / all-gather match NCCL; train step matches", flush=True)
+
+
 def scenario_pp_tied_gpu():
     """Tied input / output embeddings on two pipeline GPUs: the two ranks' gradient contributions are summed by a
     cross-stage all-reduce, which for a tensor this large runs as the one-kernel all-reduce over peer memory;
@@ -325,6 +394,7 @@ SCENARIOS = {
     "fused_moe": scenario_fused_moe,
     "pp_tied": scenario_pp_tied_gpu,
     "moe_train": scenario_moe_train_gpu,
+    "zero": scenario_zero_gpu,
     "p2p_native": scenario_p2p_native,
     "pp2_tp2_std": lambda: scenario_pp_tp_gpu(2, 2, "std"),
     "pp2_tp2_interleaved": lambda: scenario_pp_tp_gpu(2, 2, "interleaved"),

@@ -132,10 +132,12 @@ def scenario_pp_tp(pp, tp, schedule):
         pass
 
 
-def scenario_dp_ep(family):
+def scenario_dp_ep(family, shard_optimizer=False):
     """2 pipeline ranks x 2 data-parallel ranks.  ``gpt2``: plain data parallelism (gradients all-reduced over
     the data axis); ``mixtral``: the data axis doubles as the expert-parallel axis (experts sharded, tokens
-    exchanged with all-to-all).  Oracle: the un-sharded step on the concatenated batch."""
+    exchanged with all-to-all).  ``shard_optimizer``: master weights and Adam moments are 1/dp slices per rank,
+    gradients are reduce-scattered and parameters all-gathered.  Oracle: the un-sharded step on the concatenated
+    batch."""
     pp, dp = 2, 2
     mesh = jp.MpmdMesh.create({"mpmd": pp, "data": dp, "model": 1}, kind=device().type, multi_process=True)
     dev = device()
@@ -181,7 +183,15 @@ def scenario_dp_ep(family):
         out["step"] = tree["step"].to(dev)
         return out
 
-    step = lt.make_train_step(cfgd, sched, hyper, dp_axis="data", dp=dp)
+    if shard_optimizer:
+        import dataclasses
+
+        whole_view = local_view
+        local_view = lambda tree: lt.shard_state_for_dp(cfgd, whole_view(tree), dp, me_dp)
+        hyper_d = dataclasses.replace(hyper, shard_optimizer=True)
+    else:
+        hyper_d = hyper
+    step = lt.make_train_step(cfgd, sched, hyper_d, dp_axis="data", dp=dp)
     f = jp.mpmd_jit_with_loop(step, mesh)
     half = mb // dp  # this data-parallel rank's sequences of every microbatch
     tok_l = tokens[:, me_dp * half:(me_dp + 1) * half].contiguous().to(dev)
@@ -249,6 +259,8 @@ SCENARIOS = {
     "reshard": scenario_reshard,
     "pp2_dp2_gpt2": lambda: scenario_dp_ep("gpt2"),
     "pp2_ep2_mixtral": lambda: scenario_dp_ep("mixtral"),
+    "pp2_dp2_gpt2_zero": lambda: scenario_dp_ep("gpt2", shard_optimizer=True),
+    "pp2_ep2_mixtral_zero": lambda: scenario_dp_ep("mixtral", shard_optimizer=True),
 }
 
 if __name__ == "__main__":

@@ -40,3 +40,8 @@ def test_pipeline_times_data_parallel():
 
 def test_pipeline_times_expert_parallel_moe():
     run("pp2_ep2_mixtral", 4)
+
+
+@pytest.mark.parametrize("scenario", ["pp2_dp2_gpt2_zero", "pp2_ep2_mixtral_zero"])
+def test_optimizer_state_sharded_over_data_parallel_ranks(scenario):
+    run(scenario, 4)
