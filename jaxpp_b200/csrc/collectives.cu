@@ -74,6 +74,46 @@ __device__ __forceinline__ bool ar_wait_all(const int* flags, int n_ranks, int r
   return *smem_ok != 0;
 }
 
+// Copy `count` 16-byte vectors, four loads in flight per thread (peer loads have microseconds of latency: the
+// bandwidth of a link is reached only with several MB outstanding per GPU).
+__device__ __forceinline__ void ar_copy_vec(uint8_t* dst, const uint8_t* src, long long count) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  for (; v + 3 * stride < count; v += 4 * stride) {
+    const uint4 a = ar_ld_v4(src + v * 16), b = ar_ld_v4(src + (v + stride) * 16);
+    const uint4 c = ar_ld_v4(src + (v + 2 * stride) * 16), d = ar_ld_v4(src + (v + 3 * stride) * 16);
+    *reinterpret_cast<uint4*>(dst + v * 16) = a;
+    *reinterpret_cast<uint4*>(dst + (v + stride) * 16) = b;
+    *reinterpret_cast<uint4*>(dst + (v + 2 * stride) * 16) = c;
+    *reinterpret_cast<uint4*>(dst + (v + 3 * stride) * 16) = d;
+  }
+  for (; v < count; v += stride) *reinterpret_cast<uint4*>(dst + v * 16) = ar_ld_v4(src + v * 16);
+}
+
+template <typename T>
+__device__ __forceinline__ void ar_accumulate(float* acc, const uint4& in) {
+  if constexpr (sizeof(T) == 4) {
+    acc[0] += __uint_as_float(in.x); acc[1] += __uint_as_float(in.y);
+    acc[2] += __uint_as_float(in.z); acc[3] += __uint_as_float(in.w);
+  } else {
+    const float2 a = unpack_bf16(in.x), b = unpack_bf16(in.y), c = unpack_bf16(in.z), d = unpack_bf16(in.w);
+    acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ uint4 ar_pack(const float* acc, float scale) {
+  uint4 o;
+  if constexpr (sizeof(T) == 4) {
+    o.x = __float_as_uint(acc[0] * scale); o.y = __float_as_uint(acc[1] * scale);
+    o.z = __float_as_uint(acc[2] * scale); o.w = __float_as_uint(acc[3] * scale);
+  } else {
+    o.x = pack_bf16(acc[0] * scale, acc[1] * scale); o.y = pack_bf16(acc[2] * scale, acc[3] * scale);
+    o.z = pack_bf16(acc[4] * scale, acc[5] * scale); o.w = pack_bf16(acc[6] * scale, acc[7] * scale);
+  }
+  return o;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(512) allreduce_kernel(const AllReduceParams p) {
   __shared__ int ok_flag;
@@ -90,40 +130,45 @@ __global__ void __launch_bounds__(512) allreduce_kernel(const AllReduceParams p)
     // ---- all-gather only: every rank's slice sits at the start of its X ------------------------------------
     for (int s = 0; s < p.n_ranks; ++s) {
       const int q = (p.rank + s) % p.n_ranks;
-      const long long qbase = slice * q;
-      for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < slice; v += (long long)gridDim.x * blockDim.x)
-        *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out) + (qbase + v) * 16) =
-            ar_ld_v4(static_cast<const uint8_t*>(p.x[q]) + v * 16);
+      ar_copy_vec(static_cast<uint8_t*>(p.out) + slice * q * 16, static_cast<const uint8_t*>(p.x[q]), slice);
     }
     return;
   }
   // ---- phase 1: reduce my slice -----------------------------------------------------------------------
   const long long base = slice * p.rank;
   const long long obase = p.mode == 1 ? 0 : base;   // reduce-scatter: `out` holds the slice only
-  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < slice; v += (long long)gridDim.x * blockDim.x) {
-    float acc[VN];
+  {
+    constexpr int U = 4;   // vectors per thread and pass: U loads in flight per peer
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    uint8_t* xo = static_cast<uint8_t*>(p.x[p.rank]) + base * 16;
+    uint8_t* oo = static_cast<uint8_t*>(p.out) + obase * 16;
+    for (long long v0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; v0 < slice; v0 += U * stride) {
+      float acc[U][VN];
 #pragma unroll
-    for (int j = 0; j < VN; ++j) acc[j] = 0.f;
-    for (int q = 0; q < p.n_ranks; ++q) {
-      const uint4 in = ar_ld_v4(static_cast<const uint8_t*>(p.x[q]) + (base + v) * 16);
-      if constexpr (sizeof(T) == 4) {
-        acc[0] += __uint_as_float(in.x); acc[1] += __uint_as_float(in.y);
-        acc[2] += __uint_as_float(in.z); acc[3] += __uint_as_float(in.w);
-      } else {
-        const float2 a = unpack_bf16(in.x), b = unpack_bf16(in.y), c = unpack_bf16(in.z), d = unpack_bf16(in.w);
-        acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int j = 0; j < VN; ++j) acc[u][j] = 0.f;
+      for (int q = 0; q < p.n_ranks; ++q) {
+        const uint8_t* xq = static_cast<const uint8_t*>(p.x[q]) + base * 16;
+        uint4 in[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long v = v0 + u * stride;
+          in[u] = v < slice ? ar_ld_v4(xq + v * 16) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) ar_accumulate<T>(acc[u], in[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long v = v0 + u * stride;
+        if (v < slice) {
+          const uint4 o = ar_pack<T>(acc[u], p.scale);
+          if (p.mode == 0) *reinterpret_cast<uint4*>(xo + v * 16) = o;
+          *reinterpret_cast<uint4*>(oo + v * 16) = o;
+        }
       }
     }
-    uint4 o;
-    if constexpr (sizeof(T) == 4) {
-      o.x = __float_as_uint(acc[0] * p.scale); o.y = __float_as_uint(acc[1] * p.scale);
-      o.z = __float_as_uint(acc[2] * p.scale); o.w = __float_as_uint(acc[3] * p.scale);
-    } else {
-      o.x = pack_bf16(acc[0] * p.scale, acc[1] * p.scale); o.y = pack_bf16(acc[2] * p.scale, acc[3] * p.scale);
-      o.z = pack_bf16(acc[4] * p.scale, acc[5] * p.scale); o.w = pack_bf16(acc[6] * p.scale, acc[7] * p.scale);
-    }
-    if (p.mode == 0) *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.x[p.rank]) + (base + v) * 16) = o;
-    *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out) + (obase + v) * 16) = o;
   }
   if (p.mode == 1) return;
   // ---- barrier: the last CTA of this rank publishes the slice to the peers ---------------------------------
@@ -141,10 +186,7 @@ __global__ void __launch_bounds__(512) allreduce_kernel(const AllReduceParams p)
   // ---- phase 2: gather the other ranks' reduced slices --------------------------------------------------------
   for (int s = 1; s < p.n_ranks; ++s) {
     const int q = (p.rank + s) % p.n_ranks;
-    const long long qbase = slice * q;
-    for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < slice; v += (long long)gridDim.x * blockDim.x)
-      *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out) + (qbase + v) * 16) =
-          ar_ld_v4(static_cast<const uint8_t*>(p.x[q]) + (qbase + v) * 16);
+    ar_copy_vec(static_cast<uint8_t*>(p.out) + slice * q * 16, static_cast<const uint8_t*>(p.x[q]) + slice * q * 16, slice);
   }
 }
 
