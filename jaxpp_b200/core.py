@@ -100,7 +100,18 @@ class CompiledMpmd:
     def _devices(self):
         return [sub.flat_devices[0].torch_device for sub in self.mesh.unstack]
 
-    def __call__(self, leaves: list, record_events: bool = False):
+    def __call__(self, *args, record_events: bool = False, **kwargs):
+        """Run the compiled step on the arguments it was compiled for (same pytree structure as at ``lower`` /
+        ``compile`` time, as the reference's compiled functions are called, core.py:3649-3793).  The flat list of
+        argument leaves is accepted as well."""
+        if len(args) == 2 and isinstance(args[1], bool) and not kwargs:     # (leaves, record_events)
+            args, record_events = args[:1], args[1]
+        if len(args) == 1 and not kwargs and isinstance(args[0], list) and len(args[0]) == self.n_leaves:
+            leaves = args[0]
+        else:
+            leaves, spec = pytree.tree_flatten((args, kwargs), is_leaf=_is_leaf)
+            if spec != self.in_spec:
+                raise TypeError("arguments do not have the structure this step was compiled for")
         with self.mesh:
             return self._run(leaves, record_events)
 
@@ -222,6 +233,8 @@ class MpmdFunction:
             self._dump(compiled)
         logger.info("compiled %s: %s", self.name, program.stats())
         return compiled
+
+    compile = lower   # name under which the reference's jitted functions expose it (core.py:3471)
 
     def _flat_specs(self, specs, tree, n, leaves, tensor_positions):
         out = []
