@@ -123,3 +123,35 @@ def test_launcher_cli_runs_modules_and_passes_arguments_through(tmp_path):
     assert bad.returncode == 3 and "rank 1 exited with 3" in bad.stderr
     usage = subprocess.run([sys.executable, "-m", "jaxpp_b200.launch", "--nproc", "2"], capture_output=True, text=True)
     assert usage.returncode == 2 and "usage" in usage.stderr
+
+
+def test_optimizer_state_slices_cover_a_parameter_exactly_once():
+    """Flat 1/n slices of a parameter (``parallel/zero.py``): padded to whole 16-byte vectors for 2- and 4-byte types,
+    their concatenation restores the parameter, and placeholders of other pipeline ranks get the slice shape."""
+    import torch
+
+    import jaxpp_b200 as jp
+    from jaxpp_b200.parallel import zero
+
+    for numel, n in ((1, 2), (8, 2), (17, 4), (1000003, 8), (4096 * 4096, 4)):
+        s = zero.shard_numel(numel, n)
+        assert s % 8 == 0 and s * n >= numel and (s - 8) * n < numel
+    t = torch.arange(37.0).view(37, 1)
+    parts = [zero.local_shard(t, 4, r) for r in range(4)]
+    assert all(p.shape == (16,) for p in parts)
+    whole = torch.cat(parts)
+    assert torch.equal(whole[:37], t.view(-1)) and whole[37:].abs().sum() == 0
+    state = {"params": {"w": t}, "master": {"w": t.clone(), "e": jp.ShapeDtypeStruct((5, 3), torch.float32)},
+             "m": {"w": torch.zeros_like(t), "e": jp.ShapeDtypeStruct((5, 3), torch.float32)},
+             "v": {"w": torch.zeros_like(t), "e": jp.ShapeDtypeStruct((5, 3), torch.float32)}, "step": torch.zeros(())}
+    sharded = zero.shard_optimizer_state(state, 4, 1, keep=lambda path: False)
+    assert torch.equal(sharded["master"]["w"], parts[1]) and sharded["m"]["e"].shape == (8,)
+    assert sharded["params"]["w"] is t                                    # the compute copy stays whole
+    kept = zero.shard_optimizer_state(state, 4, 1, keep=lambda path: path == ("w",))
+    assert kept["master"]["w"].shape == (37, 1)
+    # outside a mesh axis of size > 1 the ops are the identity on the padded flat tensor
+    mesh = jp.MpmdMesh.create({"mpmd": 1, "data": 1, "model": 1}, kind="cpu", multi_process=False)
+    with mesh:
+        flat = zero.reduce_scatter_flat(t, "data", 0.5)
+        assert flat.shape == (40,) and torch.equal(flat[:37], t.view(-1) * 0.5)
+        assert torch.equal(zero.all_gather_flat(flat, "data", 37), t.view(-1) * 0.5)
