@@ -155,3 +155,54 @@ def test_optimizer_state_slices_cover_a_parameter_exactly_once():
         flat = zero.reduce_scatter_flat(t, "data", 0.5)
         assert flat.shape == (40,) and torch.equal(flat[:37], t.view(-1) * 0.5)
         assert torch.equal(zero.all_gather_flat(flat, "data", 37), t.view(-1) * 0.5)
+
+
+def test_public_api_names():
+    """Every name of the reference's façade (src/jaxpp/api.py:19-65) is importable from the package root and from
+    ``jaxpp_b200.api``, with the call shapes its users rely on."""
+    import inspect
+
+    import jaxpp_b200 as jp
+    from jaxpp_b200 import api
+
+    names = ["mpmd_jit_with_loop", "mpmd_jit_by_yield", "treduce", "treduce_i", "Add", "Max", "Concat", "mark_stage_end",
+             "pipeline_enter_stage", "MpmdMesh", "MpmdArray", "MpmdSharding", "BaseSchedule", "Std1F1B", "Eager1F1B",
+             "Interleaved1F1B", "KimiK2", "ZeroBubble", "DualPipeV", "cross_mpmd_all_reduce", "cross_mpmd_stack", "place_with",
+             "spmd_to_mpmd_reshard", "mpmd_to_spmd_reshard", "collect_task_times_ms", "_to_global_jax_array"]
+    for n in names:
+        assert hasattr(api, n), n
+        assert getattr(jp, n) is getattr(api, n), n
+    for jit in (jp.mpmd_jit_with_loop, jp.mpmd_jit_by_yield):
+        params = inspect.signature(jit).parameters
+        assert list(params)[:2] == ["fun", "mpmd_mesh"]
+        for kw in ("in_shardings", "out_shardings", "static_argnums", "static_argnames", "donate_argnums", "donate_argnames",
+                   "compiler_options"):
+            assert params[kw].kind is inspect.Parameter.KEYWORD_ONLY, kw
+    assert list(inspect.signature(jp.treduce).parameters)[:2] == ["fun", "xs"]
+    assert {"schedule", "operation"} <= set(inspect.signature(jp.treduce).parameters)
+    assert issubclass(jp.Std1F1B, jp.BaseSchedule) and jp.Interleaved1F1B(4, 2).num_stages == 4
+    from jaxpp_b200.launch import distributed_main  # the bootstrap entry point of distributed_utils.py:51-54
+
+    assert callable(distributed_main)
+
+
+def test_collect_task_times_ms_records_every_task():
+    """Inside the context every task run adds one sample under its name (reference: prim.py:704-859); outside, and
+    with ``enabled=False``, nothing is recorded."""
+    import torch
+
+    import jaxpp_b200 as jp
+    from helpers import make_mlp_step, mlp_params
+
+    mesh = jp.MpmdMesh.create({"mpmd": 2, "data": 1, "model": 1}, kind="cpu", multi_process=False)
+    f = jp.mpmd_jit_with_loop(make_mlp_step(2, jp.Std1F1B(2), 3), mesh)
+    params, batch = mlp_params(2, 8), torch.randn(3, 2, 8)
+    f(params, batch)
+    with jp.collect_task_times_ms() as times:
+        f(params, batch)
+    fwd = [k for k in times if k.startswith("fwd")]
+    bwd = [k for k in times if k.startswith("bwd")]
+    assert len(fwd) == 6 and len(bwd) == 6 and all(len(v) == 1 and v[0] >= 0 for v in times.values())
+    with jp.collect_task_times_ms(enabled=False) as nothing:
+        f(params, batch)
+    assert nothing is None
