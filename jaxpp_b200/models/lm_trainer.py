@@ -38,6 +38,8 @@ class Hyper:
     # master weights and Adam moments sharded over the data-parallel ranks (``parallel/zero.py``): the state then
     # holds flat 1/dp slices (``shard_state_for_dp``), gradients are reduce-scattered and parameters all-gathered
     shard_optimizer: bool = False
+    # clip the gradient to this global L2 norm (over every pipeline stage, tensor- / expert-parallel shard); None = off
+    clip_grad_norm: float | None = None
 
 
 def stage_of_layer(cfg: tf.ModelConfig, layer: int) -> int:
@@ -130,11 +132,22 @@ def make_train_step(cfg: tf.ModelConfig, schedule, hyper: Hyper = Hyper(), dp_ax
             grads = tf.sync_data_parallel_grads(cfg, grads, dp_axis)
         new_step = state["step"] + 1
         whole = _not_replicated_over(cfg, params, dp_axis) if sharded_update else None
+        flat_p, spec = pytree.tree_flatten(params)
+        flat_g = pytree.tree_leaves(grads)
+        keep = pytree.tree_leaves(whole) if sharded_update else [True] * len(flat_p)
+        if sharded_update:
+            # this rank's slice of the summed gradient (parameters that are not replicas over the axis keep theirs)
+            flat_g = [g if k else zero.reduce_scatter_flat(g, dp_axis) for g, k in zip(flat_g, keep)]
+        clip = None
+        if hyper.clip_grad_norm is not None:
+            clip = _clip_coefficient(cfg, schedule, params, flat_g, keep, dp_axis if dp > 1 else None,
+                                     hyper.clip_grad_norm, 1.0 / total_tokens)
 
         def update(p, master, g, m, v, keep_whole=True):
+            if clip is not None:
+                g = g * clip.to(g.dtype)
             if not keep_whole:
-                # this rank's slice of the summed gradient -> AdamW on the slice -> parameter gathered from the owners
-                g = zero.reduce_scatter_flat(g, dp_axis)
+                # AdamW on the slice -> bf16 slice -> parameter gathered from the owners of the slices
                 pm, mm, vm, lp = ops.adamw(master, g, m, v, new_step, hyper.lr, hyper.beta1, hyper.beta2, hyper.eps,
                                            hyper.weight_decay if p.dim() > 1 else 0.0, 1.0 / total_tokens, p.dtype,
                                            None, hyper.inplace_update)
@@ -144,16 +157,56 @@ def make_train_step(cfg: tf.ModelConfig, schedule, hyper: Hyper = Hyper(), dp_ax
                                        p if hyper.inplace_update else None, hyper.inplace_update)
             return lp, pm, mm, vm
 
-        flat_p, spec = pytree.tree_flatten(params)
-        keep = pytree.tree_leaves(whole) if sharded_update else [True] * len(flat_p)
         flat = [update(p, ma, g, m, v, k) for p, ma, g, m, v, k in zip(
-            flat_p, pytree.tree_leaves(state["master"]), pytree.tree_leaves(grads), pytree.tree_leaves(state["m"]),
+            flat_p, pytree.tree_leaves(state["master"]), flat_g, pytree.tree_leaves(state["m"]),
             pytree.tree_leaves(state["v"]), keep)]
         unf = lambda k: pytree.tree_unflatten([f[k] for f in flat], spec)
         new_state = {"params": unf(0), "master": unf(1), "m": unf(2), "v": unf(3), "step": new_step}
         return new_state, losses
 
     return step
+
+
+def _clip_coefficient(cfg: tf.ModelConfig, schedule, params: dict, flat_g: list, whole: list, dp_axis: str | None,
+                      max_norm: float, grad_scale: float) -> torch.Tensor:
+    """min(1, max_norm / ||grad_scale * g||) over the whole model, as a scalar that lives on every pipeline rank.
+
+    Squares are summed per pipeline rank first; parts held as shards are completed over their axis (tensor-parallel
+    weights over the model axis, experts over the expert axis, optimizer-state slices over the data axis; replicas
+    count once); the per-rank sums meet in one cross-stage all-reduce (what the reference's users do with
+    ``cross_mpmd_all_reduce`` for the global gradient norm, api.py:48-54)."""
+    owners = owner_ranks(cfg, schedule)
+    tp_sharded = {"wqkv", "w_up", "b_qkv", "b_up", "wo", "w_down"} if cfg.tp > 1 else set()
+    ep_sharded = {"e_up", "e_down"} if cfg.ep > 1 else set()
+    paths = []   # (owner rank, parameter name) in flattening order
+    for k, v in params.items():
+        if k == "layers":
+            for name, ld in v.items():
+                paths.extend((owners[int(name)], kk) for kk in ld)
+        else:
+            paths.append((owners["embed" if k in ("embed", "pos") else "head"], k))
+    assert len(paths) == len(flat_g)
+    groups: dict = {}  # (rank, axes to complete over) -> sum of squares
+    for (rank, name), g, keep_whole in zip(paths, flat_g, whole):
+        axes = []
+        if name in tp_sharded:
+            axes.append(cfg.tp_axis)
+        if name in ep_sharded:
+            axes.append(cfg.ep_axis)
+        elif not keep_whole:
+            axes.append(dp_axis)      # a 1/dp slice of a replicated parameter's gradient
+        sq = g.float().pow(2).sum()
+        key = (rank, tuple(dict.fromkeys(axes)))
+        groups[key] = sq if key not in groups else groups[key] + sq
+    per_rank: dict = {}
+    for (rank, axes), sq in groups.items():
+        for axis in axes:
+            sq = tpops.all_reduce(sq.reshape(1), axis).reshape(())
+        per_rank[rank] = sq if rank not in per_rank else per_rank[rank] + sq
+    parts = [per_rank[r] for r in sorted(per_rank)]
+    total = jp.cross_mpmd_all_reduce(*parts) if len(parts) > 1 else parts[0]
+    norm = total.sqrt() * grad_scale
+    return torch.clamp(max_norm / (norm + 1e-6), max=1.0)
 
 
 def _not_replicated_over(cfg: tf.ModelConfig, params_like: dict, axis: str | None) -> dict:

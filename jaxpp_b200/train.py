@@ -37,6 +37,7 @@ def main(argv=None):
     ap.add_argument("--metrics", default=None)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--lr", type=float, default=3e-4)
+    ap.add_argument("--clip-grad-norm", type=float, default=None, help="clip gradients to this global L2 norm")
     ap.add_argument("--shard-optimizer", action="store_true",
                     help="keep master weights and Adam moments as 1/dp slices per data-parallel rank (ZeRO stage 1)")
     args = ap.parse_args(argv)
@@ -69,7 +70,7 @@ def main(argv=None):
         tp_rank = mesh.axis_index("model") if multi and rc.tp > 1 else 0
         dp_rank = mesh.axis_index("data") if multi and rc.dp > 1 else 0
         sharded_opt = args.shard_optimizer and multi and rc.dp > 1
-        hyper = lt.Hyper(lr=args.lr, inplace_update=True, shard_optimizer=sharded_opt)
+        hyper = lt.Hyper(lr=args.lr, inplace_update=True, shard_optimizer=sharded_opt, clip_grad_norm=args.clip_grad_norm)
         step_fn = lt.make_train_step(cfg, sched, hyper, dp_axis="data" if rc.dp > 1 else None, dp=rc.dp)
         state = lt.init_state(cfg, sched, device, my_rank=my_pp, tp_rank=tp_rank + 1000 * dp_rank * (rc.ep > 1), seed=args.seed)
         if sharded_opt:

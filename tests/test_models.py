@@ -138,3 +138,25 @@ def test_activation_recompute_matches_and_moves_forward_ops_into_backward():
     # and the forward task hands fewer activations to the backward task
     fwd = lambda prog: next(i for i in prog.instrs if isinstance(i, RunTask) and i.name == "fwd_1__0")
     assert len(fwd(progs[1]).outs) < len(fwd(progs[0]).outs)
+
+
+@pytest.mark.parametrize("family,schedule,tied", [
+    ("llama", jp.Interleaved1F1B(4, 2), False), ("gpt2", jp.Std1F1B(2), True), ("llama", jp.ZeroBubble(2), False),
+])
+def test_gradient_clipping_by_global_norm(family, schedule, tied):
+    """``Hyper.clip_grad_norm``: per-rank sums of squares meet in a cross-stage all-reduce; the first Adam moment after
+    one step is (1 - beta1) * clipped gradient, so its norm shows the threshold."""
+    cfg = tf.ModelConfig(family, vocab=250, d_model=64, n_layers=4, n_heads=4, n_kv_heads=2 if family == "llama" else 4,
+                         ffn=128, seq=32, n_stages=schedule.num_stages, dtype=torch.float32, tie_embeddings=tied)
+    g = torch.Generator().manual_seed(5)
+    tokens = torch.randint(0, cfg.vocab, (4, 2, cfg.seq), generator=g)
+    labels = torch.randint(0, cfg.vocab, (4, 2, cfg.seq), generator=g)
+    norms = {}
+    for clip in (None, 0.05):
+        step = lt.make_train_step(cfg, schedule, lt.Hyper(lr=1e-2, inplace_update=False, clip_grad_norm=clip))
+        state = lt.init_state(cfg, schedule, "cpu")
+        ref_state, _ = step(state, tokens, labels)
+        got_state, _ = jp.mpmd_jit_with_loop(step, cpu_mesh(2))(state, tokens, labels)
+        assert_trees_equal(ref_state, got_state, exact=not tied, rtol=1e-5, atol=1e-6)
+        norms[clip] = float(torch.cat([t.reshape(-1) for t in pytree.tree_leaves(ref_state["m"])]).norm() / (1 - 0.9))
+    assert norms[None] > 0.5 and abs(norms[0.05] - 0.05) < 1e-4

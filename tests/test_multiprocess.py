@@ -10,8 +10,8 @@ from jaxpp_b200.launch import launch
 WORKER = os.path.join(os.path.dirname(os.path.abspath(__file__)), "mp_worker.py")
 
 
-def run(scenario, nproc):
-    rc = launch([WORKER, scenario], nproc, env={"CUDA_VISIBLE_DEVICES": "", "OMP_NUM_THREADS": "1"}, timeout_s=300)
+def run(scenario, nproc, **extra_env):
+    rc = launch([WORKER, scenario], nproc, env={"CUDA_VISIBLE_DEVICES": "", "OMP_NUM_THREADS": "1", **extra_env}, timeout_s=300)
     assert rc == 0, f"scenario {scenario} failed with exit code {rc}"
 
 
@@ -45,3 +45,10 @@ def test_pipeline_times_expert_parallel_moe():
 @pytest.mark.parametrize("scenario", ["pp2_dp2_gpt2_zero", "pp2_ep2_mixtral_zero"])
 def test_optimizer_state_sharded_over_data_parallel_ranks(scenario):
     run(scenario, 4)
+
+
+@pytest.mark.parametrize("scenario", ["pp2_tp2", "pp2_dp2_gpt2_zero", "pp2_ep2_mixtral"])
+def test_gradient_clipping_by_global_norm_across_stages_and_shards(scenario):
+    """The clip coefficient needs the norm over every pipeline stage and every tensor- / expert-parallel shard or
+    optimizer-state slice; the oracle is the un-sharded, un-pipelined step with the same (active) threshold."""
+    run(scenario, 4, TEST_CLIP="0.05")

@@ -29,7 +29,7 @@ def test_train_driver_with_sharded_optimizer_state(tmp_path):
     slices are checkpointed as one global 1-d array split over the data axis, and the run resumes from them."""
     ck = str(tmp_path / "ckpt")
     base = ["-m", "jaxpp_b200.train", "--config", "gpt2xl_pp2dp4", "--tiny", "--device", "cpu", "--ckpt-dir", ck,
-            "--ckpt-every", "1", "--lr", "0.01", "--shard-optimizer"]
+            "--ckpt-every", "1", "--lr", "0.01", "--shard-optimizer", "--clip-grad-norm", "1.0"]
     env = {"CUDA_VISIBLE_DEVICES": "", "OMP_NUM_THREADS": "1",
            "PYTHONPATH": os.path.dirname(os.path.dirname(os.path.abspath(__file__)))}
     assert launch(base + ["--steps", "1"], 8, env=env, timeout_s=300) == 0
