@@ -426,6 +426,27 @@ def _min_free_memory(devices: Iterable[Device]) -> float:
     return free
 
 
+def logically_stacked(array: DistArray, comm_mesh: Mesh, mesh_axis_name: str, array_axis: int = 0,
+                      strict: bool = False) -> DistArray:
+    """View the per-rank copies of ``array`` as one array over ``comm_mesh`` with a new dimension at ``array_axis``
+    that is split over ``mesh_axis_name`` (one entry per pipeline rank); no data moves: every addressable shard gains
+    a dimension of size 1 (reference: array.py:553-600).
+
+    With ``strict`` the spec must not mention ``mesh_axis_name`` already; otherwise that axis is dropped from it."""
+    spec = array.sharding.spec
+    mentioned = any(mesh_axis_name == e or (isinstance(e, tuple) and mesh_axis_name in e) for e in spec)
+    if strict:
+        assert not mentioned, f"axis_name {mesh_axis_name!r} already exists in spec {spec}"
+    else:
+        spec = filter_axes(spec, {mesh_axis_name})
+    entries = list(spec) + [None] * (len(array.shape) - len(spec))
+    new_spec = PartitionSpec(*entries[:array_axis], mesh_axis_name, *entries[array_axis:])
+    n = comm_mesh.shape[mesh_axis_name]
+    shape = (*array.shape[:array_axis], n, *array.shape[array_axis:])
+    shards = {d: (None if t is None else t.unsqueeze(array_axis)) for d, t in array.shards.items()}
+    return DistArray(shards, NamedSharding(comm_mesh, new_spec), shape, array.dtype)
+
+
 def spmd_to_mpmd_reshard(mpmd_mesh: MpmdMesh, spmd_arrays: Any, mpmd_shardings: Any, threshold: float | None = None,
                          donate: bool = True) -> Any:
     """Move arrays sharded over the *whole* mesh (stage axis included) to the pipeline ranks that use

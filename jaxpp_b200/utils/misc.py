@@ -95,3 +95,50 @@ def unique_in_order(xs: Iterable[A]) -> list[A]:
             seen.add(x)
             out.append(x)
     return out
+
+
+def _device_memory_lines() -> list[str]:
+    import torch
+
+    lines = []
+    if not torch.cuda.is_available():
+        return lines
+    for i in range(torch.cuda.device_count()):
+        free, limit = torch.cuda.mem_get_info(i)
+        stats = torch.cuda.memory_stats(i)
+        used = (limit - free) / 2 ** 30
+        peak = stats.get("allocated_bytes.all.peak", 0) / 2 ** 30
+        lines.append(f"\tUsing (GiB) {used:.2f} / {limit / 2 ** 30:.2f} ({used / (limit / 2 ** 30):.1%}) "
+                     f"(peak allocated {peak:.2f} GiB) on cuda:{i}")
+    return lines
+
+
+@contextlib.contextmanager
+def print_memstats(label: str, enabled: bool = False):
+    """Print the device memory in use, its limit and the allocator's peak for every visible GPU before and after the
+    ``with`` body (reference: utils.py:241-268).  Off unless ``enabled``; prints only the labels without a GPU."""
+    if not enabled:
+        yield
+        return
+    print(f"\nBefore: {label}:")
+    for line in _device_memory_lines():
+        print(line, flush=True)
+    yield
+    print(f"\nAfter: {label}:")
+    for line in _device_memory_lines():
+        print(line, flush=True)
+
+
+def updated_named_sharding_mesh(shardings, new_mesh):
+    """The same partition specs over ``new_mesh``: ``None`` entries pass through (reference: utils.py:223-238)."""
+    from ..mesh import NamedSharding
+
+    out = []
+    for s in shardings:
+        if s is None:
+            out.append(None)
+            continue
+        if not isinstance(s, NamedSharding):
+            raise TypeError(f"expected a NamedSharding or None, got {type(s).__name__}")
+        out.append(NamedSharding(new_mesh, s.spec))
+    return out

@@ -105,3 +105,27 @@ def test_reshard_plan_between_different_mesh_shapes():
     from jaxpp_b200.array import reshard
 
     torch.testing.assert_close(reshard(DistArray.from_global(x, src), dst).to_global(), x)
+
+
+def test_logically_stacked_view_over_the_whole_mesh():
+    """Per-rank copies of an array seen as one array with a leading stage dimension split over the stage axis
+    (reference: array.py:553-600): no data moves, the global view stacks the ranks' values."""
+    from jaxpp_b200.array import logically_stacked
+
+    mesh = mesh_3x2()
+    xs = [torch.arange(24.0).reshape(4, 6) + 100 * i for i in range(3)]
+    whole = mesh.jax_mesh
+    shards = {}
+    for i in range(3):
+        shards.update(local_array(mesh, i, xs[i], P("data", None)).shards)
+    per_rank = DistArray(shards, NamedSharding(mesh.unstack[0], P("data", None)), (4, 6))
+    stacked = logically_stacked(per_rank, whole, "mpmd")
+    assert stacked.shape == (3, 4, 6) and stacked.spec == P("mpmd", "data", None)
+    torch.testing.assert_close(stacked.to_global(), torch.stack(xs))
+    for d, t in stacked.shards.items():
+        assert t.data_ptr() == shards[d].data_ptr()        # a view: nothing was copied
+    inner = logically_stacked(per_rank, whole, "mpmd", array_axis=1)
+    assert inner.shape == (4, 3, 6) and inner.spec == P("data", "mpmd", None)
+    torch.testing.assert_close(inner.to_global(), torch.stack(xs, dim=1))
+    with pytest.raises(AssertionError, match="already exists"):
+        logically_stacked(DistArray(shards, NamedSharding(whole, P("mpmd", None)), (6, 6)), whole, "mpmd", strict=True)

@@ -206,3 +206,22 @@ def test_collect_task_times_ms_records_every_task():
     with jp.collect_task_times_ms(enabled=False) as nothing:
         f(params, batch)
     assert nothing is None
+
+
+def test_memstats_and_sharding_mesh_helpers(capsys):
+    """``print_memstats`` is silent unless enabled and brackets the body with labelled reports; shardings are
+    re-pointed at another mesh with their specs unchanged (reference: utils.py:223-268)."""
+    import jaxpp_b200 as jp
+    from jaxpp_b200.utils.misc import print_memstats, updated_named_sharding_mesh
+
+    with print_memstats("quiet"):
+        pass
+    assert capsys.readouterr().out == ""
+    with print_memstats("optimizer step", enabled=True):
+        print("body")
+    out = capsys.readouterr().out
+    assert out.index("Before: optimizer step") < out.index("body") < out.index("After: optimizer step")
+    a = jp.MpmdMesh.create({"mpmd": 1, "data": 2, "model": 1}, kind="cpu", multi_process=False).jax_mesh
+    b = jp.MpmdMesh.create({"mpmd": 1, "data": 2, "model": 1}, kind="cpu", multi_process=False).jax_mesh
+    moved = updated_named_sharding_mesh([jp.NamedSharding(a, jp.P("data")), None], b)
+    assert moved[1] is None and moved[0].mesh is b and moved[0].spec == jp.P("data")
