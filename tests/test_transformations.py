@@ -363,3 +363,109 @@ def test_norm_backward_absorbs_the_residual_gradient_add():
             if isinstance(ins, RunTask):
                 used2 |= {str(t) for t in ins.code.targets}
         assert "b200.rmsnorm_bwd_add.default" not in used2
+
+
+def test_loop_body_constant_needs_the_relaxed_clustering_flag():
+    """A value made inside the loop body that neither depends on nor feeds a stage (a literal returned next to the
+    loss) is refused under conservative clustering and joins the last cluster with the flag off; custom reduction
+    ops per output (the case of the reference's tests/test_transformations.py:218-251)."""
+    g = torch.Generator().manual_seed(7)
+    sched = jp.Std1F1B(1)
+    w, X, Y = torch.rand(10, 10, generator=g), torch.rand(2, 10, generator=g), torch.rand(2, 10, generator=g)
+
+    def step(w, X, Y):
+        def body(d):
+            x, y = d
+            loss, grad = jp.value_and_grad(lambda w: ((jp.mark_stage_end(w @ x) - y) ** 2).mean())(w)
+            return loss, grad, torch.tensor(1.0)
+
+        return jp.treduce(body, (X, Y), schedule=sched, operation=(jp.Concat(), jp.Add, jp.Add))
+
+    ref = step(w, X, Y)
+    with pytest.raises(AssertionError, match="neither depends on nor feeds"):
+        jp.mpmd_jit_with_loop(step, cpu_mesh(1))(w, X, Y)
+    with config.conservative_loop_clustering.set(False):
+        got = jp.mpmd_jit_with_loop(step, cpu_mesh(1))(w, X, Y)
+    assert_trees_equal(ref, got, exact=True)
+    assert float(local(got[2])) == 2.0
+
+
+def test_parallel_branches_each_end_a_stage():
+    """Two stages that both read the microbatch and do not depend on each other, merged by a third; the step also
+    returns a Python constant and passes an input through (the case of the reference's
+    tests/test_transformations.py:254-322)."""
+    g = torch.Generator().manual_seed(7)
+    sched = jp.Eager1F1B(3)
+    ws = tuple(torch.rand(10, 10, generator=g) for _ in range(3))
+    X, Y = torch.rand(5, 10, generator=g), torch.rand(5, 10, generator=g)
+
+    def predict(params, x):
+        w1, w2, w3 = params
+        a = jp.mark_stage_end(w1 @ x)
+        b = jp.mark_stage_end(w2 @ x)
+        return jp.mark_stage_end(w3 @ (a + b))
+
+    def step(params, X, Y):
+        def body(d):
+            x, y = d
+            return jp.value_and_grad(lambda p: ((predict(p, x) - y) ** 2).mean())(params)
+
+        losses, grads = jp.treduce(body, (X, Y), schedule=sched)
+        return (losses, pytree.tree_map(lambda p, gg: p - 0.1 * gg, params, grads)), 5, X
+
+    ref = step(ws, X, Y)
+    f = jp.mpmd_jit_with_loop(step, cpu_mesh(3))
+    got = f(ws, X, Y)
+    assert got[1] == 5
+    assert_trees_equal((ref[0], ref[2]), (got[0], got[2]), exact=False, rtol=1e-5, atol=1e-6)
+    verify_program(f.lower(ws, X, Y).program)
+
+
+def _marked_mlp(params, x):
+    first_stage_output = None
+    for i, (w, b) in enumerate(params):
+        if i == 1:
+            first_stage_output = x
+        x = jp.mark_stage_end(torch.tanh(x @ w + b))
+    return x, first_stage_output
+
+
+def _late_param(p, X):
+    return _marked_mlp(p, X)[0] + p[1][1]
+
+
+def _early_value(p, X):
+    return _marked_mlp(p, X)[1] + p[1][1]
+
+
+def _select(p, X):
+    preds, early = _marked_mlp(p, X)
+    picked = torch.where((preds < 0).any(), early, early * 2 + torch.zeros_like(early))
+    return picked + p[0][1]
+
+
+@pytest.mark.parametrize("fn,rank", [(_late_param, 3), (_early_value, 0), (_select, 3)])
+def test_forward_only_pipeline_with_values_used_across_stages(fn, rank):
+    """Forward-only pipelines whose result uses a parameter of an earlier stage after the last marker, returns a
+    value of the first stage, or selects between stages' values (the cases of the reference's
+    tests/test_transformations.py:331-435); the result lives on the rank that computes it."""
+    g = torch.Generator().manual_seed(3)
+    params = [(torch.rand(10, 10, generator=g), torch.rand(10, generator=g)) for _ in range(4)]
+    X = torch.rand(6, 10, generator=g)
+    got = jp.mpmd_jit_by_yield(fn, cpu_mesh(4))(params, X)
+    torch.testing.assert_close(local(got), fn(params, X), rtol=1e-6, atol=1e-6)
+    assert got.mpmd_idxs == (rank,)
+
+
+def test_loop_without_after_loop_computation():
+    """The step returns the reduced values as they are: nothing runs after the loop."""
+    sched = jp.Eager1F1B(3)
+    params, batch = mlp_params(3, 8), torch.randn(5, 2, 8, generator=torch.Generator().manual_seed(2))
+
+    def step(params, batch):
+        def body(mb):
+            return jp.value_and_grad(lambda p: ((mlp_forward(p, mb, 3) - mb) ** 2).mean())(params)
+
+        return jp.treduce(body, batch, schedule=sched)
+
+    assert_trees_equal(step(params, batch), jp.mpmd_jit_with_loop(step, cpu_mesh(3))(params, batch), exact=True)
