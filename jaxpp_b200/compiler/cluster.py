@@ -116,6 +116,19 @@ def find_loop(graph: fx.Graph) -> LoopRegions | None:
             body.append(n)
             body_set.add(n)
     out_nodes = list(end.args[0])
+    # a microbatch slice (or the index) returned as it is: give it a node of its own in the body, so that it has a
+    # producing task like every other loop output (it joins the first stage, which reads the microbatch anyway)
+    if any(o in sources for o in out_nodes):
+        for k, o in enumerate(out_nodes):
+            if o in sources:
+                with graph.inserting_before(end):
+                    copy = graph.call_function(aten.clone.default, (o,))
+                copy.meta.update({key: o.meta[key] for key in ("val", "tensor_meta") if key in o.meta})
+                copy.meta["pp_passthrough"] = True
+                out_nodes[k] = copy
+                body.append(copy)
+        end.args = (out_nodes, *end.args[1:])
+        out_nodes = list(end.args[0])
     results = {u.args[1]: u for u in end.users}
     return LoopRegions(
         begin, index, end, end.args[3], begin.args[1] if begin is not None else 0, slice_of,
@@ -201,6 +214,8 @@ def cluster_stages(region: Sequence[fx.Node], get_rank, mpmd_dim: int) -> tuple[
             continue
         if is_marker(m, "place_with") and m.args[1] in assign:
             c = assign[m.args[1]]
+        elif m.meta.get("pp_passthrough"):
+            c = 0
         else:
             cs = [assign[i] for i in m.all_input_nodes if i in assign]
             c = max(cs) if cs else None

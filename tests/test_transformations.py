@@ -469,3 +469,41 @@ def test_loop_without_after_loop_computation():
         return jp.treduce(body, batch, schedule=sched)
 
     assert_trees_equal(step(params, batch), jp.mpmd_jit_with_loop(step, cpu_mesh(3))(params, batch), exact=True)
+
+
+@pytest.mark.parametrize("pp", [1, 2])
+def test_microbatch_inputs_passed_through_the_loop(pp):
+    """The body returns its own inputs next to the loss (stacked over microbatches again by ``Concat``), one of them
+    also used after the last marker (the case of the reference's tests/functional_testing/test_passthrough_vars.py:
+    36-75)."""
+    g = torch.Generator().manual_seed(1)
+    ws = [torch.randn(100, 100, generator=g) * 0.1 for _ in range(4)]
+    X, Yin = torch.randn(3, 10, 100, generator=g), torch.randn(3, 10, 100, generator=g)
+    T = torch.randint(0, 100, (3, 10), generator=g)
+    sched = jp.Std1F1B(pp)
+
+    def step(ws, X, Yin, T):
+        def body(d):
+            (x, y), t = d
+
+            def loss_fn(ws):
+                out = x
+                for i, w in enumerate(ws):
+                    out = out @ w
+                    if pp == 2 and i == 1:
+                        out = jp.mark_stage_end(out)
+                out = jp.mark_stage_end(out)
+                logits = out + y
+                return ops.cross_entropy(logits, t)[0].mean(), (logits, x, y)
+
+            return jp.value_and_grad(loss_fn, has_aux=True)(ws)
+
+        (loss, (logits, x, y)), grads = jp.treduce(body, ((X, Yin), T), schedule=sched)
+        return [w - 0.1 * gg for w, gg in zip(ws, grads)], loss.mean(), x, y, logits
+
+    ref = step(ws, X, Yin, T)
+    f = jp.mpmd_jit_with_loop(step, cpu_mesh(pp))
+    got = f(ws, X, Yin, T)
+    assert_trees_equal(ref, got, exact=True)
+    assert torch.equal(local(got[2]), X) and torch.equal(local(got[3]), Yin)
+    verify_program(f.lower(ws, X, Yin, T).program)
