@@ -104,6 +104,15 @@ def make_train_step(cfg: tf.ModelConfig, schedule, hyper: Hyper = Hyper(), dp_ax
     [n_microbatches, microbatch, seq]; ``losses[i]`` is the mean token loss of microbatch ``i`` over this
     device's tokens."""
 
+    if cfg.cp > 1:
+        # chunks of a sequence over the context axis: parameters are replicas there, so their gradients are summed over
+        # it exactly as over a data-parallel axis (each rank contributes its tokens)
+        if dp > 1 and dp_axis == cfg.cp_axis:
+            raise ValueError(f"axis {dp_axis!r} cannot be the data-parallel and the context-parallel axis at once")
+        if dp > 1:
+            raise NotImplementedError("context parallelism together with data parallelism needs a mesh axis of its own")
+        dp_axis, dp = cfg.cp_axis, cfg.cp
+
     def step(state, tokens, labels):
         params = state["params"]
         n_mb, mb, seq = tokens.shape

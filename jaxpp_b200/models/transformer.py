@@ -54,6 +54,11 @@ class ModelConfig:
     ep: int = 1  # expert-parallel size (experts are sharded over ``ep_axis``; everything else is replicated there)
     ep_axis: str = "data"
     aux_coef: float = 0.01
+    # context parallelism: every sequence is split into ``cp`` contiguous chunks over ``cp_axis`` (attention runs as
+    # ring attention, everything else is token-local; parameters are replicas over the axis, their gradients are
+    # summed over it like data-parallel ones).  ``seq`` stays the full sequence length.  RoPE families only.
+    cp: int = 1
+    cp_axis: str = "data"
 
     @property
     def head_dim(self) -> int:
@@ -180,7 +185,10 @@ def init_params(cfg: ModelConfig, device="cpu", seed: int = 0, tp_rank: int = 0,
 def rope_tables(cfg: ModelConfig, device="cpu") -> tuple[torch.Tensor, torch.Tensor]:
     half = cfg.head_dim // 2
     inv = cfg.rope_theta ** (-torch.arange(half, dtype=torch.float32, device=device) / half)
-    ang = torch.arange(cfg.seq, dtype=torch.float32, device=device)[:, None] * inv[None, :]
+    pos = torch.arange(cfg.seq, dtype=torch.float32, device=device)
+    if cfg.cp > 1:   # this rank's chunk of every sequence
+        pos = tpops.local_token_slice_along(pos, cfg.cp_axis, cfg.cp)
+    ang = pos[:, None] * inv[None, :]
     return ang.cos().contiguous(), ang.sin().contiguous()
 
 
@@ -193,7 +201,12 @@ def _attention(cfg: ModelConfig, qkv: torch.Tensor, batch: int, rope) -> torch.T
     qkv = qkv.view(batch, -1, hq + 2 * hkv, hd)
     cos, sin = rope if rope is not None else (None, None)
     q, k, v = ops.qkv_split(qkv, cos, sin, hq, hkv)  # one pass: split into contiguous q/k/v + RoPE on q, k
-    o, _ = ops.attention(q, k, v, cfg.causal, hd ** -0.5)
+    if cfg.cp > 1:
+        from ..parallel import context
+
+        o = context.ring_attention(q, k, v, cfg.causal, hd ** -0.5, cfg.cp_axis)
+    else:
+        o, _ = ops.attention(q, k, v, cfg.causal, hd ** -0.5)
     return o.view(-1, hq * hd)
 
 
@@ -329,6 +342,8 @@ def lm_loss(cfg: ModelConfig, params: dict, tokens: torch.Tensor, labels: torch.
     (sequence parallel), so the returned value is a partial sum."""
     b = tokens.shape[0]
     tp = cfg.tp
+    if cfg.cp > 1 and cfg.family == "gpt2":
+        raise NotImplementedError("context parallelism needs rotary positions (learned absolute positions are not split)")
     flat_tok, flat_lab = tokens.reshape(-1), labels.reshape(-1)
     if tp > 1:
         flat_tok, flat_lab = tpops.local_token_slice(flat_tok, cfg), tpops.local_token_slice(flat_lab, cfg)

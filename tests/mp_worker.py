@@ -148,8 +148,10 @@ def scenario_dp_ep(family, shard_optimizer=False):
     base = dict(vocab=250, d_model=32, n_layers=2, n_heads=2, n_kv_heads=2, ffn=64, seq=16, dtype=torch.float32, n_stages=2)
     # aux_coef 0: the load-balancing statistics are per rank by design, so only the task loss is comparable
     moe = dict(n_experts=4, top_k=2, capacity_factor=8.0, aux_coef=0.0) if family == "mixtral" else {}
+    context_parallel = family == "llama_cp"   # the data axis carries chunks of every sequence instead of sequences
+    family = "llama" if context_parallel else family
     cfg1 = tf.ModelConfig(family, **base, **moe)
-    cfgd = tf.ModelConfig(family, **base, **moe, ep=dp if family == "mixtral" else 1)
+    cfgd = tf.ModelConfig(family, **base, **moe, ep=dp if family == "mixtral" else 1, cp=dp if context_parallel else 1)
     hyper = lt.Hyper(lr=1e-2, inplace_update=False, clip_grad_norm=float(os.environ["TEST_CLIP"]) if os.environ.get("TEST_CLIP") else None)
     n_mb, mb = 2, 4
     g = torch.Generator().manual_seed(9)
@@ -194,11 +196,17 @@ def scenario_dp_ep(family, shard_optimizer=False):
         hyper_d = dataclasses.replace(hyper, shard_optimizer=True)
     else:
         hyper_d = hyper
-    step = lt.make_train_step(cfgd, sched, hyper_d, dp_axis="data", dp=dp)
+    step = (lt.make_train_step(cfgd, sched, hyper_d) if context_parallel
+            else lt.make_train_step(cfgd, sched, hyper_d, dp_axis="data", dp=dp))
     f = jp.mpmd_jit_with_loop(step, mesh)
-    half = mb // dp  # this data-parallel rank's sequences of every microbatch
-    tok_l = tokens[:, me_dp * half:(me_dp + 1) * half].contiguous().to(dev)
-    lab_l = labels[:, me_dp * half:(me_dp + 1) * half].contiguous().to(dev)
+    if context_parallel:
+        part = 16 // dp  # this rank's chunk of every sequence
+        tok_l = tokens[:, :, me_dp * part:(me_dp + 1) * part].contiguous().to(dev)
+        lab_l = labels[:, :, me_dp * part:(me_dp + 1) * part].contiguous().to(dev)
+    else:
+        half = mb // dp  # this data-parallel rank's sequences of every microbatch
+        tok_l = tokens[:, me_dp * half:(me_dp + 1) * half].contiguous().to(dev)
+        lab_l = labels[:, me_dp * half:(me_dp + 1) * half].contiguous().to(dev)
     got_state, got_losses = f(local_view(state1), tok_l, lab_l)
     ref_local = local_view(ref_state)
     # with capacity-based routing the per-rank capacity differs from the single-rank run only if tokens are dropped;
@@ -219,6 +227,62 @@ def scenario_dp_ep(family, shard_optimizer=False):
                 assert bad < 0.01, f"{bad:.3%} of a parameter tensor differs"
             n += 1
     assert n > 0
+
+
+def scenario_ring_attention():
+    """Context parallelism: every rank holds one contiguous chunk of the sequence; forward output and the gradients of
+    q, k, v against full attention on the whole sequence (grouped-query heads, causal and not), eagerly and through a
+    captured pipelined step."""
+    from jaxpp_b200.ops import core as ops
+    from jaxpp_b200.parallel import context
+
+    n, r = dist.get_world_size(), dist.get_rank()
+    mesh = jp.MpmdMesh.create({"mpmd": 1, "data": n, "model": 1}, kind=device().type, multi_process=True)
+    dev = device()
+    B, S, H, Hkv, D = 2, 8 * n, 4, 2, 16
+    g = torch.Generator().manual_seed(4)
+    q, k, v = (torch.randn(B, S, h, D, generator=g) for h in (H, Hkv, Hkv))
+    do = torch.randn(B, S, H, D, generator=g)
+    scale = D ** -0.5
+    chunk = lambda t: t[:, r * S // n:(r + 1) * S // n].contiguous().to(dev)
+    with mesh:
+        for causal in (False, True):
+            qf, kf, vf = (t.clone().requires_grad_() for t in (q, k, v))
+            want, _ = ops.attention(qf, kf, vf, causal, scale)
+            want.backward(do)
+            ql, kl, vl = (chunk(t).requires_grad_() for t in (q, k, v))
+            got = context.ring_attention(ql, kl, vl, causal, scale, "data")
+            got.backward(chunk(do))
+            torch.testing.assert_close(got.detach().cpu(), chunk(want.detach()).cpu(), rtol=1e-5, atol=1e-5)
+            for name, a, b in (("dq", ql.grad, qf.grad), ("dk", kl.grad, kf.grad), ("dv", vl.grad, vf.grad)):
+                torch.testing.assert_close(a.cpu(), chunk(b).cpu(), rtol=1e-4, atol=1e-5, msg=lambda m: f"{name} causal={causal}: {m}")
+        assert torch.equal(context.local_sequence_slice(q.to(dev), "data"), chunk(q))
+
+    # inside a compiled step (one pipeline rank, the data axis as the context axis)
+    w = (torch.randn(H * D, H * D, generator=g) * 0.1).to(dev)
+
+    def step(w, q, k, v):
+        def body(mb):
+            qb, kb, vb = mb
+
+            def loss_fn(w):
+                o = context.ring_attention(qb, kb, vb, True, scale, "data")
+                y = jp.mark_stage_end(ops.linear(o.reshape(-1, H * D), w, None))
+                return (y ** 2).sum()
+
+            return jp.value_and_grad(loss_fn)(w)
+
+        return jp.treduce(body, (q, k, v), schedule=jp.Std1F1B(1))
+
+    stack = lambda t: torch.stack([chunk(t), chunk(t) * 0.5])
+    losses, gw = jp.mpmd_jit_with_loop(step, mesh)(w, stack(q), stack(k), stack(v))
+    with mesh:
+        ref_losses, ref_gw = step(w, stack(q), stack(k), stack(v))
+    torch.testing.assert_close(losses.local_tensor().cpu(), ref_losses.cpu(), rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(gw.local_tensor().cpu(), ref_gw.cpu(), rtol=1e-5, atol=1e-5)
+    full_o, _ = ops.attention(q, k, v, True, scale)
+    want_loss = (ops.linear(chunk(full_o).reshape(-1, H * D), w, None) ** 2).sum()
+    torch.testing.assert_close(losses.local_tensor()[0].cpu(), want_loss.cpu(), rtol=1e-4, atol=1e-4)
 
 
 def scenario_reshard():
@@ -260,8 +324,10 @@ SCENARIOS = {
     "pp2_tp2": lambda: scenario_pp_tp(2, 2, jp.Interleaved1F1B(4, 2)),
     "tp2": lambda: scenario_pp_tp(1, 2, jp.Std1F1B(1)),
     "reshard": scenario_reshard,
+    "ring_attention": scenario_ring_attention,
     "pp2_dp2_gpt2": lambda: scenario_dp_ep("gpt2"),
     "pp2_ep2_mixtral": lambda: scenario_dp_ep("mixtral"),
+    "pp2_cp2_llama": lambda: scenario_dp_ep("llama_cp"),
     "pp2_dp2_gpt2_zero": lambda: scenario_dp_ep("gpt2", shard_optimizer=True),
     "pp2_ep2_mixtral_zero": lambda: scenario_dp_ep("mixtral", shard_optimizer=True),
 }

@@ -52,3 +52,15 @@ def test_gradient_clipping_by_global_norm_across_stages_and_shards(scenario):
     """The clip coefficient needs the norm over every pipeline stage and every tensor- / expert-parallel shard or
     optimizer-state slice; the oracle is the un-sharded, un-pipelined step with the same (active) threshold."""
     run(scenario, 4, TEST_CLIP="0.05")
+
+
+@pytest.mark.parametrize("nproc", [2, 4])
+def test_ring_attention_over_a_sequence_split_across_ranks(nproc):
+    run("ring_attention", nproc)
+
+
+def test_pipeline_times_context_parallel():
+    """2 pipeline ranks x 2 context-parallel ranks (every sequence split in two chunks, ring attention, RoPE offsets,
+    gradients summed over the axis) against the un-sharded step; with gradient clipping on."""
+    run("pp2_cp2_llama", 4)
+    run("pp2_cp2_llama", 4, TEST_CLIP="0.05")
