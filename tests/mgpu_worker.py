@@ -301,6 +301,35 @@ def scenario_zero_gpu():
         print("sharded optimizer state: peer-memory reduce-scatter / all-gather match NCCL; train step matches", flush=True)
 
 
+def scenario_ring_attention_gpu():
+    """Context parallelism on GPUs: the native flash-attention kernels per block, NCCL point-to-point for the ring;
+    forward and gradients against the native kernel on the whole sequence (bf16, grouped-query heads)."""
+    from jaxpp_b200.ops import core as ops
+    from jaxpp_b200.parallel import context
+
+    n, r = dist.get_world_size(), dist.get_rank()
+    mesh = jp.MpmdMesh.create({"mpmd": 1, "data": n, "model": 1}, kind="cuda", multi_process=True)
+    B, S, H, Hkv, D = 2, 512 * n, 8, 2, 128
+    q, k, v, do = (rnd(B, S, h, D, seed=10 + i) for i, h in enumerate((H, Hkv, Hkv, H)))   # same on every rank
+    scale = D ** -0.5
+    chunk = lambda t: t[:, r * S // n:(r + 1) * S // n].contiguous()
+    with mesh:
+        for causal in (False, True):
+            want, lse = ops.attention(q, k, v, causal, scale)
+            dq, dk, dv = ops.attention_bwd(do, q, k, v, want, lse, causal, scale)
+            ql, kl, vl = (chunk(t).requires_grad_() for t in (q, k, v))
+            got = context.ring_attention(ql, kl, vl, causal, scale, "data")
+            got.backward(chunk(do))
+            torch.cuda.synchronize()
+            close(got.detach(), chunk(want), 2e-2, f"ring attention forward causal={causal}")
+            close(ql.grad, chunk(dq), 3e-2, f"ring attention dq causal={causal}")
+            close(kl.grad, chunk(dk), 3e-2, f"ring attention dk causal={causal}")
+            close(vl.grad, chunk(dv), 3e-2, f"ring attention dv causal={causal}")
+    assert native.read_status() == 0
+    if r == 0:
+        print("ring attention on GPUs matches the single-GPU kernels", flush=True)
+
+
 def scenario_pp_tied_gpu():
     """Tied input / output embeddings on two pipeline GPUs: the two ranks' gradient contributions are summed by a
     cross-stage all-reduce, which for a tensor this large runs as the one-kernel all-reduce over peer memory;
@@ -395,6 +424,7 @@ SCENARIOS = {
     "pp_tied": scenario_pp_tied_gpu,
     "moe_train": scenario_moe_train_gpu,
     "zero": scenario_zero_gpu,
+    "ring_attention": scenario_ring_attention_gpu,
     "p2p_native": scenario_p2p_native,
     "pp2_tp2_std": lambda: scenario_pp_tp_gpu(2, 2, "std"),
     "pp2_tp2_interleaved": lambda: scenario_pp_tp_gpu(2, 2, "interleaved"),

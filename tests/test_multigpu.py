@@ -29,6 +29,12 @@ def test_sharded_optimizer_state_two_gpus():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_ring_attention_two_gpus():
+    rc = launch([WORKER, "ring_attention"], 2, env={"NCCL_NVLS_ENABLE": "0"}, timeout_s=240)
+    assert rc == 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
 def test_fused_moe_dispatch_combine_two_gpus():
     rc = launch([WORKER, "fused_moe"], 2, env={"NCCL_NVLS_ENABLE": "0"}, timeout_s=300)
     assert rc == 0
