@@ -66,8 +66,9 @@ CONFIGS: dict[str, RunConfig] = {c.name: c for c in [
     RunConfig("llama7b_pp2tp2", tf.llama2_7b, 2, 1, 2, 4, _inter, 64, 4, description="4-GPU slice of the headline layout"),
     RunConfig("llama7b_tp2", tf.llama2_7b, 1, 1, 2, 1, _std, 32, 4, description="2-GPU slice of the headline layout"),
     RunConfig("llama7b_single", tf.llama2_7b, 1, 1, 1, 1, _std, 16, 1, description="one GPU, 16 microbatches of 1"),
-    RunConfig("mixtral8x7b_pp2ep4", tf.mixtral_8x7b, 2, 4, 1, 4, _dpv, 64, 8, ep=4,
-              description="Mixtral-8x7B shape, PP2 x EP4 (experts over the data axis), DualPipeV, microbatches of 2 per replica"),
+    RunConfig("mixtral8x7b_pp2ep4", tf.mixtral_8x7b, 2, 4, 1, 4, _dpv, 64, 8, ep=4, recompute=True,
+              description="Mixtral-8x7B shape, PP2 x EP4 (experts over the data axis), DualPipeV, microbatches of 2 per replica; "
+                          "blocks recomputed in backward: without it the memory plan exceeds 180 GB per GPU"),
     RunConfig("llama70b_pp4tp2", tf.llama2_70b, 4, 1, 2, 4, _zb, 64, 1, recompute=True,
               description="Llama-2-70B shape, PP4 x TP2, ZeroBubble, 64 microbatches of 1, full activation recompute"),
 ]}
@@ -77,3 +78,103 @@ def get(name: str) -> RunConfig:
     if name not in CONFIGS:
         raise KeyError(f"unknown configuration {name!r}; available: {sorted(CONFIGS)}")
     return CONFIGS[name]
+
+
+# =============================================================================================
+# memory plan: does a configuration fit the 180 GB of a B200?
+# =============================================================================================
+HBM_BYTES = 180e9
+
+
+def peak_live_microbatches(schedule: jp.BaseSchedule, n_microbatches: int) -> list[int]:
+    """Per pipeline rank: the largest number of (stage, microbatch) forward activations alive at once, i.e. forwards
+    run whose backward (the weight-gradient half, when the backward is split) has not run yet, in the rank's task
+    order."""
+    from .schedules import FusedTask
+    from .types import TaskType
+
+    releases = TaskType.BWD_W if schedule.is_partial_bwd else TaskType.BWD
+    peaks = []
+    for row in schedule.tasks(n_microbatches):
+        live = peak = 0
+        for unit in row:
+            if unit is None:
+                continue
+            for t in (unit if isinstance(unit, FusedTask) else (unit,)):
+                if t.fwd_or_bwd is TaskType.FWD:
+                    live += 1
+                    peak = max(peak, live)
+                elif t.fwd_or_bwd is releases:
+                    live -= 1
+        peaks.append(peak)
+    return peaks
+
+
+def memory_plan(rc: RunConfig, shard_optimizer: bool = False) -> dict:
+    """Estimated bytes per GPU of the busiest pipeline rank: bf16 parameters, fp32 master weights and Adam moments
+    (1/dp of them with ``shard_optimizer``), fp32 gradient accumulators, and the activations that the schedule keeps
+    alive (per block: what the backward of the fused kernels needs; with recompute only the block inputs plus one
+    block's working set).  An estimate for sizing, not an allocator trace."""
+    cfg = rc.model_config()
+    d, f, hd = cfg.d_model, cfg.ffn, cfg.head_dim
+    tp, ep = rc.tp, max(1, rc.ep)
+    attn_w = d * (cfg.n_heads + 2 * cfg.n_kv_heads) * hd + cfg.n_heads * hd * d
+    if cfg.n_experts:
+        mlp_w = 3 * d * f * cfg.n_experts / ep + d * cfg.n_experts          # experts over the expert axis + router
+    else:
+        mlp_w = (3 if cfg.family in ("llama", "mixtral") else 2) * d * f
+    per_layer = (attn_w + (mlp_w if cfg.n_experts else mlp_w)) / tp if not cfg.n_experts else attn_w / tp + mlp_w
+    layers_per_rank = cfg.n_layers / rc.pp
+    embed = cfg.padded_vocab * d                                           # embedding on the first rank, head on the last
+    params = layers_per_rank * per_layer + embed
+    weights = 2 * params
+    optimizer = 12 * params
+    if shard_optimizer and rc.dp > 1:
+        # only replicas over the data axis are sliced; experts sharded over that axis stay whole on their owner
+        experts = layers_per_rank * 3 * d * f * cfg.n_experts / ep if cfg.n_experts else 0.0
+        optimizer = 12 * (experts + (params - experts) / rc.dp)
+    grads = 4 * params
+    # activations of one block for one microbatch, bytes per local token (bf16 unless noted)
+    tokens = (rc.microbatch // rc.dp) * cfg.seq
+    heads_local = (cfg.n_heads + 2 * cfg.n_kv_heads) * hd / tp
+    ffn_local = (f / tp) * (cfg.top_k if cfg.n_experts else 1)
+    block = 2 * (d / tp            # block input, sequence-sharded under tensor parallelism
+                 + d / tp          # normalised input (sharded, re-gathered by the fused kernel)
+                 + heads_local     # q, k, v after the split
+                 + cfg.n_heads * hd / tp   # attention output
+                 + d / tp          # residual / second norm input
+                 + d / tp          # second normalised input
+                 + (2 if cfg.family in ("llama", "mixtral") else 1) * ffn_local   # gate | up (or the GELU input)
+                 + ffn_local)      # activation output
+    block += 4 * cfg.n_heads / tp  # log-sum-exp, fp32
+    live = max(peak_live_microbatches(rc.make_schedule(), rc.n_microbatches))
+    layers_per_stage = cfg.n_layers / rc.n_stages
+    if rc.recompute:
+        acts = tokens * (live * layers_per_stage * 2 * d / tp + block)
+    else:
+        acts = tokens * live * layers_per_stage * block
+    logits = tokens / tp * cfg.padded_vocab * (2 + 4)                       # bf16 logits + fp32 gradient of one microbatch
+    total = weights + optimizer + grads + acts + logits
+    return {"config": rc.name, "params_per_gpu": params, "weights": weights, "optimizer": optimizer, "grads": grads,
+            "activations": acts, "logits": logits, "live_stage_microbatches": live, "total": total,
+            "fits": total < 0.92 * HBM_BYTES}
+
+
+def _main():
+    import argparse
+
+    ap = argparse.ArgumentParser(description="per-GPU memory estimate of every named configuration")
+    ap.add_argument("--shard-optimizer", action="store_true")
+    args = ap.parse_args()
+    gb = lambda x: f"{x / 1e9:7.1f}"
+    print(f"{'configuration':<22}{'params/GPU':>11}{'weights':>9}{'optim':>8}{'grads':>8}{'acts':>8}{'logits':>8}{'total GB':>10}  fits 180 GB")
+    for rc in CONFIGS.values():
+        if rc.name.startswith("encoder"):
+            continue
+        m = memory_plan(rc, args.shard_optimizer)
+        print(f"{rc.name:<22}{m['params_per_gpu'] / 1e9:>10.2f}B{gb(m['weights']):>9}{gb(m['optimizer']):>8}{gb(m['grads']):>8}"
+              f"{gb(m['activations']):>8}{gb(m['logits']):>8}{gb(m['total']):>10}  {'yes' if m['fits'] else 'NO'}")
+
+
+if __name__ == "__main__":
+    _main()

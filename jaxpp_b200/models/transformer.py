@@ -274,7 +274,7 @@ class _Recompute(torch.autograd.Function):
         return out
 
     @staticmethod
-    def backward(ctx, g):
+    def backward(ctx, *gs):
         saved, others = list(ctx.saved_tensors), list(ctx.others)
         args = []
         for is_t in ctx.is_tensor:
@@ -285,8 +285,10 @@ class _Recompute(torch.autograd.Function):
                 args.append(others.pop(0))
         with torch.enable_grad():
             out = ctx.fn(*args)
+            outs = out if isinstance(out, tuple) else (out,)
+            pairs = [(o, g) for o, g in zip(outs, gs) if g is not None and o.requires_grad]   # several outputs: x and aux loss
             diff = [a for a in args if isinstance(a, torch.Tensor) and a.requires_grad]
-            grads = list(torch.autograd.grad(out, diff, g, allow_unused=True))
+            grads = list(torch.autograd.grad([o for o, _ in pairs], diff, [g for _, g in pairs], allow_unused=True))
         res = [None]
         for a in args:
             res.append(grads.pop(0) if isinstance(a, torch.Tensor) and a.requires_grad else None)
@@ -314,7 +316,7 @@ def run_layers(cfg: ModelConfig, params: dict, x: torch.Tensor, batch: int, rope
         aux = torch.zeros((), dtype=torch.float32, device=x.device)
         for name in sorted(params["layers"]):
             i = int(name)
-            x, a = mixtral_block(cfg, params["layers"][name], x, batch, rope)
+            x, a = _maybe_recompute(cfg, mixtral_block, params["layers"][name], x, batch, rope)
             aux = aux + a
             if (i + 1) % per == 0 and (i + 1) < cfg.n_layers:
                 x, aux = mark_stage_end((x, aux))

@@ -151,7 +151,8 @@ def scenario_dp_ep(family, shard_optimizer=False):
     context_parallel = family == "llama_cp"   # the data axis carries chunks of every sequence instead of sequences
     family = "llama" if context_parallel else family
     cfg1 = tf.ModelConfig(family, **base, **moe)
-    cfgd = tf.ModelConfig(family, **base, **moe, ep=dp if family == "mixtral" else 1, cp=dp if context_parallel else 1)
+    cfgd = tf.ModelConfig(family, **base, **moe, ep=dp if family == "mixtral" else 1, cp=dp if context_parallel else 1,
+                          recompute=bool(os.environ.get("TEST_RECOMPUTE")))
     hyper = lt.Hyper(lr=1e-2, inplace_update=False, clip_grad_norm=float(os.environ["TEST_CLIP"]) if os.environ.get("TEST_CLIP") else None)
     n_mb, mb = 2, 4
     g = torch.Generator().manual_seed(9)

@@ -160,3 +160,28 @@ def test_gradient_clipping_by_global_norm(family, schedule, tied):
         assert_trees_equal(ref_state, got_state, exact=not tied, rtol=1e-5, atol=1e-6)
         norms[clip] = float(torch.cat([t.reshape(-1) for t in pytree.tree_leaves(ref_state["m"])]).norm() / (1 - 0.9))
     assert norms[None] > 0.5 and abs(norms[0.05] - 0.05) < 1e-4
+
+
+def test_activation_recompute_of_mixture_of_experts_blocks():
+    """A block with two outputs (hidden state and load-balancing loss) under recompute: same results as without, the
+    forward task keeps fewer activations (what lets the Mixtral benchmark configuration fit in 180 GB)."""
+    from jaxpp_b200.compiler.program import RunTask
+
+    sched = jp.DualPipeV(4, 2)
+    kw = dict(vocab=128, d_model=32, n_layers=4, n_heads=2, n_kv_heads=2, ffn=64, seq=16, n_stages=4, dtype=torch.float32,
+              n_experts=4, top_k=2, capacity_factor=4.0, aux_coef=0.01)
+    g = torch.Generator().manual_seed(2)
+    tokens = torch.randint(0, 128, (4, 2, 16), generator=g)
+    labels = torch.randint(0, 128, (4, 2, 16), generator=g)
+    outs, progs = [], []
+    for rec in (False, True):
+        cfg = tf.ModelConfig("mixtral", recompute=rec, **kw)
+        step = lt.make_train_step(cfg, sched, lt.Hyper(lr=1e-2, inplace_update=False))
+        state = lt.init_state(cfg, sched, "cpu")
+        f = jp.mpmd_jit_with_loop(step, cpu_mesh(2))
+        outs.append(f(state, tokens, labels))
+        progs.append(f.lower(state, tokens, labels).program)
+    assert_trees_equal(pytree.tree_map(local, outs[0], is_leaf=lambda x: isinstance(x, jp.MpmdArray)), outs[1],
+                       exact=False, rtol=1e-5, atol=1e-6)
+    fwd = lambda prog: next(i for i in prog.instrs if isinstance(i, RunTask) and i.name.startswith("fwd_1"))
+    assert len(fwd(progs[1]).outs) < len(fwd(progs[0]).outs)

@@ -64,3 +64,9 @@ def test_pipeline_times_context_parallel():
     gradients summed over the axis) against the un-sharded step; with gradient clipping on."""
     run("pp2_cp2_llama", 4)
     run("pp2_cp2_llama", 4, TEST_CLIP="0.05")
+
+
+def test_expert_parallel_blocks_under_activation_recompute():
+    """The dispatch / combine exchanges of a mixture-of-experts block run again inside the backward task when the
+    block is recomputed: every expert-parallel rank repeats them in the same order."""
+    run("pp2_ep2_mixtral", 4, TEST_RECOMPUTE="1")

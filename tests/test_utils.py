@@ -225,3 +225,28 @@ def test_memstats_and_sharding_mesh_helpers(capsys):
     b = jp.MpmdMesh.create({"mpmd": 1, "data": 2, "model": 1}, kind="cpu", multi_process=False).jax_mesh
     moved = updated_named_sharding_mesh([jp.NamedSharding(a, jp.P("data")), None], b)
     assert moved[1] is None and moved[0].mesh is b and moved[0].spec == jp.P("data")
+
+
+def test_memory_plan_of_the_benchmark_configurations():
+    """Every named GPU configuration fits a 180 GB B200 by the planner's estimate; the schedule's peak of live
+    activations follows the textbook values; sharding the optimizer state shrinks the replicated part only."""
+    import dataclasses
+
+    import jaxpp_b200 as jp
+    from jaxpp_b200 import configs
+
+    assert configs.peak_live_microbatches(jp.Std1F1B(4), 8) == [4, 3, 2, 1]          # warm-up depth of 1F1B
+    assert configs.peak_live_microbatches(jp.GPipe(2), 6) == [6, 6]                  # everything in flight
+    assert max(configs.peak_live_microbatches(jp.ZeroBubble(4), 8)) >= 4             # weight halves release later
+    for name, rc in configs.CONFIGS.items():
+        if name.startswith("encoder"):
+            continue
+        plan = configs.memory_plan(rc)
+        assert plan["fits"], (name, plan["total"] / 1e9)
+        assert abs(plan["total"] - sum(plan[k] for k in ("weights", "optimizer", "grads", "activations", "logits"))) < 1
+    mix = configs.get("mixtral8x7b_pp2ep4")
+    assert not configs.memory_plan(dataclasses.replace(mix, recompute=False))["fits"]   # why that configuration recomputes
+    gpt = configs.get("gpt2xl_pp2dp4")
+    assert configs.memory_plan(gpt, shard_optimizer=True)["optimizer"] * 4 == pytest.approx(configs.memory_plan(gpt)["optimizer"])
+    whole, sliced = configs.memory_plan(mix)["optimizer"], configs.memory_plan(mix, shard_optimizer=True)["optimizer"]
+    assert 0.8 * whole < sliced < whole                                               # experts are not replicas
