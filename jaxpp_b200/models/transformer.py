@@ -59,6 +59,7 @@ class ModelConfig:
     # summed over it like data-parallel ones).  ``seq`` stays the full sequence length.  RoPE families only.
     cp: int = 1
     cp_axis: str = "data"
+    cp_layout: str = "contiguous"   # or "zigzag": pieces r and 2*cp-1-r per rank, which balances causal attention
 
     @property
     def head_dim(self) -> int:
@@ -187,7 +188,9 @@ def rope_tables(cfg: ModelConfig, device="cpu") -> tuple[torch.Tensor, torch.Ten
     inv = cfg.rope_theta ** (-torch.arange(half, dtype=torch.float32, device=device) / half)
     pos = torch.arange(cfg.seq, dtype=torch.float32, device=device)
     if cfg.cp > 1:   # this rank's chunk of every sequence
-        pos = tpops.local_token_slice_along(pos, cfg.cp_axis, cfg.cp)
+        from ..parallel import context
+
+        pos = context.local_sequence_slice(pos, cfg.cp_axis, 0, cfg.cp_layout)
     ang = pos[:, None] * inv[None, :]
     return ang.cos().contiguous(), ang.sin().contiguous()
 
@@ -204,7 +207,7 @@ def _attention(cfg: ModelConfig, qkv: torch.Tensor, batch: int, rope) -> torch.T
     if cfg.cp > 1:
         from ..parallel import context
 
-        o = context.ring_attention(q, k, v, cfg.causal, hd ** -0.5, cfg.cp_axis)
+        o = context.ring_attention(q, k, v, cfg.causal, hd ** -0.5, cfg.cp_axis, cfg.cp_layout)
     else:
         o, _ = ops.attention(q, k, v, cfg.causal, hd ** -0.5)
     return o.view(-1, hq * hd)

@@ -13,7 +13,13 @@ Transfers are point-to-point operations on the axis' own process group (NCCL on 
 block's attention kernel so that they overlap it.  The reference has no context parallelism (its long-context advice
 is rematerialisation and offloading, PERF_GUIDE.md:51-54); everything else in a transformer block is token-local, so a
 model shards its sequence over the axis, uses this op for attention and sums parameter gradients over the axis as it
-does for data parallelism.  Work is not balanced under ``causal`` (rank ``r`` computes ``r + 1`` blocks).
+does for data parallelism.
+
+Layouts.  ``contiguous``: rank ``r`` holds chunk ``r``; under ``causal`` rank ``r`` computes ``r + 1`` of the ``n``
+blocks, so the last rank paces the ring.  ``zigzag``: the sequence is cut into ``2n`` pieces and rank ``r`` holds pieces
+``r`` and ``2n-1-r`` (concatenated); then every rank computes the causal block on its own chunk plus, per other rank,
+exactly half a block (all its queries against the earlier rank's first piece, or its second piece's queries against
+the later rank's whole chunk), which balances the causal work.
 """
 from __future__ import annotations
 
@@ -54,10 +60,25 @@ def _wait(reqs: list) -> None:
         q.wait()
 
 
-def _fwd_impl(q: Tensor, k: Tensor, v: Tensor, causal: bool, scale: float, axis: str):
+def _merge(out: Tensor, lse: Tensor, o_i: Tensor, lse_i: Tensor, rows: slice) -> None:
+    """Fold a block's (o_i, lse_i) for query rows ``rows`` into the running fp32 output / log-sum-exp, in place."""
+    old = lse[:, :, rows]
+    new = torch.logaddexp(old, lse_i)
+    w_old = torch.exp(old - new).transpose(1, 2).unsqueeze(-1)                             # [B, S, H, 1]
+    w_new = torch.exp(lse_i - new).transpose(1, 2).unsqueeze(-1)
+    out[:, rows] = out[:, rows] * w_old + o_i.float() * w_new
+    lse[:, :, rows] = new
+
+
+def _fwd_impl(q: Tensor, k: Tensor, v: Tensor, causal: bool, scale: float, axis: str, layout: str = "contiguous"):
     n, r, nxt, prv, group = _ring(axis)
     if n == 1:
         return ops.attention(q, k, v, causal, scale)
+    if layout not in ("contiguous", "zigzag"):
+        raise ValueError(f"unknown sequence layout {layout!r}")
+    zigzag = causal and layout == "zigzag"
+    half = q.shape[1] // 2
+    everything, back = slice(None), slice(half, None)
     out = torch.zeros(q.shape, dtype=torch.float32, device=q.device)                       # [B, S, H, D]
     lse = torch.full((q.shape[0], q.shape[2], q.shape[1]), float("-inf"), dtype=torch.float32, device=q.device)
     k_cur, v_cur = k.contiguous(), v.contiguous()
@@ -66,23 +87,28 @@ def _fwd_impl(q: Tensor, k: Tensor, v: Tensor, causal: bool, scale: float, axis:
         reqs = None
         if step < n - 1:
             (k_nxt, v_nxt), reqs = _rotate([k_cur, v_cur], nxt, prv, group)
-        if not (causal and src > r):
+        if zigzag and src < r:      # an earlier rank: only its first piece precedes my queries, and all of them
+            o_i, lse_i = ops.attention(q, k_cur[:, :half].contiguous(), v_cur[:, :half].contiguous(), False, scale)
+            _merge(out, lse, o_i, lse_i, everything)
+        elif zigzag and src > r:    # a later rank: both its pieces precede my second piece and follow my first
+            o_i, lse_i = ops.attention(q[:, half:].contiguous(), k_cur, v_cur, False, scale)
+            _merge(out, lse, o_i, lse_i, back)
+        elif not (causal and src > r):
             o_i, lse_i = ops.attention(q, k_cur, v_cur, causal and src == r, scale)
-            new = torch.logaddexp(lse, lse_i)
-            w_old = torch.exp(lse - new).transpose(1, 2).unsqueeze(-1)                     # [B, S, H, 1]
-            w_new = torch.exp(lse_i - new).transpose(1, 2).unsqueeze(-1)
-            out = out * w_old + o_i.float() * w_new
-            lse = new
+            _merge(out, lse, o_i, lse_i, everything)
         if reqs is not None:
             _wait(reqs)
             k_cur, v_cur = k_nxt, v_nxt
     return out.to(q.dtype), lse
 
 
-def _bwd_impl(do: Tensor, q: Tensor, k: Tensor, v: Tensor, o: Tensor, lse: Tensor, causal: bool, scale: float, axis: str):
+def _bwd_impl(do: Tensor, q: Tensor, k: Tensor, v: Tensor, o: Tensor, lse: Tensor, causal: bool, scale: float, axis: str,
+              layout: str = "contiguous"):
     n, r, nxt, prv, group = _ring(axis)
     if n == 1:
         return ops.attention_bwd(do, q, k, v, o, lse, causal, scale)
+    zigzag = causal and layout == "zigzag"
+    half = q.shape[1] // 2
     do = do.contiguous()
     dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
     k_cur, v_cur = k.contiguous(), v.contiguous()
@@ -93,7 +119,19 @@ def _bwd_impl(do: Tensor, q: Tensor, k: Tensor, v: Tensor, o: Tensor, lse: Tenso
         kv_reqs = None
         if step < n - 1:                          # the chunk itself is needed by n - 1 more ranks
             (k_nxt, v_nxt), kv_reqs = _rotate([k_cur, v_cur], nxt, prv, group)
-        if not (causal and src > r):
+        if zigzag and src < r:
+            dq_i, dk_i, dv_i = ops.attention_bwd(do, q, k_cur[:, :half].contiguous(), v_cur[:, :half].contiguous(), o, lse,
+                                                 False, scale)
+            dq += dq_i.float()
+            dk_cur[:, :half] += dk_i.float()
+            dv_cur[:, :half] += dv_i.float()
+        elif zigzag and src > r:
+            dq_i, dk_i, dv_i = ops.attention_bwd(do[:, half:].contiguous(), q[:, half:].contiguous(), k_cur, v_cur,
+                                                 o[:, half:].contiguous(), lse[:, :, half:].contiguous(), False, scale)
+            dq[:, half:] += dq_i.float()
+            dk_cur += dk_i.float()
+            dv_cur += dv_i.float()
+        elif not (causal and src > r):
             # the global o and lse make every block's probabilities and row sums those of the whole sequence
             dq_i, dk_i, dv_i = ops.attention_bwd(do, q, k_cur, v_cur, o, lse, causal and src == r, scale)
             dq += dq_i.float()
@@ -109,47 +147,56 @@ def _bwd_impl(do: Tensor, q: Tensor, k: Tensor, v: Tensor, o: Tensor, lse: Tenso
     return dq.to(q.dtype), dk_cur.to(k.dtype), dv_cur.to(v.dtype)
 
 
-_lib.define("ring_attention(Tensor q, Tensor k, Tensor v, bool causal, float scale, str axis) -> (Tensor, Tensor)")
+_lib.define("ring_attention(Tensor q, Tensor k, Tensor v, bool causal, float scale, str axis, str layout=\"contiguous\")"
+            " -> (Tensor, Tensor)")
 _lib.impl("ring_attention", _fwd_impl, "CompositeExplicitAutograd")
 torch.library.register_fake(
     "b200cp::ring_attention",
-    lambda q, k, v, causal, scale, axis: (torch.empty_like(q),
+    lambda q, k, v, causal, scale, axis, layout="contiguous": (torch.empty_like(q),
                                           q.new_empty(q.shape[0], q.shape[2], q.shape[1], dtype=torch.float32)))
 
 _lib.define("ring_attention_bwd(Tensor do, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, bool causal, float scale,"
-            " str axis) -> (Tensor, Tensor, Tensor)")
+            " str axis, str layout=\"contiguous\") -> (Tensor, Tensor, Tensor)")
 _lib.impl("ring_attention_bwd", _bwd_impl, "CompositeExplicitAutograd")
 torch.library.register_fake(
     "b200cp::ring_attention_bwd",
-    lambda do, q, k, v, o, lse, causal, scale, axis: (torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)))
+    lambda do, q, k, v, o, lse, causal, scale, axis, layout="contiguous": (torch.empty_like(q), torch.empty_like(k),
+                                                                           torch.empty_like(v)))
 
 
 def _setup(ctx, inputs, output):
-    q, k, v, causal, scale, axis = inputs
+    q, k, v, causal, scale, axis, layout = inputs
     ctx.save_for_backward(q, k, v, output[0], output[1])
-    ctx.causal, ctx.scale, ctx.axis = causal, scale, axis
+    ctx.causal, ctx.scale, ctx.axis, ctx.layout = causal, scale, axis, layout
 
 
 def _backward(ctx, do, dlse):
     q, k, v, o, lse = ctx.saved_tensors
-    dq, dk, dv = torch.ops.b200cp.ring_attention_bwd(do.contiguous(), q, k, v, o, lse, ctx.causal, ctx.scale, ctx.axis)
-    return dq, dk, dv, None, None, None
+    dq, dk, dv = torch.ops.b200cp.ring_attention_bwd(do.contiguous(), q, k, v, o, lse, ctx.causal, ctx.scale, ctx.axis,
+                                                     ctx.layout)
+    return dq, dk, dv, None, None, None, None
 
 
 torch.library.register_autograd("b200cp::ring_attention", _backward, setup_context=_setup)
 
 
-def ring_attention(q: Tensor, k: Tensor, v: Tensor, causal: bool, scale: float, axis: str) -> Tensor:
+def ring_attention(q: Tensor, k: Tensor, v: Tensor, causal: bool, scale: float, axis: str,
+                   layout: str = "contiguous") -> Tensor:
     """Attention of this rank's queries over the whole sequence held by the ranks of ``axis``; ``q, k, v`` are this
-    rank's ``[batch, s_local, heads, head_dim]`` chunk (grouped-query layouts as in ``ops.attention``)."""
-    return torch.ops.b200cp.ring_attention(q, k, v, causal, float(scale), axis)[0]
+    rank's ``[batch, s_local, heads, head_dim]`` chunk in the given ``layout`` (grouped-query heads as in
+    ``ops.attention``)."""
+    return torch.ops.b200cp.ring_attention(q, k, v, causal, float(scale), axis, layout)[0]
 
 
-def local_sequence_slice(x: Tensor, axis: str, dim: int = 1) -> Tensor:
-    """This rank's contiguous chunk of ``x`` along the sequence dimension ``dim``."""
+def local_sequence_slice(x: Tensor, axis: str, dim: int = 1, layout: str = "contiguous") -> Tensor:
+    """This rank's chunk of ``x`` along the sequence dimension ``dim``: chunk ``r`` of ``n``, or for ``zigzag`` pieces
+    ``r`` and ``2n-1-r`` of ``2n`` concatenated."""
     n = tpmod.axis_size(axis)
     if n == 1:
         return x
     r = tpmod.axis_rank(axis)
+    if layout == "zigzag":
+        s = x.shape[dim] // (2 * n)
+        return torch.cat([x.narrow(dim, r * s, s), x.narrow(dim, (2 * n - 1 - r) * s, s)], dim=dim)
     s = x.shape[dim] // n
     return x.narrow(dim, r * s, s)

@@ -251,13 +251,6 @@ def local_token_slice(flat: Tensor, cfg) -> Tensor:
     return flat[r * n:(r + 1) * n]
 
 
-def local_token_slice_along(x: Tensor, axis: str, n: int, dim: int = 0) -> Tensor:
-    """This rank's contiguous chunk (of ``n``) of ``x`` along ``dim`` for mesh axis ``axis``."""
-    r = axis_rank(axis)
-    size = x.shape[dim] // n
-    return x.narrow(dim, r * size, size)
-
-
 def local_positions(n_local: int, cfg, device) -> Tensor:
     """Position ids of this device's token slice."""
     r = axis_rank(cfg.tp_axis) if cfg.tp > 1 else 0

@@ -148,10 +148,11 @@ def scenario_dp_ep(family, shard_optimizer=False):
     base = dict(vocab=250, d_model=32, n_layers=2, n_heads=2, n_kv_heads=2, ffn=64, seq=16, dtype=torch.float32, n_stages=2)
     # aux_coef 0: the load-balancing statistics are per rank by design, so only the task loss is comparable
     moe = dict(n_experts=4, top_k=2, capacity_factor=8.0, aux_coef=0.0) if family == "mixtral" else {}
-    context_parallel = family == "llama_cp"   # the data axis carries chunks of every sequence instead of sequences
+    context_parallel = family.startswith("llama_cp")   # the data axis carries chunks of every sequence instead of sequences
+    cp_layout = "zigzag" if family.endswith("zigzag") else "contiguous"
     family = "llama" if context_parallel else family
     cfg1 = tf.ModelConfig(family, **base, **moe)
-    cfgd = tf.ModelConfig(family, **base, **moe, ep=dp if family == "mixtral" else 1, cp=dp if context_parallel else 1,
+    cfgd = tf.ModelConfig(family, **base, **moe, ep=dp if family == "mixtral" else 1, cp=dp if context_parallel else 1, cp_layout=cp_layout,
                           recompute=bool(os.environ.get("TEST_RECOMPUTE")))
     hyper = lt.Hyper(lr=1e-2, inplace_update=False, clip_grad_norm=float(os.environ["TEST_CLIP"]) if os.environ.get("TEST_CLIP") else None)
     n_mb, mb = 2, 4
@@ -201,9 +202,14 @@ def scenario_dp_ep(family, shard_optimizer=False):
             else lt.make_train_step(cfgd, sched, hyper_d, dp_axis="data", dp=dp))
     f = jp.mpmd_jit_with_loop(step, mesh)
     if context_parallel:
-        part = 16 // dp  # this rank's chunk of every sequence
-        tok_l = tokens[:, :, me_dp * part:(me_dp + 1) * part].contiguous().to(dev)
-        lab_l = labels[:, :, me_dp * part:(me_dp + 1) * part].contiguous().to(dev)
+        if cp_layout == "zigzag":
+            pc = 16 // (2 * dp)
+            cut = lambda t: torch.cat([t[:, :, me_dp * pc:(me_dp + 1) * pc],
+                                       t[:, :, (2 * dp - 1 - me_dp) * pc:(2 * dp - me_dp) * pc]], dim=2)
+        else:
+            part = 16 // dp  # this rank's chunk of every sequence
+            cut = lambda t: t[:, :, me_dp * part:(me_dp + 1) * part]
+        tok_l, lab_l = cut(tokens).contiguous().to(dev), cut(labels).contiguous().to(dev)
     else:
         half = mb // dp  # this data-parallel rank's sequences of every microbatch
         tok_l = tokens[:, me_dp * half:(me_dp + 1) * half].contiguous().to(dev)
@@ -245,19 +251,25 @@ def scenario_ring_attention():
     q, k, v = (torch.randn(B, S, h, D, generator=g) for h in (H, Hkv, Hkv))
     do = torch.randn(B, S, H, D, generator=g)
     scale = D ** -0.5
-    chunk = lambda t: t[:, r * S // n:(r + 1) * S // n].contiguous().to(dev)
+    piece = S // (2 * n)
+    chunks = {"contiguous": lambda t: t[:, r * S // n:(r + 1) * S // n].contiguous().to(dev),
+              "zigzag": lambda t: torch.cat([t[:, r * piece:(r + 1) * piece],
+                                             t[:, (2 * n - 1 - r) * piece:(2 * n - r) * piece]], dim=1).contiguous().to(dev)}
+    chunk = chunks["contiguous"]
     with mesh:
-        for causal in (False, True):
+        for causal, layout in ((False, "contiguous"), (True, "contiguous"), (True, "zigzag"), (False, "zigzag")):
+            chunk = chunks[layout]
             qf, kf, vf = (t.clone().requires_grad_() for t in (q, k, v))
             want, _ = ops.attention(qf, kf, vf, causal, scale)
             want.backward(do)
             ql, kl, vl = (chunk(t).requires_grad_() for t in (q, k, v))
-            got = context.ring_attention(ql, kl, vl, causal, scale, "data")
+            got = context.ring_attention(ql, kl, vl, causal, scale, "data", layout)
             got.backward(chunk(do))
             torch.testing.assert_close(got.detach().cpu(), chunk(want.detach()).cpu(), rtol=1e-5, atol=1e-5)
             for name, a, b in (("dq", ql.grad, qf.grad), ("dk", kl.grad, kf.grad), ("dv", vl.grad, vf.grad)):
                 torch.testing.assert_close(a.cpu(), chunk(b).cpu(), rtol=1e-4, atol=1e-5, msg=lambda m: f"{name} causal={causal}: {m}")
-        assert torch.equal(context.local_sequence_slice(q.to(dev), "data"), chunk(q))
+            assert torch.equal(context.local_sequence_slice(q.to(dev), "data", 1, layout), chunk(q))
+        chunk = chunks["contiguous"]
 
     # inside a compiled step (one pipeline rank, the data axis as the context axis)
     w = (torch.randn(H * D, H * D, generator=g) * 0.1).to(dev)
@@ -329,6 +341,7 @@ SCENARIOS = {
     "pp2_dp2_gpt2": lambda: scenario_dp_ep("gpt2"),
     "pp2_ep2_mixtral": lambda: scenario_dp_ep("mixtral"),
     "pp2_cp2_llama": lambda: scenario_dp_ep("llama_cp"),
+    "pp2_cp2_llama_zigzag": lambda: scenario_dp_ep("llama_cp_zigzag"),
     "pp2_dp2_gpt2_zero": lambda: scenario_dp_ep("gpt2", shard_optimizer=True),
     "pp2_ep2_mixtral_zero": lambda: scenario_dp_ep("mixtral", shard_optimizer=True),
 }

@@ -64,6 +64,7 @@ def test_pipeline_times_context_parallel():
     gradients summed over the axis) against the un-sharded step; with gradient clipping on."""
     run("pp2_cp2_llama", 4)
     run("pp2_cp2_llama", 4, TEST_CLIP="0.05")
+    run("pp2_cp2_llama_zigzag", 4)      # pieces r and 2n-1-r per rank: balanced causal work
 
 
 def test_expert_parallel_blocks_under_activation_recompute():
