@@ -9,6 +9,9 @@ from the owners of the slices:
     master', m', v', lp = adamw(master, g_shard, m, v, ...)
     p'      = all_gather_flat(lp, numel).view(shape)
 
+The slices are padded per axis size, so a checkpoint of sliced optimizer state restores into the same data-parallel
+size only (the parameters themselves restore into any layout).
+
 On GPUs both collectives are one peer-memory kernel each (the two halves of the one-kernel all-reduce,
 ``csrc/collectives.cu``); elsewhere, and below 1 MiB, NCCL / gloo.  The reference leaves this to XLA's SPMD
 partitioner: a parameter annotated ``P("fsdp")`` gets a cast + all-gather before the loop and a reduce-scatter
