@@ -30,7 +30,8 @@ def run(args):
     mesh = jp.MpmdMesh.create({"mpmd": args.pp, "data": 1, "model": 1}, kind=args.device, multi_process=multi)
     device = mesh.my_device.torch_device if multi else torch.device(args.device)
     dtype = torch.float32 if args.device == "cpu" else torch.bfloat16
-    cfg = tf.ModelConfig("llama", vocab=512, d_model=128, n_layers=args.stages * 2, n_heads=4, n_kv_heads=2, ffn=256, seq=64,
+    # head_dim 64: one of the sizes the flash-attention kernels take
+    cfg = tf.ModelConfig("llama", vocab=512, d_model=256, n_layers=args.stages * 2, n_heads=4, n_kv_heads=2, ffn=512, seq=128,
                          n_stages=args.stages, dtype=dtype)
     params = tf.init_params(cfg, device, seed=0)
     rope = tf.rope_tables(cfg, device)
@@ -51,7 +52,7 @@ def run(args):
     got = pipelined(params, tokens)
     mine = got.local_tensor()
     if mine is not None:       # the result lives on the rank of the last stage
-        tol = 0.0 if args.device == "cpu" else 2e-2
+        tol = 0.0 if args.device == "cpu" else 5e-2
         torch.testing.assert_close(mine.float().cpu(), want.float().cpu(), rtol=tol, atol=tol)
         print(f"log-likelihood per sequence (pipelined over {args.pp} ranks, {args.stages} stages): "
               f"{[round(float(v), 3) for v in mine.float().cpu()]} -- matches the un-pipelined forward", flush=True)

@@ -43,8 +43,9 @@ def run(args):
     specs = [P(("stage", "fsdp"), "tensor"), P("tensor", ("stage", "fsdp")), P("fsdp", None, None)]
     shardings = [jp.NamedSharding(whole, s) for s in specs]
     g = torch.Generator().manual_seed(0)
-    full = [torch.randn(HIDDEN, EMBED, generator=g) * 0.05, torch.randn(EMBED, HIDDEN, generator=g) * 0.05,
-            torch.randn(4, 32, EMBED, generator=g)]
+    dtype = torch.float32 if args.device == "cpu" else torch.bfloat16      # the native GEMM kernels are bf16
+    full = [(torch.randn(HIDDEN, EMBED, generator=g) * 0.05).to(dtype), (torch.randn(EMBED, HIDDEN, generator=g) * 0.05).to(dtype),
+            torch.randn(4, 32, EMBED, generator=g).to(dtype)]
     # SPMD initialisation: every process keeps only the shards of its own devices
     mine = [mesh.my_device] if multi else None
     W1, W2, x = (DistArray.from_global(t, s, devices=mine) for t, s in zip(full, shardings))
@@ -87,13 +88,14 @@ def run(args):
     say(f"dW1 sharding: {dW1.sharding.spec}; dW2 sharding: {dW2.sharding.spec}")
 
     # check against plain autograd on the full arrays
-    w1, w2 = full[0].clone().requires_grad_(), full[1].clone().requires_grad_()
-    flat = full[2].reshape(-1, EMBED)
+    w1, w2 = full[0].float().requires_grad_(), full[1].float().requires_grad_()
+    flat = full[2].float().reshape(-1, EMBED)
     ((flat - (flat @ w1.T) @ w2.T) ** 2).sum().backward()
+    tol = 1e-4 if dtype == torch.float32 else 5e-2
     for got, want, name in ((dW1, w1.grad, "dW1"), (dW2, w2.grad, "dW2")):
         for dev, shard in got.shards.items():
             idx = got.sharding.device_index(dev, want.shape)
-            torch.testing.assert_close(shard.cpu(), want[idx], rtol=1e-4, atol=1e-4)
+            torch.testing.assert_close(shard.float().cpu(), want[idx], rtol=tol, atol=tol * float(want.abs().max()))
     say("gradients match plain autograd")
 
 
