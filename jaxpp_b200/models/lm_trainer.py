@@ -186,6 +186,8 @@ def _clip_coefficient(cfg: tf.ModelConfig, schedule, params: dict, flat_g: list,
     ``cross_mpmd_all_reduce`` for the global gradient norm, api.py:48-54)."""
     owners = owner_ranks(cfg, schedule)
     tp_sharded = {"wqkv", "w_up", "b_qkv", "b_up", "wo", "w_down"} if cfg.tp > 1 else set()
+    if cfg.tp > 1 and cfg.vocab_parallel:
+        tp_sharded.add("lm_head")
     ep_sharded = {"e_up", "e_down"} if cfg.ep > 1 else set()
     paths = []   # (owner rank, parameter name) in flattening order
     for k, v in params.items():
@@ -256,7 +258,8 @@ def param_specs(cfg: tf.ModelConfig, params_like: dict) -> dict:
         return {k: col.get(k) or row.get(k) or exp.get(k) or P() for k in ld}
 
     # same key order as the parameter tree (pytrees flatten dicts in insertion order)
-    return {k: ({name: layer(ld) for name, ld in v.items()} if k == "layers" else P()) for k, v in params_like.items()}
+    top = lambda k: P(tp, None) if k == "lm_head" and cfg.vocab_parallel and tp else P()
+    return {k: ({name: layer(ld) for name, ld in v.items()} if k == "layers" else top(k)) for k, v in params_like.items()}
 
 
 def state_specs(cfg: tf.ModelConfig, state_like: dict, shard_optimizer_axis: str | None = None) -> dict:

@@ -57,6 +57,9 @@ class ModelConfig:
     # context parallelism: every sequence is split into ``cp`` contiguous chunks over ``cp_axis`` (attention runs as
     # ring attention, everything else is token-local; parameters are replicas over the axis, their gradients are
     # summed over it like data-parallel ones).  ``seq`` stays the full sequence length.  RoPE families only.
+    # the output projection split by vocabulary rows over the tensor-parallel axis: logits stay sharded and the cross
+    # entropy combines the ranks' log-sum-exps (``tp.vocab_parallel_cross_entropy``); needs untied embeddings
+    vocab_parallel: bool = False
     cp: int = 1
     cp_axis: str = "data"
     cp_layout: str = "contiguous"   # or "zigzag": pieces r and 2*cp-1-r per rank, which balances causal attention
@@ -180,6 +183,9 @@ def init_params(cfg: ModelConfig, device="cpu", seed: int = 0, tp_rank: int = 0,
                 params["final_norm_b"] = torch.zeros(d, dtype=dtype, device=device)
             if not cfg.tie_embeddings:
                 params["lm_head"] = _randn(gen, (cfg.padded_vocab, d), 0.02, dtype, device)
+                if cfg.vocab_parallel and cfg.tp > 1:   # this rank's rows of the same matrix
+                    rows = cfg.padded_vocab // cfg.tp
+                    params["lm_head"] = params["lm_head"][tp_rank * rows:(tp_rank + 1) * rows].contiguous()
     return params
 
 
@@ -367,8 +373,17 @@ def lm_loss(cfg: ModelConfig, params: dict, tokens: torch.Tensor, labels: torch.
     else:
         x = ops.rmsnorm(x, params["final_norm"], cfg.eps)[0]
     head = params["embed"] if cfg.tie_embeddings else params["lm_head"]
-    logits = ops.linear(x, head, None)
-    loss, _ = ops.cross_entropy(logits, flat_lab)
+    if cfg.vocab_parallel and tp > 1:
+        if cfg.tie_embeddings:
+            raise NotImplementedError("a vocabulary-parallel output projection needs untied embeddings")
+        # all tokens x this rank's vocabulary rows (all-gather -> GEMM); the per-token loss is shared by the ranks and
+        # every rank keeps the part of its own token slice, so that the ranks' partial sums add up to the total
+        logits = tpops.column_linear(x, head, None, cfg)
+        every = tpops.vocab_parallel_cross_entropy(logits, labels.reshape(-1), cfg.tp_axis)
+        loss = tpops.local_token_slice(every, cfg)
+    else:
+        logits = ops.linear(x, head, None)
+        loss, _ = ops.cross_entropy(logits, flat_lab)
     total = loss.sum()
     if aux is not None:  # the load-balancing term is per token: scale it like the summed cross entropy
         total = total + cfg.aux_coef * aux * flat_lab.shape[0]
@@ -386,6 +401,8 @@ def sync_replicated_grads(cfg: ModelConfig, grads: dict) -> dict:
         for name, layer in grads["layers"].items()
     }
     for k in ("embed", "pos", "final_norm", "final_norm_b", "lm_head"):
+        if k == "lm_head" and cfg.vocab_parallel:
+            continue   # sharded by vocabulary rows: every rank owns its gradient
         if k in grads:
             out[k] = tpops.all_reduce(grads[k], cfg.tp_axis)
     return out
@@ -441,5 +458,8 @@ def shard_layer_for_tp(cfg: ModelConfig, full: dict, tp: int, r: int) -> dict:
 
 def shard_params_for_tp(cfg: ModelConfig, full: dict, tp: int, r: int) -> dict:
     out = {k: v for k, v in full.items() if k != "layers"}
+    if cfg.vocab_parallel and "lm_head" in out and not isinstance(out["lm_head"], type(None)) and tp > 1:
+        rows = out["lm_head"].shape[0] // tp
+        out["lm_head"] = out["lm_head"][r * rows:(r + 1) * rows]
     out["layers"] = {name: shard_layer_for_tp(cfg, layer, tp, r) for name, layer in full["layers"].items()}
     return out

@@ -256,3 +256,72 @@ def local_positions(n_local: int, cfg, device) -> Tensor:
     r = axis_rank(cfg.tp_axis) if cfg.tp > 1 else 0
     start = r * n_local
     return (torch.arange(n_local, device=device) + start) % cfg.seq
+
+
+# ---- vocabulary-parallel cross entropy ---------------------------------------------------------------------------
+def _vp_ce_impl(logits: Tensor, labels: Tensor, axis: str):
+    """logits [T, V/n] (this rank's slice of the vocabulary, rank r holds entries [r V/n, (r+1) V/n)), labels [T] ->
+    (loss [T] fp32, lse [T] fp32), both the same on every rank of ``axis``."""
+    n = axis_size(axis)
+    lf = logits.float()
+    local_lse = torch.logsumexp(lf, dim=-1)
+    if n == 1:
+        return local_lse - lf.gather(1, labels.view(-1, 1)).view(-1), local_lse
+    r = axis_rank(axis)
+    width = logits.shape[-1]
+    every = torch.empty(n * local_lse.shape[0], dtype=torch.float32, device=logits.device)
+    dist.all_gather_into_tensor(every, local_lse.contiguous(), group=_group(axis))
+    lse = torch.logsumexp(every.view(n, -1), dim=0)                       # stable: combines the ranks' log-sum-exps
+    local = labels - r * width
+    mine = (local >= 0) & (local < width)
+    target = lf.gather(1, local.clamp(0, width - 1).view(-1, 1)).view(-1) * mine
+    dist.all_reduce(target, group=_group(axis))                           # the owner of the label's entry contributes
+    return lse - target, lse
+
+
+def _vp_ce_bwd_impl(dloss: Tensor, logits: Tensor, labels: Tensor, lse: Tensor, axis: str) -> Tensor:
+    """The loss is one value per token shared by the ranks: the gradients the ranks hold for it add up, then every
+    rank forms its slice of softmax - onehot."""
+    n = axis_size(axis)
+    dl = dloss.float().contiguous().clone()
+    r = 0
+    if n > 1:
+        dist.all_reduce(dl, group=_group(axis))
+        r = axis_rank(axis)
+    width = logits.shape[-1]
+    p = torch.exp(logits.float() - lse.unsqueeze(-1))
+    local = labels - r * width
+    mine = (local >= 0) & (local < width)
+    p.scatter_add_(1, local.clamp(0, width - 1).view(-1, 1), -mine.to(p.dtype).view(-1, 1))
+    return (p * dl.unsqueeze(-1)).to(logits.dtype)
+
+
+_lib.define("vocab_parallel_ce(Tensor logits, Tensor labels, str axis) -> (Tensor, Tensor)")
+_lib.impl("vocab_parallel_ce", _vp_ce_impl, "CompositeExplicitAutograd")
+torch.library.register_fake(
+    "b200tp::vocab_parallel_ce",
+    lambda logits, labels, axis: (logits.new_empty(logits.shape[0], dtype=torch.float32),
+                                  logits.new_empty(logits.shape[0], dtype=torch.float32)))
+_lib.define("vocab_parallel_ce_bwd(Tensor dloss, Tensor logits, Tensor labels, Tensor lse, str axis) -> Tensor")
+_lib.impl("vocab_parallel_ce_bwd", _vp_ce_bwd_impl, "CompositeExplicitAutograd")
+torch.library.register_fake("b200tp::vocab_parallel_ce_bwd", lambda dloss, logits, labels, lse, axis: torch.empty_like(logits))
+
+
+def _vp_ce_setup(ctx, inputs, output):
+    logits, labels, axis = inputs
+    ctx.save_for_backward(logits, labels, output[1])
+    ctx.axis = axis
+
+
+def _vp_ce_backward(ctx, dloss, dlse):
+    logits, labels, lse = ctx.saved_tensors
+    return torch.ops.b200tp.vocab_parallel_ce_bwd(dloss.contiguous(), logits, labels, lse, ctx.axis), None, None
+
+
+torch.library.register_autograd("b200tp::vocab_parallel_ce", _vp_ce_backward, setup_context=_vp_ce_setup)
+
+
+def vocab_parallel_cross_entropy(logits: Tensor, labels: Tensor, axis: str) -> Tensor:
+    """Per-token cross entropy from logits whose vocabulary dimension is split over ``axis`` (the full [tokens, vocab]
+    matrix is never assembled): log-sum-exps are combined across the ranks, the label's logit comes from its owner."""
+    return torch.ops.b200tp.vocab_parallel_ce(logits, labels, axis)[0]

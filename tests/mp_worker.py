@@ -68,7 +68,8 @@ def scenario_pp_tp(pp, tp, schedule):
     """Pipeline x tensor parallel language model against the un-sharded single-process step."""
     mesh = jp.MpmdMesh.create({"mpmd": pp, "data": 1, "model": tp}, kind=device().type, multi_process=True)
     dev = device()
-    base = dict(vocab=250, d_model=64, n_layers=4, n_heads=4, n_kv_heads=2, ffn=128, seq=32, dtype=torch.float32)
+    base = dict(vocab=250, d_model=64, n_layers=4, n_heads=4, n_kv_heads=2, ffn=128, seq=32, dtype=torch.float32,
+                vocab_parallel=bool(os.environ.get("TEST_VOCAB_PARALLEL")))
     cfg1 = tf.ModelConfig("llama", n_stages=schedule.num_stages, tp=1, **base)
     cfgt = tf.ModelConfig("llama", n_stages=schedule.num_stages, tp=tp, **base)
     hyper = lt.Hyper(lr=1e-2, inplace_update=False, clip_grad_norm=float(os.environ["TEST_CLIP"]) if os.environ.get("TEST_CLIP") else None)

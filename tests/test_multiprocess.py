@@ -71,3 +71,11 @@ def test_expert_parallel_blocks_under_activation_recompute():
     """The dispatch / combine exchanges of a mixture-of-experts block run again inside the backward task when the
     block is recomputed: every expert-parallel rank repeats them in the same order."""
     run("pp2_ep2_mixtral", 4, TEST_RECOMPUTE="1")
+
+
+@pytest.mark.parametrize("scenario,nproc", [("tp2", 2), ("pp2_tp2", 4)])
+def test_vocabulary_parallel_output_projection_and_cross_entropy(scenario, nproc):
+    """The output projection split by vocabulary rows over the tensor-parallel ranks: sharded logits, log-sum-exps
+    combined across ranks, the label's logit from its owner; against the un-sharded step (gradient clipping on, so
+    the sharded head also enters the global norm)."""
+    run(scenario, nproc, TEST_VOCAB_PARALLEL="1", TEST_CLIP="0.05")
