@@ -8,7 +8,8 @@
 Weak scaling: every GPU contributes 16 sequences of 4096 tokens per step.  N=8 is the headline layout
 (PP=4 x TP=2, Interleaved1F1B with 2 virtual stages per rank, 32 microbatches of 4 sequences); smaller N
 keep the model and the per-GPU batch and shrink the mesh: N=4 PP2xTP2, N=2 TP2, N=1 a single device
-(16 microbatches of 1 sequence so that activations fit beside 7B of optimizer state).
+(16 microbatches of 1 sequence so that activations fit beside 7B of optimizer state).  ``--config NAME`` runs
+any other named configuration (GPT-2-XL PP2xDP4, Mixtral-8x7B PP2xEP4, Llama-2-70B PP4xTP2) the same way.
 
 Prints ONE JSON line from rank 0.  ``value`` is device-timed (CUDA events around K steps, max over ranks);
 ``e2e`` repeats the measurement through the public API with a host->device copy of the step's token ids
@@ -18,6 +19,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import subprocess
 import sys
@@ -33,19 +35,28 @@ def parse():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--model", default="llama2_7b")
+    ap.add_argument("--config", default=None,
+                    help="a named run configuration of jaxpp_b200.configs (gpt2xl_pp2dp4, mixtral8x7b_pp2ep4, llama70b_pp4tp2, "
+                         "...) instead of the headline layout for --gpus; its GPU count must equal --gpus")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only; invalid as a result)")
-    ap.add_argument("--seqs-per-gpu", type=int, default=16)
+    ap.add_argument("--seqs-per-gpu", type=int, default=16, help="headline layouts: sequences per GPU and step (weak scaling)")
     ap.add_argument("--nccl-only", action="store_true", help="baseline: NCCL collectives instead of fused kernels")
+    ap.add_argument("--stage-layers", default="auto",
+                    help="blocks per pipeline stage: 'equal', 'auto' (balance the pipeline ranks, counting the output "
+                         "projection and loss of the last stage) or a comma-separated list (entries may end in .5)")
+    ap.add_argument("--shard-optimizer", action="store_true", help="optimizer state as 1/dp slices (data-parallel configs)")
+    ap.add_argument("--timeline", default=None, help="write a per-rank, per-task-kind timeline of one step to this file")
+    ap.add_argument("--p2p", default=None, choices=[None, "torch", "native"], help="point-to-point backend between stages")
     return ap.parse_args()
 
 
-LAYOUTS = {  # n_gpus -> (pp, tp, virtual stages per rank, microbatch size)
-    1: (1, 1, 1, 1),
-    2: (1, 2, 1, 4),
-    4: (2, 2, 2, 4),
-    8: (4, 2, 2, 4),
-}
+# headline layouts: n_gpus -> named configuration (all the Llama-2-7B shape; 16 sequences of 4096 per GPU)
+HEADLINE = {1: "llama7b_single", 2: "llama7b_tp2", 4: "llama7b_pp2tp2", 8: "llama7b_pp4tp2"}
+
+# Cost model behind --stage-layers auto, in units of one decoder block's forward + backward time: share of a block
+# spent in its attention half, and the extra work of the last stage (final norm, output projection, cross entropy),
+# both from the per-task timeline of the headline step (profiles/step_timeline_n8.txt).
+ATTN_SHARE, HEAD_EXTRA = 0.36, 0.73
 
 
 class ClockSampler:
@@ -106,14 +117,18 @@ def main():
     if args.impl == "reference":
         return reference_arm()
 
+    import dataclasses
+
     import torch
     import torch.distributed as dist
 
     import jaxpp_b200 as jp
+    from jaxpp_b200 import configs
     from jaxpp_b200.models import lm_trainer as lt
     from jaxpp_b200.models import transformer as tf
     from jaxpp_b200.ops import native
-    from jaxpp_b200.utils import config
+    from jaxpp_b200.parallel import fused, symm
+    from jaxpp_b200.utils import config, timeline
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -121,8 +136,12 @@ def main():
     n = args.gpus
     if world != n:
         raise SystemExit(f"--gpus {n} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {n}")
-    if n not in LAYOUTS:
-        raise SystemExit(f"supported GPU counts: {sorted(LAYOUTS)}")
+    headline = args.config is None
+    if headline and n not in HEADLINE:
+        raise SystemExit(f"supported GPU counts: {sorted(HEADLINE)}")
+    rc = configs.get(HEADLINE[n] if headline else args.config)
+    if rc.n_gpus != n:
+        raise SystemExit(f"{rc.name} runs on {rc.n_gpus} GPUs, not {n}")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
@@ -130,33 +149,49 @@ def main():
     native.load()
     if args.nccl_only:
         config.use_fused_collectives._override = False
+    if args.p2p:
+        config.p2p_backend._override = args.p2p
     config.transfer_done_delay._override = 2  # release sent activations two sends later instead of at step end
 
-    pp, tp, vstages, mb = LAYOUTS[n]
-    n_stages = pp * vstages
-    seqs = args.seqs_per_gpu * n
+    pp, tp, dp = rc.pp, rc.tp, rc.dp
+    n_stages = rc.n_stages
+    seqs = args.seqs_per_gpu * n if headline else rc.global_batch
+    mb = rc.microbatch
     n_mb = seqs // mb
-    cfg = getattr(tf, args.model)(n_stages=n_stages, tp=tp)
+    mb_local = max(1, mb // dp)
+    schedule = rc.make_schedule()
+    cfg = rc.model_config()
     if args.layers:
-        import dataclasses
-
         cfg = dataclasses.replace(cfg, n_layers=args.layers)
-    schedule = jp.Interleaved1F1B(n_stages, pp) if vstages > 1 else jp.Std1F1B(pp)
-    mesh = jp.MpmdMesh.create({"mpmd": pp, "data": 1, "model": tp}, kind="cuda", multi_process=world > 1)
-    if world > 1 and tp > 1:
-        mesh.axis_group("model")  # created collectively, up front
+    if args.stage_layers != "equal" and n_stages > 1:
+        if args.stage_layers == "auto":
+            sizes = tf.balanced_stage_layers(cfg.n_layers, n_stages, schedule.get_mpmd_idx, pp, last_extra=HEAD_EXTRA,
+                                             attn_share=ATTN_SHARE)
+        else:
+            sizes = tuple(float(x) for x in args.stage_layers.split(","))
+        cfg = dataclasses.replace(cfg, stage_layers=sizes)
+    mesh = jp.MpmdMesh.create({"mpmd": pp, "data": dp, "model": tp}, kind="cuda", multi_process=world > 1)
+    if world > 1:
+        for axis, size in (("model", tp), ("data", dp)):
+            if size > 1:
+                mesh.axis_group(axis)  # created collectively, up front
     my_pp = mesh.my_mpmd_axis_index if world > 1 else None
     tp_rank = mesh.axis_index("model") if world > 1 and tp > 1 else 0
+    dp_rank = mesh.axis_index("data") if world > 1 and dp > 1 else 0
 
-    hyper = lt.Hyper()
-    step_fn = lt.make_train_step(cfg, schedule, hyper)
-    jitted = jp.mpmd_jit_with_loop(step_fn, mesh, name="llama_train_step")
-    state = lt.init_state(cfg, schedule, device, my_rank=my_pp, tp_rank=tp_rank, seed=0)
+    sharded_opt = args.shard_optimizer and dp > 1
+    hyper = lt.Hyper(shard_optimizer=sharded_opt)
+    step_fn = lt.make_train_step(cfg, schedule, hyper, dp_axis="data" if dp > 1 else None, dp=dp)
+    jitted = jp.mpmd_jit_with_loop(step_fn, mesh, name=f"{rc.name}_train_step")
+    # expert weights differ between the ranks of the expert axis; everything else is replicated over the data axis
+    state = lt.init_state(cfg, schedule, device, my_rank=my_pp, tp_rank=tp_rank + 1000 * dp_rank * (rc.ep > 1), seed=0)
+    if sharded_opt:
+        state = lt.shard_state_for_dp(cfg, state, dp, dp_rank)
 
-    g = torch.Generator().manual_seed(1234)
-    host_tokens = [torch.randint(0, cfg.vocab, (n_mb, mb, cfg.seq + 1), generator=g).pin_memory() for _ in range(2)]
+    g = torch.Generator().manual_seed(1234 + dp_rank)
+    host_tokens = [torch.randint(0, cfg.vocab, (n_mb, mb_local, cfg.seq + 1), generator=g).pin_memory() for _ in range(2)]
     tokens_per_step = seqs * cfg.seq
-    h2d_bytes = 2 * n_mb * mb * cfg.seq * 8
+    h2d_bytes = n_mb * mb_local * (cfg.seq + 1) * 8
 
     def load_batch(i):
         t = host_tokens[i % 2].to(device, non_blocking=True)
@@ -172,12 +207,23 @@ def main():
         t = losses.local_tensor()
         return float(t.mean().item()) if t is not None else None
 
+    def mean_over_ranks(v):
+        """Mean of a per-rank value over the ranks that have one (the ranks of the last pipeline stage)."""
+        if world == 1:
+            return v
+        t = torch.tensor([v if v is not None else 0.0, 0.0 if v is None else 1.0], device=device, dtype=torch.float64)
+        dist.all_reduce(t)
+        return float(t[0] / t[1]) if float(t[1]) > 0 else None
+
     tok, lab = load_batch(0)
-    loss_val = None
+    loss_val = first_loss = None
     for i in range(args.warmup):
         state, losses = jitted(state, tok, lab)
         loss_val = read_loss(losses)
+        if i == 0:
+            first_loss = loss_val
     sync_all()
+    torch.cuda.reset_peak_memory_stats()
 
     # ---- device-timed region: K steps, inputs resident -------------------------------------------------------
     sampler = ClockSampler(local_rank)
@@ -206,8 +252,9 @@ def main():
         loss_val = lv if lv is not None else loss_val
     sync_all()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    peak_mem = torch.cuda.max_memory_allocated() / 1e9
 
-    # ---- bubble: one extra step with per-task CUDA events ---------------------------------------------------------------
+    # ---- bubble and timeline: one extra step with per-task CUDA events ---------------------------------------------------
     compiled = jitted.lower(state, tok, lab)
     leaves, *_ = jitted._prepare((state, tok, lab), {})
     sync_all()
@@ -219,39 +266,65 @@ def main():
     step_ms_b = b0.elapsed_time(b1)
     busy = compiled.last_states[0].busy_ms() if world > 1 else sum(s.busy_ms() for s in compiled.last_states)
     bubble = max(0.0, 1.0 - busy / step_ms_b)
+    if args.timeline:
+        text = "\n".join(timeline.format_summary(
+            f"process {rank} (pipeline rank {st.rank}, tp {tp_rank}, dp {dp_rank})", timeline.summarise_events(st.events, b0, b1))
+            for st in compiled.last_states)
+        texts = [text]
+        if world > 1:
+            texts = [None] * world
+            dist.all_gather_object(texts, text)
+        if rank == 0:
+            os.makedirs(os.path.dirname(os.path.abspath(args.timeline)), exist_ok=True)
+            with open(args.timeline, "w") as f:
+                f.write(f"# one step of {rc.name} on {n} GPUs with per-task CUDA events (stage sizes {cfg.stage_sizes}); "
+                        "'idle before' = compute stream idle in front of a task (waiting for another rank)\n")
+                f.write("\n\n".join(texts) + "\n")
 
-    bubbles = [bubble]
+    canaries_ok = symm.check_all_canaries()
+    fallbacks = fused.FALLBACKS[0]
+    loss_val, first_loss = mean_over_ranks(loss_val), mean_over_ranks(first_loss)
+    bubbles, peaks = [bubble], [peak_mem]
     if world > 1:
-        allb = [torch.zeros(1, device=device, dtype=torch.float64) for _ in range(world)]
-        dist.all_gather(allb, torch.tensor([bubble], device=device, dtype=torch.float64))
-        bubbles = [float(x.item()) for x in allb]
-        t = torch.tensor([ms, e2e_ms, bubble, float(launches), float(status)], device=device, dtype=torch.float64)
+        allb = [torch.zeros(2, device=device, dtype=torch.float64) for _ in range(world)]
+        dist.all_gather(allb, torch.tensor([bubble, peak_mem], device=device, dtype=torch.float64))
+        bubbles, peaks = [float(x[0]) for x in allb], [float(x[1]) for x in allb]
+        t = torch.tensor([ms, e2e_ms, bubble, float(launches), float(status), float(fallbacks), float(not canaries_ok)],
+                         device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms, bubble, launches, status = (float(x) for x in t.tolist())
-        lt_ = torch.tensor([loss_val if loss_val is not None else -1.0], device=device, dtype=torch.float64)
-        dist.all_reduce(lt_, op=dist.ReduceOp.MAX)
-        loss_val = float(lt_.item())
+        ms, e2e_ms, bubble, launches, status, fallbacks, bad_canary = (float(x) for x in t.tolist())
+        canaries_ok = not bad_canary
 
     if rank == 0:
         value = tokens_per_step / (ms / 1e3)
-        flops = cfg.flops_per_token() * tokens_per_step
+        flops = cfg.flops_per_token() * tokens_per_step   # model FLOPs: recomputed forwards are not counted
         peak = 1412.0e12
         try:
-            peaks = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")))
-            peak = float(peaks.get("bf16_tflops_sustained", 1412.0)) * 1e12
+            peaks_json = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")))
+            peak = float(peaks_json.get("bf16_tflops_sustained", 1412.0)) * 1e12
         except Exception:
             pass
+        par = "".join(f"{k}{v}" for k, v in (("pp", pp), ("dp", dp), ("tp", tp)) if v > 1 or k == "pp")
+        if rc.ep > 1:
+            par = par.replace(f"dp{dp}", f"ep{rc.ep}")
+        vstages = n_stages // pp
+        metric = ("train tokens/s, Llama-7B-shape PP4xTP2 on 8xB200 (max over ranks); bubble %" if headline
+                  else f"train tokens/s, {rc.name} on {n}xB200 (max over ranks); bubble %")
         out = {
-            "metric": "train tokens/s, Llama-7B-shape PP4xTP2 on 8xB200 (max over ranks); bubble %",
+            "metric": metric,
             "value": round(value, 1), "unit": "tokens/s", "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init weights)",
-            "config": {"model": f"{args.model} ({cfg.n_layers} layers, d_model {cfg.d_model}, seq {cfg.seq})",
+            "config": {"name": rc.name,
+                       "model": f"{rc.model.__name__} ({cfg.n_layers} layers, d_model {cfg.d_model}, seq {cfg.seq})",
                        "global_batch": seqs, "seq_len": cfg.seq, "microbatches": n_mb, "microbatch_size": mb,
-                       "parallelism": f"pp{pp}tp{tp}" + (f" interleaved v={vstages}" if vstages > 1 else ""),
-                       "schedule": type(schedule).__name__, "optimizer": "AdamW fp32 master, fused kernel",
+                       "parallelism": par + (f" v={vstages}" if vstages > 1 else ""),
+                       "schedule": type(schedule).__name__, "stage_layers": list(cfg.stage_sizes),
+                       "recompute": bool(cfg.recompute),
+                       "optimizer": "AdamW fp32 master, fused kernel" + (", state sharded over dp" if sharded_opt else ""),
                        "l2": "inputs exceed L2 (weights and activations are GBs per step)",
-                       "fused_collectives": bool(config.use_fused_collectives.value) and tp > 1},
+                       "fused_collectives": bool(config.use_fused_collectives.value) and (tp > 1 or dp > 1),
+                       "p2p": config.p2p_backend.value},
             "clocks": clocks,
             "e2e": {"value": round(tokens_per_step / (e2e_ms / 1e3), 1), "unit": "tokens/s",
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4, "ms_per_step": round(e2e_ms, 3)},
@@ -260,7 +333,10 @@ def main():
             "ideal_bubble_pct": round(100 * schedule.ideal_bubble_fraction(n_mb), 2),
             "mfu_of_measured_sustained_peak": round(flops / (ms / 1e3) / (peak * n), 4),
             "bubble_pct_per_rank": [round(100 * b, 2) for b in bubbles],
+            "peak_mem_gb_per_rank": [round(x, 1) for x in peaks],
+            "first_step_loss": first_loss, "ln_vocab": round(math.log(cfg.vocab), 3),
             "final_loss": loss_val, "kernel_status": int(status),
+            "fused_fallbacks": int(fallbacks), "canaries_ok": bool(canaries_ok),
         }
         print(json.dumps(out))
     if world > 1:

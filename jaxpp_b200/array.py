@@ -344,29 +344,41 @@ def _my_process() -> int:
 def reshard(arr: DistArray, dst: NamedSharding, donate: bool = False) -> DistArray:
     """Redistribute ``arr`` to ``dst`` (possibly a different mesh).  Collective over all processes that
     own a device of either mesh; every process must call it with the same arguments in the same order."""
+    return reshard_group([arr], [dst], donate)[0]
+
+
+def reshard_group(arrs: Sequence[DistArray], dsts: Sequence[NamedSharding], donate: bool = False) -> list[DistArray]:
+    """Redistribute several arrays as one unit: the copies of all of them are posted together (one batch of
+    point-to-point operations between processes), completed, and only then are the sources released.  What is in
+    flight at once -- destination shards, staging buffers of strided pieces, and the sources -- is therefore bounded
+    by the bytes of the group, which is how the memory-bounded groups of :func:`spmd_to_mpmd_reshard` bound peak
+    memory.  Collective: same arguments, same order on every process."""
     import torch.distributed as dist
 
-    ops = plan_reshard(arr.shape, arr.sharding, dst)
-    multi = arr.mesh.is_multi_process or dst.mesh.is_multi_process
     me = _my_process()
-    mine = lambda d: (not multi) or d.process_index == me
-    out: dict[Device, torch.Tensor] = {}
-    shard_shape = dst.shard_shape(arr.shape)
-    for d in dst.mesh.flat_devices:
-        if mine(d):
-            out[d] = torch.empty(shard_shape, dtype=arr.dtype, device=d.torch_device)
+    outs: list[dict] = []
     pending = []
-    for op in ops:
-        s_mine, d_mine = mine(op.src), mine(op.dst)
-        if s_mine and d_mine:
-            out[op.dst][op.dst_idx].copy_(arr.shards[op.src][op.src_idx])
-        elif s_mine:
-            buf = arr.shards[op.src][op.src_idx].contiguous()
-            pending.append(dist.P2POp(dist.isend, buf, op.dst.process_index))
-        elif d_mine:
-            view = out[op.dst][op.dst_idx]
-            buf = view if view.is_contiguous() else torch.empty(view.shape, dtype=arr.dtype, device=view.device)
-            pending.append((dist.P2POp(dist.irecv, buf, op.src.process_index), view, buf))
+    for arr, dst in zip(arrs, dsts):
+        ops = plan_reshard(arr.shape, arr.sharding, dst)
+        multi = arr.mesh.is_multi_process or dst.mesh.is_multi_process
+        mine = lambda d, multi=multi: (not multi) or d.process_index == me
+        out: dict[Device, torch.Tensor] = {}
+        shard_shape = dst.shard_shape(arr.shape)
+        for d in dst.mesh.flat_devices:
+            if mine(d):
+                out[d] = torch.empty(shard_shape, dtype=arr.dtype, device=d.torch_device)
+        for op in ops:
+            s_mine, d_mine = mine(op.src), mine(op.dst)
+            if s_mine and d_mine:
+                out[op.dst][op.dst_idx].copy_(arr.shards[op.src][op.src_idx])
+            elif s_mine:
+                buf = arr.shards[op.src][op.src_idx].contiguous()
+                pending.append(dist.P2POp(dist.isend, buf, op.dst.process_index))
+            elif d_mine:
+                view = out[op.dst][op.dst_idx]
+                buf = view if view.is_contiguous() else torch.empty(view.shape, dtype=arr.dtype, device=view.device)
+                pending.append((dist.P2POp(dist.irecv, buf, op.src.process_index), view, buf))
+        outs.append(out)
     if pending:
         p2p = [p if isinstance(p, dist.P2POp) else p[0] for p in pending]
         for w in dist.batch_isend_irecv(p2p):
@@ -375,8 +387,9 @@ def reshard(arr: DistArray, dst: NamedSharding, donate: bool = False) -> DistArr
             if not isinstance(p, dist.P2POp) and p[1] is not p[2]:
                 p[1].copy_(p[2])
     if donate:
-        arr.delete()
-    return DistArray(out, dst, arr.shape, arr.dtype)
+        for arr in arrs:
+            arr.delete()
+    return [DistArray(out, dst, arr.shape, arr.dtype) for out, arr, dst in zip(outs, arrs, dsts)]
 
 
 def _group_by_size_threshold(sizes: Sequence[int], order: Sequence[int], threshold: float) -> list[list[int]]:
@@ -475,11 +488,14 @@ def spmd_to_mpmd_reshard(mpmd_mesh: MpmdMesh, spmd_arrays: Any, mpmd_shardings: 
     multi = mpmd_mesh.jax_mesh.is_multi_process
     me = _my_process()
     for group in groups:
+        effs = []
         for i in group:
             sh = shardings[i]
             ids = sorted(sh.mesh_ids) if sh.mesh_ids else [0]
-            eff = MpmdSharding(mpmd_mesh, frozenset(ids), sh.spec)
-            moved = reshard(arrays[i], eff.sharding, donate=donate)
+            effs.append((ids, MpmdSharding(mpmd_mesh, frozenset(ids), sh.spec)))
+        # one group = one batch of copies: posted together, completed, sources released, then the next group
+        moved_all = reshard_group([arrays[i] for i in group], [eff.sharding for _, eff in effs], donate=donate)
+        for i, (ids, eff), moved in zip(group, effs, moved_all):
             locals_ = []
             for idx in ids:
                 sub = mpmd_mesh.unstack[idx]

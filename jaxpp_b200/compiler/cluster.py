@@ -48,6 +48,77 @@ def is_nondeterministic(node: fx.Node) -> bool:
     return torch.Tag.nondeterministic_seeded in tags
 
 
+def node_bytes(node: fx.Node) -> int:
+    """Bytes of the tensor(s) a node produces (0 for non-tensor values)."""
+    val = node.meta.get("val")
+    vals = val if isinstance(val, (list, tuple)) else [val]
+    return sum(v.numel() * v.element_size() for v in vals if isinstance(v, torch.Tensor))
+
+
+_FP8_DTYPES = tuple(getattr(torch, n) for n in ("float8_e4m3fn", "float8_e5m2", "float8_e4m3fnuz", "float8_e5m2fnuz")
+                    if hasattr(torch, n))
+
+
+def is_fp8_cast(node: fx.Node) -> bool:
+    """A conversion to an 8-bit float type.  Such casts stay next to the GEMM that consumes them (the reference keeps
+    them inside the loop for the same reason, src/jaxpp/licm.py:429-452): hoisting one would keep a low-precision copy of
+    every weight alive for the whole step and separate the cast from the scaling that belongs to it."""
+    if node.op != "call_function" or node.target not in (aten._to_copy.default, aten.to.dtype):
+        return False
+    val = node.meta.get("val")
+    return isinstance(val, torch.Tensor) and val.dtype in _FP8_DTYPES
+
+
+# cheap ops whose result is at least as large as their operands: hoisting them out of the loop trades a small
+# resident value for a large one, so with scarce memory they go back into the loop (licm.py:301-345)
+_EXPANDING_TARGETS = {aten._to_copy.default, aten.to.dtype, aten.add.Tensor, aten.mul.Tensor, aten.clone.default,
+                      aten.repeat.default, aten.expand_copy.default, aten.ones_like.default, aten.zeros_like.default,
+                      aten.full_like.default}
+
+
+def _freeze(a):
+    if isinstance(a, fx.Node):
+        return ("n", id(a))
+    if isinstance(a, (list, tuple)):
+        return (type(a).__name__,) + tuple(_freeze(x) for x in a)
+    if isinstance(a, dict):
+        return ("d",) + tuple((k, _freeze(v)) for k, v in sorted(a.items()))
+    if isinstance(a, slice):
+        return ("s", _freeze(a.start), _freeze(a.stop), _freeze(a.step))
+    if isinstance(a, float):
+        return ("f", repr(a))
+    try:
+        hash(a)
+        return (type(a).__name__, a)
+    except TypeError:
+        return ("id", id(a))
+
+
+def cse(graph: fx.Graph) -> int:
+    """Common-subexpression elimination: a node that applies the same pure op to the same operands as an earlier one
+    is replaced by it (the reference re-traces the step through a CSE trace before hoisting, src/jaxpp/licm.py:66-126).
+    Stage markers, loop markers, seeded random ops and ``get_attr`` nodes are left alone.  Returns the number of nodes
+    removed."""
+    markers = set(prim.marker_targets().values())
+    seen: dict = {}
+    removed = 0
+    for node in list(graph.nodes):
+        if node.op != "call_function" or node.target in markers or is_nondeterministic(node):
+            continue
+        schema = getattr(node.target, "_schema", None)
+        if schema is not None and getattr(schema, "is_mutable", False):
+            continue
+        key = (id(node.target), _freeze(node.args), _freeze(node.kwargs))
+        first = seen.get(key)
+        if first is None:
+            seen[key] = node
+            continue
+        node.replace_all_uses_with(first)
+        graph.erase_node(node)
+        removed += 1
+    return removed
+
+
 @dataclasses.dataclass
 class LoopRegions:
     begin: fx.Node | None
@@ -106,7 +177,9 @@ def find_loop(graph: fx.Graph) -> LoopRegions | None:
         movable = (
             inputs_outside
             and not is_marker(n, "yield")
+            and not is_marker(n, "place_with")     # pins its value inside the loop (licm.py:455-456)
             and not is_nondeterministic(n)
+            and not is_fp8_cast(n)
             and (licm or n.target in _ALIAS_TARGETS or n.target is operator.getitem and ins[0] in hoisted_set)
         )
         if movable:
@@ -115,6 +188,20 @@ def find_loop(graph: fx.Graph) -> LoopRegions | None:
         else:
             body.append(n)
             body_set.add(n)
+    if licm and config.licm_memory_scarce.value:
+        # scarce memory: a hoisted op that only expands its operands (a cast to a wider type, a broadcast add, ...)
+        # and feeds nothing but the loop goes back inside, last one first, so that chains of them move together
+        for n in reversed(list(hoisted)):
+            if n.target not in _EXPANDING_TARGETS or not n.users:
+                continue
+            if not all(u in body_set for u in n.users):
+                continue
+            if node_bytes(n) < sum(node_bytes(i) for i in n.all_input_nodes):
+                continue
+            hoisted.remove(n)
+            hoisted_set.discard(n)
+            body_set.add(n)
+        body = [n for n in between if n in body_set]
     out_nodes = list(end.args[0])
     # a microbatch slice (or the index) returned as it is: give it a node of its own in the body, so that it has a
     # producing task like every other loop output (it joins the first stage, which reads the microbatch anyway)
@@ -348,11 +435,35 @@ def split_shared_weight_grads(graph: fx.Graph, loop: LoopRegions, clusters: list
     return n_split
 
 
+def _matmul_like(node: fx.Node) -> bool:
+    """Ops that a zero-bubble split never pulls forward for free: GEMMs, attention, and the fused GEMM+collective ops."""
+    name = str(node.target)
+    return any(k in name for k in ("linear", "wgrad", "dgrad", "attention", "mm.", "bmm", "matmul", "ag_", "_rs"))
+
+
 def split_backward_clusters(clusters: list[Cluster], assign: dict, loop_end: fx.Node | None,
-                            first_stage_id: int = 0) -> tuple[list[Cluster], dict]:
+                            first_stage_id: int = 0, memory_scarce: bool | None = None,
+                            defer_budget_bytes: int | None = None) -> tuple[list[Cluster], dict]:
     """Zero-bubble split: each backward cluster (except the first stage's) becomes ``BWD_I`` — the
     backward slice of the values other clusters consume, i.e. the activation gradients — and
-    ``BWD_W`` — everything else (weight gradients).  The first stage keeps one task typed ``BWD_I``."""
+    ``BWD_W`` — everything else (weight gradients).  The first stage keeps one task typed ``BWD_I``.
+
+    Activation recompute is traced flat (the re-run forward ops are ordinary nodes of the backward cluster), so the
+    slice cuts *through* a recomputed block op by op: what the reference does by splitting a ``remat`` equation in two
+    (src/jaxpp/jaxpr_utils.py:60-102).  Two refinements bound what stays alive from ``BWD_I`` to ``BWD_W``:
+
+    * ``memory_scarce`` (default ``JAXPP_B200_ZB_MEMORY_SCARCE``, on): a left-over op that is not a GEMM, does not
+      depend on a left-over GEMM and does not produce more bytes than it consumes moves into ``BWD_I`` — the smaller
+      result is kept instead of its operands (jaxpr_utils.py:138-169);
+    * ``defer_budget_bytes`` (default ``JAXPP_B200_ZB_DEFER_BYTES``, unlimited when negative): weight-gradient GEMMs
+      are deferred to ``BWD_W`` in program order only while the operands they keep alive fit the budget; the others
+      run in ``BWD_I``.  With full recompute the deferred operands (activation gradients and recomputed inputs of
+      every linear) are what a zero-bubble schedule holds per outstanding microbatch, so this is the knob that makes
+      a large model fit."""
+    if memory_scarce is None:
+        memory_scarce = config.zb_memory_scarce.value
+    if defer_budget_bytes is None:
+        defer_budget_bytes = config.zb_defer_bytes.value
     out: list[Cluster] = []
     new_assign: dict = {}
     for c, cl in enumerate(clusters):
@@ -376,6 +487,32 @@ def split_backward_clusters(clusters: list[Cluster], assign: dict, loop_end: fx.
         for m in cl.nodes:
             if m.target is operator.getitem and m.args[0] in need:
                 need.add(m)
+        if defer_budget_bytes is not None and defer_budget_bytes >= 0:
+            kept = 0
+            counted: set = set()
+            for m in cl.nodes:                      # program order
+                if m in need or not _matmul_like(m):
+                    continue
+                extra = sum(node_bytes(i) for i in m.all_input_nodes if i not in counted and i.op != "placeholder")
+                if kept + extra <= defer_budget_bytes:
+                    kept += extra
+                    counted.update(m.all_input_nodes)
+                else:
+                    need.update(_closure([m], inside, {}))   # runs with the activation gradients
+        if memory_scarce:
+            deferred_defs: set = set()
+            for m in cl.nodes:                      # program order: producers before consumers
+                if m in need:
+                    continue
+                if _matmul_like(m) or any(i in deferred_defs for i in m.all_input_nodes):
+                    deferred_defs.add(m)
+                    continue
+                ins_bytes = sum(node_bytes(i) for i in m.all_input_nodes)
+                if m.target is operator.getitem or (ins_bytes > 0 and node_bytes(m) <= ins_bytes):
+                    if all(i in need or i not in inside for i in m.all_input_nodes):
+                        need.add(m)
+                        continue
+                deferred_defs.add(m)
         part_i = Cluster(cl.stage_id, TaskType.BWD_I, cl.rank, [m for m in cl.nodes if m in need])
         part_w = Cluster(cl.stage_id, TaskType.BWD_W, cl.rank, [m for m in cl.nodes if m not in need])
         for part in (part_i, part_w):

@@ -75,7 +75,8 @@ def _external_io(nodes: list, extra_users: set) -> tuple[list, list]:
 
 
 class Lowering:
-    def __init__(self, cap: Captured, mpmd_dim: int, name: str = "step"):
+    def __init__(self, cap: Captured, mpmd_dim: int, name: str = "step", donated_inputs: set | None = None):
+        self.donated_inputs = set(donated_inputs or ())   # positions (flat tensor inputs) the caller gave up
         self.cap = cap
         self.graph = cap.graph
         self.mpmd_dim = mpmd_dim
@@ -132,6 +133,10 @@ class Lowering:
     def run(self, schedule: BaseSchedule | None) -> Program:
         cap, graph = self.cap, self.graph
         cl.dce(graph)
+        if config.enable_licm.value:
+            n_cse = cl.cse(graph)
+            if n_cse:
+                logger.info("common-subexpression elimination removed %d ops", n_cse)
         if config.fuse_norm_backward_adds.value:
             from .peephole import fuse_norm_backward_adds
 
@@ -179,8 +184,10 @@ class Lowering:
                 outputs.append(("v", vid, tuple(sorted(self.where[vid]))))
             else:
                 outputs.append(("c", o))
+        # program inputs stay alive for the whole step unless the caller donated them: a donated input is freed
+        # after its last use on each rank like any intermediate (reference: infer_donation, core.py:1732-1809)
         self.finish_lifetimes({v for kind, v, *_ in [o for o in outputs if o[0] == "v"]},
-                              {vid for vid, _ in inputs})
+                              {vid for k, (vid, _) in enumerate(inputs) if k not in self.donated_inputs})
         prog = Program(self.mpmd_dim, self.instrs, self.ids.values, inputs, outputs)
         prog.meta["name"] = self.name
         prog.meta["n_mubatches"] = loop.n if loop is not None else 1
@@ -783,14 +790,13 @@ class Lowering:
                 if last.get((rank, v)) == k and v not in keep:
                     if isinstance(ins, RunTask) and rank == ins.rank and v in ins.ins and ins.donate[ins.ins.index(v)]:
                         continue  # already dropped by donation
-                    if isinstance(ins, Accum) and v == ins.val and ins.steal and ins.index == 0:
-                        pass
                     dead[rank].append(v)
             for rank, vids in dead.items():
                 final.append(Delete(rank, vids))
         self.instrs = final
 
 
-def lower(cap: Captured, mpmd_dim: int, schedule: BaseSchedule | None = None, name: str = "step") -> Program:
+def lower(cap: Captured, mpmd_dim: int, schedule: BaseSchedule | None = None, name: str = "step",
+          donated_inputs: set | None = None) -> Program:
     with log_elapsed_time("compile/lower"):
-        return Lowering(cap, mpmd_dim, name).run(schedule)
+        return Lowering(cap, mpmd_dim, name, donated_inputs).run(schedule)

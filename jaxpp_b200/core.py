@@ -64,8 +64,7 @@ class CompiledMpmd:
         self.n_leaves = n_leaves
         self.in_specs_flat = in_specs_flat
         self.out_specs_flat = out_specs_flat
-        self.donate_flat = donate_flat
-        self.multi = mesh.jax_mesh.is_multi_process or config.debug_force_mpmdify.value and False
+        self.donate_flat = donate_flat      # per tensor input: the caller gave the buffer up (donate_argnums/names)
         self._comm = None
         self.last_states = None
 
@@ -119,6 +118,24 @@ class CompiledMpmd:
         mesh = self.mesh
         prog = self.program
         tensors = [None if isinstance(leaves[p], ShapeDtypeStruct) else leaves[p] for p in self.tensor_positions]
+        donated_arrays = [x for x, d in zip(tensors, self.donate_flat or ()) if d and isinstance(x, (MpmdArray, DistArray))]
+        if not mesh.jax_mesh.is_multi_process and config.debug_force_mpmdify.value and mesh.unstack[0].size == 1:
+            # one process, but the per-rank programs of the multi-process path: every pipeline rank runs its own
+            # instruction list in a thread and talks to the others through in-process queues (reference:
+            # JAXPP_DEBUG_FORCE_MPMDIFY, src/jaxpp/core.py:3817-3820)
+            from .runtime.local_comm import run_scalarized_in_threads
+
+            flat_in = []
+            for x in tensors:
+                if isinstance(x, MpmdArray):
+                    x = x.local_tensor()
+                elif isinstance(x, DistArray):
+                    x = next(t for t in x.shards.values() if t is not None)
+                flat_in.append(x)
+            self._release_donated(donated_arrays)
+            states, outs = run_scalarized_in_threads(prog, flat_in, self._devices(), record_events)
+            self.last_states = states
+            return self._wrap_outputs(outs)
         if not mesh.jax_mesh.is_multi_process:
             if mesh.unstack[0].size != 1:
                 raise NotImplementedError(
@@ -132,6 +149,7 @@ class CompiledMpmd:
                 elif isinstance(x, DistArray):
                     x = next(t for t in x.shards.values() if t is not None)
                 flat_in.append(x)
+            self._release_donated(donated_arrays)
             states, outs = run_single_controller(prog, flat_in, devices, record_events)
             self.last_states = states
         else:
@@ -149,9 +167,23 @@ class CompiledMpmd:
                 elif isinstance(x, DistArray):
                     x = x.shards.get(mesh.my_device)
                 flat_in.append(x)
+            self._release_donated(donated_arrays)
+            del tensors
             st, outs = run_multi_controller(prog, rank, flat_in, device, self._comm, record_events)
             self.last_states = [st]
         return self._wrap_outputs(outs)
+
+    @staticmethod
+    def _release_donated(arrays):
+        """A donated argument is given up by the caller: the array objects passed in drop their buffers (they read as
+        deleted afterwards, like a donated ``jax.Array``), so that the program's own deletes free the memory at the
+        last use inside the step instead of when the caller lets go of the old state."""
+        for a in arrays:
+            try:
+                if not a.is_deleted():
+                    a.delete()
+            except AssertionError:
+                pass   # a metadata-only array of another pipeline rank: nothing to release here
 
     def _wrap_outputs(self, outs):
         mesh = self.mesh
@@ -183,7 +215,7 @@ class MpmdFunction:
     def __init__(self, fun: Callable, mpmd_mesh: MpmdMesh, with_loop: bool, in_specs=None, out_specs=None,
                  static_argnums: Sequence[int] = (), static_argnames: Sequence[str] = (),
                  donate_argnums: Sequence[int] = (), donate_argnames: Sequence[str] = (),
-                 schedule: BaseSchedule | None = None, name: str | None = None):
+                 schedule: BaseSchedule | None = None, name: str | None = None, compiler_options=None):
         self.fun = fun
         self.mpmd_mesh = mpmd_mesh
         self.with_loop = with_loop
@@ -195,6 +227,11 @@ class MpmdFunction:
         self.donate_argnames = tuple(donate_argnames)
         self.schedule = schedule
         self.name = name or getattr(fun, "__name__", "step")
+        self.compiler_options = dict(compiler_options or {})
+        if self.compiler_options:
+            # the reference forwards these to XLA; tasks here are kernel launches from generated Python, there is no
+            # compiler to configure
+            logger.warning("compiler_options %s have no effect: tasks are not XLA executables", sorted(self.compiler_options))
         self._cache: dict[Any, CompiledMpmd] = {}
 
     # -- compile -------------------------------------------------------------------------------
@@ -207,9 +244,36 @@ class MpmdFunction:
                 static[pos] = leaf
             else:
                 metas.append(m)
-        # arguments named static are baked in whole
+        # Every leaf that is not an array is static: it is baked into the program and is part of the cache key (a new
+        # value compiles a new program).  static_argnums / static_argnames are therefore only checked: an argument
+        # named static must not contain arrays (the reference requires static arguments to be hashable constants).
         key = (in_spec, tuple(metas), tuple(sorted((p, repr(v)) for p, v in static.items())))
         return leaves, in_spec, metas, static, key
+
+    def _arg_leaf_ranges(self, args, kwargs) -> tuple[dict, dict]:
+        """Flat leaf positions of every positional and keyword argument in the flattening of ``(args, kwargs)``."""
+        pos, by_num, by_name = 0, {}, {}
+        for i, a in enumerate(args):
+            n = len(pytree.tree_leaves(a, is_leaf=_is_leaf))
+            by_num[i] = range(pos, pos + n)
+            pos += n
+        for k, v in kwargs.items():
+            n = len(pytree.tree_leaves(v, is_leaf=_is_leaf))
+            by_name[k] = range(pos, pos + n)
+            pos += n
+        return by_num, by_name
+
+    def _selected_leaves(self, args, kwargs, nums, names, what: str) -> set:
+        by_num, by_name = self._arg_leaf_ranges(args, kwargs)
+        out: set = set()
+        for i in nums:
+            if i not in by_num:
+                raise ValueError(f"{what}_argnums names positional argument {i} but the call has {len(args)}")
+            out.update(by_num[i])
+        for k in names:
+            if k in by_name:
+                out.update(by_name[k])
+        return out
 
     def lower(self, *args, **kwargs) -> CompiledMpmd:
         leaves, in_spec, metas, static, key = self._prepare(args, kwargs)
@@ -217,17 +281,26 @@ class MpmdFunction:
         if hit is not None:
             return hit
         mesh = self.mpmd_mesh
+        config.warn_about_flags_without_effect(logger)
+        tensor_positions = [p for p in range(len(leaves)) if p not in static]
+        static_named = self._selected_leaves(args, kwargs, self.static_argnums, self.static_argnames, "static")
+        bad = sorted(p for p in static_named if p not in static)
+        if bad:
+            raise TypeError(f"static_argnums / static_argnames name an argument that contains arrays (flat leaves {bad}); "
+                            "static arguments must be Python constants")
+        donated_leaves = self._selected_leaves(args, kwargs, self.donate_argnums, self.donate_argnames, "donate")
+        donate_flat = [p in donated_leaves for p in tensor_positions]
         with mesh:
             cap = capture(self.fun, in_spec, metas, static, len(leaves))
             if self.with_loop and cap.trace.n_loops != 1:
                 raise AssertionError("mpmd_jit_with_loop needs exactly one treduce loop in the function")
-            program = lower(cap, mesh.mpmd_dim, self.schedule, self.name)
-        tensor_positions = [p for p in range(len(leaves)) if p not in static]
+            program = lower(cap, mesh.mpmd_dim, self.schedule, self.name,
+                            donated_inputs={k for k, d in enumerate(donate_flat) if d})
         in_specs_flat = self._flat_specs(self.in_specs, (args, kwargs), len(metas), leaves, tensor_positions)
         out_leaves_n = len(program.outputs)
         out_specs_flat = self._flat_out_specs(self.out_specs, cap.out_spec, out_leaves_n)
         compiled = CompiledMpmd(program, mesh, in_spec, cap.out_spec, tensor_positions, static, len(leaves),
-                                in_specs_flat, out_specs_flat, None)
+                                in_specs_flat, out_specs_flat, donate_flat)
         self._cache[key] = compiled
         if config.dump_dir.value:
             self._dump(compiled)
@@ -295,11 +368,18 @@ def mpmd_jit_with_loop(fun: Callable, mpmd_mesh: MpmdMesh, *, in_shardings=None,
                        out_specs=None, static_argnums=(), static_argnames=(), donate_argnums=(), donate_argnames=(),
                        compiler_options=None, name: str | None = None) -> MpmdFunction:
     """Compile a train step that contains exactly one :func:`~jaxpp_b200.training.treduce` loop into
-    one program per pipeline rank of ``mpmd_mesh`` (reference: core.py:3892-3923)."""
+    one program per pipeline rank of ``mpmd_mesh`` (reference: core.py:3892-3923).
+
+    ``donate_argnums`` / ``donate_argnames``: the caller gives these arguments' buffers up.  The program frees each of
+    them after its last use on every rank (instead of keeping program inputs alive for the whole step), and array
+    objects passed for them read as deleted after the call (reference: core.py:1732-1809, 3892-3923).
+    ``static_argnums`` / ``static_argnames``: every non-array leaf is a compile-time constant here anyway; the named
+    arguments are checked to contain no arrays.  ``compiler_options`` are kept on the returned object and otherwise
+    unused (there is no XLA executable to configure)."""
     _check_specs(in_specs, in_shardings, out_specs, out_shardings)
     return MpmdFunction(fun, mpmd_mesh, True, in_specs if in_specs is not None else _specs_of(in_shardings),
                         out_specs if out_specs is not None else _specs_of(out_shardings), static_argnums,
-                        static_argnames, donate_argnums, donate_argnames, name=name)
+                        static_argnames, donate_argnums, donate_argnames, name=name, compiler_options=compiler_options)
 
 
 def mpmd_jit_by_yield(fun: Callable, mpmd_mesh: MpmdMesh, *, in_shardings=None, in_specs=None, out_shardings=None,
@@ -310,7 +390,7 @@ def mpmd_jit_by_yield(fun: Callable, mpmd_mesh: MpmdMesh, *, in_shardings=None, 
     _check_specs(in_specs, in_shardings, out_specs, out_shardings)
     return MpmdFunction(fun, mpmd_mesh, False, in_specs if in_specs is not None else _specs_of(in_shardings),
                         out_specs if out_specs is not None else _specs_of(out_shardings), static_argnums,
-                        static_argnames, donate_argnums, donate_argnames, name=name)
+                        static_argnames, donate_argnums, donate_argnames, name=name, compiler_options=compiler_options)
 
 
 # ---------------------------------------------------------------------------------------------------

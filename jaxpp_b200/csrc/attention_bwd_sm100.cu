@@ -194,7 +194,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const uint64_t t0 = globaltimer_ns();
         for (int id = 0; id < K1_QE; ++id) {
           if (id == K1_KVE || !(armed & (1u << id))) continue;
-          while (!mbar_try_wait(&bar[id], (armed_phase >> id) & 1) && globaltimer_ns() - t0 < JPB_WAIT_BUDGET_NS) {
+          while (!mbar_try_wait(&bar[id], (armed_phase >> id) & 1) && globaltimer_ns() - t0 < wait_budget_ns()) {
           }
         }
       }
@@ -528,7 +528,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const uint64_t t0 = globaltimer_ns();
         for (int id = 0; id < K2_KE; ++id) {
           if (id == K2_QFREE || !(armed & (1u << id))) continue;
-          while (!mbar_try_wait(&bar[id], (armed_phase >> id) & 1) && globaltimer_ns() - t0 < JPB_WAIT_BUDGET_NS) {
+          while (!mbar_try_wait(&bar[id], (armed_phase >> id) & 1) && globaltimer_ns() - t0 < wait_budget_ns()) {
           }
         }
       }

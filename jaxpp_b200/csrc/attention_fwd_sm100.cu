@@ -144,7 +144,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const uint64_t t0 = globaltimer_ns();
         for (int id = 0; id < BAR_KE; ++id) {
           if (!(armed & (1u << id))) continue;
-          while (!mbar_try_wait(&bar[id], (armed_phase >> id) & 1) && globaltimer_ns() - t0 < JPB_WAIT_BUDGET_NS) {
+          while (!mbar_try_wait(&bar[id], (armed_phase >> id) & 1) && globaltimer_ns() - t0 < wait_budget_ns()) {
           }
         }
       }

@@ -61,7 +61,7 @@ __device__ __forceinline__ bool ar_wait_all(const int* flags, int n_ranks, int r
       if (q == rank) continue;
       uint32_t spins = 0;
       while (ar_ld_acquire_sys(flags + q) < epoch) {
-        if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > JPB_WAIT_BUDGET_NS) {
+        if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > wait_budget_ns()) {
           if (status) atomicCAS(status, JPB_OK, JPB_ERR_PEER_TIMEOUT);
           ok = 0;
           break;
@@ -206,15 +206,24 @@ struct JpbAllReduceDesc {
 
 JPB_API int jpb_allreduce_desc_bytes() { return int(sizeof(JpbAllReduceDesc)); }
 
-JPB_API int jpb_allreduce_grid(long long n_elems, int elem_bytes) {
-  int dev = 0, sms = 0;
+// Grid of an all-reduce over `n_elems` elements.  The kernel's CTAs wait for one another (the last one to finish
+// phase 1 raises the flags the others poll), so all of them must be resident at once: at most one 512-thread CTA
+// per SM, checked against the occupancy calculator, less `reserved_sms` SMs left to kernels of other streams.
+JPB_API int jpb_allreduce_grid2(long long n_elems, int elem_bytes, int reserved_sms) {
+  int dev = 0, sms = 0, per_sm = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, jpb::allreduce_kernel<float>, 512, 0) != cudaSuccess || per_sm < 1)
+    return 1;   // cannot show that more than one CTA fits: a grid of one needs no co-residency
+  if (reserved_sms < 0) reserved_sms = 0;
+  if (reserved_sms > sms - 1) reserved_sms = sms - 1;
+  const long long cap = sms - reserved_sms;
   const long long nvec = n_elems * elem_bytes / 16;
   long long blocks = (nvec + 511) / 512;
   if (blocks < 1) blocks = 1;
-  return int(blocks < sms ? blocks : sms);  // one resident CTA per SM at most: all CTAs must be co-resident
+  return int(blocks < cap ? blocks : cap);
 }
+JPB_API int jpb_allreduce_grid(long long n_elems, int elem_bytes) { return jpb_allreduce_grid2(n_elems, elem_bytes, 0); }
 
 // In-place semantics on the staged symmetric buffers; `out` receives scale * sum over ranks.
 // n must be a multiple of (16 / elem_bytes) * n_ranks.

@@ -19,12 +19,19 @@ enum JpbStatus : int {
   JPB_ERR_PEER_TIMEOUT = 3,   // a bounded wait on a peer GPU's flag ran out
 };
 
-// Longest time a device-side wait may spin before the kernel gives up (nanoseconds).
+// Longest time a device-side wait may spin before the kernel gives up (nanoseconds): the value a device starts
+// with.  jpb_set_wait_budget_ns() changes it at run time (per device).
 #ifndef JPB_WAIT_BUDGET_NS
 #define JPB_WAIT_BUDGET_NS 4000000000ull
 #endif
 
 namespace jpb {
+
+// The budget lives in device memory, one copy per translation unit of the library (the library is linked without
+// relocatable device code, so a device variable cannot be shared between .cu files); the host-side registration
+// at the end of this header lets jpb_set_wait_budget_ns() update every copy.
+static __device__ unsigned long long g_wait_budget_ns = JPB_WAIT_BUDGET_NS;
+__device__ __forceinline__ uint64_t wait_budget_ns() { return g_wait_budget_ns; }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -76,7 +83,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3ff) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > JPB_WAIT_BUDGET_NS) {
+      if (globaltimer_ns() - t0 > wait_budget_ns()) {
         *abort_flag = 1;
         if (status) atomicCAS(status, JPB_OK, code);
         return false;
@@ -252,3 +259,16 @@ int* jpb_status_device_ptr();
 // Encode a 2-D..4-D tiled tensor map; returns 0 on success.
 int jpb_make_tensor_map(CUtensorMap* out, const void* base, int elem_bytes, int rank, const uint64_t* dims,
                         const uint64_t* strides_bytes /* rank-1 entries */, const uint32_t* box, int swizzle_128b);
+
+// ---- run-time wait budget: every translation unit registers a setter for its own copy of the variable ------------
+typedef int (*JpbWaitBudgetSetter)(unsigned long long);
+void jpb_register_wait_budget_setter(JpbWaitBudgetSetter fn);  // defined in runtime.cu
+namespace {
+inline int jpb_tu_set_wait_budget(unsigned long long ns) {
+  return int(cudaMemcpyToSymbol(jpb::g_wait_budget_ns, &ns, sizeof(ns)));
+}
+struct JpbWaitBudgetRegistration {
+  JpbWaitBudgetRegistration() { jpb_register_wait_budget_setter(&jpb_tu_set_wait_budget); }
+};
+static JpbWaitBudgetRegistration jpb_wait_budget_registration;
+}  // namespace

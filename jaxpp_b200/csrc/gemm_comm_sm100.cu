@@ -85,7 +85,7 @@ __device__ __forceinline__ void st_release_sys(int* p, int v) {
 }
 __device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
-// Spin until *flag >= want (flags only grow), at most JPB_WAIT_BUDGET_NS.  The poll is a relaxed load and one
+// Spin until *flag >= want (flags only grow), at most the wait budget (jpb_set_wait_budget_ns).  The poll is a relaxed load and one
 // acquire fence follows the successful one: an acquire load at system scope per poll measured about 2 us each
 // on this hardware, which added up to tens of microseconds per CTA in the reduction-gather.
 __device__ __forceinline__ bool flag_wait_bounded(const int* flag, int want, bool sys, volatile int* abort_flag, int* status,
@@ -103,7 +103,7 @@ __device__ __forceinline__ bool flag_wait_bounded(const int* flag, int want, boo
       if (*abort_flag) return false;
       const uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > JPB_WAIT_BUDGET_NS) {
+      if (now - t0 > wait_budget_ns()) {
         *abort_flag = 1;
         if (status) atomicCAS(status, JPB_OK, code);
         return false;
@@ -127,7 +127,7 @@ __device__ __forceinline__ bool flag_wait4_bounded(const int* flags, int want, v
       if (*abort_flag) return false;
       const uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > JPB_WAIT_BUDGET_NS) {
+      if (now - t0 > wait_budget_ns()) {
         *abort_flag = 1;
         if (status) atomicCAS(status, JPB_OK, code);
         return false;
@@ -167,7 +167,7 @@ __device__ __forceinline__ bool flags_wait_all_bounded(const int* flags, int cou
       if (*abort_flag) return false;
       const uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > JPB_WAIT_BUDGET_NS) {
+      if (now - t0 > wait_budget_ns()) {
         *abort_flag = 1;
         if (status) atomicCAS(status, JPB_OK, code);
         return false;
@@ -380,7 +380,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const uint64_t t0 = globaltimer_ns();
         for (int s = 0; s < CSTAGES; ++s) {
           if (!(armed & (1u << s))) continue;
-          while (!mbar_try_wait(&full[s], (armed_phase >> s) & 1) && globaltimer_ns() - t0 < JPB_WAIT_BUDGET_NS) {
+          while (!mbar_try_wait(&full[s], (armed_phase >> s) & 1) && globaltimer_ns() - t0 < wait_budget_ns()) {
           }
         }
       }

@@ -153,7 +153,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         for (int s = 0; s < STAGES; ++s) {
           if (!(armed & (1u << s))) continue;
           const uint32_t ph = (armed_phase >> s) & 1;
-          while (!mbar_try_wait(&full[s], ph) && globaltimer_ns() - t0 < JPB_WAIT_BUDGET_NS) {
+          while (!mbar_try_wait(&full[s], ph) && globaltimer_ns() - t0 < wait_budget_ns()) {
           }
         }
       }

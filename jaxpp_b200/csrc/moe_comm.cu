@@ -83,7 +83,7 @@ __device__ __forceinline__ bool moe_wait_peer(const MoeParams& p, int q, int lan
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (moe_ld_acquire_sys(p.flags_local + q) < p.epoch) {
-      if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > JPB_WAIT_BUDGET_NS) {
+      if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > wait_budget_ns()) {
         if (p.status) atomicCAS(p.status, JPB_OK, JPB_ERR_PEER_TIMEOUT);
         ok = 0;
         break;
@@ -93,7 +93,7 @@ __device__ __forceinline__ bool moe_wait_peer(const MoeParams& p, int q, int lan
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
-__global__ void __launch_bounds__(MOE_THREADS) moe_dispatch_kernel(const MoeParams p) {
+__global__ void __launch_bounds__(MOE_THREADS, 4) moe_dispatch_kernel(const MoeParams p) {
   const int lane = threadIdx.x & 31;
   const int warp_g = (blockIdx.x * MOE_THREADS + threadIdx.x) >> 5;
   const int n_warps = (gridDim.x * MOE_THREADS) >> 5;
@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_dispatch_kernel(const MoePara
   }
 }
 
-__global__ void __launch_bounds__(MOE_THREADS) moe_combine_kernel(const MoeParams p) {
+__global__ void __launch_bounds__(MOE_THREADS, 4) moe_combine_kernel(const MoeParams p) {
   const int lane = threadIdx.x & 31;
   const int warp_g = (blockIdx.x * MOE_THREADS + threadIdx.x) >> 5;
   const int n_warps = (gridDim.x * MOE_THREADS) >> 5;
@@ -203,7 +203,8 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_combine_kernel(const MoeParam
 
 // Control block: [0..7] flags written by peers, [8] local CTA counter.
 struct JpbMoeDesc {
-  int n_ranks, rank, epoch, pad;
+  int n_ranks, rank, epoch;
+  int reserved_sms;  // SMs kept out of the grid for kernels of other streams
   void* ctrl[8];
   void* recv[8];   // receive buffer (current parity) of every rank, E*C*d bf16 each
 };
@@ -228,11 +229,20 @@ static int moe_fill(jpb::MoeParams& p, const JpbMoeDesc* desc, int n_experts, in
   return 0;
 }
 
-static int moe_grid() {
-  int dev = 0, sms = 0;
+// Phase 2 of both kernels waits for flags that a peer raises only after ALL of its CTAs have finished phase 1, so
+// every CTA of the grid has to be resident at once: the grid is what the occupancy calculator says fits (at most
+// four CTAs per SM), less `reserved_sms` SMs left to kernels of other streams (point-to-point transfers).
+template <typename K>
+static int moe_grid(K kernel, int reserved_sms) {
+  int dev = 0, sms = 0, per_sm = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  return sms * 4;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, jpb::MOE_THREADS, 0) != cudaSuccess || per_sm < 1)
+    per_sm = 1;
+  if (per_sm > 4) per_sm = 4;
+  if (reserved_sms < 0) reserved_sms = 0;
+  if (reserved_sms > sms - 1) reserved_sms = sms - 1;
+  return (sms - reserved_sms) * per_sm;
 }
 
 JPB_API int jpb_moe_dispatch(const void* x, const int* src_of_slot, const float* slot_scale, void* out, int n_tokens,
@@ -242,7 +252,7 @@ JPB_API int jpb_moe_dispatch(const void* x, const int* src_of_slot, const float*
   if (rc) return rc;
   p.in = static_cast<const __nv_bfloat16*>(x); p.index = src_of_slot; p.scale = slot_scale;
   p.out = static_cast<__nv_bfloat16*>(out);
-  jpb::moe_dispatch_kernel<<<moe_grid(), jpb::MOE_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  jpb::moe_dispatch_kernel<<<moe_grid(jpb::moe_dispatch_kernel, desc->reserved_sms), jpb::MOE_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return int(cudaGetLastError());
 }
 
@@ -253,7 +263,7 @@ JPB_API int jpb_moe_combine(const void* y, const int* dest, const float* weights
   if (rc) return rc;
   p.in = static_cast<const __nv_bfloat16*>(y); p.index = dest; p.scale = weights;
   p.out = static_cast<__nv_bfloat16*>(out); p.picked = static_cast<__nv_bfloat16*>(picked);
-  jpb::moe_combine_kernel<<<moe_grid(), jpb::MOE_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  jpb::moe_combine_kernel<<<moe_grid(jpb::moe_combine_kernel, desc->reserved_sms), jpb::MOE_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return int(cudaGetLastError());
 }
 
@@ -269,7 +279,7 @@ constexpr int ROUTER_MAX_E = 64;
 template <typename T>
 __global__ void router_kernel(const T* __restrict__ logits, float* __restrict__ probs, long long* __restrict__ top_i,
                               float* __restrict__ weights, float* __restrict__ prob_sum, float* __restrict__ hits, int n_tok,
-                              int E, int k) {
+                              int E, int k, int* status) {
   __shared__ float s_prob[ROUTER_MAX_E];
   __shared__ float s_hits[ROUTER_MAX_E];
   for (int e = threadIdx.x; e < E; e += blockDim.x) { s_prob[e] = 0.f; s_hits[e] = 0.f; }
@@ -296,6 +306,14 @@ __global__ void router_kernel(const T* __restrict__ logits, float* __restrict__ 
       float bv = -1.f;
       for (int e = 0; e < E; ++e)
         if (!((taken >> e) & 1ull) && p[e] > bv) { bv = p[e]; best = e; }   // ties: lowest index, like torch.topk
+      if (best < 0) {
+        // no comparison succeeded: the probabilities are not finite (NaN logits of a diverged step).  Take the
+        // lowest expert not yet picked, so that every index stays in range, and report through the status word.
+        for (int e = 0; e < E && best < 0; ++e)
+          if (!((taken >> e) & 1ull)) best = e;
+        bv = 0.f;
+        if (status) atomicCAS(status, JPB_OK, JPB_ERR_BAD_ARGUMENT);
+      }
       taken |= 1ull << best;
       idx[j] = best; val[j] = bv; picked += bv;
       atomicAdd(&s_hits[best], 1.f);
@@ -316,7 +334,8 @@ __global__ void router_kernel(const T* __restrict__ logits, float* __restrict__ 
 }  // namespace jpb
 
 // logits [n_tok, E] (fp32 dtype 0 or bf16 dtype 1) -> probs [n_tok, E] fp32, top_i [n_tok, k] int64, weights [n_tok, k]
-// fp32, prob_sum [E] and hits [E] fp32 (both zeroed here).  E <= 64, k <= 8.
+// fp32, prob_sum [E] and hits [E] fp32 (both zeroed here).  E <= 64, k <= 8.  A token whose probabilities are not
+// finite gets the lowest-numbered experts (indices stay in range) and the status word is set to JPB_ERR_BAD_ARGUMENT.
 JPB_API int jpb_router(int dtype, const void* logits, float* probs, long long* top_i, float* weights, float* prob_sum,
                        float* hits, int n_tok, int E, int k, void* stream) {
   using namespace jpb;
@@ -326,9 +345,10 @@ JPB_API int jpb_router(int dtype, const void* logits, float* probs, long long* t
   cudaMemsetAsync(hits, 0, sizeof(float) * E, s);
   const int threads = 128, blocks = (n_tok + threads - 1) / threads;
   if (dtype == 0)
-    router_kernel<float><<<blocks, threads, 0, s>>>(static_cast<const float*>(logits), probs, top_i, weights, prob_sum, hits, n_tok, E, k);
+    router_kernel<float><<<blocks, threads, 0, s>>>(static_cast<const float*>(logits), probs, top_i, weights, prob_sum, hits, n_tok, E, k,
+                                         jpb_status_device_ptr());
   else
     router_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>(static_cast<const __nv_bfloat16*>(logits), probs, top_i, weights,
-                                                            prob_sum, hits, n_tok, E, k);
+                                                            prob_sum, hits, n_tok, E, k, jpb_status_device_ptr());
   return int(cudaGetLastError());
 }

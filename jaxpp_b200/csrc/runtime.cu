@@ -76,6 +76,36 @@ JPB_API int jpb_read_status(int clear) {
   return v;
 }
 
+// ---- run-time wait budget ----------------------------------------------------------------------------------------
+// Every .cu file of the library holds its own copy of the device variable (see common.cuh) and registers a setter
+// for it during static initialisation; the table is a function-local static so that it exists before the first
+// registration whatever the initialisation order of the object files.
+struct BudgetSetters {
+  JpbWaitBudgetSetter fn[32];
+  int n = 0;
+};
+static BudgetSetters& budget_setters() {
+  static BudgetSetters table;
+  return table;
+}
+void jpb_register_wait_budget_setter(JpbWaitBudgetSetter fn) {
+  BudgetSetters& t = budget_setters();
+  if (t.n < 32) t.fn[t.n++] = fn;
+}
+
+// Longest time any device-side wait of this library may spin on the CURRENT device before its kernel gives up,
+// records a status and returns (default 4 s).  Takes effect for kernels launched after the call; a value of 0 is
+// rejected.  Returns 0 or the first CUDA error.
+JPB_API int jpb_set_wait_budget_ns(unsigned long long ns) {
+  if (ns == 0) return -JPB_ERR_BAD_ARGUMENT;
+  BudgetSetters& t = budget_setters();
+  for (int i = 0; i < t.n; ++i) {
+    int rc = t.fn[i](ns);
+    if (rc != 0) return rc;
+  }
+  return 0;
+}
+
 JPB_API int jpb_num_sms() {
   int dev = 0, n = 0;
   cudaGetDevice(&dev);

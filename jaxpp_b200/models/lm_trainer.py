@@ -43,15 +43,25 @@ class Hyper:
 
 
 def stage_of_layer(cfg: tf.ModelConfig, layer: int) -> int:
-    return layer // cfg.layers_per_stage
+    return cfg.stage_of_layer(layer)
 
 
 def owner_ranks(cfg: tf.ModelConfig, schedule) -> dict:
-    """Pipeline rank of every parameter group: ``{"embed": r, "head": r, layer index: r}``."""
-    out: dict[Any, int] = {i: int(schedule.get_mpmd_idx(stage_of_layer(cfg, i))) for i in range(cfg.n_layers)}
+    """Pipeline rank of every parameter group: ``{"embed": r, "head": r, layer index: r, (layer index, half): r}`` with half 0 for
+    the parameters of a block's attention half and 1 for those of its feed-forward half (a stage boundary may fall
+    between the two, ``ModelConfig.stage_layers``); ``owner_of(owners, layer, key)`` looks a parameter up."""
+    out: dict[Any, int] = {}
+    for i in range(cfg.n_layers):
+        out[i] = int(schedule.get_mpmd_idx(cfg.stage_of_layer(i)))   # a whole block (its attention half when cut)
+        for half in (0, 1):
+            out[(i, half)] = int(schedule.get_mpmd_idx(cfg.stage_of_half(2 * i + half)))
     out["embed"] = int(schedule.get_mpmd_idx(0))
     out["head"] = int(schedule.get_mpmd_idx(cfg.n_stages - 1))
     return out
+
+
+def owner_of(owners: dict, layer: int, key: str) -> int:
+    return owners[(layer, 0 if key in tf.ATTN_HALF_KEYS else 1)]
 
 
 def init_state(cfg: tf.ModelConfig, schedule, device, my_rank: int | None = None, tp_rank: int = 0, seed: int = 0) -> dict:
@@ -64,9 +74,12 @@ def init_state(cfg: tf.ModelConfig, schedule, device, my_rank: int | None = None
     mine = lambda key: my_rank is None or owners[key] == my_rank
     tied_extra = cfg.tie_embeddings and my_rank is not None and owners["head"] == my_rank
     full = tf.init_params(cfg, "meta", seed, tp_rank)  # structure and shapes only
-    local_layers = [i for i in range(cfg.n_layers) if mine(i)]
+    local_layers = [i for i in range(cfg.n_layers) if mine((i, 0)) or mine((i, 1))]
     real = tf.init_params(cfg, device, seed, tp_rank, layers=local_layers, with_embed=mine("embed") or tied_extra,
                           with_head=mine("head"))
+    for name, layer in real["layers"].items():   # a block cut by a stage boundary: keep the half this rank runs
+        for k in [k for k in layer if not mine((int(name), 0 if k in tf.ATTN_HALF_KEYS else 1))]:
+            del layer[k]
 
     def pick(path_keys, meta_leaf):
         node = real
@@ -193,7 +206,7 @@ def _clip_coefficient(cfg: tf.ModelConfig, schedule, params: dict, flat_g: list,
     for k, v in params.items():
         if k == "layers":
             for name, ld in v.items():
-                paths.extend((owners[int(name)], kk) for kk in ld)
+                paths.extend((owner_of(owners, int(name), kk), kk) for kk in ld)
         else:
             paths.append((owners["embed" if k in ("embed", "pos") else "head"], k))
     assert len(paths) == len(flat_g)

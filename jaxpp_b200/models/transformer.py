@@ -13,7 +13,7 @@ size ``tp`` the layers follow the Megatron sequence-parallel recipe: activations
 over tokens, column-parallel linears gather them (``ag_linear``), row-parallel linears reduce-scatter
 their output (``linear_rs``); parameters that are replicated across the axis (norm weights, embeddings,
 LM head) get their gradients summed with :func:`sync_replicated_grads`.  Stage boundaries are marked with
-``mark_stage_end`` every ``layers_per_stage`` layers.
+``mark_stage_end`` after the last block of every stage (``ModelConfig.stage_sizes``; equal stages by default).
 """
 from __future__ import annotations
 
@@ -26,6 +26,10 @@ import torch
 from ..ops import core as ops
 from ..parallel import tp as tpops
 from ..pipelining import mark_stage_end
+
+
+# parameters of a block that its attention half uses; the others belong to the feed-forward half
+ATTN_HALF_KEYS = frozenset({"attn_norm", "wqkv", "wo", "b_qkv", "b_o", "ln1_w", "ln1_b"})
 
 
 @dataclasses.dataclass(frozen=True)
@@ -63,6 +67,22 @@ class ModelConfig:
     cp: int = 1
     cp_axis: str = "data"
     cp_layout: str = "contiguous"   # or "zigzag": pieces r and 2*cp-1-r per rank, which balances causal attention
+    # size of every pipeline stage in blocks (``n_stages`` entries that sum to ``n_layers``; None = equal stages).  An
+    # entry may end in .5: a block is two halves, the attention half (norm, qkv, attention, output projection, residual)
+    # and the feed-forward half, and a stage boundary may fall between them.  The first stage also embeds the tokens and
+    # the last one carries the final norm, the output projection and the cross entropy, so equal block counts leave
+    # the rank that holds the last stage busier than the rest; ``balanced_stage_layers`` picks sizes that even out
+    # the pipeline ranks' total work.
+    stage_layers: tuple | None = None
+
+    def __post_init__(self):
+        if self.stage_layers is not None:
+            sl = tuple(float(n) for n in self.stage_layers)
+            if (len(sl) != self.n_stages or abs(sum(sl) - self.n_layers) > 1e-9 or min(sl) < 0.5
+                    or any(abs(2 * n - round(2 * n)) > 1e-9 for n in sl)):
+                raise ValueError(f"stage_layers {sl} must have n_stages={self.n_stages} entries that are multiples of 0.5, "
+                                 f"at least 0.5 each, and sum to n_layers={self.n_layers}")
+            object.__setattr__(self, "stage_layers", tuple(int(n) if n == int(n) else n for n in sl))
 
     @property
     def head_dim(self) -> int:
@@ -70,8 +90,42 @@ class ModelConfig:
 
     @property
     def layers_per_stage(self) -> int:
+        """Blocks per stage when the stages are equal (see ``stage_sizes`` for the general case)."""
+        if self.stage_layers is not None and len(set(self.stage_layers)) > 1:
+            raise ValueError("stages have different sizes: use stage_sizes / stage_of_half")
         assert self.n_layers % self.n_stages == 0
         return self.n_layers // self.n_stages
+
+    @property
+    def stage_sizes(self) -> tuple:
+        if self.stage_layers is not None:
+            return self.stage_layers
+        assert self.n_layers % self.n_stages == 0, "n_layers must be a multiple of n_stages (or give stage_layers)"
+        return (self.n_layers // self.n_stages,) * self.n_stages
+
+    @property
+    def stage_ends_half(self) -> tuple:
+        """For every stage, one past its last half-block (half-block 2*i is the attention half of block i,
+        2*i + 1 its feed-forward half)."""
+        out, acc = [], 0
+        for n in self.stage_sizes:
+            acc += int(round(2 * n))
+            out.append(acc)
+        return tuple(out)
+
+    def stage_of_half(self, half: int) -> int:
+        for s, end in enumerate(self.stage_ends_half):
+            if half < end:
+                return s
+        raise IndexError(half)
+
+    def stage_of_layer(self, layer: int) -> int:
+        """Stage of a block that is not cut by a stage boundary (of its attention half otherwise)."""
+        return self.stage_of_half(2 * layer)
+
+    def stage_of_param(self, layer: int, key: str) -> int:
+        """Stage that uses parameter ``key`` of block ``layer``."""
+        return self.stage_of_half(2 * layer + (0 if key in ATTN_HALF_KEYS else 1))
 
     @property
     def padded_vocab(self) -> int:
@@ -94,6 +148,61 @@ class ModelConfig:
         matmul = 6.0 * (self.n_layers * (attn_w + mlp_w) + head)
         attn = 12.0 * self.n_layers * self.n_heads * hd * self.seq * (0.5 if self.causal else 1.0)
         return matmul + attn
+
+
+def rank_loads(sizes, stage_to_rank, n_ranks: int, attn_share: float, first_extra: float, last_extra: float) -> list:
+    """Work per pipeline rank, in blocks, of stages of ``sizes`` blocks (entries may end in .5) placed by
+    ``stage_to_rank``.  The attention half of a block costs ``attn_share`` of a block; the first stage carries
+    ``first_extra`` and the last one ``last_extra`` blocks' worth of other work."""
+    loads = [0.0] * n_ranks
+    half = 0
+    for s, n in enumerate(sizes):
+        cost = 0.0
+        for _ in range(int(round(2 * n))):
+            cost += attn_share if half % 2 == 0 else 1.0 - attn_share
+            half += 1
+        if s == 0:
+            cost += first_extra
+        if s == len(sizes) - 1:
+            cost += last_extra
+        loads[stage_to_rank(s)] += cost
+    return loads
+
+
+def balanced_stage_layers(n_layers: int, n_stages: int, stage_to_rank=None, n_ranks: int | None = None,
+                          first_extra: float = 0.0, last_extra: float = 0.0, attn_share: float = 0.36,
+                          max_shift: float = 1.0, tolerance: float = 0.05) -> tuple:
+    """Stage sizes (blocks, multiples of 0.5) that minimise the work of the busiest pipeline rank -- what paces a
+    pipeline in its steady state -- when the first stage carries ``first_extra`` and the last stage ``last_extra``
+    blocks' worth of other work (embedding; final norm + output projection + cross entropy).
+
+    ``stage_to_rank`` is the schedule's placement (``schedule.get_mpmd_idx``; default: one stage per rank).  Every
+    boundary moves at most ``max_shift`` blocks away from the equal split; among splits whose busiest rank is within
+    ``tolerance`` blocks of the best the one closest to equal wins.  With measured task times the extras are
+    ``t_head / t_block`` etc.
+    """
+    if n_layers % n_stages:
+        raise ValueError("the equal split needs n_layers to be a multiple of n_stages")
+    if stage_to_rank is None:
+        stage_to_rank, n_ranks = (lambda s: s), n_stages
+    if n_ranks is None:
+        n_ranks = max(stage_to_rank(s) for s in range(n_stages)) + 1
+    per = 2 * (n_layers // n_stages)                      # half-blocks per stage of the equal split
+    shifts = range(-int(round(2 * max_shift)), int(round(2 * max_shift)) + 1)
+    best = None
+    import itertools
+
+    for combo in itertools.product(shifts, repeat=n_stages - 1):
+        cuts = [per * (k + 1) + d for k, d in enumerate(combo)]
+        bounds = [0] + cuts + [2 * n_layers]
+        if any(b1 - b0 < 1 for b0, b1 in zip(bounds, bounds[1:])):
+            continue
+        sizes = tuple((b1 - b0) / 2 for b0, b1 in zip(bounds, bounds[1:]))
+        loads = rank_loads(sizes, stage_to_rank, n_ranks, attn_share, first_extra, last_extra)
+        key = (int(max(loads) / tolerance + 1e-6), sum(abs(d) for d in combo), combo)
+        if best is None or key < best[0]:
+            best = (key, sizes)
+    return tuple(int(n) if n == int(n) else n for n in best[1])
 
 
 # presets named after the shapes in the benchmark configurations
@@ -219,53 +328,75 @@ def _attention(cfg: ModelConfig, qkv: torch.Tensor, batch: int, rope) -> torch.T
     return o.view(-1, hq * hd)
 
 
-def llama_block(cfg: ModelConfig, p: dict, x: torch.Tensor, batch: int, rope) -> torch.Tensor:
+# Every block is two halves with the residual stream as their only link, so that a pipeline stage boundary can fall
+# between them: ``<family>_attn(cfg, p, x, batch, rope) -> x`` and ``<family>_ffn(cfg, p, x) -> x`` (mixtral: (x, aux)).
+def llama_attn(cfg: ModelConfig, p: dict, x: torch.Tensor, batch: int, rope) -> torch.Tensor:
     h = ops.rmsnorm(x, p["attn_norm"], cfg.eps)[0]
     qkv = tpops.column_linear(h, p["wqkv"], None, cfg)
     a = _attention(cfg, qkv, batch, rope)
-    x = x + tpops.row_linear(a, p["wo"], None, cfg)
+    return x + tpops.row_linear(a, p["wo"], None, cfg)
+
+
+def llama_ffn(cfg: ModelConfig, p: dict, x: torch.Tensor) -> torch.Tensor:
     h = ops.rmsnorm(x, p["ffn_norm"], cfg.eps)[0]
     gu = tpops.column_linear(h, p["w_up"], None, cfg)
-    x = x + tpops.row_linear(ops.swiglu(gu), p["w_down"], None, cfg)
-    return x
+    return x + tpops.row_linear(ops.swiglu(gu), p["w_down"], None, cfg)
 
 
-def mixtral_block(cfg: ModelConfig, p: dict, x: torch.Tensor, batch: int, rope):
-    """Llama attention + top-k mixture-of-experts SwiGLU FFN; returns (x, load-balancing loss of this block)."""
+def llama_block(cfg: ModelConfig, p: dict, x: torch.Tensor, batch: int, rope) -> torch.Tensor:
+    return llama_ffn(cfg, p, llama_attn(cfg, p, x, batch, rope))
+
+
+def mixtral_ffn(cfg: ModelConfig, p: dict, x: torch.Tensor):
     from ..parallel import moe
 
-    h = ops.rmsnorm(x, p["attn_norm"], cfg.eps)[0]
-    qkv = tpops.column_linear(h, p["wqkv"], None, cfg)
-    a = _attention(cfg, qkv, batch, rope)
-    x = x + tpops.row_linear(a, p["wo"], None, cfg)
     h = ops.rmsnorm(x, p["ffn_norm"], cfg.eps)[0]
     y, aux = moe.moe_ffn(h, {"router": p["router"], "w_up": p["e_up"], "w_down": p["e_down"]}, cfg.n_experts, cfg.top_k,
                          cfg.capacity_factor, cfg.ep, cfg.ep_axis)
     return x + y, aux
 
 
-def gpt2_block(cfg: ModelConfig, p: dict, x: torch.Tensor, batch: int, rope) -> torch.Tensor:
+def mixtral_block(cfg: ModelConfig, p: dict, x: torch.Tensor, batch: int, rope):
+    """Llama attention + top-k mixture-of-experts SwiGLU FFN; returns (x, load-balancing loss of this block)."""
+    return mixtral_ffn(cfg, p, llama_attn(cfg, p, x, batch, rope))
+
+
+def gpt2_attn(cfg: ModelConfig, p: dict, x: torch.Tensor, batch: int, rope) -> torch.Tensor:
     h = ops.layernorm(x, p["ln1_w"], p["ln1_b"], cfg.eps)[0]
     qkv = tpops.column_linear(h, p["wqkv"], p["b_qkv"], cfg)
     a = _attention(cfg, qkv, batch, None)
-    x = x + tpops.row_linear(a, p["wo"], p["b_o"], cfg)
+    return x + tpops.row_linear(a, p["wo"], p["b_o"], cfg)
+
+
+def gpt2_ffn(cfg: ModelConfig, p: dict, x: torch.Tensor) -> torch.Tensor:
     h = ops.layernorm(x, p["ln2_w"], p["ln2_b"], cfg.eps)[0]
     u = ops.gelu(tpops.column_linear(h, p["w_up"], p["b_up"], cfg))
-    x = x + tpops.row_linear(u, p["w_down"], p["b_down"], cfg)
-    return x
+    return x + tpops.row_linear(u, p["w_down"], p["b_down"], cfg)
+
+
+def gpt2_block(cfg: ModelConfig, p: dict, x: torch.Tensor, batch: int, rope) -> torch.Tensor:
+    return gpt2_ffn(cfg, p, gpt2_attn(cfg, p, x, batch, rope))
+
+
+def encoder_attn(cfg: ModelConfig, p: dict, x: torch.Tensor, batch: int, rope) -> torch.Tensor:
+    qkv = tpops.column_linear(x, p["wqkv"], p["b_qkv"], cfg)
+    a = _attention(cfg, qkv, batch, None)
+    return ops.layernorm(x + tpops.row_linear(a, p["wo"], p["b_o"], cfg), p["ln1_w"], p["ln1_b"], cfg.eps)[0]
+
+
+def encoder_ffn(cfg: ModelConfig, p: dict, x: torch.Tensor) -> torch.Tensor:
+    u = ops.gelu(tpops.column_linear(x, p["w_up"], p["b_up"], cfg))
+    return ops.layernorm(x + tpops.row_linear(u, p["w_down"], p["b_down"], cfg), p["ln2_w"], p["ln2_b"], cfg.eps)[0]
 
 
 def encoder_block(cfg: ModelConfig, p: dict, x: torch.Tensor, batch: int, rope) -> torch.Tensor:
     """Post-LayerNorm block: x = LN(x + Attn(x)); x = LN(x + FFN(x))."""
-    qkv = tpops.column_linear(x, p["wqkv"], p["b_qkv"], cfg)
-    a = _attention(cfg, qkv, batch, None)
-    x = ops.layernorm(x + tpops.row_linear(a, p["wo"], p["b_o"], cfg), p["ln1_w"], p["ln1_b"], cfg.eps)[0]
-    u = ops.gelu(tpops.column_linear(x, p["w_up"], p["b_up"], cfg))
-    x = ops.layernorm(x + tpops.row_linear(u, p["w_down"], p["b_down"], cfg), p["ln2_w"], p["ln2_b"], cfg.eps)[0]
-    return x
+    return encoder_ffn(cfg, p, encoder_attn(cfg, p, x, batch, rope))
 
 
-_BLOCKS = {"llama": llama_block, "gpt2": gpt2_block, "encoder": encoder_block}
+_BLOCKS = {"llama": llama_block, "gpt2": gpt2_block, "encoder": encoder_block, "mixtral": mixtral_block}
+_HALVES = {"llama": (llama_attn, llama_ffn), "gpt2": (gpt2_attn, gpt2_ffn), "encoder": (encoder_attn, encoder_ffn),
+           "mixtral": (llama_attn, mixtral_ffn)}
 
 
 class _Recompute(torch.autograd.Function):
@@ -318,25 +449,40 @@ def _maybe_recompute(cfg: ModelConfig, block, p: dict, x: torch.Tensor, batch: i
     return _Recompute.apply(fn, x, *[p[k] for k in keys], *rope_t)
 
 
-def run_layers(cfg: ModelConfig, params: dict, x: torch.Tensor, batch: int, rope=None) -> torch.Tensor:
-    """Apply every block in ``params['layers']`` with a stage marker after each ``layers_per_stage``."""
-    per = cfg.layers_per_stage
-    if cfg.family == "mixtral":
-        aux = torch.zeros((), dtype=torch.float32, device=x.device)
-        for name in sorted(params["layers"]):
-            i = int(name)
-            x, a = _maybe_recompute(cfg, mixtral_block, params["layers"][name], x, batch, rope)
-            aux = aux + a
-            if (i + 1) % per == 0 and (i + 1) < cfg.n_layers:
-                x, aux = mark_stage_end((x, aux))
-        return x, aux
+def run_layers(cfg: ModelConfig, params: dict, x: torch.Tensor, batch: int, rope=None):
+    """Apply every block in ``params['layers']`` with a stage marker at the end of every stage but the final one
+    (whose marker follows the loss).  A stage may end between the two halves of a block (``ModelConfig.stage_layers``);
+    such a block runs (and, with ``recompute``, is recomputed) as two halves, every other block as one unit.
+    Returns ``x``, or ``(x, aux)`` for the mixture-of-experts family."""
+    cuts = set(cfg.stage_ends_half[:-1])
+    moe_family = cfg.family == "mixtral"
+    aux = torch.zeros((), dtype=torch.float32, device=x.device) if moe_family else None
     block = _BLOCKS[cfg.family]
+    attn_half, ffn_half = _HALVES[cfg.family]
+
+    def mark(x_, aux_):
+        if moe_family:
+            return mark_stage_end((x_, aux_))
+        return mark_stage_end(x_), aux_
+
     for name in sorted(params["layers"]):
         i = int(name)
-        x = _maybe_recompute(cfg, block, params["layers"][name], x, batch, rope)
-        if (i + 1) % per == 0 and (i + 1) < cfg.n_layers:
-            x = mark_stage_end(x)
-    return x
+        p = params["layers"][name]
+        if 2 * i + 1 in cuts:     # a stage ends after this block's attention half
+            x = _maybe_recompute(cfg, attn_half, {k: v for k, v in p.items() if k in ATTN_HALF_KEYS}, x, batch, rope)
+            x, aux = mark(x, aux)
+            out = _maybe_recompute(cfg, lambda c, q, x_, b_, r_: ffn_half(c, q, x_),
+                                   {k: v for k, v in p.items() if k not in ATTN_HALF_KEYS}, x, batch, None)
+        else:
+            out = _maybe_recompute(cfg, block, p, x, batch, rope)
+        if moe_family:
+            x, a = out
+            aux = aux + a
+        else:
+            x = out
+        if 2 * i + 2 in cuts:
+            x, aux = mark(x, aux)
+    return (x, aux) if moe_family else x
 
 
 def encoder_forward(cfg: ModelConfig, params: dict, hidden: torch.Tensor) -> torch.Tensor:

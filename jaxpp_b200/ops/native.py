@@ -86,6 +86,41 @@ def read_status(clear: bool = True) -> int:
     return load().jpb_read_status(1 if clear else 0)
 
 
+STATUS_NAMES = {1: "a bounded wait on an mbarrier ran out (JPB_ERR_WAIT_TIMEOUT)",
+                2: "a kernel rejected an argument or met an out-of-range index (JPB_ERR_BAD_ARGUMENT)",
+                3: "a bounded wait on a peer GPU's flag ran out (JPB_ERR_PEER_TIMEOUT)"}
+
+
+class KernelStatusError(NativeError):
+    """A kernel of the step reported through the device's status word that it gave up: its outputs are not valid."""
+
+    def __init__(self, code: int, where: str = ""):
+        self.code = code
+        super().__init__(f"kernel status {code}{' after ' + where if where else ''}: "
+                         f"{STATUS_NAMES.get(code, 'unknown status')}; the results of this step must not be used")
+
+
+def raise_on_status(where: str = "", synchronize: bool = True) -> None:
+    """Synchronise the current device and raise :class:`KernelStatusError` if any kernel of this library gave up
+    since the last check.  A kernel that runs out of its wait budget returns early and leaves its outputs
+    unwritten, so a training loop calls this once per step before it trusts (or checkpoints) the new state."""
+    if synchronize and torch.cuda.is_available():
+        torch.cuda.synchronize()
+    code = read_status(clear=True)
+    if code != 0:
+        raise KernelStatusError(code, where)
+
+
+def set_wait_budget_ms(ms: float) -> None:
+    """Longest time a device-side wait of this library spins on the current device before its kernel gives up
+    (default 4000 ms).  Applies to kernels launched afterwards."""
+    lib = load()
+    lib.jpb_set_wait_budget_ns.argtypes = [ctypes.c_ulonglong]
+    rc = lib.jpb_set_wait_budget_ns(int(ms * 1e6))
+    if rc != 0:
+        raise NativeError(f"jpb_set_wait_budget_ns failed with code {rc}")
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 

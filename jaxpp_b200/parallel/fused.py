@@ -213,7 +213,7 @@ def _peer_collective(flat: torch.Tensor, group, ranks: list, scale: float, mode:
     slices -> [n_ranks * flat.numel()]."""
     lib = _lib()
     lib.jpb_allreduce.argtypes = [ctypes.POINTER(_AllReduceDesc), ctypes.c_void_p]
-    lib.jpb_allreduce_grid.argtypes = [ctypes.c_longlong, ctypes.c_int]
+    lib.jpb_allreduce_grid2.argtypes = [ctypes.c_longlong, ctypes.c_int, ctypes.c_int]
     if lib.jpb_allreduce_desc_bytes() != ctypes.sizeof(_AllReduceDesc):
         raise native.NativeError("all-reduce call descriptor layout of the native library differs from the Python binding")
     n_ranks = len(ranks)
@@ -243,7 +243,7 @@ def _peer_collective(flat: torch.Tensor, group, ranks: list, scale: float, mode:
     d.n_ranks, d.rank, d.epoch, d.mode = ws.buf.n, ws.buf.rank, ws.epoch, mode
     d.dtype = 0 if flat.dtype == torch.float32 else 1
     d.n, d.scale = n, float(scale)
-    d.grid = lib.jpb_allreduce_grid(n, es)
+    d.grid = lib.jpb_allreduce_grid2(n, es, symm.reserved_sms())
     if mode == 0:
         ws.ctas += d.grid
     d.counter_target = ws.ctas & 0xFFFFFFFF

@@ -17,7 +17,7 @@ from . import tp as tpmod
 
 
 class JpbMoeDesc(ctypes.Structure):
-    _fields_ = [("n_ranks", ctypes.c_int), ("rank", ctypes.c_int), ("epoch", ctypes.c_int), ("pad", ctypes.c_int),
+    _fields_ = [("n_ranks", ctypes.c_int), ("rank", ctypes.c_int), ("epoch", ctypes.c_int), ("reserved_sms", ctypes.c_int),
                 ("ctrl", ctypes.c_void_p * 8), ("recv", ctypes.c_void_p * 8)]
 
 
@@ -32,11 +32,14 @@ class _Workspace:
         self.slot = (nbytes + 1023) // 1024 * 1024
         self.buf = symm.SymmetricBuffer(self.CTRL + 2 * self.slot, mesh.axis_group(axis), ranks)
         self.epoch = 0
+        # with pipeline stages on other GPUs a few SMs stay out of the grid, so that point-to-point kernels of side
+        # streams can start while these kernels wait for their peers (same rule as the fused GEMMs' workspaces)
+        self.reserved_sms = symm.reserved_sms(mesh)
 
     def next_call(self) -> JpbMoeDesc:
         self.epoch += 1
         d = JpbMoeDesc()
-        d.n_ranks, d.rank, d.epoch = self.buf.n, self.buf.rank, self.epoch
+        d.n_ranks, d.rank, d.epoch, d.reserved_sms = self.buf.n, self.buf.rank, self.epoch, self.reserved_sms
         for q in range(self.buf.n):
             d.ctrl[q] = self.buf.ptrs[q]
             d.recv[q] = self.buf.ptrs[q] + self.CTRL + (self.epoch & 1) * self.slot

@@ -28,6 +28,7 @@ class SymmetricBuffer:
 
     GUARD = 256
     PATTERN = 0xA5
+    LIVE: list = []   # every buffer of this process that has not been closed (what check_all_canaries walks)
 
     def __init__(self, nbytes: int, group, group_ranks: list[int]):
         lib = native.load()
@@ -66,6 +67,7 @@ class SymmetricBuffer:
         # posted ahead of time on side streams and cannot complete before this rank moves on)
         torch.cuda.current_stream().synchronize()
         dist.barrier(group=group)
+        SymmetricBuffer.LIVE.append(self)
 
     def check_canaries(self) -> bool:
         """True iff both guard bands of the local copy still hold the pattern (synchronises the current stream)."""
@@ -82,12 +84,28 @@ class SymmetricBuffer:
         if self.local_base:
             self.lib.jpb_ipc_free(self.local_base)
         self.bases, self.ptrs, self.local_base, self.local_ptr = [], [], None, None
+        if self in SymmetricBuffer.LIVE:
+            SymmetricBuffer.LIVE.remove(self)
 
 
 def check_all_canaries() -> bool:
-    """Guard bands of every live symmetric buffer of this process (fused GEMM workspaces; all-reduce and MoE
-    workspaces register theirs through the same class)."""
-    return all(ws.buf.check_canaries() for ws in _WORKSPACES.values())
+    """Guard bands of every symmetric buffer of this process that is still allocated: the fused GEMM workspaces, the
+    all-reduce / reduce-scatter / all-gather workspaces and the expert-parallel ones (every :class:`SymmetricBuffer`
+    registers itself; closed and released buffers drop out)."""
+    return all(buf.check_canaries() for buf in list(SymmetricBuffer.LIVE) if buf.local_base)
+
+
+def reserved_sms(mesh=None) -> int:
+    """SMs that kernels whose CTAs wait for peers leave free when pipeline stages live on other GPUs: point-to-point
+    kernels of side streams must be able to start while such a kernel waits."""
+    from ..mesh import MpmdMesh
+    from ..utils import config
+
+    if mesh is None:
+        if not MpmdMesh.mesh_stack:
+            return 0
+        mesh = MpmdMesh.current()
+    return int(config.comm_reserved_sms.value) if mesh.mpmd_dim > 1 else 0
 
 
 class JpbCommDesc(ctypes.Structure):
@@ -120,7 +138,7 @@ class CommWorkspace:
 
         mesh = MpmdMesh.current()
         sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
-        reserve = config.comm_reserved_sms.value if mesh.mpmd_dim > 1 else 0
+        reserve = reserved_sms(mesh)
         self.max_ctas = max(1, sms - reserve) if reserve > 0 else 0
 
     def next_call(self, gather: int, gathered_is_b: bool, scatter: bool) -> JpbCommDesc:
@@ -182,4 +200,6 @@ def release_retired() -> None:
         dist.barrier(group=ws.buf.group)   # ... and has closed it before the owner frees the memory
         ws.buf.lib.jpb_ipc_free(ws.buf.local_base)
         ws.buf.bases, ws.buf.ptrs, ws.buf.local_base, ws.buf.local_ptr = [], [], None, None
+        if ws.buf in SymmetricBuffer.LIVE:
+            SymmetricBuffer.LIVE.remove(ws.buf)
     _RETIRED.clear()

@@ -190,24 +190,29 @@ class DistComm:
         return buf
 
     def all_gather(self, st, ins: AllGather, prog: Program):
+        """Concatenate operands that live on different pipeline ranks (``cross_mpmd_stack``): ONE all-gather over
+        the group.  Every rank packs the operands it owns into a flat buffer; operand shapes are static (all equal
+        along every dimension, the output's extent along ``axis`` divided by the operand count), so every rank knows
+        every pack's size, and packs are padded to the largest one."""
         group = self._group(ins.ranks)
         info = prog.values[ins.out]
-        parts = []
-        for p, owner in enumerate(ins.owners):
-            if owner == self.rank:
-                t = st.env[ins.local[p]].contiguous()
-            else:
-                # operand shapes: all operands share every dim except ``axis``; sizes come from the output
-                t = None
-            parts.append(t)
-        # exchange shapes are static: an operand's extent along axis is out_extent / n when equal, else sent first
         n = len(ins.owners)
         shape = list(info.shape)
         shape[ins.axis] = info.shape[ins.axis] // n
-        for p, owner in enumerate(ins.owners):
-            if parts[p] is None:
-                parts[p] = torch.empty(shape, dtype=info.dtype, device=self.device)
-            dist.broadcast(parts[p], src=self.peer(owner), group=group)
+        numel = 1
+        for s_ in shape:
+            numel *= s_
+        owned = {r: [p for p, o in enumerate(ins.owners) if o == r] for r in ins.ranks}
+        width = max(len(ps) for ps in owned.values()) * numel
+        pack = torch.zeros(width, dtype=info.dtype, device=self.device)
+        for k, p in enumerate(owned[self.rank]):
+            pack[k * numel:(k + 1) * numel].copy_(st.env[ins.local[p]].reshape(-1))
+        every = torch.empty(len(ins.ranks) * width, dtype=info.dtype, device=self.device)
+        dist.all_gather_into_tensor(every, pack, group=group)
+        parts: list = [None] * n
+        for g, r in enumerate(ins.ranks):
+            for k, p in enumerate(owned[r]):
+                parts[p] = every[g * width + k * numel:g * width + (k + 1) * numel].view(shape)
         return torch.cat(parts, dim=ins.axis)
 
 

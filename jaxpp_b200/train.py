@@ -100,6 +100,13 @@ def main(argv=None):
             scope = det.step_scope(step) if det is not None else _null()
             with scope:
                 state, losses = jitted(state, batch[:, :, :-1].contiguous(), batch[:, :, 1:].contiguous())
+                if device.type == "cuda":
+                    # a fused kernel that ran out of its wait budget returned early and left outputs unwritten:
+                    # raise inside the step scope, so that the failure record reaches the other ranks and nothing of
+                    # this step is checkpointed
+                    from jaxpp_b200.ops import native
+
+                    native.raise_on_status(f"step {step}")
             lt_ = losses.local_tensor()
             rec = metrics.end(step, float(lt_.float().mean()) if lt_ is not None else None)
             if rank == 0:

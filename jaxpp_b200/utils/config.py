@@ -48,10 +48,13 @@ class OverwriteableVar(Generic[T]):
 class EnvVar(OverwriteableVar[T]):
     """Flag backed by an environment variable; the environment is consulted once."""
 
-    def __init__(self, env_key: str, default_value: T | None = None):
+    def __init__(self, env_key: str, default_value: T | None = None, no_effect: str | None = None):
         super().__init__(default_value)
         self.env_key = env_key
         self._cached = _UNSET
+        # flags kept only so that launch scripts and code written for the reference keep working: the reason why
+        # the setting changes nothing here (``warn_about_flags_without_effect`` reports a non-default value)
+        self.no_effect = no_effect
 
     def parse(self, text: str) -> T | None:  # pragma: no cover - overridden
         raise NotImplementedError
@@ -105,19 +108,34 @@ class IntEnvVar(EnvVar[int]):
 
 
 # --- flags (same names and defaults as the reference, env_vars.py:3-22) -----------------
-share_donation = BoolEnvVar("JAXPP_SHARE_DONATION", True)
-enable_local_propagation = BoolEnvVar("JAXPP_ENABLE_LOCAL_PROPAGATION", False)
+share_donation = BoolEnvVar(
+    "JAXPP_SHARE_DONATION", True,
+    no_effect="donation is a per-call list handed to the interpreter, not part of an executable: tasks that share code "
+              "never recompile because their donation differs")
+enable_local_propagation = BoolEnvVar(
+    "JAXPP_ENABLE_LOCAL_PROPAGATION", False,
+    no_effect="shardings are explicit (tensor-/data-/expert-parallel layers state them); nothing is inferred per task")
 enable_licm = BoolEnvVar("JAXPP_ENABLE_LICM", False)
 dump_dir = StrEnvVar("JAXPP_DUMP_DIR", "")
 # inf (the default) = sent buffers are only collected at the end of the step.
 transfer_done_delay = IntEnvVar("JAXPP_TRANSFER_DONE_DELAY", math.inf)  # type: ignore[arg-type]
 disable_schedule_task_fusion = BoolEnvVar("JAXPP_DISABLE_SCHEDULE_TASK_FUSION", False)
-disable_prevent_cse = BoolEnvVar("JAXPP_DISABLE_PREVENT_CSE", False)
-directional_communicators = BoolEnvVar("JAXPP_DIRECTIONAL_COMMUNICATORS", False)
+disable_prevent_cse = BoolEnvVar(
+    "JAXPP_DISABLE_PREVENT_CSE", False,
+    no_effect="recomputed blocks are traced as ordinary ops of the backward task and no pass merges them with the "
+              "forward pass' ops across tasks, so there is no barrier to relax")
+directional_communicators = BoolEnvVar(
+    "JAXPP_DIRECTIONAL_COMMUNICATORS", False,
+    no_effect="point-to-point transfers always use one communicator per direction of a pair of pipeline ranks: "
+              "receives are posted ahead of time here, and on a shared communicator one would hold back the sends "
+              "issued after it")
 conservative_loop_clustering = BoolEnvVar("JAXPP_CONSERVATIVE_LOOP_CLUSTERING", True)
-debug_skip_propagation = BoolEnvVar("JAXPP_DEBUG_SKIP_PROPAGATION", False)
+debug_skip_propagation = BoolEnvVar(
+    "JAXPP_DEBUG_SKIP_PROPAGATION", False, no_effect="there is no sharding propagation to skip (shardings are explicit)")
+# run the per-rank programs of the multi-process path as threads of one process (runtime/local_comm.py)
 debug_force_mpmdify = BoolEnvVar("JAXPP_DEBUG_FORCE_MPMDIFY", False)
-fast_infer_shardings = BoolEnvVar("JAXPP_FAST_INFER_SHARDINGS", False)
+fast_infer_shardings = BoolEnvVar(
+    "JAXPP_FAST_INFER_SHARDINGS", False, no_effect="there is no throw-away driver compile that infers shardings")
 enable_check_ir = BoolEnvVar("JAXPP_ENABLE_CHECK_JAXPR", False)
 
 # --- flags that only exist in this framework ----------------------------------------------
@@ -135,7 +153,30 @@ p2p_backend = StrEnvVar("JAXPP_B200_P2P", "torch")
 fuse_norm_backward_adds = BoolEnvVar("JAXPP_B200_FUSE_NORM_BWD_ADD", True)
 # Let weight-gradient GEMMs add straight into the microbatch loop's accumulators (ops/sink.py).
 wgrad_sinks = BoolEnvVar("JAXPP_B200_WGRAD_SINKS", True)
+# Hoisting with scarce memory: cheap ops that only expand their operands go back into the loop (needs JAXPP_ENABLE_LICM).
+licm_memory_scarce = BoolEnvVar("JAXPP_B200_LICM_MEMORY_SCARCE", True)
+# Zero-bubble split: move left-over cheap, non-expanding, non-GEMM ops into the activation-gradient half.
+zb_memory_scarce = BoolEnvVar("JAXPP_B200_ZB_MEMORY_SCARCE", True)
+# Zero-bubble split: bytes of operands that deferred weight-gradient GEMMs may keep alive per (stage, microbatch);
+# weight gradients beyond the budget run with the activation gradients.  Negative = no limit.
+zb_defer_bytes = IntEnvVar("JAXPP_B200_ZB_DEFER_BYTES", -1)
 # Seconds a rank may go without a heartbeat before the watchdog reports it.
 heartbeat_timeout_s = IntEnvVar("JAXPP_B200_HEARTBEAT_TIMEOUT", 30)
 # Wrap every task in an NVTX range named like the task (fwd_3__5, …) for timeline profilers.
 nvtx_ranges = BoolEnvVar("JAXPP_B200_NVTX", False)
+
+
+_WARNED: set = set()
+
+
+def warn_about_flags_without_effect(log) -> None:
+    """Tell the user once about every reference flag that is set to a non-default value but changes nothing here."""
+    for name, var in list(globals().items()):
+        if isinstance(var, EnvVar) and var.no_effect and name not in _WARNED:
+            try:
+                changed = var.value != var.default_value
+            except ValueError:
+                changed = True
+            if changed:
+                _WARNED.add(name)
+                log.warning("%s is set but has no effect in this framework: %s", var.env_key, var.no_effect)

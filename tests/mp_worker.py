@@ -64,6 +64,35 @@ def scenario_pp(schedule, n_mb):
     check_tree(ref2, got2, 0 if exact else 1e-5, 0 if exact else 1e-6, "pp step 2")
 
 
+def scenario_stack():
+    """cross_mpmd_stack of values that live on different pipeline ranks: one all-gather over the owners, with the
+    ranks owning different numbers of operands (3 stages' statistics on 2 ranks)."""
+    from jaxpp_b200.ops import core as ops
+
+    world = dist.get_world_size()
+    sched = jp.Interleaved1F1B(3 * world, world) if world > 1 else jp.Std1F1B(1)
+    n_stages = sched.num_stages
+    mesh = jp.MpmdMesh.create({"mpmd": world, "data": 1, "model": 1}, kind=device().type, multi_process=True)
+    params = mlp_params(n_stages, 16)
+    batch = torch.randn(4, 4, 16, generator=torch.Generator().manual_seed(1))
+    inner = make_mlp_step(n_stages, sched, 4)
+
+    def step(params, batch):
+        loss, new = inner(params, batch)
+        # per-layer statistics of the new weights: layers 0, 2, 4 (rank 0) and layer 1 (rank 1), stacked in this order
+        picks = [0, 2, 1, 4] if n_stages >= 5 else list(range(n_stages))
+        stats = jp.cross_mpmd_stack([new[i]["w1"].pow(2).sum(0) for i in picks], axis=0)
+        return loss, new, stats
+
+    ref = step(params, batch)
+    dev = device()
+    to = lambda t: pytree.tree_map(lambda x: x.to(dev), t)
+    got = jp.mpmd_jit_with_loop(step, mesh)(to(params), to(batch))
+    exact = dev.type == "cpu"
+    check_tree(ref, got, 0 if exact else 1e-5, 0 if exact else 1e-6, "stack")
+    assert got[2].is_partially_addressable and tuple(got[2].shape) == tuple(ref[2].shape)
+
+
 def scenario_pp_tp(pp, tp, schedule):
     """Pipeline x tensor parallel language model against the un-sharded single-process step."""
     mesh = jp.MpmdMesh.create({"mpmd": pp, "data": 1, "model": tp}, kind=device().type, multi_process=True)
@@ -338,6 +367,7 @@ SCENARIOS = {
     "pp2_tp2": lambda: scenario_pp_tp(2, 2, jp.Interleaved1F1B(4, 2)),
     "tp2": lambda: scenario_pp_tp(1, 2, jp.Std1F1B(1)),
     "reshard": scenario_reshard,
+    "stack": scenario_stack,
     "ring_attention": scenario_ring_attention,
     "pp2_dp2_gpt2": lambda: scenario_dp_ep("gpt2"),
     "pp2_ep2_mixtral": lambda: scenario_dp_ep("mixtral"),

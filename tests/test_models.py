@@ -185,3 +185,90 @@ def test_activation_recompute_of_mixture_of_experts_blocks():
                        exact=False, rtol=1e-5, atol=1e-6)
     fwd = lambda prog: next(i for i in prog.instrs if isinstance(i, RunTask) and i.name.startswith("fwd_1"))
     assert len(fwd(progs[1]).outs) < len(fwd(progs[0]).outs)
+
+
+@pytest.mark.parametrize("family,schedule,pp,stage_layers,recompute", [
+    ("llama", jp.Interleaved1F1B(4, 2), 2, (1.5, 1, 1, 0.5), False),   # boundaries inside blocks 1 and 3
+    ("gpt2", jp.Std1F1B(2), 2, (3, 1), False),                        # whole blocks, unequal
+    ("llama", jp.ZeroBubble(2), 2, (2.5, 1.5), True),                 # cut block recomputed as two halves
+    ("mixtral", jp.DualPipeV(4, 2), 2, (1, 1.5, 0.5, 1), False),
+])
+def test_unequal_and_half_block_stages_match_unpipelined(family, schedule, pp, stage_layers, recompute):
+    extra = dict(n_experts=4, top_k=2, capacity_factor=2.0) if family == "mixtral" else {}
+    cfg = tf.ModelConfig(family, vocab=250, d_model=64, n_layers=4, n_heads=4, n_kv_heads=2 if family != "gpt2" else 4,
+                         ffn=128, seq=32, n_stages=schedule.num_stages, dtype=torch.float32, stage_layers=stage_layers,
+                         recompute=recompute, **extra)
+    step = lt.make_train_step(cfg, schedule, lt.Hyper(lr=1e-2, inplace_update=False))
+    state = lt.init_state(cfg, schedule, "cpu")
+    g = torch.Generator().manual_seed(5)
+    tokens = torch.randint(0, cfg.vocab, (4, 2, cfg.seq), generator=g)
+    labels = torch.randint(0, cfg.vocab, (4, 2, cfg.seq), generator=g)
+    ref = step(state, tokens, labels)
+    got = jp.mpmd_jit_with_loop(step, cpu_mesh(pp))(state, tokens, labels)
+    assert_trees_equal(ref, got, exact=True)
+    owners = lt.owner_ranks(cfg, schedule)
+    for name, layer in got[0]["params"]["layers"].items():
+        for key, leaf in layer.items():
+            assert leaf.mpmd_idxs == (lt.owner_of(owners, int(name), key),), (name, key)
+
+
+def test_stage_layers_validation_and_balancing():
+    with pytest.raises(ValueError):
+        tf.llama2_7b(n_stages=8, stage_layers=(4,) * 7 + (5,))
+    with pytest.raises(ValueError):
+        tf.llama2_7b(n_stages=8, stage_layers=(4.25, 3.75) + (4,) * 6)
+    cfg = tf.llama2_7b(n_stages=8, stage_layers=(4, 4, 4, 4, 4, 4, 4.5, 3.5))
+    assert cfg.stage_ends_half == (8, 16, 24, 32, 40, 48, 57, 64)
+    assert cfg.stage_of_param(28, "wqkv") == 6 and cfg.stage_of_param(28, "w_up") == 7
+    sched = jp.Interleaved1F1B(8, 4)
+    sizes = tf.balanced_stage_layers(32, 8, sched.get_mpmd_idx, 4, last_extra=0.73)
+    equal = tf.rank_loads((4,) * 8, sched.get_mpmd_idx, 4, 0.36, 0.0, 0.73)
+    best = tf.rank_loads(sizes, sched.get_mpmd_idx, 4, 0.36, 0.0, 0.73)
+    assert abs(sum(sizes) - 32) < 1e-9 and max(best) < max(equal) - 0.3
+    # per-process state with a cut block: each pipeline rank holds only the half it runs
+    small = tf.ModelConfig("llama", vocab=64, d_model=32, n_layers=2, n_heads=2, n_kv_heads=2, ffn=64, seq=8, n_stages=2,
+                           dtype=torch.float32, stage_layers=(1.5, 0.5))
+    s0 = lt.init_state(small, jp.Std1F1B(2), "cpu", my_rank=0)
+    s1 = lt.init_state(small, jp.Std1F1B(2), "cpu", my_rank=1)
+    assert isinstance(s0["params"]["layers"]["001"]["wqkv"], torch.Tensor)
+    assert isinstance(s0["params"]["layers"]["001"]["w_up"], jp.ShapeDtypeStruct)
+    assert isinstance(s1["params"]["layers"]["001"]["w_up"], torch.Tensor)
+    assert isinstance(s1["params"]["layers"]["001"]["wqkv"], jp.ShapeDtypeStruct)
+
+
+def test_zero_bubble_split_bounds_what_stays_alive_until_the_weight_gradient_half():
+    """ZeroBubble with full recompute: the recomputed inputs and the activation gradients of every linear live from the
+    activation-gradient task to the weight-gradient task.  ``JAXPP_B200_ZB_DEFER_BYTES`` bounds those bytes by running
+    the weight gradients that do not fit with the activation gradients; results do not change."""
+    import math
+
+    from jaxpp_b200.compiler.program import RunTask
+    from jaxpp_b200.utils import config
+
+    sched = jp.ZeroBubble(2)
+    cfg = tf.ModelConfig("llama", vocab=128, d_model=32, n_layers=2, n_heads=2, n_kv_heads=2, ffn=64, seq=16, n_stages=2,
+                         dtype=torch.float32, recompute=True)
+    step = lt.make_train_step(cfg, sched, lt.Hyper(lr=1e-2, inplace_update=False))
+    state = lt.init_state(cfg, sched, "cpu")
+    g = torch.Generator().manual_seed(2)
+    tokens = torch.randint(0, 128, (4, 2, 16), generator=g)
+    labels = torch.randint(0, 128, (4, 2, 16), generator=g)
+    ref = step(state, tokens, labels)
+
+    def carried(prog):
+        a = next(i for i in prog.instrs if isinstance(i, RunTask) and i.name == "bwdA_1__0")
+        w = next(i for i in prog.instrs if isinstance(i, RunTask) and i.name == "bwdW_1__0")
+        vids = set(a.outs) & set(w.ins)
+        wgrads = sum("linear_wgrad" in str(t) for t in w.code.targets)
+        return sum(math.prod(prog.values[v].shape) * prog.values[v].dtype.itemsize for v in vids), wgrads
+
+    seen = {}
+    for budget in (-1, 40000, 0):
+        with config.zb_defer_bytes.set(budget):
+            f = jp.mpmd_jit_with_loop(step, cpu_mesh(2))
+            prog = f.lower(state, tokens, labels).program
+            got = f(state, tokens, labels)
+        assert_trees_equal(ref, got, exact=True)
+        seen[budget] = carried(prog)
+    assert seen[-1][0] > seen[40000][0] > seen[0][0] == 0
+    assert seen[40000][0] <= 40000 and seen[-1][1] == 1 and seen[0][1] == 0

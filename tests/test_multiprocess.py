@@ -34,6 +34,10 @@ def test_reshard_round_trip():
     run("reshard", 4)
 
 
+def test_cross_stage_stack_is_one_all_gather_with_uneven_owners():
+    run("stack", 2)
+
+
 def test_pipeline_times_data_parallel():
     run("pp2_dp2_gpt2", 4)
 

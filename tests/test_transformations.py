@@ -235,9 +235,12 @@ def test_in_shardings_and_dump(tmp_path):
     assert "send#" in (tmp_path / "toy.local.0.rank0.program.txt").read_text()
 
 
-def test_licm_hoists_loop_invariant_casts():
+@pytest.mark.parametrize("scarce", [False, True])
+def test_licm_hoists_loop_invariant_casts(scarce):
     """With JAXPP_ENABLE_LICM a cast of the parameters written inside the loop body runs once before the loop
-    (on each consumer rank) instead of once per microbatch; results are unchanged."""
+    (on each consumer rank) instead of once per microbatch; results are unchanged.  With scarce memory (the default)
+    a *widening* cast that only the loop reads goes back inside: the small operand stays resident, not the large
+    result (reference: src/jaxpp/licm.py:301-345)."""
     sched = jp.Std1F1B(2)
     params, batch = mlp_params(2, 8), torch.randn(4, 2, 8)
 
@@ -253,7 +256,7 @@ def test_licm_hoists_loop_invariant_casts():
 
     ref = step(params, batch)
     plain = jp.mpmd_jit_with_loop(step, cpu_mesh(2)).lower(params, batch).program
-    with config.enable_licm.set(True):
+    with config.enable_licm.set(True), config.licm_memory_scarce.set(scarce):
         f = jp.mpmd_jit_with_loop(step, cpu_mesh(2))
         hoisted = f.lower(params, batch).program
         got = f(params, batch)
@@ -264,8 +267,52 @@ def test_licm_hoists_loop_invariant_casts():
         return task.code.src.count("T[%d]" % next(k for k, t in enumerate(task.code.targets) if "_to_copy" in str(t))) \
             if any("_to_copy" in str(t) for t in task.code.targets) else 0
 
-    assert casts_in(hoisted, "before_loop_r0") >= 5 and casts_in(plain, "fwd_0__0") >= 6
-    assert casts_in(hoisted, "fwd_0__0") == 1  # only the microbatch itself is still cast inside the loop
+    assert casts_in(plain, "fwd_0__0") >= 6
+    if scarce:   # float32 -> float64 doubles the bytes: the casts stay with their consumers
+        assert casts_in(hoisted, "fwd_0__0") >= 6
+    else:
+        assert casts_in(hoisted, "before_loop_r0") >= 5
+        assert casts_in(hoisted, "fwd_0__0") == 1  # only the microbatch itself is still cast inside the loop
+
+
+def test_licm_rules_narrowing_casts_fp8_and_cse():
+    """Narrowing casts are hoisted even with scarce memory, casts to 8-bit floats never are, and identical pure ops
+    are merged (reference: src/jaxpp/licm.py:66-126, 429-452)."""
+    sched = jp.Std1F1B(2)
+    params, batch = mlp_params(2, 8), torch.randn(4, 2, 8)
+
+    def step(params, batch):
+        def body(mb):
+            def loss_fn(p):
+                lo = pytree.tree_map(lambda t: t.to(torch.bfloat16).to(torch.float32), p)      # narrowing, then widening
+                dup = pytree.tree_map(lambda t: t.to(torch.bfloat16).to(torch.float32), p)     # the same again
+                q = pytree.tree_map(lambda t: t.to(torch.float8_e4m3fn).to(torch.float32), p)  # 8-bit round trip
+                mixed = pytree.tree_map(lambda a, b, c: (a + b) * 0.5 + 0.0 * c, lo, dup, q)
+                return ((mlp_forward(mixed, mb, 2) - mb) ** 2).mean()
+
+            return jp.value_and_grad(loss_fn)(params)
+
+        return jp.treduce(body, batch, schedule=sched)
+
+    ref = step(params, batch)
+    with config.enable_licm.set(True):
+        f = jp.mpmd_jit_with_loop(step, cpu_mesh(2))
+        prog = f.lower(params, batch).program
+        got = f(params, batch)
+    assert_trees_equal(ref, got, exact=True)
+    src = {i.name: i.code for i in prog.instrs if isinstance(i, RunTask)}
+
+    def count(code, dtype):
+        return sum(1 for line in code.src.splitlines() if "dtype=" in line and f"C[{code.consts.index(dtype)}]" in line) \
+            if dtype in code.consts else 0
+
+    before, fwd = src["before_loop_r0"], src["fwd_0__0"]
+    assert count(before, torch.bfloat16) >= 1 and count(fwd, torch.bfloat16) == 0       # hoisted once
+    assert count(before, torch.float8_e4m3fn) == 0 and count(fwd, torch.float8_e4m3fn) >= 1   # stays in the loop
+    plain = jp.mpmd_jit_with_loop(step, cpu_mesh(2)).lower(params, batch).program
+    plain_fwd = next(i.code for i in plain.instrs if isinstance(i, RunTask) and i.name == "fwd_0__0")
+    # without the pass every parameter is narrowed twice (lo and dup); with it once, before the loop
+    assert count(plain_fwd, torch.bfloat16) == 2 * count(before, torch.bfloat16)
 
 
 @pytest.mark.parametrize("schedule", [jp.Std1F1B(2), jp.Interleaved1F1B(4, 2), jp.ZeroBubble(2)], ids=["1f1b", "interleaved", "zb"])
@@ -507,3 +554,150 @@ def test_microbatch_inputs_passed_through_the_loop(pp):
     assert_trees_equal(ref, got, exact=True)
     assert torch.equal(local(got[2]), X) and torch.equal(local(got[3]), Yin)
     verify_program(f.lower(ws, X, Yin, T).program)
+
+
+# ---- donation, static arguments, per-rank programs in one process -----------------------------------------------------
+def test_donated_arguments_are_freed_at_their_last_use():
+    """``donate_argnums``: program inputs the caller gave up are deleted (or handed to their last task) after their last
+    use on every rank instead of living for the whole step; arrays passed for them read as deleted afterwards
+    (reference: infer_donation, src/jaxpp/core.py:1732-1809; jit arguments :3892-3923)."""
+    from jaxpp_b200.compiler.program import Delete
+
+    sched = jp.Std1F1B(2)
+    params, batch = mlp_params(2, 8), torch.randn(4, 2, 8)
+    step = make_mlp_step(2, sched, 4)
+    ref = step(params, batch)
+    kept = jp.mpmd_jit_with_loop(step, cpu_mesh(2))
+    gave = jp.mpmd_jit_with_loop(step, cpu_mesh(2), donate_argnums=(0,))
+    p_kept, p_gave = kept.lower(params, batch).program, gave.lower(params, batch).program
+    param_vids = {vid for k, (vid, _) in enumerate(p_gave.inputs) if k < len(leaves(params))}
+
+    def freed(prog):
+        out = set()
+        for i in prog.instrs:
+            if isinstance(i, Delete):
+                out.update(v for v in i.vids if v in param_vids)
+            if isinstance(i, RunTask):
+                out.update(v for v, d in zip(i.ins, i.donate) if d and v in param_vids)
+        return out
+
+    assert not freed(p_kept) and freed(p_gave) == param_vids
+    verify_program(p_gave)
+    first = gave(params, batch)                       # plain tensors: the caller still owns them
+    assert_trees_equal(ref, first, exact=True)
+    state = first[1]                                  # MpmdArrays: donated on the next call
+    ref2 = step(pytree.tree_map(local, state), batch)
+    second = gave(state, batch)
+    assert_trees_equal(ref2, second, exact=True)
+    assert all(a.is_deleted() for a in leaves(state))
+    with pytest.raises(ValueError):
+        jp.mpmd_jit_with_loop(step, cpu_mesh(2), donate_argnums=(5,)).lower(params, batch)
+
+
+def test_donation_lowers_peak_memory_of_a_step():
+    """Live bytes over the instruction list: with the old state donated, old and new parameters never coexist in full."""
+    import math
+
+    from jaxpp_b200.compiler.program import Delete
+
+    from jaxpp_b200.models import lm_trainer as lt
+    from jaxpp_b200.models import transformer as tf
+
+    sched = jp.Std1F1B(2)
+    cfg = tf.ModelConfig("llama", vocab=64, d_model=64, n_layers=2, n_heads=2, n_kv_heads=2, ffn=128, seq=8, n_stages=2,
+                         dtype=torch.float32)
+    step = lt.make_train_step(cfg, sched, lt.Hyper(inplace_update=False))     # the new state is fresh memory
+    state = lt.init_state(cfg, sched, "cpu")
+    tokens = torch.randint(0, 64, (2, 1, 8))
+
+    def peak_bytes(prog):
+        size = lambda v: math.prod(prog.values[v].shape) * prog.values[v].dtype.itemsize
+        live = [set(v for v, ranks in prog.inputs if r in ranks) for r in range(prog.n_ranks)]
+        peak = [sum(size(v) for v in s) for s in live]
+        for i in prog.instrs:
+            r = i.rank
+            if isinstance(i, RunTask):
+                live[r] -= {v for v, d in zip(i.ins, i.donate) if d}
+                live[r] |= {v for v in i.outs if v >= 0}
+            elif isinstance(i, Delete):
+                live[r] -= set(i.vids)
+            elif isinstance(i, Transfer):
+                live[i.dst] |= set(i.vids)
+            elif hasattr(i, "out") and isinstance(getattr(i, "out"), int):
+                live[r].add(i.out)
+            peak[r] = max(peak[r], sum(size(v) for v in live[r]))
+        return max(peak)
+
+    kept = jp.mpmd_jit_with_loop(step, cpu_mesh(2)).lower(state, tokens, tokens).program
+    gave = jp.mpmd_jit_with_loop(step, cpu_mesh(2), donate_argnums=(0,)).lower(state, tokens, tokens).program
+    # kept: old and new (parameters, master weights, two moments) coexist after the optimizer task; donated: one set
+    assert peak_bytes(gave) < 0.75 * peak_bytes(kept)
+
+
+def test_static_arguments_are_constants_and_must_not_hold_arrays():
+    sched = jp.Std1F1B(2)
+    params, batch = mlp_params(2, 8), torch.randn(4, 2, 8)
+
+    def step(params, batch, scale):
+        loss, new = make_mlp_step(2, sched, 4)(params, batch)
+        return loss * scale, new
+
+    f = jp.mpmd_jit_with_loop(step, cpu_mesh(2), static_argnums=(2,))
+    assert_trees_equal(step(params, batch, 2.0), f(params, batch, 2.0), exact=True)
+    assert_trees_equal(step(params, batch, 3.0), f(params, batch, 3.0), exact=True)   # a new constant: a new program
+    assert len(f._cache) == 2
+    with pytest.raises(TypeError):
+        jp.mpmd_jit_with_loop(step, cpu_mesh(2), static_argnums=(1,)).lower(params, batch, 2.0)
+
+
+@pytest.mark.parametrize("pp,schedule,n_mb", [(2, jp.Std1F1B(2), 4), (2, jp.Interleaved1F1B(4, 2), 4), (4, jp.ZeroBubble(4), 6),
+                                              (2, jp.DualPipeV(4, 2), 4)], ids=["1f1b", "interleaved", "zb", "dualpipev"])
+def test_force_mpmdify_runs_the_per_rank_programs_in_one_process(pp, schedule, n_mb):
+    """``JAXPP_DEBUG_FORCE_MPMDIFY``: the per-rank instruction lists of the multi-process path (send / recv /
+    send_done / all_reduce per rank), run as threads of one process, give the results of the global program."""
+    params = mlp_params(schedule.num_stages, 16)
+    batch = torch.randn(n_mb, 4, 16, generator=torch.Generator().manual_seed(1))
+    step = make_mlp_step(schedule.num_stages, schedule, n_mb)
+    ref = step(params, batch)
+    with config.debug_force_mpmdify.set(True):
+        f = jp.mpmd_jit_with_loop(step, cpu_mesh(pp))
+        got = f(params, batch)
+        again = f(got[1], batch)
+    assert_trees_equal(ref, got, exact=True)
+    assert_trees_equal(step(pytree.tree_map(local, got[1]), batch), again, exact=True)
+
+
+def test_force_mpmdify_with_cross_rank_collectives_and_a_failing_rank():
+    sched = jp.Std1F1B(2)
+    g = torch.Generator().manual_seed(3)
+    params = {"emb": torch.randn(8, 8, generator=g) * 0.3, "mid": torch.randn(8, 8, generator=g) * 0.3}
+    batch = torch.randn(4, 4, 8, generator=g)
+
+    def step(params, batch):
+        def body(mb):
+            def loss_fn(p):
+                x = jp.mark_stage_end(ops.gelu(ops.linear(mb, p["emb"], None)))
+                x = ops.linear(ops.linear(x, p["mid"], None), p["emb"], None)   # tied weight: cross-rank all-reduce
+                return (jp.mark_stage_end(x) ** 2).mean() / 4
+
+            return jp.value_and_grad(loss_fn)(params)
+
+        loss, grads = jp.treduce(body, batch, schedule=sched)
+        norms = jp.cross_mpmd_stack([grads["emb"].pow(2).sum().reshape(1), grads["mid"].pow(2).sum().reshape(1)], axis=0)
+        return loss, pytree.tree_map(lambda p, gr: p - 0.5 * gr, params, grads), norms
+
+    ref = step(params, batch)
+    global_run = jp.mpmd_jit_with_loop(step, cpu_mesh(2))(params, batch)
+    with config.debug_force_mpmdify.set(True):
+        f = jp.mpmd_jit_with_loop(step, cpu_mesh(2))
+        got = f(params, batch)
+        assert_trees_equal(ref, got, exact=False)           # the tied gradient is summed in a different order
+        assert_trees_equal(pytree.tree_map(local, global_run), got, exact=True)   # same as the global program, bit for bit
+        from jaxpp_b200 import fault
+
+        fault.set_fault_plan(fault.FaultPlan(raise_in_task="bwd_1__2", on_rank=1))
+        try:
+            with pytest.raises(fault.InjectedFault):   # the failing rank's error, not the others' "partner failed"
+                f(params, batch)
+        finally:
+            fault.set_fault_plan(None)

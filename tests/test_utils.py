@@ -250,3 +250,26 @@ def test_memory_plan_of_the_benchmark_configurations():
     assert configs.memory_plan(gpt, shard_optimizer=True)["optimizer"] * 4 == pytest.approx(configs.memory_plan(gpt)["optimizer"])
     whole, sliced = configs.memory_plan(mix)["optimizer"], configs.memory_plan(mix, shard_optimizer=True)["optimizer"]
     assert 0.8 * whole < sliced < whole                                               # experts are not replicas
+
+
+def test_reference_flags_without_an_effect_here_say_so(caplog):
+    """Flags that exist for compatibility with the reference's launch scripts but cannot change anything in this
+    design carry the reason, and a non-default setting is reported once at compile time."""
+    import logging
+
+    from jaxpp_b200.utils import config
+
+    inert = [v for v in vars(config).values() if isinstance(v, config.EnvVar) and v.no_effect]
+    assert {v.env_key for v in inert} == {
+        "JAXPP_SHARE_DONATION", "JAXPP_ENABLE_LOCAL_PROPAGATION", "JAXPP_DISABLE_PREVENT_CSE",
+        "JAXPP_DIRECTIONAL_COMMUNICATORS", "JAXPP_DEBUG_SKIP_PROPAGATION", "JAXPP_FAST_INFER_SHARDINGS"}
+    config._WARNED.clear()
+    log = logging.getLogger("test_flags")
+    with caplog.at_level(logging.WARNING, logger="test_flags"):
+        config.warn_about_flags_without_effect(log)
+        assert not caplog.records                       # defaults: nothing to report
+        with config.fast_infer_shardings.set(True):
+            config.warn_about_flags_without_effect(log)
+            config.warn_about_flags_without_effect(log)   # once only
+    assert len(caplog.records) == 1 and "JAXPP_FAST_INFER_SHARDINGS" in caplog.records[0].getMessage()
+    config._WARNED.clear()
