@@ -46,6 +46,8 @@ def parse():
                          "projection and loss of the last stage) or a comma-separated list (entries may end in .5)")
     ap.add_argument("--shard-optimizer", action="store_true", help="optimizer state as 1/dp slices (data-parallel configs)")
     ap.add_argument("--timeline", default=None, help="write a per-rank, per-task-kind timeline of one step to this file")
+    ap.add_argument("--op-times", default=None,
+                    help="write per-op device times of one extra step (CUDA events around every op call) to this file")
     ap.add_argument("--p2p", default=None, choices=[None, "torch", "native"], help="point-to-point backend between stages")
     return ap.parse_args()
 
@@ -279,6 +281,30 @@ def main():
             with open(args.timeline, "w") as f:
                 f.write(f"# one step of {rc.name} on {n} GPUs with per-task CUDA events (stage sizes {cfg.stage_sizes}); "
                         "'idle before' = compute stream idle in front of a task (waiting for another rank)\n")
+                f.write("\n\n".join(texts) + "\n")
+
+    if args.op_times:
+        from jaxpp_b200.utils import optimes
+
+        sync_all()
+        with optimes.collecting():
+            o0, o1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            o0.record()
+            compiled(leaves)
+            o1.record()
+            torch.cuda.synchronize()
+            rows = optimes.table()
+        text = optimes.format_table(rows, o0.elapsed_time(o1),
+                                    f"process {rank} (pipeline rank {my_pp if my_pp is not None else 0}, tp {tp_rank}, dp {dp_rank})")
+        texts = [text]
+        if world > 1:
+            texts = [None] * world
+            dist.all_gather_object(texts, text)
+        if rank == 0:
+            os.makedirs(os.path.dirname(os.path.abspath(args.op_times)), exist_ok=True)
+            with open(args.op_times, "w") as f:
+                f.write(f"# per-op device time of one step of {rc.name} on {n} GPUs: CUDA events around every op call of every "
+                        f"task, under the conditions of the timed run (uninstrumented step: {ms:.1f} ms)\n")
                 f.write("\n\n".join(texts) + "\n")
 
     canaries_ok = symm.check_all_canaries()

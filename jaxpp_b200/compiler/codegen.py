@@ -55,15 +55,20 @@ class TaskCode:
         return (self.src, tuple(id(t) for t in self.targets), tuple(repr(c) for c in self.consts))
 
     def bind(self, device: torch.device) -> Callable:
-        fn = self._bound.get(device)
+        from ..utils import optimes
+
+        timed = optimes.ACTIVE[0]      # per-op timing: the same code over call targets that record CUDA events
+        key = (device, timed)
+        fn = self._bound.get(key)
         if fn is None:
             consts = [device if isinstance(c, torch.device) else c for c in self.consts]
             from ..ops import sink as _sink
 
-            scope = {"T": self.targets, "C": consts, "DEV": device, "WG": _sink.call}
+            targets = [optimes.Timed(t) for t in self.targets] if timed else self.targets
+            scope = {"T": targets, "C": consts, "DEV": device, "WG": _sink.call}
             exec(compile(self.src, f"<task {self.name}>", "exec"), scope)
             fn = scope["run"]
-            self._bound[device] = fn
+            self._bound[key] = fn
         return fn
 
 

@@ -155,9 +155,11 @@ class Lowering:
             if schedule is None:
                 schedule = cap.trace.schedule
             body_templates, loop_out_rank = self.lower_loop(loop, schedule, in_ranks)
+            moved = self.plan_early_collectives(loop) if config.overlap_grad_reduce.value else {}
             after_exclude = set(loop.body) | set(loop.slice_of) | {loop.begin, loop.index, loop.end}
             after_exclude.discard(None)
             after_exclude |= set(loop.results.values())
+            after_exclude |= set(moved)
             after_nodes = [
                 n for n in graph.nodes
                 if n.op in ("call_function", "get_attr") and n not in after_exclude
@@ -165,6 +167,8 @@ class Lowering:
             fixed = {}
             for k, res in loop.results.items():
                 fixed[res] = {loop_out_rank[k]}
+            for node, rank in moved.items():
+                fixed[node] = {rank}
             self.lower_straight(after_nodes, fixed, in_ranks, flat_outputs, label="after_loop")
         else:
             region = [n for n in graph.nodes if n.op in ("call_function", "get_attr")]
@@ -458,7 +462,59 @@ class Lowering:
                 pending.append((fu, rank, dst, [v for _, v in items]))
         flush()
         self.units = units
+        self.acc_vid = acc_vid
         return templates, loop_out_rank
+
+    # ------------------------------------------------------------------------------------------
+    def plan_early_collectives(self, loop) -> dict:
+        """Move gradient collectives from after the loop into the backward pass of the last microbatch.
+
+        A step sums every weight gradient over the microbatches (``treduce``) and then, after the loop, reduces it
+        over the data-parallel ranks (``b200tp::all_reduce``, or ``b200dp::reduce_scatter_flat`` with sharded
+        optimizer state).  When the accumulator is fed through a weight-gradient sink, the task that adds the
+        *last* contribution is known here, and so is the moment inside it when the gradient is final: right after
+        that weight-gradient GEMM.  The collective is attached to the task as a hook; the executor issues it at
+        that point on a side stream, where it overlaps the rest of the backward pass (earlier layers' gradients,
+        other stages' tasks), and the after-loop region reads its result instead of running it.  The reference gets
+        the same overlap from XLA's latency-hiding scheduler over its after-loop reduce-scatter (PERF_GUIDE.md:63-70).
+        Same kernels, same operands: the results are bit-identical to the after-loop form.
+
+        Returns ``{after-loop collective node: pipeline rank}`` for the nodes that were moved."""
+        from ..ops.sink import early_collective_targets
+
+        targets = early_collective_targets()
+        moved: dict = {}
+        if loop.n < 2:
+            return moved
+        for k, res in loop.results.items():
+            if loop.out_kinds[k] != prim.OP_ADD or k not in self.acc_vid:
+                continue
+            users = list(res.users)
+            if len(users) != 1 or users[0].target not in targets or users[0].args[0] is not res:
+                continue
+            node = users[0]
+            if any(isinstance(a, fx.Node) for a in node.args[1:]) or node.kwargs:
+                continue
+            acc = self.acc_vid[k]
+            last_task = None
+            last_acc = None
+            for ins in self.instrs:
+                if isinstance(ins, RunTask) and any(a == acc for _, a in ins.sinks):
+                    last_task = ins
+                elif isinstance(ins, Accum) and ins.acc == acc:
+                    last_acc = ins
+            if last_task is None or last_acc is None:
+                continue
+            pos = next(j for j, a in last_task.sinks if a == acc)
+            if last_task.outs[pos] != last_acc.val:
+                continue   # the final contribution does not come through the sink
+            result = self.vid_of_const(node)
+            last_task.hooks.append((pos, acc, result, node.target, tuple(node.args[1:])))
+            self.where[result].add(last_task.rank)
+            moved[node] = last_task.rank
+        if moved:
+            logger.info("%d gradient collectives issued from the last microbatch's backward tasks", len(moved))
+        return moved
 
     def graph_val(self, node: fx.Node, k: int):
         return _meta(node)[k]
@@ -765,7 +821,7 @@ class Lowering:
 
         def defs(ins):
             if isinstance(ins, RunTask):
-                return [(ins.rank, v) for v in ins.outs if v >= 0]
+                return [(ins.rank, v) for v in ins.outs if v >= 0] + [(ins.rank, h[2]) for h in ins.hooks]
             if isinstance(ins, (Slice, LoopIndex)):
                 return [(ins.rank, ins.out)]
             if isinstance(ins, Transfer):

@@ -57,6 +57,11 @@ class RunTask(Instr):
     # (output position, accumulator value id): outputs that only feed the loop's Add accumulation and that the
     # task can add into the accumulator itself (weight gradients, see ops/sink.py)
     sinks: list = dataclasses.field(default_factory=list)
+    # (output position, accumulator value id, result value id, collective op, its other arguments): a gradient
+    # collective that the step applies to a loop accumulator after the loop, issued instead from inside this task --
+    # the one that adds the last microbatch's contribution -- as soon as the weight-gradient GEMM has run, on a side
+    # stream, so that it overlaps the rest of the backward pass (see lower.Lowering.plan_early_collectives)
+    hooks: list = dataclasses.field(default_factory=list)
 
 
 @dataclasses.dataclass
@@ -183,7 +188,8 @@ def format_instr(ins: Instr, values, view_rank: int | None = None) -> str:
     if isinstance(ins, RunTask):
         outs = ", ".join(_v(values, v) for v in ins.outs)
         inn = ", ".join(("~" if d else "") + f"%{v}" for v, d in zip(ins.ins, ins.donate))
-        return f"{r}{outs} = task {ins.name} t={ins.start}..{ins.end} ({inn})"
+        early = "".join(f" ; %{h[2]} = early {str(h[3]).split('.')[-2]}(%{h[1]})" for h in ins.hooks)
+        return f"{r}{outs} = task {ins.name} t={ins.start}..{ins.end} ({inn}){early}"
     if isinstance(ins, Slice):
         return f"{r}%{ins.out} = slice %{ins.src} axis={ins.axis} index={ins.index}"
     if isinstance(ins, LoopIndex):

@@ -21,7 +21,7 @@ class ProgramError(AssertionError):
 
 def _uses_defs(ins, rank):
     if isinstance(ins, RunTask):
-        return list(ins.ins), [v for v in ins.outs if v >= 0]
+        return list(ins.ins), [v for v in ins.outs if v >= 0] + [h[2] for h in ins.hooks]
     if isinstance(ins, Slice):
         return [ins.src], [ins.out]
     if isinstance(ins, LoopIndex):

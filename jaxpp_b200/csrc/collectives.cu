@@ -62,7 +62,7 @@ __device__ __forceinline__ bool ar_wait_all(const int* flags, int n_ranks, int r
       uint32_t spins = 0;
       while (ar_ld_acquire_sys(flags + q) < epoch) {
         if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > wait_budget_ns()) {
-          if (status) atomicCAS(status, JPB_OK, JPB_ERR_PEER_TIMEOUT);
+          report_status(status, JPB_ERR_PEER_TIMEOUT);
           ok = 0;
           break;
         }

@@ -11,7 +11,8 @@
 #define JPB_STR2(x) #x
 #define JPB_STR(x) JPB_STR2(x)
 
-// Status codes written to the status word (first error wins).
+// Status codes written to the status word.  The larger code wins: a kernel that gives up on a silent peer also makes
+// its own internal waits run out, and the report should name the cause (the peer), not the symptom.
 enum JpbStatus : int {
   JPB_OK = 0,
   JPB_ERR_WAIT_TIMEOUT = 1,   // a bounded wait on an mbarrier / flag ran out
@@ -35,6 +36,18 @@ __device__ __forceinline__ uint64_t wait_budget_ns() { return g_wait_budget_ns; 
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// Record `code` in the status word unless a higher code is already there (compare-and-swap loop: the word lives in
+// mapped host memory, where compare-and-swap is the atomic known to work from the device).
+__device__ __forceinline__ void report_status(int* status, int code) {
+  if (status == nullptr) return;
+  int old = *reinterpret_cast<volatile int*>(status);
+  while (old < code) {
+    const int prev = atomicCAS(status, old, code);
+    if (prev == old) break;
+    old = prev;
+  }
 }
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
@@ -85,7 +98,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
       if (*abort_flag) return false;
       if (globaltimer_ns() - t0 > wait_budget_ns()) {
         *abort_flag = 1;
-        if (status) atomicCAS(status, JPB_OK, code);
+        report_status(status, code);
         return false;
       }
     }

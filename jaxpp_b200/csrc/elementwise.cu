@@ -486,7 +486,7 @@ __global__ void embedding_fwd_kernel(const int64_t* __restrict__ ids, const T* _
     const int c = int(i % dv) * VN;
     int64_t id = ids[t];
     if (id < 0 || id >= vocab) {  // record and clamp instead of faulting
-      if (status) atomicCAS(status, JPB_OK, JPB_ERR_BAD_ARGUMENT);
+      report_status(status, JPB_ERR_BAD_ARGUMENT);
       id = 0;
     }
     Vec<T> v; v.load(table + size_t(id) * d + c);

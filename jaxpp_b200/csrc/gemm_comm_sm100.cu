@@ -105,7 +105,7 @@ __device__ __forceinline__ bool flag_wait_bounded(const int* flag, int want, boo
       if (t0 == 0) t0 = now;
       if (now - t0 > wait_budget_ns()) {
         *abort_flag = 1;
-        if (status) atomicCAS(status, JPB_OK, code);
+        report_status(status, code);
         return false;
       }
     }
@@ -129,7 +129,7 @@ __device__ __forceinline__ bool flag_wait4_bounded(const int* flags, int want, v
       if (t0 == 0) t0 = now;
       if (now - t0 > wait_budget_ns()) {
         *abort_flag = 1;
-        if (status) atomicCAS(status, JPB_OK, code);
+        report_status(status, code);
         return false;
       }
     }
@@ -169,7 +169,7 @@ __device__ __forceinline__ bool flags_wait_all_bounded(const int* flags, int cou
       if (t0 == 0) t0 = now;
       if (now - t0 > wait_budget_ns()) {
         *abort_flag = 1;
-        if (status) atomicCAS(status, JPB_OK, code);
+        report_status(status, code);
         return false;
       }
     }

@@ -84,7 +84,7 @@ __device__ __forceinline__ bool moe_wait_peer(const MoeParams& p, int q, int lan
     uint32_t spins = 0;
     while (moe_ld_acquire_sys(p.flags_local + q) < p.epoch) {
       if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > wait_budget_ns()) {
-        if (p.status) atomicCAS(p.status, JPB_OK, JPB_ERR_PEER_TIMEOUT);
+        report_status(p.status, JPB_ERR_PEER_TIMEOUT);
         ok = 0;
         break;
       }
@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(MOE_THREADS, 4) moe_dispatch_kernel(const MoeP
     const int slot = (owner * p.e_local + el) * C + pos;
     int tok = p.index[slot];
     if (tok >= p.n_tokens) {  // an index outside the token range: record it and treat the slot as empty
-      if (lane == 0 && p.status) atomicCAS(p.status, JPB_OK, JPB_ERR_BAD_ARGUMENT);
+      if (lane == 0) report_status(p.status, JPB_ERR_BAD_ARGUMENT);
       tok = -1;
     }
     const float s = (p.scale != nullptr && tok >= 0) ? p.scale[slot] : 1.f;
@@ -176,7 +176,7 @@ __global__ void __launch_bounds__(MOE_THREADS, 4) moe_combine_kernel(const MoePa
         const int slot = p.index[t * p.top_k + j];
         uint4 val = make_uint4(0u, 0u, 0u, 0u);
         if (slot < 0 || slot > dump) {  // not a slot and not the "dropped" marker: record it, contribute nothing
-          if (lane == 0 && v == lane && p.status) atomicCAS(p.status, JPB_OK, JPB_ERR_BAD_ARGUMENT);
+          if (lane == 0 && v == lane) report_status(p.status, JPB_ERR_BAD_ARGUMENT);
         } else if (slot < dump) {
           const int e = slot / C, pos = slot % C;
           const int owner = e / p.e_local, el = e % p.e_local;
@@ -312,7 +312,7 @@ __global__ void router_kernel(const T* __restrict__ logits, float* __restrict__ 
         for (int e = 0; e < E && best < 0; ++e)
           if (!((taken >> e) & 1ull)) best = e;
         bv = 0.f;
-        if (status) atomicCAS(status, JPB_OK, JPB_ERR_BAD_ARGUMENT);
+        report_status(status, JPB_ERR_BAD_ARGUMENT);
       }
       taken |= 1ull << best;
       idx[j] = best; val[j] = bv; picked += bv;

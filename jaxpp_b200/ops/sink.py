@@ -27,6 +27,13 @@ def sink_targets() -> tuple:
     return tuple(out)
 
 
+def early_collective_targets() -> tuple:
+    """Collectives on a summed gradient that may be issued from inside the task that completes the sum."""
+    from ..parallel import tp, zero  # noqa: F401  (register the ops)
+
+    return (torch.ops.b200tp.all_reduce.default, torch.ops.b200dp.reduce_scatter_flat.default)
+
+
 def _fits(acc: torch.Tensor, rows: int, cols: int, out_dtype) -> bool:
     return acc.dim() == 2 and acc.shape[0] == rows and acc.shape[1] == cols and (out_dtype is None or acc.dtype == out_dtype)
 
@@ -60,9 +67,30 @@ def accumulate(op, acc: torch.Tensor, *args, **kwargs) -> torch.Tensor:
     return acc.add_(op(*args, **kwargs))
 
 
+class _Named:
+    def __init__(self, fn, name):
+        self.fn, self.__name__ = fn, name
+
+    def __call__(self, *a, **k):
+        return self.fn(*a, **k)
+
+    def __str__(self):
+        return self.__name__
+
+
 def call(op, sink, index: int, *args, **kwargs):
     """What generated task code calls for a sinkable op: ``sink`` maps output positions to accumulators."""
     acc = sink.get(index) if sink else None
     if acc is None:
         return op(*args, **kwargs)
+    from ..utils import optimes
+
+    if isinstance(op, optimes.Timed):      # per-op timing is on: time the accumulating form under the op's name
+        inner, s2 = op.target, {index: acc}
+        return optimes.Timed(_Named(lambda *a, **k: call(inner, s2, index, *a, **k), op.name))(*args, **kwargs)
+    if isinstance(acc, tuple):   # (accumulator, hook): the gradient is final after this contribution
+        acc, hook = acc
+        out = accumulate(op, acc, *args, **kwargs)
+        hook(out)
+        return out
     return accumulate(op, acc, *args, **kwargs)

@@ -230,7 +230,11 @@ def _peer_collective(flat: torch.Tensor, group, ranks: list, scale: float, mode:
         n = (flat.numel() + quantum - 1) // quantum * quantum
     staged = flat.numel() if mode == 2 else n        # elements of X that this call uses
     nbytes = staged * es
-    key = tuple(ranks)
+    from ..runtime import executor as _ex
+    from ..utils import config as _config
+
+    side = _ex.OVERLAPPED[0]
+    key = (tuple(ranks), "side") if side else tuple(ranks)
     ws = _AR_WS.get(key)
     if ws is None or ws.slot < nbytes:
         if ws is not None:
@@ -244,6 +248,8 @@ def _peer_collective(flat: torch.Tensor, group, ranks: list, scale: float, mode:
     d.dtype = 0 if flat.dtype == torch.float32 else 1
     d.n, d.scale = n, float(scale)
     d.grid = lib.jpb_allreduce_grid2(n, es, symm.reserved_sms())
+    if side:   # runs beside the backward pass: a few CTAs are enough for a link and leave the SMs to the GEMMs
+        d.grid = max(1, min(d.grid, int(_config.overlap_collective_ctas.value)))
     if mode == 0:
         ws.ctas += d.grid
     d.counter_target = ws.ctas & 0xFFFFFFFF

@@ -44,6 +44,29 @@ def collect_task_times_ms(enabled: bool = True):
         _TIMES.pop()
 
 
+_SIDE_STREAMS: dict = {}
+OVERLAPPED = [False]
+
+
+def _side_stream(device: torch.device):
+    s = _SIDE_STREAMS.get(device)
+    if s is None:
+        s = _SIDE_STREAMS[device] = torch.cuda.Stream(device)
+    return s
+
+
+@contextlib.contextmanager
+def overlapped_collectives():
+    """Inside: peer-memory collectives use their side-stream workspace (its flags and epochs are independent of the
+    compute stream's, whose calls are ordered separately) and a small grid that shares the SMs with compute kernels."""
+    prev = OVERLAPPED[0]
+    OVERLAPPED[0] = True
+    try:
+        yield
+    finally:
+        OVERLAPPED[0] = prev
+
+
 class RankState:
     """Environment and instruction semantics of one pipeline rank."""
 
@@ -54,6 +77,7 @@ class RankState:
         self.index_cache: dict[int, torch.Tensor] = {}
         self.record_events = record_events and device.type == "cuda"
         self.events: list[tuple[str, Any, Any]] = []
+        self.pending_events: dict[int, Any] = {}   # value id -> CUDA event of the side-stream work that produces it
 
     # -- individual instructions --------------------------------------------------------------
     def run_task(self, ins: RunTask):
@@ -61,10 +85,18 @@ class RankState:
         args = []
         for v, donate in zip(ins.ins, ins.donate):
             args.append(env.pop(v) if donate else env[v])
+        if self.pending_events:
+            for v in ins.ins:
+                ev = self.pending_events.pop(v, None)
+                if ev is not None:
+                    torch.cuda.current_stream(self.device).wait_event(ev)
         fn = ins.code.bind(self.device)
         sink = None
         if ins.sinks:
             sink = {j: env[acc] for j, acc in ins.sinks if acc in env}
+            for hook in ins.hooks:
+                if hook[0] in sink:
+                    sink[hook[0]] = (sink[hook[0]], self._early_collective(hook))
         timing = _TIMES[-1] if _TIMES else None
         if timing is not None:
             if self.device.type == "cuda":
@@ -92,6 +124,33 @@ class RankState:
         for v, o in zip(ins.outs, outs):
             if v >= 0:
                 env[v] = o
+
+    def _early_collective(self, hook):
+        """The callable a weight-gradient sink runs once the last contribution is in the accumulator: launch the
+        gradient collective on the side stream (ordered after the GEMM that was just enqueued) and leave its result
+        in the environment for the after-loop task, which waits for the side stream's event."""
+        _, _, result_vid, op, args = hook
+
+        def run(acc: torch.Tensor):
+            if self.device.type != "cuda":
+                self.env[result_vid] = op(acc, *args)
+                return
+            main = torch.cuda.current_stream(self.device)
+            side = _side_stream(self.device)
+            ready = torch.cuda.Event()
+            ready.record(main)
+            with torch.cuda.stream(side):
+                side.wait_event(ready)
+                with overlapped_collectives():
+                    out = op(acc, *args)
+                done = torch.cuda.Event()
+                done.record(side)
+            acc.record_stream(side)     # read by the side stream after this task has dropped it
+            out.record_stream(main)     # allocated on the side stream, consumed on the compute stream
+            self.env[result_vid] = out
+            self.pending_events[result_vid] = done
+
+        return run
 
     def slice(self, ins: Slice):
         self.env[ins.out] = self.env[ins.src].select(ins.axis, ins.index)

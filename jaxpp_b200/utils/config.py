@@ -160,6 +160,11 @@ zb_memory_scarce = BoolEnvVar("JAXPP_B200_ZB_MEMORY_SCARCE", True)
 # Zero-bubble split: bytes of operands that deferred weight-gradient GEMMs may keep alive per (stage, microbatch);
 # weight gradients beyond the budget run with the activation gradients.  Negative = no limit.
 zb_defer_bytes = IntEnvVar("JAXPP_B200_ZB_DEFER_BYTES", -1)
+# Issue the data-parallel gradient collectives (all-reduce, or reduce-scatter with sharded optimizer state) from inside
+# the backward task that adds the last microbatch's weight gradient, on a side stream, instead of after the loop.
+overlap_grad_reduce = BoolEnvVar("JAXPP_B200_OVERLAP_GRAD_REDUCE", True)
+# CTAs of a peer-memory collective that runs beside compute kernels (it shares the SMs with them).
+overlap_collective_ctas = IntEnvVar("JAXPP_B200_OVERLAP_CTAS", 32)
 # Seconds a rank may go without a heartbeat before the watchdog reports it.
 heartbeat_timeout_s = IntEnvVar("JAXPP_B200_HEARTBEAT_TIMEOUT", 30)
 # Wrap every task in an NVTX range named like the task (fwd_3__5, …) for timeline profilers.

@@ -245,6 +245,30 @@ def scenario_dp_ep(family, shard_optimizer=False):
         tok_l = tokens[:, me_dp * half:(me_dp + 1) * half].contiguous().to(dev)
         lab_l = labels[:, me_dp * half:(me_dp + 1) * half].contiguous().to(dev)
     got_state, got_losses = f(local_view(state1), tok_l, lab_l)
+    if not context_parallel and os.environ.get("TEST_OVERLAP"):
+        # the gradient collectives issued from inside the last microbatch's backward tasks against the same step with
+        # the collectives after the loop: same kernels on the same operands, so bit for bit
+        from jaxpp_b200.compiler.program import RunTask
+        from jaxpp_b200.utils import config
+
+        prog = f.lower(local_view(state1), tok_l, lab_l).program
+        n_hooks = sum(len(i.hooks) for i in prog.instrs if isinstance(i, RunTask))
+        assert n_hooks >= 6, f"only {n_hooks} gradient collectives were moved into the backward pass"
+        with config.overlap_grad_reduce.set(False):
+            f_after = jp.mpmd_jit_with_loop(step, mesh)
+            prog_after = f_after.lower(local_view(state1), tok_l, lab_l).program
+            assert not any(i.hooks for i in prog_after.instrs if isinstance(i, RunTask))
+            after_state, after_losses = f_after(local_view(state1), tok_l, lab_l)
+        a = pytree.tree_leaves(after_state, is_leaf=lambda x: isinstance(x, jp.MpmdArray))
+        b = pytree.tree_leaves(got_state, is_leaf=lambda x: isinstance(x, jp.MpmdArray))
+        compared = 0
+        for x, y in zip(a, b):
+            tx, ty = x.local_tensor(), y.local_tensor()
+            assert (tx is None) == (ty is None)
+            if tx is not None:
+                assert torch.equal(tx, ty), "overlapped and after-loop gradient reduction differ"
+                compared += 1
+        assert compared > 0
     ref_local = local_view(ref_state)
     # with capacity-based routing the per-rank capacity differs from the single-rank run only if tokens are dropped;
     # the generous capacity factor above keeps every token, so results agree up to reassociation

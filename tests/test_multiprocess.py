@@ -42,6 +42,13 @@ def test_pipeline_times_data_parallel():
     run("pp2_dp2_gpt2", 4)
 
 
+@pytest.mark.parametrize("scenario", ["pp2_dp2_gpt2", "pp2_dp2_gpt2_zero", "pp2_ep2_mixtral"])
+def test_gradient_reduction_issued_from_the_last_backward_matches_the_after_loop_form(scenario):
+    """Data-parallel gradient all-reduce (or reduce-scatter with sharded optimizer state) hooked into the task that adds
+    the last microbatch's weight gradient, against the same collectives run after the loop: identical bits."""
+    run(scenario, 4, TEST_OVERLAP="1")
+
+
 def test_pipeline_times_expert_parallel_moe():
     run("pp2_ep2_mixtral", 4)
 
