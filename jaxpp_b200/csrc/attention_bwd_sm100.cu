@@ -14,9 +14,22 @@
 // transposed in memory.  All waits are bounded.
 #include "common.cuh"
 
+#include <cstdlib>
+
 namespace jpb {
 
-constexpr int BWD_THREADS = 320;  // TMA warp, MMA warp, 2 x 4 softmax warps (each group owns 32 of the 64 columns)
+// Threads of both main kernels: a TMA warp, an MMA warp and NG softmax groups of four warps.  A group owns 64 / NG of
+// the 64 columns of an S tile (and D / NG of the accumulator columns in the epilogue).  NG = 4 puts four warps on
+// every scheduler: each thread then holds 16 columns (half the registers) and the chain "S ready -> TMEM load ->
+// exponentials -> pack -> shared memory -> hand-over", which paces the loop, is spread over twice the warps.
+constexpr int bwd_threads(int ng) { return 64 + 128 * ng; }
+
+// 32 lanes x W consecutive fp32 columns from TMEM, W = 16 or 32
+template <int W>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[W]) {
+  if constexpr (W == 32) tmem_ld_32x32(taddr, r);
+  else tmem_ld_32x16(taddr, r);
+}
 
 struct AttnBwdParams {
   int B, Sq, Sk, H, Hkv;
@@ -110,8 +123,8 @@ struct DkvTiles {
   }
 };
 
-template <int D>
-__global__ void __launch_bounds__(BWD_THREADS, 1)
+template <int D, int NG>
+__global__ void __launch_bounds__(bwd_threads(NG), 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                      const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                      const AttnBwdParams p) {
@@ -135,8 +148,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     mbar_init(&bar[K1_KVE], 1);
     for (int s = 0; s < BWD_NS; ++s) { mbar_init(&bar[K1_QF + s], 1); mbar_init(&bar[K1_QE + s], 1); }
     mbar_init(&bar[K1_SF], 1);
-    mbar_init(&bar[K1_SFREE], 8);
-    mbar_init(&bar[K1_PF], 8);
+    mbar_init(&bar[K1_SFREE], 4 * NG);
+    mbar_init(&bar[K1_PF], 4 * NG);
     mbar_init(&bar[K1_PE], 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -267,8 +280,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const int r = quarter * 32 + lane;  // kv row within the block == TMEM lane
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
     const float sl2 = p.scale * 1.4426950408889634f;
-    const int grp = (warp - 2) >> 2;  // which half of the 64 query columns this warp group handles
-    const int cb = grp * 32;
+    constexpr int CW = 64 / NG;       // query columns of an S^T tile per warp group
+    constexpr int EC = D / NG;        // accumulator columns per warp group in the epilogue
+    const int grp = (warp - 2) >> 2;  // which part of the 64 query columns this warp group handles
+    const int cb = grp * CW;
     const int off = p.Sk - p.Sq;
     bool ok = true;
     uint32_t g = 0;
@@ -283,7 +298,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       __nv_bfloat16* dv_row = p.dv + ((size_t(b) * p.Sk + kv) * p.Hkv + hk) * D;
       if (n_iter == 0) {
         if (row_ok) {
-          for (int i = grp * (D / 2); i < (grp + 1) * (D / 2); i += 8) {
+          for (int i = grp * EC; i < (grp + 1) * EC; i += 8) {
             *reinterpret_cast<uint4*>(dk_row + i) = make_uint4(0, 0, 0, 0);
             *reinterpret_cast<uint4*>(dv_row + i) = make_uint4(0, 0, 0, 0);
           }
@@ -296,21 +311,21 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         // per-column statistics of this block, fetched before the tensor core is done (same address in every lane)
         const float* lse_q = p.lse + (size_t(b) * p.H + h) * p.Sq;
         const float* dl_q = p.delta + (size_t(b) * p.H + h) * p.Sq;
-        // tile-level test (warp-uniform): is every (kv row, query column) of this warp group's 128 x 32 block visible?
-        const bool full = q0 + 31 < p.Sq && kv0 + 127 < p.Sk && (!p.causal || kv0 + 127 <= q0 + off) && (p.Sq & 3) == 0;
-        float lq[32], dl[32];
+        // tile-level test (warp-uniform): is every (kv row, query column) of this warp group's 128 x CW block visible?
+        const bool full = q0 + CW - 1 < p.Sq && kv0 + 127 < p.Sk && (!p.causal || kv0 + 127 <= q0 + off) && (p.Sq & 3) == 0;
+        float lq[CW], dl[CW];
         if (full) {
           const float4* l4 = reinterpret_cast<const float4*>(lse_q + q0);
           const float4* d4 = reinterpret_cast<const float4*>(dl_q + q0);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
+          for (int i = 0; i < CW / 4; ++i) {
             const float4 a = __ldg(l4 + i), c = __ldg(d4 + i);
             lq[4 * i] = a.x; lq[4 * i + 1] = a.y; lq[4 * i + 2] = a.z; lq[4 * i + 3] = a.w;
             dl[4 * i] = c.x; dl[4 * i + 1] = c.y; dl[4 * i + 2] = c.z; dl[4 * i + 3] = c.w;
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < CW; ++i) {
             const bool in = q0 + i < p.Sq;
             lq[i] = in ? __ldg(lse_q + q0 + i) : 0.f;
             dl[i] = in ? __ldg(dl_q + q0 + i) : 0.f;
@@ -318,28 +333,28 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
         if (!mbar_wait_bounded_warp(&bar[K1_SF], g & 1, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
-        float sv[32], dp[32];
+        float sv[CW], dp[CW];
         {
-          uint32_t a[32], d2[32];
-          tmem_ld_32x32(t_s + lane_addr + cb, a);
-          tmem_ld_32x32(t_dp + lane_addr + cb, d2);
+          uint32_t a[CW], d2[CW];
+          tmem_ld_cols<CW>(t_s + lane_addr + cb, a);
+          tmem_ld_cols<CW>(t_dp + lane_addr + cb, d2);
           tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) { sv[i] = __uint_as_float(a[i]); dp[i] = __uint_as_float(d2[i]); }
+          for (int i = 0; i < CW; ++i) { sv[i] = __uint_as_float(a[i]); dp[i] = __uint_as_float(d2[i]); }
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar[K1_SFREE]);
         if (full) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < CW; ++i) {
             const float pv = exp2f(fmaf(sv[i], sl2, -lq[i]));
             dp[i] = pv * fmaf(dp[i], p.scale, -dl[i]);
             sv[i] = pv;
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < CW; ++i) {
             const int q = q0 + i;
             const bool visible = q < p.Sq && kv < p.Sk && (!p.causal || kv <= q + off);
             float pv = 0.f, ds = 0.f;
@@ -357,14 +372,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         uint8_t* tp = smem + L::OFF_P;
         uint8_t* tds = smem + L::OFF_DS;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < CW / 8; ++c) {
           uint4 v, w;
           v.x = pack_bf16(sv[c * 8 + 0], sv[c * 8 + 1]); v.y = pack_bf16(sv[c * 8 + 2], sv[c * 8 + 3]);
           v.z = pack_bf16(sv[c * 8 + 4], sv[c * 8 + 5]); v.w = pack_bf16(sv[c * 8 + 6], sv[c * 8 + 7]);
           w.x = pack_bf16(dp[c * 8 + 0], dp[c * 8 + 1]); w.y = pack_bf16(dp[c * 8 + 2], dp[c * 8 + 3]);
           w.z = pack_bf16(dp[c * 8 + 4], dp[c * 8 + 5]); w.w = pack_bf16(dp[c * 8 + 6], dp[c * 8 + 7]);
-          st_swz(tp, r, grp * 4 + c, v);
-          st_swz(tds, r, grp * 4 + c, w);
+          st_swz(tp, r, grp * (CW / 8) + c, v);
+          st_swz(tds, r, grp * (CW / 8) + c, w);
         }
         fence_proxy_async();
         tc_fence_before();
@@ -381,19 +396,20 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const uint32_t src = which ? t_dk : t_dv;
         __nv_bfloat16* dst = which ? dk_row : dv_row;
 #pragma unroll
-        for (int c = grp * (D / 64); c < (grp + 1) * (D / 64); ++c) {  // each warp group writes half of the columns
-          uint32_t a[32];
-          tmem_ld_32x32(src + lane_addr + c * 32, a);
+        for (int c = 0; c < EC / 16; ++c) {  // each warp group writes its EC of the D columns, 16 at a time
+          const int col = grp * EC + c * 16;
+          uint32_t a[16];
+          tmem_ld_32x16(src + lane_addr + col, a);
           tc_wait_ld();
           if (row_ok) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
+            for (int i = 0; i < 16; i += 8) {
               uint4 v;
               v.x = pack_bf16(__uint_as_float(a[i]), __uint_as_float(a[i + 1]));
               v.y = pack_bf16(__uint_as_float(a[i + 2]), __uint_as_float(a[i + 3]));
               v.z = pack_bf16(__uint_as_float(a[i + 4]), __uint_as_float(a[i + 5]));
               v.w = pack_bf16(__uint_as_float(a[i + 6]), __uint_as_float(a[i + 7]));
-              *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
+              *reinterpret_cast<uint4*>(dst + col + i) = v;
             }
           }
         }
@@ -447,8 +463,8 @@ struct DqTiles {
   }
 };
 
-template <int D>
-__global__ void __launch_bounds__(BWD_THREADS, 1)
+template <int D, int NG>
+__global__ void __launch_bounds__(bwd_threads(NG), 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                    const AttnBwdParams p) {
@@ -472,8 +488,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     mbar_init(&bar[K2_QFREE], 1);
     for (int s = 0; s < BWD_NS; ++s) { mbar_init(&bar[K2_KF + s], 1); mbar_init(&bar[K2_KE + s], 1); }
     mbar_init(&bar[K2_SF], 1);
-    mbar_init(&bar[K2_SFREE], 8);
-    mbar_init(&bar[K2_DF], 8);
+    mbar_init(&bar[K2_SFREE], 4 * NG);
+    mbar_init(&bar[K2_DF], 4 * NG);
     mbar_init(&bar[K2_DE], 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -595,8 +611,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
     const float sl2 = p.scale * 1.4426950408889634f;
     const int off = p.Sk - p.Sq;
-    const int grp = (warp - 2) >> 2;  // which half of the 64 kv columns this warp group handles
-    const int cb = grp * 32;
+    constexpr int CW = 64 / NG;       // kv columns of an S tile per warp group
+    constexpr int EC = D / NG;        // dQ columns per warp group in the epilogue
+    const int grp = (warp - 2) >> 2;  // which part of the 64 kv columns this warp group handles
+    const int cb = grp * CW;
     bool ok = true;
     uint32_t g = 0;
     int m_blk, h, b, n_iter;
@@ -610,30 +628,30 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       for (int t = 0; t < n_iter && ok; ++t, ++g) {
         if (!mbar_wait_bounded_warp(&bar[K2_SF], g & 1, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
-        float sv[32], dp[32];
+        float sv[CW], dp[CW];
         {
-          uint32_t a[32], d2[32];
-          tmem_ld_32x32(t_s + lane_addr + cb, a);
-          tmem_ld_32x32(t_dp + lane_addr + cb, d2);
+          uint32_t a[CW], d2[CW];
+          tmem_ld_cols<CW>(t_s + lane_addr + cb, a);
+          tmem_ld_cols<CW>(t_dp + lane_addr + cb, d2);
           tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) { sv[i] = __uint_as_float(a[i]); dp[i] = __uint_as_float(d2[i]); }
+          for (int i = 0; i < CW; ++i) { sv[i] = __uint_as_float(a[i]); dp[i] = __uint_as_float(d2[i]); }
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar[K2_SFREE]);
-        // warp-uniform: every (query row, kv column) of this warp group's 128 x 32 block visible?
+        // warp-uniform: every (query row, kv column) of this warp group's 128 x CW block visible?
         const int kv_first = t * 64 + cb;
-        const bool full = m0 + 127 < p.Sq && kv_first + 31 < p.Sk && (!p.causal || kv_first + 31 <= m0 + off);
+        const bool full = m0 + 127 < p.Sq && kv_first + CW - 1 < p.Sk && (!p.causal || kv_first + CW - 1 <= m0 + off);
         if (full) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < CW; ++i) {
             const float pv = exp2f(fmaf(sv[i], sl2, -lse_r));
             dp[i] = pv * fmaf(dp[i], p.scale, -dl_r);
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < CW; ++i) {
             const int kv = kv_first + i;
             const bool visible = row_ok && kv < p.Sk && (!p.causal || kv <= qi + off);
             float ds = 0.f;
@@ -649,11 +667,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         uint8_t* tds = smem + L::OFF_DS;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < CW / 8; ++c) {
           uint4 w;
           w.x = pack_bf16(dp[c * 8 + 0], dp[c * 8 + 1]); w.y = pack_bf16(dp[c * 8 + 2], dp[c * 8 + 3]);
           w.z = pack_bf16(dp[c * 8 + 4], dp[c * 8 + 5]); w.w = pack_bf16(dp[c * 8 + 6], dp[c * 8 + 7]);
-          st_swz(tds, r, grp * 4 + c, w);
+          st_swz(tds, r, grp * (CW / 8) + c, w);
         }
         fence_proxy_async();
         tc_fence_before();
@@ -667,19 +685,20 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       tc_fence_after();
       __nv_bfloat16* dst = p.dq + ((size_t(b) * p.Sq + qi) * p.H + h) * D;
 #pragma unroll
-      for (int c = grp * (D / 64); c < (grp + 1) * (D / 64); ++c) {
-        uint32_t a[32];
-        tmem_ld_32x32(t_dq + lane_addr + c * 32, a);
+      for (int c = 0; c < EC / 16; ++c) {
+        const int col = grp * EC + c * 16;
+        uint32_t a[16];
+        tmem_ld_32x16(t_dq + lane_addr + col, a);
         tc_wait_ld();
         if (row_ok) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
+          for (int i = 0; i < 16; i += 8) {
             uint4 v;
             v.x = pack_bf16(__uint_as_float(a[i]), __uint_as_float(a[i + 1]));
             v.y = pack_bf16(__uint_as_float(a[i + 2]), __uint_as_float(a[i + 3]));
             v.z = pack_bf16(__uint_as_float(a[i + 4]), __uint_as_float(a[i + 5]));
             v.w = pack_bf16(__uint_as_float(a[i + 6]), __uint_as_float(a[i + 7]));
-            *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
+            *reinterpret_cast<uint4*>(dst + col + i) = v;
           }
         }
       }
@@ -699,7 +718,17 @@ static int make_map_rows(CUtensorMap* out, const void* base, int B, int S, int H
   return jpb_make_tensor_map(out, base, 2, 4, dims, strides, box, 1);
 }
 
-template <int D>
+// Softmax groups per CTA of the two backward kernels (2 or 4; JAXPP_B200_ATTN_BWD_GROUPS overrides the default).
+static int bwd_groups() {
+  static int ng = 0;
+  if (ng == 0) {
+    const char* e = getenv("JAXPP_B200_ATTN_BWD_GROUPS");
+    ng = (e && e[0] == '2') ? 2 : 4;
+  }
+  return ng;
+}
+
+template <int D, int NG>
 static int launch_bwd(const void* dO, const void* q, const void* k, const void* v, const AttnBwdParams& p, cudaStream_t stream) {
   CUtensorMap mq64, mdo64, mk128, mv128, mq128, mdo128, mk64, mv64;
   int rc = 0;
@@ -712,8 +741,8 @@ static int launch_bwd(const void* dO, const void* q, const void* k, const void* 
   rc |= make_map_rows(&mk64, k, p.B, p.Sk, p.Hkv, D, 64);
   rc |= make_map_rows(&mv64, v, p.B, p.Sk, p.Hkv, D, 64);
   if (rc) return rc;
-  auto k1 = attn_bwd_dkdv_kernel<D>;
-  auto k2 = attn_bwd_dq_kernel<D>;
+  auto k1 = attn_bwd_dkdv_kernel<D, NG>;
+  auto k2 = attn_bwd_dq_kernel<D, NG>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvSmem<D>::TOTAL) != cudaSuccess) return -3;
@@ -726,11 +755,11 @@ static int launch_bwd(const void* dO, const void* q, const void* k, const void* 
   const int n_kvb = (p.Sk + 127) / 128;
   const int items = ((n_kvb + 1) / 2) * p.Hkv * p.B;  // pairs of kv blocks, see DkvTiles
   const int g1 = items < sms ? items : sms;
-  k1<<<g1, BWD_THREADS, DkvSmem<D>::TOTAL, stream>>>(mq64, mdo64, mk128, mv128, p);
+  k1<<<g1, bwd_threads(NG), DkvSmem<D>::TOTAL, stream>>>(mq64, mdo64, mk128, mv128, p);
   const int num_m = (p.Sq + 127) / 128;
   const int items2 = ((num_m + 1) / 2) * p.H * p.B;  // pairs of query blocks, see DqTiles
   const int g2 = items2 < sms ? items2 : sms;
-  k2<<<g2, BWD_THREADS, DqSmem<D>::TOTAL, stream>>>(mq128, mdo128, mk64, mv64, p);
+  k2<<<g2, bwd_threads(NG), DqSmem<D>::TOTAL, stream>>>(mq128, mdo128, mk64, mv64, p);
   return int(cudaGetLastError());
 }
 
@@ -764,5 +793,6 @@ JPB_API int jpb_attention_bwd(const void* dO, const void* q, const void* k, cons
   p.lse = lse2; p.delta = delta;
   p.dq = static_cast<__nv_bfloat16*>(dq); p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
   p.status = jpb_status_device_ptr();
-  return D == 128 ? launch_bwd<128>(dO, q, k, v, p, s) : launch_bwd<64>(dO, q, k, v, p, s);
+  if (bwd_groups() == 2) return D == 128 ? launch_bwd<128, 2>(dO, q, k, v, p, s) : launch_bwd<64, 2>(dO, q, k, v, p, s);
+  return D == 128 ? launch_bwd<128, 4>(dO, q, k, v, p, s) : launch_bwd<64, 4>(dO, q, k, v, p, s);
 }

@@ -12,11 +12,15 @@
 // and halve the live registers.  All waits are bounded and report through the status word.
 #include "common.cuh"
 
+#include <cstdlib>
+
 namespace jpb {
 
 constexpr int ATT_BM = 128;   // query rows per CTA
 constexpr int ATT_BN = 128;   // kv rows per block
-constexpr int ATT_THREADS = 320;  // TMA warp, MMA warp, 2 softmax groups of 4 warps
+// TMA warp, MMA warp and NG softmax groups of four warps; a group owns 128 / NG of the kv columns of a block (and
+// D / NG of the O columns).  NG = 4 gives every scheduler four softmax warps and each thread 32 columns.
+constexpr int att_threads(int ng) { return 64 + 128 * ng; }
 
 struct AttnParams {
   int B, Sq, Sk, H, Hkv;
@@ -38,16 +42,16 @@ struct AttnSmem {
   static constexpr int OFF_K = OFF_Q + Q_BYTES;       // 2 stages
   static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;  // 2 stages
   static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
-  static constexpr int OFF_MAX = OFF_P + P_BYTES;       // [2 block parities][2 halves][128 rows] fp32 row maxima
-  static constexpr int OFF_SUM = OFF_MAX + 2048;      // [2 halves][128 rows] fp32 partial row sums
-  static constexpr int OFF_BAR = OFF_SUM + 1024;
+  static constexpr int OFF_MAX = OFF_P + P_BYTES;       // [2 block parities][up to 4 groups][128 rows] fp32 row maxima
+  static constexpr int OFF_SUM = OFF_MAX + 4096;      // [up to 4 groups][128 rows] fp32 partial row sums
+  static constexpr int OFF_BAR = OFF_SUM + 2048;
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
 };
 
 enum { BAR_Q = 0, BAR_KF = 1, BAR_VF = 3, BAR_KE = 5, BAR_VE = 7, BAR_SF = 9, BAR_SE = 11, BAR_PF = 13, BAR_PV = 14, BAR_MX = 15, BAR_N = 16 };
 
-template <int D>
-__global__ void __launch_bounds__(ATT_THREADS, 1)
+template <int D, int NG>
+__global__ void __launch_bounds__(att_threads(NG), 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
   using L = AttnSmem<D>;
@@ -78,11 +82,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       mbar_init(&bar[BAR_KE + s], 1);
       mbar_init(&bar[BAR_VE + s], 1);
       mbar_init(&bar[BAR_SF + s], 1);
-      mbar_init(&bar[BAR_SE + s], 8);
+      mbar_init(&bar[BAR_SE + s], 4 * NG);
     }
-    mbar_init(&bar[BAR_PF], 8);
+    mbar_init(&bar[BAR_PF], 4 * NG);
     mbar_init(&bar[BAR_PV], 1);
-    mbar_init(&bar[BAR_MX], 8);   // the eight softmax warps meet here once per block (and once at the end)
+    mbar_init(&bar[BAR_MX], 4 * NG);   // all softmax warps meet here once per block (and once at the end)
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&map_q);
@@ -195,15 +199,16 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     }
   } else {
     // ------------------------------------- softmax / correction / epilogue -----------------------------
-    constexpr int HALF = ATT_BN / 2;
+    constexpr int HALF = ATT_BN / NG;           // kv columns of a block per softmax group
+    constexpr int OC = D / NG;                  // O columns per softmax group
     const int quarter = warp & 3;
-    const int grp = (warp - 2) >> 2;            // which half of the kv columns (and of the O columns)
+    const int grp = (warp - 2) >> 2;            // which part of the kv columns (and of the O columns)
     const int r = quarter * 32 + lane;          // row within the tile == TMEM lane
     const int qi = m0 + r;                      // query index
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
     const float sl2 = p.scale * 1.4426950408889634f;
     float* smax = reinterpret_cast<float*>(smem + L::OFF_MAX);
-    float m_run = -INFINITY, l_run = 0.f;       // l_run: this thread's half of the row sum
+    float m_run = -INFINITY, l_run = 0.f;       // l_run: this thread's part of the row sum
     bool ok = true;
     uint8_t* sp = smem + L::OFF_P;
     for (int j = 0; j < n_blocks && ok; ++j) {
@@ -233,17 +238,18 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       float mx = sv[0];
 #pragma unroll
       for (int i = 1; i < HALF; ++i) mx = fmaxf(mx, sv[i]);
-      // the two halves of the row agree on the block maximum (double-buffered by block parity, so the next
+      // the groups of a row agree on the block maximum (double-buffered by block parity, so the next
       // block's write cannot overtake a slow reader of this one)
-      smax[(s * 2 + grp) * ATT_BM + r] = mx;
+      smax[(s * NG + grp) * ATT_BM + r] = mx;
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar[BAR_MX]);
       if (!mbar_wait_bounded_warp(&bar[BAR_MX], j & 1, abort_flag, p.status)) { ok = false; break; }
-      mx = fmaxf(mx, smax[(s * 2 + (grp ^ 1)) * ATT_BM + r]);
+#pragma unroll
+      for (int o = 1; o < NG; ++o) mx = fmaxf(mx, smax[(s * NG + ((grp + o) % NG)) * ATT_BM + r]);
       // Lazy rescaling: the reference maximum of a row only moves when the new maximum exceeds it by more than
       // 8 in log2 units (P then stays below 2^8, harmless in fp32 sums and bf16 P), so the read-scale-write
       // pass over O in TMEM, a chain of TMEM round trips, runs in a few blocks instead of nearly all of them.
-      // Both halves of a row see the same maxima and therefore take the same decision.
+      // All groups of a row see the same maxima and therefore take the same decision.
       const float m_cand = fmaxf(m_run, mx);
       const bool bump = (m_cand - m_run) * sl2 > 8.f;   // also true for the first finite maximum (m_run = -inf)
       const float m_new = bump ? m_cand : m_run;
@@ -263,20 +269,20 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         tc_fence_after();
         if (__any_sync(0xffffffffu, bump)) {
 #pragma unroll
-          for (int c = 0; c < D / 64; ++c) {   // this group's half of the O columns, 32 at a time
-            uint32_t t[32];
-            tmem_ld_32x32(tmem_o + lane_addr + grp * (D / 2) + c * 32, t);
+          for (int c = 0; c < OC / 16; ++c) {   // this group's part of the O columns, 16 at a time
+            uint32_t t[16];
+            tmem_ld_32x16(tmem_o + lane_addr + grp * OC + c * 16, t);
             tc_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * alpha);
-            tmem_st_32x32(tmem_o + lane_addr + grp * (D / 2) + c * 32, t);
+            for (int i = 0; i < 16; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * alpha);
+            tmem_st_32x16(tmem_o + lane_addr + grp * OC + c * 16, t);
           }
           tc_wait_st();
         }
       }
       m_run = m_new;
       // P -> shared memory, bf16, swizzled K-major: element (r, kv) lives in block kv/64 at
-      // r*128 + ((kv%64)/8 ^ (r%8))*16 + (kv%8)*2; this group's 64 columns are exactly block `grp`
+      // r*128 + ((kv%64)/8 ^ (r%8))*16 + (kv%8)*2
 #pragma unroll
       for (int c = 0; c < HALF / 8; ++c) {
         uint4 v;
@@ -284,7 +290,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         v.y = pack_bf16(sv[c * 8 + 2], sv[c * 8 + 3]);
         v.z = pack_bf16(sv[c * 8 + 4], sv[c * 8 + 5]);
         v.w = pack_bf16(sv[c * 8 + 6], sv[c * 8 + 7]);
-        *reinterpret_cast<uint4*>(sp + grp * L::TILE + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+        const int col = grp * HALF + c * 8;           // kv column of this chunk within the block
+        *reinterpret_cast<uint4*>(sp + (col >> 6) * L::TILE + r * 128 + ((((col & 63) >> 3) ^ (r & 7)) << 4)) = v;
       }
       fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's async proxy
       tc_fence_before();
@@ -293,30 +300,34 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     }
     if (ok && mbar_wait_bounded_warp(&bar[BAR_PV], (n_blocks - 1) & 1, abort_flag, p.status)) {
       tc_fence_after();
-      // combine the two partial row sums
+      // combine the partial row sums
       float* ssum = reinterpret_cast<float*>(smem + L::OFF_SUM);
       ssum[grp * ATT_BM + r] = l_run;
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar[BAR_MX]);
       if (!mbar_wait_bounded_warp(&bar[BAR_MX], n_blocks & 1, abort_flag, p.status)) ok = false;
-      const float l_all = ok ? l_run + ssum[(grp ^ 1) * ATT_BM + r] : 0.f;
+      float l_all = 0.f;
+      if (ok) {
+#pragma unroll
+        for (int o = 0; o < NG; ++o) l_all += ssum[o * ATT_BM + r];
+      }
       const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
       const bool row_ok = ok && qi < p.Sq;
-      __nv_bfloat16* orow = p.o + ((size_t(b) * p.Sq + qi) * p.H + h) * D + grp * (D / 2);
+      __nv_bfloat16* orow = p.o + ((size_t(b) * p.Sq + qi) * p.H + h) * D + grp * OC;
 #pragma unroll
-      for (int c = 0; c < D / 64; ++c) {
-        uint32_t t[32];
-        tmem_ld_32x32(tmem_o + lane_addr + grp * (D / 2) + c * 32, t);
+      for (int c = 0; c < OC / 16; ++c) {
+        uint32_t t[16];
+        tmem_ld_32x16(tmem_o + lane_addr + grp * OC + c * 16, t);
         tc_wait_ld();
         if (row_ok) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
+          for (int i = 0; i < 16; i += 8) {
             uint4 v;
             v.x = pack_bf16(__uint_as_float(t[i]) * inv, __uint_as_float(t[i + 1]) * inv);
             v.y = pack_bf16(__uint_as_float(t[i + 2]) * inv, __uint_as_float(t[i + 3]) * inv);
             v.z = pack_bf16(__uint_as_float(t[i + 4]) * inv, __uint_as_float(t[i + 5]) * inv);
             v.w = pack_bf16(__uint_as_float(t[i + 6]) * inv, __uint_as_float(t[i + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c * 32 + i) = v;
+            *reinterpret_cast<uint4*>(orow + c * 16 + i) = v;
           }
         }
       }
@@ -341,7 +352,16 @@ static int make_bshd_map(CUtensorMap* out, const void* base, int B, int S, int H
   return jpb_make_tensor_map(out, base, 2, 4, dims, strides, box, 1);
 }
 
-template <int D>
+static int fwd_groups() {
+  static int ng = 0;
+  if (ng == 0) {
+    const char* e = getenv("JAXPP_B200_ATTN_FWD_GROUPS");
+    ng = (e && e[0] == '2') ? 2 : 4;
+  }
+  return ng;
+}
+
+template <int D, int NG>
 static int launch_attn_fwd(const void* q, const void* k, const void* v, const AttnParams& p, cudaStream_t stream) {
   using L = AttnSmem<D>;
   CUtensorMap mq, mk, mv;
@@ -351,7 +371,7 @@ static int launch_attn_fwd(const void* q, const void* k, const void* v, const At
   if (rc) return rc;
   rc = make_bshd_map(&mv, v, p.B, p.Sk, p.Hkv, D);
   if (rc) return rc;
-  auto kernel = attention_fwd_kernel<D>;
+  auto kernel = attention_fwd_kernel<D, NG>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
@@ -359,7 +379,7 @@ static int launch_attn_fwd(const void* q, const void* k, const void* v, const At
     configured = true;
   }
   dim3 grid((p.Sq + ATT_BM - 1) / ATT_BM, p.H, p.B);
-  kernel<<<grid, ATT_THREADS, L::TOTAL, stream>>>(mq, mk, mv, p);
+  kernel<<<grid, att_threads(NG), L::TOTAL, stream>>>(mq, mk, mv, p);
   return int(cudaGetLastError());
 }
 
@@ -374,5 +394,6 @@ JPB_API int jpb_attention_fwd(const void* q, const void* k, const void* v, void*
   p.B = B; p.Sq = Sq; p.Sk = Sk; p.H = H; p.Hkv = Hkv; p.causal = causal; p.scale = scale;
   p.o = static_cast<__nv_bfloat16*>(o); p.lse = lse; p.status = jpb_status_device_ptr();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return D == 128 ? launch_attn_fwd<128>(q, k, v, p, s) : launch_attn_fwd<64>(q, k, v, p, s);
+  if (fwd_groups() == 2) return D == 128 ? launch_attn_fwd<128, 2>(q, k, v, p, s) : launch_attn_fwd<64, 2>(q, k, v, p, s);
+  return D == 128 ? launch_attn_fwd<128, 4>(q, k, v, p, s) : launch_attn_fwd<64, 4>(q, k, v, p, s);
 }

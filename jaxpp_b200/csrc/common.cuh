@@ -84,9 +84,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait: returns false if the barrier did not flip within the budget or if another thread of
+// Bounded wait: returns false if the barrier did not flip within TWICE the budget or if another thread of
 // the CTA has already raised `*abort_flag` (shared memory).  On time-out it raises the flag itself and
-// records the reason in the global status word.
+// records the reason in the global status word.  The waits inside a CTA get twice the budget of the waits on a peer
+// GPU: when a peer stays silent, the role that polls the peer's flag gives up first and the status names the peer
+// (JPB_ERR_PEER_TIMEOUT) instead of one of the internal waits that it starved.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                                   int* status, int code = JPB_ERR_WAIT_TIMEOUT) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -96,7 +98,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3ff) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > wait_budget_ns()) {
+      if (globaltimer_ns() - t0 > 2 * wait_budget_ns()) {
         *abort_flag = 1;
         report_status(status, code);
         return false;

@@ -38,25 +38,40 @@ def scenario_fused_tp():
                 ref = torch.ops.b200tp.ag_linear(x_shard, w, bias, "model")
             got = torch.ops.b200tp.ag_linear(x_shard, w, bias, "model")
             close(got, ref, 0.05, f"ag_linear {Ml}x{K}x{N}")
+            # ... and against fp32 math on the gathered operand (not only against the twin, which shares the GEMM)
+            parts = [torch.empty_like(x_shard) for _ in range(n)]
+            dist.all_gather(parts, x_shard)
+            x_all = torch.cat(parts).float()
+            close(got, x_all @ w.float().t() + bias.float(), 0.02 * K ** 0.5 * 0.5 * 0.1 + 0.05, f"ag_linear vs fp32 {Ml}x{K}x{N}")
             # GEMM -> reduce-scatter
             x_full, w_row = rnd(M, K, seed=20 + r + rep), rnd(N, K, seed=30 + r + rep, scale=0.1)
             with config.use_fused_collectives.set(False):
                 ref = torch.ops.b200tp.linear_rs(x_full, w_row, "model")
             got = torch.ops.b200tp.linear_rs(x_full, w_row, "model")
             close(got, ref, 0.08, f"linear_rs {M}x{K}x{N}")
+            total = x_full.float() @ w_row.float().t()          # this rank's partial product in fp32 ...
+            dist.all_reduce(total)                              # ... summed over the ranks
+            close(got, total[r * Ml:(r + 1) * Ml], 0.02 * (n * K) ** 0.5 * 0.5 * 0.1 + 0.08, f"linear_rs vs fp32 {M}x{K}x{N}")
             # backward ops
             dy = rnd(M, N, seed=40 + r + rep)
             with config.use_fused_collectives.set(False):
                 ref_dx = torch.ops.b200tp.dgrad_rs(dy, w, "model")
                 ref_dw = torch.ops.b200tp.ag_wgrad(dy, x_shard, "model", torch.float32)
             close(torch.ops.b200tp.dgrad_rs(dy, w, "model"), ref_dx, 0.08, "dgrad_rs")
-            close(torch.ops.b200tp.ag_wgrad(dy, x_shard, "model", torch.float32), ref_dw, 0.05 * (M ** 0.5) / 8, "ag_wgrad")
+            got_dw = torch.ops.b200tp.ag_wgrad(dy, x_shard, "model", torch.float32)
+            close(got_dw, ref_dw, 0.05 * (M ** 0.5) / 8, "ag_wgrad")
+            dx32 = dy.float() @ w.float()
+            dist.all_reduce(dx32)
+            close(torch.ops.b200tp.dgrad_rs(dy, w, "model"), dx32[r * Ml:(r + 1) * Ml], 0.02 * (n * N) ** 0.5 * 0.5 * 0.1 + 0.08,
+                  "dgrad_rs vs fp32")
+            close(got_dw, dy.float().t() @ x_all, 0.02 * M ** 0.5 * 0.25 + 0.05, "ag_wgrad vs fp32")
             dy_shard = rnd(Ml, N, seed=50 + r + rep)
             with config.use_fused_collectives.set(False):
                 ref_dx2, ref_full = torch.ops.b200tp.ag_dgrad(dy_shard, w, "model")
             got_dx2, got_full = torch.ops.b200tp.ag_dgrad(dy_shard, w, "model")
             close(got_dx2, ref_dx2, 0.08, "ag_dgrad dx")
             assert torch.equal(got_full, ref_full), "ag_dgrad gathered dy"
+            close(got_dx2, got_full.float() @ w.float(), 0.02 * N ** 0.5 * 0.5 * 0.1 + 0.08, "ag_dgrad vs fp32")
         # all-reduce over peer memory (three calls: both buffer parities and a reuse)
         for rep, (numel, dt) in enumerate([(3 * 1024 * 1024 + 5, torch.float32), (2 * 1024 * 1024, torch.bfloat16),
                                            (1024 * 1024 + 3, torch.float32)]):
@@ -418,7 +433,129 @@ def scenario_pp_tp_gpu(pp, tp, schedule_name):
         print(f"pp{pp} x tp{tp} ({schedule_name}): fused collectives match NCCL through two steps", flush=True)
 
 
+def scenario_dp_overlap():
+    """Data-parallel gradient collectives issued from the last microbatch's backward tasks on the side stream (all-reduce,
+    and reduce-scatter with sharded optimizer state) against the same step with the collectives after the loop: the
+    same peer-memory kernels on the same operands, so the new states must be identical bit for bit."""
+    from torch.utils import _pytree as pytree
+
+    from jaxpp_b200.compiler.program import RunTask
+    from jaxpp_b200.models import lm_trainer as lt
+    from jaxpp_b200.models import transformer as tf
+
+    n, r = dist.get_world_size(), dist.get_rank()
+    sched = jp.Std1F1B(1)
+    mesh = jp.MpmdMesh.create({"mpmd": 1, "data": n, "model": 1}, kind="cuda", multi_process=True)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    cfg = tf.ModelConfig("gpt2", vocab=2048, d_model=1024, n_layers=2, n_heads=16, n_kv_heads=16, ffn=4096, seq=128, n_stages=1,
+                         tp=1, dtype=torch.bfloat16)     # weight matrices of 2-8 MiB: above the peer-memory threshold
+    g = torch.Generator().manual_seed(3 + r)
+    tokens = torch.randint(0, 2048, (4, 2, 128), generator=g).to(dev)
+    labels = torch.randint(0, 2048, (4, 2, 128), generator=g).to(dev)
+    is_arr = lambda a: isinstance(a, jp.MpmdArray)
+    for sharded in (False, True):
+        results = {}
+        for overlap in (False, True):
+            with config.overlap_grad_reduce.set(overlap):
+                hyper = lt.Hyper(lr=1e-3, inplace_update=False, shard_optimizer=sharded)
+                state = lt.init_state(cfg, sched, dev, my_rank=0, tp_rank=0, seed=0)
+                if sharded:
+                    state = lt.shard_state_for_dp(cfg, state, n, r)
+                f = jp.mpmd_jit_with_loop(lt.make_train_step(cfg, sched, hyper, dp_axis="data", dp=n), mesh)
+                hooks = sum(len(i.hooks) for i in f.lower(state, tokens, labels).program.instrs if isinstance(i, RunTask))
+                assert (hooks >= 8) == overlap, f"overlap={overlap}: {hooks} gradient collectives hooked into backward tasks"
+                state, losses = f(state, tokens, labels)
+                state, losses2 = f(state, tokens, labels)
+                torch.cuda.synchronize()
+                results[overlap] = (state, losses, losses2)
+        assert native.read_status() == 0, "a peer-memory collective reported a time-out"
+        for a, b in zip(pytree.tree_leaves(results[False], is_leaf=is_arr), pytree.tree_leaves(results[True], is_leaf=is_arr)):
+            assert torch.equal(a.local_tensor(), b.local_tensor()), f"sharded={sharded}: overlapped gradient reduction differs"
+    from jaxpp_b200.parallel import symm
+
+    dist.barrier()
+    assert symm.check_all_canaries()
+    assert any(isinstance(k, tuple) and k and k[-1] == "side" for k in fused._AR_WS), "no collective ran on the side stream"
+    if r == 0:
+        print("gradient collectives overlapped with the backward pass match the after-loop form bit for bit", flush=True)
+
+
+def scenario_vocab_parallel_gpu():
+    """Output projection split by vocabulary rows over two tensor-parallel GPUs (sharded logits, combined log-sum-exps)
+    against the replicated head on the same two GPUs, and the first-step loss against ln(vocab)-scale expectations."""
+    from torch.utils import _pytree as pytree
+
+    from jaxpp_b200.models import lm_trainer as lt
+    from jaxpp_b200.models import transformer as tf
+
+    n = dist.get_world_size()
+    sched = jp.Std1F1B(1)
+    mesh = jp.MpmdMesh.create({"mpmd": 1, "data": 1, "model": n}, kind="cuda", multi_process=True)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    me_tp = mesh.axis_index("model")
+    g = torch.Generator().manual_seed(5)
+    tokens = torch.randint(0, 1024, (2, 2, 128), generator=g).to(dev)
+    labels = torch.randint(0, 1024, (2, 2, 128), generator=g).to(dev)
+    losses = {}
+    params = {}
+    for vp in (False, True):
+        cfg = tf.ModelConfig("llama", vocab=1024, d_model=256, n_layers=2, n_heads=4, n_kv_heads=2, ffn=512, seq=128, n_stages=1,
+                             tp=n, dtype=torch.bfloat16, vocab_parallel=vp)
+        state = lt.init_state(cfg, sched, dev, my_rank=0, tp_rank=me_tp, seed=0)
+        if vp:   # the same matrix as the replicated head: this rank's rows
+            full = params[False]
+            rows = full.shape[0] // n
+            for key in ("params", "master"):
+                state[key]["lm_head"] = full[me_tp * rows:(me_tp + 1) * rows].to(state[key]["lm_head"].dtype).clone()
+        else:
+            params[False] = state["master"]["lm_head"].clone()
+        f = jp.mpmd_jit_with_loop(lt.make_train_step(cfg, sched, lt.Hyper(lr=1e-3, inplace_update=False)), mesh)
+        new_state, l1 = f(state, tokens, labels)
+        torch.cuda.synchronize()
+        t = l1.local_tensor().float()
+        dist.all_reduce(t)
+        losses[vp] = t / n
+        params[("head", vp)] = new_state["master"]["lm_head"].local_tensor()
+    assert native.read_status() == 0
+    torch.testing.assert_close(losses[True], losses[False], rtol=2e-2, atol=2e-2)
+    rows = params[("head", False)].shape[0] // n
+    torch.testing.assert_close(params[("head", True)], params[("head", False)][me_tp * rows:(me_tp + 1) * rows], rtol=0, atol=2.5e-3)
+    if dist.get_rank() == 0:
+        print("vocabulary-parallel head and cross entropy match the replicated head", flush=True)
+
+
+def scenario_ring_attention_zigzag_gpu():
+    """The zigzag sequence layout of ring attention on GPUs (pieces r and 2n-1-r per rank; calls the flash-attention
+    kernels with different query and key lengths) against the single-GPU kernels on the whole sequence."""
+    from jaxpp_b200.ops import core as ops
+    from jaxpp_b200.parallel import context
+
+    n, r = dist.get_world_size(), dist.get_rank()
+    mesh = jp.MpmdMesh.create({"mpmd": 1, "data": n, "model": 1}, kind="cuda", multi_process=True)
+    B, S, H, Hkv, D = 2, 512 * n, 8, 2, 128
+    q, k, v, do = (rnd(B, S, h, D, seed=10 + i) for i, h in enumerate((H, Hkv, Hkv, H)))
+    scale = D ** -0.5
+    with mesh:
+        chunk = lambda t: context.local_sequence_slice(t, "data", 1, "zigzag").contiguous()
+        want, lse = ops.attention(q, k, v, True, scale)
+        dq, dk, dv = ops.attention_bwd(do, q, k, v, want, lse, True, scale)
+        ql, kl, vl = (chunk(t).requires_grad_() for t in (q, k, v))
+        got = context.ring_attention(ql, kl, vl, True, scale, "data", "zigzag")
+        got.backward(chunk(do))
+        torch.cuda.synchronize()
+        close(got.detach(), chunk(want), 2e-2, "zigzag ring attention forward")
+        close(ql.grad, chunk(dq), 3e-2, "zigzag ring attention dq")
+        close(kl.grad, chunk(dk), 3e-2, "zigzag ring attention dk")
+        close(vl.grad, chunk(dv), 3e-2, "zigzag ring attention dv")
+    assert native.read_status() == 0
+    if r == 0:
+        print("zigzag ring attention on GPUs matches the single-GPU kernels", flush=True)
+
+
 SCENARIOS = {
+    "dp_overlap": scenario_dp_overlap,
+    "vocab_parallel": scenario_vocab_parallel_gpu,
+    "ring_attention_zigzag": scenario_ring_attention_zigzag_gpu,
     "fused_tp": scenario_fused_tp,
     "fused_moe": scenario_fused_moe,
     "pp_tied": scenario_pp_tied_gpu,

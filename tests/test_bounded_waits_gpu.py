@@ -51,7 +51,7 @@ def test_mbarrier_wait_runs_out_and_reports(native):
     torch.cuda.synchronize()                       # returns: the kernel did not hang
     timed_out, spent_ns = out.tolist()
     assert timed_out == 1
-    assert BUDGET_MS * 1e6 <= spent_ns < 100 * BUDGET_MS * 1e6
+    assert 2 * BUDGET_MS * 1e6 <= spent_ns < 100 * BUDGET_MS * 1e6   # waits inside a CTA get twice the budget
     assert native.read_status() == 1               # JPB_ERR_WAIT_TIMEOUT
     # the context is healthy: an ordinary kernel runs and is correct
     x = torch.randn(256, 128, device="cuda").bfloat16()

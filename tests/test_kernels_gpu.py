@@ -253,22 +253,27 @@ def test_ops_dispatch_to_native_and_autograd(native):
 
 
 ATTN_CASES = [
-    # B, S, H, Hkv, D, causal
-    (2, 256, 4, 4, 64, True),
-    (1, 512, 4, 2, 128, True),
-    (2, 384, 2, 2, 128, False),
-    (1, 200, 2, 1, 64, True),   # ragged sequence: masks past the end of K and padded query rows
-    (1, 1024, 8, 2, 128, True),
+    # B, Sq, Sk, H, Hkv, D, causal
+    (2, 256, 256, 4, 4, 64, True),
+    (1, 512, 512, 4, 2, 128, True),
+    (2, 384, 384, 2, 2, 128, False),
+    (1, 200, 200, 2, 1, 64, True),   # ragged sequence: masks past the end of K and padded query rows
+    (1, 1024, 1024, 8, 2, 128, True),
+    # different query and key lengths: what ring attention's zigzag layout and any cached-key use call
+    (1, 512, 256, 4, 2, 128, False),   # all queries against half as many keys
+    (2, 256, 512, 4, 4, 64, False),    # half the queries against all keys
+    (1, 256, 640, 4, 2, 128, True),    # causal with an offset: query i sees keys up to i + (Sk - Sq)
+    (1, 200, 328, 2, 2, 64, True),     # the same, ragged
 ]
 
 
-@pytest.mark.parametrize("B,S,H,Hkv,D,causal", ATTN_CASES)
-def test_flash_attention_forward_backward(native, B, S, H, Hkv, D, causal):
+@pytest.mark.parametrize("B,Sq,Sk,H,Hkv,D,causal", ATTN_CASES)
+def test_flash_attention_forward_backward(native, B, Sq, Sk, H, Hkv, D, causal):
     from jaxpp_b200.ops import attention as att
     from jaxpp_b200.ops import core as ops
 
-    q, k, v = rnd(B, S, H, D, seed=1), rnd(B, S, Hkv, D, seed=2), rnd(B, S, Hkv, D, seed=3)
-    do = rnd(B, S, H, D, seed=4)
+    q, k, v = rnd(B, Sq, H, D, seed=1), rnd(B, Sk, Hkv, D, seed=2), rnd(B, Sk, Hkv, D, seed=3)
+    do = rnd(B, Sq, H, D, seed=4)
     scale = D ** -0.5
     o, lse = att.attention_fwd(q, k, v, causal, scale)
     ro, rlse = ops._attn_ref(q.float(), k.float(), v.float(), causal, scale)

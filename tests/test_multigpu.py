@@ -35,6 +35,13 @@ def test_ring_attention_two_gpus():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+@pytest.mark.parametrize("scenario", ["dp_overlap", "vocab_parallel", "ring_attention_zigzag"])
+def test_overlapped_gradient_reduction_vocab_parallel_head_and_zigzag_ring_two_gpus(scenario):
+    rc = launch([WORKER, scenario], 2, env={"NCCL_NVLS_ENABLE": "0"}, timeout_s=300)
+    assert rc == 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
 def test_fused_moe_dispatch_combine_two_gpus():
     rc = launch([WORKER, "fused_moe"], 2, env={"NCCL_NVLS_ENABLE": "0"}, timeout_s=300)
     assert rc == 0
