@@ -39,6 +39,7 @@ class _Consts:
 
 
 _SIMPLE = (int, float, bool, str, type(None))
+_IDENTITY_TARGETS = {torch.ops.aten.detach.default, torch.ops.aten.alias.default}
 
 
 class TaskCode:
@@ -64,8 +65,15 @@ class TaskCode:
             consts = [device if isinstance(c, torch.device) else c for c in self.consts]
             from ..ops import sink as _sink
 
-            targets = [optimes.Timed(t) for t in self.targets] if timed else self.targets
-            scope = {"T": targets, "C": consts, "DEV": device, "WG": _sink.call}
+            from ..ops import core as _ops
+
+            # D: the implementation function of an op where one is known (called without the dispatcher), else the op
+            direct = [_ops.DIRECT.get(t, t) for t in self.targets]
+            targets = self.targets
+            if timed:
+                direct = [optimes.Timed(d, optimes.name_of(t)) for d, t in zip(direct, self.targets)]
+                targets = [optimes.Timed(t) for t in self.targets]
+            scope = {"T": targets, "D": direct, "C": consts, "DEV": device, "WG": _sink.call}
             exec(compile(self.src, f"<task {self.name}>", "exec"), scope)
             fn = scope["run"]
             self._bound[key] = fn
@@ -155,6 +163,9 @@ def generate(name: str, nodes: Sequence[fx.Node], inputs: Sequence[Any], outputs
                 lines.append(f"    {var} = {aref(n.args[0], m)}")
             elif n.target is operator.getitem:
                 lines.append(f"    {var} = {aref(n.args[0], m)}[{aref(n.args[1], m)}]")
+            elif n.target in _IDENTITY_TARGETS:
+                # an alias of its operand: tasks are functional, so the operand itself serves
+                lines.append(f"    {var} = {aref(n.args[0], m)}")
             else:
                 parts = [aref(a, m) for a in n.args]
                 parts += [f"{kw}={aref(v, m)}" for kw, v in n.kwargs.items()]
@@ -163,6 +174,8 @@ def generate(name: str, nodes: Sequence[fx.Node], inputs: Sequence[Any], outputs
                     j = out_index[k][0]
                     sink_outputs.append(j)
                     lines.append(f"    {var} = WG({tref(n.target)}, sink, {j}, {', '.join(parts)})")
+                elif not n.kwargs:
+                    lines.append(f"    {var} = D{tref(n.target)[1:]}({', '.join(parts)})")   # implementation, no dispatcher
                 else:
                     lines.append(f"    {var} = {tref(n.target)}({', '.join(parts)})")
         else:  # pragma: no cover

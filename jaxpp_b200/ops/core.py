@@ -27,6 +27,11 @@ _lib = torch.library.Library("b200", "DEF")
 
 _NATIVE = None
 
+# op overload -> the Python function registered as its implementation.  Generated task code calls these directly
+# instead of going through ``torch.ops`` (the dispatcher costs about 10 us per call of a Python-implemented op, which
+# is the whole budget of a small kernel); eager calls and tracing still use the registered ops.
+DIRECT: dict = {}
+
 
 def _native():
     """The native kernel module; raises if it cannot be loaded (no silent fallback on CUDA)."""
@@ -60,6 +65,7 @@ def _define(schema: str, ref_impl, fake_impl, native_name: str | None = None):
 
     _lib.impl(name, impl, "CompositeExplicitAutograd")
     torch.library.register_fake(qual, fake_impl)
+    DIRECT[getattr(torch.ops.b200, name).default] = impl
     return getattr(torch.ops.b200, name)
 
 
@@ -128,6 +134,7 @@ torch.library.register_fake(
     lambda dy, x, out_dtype=None: dy.new_empty(dy.shape[-1], x.shape[-1], dtype=out_dtype or dy.dtype),
 )
 linear_wgrad = torch.ops.b200.linear_wgrad
+DIRECT[linear_wgrad.default] = _linear_wgrad_native_or_ref
 
 # column sums, used for bias gradients
 colsum = _define(

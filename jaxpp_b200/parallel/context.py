@@ -200,3 +200,13 @@ def local_sequence_slice(x: Tensor, axis: str, dim: int = 1, layout: str = "cont
         return torch.cat([x.narrow(dim, r * s, s), x.narrow(dim, (2 * n - 1 - r) * s, s)], dim=dim)
     s = x.shape[dim] // n
     return x.narrow(dim, r * s, s)
+
+def _register_direct_calls():
+    """Generated task code calls these implementations without the dispatcher (see ops.core.DIRECT)."""
+    from ..ops import core as _core
+
+    _core.DIRECT[torch.ops.b200cp.ring_attention.default] = _fwd_impl
+    _core.DIRECT[torch.ops.b200cp.ring_attention_bwd.default] = _bwd_impl
+
+
+_register_direct_calls()

@@ -302,3 +302,15 @@ def moe_ffn(x: Tensor, p: dict, n_experts: int, top_k: int, capacity_factor: flo
     buf = dispatch(x, dest, n_experts, capacity, top_k)                        # [E, C, d]
     y = expert_ffn(buf, p["w_up"], p["w_down"])
     return combine(y.reshape(n_experts, capacity, d), dest, weights, top_k), aux
+
+def _register_direct_calls():
+    """Generated task code calls these implementations without the dispatcher (see ops.core.DIRECT)."""
+    from ..ops import core as _core
+
+    _core.DIRECT[torch.ops.b200moe.all_to_all.default] = _all_to_all_impl
+    _core.DIRECT[torch.ops.b200moe.dispatch_a2a.default] = _dispatch_a2a_impl
+    _core.DIRECT[torch.ops.b200moe.combine_a2a.default] = _combine_a2a_impl
+    _core.DIRECT[torch.ops.b200moe.router.default] = _router_impl
+
+
+_register_direct_calls()

@@ -193,6 +193,12 @@ torch.library.register_fake(
 )
 
 
+for _name, _fn in (("all_gather", _all_gather_rows), ("reduce_scatter", _reduce_scatter_rows), ("all_reduce", _all_reduce_impl),
+                   ("ag_linear", _ag_linear_impl), ("linear_rs", _linear_rs_impl), ("dgrad_rs", _dgrad_rs_impl),
+                   ("ag_wgrad", _ag_wgrad_impl), ("ag_dgrad", _ag_dgrad_impl)):
+    ops.DIRECT[getattr(torch.ops.b200tp, _name).default] = _fn      # see ops.core.DIRECT
+
+
 def _ag_linear_setup(ctx, inputs, output):
     x, w, bias, axis = inputs
     ctx.save_for_backward(x, w)
@@ -305,6 +311,10 @@ torch.library.register_fake(
 _lib.define("vocab_parallel_ce_bwd(Tensor dloss, Tensor logits, Tensor labels, Tensor lse, str axis) -> Tensor")
 _lib.impl("vocab_parallel_ce_bwd", _vp_ce_bwd_impl, "CompositeExplicitAutograd")
 torch.library.register_fake("b200tp::vocab_parallel_ce_bwd", lambda dloss, logits, labels, lse, axis: torch.empty_like(logits))
+
+
+ops.DIRECT[torch.ops.b200tp.vocab_parallel_ce.default] = _vp_ce_impl
+ops.DIRECT[torch.ops.b200tp.vocab_parallel_ce_bwd.default] = _vp_ce_bwd_impl
 
 
 def _vp_ce_setup(ctx, inputs, output):

@@ -131,3 +131,13 @@ def shard_optimizer_state(state: dict, n: int, r: int, keep=lambda path: False) 
     for key in ("master", "m", "v"):
         out[key] = walk(state[key])
     return out
+
+def _register_direct_calls():
+    """Generated task code calls these implementations without the dispatcher (see ops.core.DIRECT)."""
+    from ..ops import core as _core
+
+    _core.DIRECT[torch.ops.b200dp.reduce_scatter_flat.default] = _reduce_scatter_impl
+    _core.DIRECT[torch.ops.b200dp.all_gather_flat.default] = _all_gather_impl
+
+
+_register_direct_calls()

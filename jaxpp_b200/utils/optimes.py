@@ -30,9 +30,9 @@ def name_of(target) -> str:
 class Timed:
     """Callable stand-in for an op overload that brackets every call with CUDA events."""
 
-    def __init__(self, target):
+    def __init__(self, target, name: str | None = None):
         self.target = target
-        self.name = name_of(target)
+        self.name = name or name_of(target)
 
     def __call__(self, *args, **kwargs):
         if not ACTIVE[0] or not torch.cuda.is_available():
