@@ -48,17 +48,22 @@ def parse():
     ap.add_argument("--timeline", default=None, help="write a per-rank, per-task-kind timeline of one step to this file")
     ap.add_argument("--op-times", default=None,
                     help="write per-op device times of one extra step (CUDA events around every op call) to this file")
+    ap.add_argument("--bf16-grads", action="store_true",
+                    help="accumulate weight gradients in bf16 instead of fp32 (2 bytes per parameter less; for models whose "
+                         "fp32 optimizer state leaves no room)")
+    ap.add_argument("--zb-defer-gb", type=float, default=None,
+                    help="zero-bubble schedules: bytes (GB) of operands that deferred weight-gradient GEMMs may keep alive per "
+                         "(stage, microbatch); the rest of the weight gradients run with the activation gradients")
+    ap.add_argument("--no-grad-overlap", action="store_true",
+                    help="run the data-parallel gradient collectives after the loop instead of from the last backward tasks")
+    ap.add_argument("--smoke-cpu", action="store_true",
+                    help="harness check only: the same script on CPU ranks over gloo with a shrunken model (not a result)")
     ap.add_argument("--p2p", default=None, choices=[None, "torch", "native"], help="point-to-point backend between stages")
     return ap.parse_args()
 
 
 # headline layouts: n_gpus -> named configuration (all the Llama-2-7B shape; 16 sequences of 4096 per GPU)
 HEADLINE = {1: "llama7b_single", 2: "llama7b_tp2", 4: "llama7b_pp2tp2", 8: "llama7b_pp4tp2"}
-
-# Cost model behind --stage-layers auto, in units of one decoder block's forward + backward time: share of a block
-# spent in its attention half, and the extra work of the last stage (final norm, output projection, cross entropy),
-# both from the per-task timeline of the headline step (profiles/step_timeline_n8.txt).
-ATTN_SHARE, HEAD_EXTRA = 0.36, 0.73
 
 
 class ClockSampler:
@@ -144,16 +149,44 @@ def main():
     rc = configs.get(HEADLINE[n] if headline else args.config)
     if rc.n_gpus != n:
         raise SystemExit(f"{rc.name} runs on {rc.n_gpus} GPUs, not {n}")
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-    native.load()
+    cuda = not args.smoke_cpu
+    if cuda:
+        torch.cuda.set_device(local_rank)
+        device = torch.device("cuda", local_rank)
+        if world > 1:
+            dist.init_process_group("nccl", device_id=device)
+        native.load()
+    else:
+        device = torch.device("cpu")
+        if world > 1:
+            dist.init_process_group("gloo")
+
+    class Ev:   # a CUDA event on the current stream, or a wall-clock stamp on CPU ranks
+        def __init__(self):
+            self.e = torch.cuda.Event(enable_timing=True) if cuda else None
+            self.t = 0.0
+
+        def record(self):
+            if cuda:
+                self.e.record()
+            else:
+                self.t = time.perf_counter()
+
+        def elapsed_time(self, other):
+            return self.e.elapsed_time(other.e) if cuda else (other.t - self.t) * 1e3
+
+    def dev_sync():
+        if cuda:
+            torch.cuda.synchronize()
     if args.nccl_only:
         config.use_fused_collectives._override = False
     if args.p2p:
         config.p2p_backend._override = args.p2p
     config.transfer_done_delay._override = 2  # release sent activations two sends later instead of at step end
+    if args.zb_defer_gb is not None:
+        config.zb_defer_bytes._override = int(args.zb_defer_gb * 1e9)
+    if args.no_grad_overlap:
+        config.overlap_grad_reduce._override = False
 
     pp, tp, dp = rc.pp, rc.tp, rc.dp
     n_stages = rc.n_stages
@@ -165,14 +198,21 @@ def main():
     cfg = rc.model_config()
     if args.layers:
         cfg = dataclasses.replace(cfg, n_layers=args.layers)
+    if args.smoke_cpu:
+        over = dict(vocab=256, d_model=64, n_layers=2 * n_stages, n_heads=4, n_kv_heads=2 if cfg.n_kv_heads != cfg.n_heads else 4,
+                    ffn=128, seq=32, dtype=torch.float32)
+        if rc.ep > 1:
+            over.update(n_experts=2 * rc.ep, capacity_factor=4.0)
+        cfg = dataclasses.replace(cfg, **over)
     if args.stage_layers != "equal" and n_stages > 1:
         if args.stage_layers == "auto":
-            sizes = tf.balanced_stage_layers(cfg.n_layers, n_stages, schedule.get_mpmd_idx, pp, last_extra=HEAD_EXTRA,
-                                             attn_share=ATTN_SHARE)
+            attn_share, head_extra = tf.stage_cost_model(cfg)   # from FLOPs; see profiles/step_timeline_n8.txt for the measured split
+            sizes = tf.balanced_stage_layers(cfg.n_layers, n_stages, schedule.get_mpmd_idx, pp, last_extra=head_extra,
+                                             attn_share=attn_share, max_shift=max(1.0, min(3.0, head_extra)))
         else:
             sizes = tuple(float(x) for x in args.stage_layers.split(","))
         cfg = dataclasses.replace(cfg, stage_layers=sizes)
-    mesh = jp.MpmdMesh.create({"mpmd": pp, "data": dp, "model": tp}, kind="cuda", multi_process=world > 1)
+    mesh = jp.MpmdMesh.create({"mpmd": pp, "data": dp, "model": tp}, kind="cuda" if cuda else "cpu", multi_process=world > 1)
     if world > 1:
         for axis, size in (("model", tp), ("data", dp)):
             if size > 1:
@@ -182,7 +222,7 @@ def main():
     dp_rank = mesh.axis_index("data") if world > 1 and dp > 1 else 0
 
     sharded_opt = args.shard_optimizer and dp > 1
-    hyper = lt.Hyper(shard_optimizer=sharded_opt)
+    hyper = lt.Hyper(shard_optimizer=sharded_opt, fp32_wgrad=not args.bf16_grads)
     step_fn = lt.make_train_step(cfg, schedule, hyper, dp_axis="data" if dp > 1 else None, dp=dp)
     jitted = jp.mpmd_jit_with_loop(step_fn, mesh, name=f"{rc.name}_train_step")
     # expert weights differ between the ranks of the expert axis; everything else is replicated over the data axis
@@ -191,7 +231,9 @@ def main():
         state = lt.shard_state_for_dp(cfg, state, dp, dp_rank)
 
     g = torch.Generator().manual_seed(1234 + dp_rank)
-    host_tokens = [torch.randint(0, cfg.vocab, (n_mb, mb_local, cfg.seq + 1), generator=g).pin_memory() for _ in range(2)]
+    host_tokens = [torch.randint(0, cfg.vocab, (n_mb, mb_local, cfg.seq + 1), generator=g) for _ in range(2)]
+    if cuda:
+        host_tokens = [t.pin_memory() for t in host_tokens]
     tokens_per_step = seqs * cfg.seq
     h2d_bytes = n_mb * mb_local * (cfg.seq + 1) * 8
 
@@ -200,10 +242,10 @@ def main():
         return t[:, :, :-1].contiguous(), t[:, :, 1:].contiguous()
 
     def sync_all():
-        torch.cuda.synchronize()
+        dev_sync()
         if world > 1:
             dist.barrier()
-            torch.cuda.synchronize()
+            dev_sync()
 
     def read_loss(losses):
         t = losses.local_tensor()
@@ -225,14 +267,15 @@ def main():
         if i == 0:
             first_loss = loss_val
     sync_all()
-    torch.cuda.reset_peak_memory_stats()
+    if cuda:
+        torch.cuda.reset_peak_memory_stats()
 
     # ---- device-timed region: K steps, inputs resident -------------------------------------------------------
     sampler = ClockSampler(local_rank)
-    if rank == 0:
+    if rank == 0 and cuda:
         sampler.start()
     native.LAUNCHES[0] = 0
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0, e1 = Ev(), Ev()
     sync_all()
     e0.record()
     for i in range(args.steps):
@@ -242,7 +285,7 @@ def main():
     ms = e0.elapsed_time(e1) / args.steps
     launches = native.LAUNCHES[0]
     clocks = sampler.stop() if rank == 0 else None
-    status = native.read_status()
+    status = native.read_status() if cuda else 0
 
     # ---- end-to-end region: H2D of the step's tokens + D2H of its loss, every step ----------------------------------
     sync_all()
@@ -254,23 +297,23 @@ def main():
         loss_val = lv if lv is not None else loss_val
     sync_all()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
-    peak_mem = torch.cuda.max_memory_allocated() / 1e9
+    peak_mem = torch.cuda.max_memory_allocated() / 1e9 if cuda else 0.0
 
     # ---- bubble and timeline: one extra step with per-task CUDA events ---------------------------------------------------
     compiled = jitted.lower(state, tok, lab)
     leaves, *_ = jitted._prepare((state, tok, lab), {})
     sync_all()
-    b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    b0, b1 = Ev(), Ev()
     b0.record()
     out = compiled(leaves, record_events=True)
     b1.record()
-    torch.cuda.synchronize()
+    dev_sync()
     step_ms_b = b0.elapsed_time(b1)
     busy = compiled.last_states[0].busy_ms() if world > 1 else sum(s.busy_ms() for s in compiled.last_states)
-    bubble = max(0.0, 1.0 - busy / step_ms_b)
-    if args.timeline:
+    bubble = max(0.0, 1.0 - busy / step_ms_b) if cuda else 0.0
+    if args.timeline and cuda:
         text = "\n".join(timeline.format_summary(
-            f"process {rank} (pipeline rank {st.rank}, tp {tp_rank}, dp {dp_rank})", timeline.summarise_events(st.events, b0, b1))
+            f"process {rank} (pipeline rank {st.rank}, tp {tp_rank}, dp {dp_rank})", timeline.summarise_events(st.events, b0.e, b1.e))
             for st in compiled.last_states)
         texts = [text]
         if world > 1:
@@ -283,7 +326,7 @@ def main():
                         "'idle before' = compute stream idle in front of a task (waiting for another rank)\n")
                 f.write("\n\n".join(texts) + "\n")
 
-    if args.op_times:
+    if args.op_times and cuda:
         from jaxpp_b200.utils import optimes
 
         sync_all()
@@ -307,7 +350,10 @@ def main():
                         f"task, under the conditions of the timed run (uninstrumented step: {ms:.1f} ms)\n")
                 f.write("\n\n".join(texts) + "\n")
 
-    canaries_ok = symm.check_all_canaries()
+    canary_lines = symm.canary_reports() if cuda else []
+    canaries_ok = not canary_lines
+    if canary_lines:
+        print(f"[rank {rank}] " + " | ".join(canary_lines), file=sys.stderr, flush=True)
     fallbacks = fused.FALLBACKS[0]
     loss_val, first_loss = mean_over_ranks(loss_val), mean_over_ranks(first_loss)
     bubbles, peaks = [bubble], [peak_mem]
@@ -347,7 +393,10 @@ def main():
                        "parallelism": par + (f" v={vstages}" if vstages > 1 else ""),
                        "schedule": type(schedule).__name__, "stage_layers": list(cfg.stage_sizes),
                        "recompute": bool(cfg.recompute),
-                       "optimizer": "AdamW fp32 master, fused kernel" + (", state sharded over dp" if sharded_opt else ""),
+                       "optimizer": "AdamW fp32 master, fused kernel" + (", state sharded over dp" if sharded_opt else "")
+                                    + (", bf16 gradient accumulators" if args.bf16_grads else ", fp32 gradient accumulators"),
+                       "grad_reduce_overlap": bool(config.overlap_grad_reduce.value) and dp > 1,
+                       "zb_defer_bytes": int(config.zb_defer_bytes.value),
                        "l2": "inputs exceed L2 (weights and activations are GBs per step)",
                        "fused_collectives": bool(config.use_fused_collectives.value) and (tp > 1 or dp > 1),
                        "p2p": config.p2p_backend.value},

@@ -150,6 +150,22 @@ class ModelConfig:
         return matmul + attn
 
 
+def stage_cost_model(cfg: "ModelConfig") -> tuple:
+    """``(attn_share, head_extra)`` for :func:`balanced_stage_layers`, from training FLOPs per token: the share of a
+    block's time spent in its attention half, and the cost of the output stage's extra work (final norm, output
+    projection, cross entropy) in blocks.  Attention-kernel FLOPs count twice (the flash-attention kernels run at about
+    half the rate of the GEMMs, per the per-op timings of a step) and the output projection gets 12 % on top for the
+    cross entropy's passes over the logits."""
+    d, hd = cfg.d_model, cfg.head_dim
+    attn_w = d * (cfg.n_heads + 2 * cfg.n_kv_heads) * hd + cfg.n_heads * hd * d
+    mlp_w = (3 if cfg.family in ("llama", "mixtral") else 2) * d * cfg.ffn * (cfg.top_k if cfg.n_experts else 1)
+    attn_kernels = 2.0 * 3.5 * 4.0 * cfg.seq * cfg.n_heads * hd * (0.5 if cfg.causal else 1.0)
+    attn_half = 6.0 * attn_w + attn_kernels
+    block = attn_half + 6.0 * mlp_w
+    head = 6.0 * cfg.padded_vocab * d * 1.12 if cfg.family != "encoder" else 0.0
+    return attn_half / block, head / block
+
+
 def rank_loads(sizes, stage_to_rank, n_ranks: int, attn_share: float, first_extra: float, last_extra: float) -> list:
     """Work per pipeline rank, in blocks, of stages of ``sizes`` blocks (entries may end in .5) placed by
     ``stage_to_rank``.  The attention half of a block costs ``attn_share`` of a block; the first stage carries

@@ -69,13 +69,27 @@ class SymmetricBuffer:
         dist.barrier(group=group)
         SymmetricBuffer.LIVE.append(self)
 
-    def check_canaries(self) -> bool:
-        """True iff both guard bands of the local copy still hold the pattern (synchronises the current stream)."""
+    def _guards(self) -> torch.Tensor:
         host = torch.empty(2 * self.GUARD, dtype=torch.uint8, device="cuda")
         stream = native._stream()
         self.lib.jpb_memcpy_async(host.data_ptr(), self.local_base, self.GUARD, stream)
         self.lib.jpb_memcpy_async(host.data_ptr() + self.GUARD, self.local_base + self.GUARD + self.nbytes, self.GUARD, stream)
-        return bool((host.cpu() == self.PATTERN).all())
+        return host.cpu()
+
+    def check_canaries(self) -> bool:
+        """True iff both guard bands of the local copy still hold the pattern (synchronises the current stream)."""
+        return bool((self._guards() == self.PATTERN).all())
+
+    def canary_report(self) -> str | None:
+        """None if the guard bands are intact, else which band was overwritten, where and with what."""
+        g = self._guards()
+        bad = (g != self.PATTERN).nonzero().flatten().tolist()
+        if not bad:
+            return None
+        side = lambda i: f"front band byte {i}" if i < self.GUARD else f"back band byte {i - self.GUARD}"
+        vals = [int(g[i]) for i in bad[:8]]
+        return (f"symmetric buffer of {self.nbytes} bytes ({self.n} ranks, rank {self.rank}): {len(bad)} guard bytes "
+                f"overwritten, first at {side(bad[0])}, last at {side(bad[-1])}, values {vals}")
 
     def close(self):
         for q, b in enumerate(self.bases):
@@ -93,6 +107,17 @@ def check_all_canaries() -> bool:
     all-reduce / reduce-scatter / all-gather workspaces and the expert-parallel ones (every :class:`SymmetricBuffer`
     registers itself; closed and released buffers drop out)."""
     return all(buf.check_canaries() for buf in list(SymmetricBuffer.LIVE) if buf.local_base)
+
+
+def canary_reports() -> list:
+    """One line per symmetric buffer of this process whose guard bands were overwritten."""
+    out = []
+    for buf in list(SymmetricBuffer.LIVE):
+        if buf.local_base:
+            r = buf.canary_report()
+            if r:
+                out.append(r)
+    return out
 
 
 def reserved_sms(mesh=None) -> int:
