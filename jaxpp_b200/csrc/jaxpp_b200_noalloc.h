@@ -17,6 +17,13 @@
  *     without an ordering between them) race.  Calls on one stream are safe.  Nothing in the array needs to
  *     start at zero: every partial row that is read has been written earlier in the same call.
  *   - Calls no cudaMalloc / cudaFree / allocating library routine.
+ *   - Speed: the partial sums come from at most JPB_NOALLOC_MAX_PARTS (148) CTAs, one per SM, so that the array stays
+ *     small; jpb_norm_bwd() with a caller-provided buffer launches twice as many and is the faster of the two.
+ *   - Threads: the first call on a device stores the array's address in a per-device slot without a lock.  Two host
+ *     threads that make that first call at the same time both look the address up and store the same value, which is
+ *     harmless; there is nothing else shared on the host side.
+ *   - A positive return value is what cudaGetLastError() reports after the launches; like every use of that call it
+ *     can also surface an error that an earlier, unrelated launch left pending in the context.
  */
 #ifndef JAXPP_B200_NOALLOC_H
 #define JAXPP_B200_NOALLOC_H

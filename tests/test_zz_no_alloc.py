@@ -31,7 +31,9 @@ def test_noalloc_matches_regular_entry_point_twice(dtype):
     lib, native = _lib()
     tol = dict(rtol=1e-4, atol=1e-4) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
     stream = torch.cuda.current_stream().cuda_stream
-    for call, (rows, H) in enumerate([(300, 4096), (37, 1024)]):  # second call reuses the array with another shape
+    # the second call reuses the array with another shape; the third repeats the second: by then every kernel it
+    # launches has been loaded, so the driver's own count of free device memory must not move either
+    for call, (rows, H) in enumerate([(300, 4096), (37, 1024), (37, 1024)]):
         g = torch.Generator(device="cuda").manual_seed(100 + call)
         x = torch.randn(rows, H, generator=g, device="cuda").to(dtype)
         dy = torch.randn(rows, H, generator=g, device="cuda").to(dtype)
@@ -40,11 +42,15 @@ def test_noalloc_matches_regular_entry_point_twice(dtype):
         ref_dx, ref_dw = native.rmsnorm_bwd(dy, x, w, rstd)
         dx, dw = torch.empty_like(x), torch.empty_like(w)
         before = torch.cuda.memory_allocated()
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = lib.jpb_rmsnorm_bwd_noalloc(0 if dtype == torch.float32 else 1, dy.data_ptr(), x.data_ptr(), w.data_ptr(),
                                          rstd.data_ptr(), dx.data_ptr(), dw.data_ptr(), rows, H, stream)
         assert rc == 0, lib.jpb_noalloc_strerror(rc).decode()
-        assert torch.cuda.memory_allocated() == before  # nothing went through the allocator
+        assert torch.cuda.memory_allocated() == before  # nothing went through torch's allocator ...
         torch.cuda.synchronize()
+        if call == 2:                                   # ... and nothing past it (a raw cudaMalloc would show here)
+            assert torch.cuda.mem_get_info()[0] >= free_before
         torch.testing.assert_close(dx.float(), ref_dx.float(), **tol)
         torch.testing.assert_close(dw.float(), ref_dw.float(), rtol=tol["rtol"], atol=tol["atol"] * rows ** 0.5)
 
