@@ -183,8 +183,10 @@ def main():
     if args.p2p:
         config.p2p_backend._override = args.p2p
     config.transfer_done_delay._override = 2  # release sent activations two sends later instead of at step end
-    if args.zb_defer_gb is not None:
-        config.zb_defer_bytes._override = int(args.zb_defer_gb * 1e9)
+    zb_defer_gb = args.zb_defer_gb if args.zb_defer_gb is not None else rc.zb_defer_gb   # the configuration's own bound
+    if zb_defer_gb is not None:
+        config.zb_defer_bytes._override = int(zb_defer_gb * 1e9)
+    bf16_grads = args.bf16_grads or rc.grad_bytes == 2
     if args.no_grad_overlap:
         config.overlap_grad_reduce._override = False
 
@@ -222,7 +224,7 @@ def main():
     dp_rank = mesh.axis_index("data") if world > 1 and dp > 1 else 0
 
     sharded_opt = args.shard_optimizer and dp > 1
-    hyper = lt.Hyper(shard_optimizer=sharded_opt, fp32_wgrad=not args.bf16_grads)
+    hyper = lt.Hyper(shard_optimizer=sharded_opt, fp32_wgrad=not bf16_grads)
     step_fn = lt.make_train_step(cfg, schedule, hyper, dp_axis="data" if dp > 1 else None, dp=dp)
     jitted = jp.mpmd_jit_with_loop(step_fn, mesh, name=f"{rc.name}_train_step")
     # expert weights differ between the ranks of the expert axis; everything else is replicated over the data axis
@@ -394,7 +396,7 @@ def main():
                        "schedule": type(schedule).__name__, "stage_layers": list(cfg.stage_sizes),
                        "recompute": bool(cfg.recompute),
                        "optimizer": "AdamW fp32 master, fused kernel" + (", state sharded over dp" if sharded_opt else "")
-                                    + (", bf16 gradient accumulators" if args.bf16_grads else ", fp32 gradient accumulators"),
+                                    + (", bf16 gradient accumulators" if bf16_grads else ", fp32 gradient accumulators"),
                        "grad_reduce_overlap": bool(config.overlap_grad_reduce.value) and dp > 1,
                        "zb_defer_bytes": int(config.zb_defer_bytes.value),
                        "l2": "inputs exceed L2 (weights and activations are GBs per step)",

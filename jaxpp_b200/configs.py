@@ -28,6 +28,11 @@ class RunConfig:
     ep: int = 1            # expert parallel size (uses the data axis)
     recompute: bool = False
     description: str = ""
+    # what the configuration needs to fit 180 GB (see memory_plan): bytes per parameter of the gradient accumulators
+    # (4 = fp32, 2 = bf16) and, for schedules that split the backward, the bound on the operands that deferred
+    # weight-gradient GEMMs keep alive per (stage, microbatch), in GB (None = no bound)
+    grad_bytes: int = 4
+    zb_defer_gb: float | None = None
 
     @property
     def n_gpus(self) -> int:
@@ -66,11 +71,14 @@ CONFIGS: dict[str, RunConfig] = {c.name: c for c in [
     RunConfig("llama7b_pp2tp2", tf.llama2_7b, 2, 1, 2, 4, _inter, 64, 4, description="4-GPU slice of the headline layout"),
     RunConfig("llama7b_tp2", tf.llama2_7b, 1, 1, 2, 1, _std, 32, 4, description="2-GPU slice of the headline layout"),
     RunConfig("llama7b_single", tf.llama2_7b, 1, 1, 1, 1, _std, 16, 1, description="one GPU, 16 microbatches of 1"),
-    RunConfig("mixtral8x7b_pp2ep4", tf.mixtral_8x7b, 2, 4, 1, 4, _dpv, 64, 8, ep=4, recompute=True,
+    RunConfig("mixtral8x7b_pp2ep4", tf.mixtral_8x7b, 2, 4, 1, 4, _dpv, 64, 8, ep=4, recompute=True, zb_defer_gb=8.0,
               description="Mixtral-8x7B shape, PP2 x EP4 (experts over the data axis), DualPipeV, microbatches of 2 per replica; "
                           "blocks recomputed in backward: without it the memory plan exceeds 180 GB per GPU"),
-    RunConfig("llama70b_pp4tp2", tf.llama2_70b, 4, 1, 2, 4, _zb, 64, 1, recompute=True,
-              description="Llama-2-70B shape, PP4 x TP2, ZeroBubble, 64 microbatches of 1, full activation recompute"),
+    RunConfig("llama70b_pp4tp2", tf.llama2_70b, 4, 1, 2, 4, _zb, 64, 1, recompute=True, grad_bytes=2, zb_defer_gb=2.0,
+              description="Llama-2-70B shape, PP4 x TP2, ZeroBubble, 64 microbatches of 1, full activation recompute; 8.8 B "
+                          "parameters per GPU leave no room for fp32 gradient accumulators (bf16 ones) nor for the operands of "
+                          "every deferred weight gradient (at most 2 GB per task stay alive, the rest run with the activation "
+                          "gradients)"),
 ]}
 
 
@@ -110,11 +118,43 @@ def peak_live_microbatches(schedule: jp.BaseSchedule, n_microbatches: int) -> li
     return peaks
 
 
-def memory_plan(rc: RunConfig, shard_optimizer: bool = False) -> dict:
+def peak_deferred_weight_gradients(schedule: jp.BaseSchedule, n_microbatches: int) -> list[int]:
+    """Per pipeline rank of a split-backward schedule: the largest number of (stage, microbatch) activation-gradient
+    tasks whose weight-gradient task has not run yet, in the rank's task order.  The operands of the deferred
+    weight-gradient GEMMs (activation gradients and, with recompute, the recomputed inputs of every linear) stay alive
+    for each of them.  The first stage's backward is never split and does not count."""
+    from .schedules import FusedTask
+    from .types import TaskType
+
+    out = []
+    for row in schedule.tasks(n_microbatches):
+        pending: set = set()
+        peak = 0
+        for unit in row:
+            if unit is None:
+                continue
+            for t in (unit if isinstance(unit, FusedTask) else (unit,)):
+                if t.fwd_or_bwd is TaskType.BWD_I and t.stage_id != 0:
+                    pending.add((t.stage_id, t.mubatch_idx))
+                    peak = max(peak, len(pending))
+                elif t.fwd_or_bwd is TaskType.BWD_W:
+                    pending.discard((t.stage_id, t.mubatch_idx))
+        out.append(peak)
+    return out
+
+
+def memory_plan(rc: RunConfig, shard_optimizer: bool = False, grad_bytes: int | None = None,
+                zb_defer_bytes: float | None = -1.0) -> dict:
     """Estimated bytes per GPU of the busiest pipeline rank: bf16 parameters, fp32 master weights and Adam moments
-    (1/dp of them with ``shard_optimizer``), fp32 gradient accumulators, and the activations that the schedule keeps
-    alive (per block: what the backward of the fused kernels needs; with recompute only the block inputs plus one
-    block's working set).  An estimate for sizing, not an allocator trace."""
+    (1/dp of them with ``shard_optimizer``), gradient accumulators (``grad_bytes`` per parameter: 4, or 2 with bf16
+    accumulation), the activations that the schedule keeps alive (per block: what the backward of the fused kernels
+    needs; with recompute only the block inputs plus one block's working set) and, for schedules that split the
+    backward, the operands that deferred weight-gradient GEMMs hold between the two halves (bounded per (stage,
+    microbatch) by ``zb_defer_bytes`` when given, see ``JAXPP_B200_ZB_DEFER_BYTES``).  An estimate for sizing, not an
+    allocator trace."""
+    grad_bytes = rc.grad_bytes if grad_bytes is None else grad_bytes
+    if zb_defer_bytes is not None and zb_defer_bytes < 0:      # default: the configuration's own bound
+        zb_defer_bytes = None if rc.zb_defer_gb is None else rc.zb_defer_gb * 1e9
     cfg = rc.model_config()
     d, f, hd = cfg.d_model, cfg.ffn, cfg.head_dim
     tp, ep = rc.tp, max(1, rc.ep)
@@ -133,7 +173,7 @@ def memory_plan(rc: RunConfig, shard_optimizer: bool = False) -> dict:
         # only replicas over the data axis are sliced; experts sharded over that axis stay whole on their owner
         experts = layers_per_rank * 3 * d * f * cfg.n_experts / ep if cfg.n_experts else 0.0
         optimizer = 12 * (experts + (params - experts) / rc.dp)
-    grads = 4 * params
+    grads = grad_bytes * params
     # activations of one block for one microbatch, bytes per local token (bf16 unless noted)
     tokens = (rc.microbatch // rc.dp) * cfg.seq
     heads_local = (cfg.n_heads + 2 * cfg.n_kv_heads) * hd / tp
@@ -154,10 +194,23 @@ def memory_plan(rc: RunConfig, shard_optimizer: bool = False) -> dict:
     else:
         acts = tokens * live * layers_per_stage * block
     logits = tokens / tp * cfg.padded_vocab * (2 + 4)                       # bf16 logits + fp32 gradient of one microbatch
-    total = weights + optimizer + grads + acts + logits
+    # operands of the weight-gradient GEMMs of one block for one microbatch (bf16): (dy, x) of the four linears, in
+    # the forms the tensor-parallel ops keep them (sequence-sharded inputs of the column-parallel ones)
+    sched = rc.make_schedule()
+    deferred = 0.0
+    if sched.is_partial_bwd:
+        wgrad_block = 2 * tokens * (heads_local + d / tp            # qkv: dy [T, heads_local], x shard
+                                    + d + cfg.n_heads * hd / tp     # wo: gathered dy [T, d], x [T, heads/tp]
+                                    + (2 if cfg.family in ("llama", "mixtral") else 1) * ffn_local + d / tp   # up
+                                    + d + ffn_local)                # down
+        per_task = wgrad_block * layers_per_stage
+        if zb_defer_bytes is not None and zb_defer_bytes >= 0:
+            per_task = min(per_task, zb_defer_bytes)
+        deferred = per_task * max(peak_deferred_weight_gradients(sched, rc.n_microbatches))
+    total = weights + optimizer + grads + acts + logits + deferred
     return {"config": rc.name, "params_per_gpu": params, "weights": weights, "optimizer": optimizer, "grads": grads,
-            "activations": acts, "logits": logits, "live_stage_microbatches": live, "total": total,
-            "fits": total < 0.92 * HBM_BYTES}
+            "activations": acts, "logits": logits, "deferred_wgrad_operands": deferred, "live_stage_microbatches": live,
+            "total": total, "fits": total < 0.92 * HBM_BYTES}
 
 
 def _main():
@@ -165,15 +218,18 @@ def _main():
 
     ap = argparse.ArgumentParser(description="per-GPU memory estimate of every named configuration")
     ap.add_argument("--shard-optimizer", action="store_true")
+    ap.add_argument("--bf16-grads", action="store_true", help="2-byte gradient accumulators")
+    ap.add_argument("--zb-defer-gb", type=float, default=None, help="bound on deferred weight-gradient operands per task")
     args = ap.parse_args()
     gb = lambda x: f"{x / 1e9:7.1f}"
-    print(f"{'configuration':<22}{'params/GPU':>11}{'weights':>9}{'optim':>8}{'grads':>8}{'acts':>8}{'logits':>8}{'total GB':>10}  fits 180 GB")
+    print(f"{'configuration':<22}{'params/GPU':>11}{'weights':>9}{'optim':>8}{'grads':>8}{'acts':>8}{'logits':>8}{'deferred':>9}{'total GB':>10}  fits 180 GB")
     for rc in CONFIGS.values():
         if rc.name.startswith("encoder"):
             continue
-        m = memory_plan(rc, args.shard_optimizer)
+        m = memory_plan(rc, args.shard_optimizer, 2 if args.bf16_grads else None,
+                        -1.0 if args.zb_defer_gb is None else args.zb_defer_gb * 1e9)
         print(f"{rc.name:<22}{m['params_per_gpu'] / 1e9:>10.2f}B{gb(m['weights']):>9}{gb(m['optimizer']):>8}{gb(m['grads']):>8}"
-              f"{gb(m['activations']):>8}{gb(m['logits']):>8}{gb(m['total']):>10}  {'yes' if m['fits'] else 'NO'}")
+              f"{gb(m['activations']):>8}{gb(m['logits']):>8}{gb(m['deferred_wgrad_operands']):>9}{gb(m['total']):>10}  {'yes' if m['fits'] else 'NO'}")
 
 
 if __name__ == "__main__":

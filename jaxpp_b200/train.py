@@ -70,7 +70,12 @@ def main(argv=None):
         tp_rank = mesh.axis_index("model") if multi and rc.tp > 1 else 0
         dp_rank = mesh.axis_index("data") if multi and rc.dp > 1 else 0
         sharded_opt = args.shard_optimizer and multi and rc.dp > 1
-        hyper = lt.Hyper(lr=args.lr, inplace_update=True, shard_optimizer=sharded_opt, clip_grad_norm=args.clip_grad_norm)
+        from jaxpp_b200.utils import config as flags
+
+        if rc.zb_defer_gb is not None and flags.zb_defer_bytes.value < 0:   # the configuration's own memory bound
+            flags.zb_defer_bytes._override = int(rc.zb_defer_gb * 1e9)
+        hyper = lt.Hyper(lr=args.lr, inplace_update=True, shard_optimizer=sharded_opt, clip_grad_norm=args.clip_grad_norm,
+                         fp32_wgrad=rc.grad_bytes == 4)
         step_fn = lt.make_train_step(cfg, sched, hyper, dp_axis="data" if rc.dp > 1 else None, dp=rc.dp)
         state = lt.init_state(cfg, sched, device, my_rank=my_pp, tp_rank=tp_rank + 1000 * dp_rank * (rc.ep > 1), seed=args.seed)
         if sharded_opt:

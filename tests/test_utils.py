@@ -243,7 +243,15 @@ def test_memory_plan_of_the_benchmark_configurations():
             continue
         plan = configs.memory_plan(rc)
         assert plan["fits"], (name, plan["total"] / 1e9)
-        assert abs(plan["total"] - sum(plan[k] for k in ("weights", "optimizer", "grads", "activations", "logits"))) < 1
+        parts = ("weights", "optimizer", "grads", "activations", "logits", "deferred_wgrad_operands")
+        assert abs(plan["total"] - sum(plan[k] for k in parts)) < 1
+    # zero-bubble with full recompute: every outstanding activation-gradient task holds the operands of its deferred
+    # weight-gradient GEMMs; without the configuration's bounds (bf16 accumulators, 2 GB per task) 70B does not fit
+    big = configs.get("llama70b_pp4tp2")
+    assert configs.peak_deferred_weight_gradients(jp.ZeroBubble(4), 64) == [0, 2, 3, 4]
+    loose = configs.memory_plan(big, grad_bytes=4, zb_defer_bytes=None)
+    assert not loose["fits"] and loose["deferred_wgrad_operands"] > 40e9
+    assert configs.memory_plan(big)["deferred_wgrad_operands"] == pytest.approx(4 * 2e9)
     mix = configs.get("mixtral8x7b_pp2ep4")
     assert not configs.memory_plan(dataclasses.replace(mix, recompute=False))["fits"]   # why that configuration recomputes
     gpt = configs.get("gpt2xl_pp2dp4")
