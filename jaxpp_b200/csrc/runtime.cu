@@ -118,11 +118,14 @@ JPB_API const char* jpb_build_info() { return "jaxpp_b200 native kernels, sm_100
 // ---- symmetric (peer-mapped) device memory through CUDA IPC ---------------------------------------------------
 // Every rank allocates the same number of bytes, publishes the 64-byte handle, and opens its peers' handles;
 // the kernels then address peers' buffers with plain pointers over NVLink.
-JPB_API int jpb_ipc_alloc(long long bytes, void** ptr, unsigned char* handle_out /* 64 bytes */) {
+// The buffer is zero-filled on `stream`: whatever the caller does to it next (guard-band patterns, staging copies,
+// kernels) must be ordered after that fill, which holds for work on the same stream.  (A fill on the default stream
+// is not ordered with a non-blocking stream: a later, smaller fill issued there could run first and be wiped out.)
+JPB_API int jpb_ipc_alloc2(long long bytes, void** ptr, unsigned char* handle_out /* 64 bytes */, void* stream) {
   void* p = nullptr;
   cudaError_t e = cudaMalloc(&p, size_t(bytes));
   if (e != cudaSuccess) return int(e);
-  e = cudaMemset(p, 0, size_t(bytes));
+  e = cudaMemsetAsync(p, 0, size_t(bytes), static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return int(e);
   cudaIpcMemHandle_t h;
   e = cudaIpcGetMemHandle(&h, p);
@@ -131,6 +134,9 @@ JPB_API int jpb_ipc_alloc(long long bytes, void** ptr, unsigned char* handle_out
   memcpy(handle_out, &h, 64);
   *ptr = p;
   return 0;
+}
+JPB_API int jpb_ipc_alloc(long long bytes, void** ptr, unsigned char* handle_out) {
+  return jpb_ipc_alloc2(bytes, ptr, handle_out, nullptr);
 }
 
 JPB_API int jpb_ipc_open(const unsigned char* handle, void** ptr) {

@@ -32,7 +32,7 @@ class SymmetricBuffer:
 
     def __init__(self, nbytes: int, group, group_ranks: list[int]):
         lib = native.load()
-        lib.jpb_ipc_alloc.argtypes = [ctypes.c_longlong, ctypes.POINTER(ctypes.c_void_p), ctypes.c_char_p]
+        lib.jpb_ipc_alloc2.argtypes = [ctypes.c_longlong, ctypes.POINTER(ctypes.c_void_p), ctypes.c_char_p, ctypes.c_void_p]
         lib.jpb_ipc_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]
         lib.jpb_ipc_close.argtypes = [ctypes.c_void_p]
         lib.jpb_ipc_free.argtypes = [ctypes.c_void_p]
@@ -45,9 +45,10 @@ class SymmetricBuffer:
         self.rank = group_ranks.index(dist.get_rank())
         ptr = ctypes.c_void_p()
         handle = ctypes.create_string_buffer(64)
-        native._check(lib.jpb_ipc_alloc(nbytes + 2 * self.GUARD, ctypes.byref(ptr), handle), "jpb_ipc_alloc", 0)  # zero-filled
-        self.local_base = ptr.value
+        # zero-filled on the current stream, the stream of the guard fills below and of the caller's first use
         stream = native._stream()
+        native._check(lib.jpb_ipc_alloc2(nbytes + 2 * self.GUARD, ctypes.byref(ptr), handle, stream), "jpb_ipc_alloc", 0)
+        self.local_base = ptr.value
         native._check(lib.jpb_memset_async(self.local_base, self.PATTERN, self.GUARD, stream), "guard", 0)
         native._check(lib.jpb_memset_async(self.local_base + self.GUARD + nbytes, self.PATTERN, self.GUARD, stream), "guard", 0)
         handles: list[Any] = [None] * self.n

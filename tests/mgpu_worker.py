@@ -271,7 +271,8 @@ def scenario_zero_gpu():
             want = want * 0.25
             got = fused.reduce_scatter_flat(x, "data", 0.25)
             assert got.shape == (s,) and got.dtype == dtype
-            tol = 0 if dtype == torch.float32 else 2e-2
+            # fp32: exact with two ranks; with more the order of the additions differs from NCCL's by an ulp
+            tol = (0 if n == 2 else 1e-6) if dtype == torch.float32 else 2e-2
             torch.testing.assert_close(got.float(), want[r * s:(r + 1) * s], rtol=tol, atol=tol)
             # the op picks the same kernel
             torch.testing.assert_close(zero.reduce_scatter_flat(x, "data", 0.25), got, rtol=0, atol=0)
