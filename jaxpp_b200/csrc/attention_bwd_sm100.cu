@@ -31,6 +31,17 @@ __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[W]) {
   else tmem_ld_32x16(taddr, r);
 }
 
+// W consecutive bf16 values of row `lane` -> W / 2 packed 32-bit columns of TMEM (the layout of an A operand that
+// tcgen05.mma reads from tensor memory: element k of the row in column k / 2, even k in the low half)
+template <int W>
+__device__ __forceinline__ void tmem_st_packed(uint32_t taddr, const float (&v)[W]) {
+  uint32_t w[W / 2];
+#pragma unroll
+  for (int i = 0; i < W / 2; ++i) w[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
+  if constexpr (W == 32) tmem_st_32x16(taddr, w);
+  else tmem_st_32x8(taddr, w);
+}
+
 struct AttnBwdParams {
   int B, Sq, Sk, H, Hkv;
   int causal;
@@ -123,7 +134,9 @@ struct DkvTiles {
   }
 };
 
-template <int D, int NG>
+// PT: P^T and dS^T go back to tensor memory as packed bf16 and the dV / dK products take their A operand from there,
+// instead of through shared memory (see the forward kernel).
+template <int D, int NG, bool PT>
 __global__ void __launch_bounds__(bwd_threads(NG), 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                      const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -161,6 +174,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t t_s = tmem_base, t_dp = tmem_base + 64, t_dv = tmem_base + 128, t_dk = tmem_base + 128 + D;
+  const uint32_t t_p = tmem_base + 384, t_ds = tmem_base + 416;   // PT: [128 kv x 64 q] bf16 = 32 columns each
 
   // Every role walks the same tiles in the same order.  `g` counts the (kv block, q block) iterations of this
   // CTA over all its tiles and `tile_i` its non-empty tiles: the barrier phases follow these two counters, so the
@@ -261,13 +275,19 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           const uint32_t sdo = sq + L::DB * L::Q_TILE;
 #pragma unroll
           for (int kk = 0; kk < 64 / 16; ++kk) {  // reduction over the 64 query rows
-            umma_bf16_ss(t_dv, make_smem_desc(sp + kk * 32, 16, 1024), make_smem_desc(sdo + kk * 2048, L::Q_TILE, 1024),
-                         idesc_acc, (t | kk) != 0);
+            if constexpr (PT)
+              umma_bf16_ts(t_dv, t_p + kk * 8, make_smem_desc(sdo + kk * 2048, L::Q_TILE, 1024), idesc_acc, (t | kk) != 0);
+            else
+              umma_bf16_ss(t_dv, make_smem_desc(sp + kk * 32, 16, 1024), make_smem_desc(sdo + kk * 2048, L::Q_TILE, 1024),
+                           idesc_acc, (t | kk) != 0);
           }
 #pragma unroll
           for (int kk = 0; kk < 64 / 16; ++kk) {
-            umma_bf16_ss(t_dk, make_smem_desc(sds + kk * 32, 16, 1024), make_smem_desc(sq + kk * 2048, L::Q_TILE, 1024),
-                         idesc_acc, (t | kk) != 0);
+            if constexpr (PT)
+              umma_bf16_ts(t_dk, t_ds + kk * 8, make_smem_desc(sq + kk * 2048, L::Q_TILE, 1024), idesc_acc, (t | kk) != 0);
+            else
+              umma_bf16_ss(t_dk, make_smem_desc(sds + kk * 32, 16, 1024), make_smem_desc(sq + kk * 2048, L::Q_TILE, 1024),
+                           idesc_acc, (t | kk) != 0);
           }
           umma_commit(&bar[K1_QE + s]);
           umma_commit(&bar[K1_PE]);
@@ -369,19 +389,25 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         if (g > 0) {  // P^T / dS^T of the previous iteration (possibly of the previous tile) have been consumed
           if (!mbar_wait_bounded_warp(&bar[K1_PE], (g - 1) & 1, abort_flag, p.status)) { ok = false; break; }
         }
-        uint8_t* tp = smem + L::OFF_P;
-        uint8_t* tds = smem + L::OFF_DS;
+        if constexpr (PT) {
+          tmem_st_packed<CW>(t_p + lane_addr + cb / 2, sv);
+          tmem_st_packed<CW>(t_ds + lane_addr + cb / 2, dp);
+          tc_wait_st();
+        } else {
+          uint8_t* tp = smem + L::OFF_P;
+          uint8_t* tds = smem + L::OFF_DS;
 #pragma unroll
-        for (int c = 0; c < CW / 8; ++c) {
-          uint4 v, w;
-          v.x = pack_bf16(sv[c * 8 + 0], sv[c * 8 + 1]); v.y = pack_bf16(sv[c * 8 + 2], sv[c * 8 + 3]);
-          v.z = pack_bf16(sv[c * 8 + 4], sv[c * 8 + 5]); v.w = pack_bf16(sv[c * 8 + 6], sv[c * 8 + 7]);
-          w.x = pack_bf16(dp[c * 8 + 0], dp[c * 8 + 1]); w.y = pack_bf16(dp[c * 8 + 2], dp[c * 8 + 3]);
-          w.z = pack_bf16(dp[c * 8 + 4], dp[c * 8 + 5]); w.w = pack_bf16(dp[c * 8 + 6], dp[c * 8 + 7]);
-          st_swz(tp, r, grp * (CW / 8) + c, v);
-          st_swz(tds, r, grp * (CW / 8) + c, w);
+          for (int c = 0; c < CW / 8; ++c) {
+            uint4 v, w;
+            v.x = pack_bf16(sv[c * 8 + 0], sv[c * 8 + 1]); v.y = pack_bf16(sv[c * 8 + 2], sv[c * 8 + 3]);
+            v.z = pack_bf16(sv[c * 8 + 4], sv[c * 8 + 5]); v.w = pack_bf16(sv[c * 8 + 6], sv[c * 8 + 7]);
+            w.x = pack_bf16(dp[c * 8 + 0], dp[c * 8 + 1]); w.y = pack_bf16(dp[c * 8 + 2], dp[c * 8 + 3]);
+            w.z = pack_bf16(dp[c * 8 + 4], dp[c * 8 + 5]); w.w = pack_bf16(dp[c * 8 + 6], dp[c * 8 + 7]);
+            st_swz(tp, r, grp * (CW / 8) + c, v);
+            st_swz(tds, r, grp * (CW / 8) + c, w);
+          }
+          fence_proxy_async();
         }
-        fence_proxy_async();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar[K1_PF]);
@@ -463,7 +489,7 @@ struct DqTiles {
   }
 };
 
-template <int D, int NG>
+template <int D, int NG, bool PT>
 __global__ void __launch_bounds__(bwd_threads(NG), 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -495,12 +521,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     fence_barrier_init();
     tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_do); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v);
   }
-  if (warp == 1) { tmem_alloc(tmem_slot, 256); tmem_relinquish(); }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t t_s = tmem_base, t_dp = tmem_base + 64, t_dq = tmem_base + 128;
+  const uint32_t t_ds = tmem_base + 256;   // PT: dS [128 q x 64 kv] as packed bf16, 32 columns
 
   // As in the dK/dV kernel: every role walks the same tiles; `g` counts this CTA's (q block, kv block) iterations
   // over all its tiles and `tile_i` its tiles, and the barrier phases follow those two counters.
@@ -596,8 +623,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           const uint32_t sk = smem_u32(smem + L::OFF_KV + s * L::STAGE);
 #pragma unroll
           for (int kk = 0; kk < 64 / 16; ++kk) {  // reduction over the 64 kv rows
-            umma_bf16_ss(t_dq, make_smem_desc(sds + kk * 32, 16, 1024), make_smem_desc(sk + kk * 2048, L::KV_TILE, 1024),
-                         idesc_dq, (t | kk) != 0);
+            if constexpr (PT)
+              umma_bf16_ts(t_dq, t_ds + kk * 8, make_smem_desc(sk + kk * 2048, L::KV_TILE, 1024), idesc_dq, (t | kk) != 0);
+            else
+              umma_bf16_ss(t_dq, make_smem_desc(sds + kk * 32, 16, 1024), make_smem_desc(sk + kk * 2048, L::KV_TILE, 1024),
+                           idesc_dq, (t | kk) != 0);
           }
           umma_commit(&bar[K2_KE + s]);
           umma_commit(&bar[K2_DE]);
@@ -665,15 +695,20 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (g > 0) {  // dS of the previous iteration (possibly of the previous tile) has been consumed
           if (!mbar_wait_bounded_warp(&bar[K2_DE], (g - 1) & 1, abort_flag, p.status)) { ok = false; break; }
         }
-        uint8_t* tds = smem + L::OFF_DS;
+        if constexpr (PT) {
+          tmem_st_packed<CW>(t_ds + lane_addr + cb / 2, dp);
+          tc_wait_st();
+        } else {
+          uint8_t* tds = smem + L::OFF_DS;
 #pragma unroll
-        for (int c = 0; c < CW / 8; ++c) {
-          uint4 w;
-          w.x = pack_bf16(dp[c * 8 + 0], dp[c * 8 + 1]); w.y = pack_bf16(dp[c * 8 + 2], dp[c * 8 + 3]);
-          w.z = pack_bf16(dp[c * 8 + 4], dp[c * 8 + 5]); w.w = pack_bf16(dp[c * 8 + 6], dp[c * 8 + 7]);
-          st_swz(tds, r, grp * (CW / 8) + c, w);
+          for (int c = 0; c < CW / 8; ++c) {
+            uint4 w;
+            w.x = pack_bf16(dp[c * 8 + 0], dp[c * 8 + 1]); w.y = pack_bf16(dp[c * 8 + 2], dp[c * 8 + 3]);
+            w.z = pack_bf16(dp[c * 8 + 4], dp[c * 8 + 5]); w.w = pack_bf16(dp[c * 8 + 6], dp[c * 8 + 7]);
+            st_swz(tds, r, grp * (CW / 8) + c, w);
+          }
+          fence_proxy_async();
         }
-        fence_proxy_async();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar[K2_DF]);
@@ -707,7 +742,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 256); }
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
 // 4-D map over [B, S, Hn, D] bf16 with a box of [rows of S] x [64 elements of D]
@@ -728,7 +763,16 @@ static int bwd_groups() {
   return ng;
 }
 
-template <int D, int NG>
+static int bwd_p_tmem() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("JAXPP_B200_ATTN_P_TMEM");
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v;
+}
+
+template <int D, int NG, bool PT>
 static int launch_bwd(const void* dO, const void* q, const void* k, const void* v, const AttnBwdParams& p, cudaStream_t stream) {
   CUtensorMap mq64, mdo64, mk128, mv128, mq128, mdo128, mk64, mv64;
   int rc = 0;
@@ -741,8 +785,8 @@ static int launch_bwd(const void* dO, const void* q, const void* k, const void* 
   rc |= make_map_rows(&mk64, k, p.B, p.Sk, p.Hkv, D, 64);
   rc |= make_map_rows(&mv64, v, p.B, p.Sk, p.Hkv, D, 64);
   if (rc) return rc;
-  auto k1 = attn_bwd_dkdv_kernel<D, NG>;
-  auto k2 = attn_bwd_dq_kernel<D, NG>;
+  auto k1 = attn_bwd_dkdv_kernel<D, NG, PT>;
+  auto k2 = attn_bwd_dq_kernel<D, NG, PT>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvSmem<D>::TOTAL) != cudaSuccess) return -3;
@@ -793,6 +837,11 @@ JPB_API int jpb_attention_bwd(const void* dO, const void* q, const void* k, cons
   p.lse = lse2; p.delta = delta;
   p.dq = static_cast<__nv_bfloat16*>(dq); p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
   p.status = jpb_status_device_ptr();
-  if (bwd_groups() == 2) return D == 128 ? launch_bwd<128, 2>(dO, q, k, v, p, s) : launch_bwd<64, 2>(dO, q, k, v, p, s);
-  return D == 128 ? launch_bwd<128, 4>(dO, q, k, v, p, s) : launch_bwd<64, 4>(dO, q, k, v, p, s);
+  const bool pt = bwd_p_tmem() != 0;
+  if (bwd_groups() == 2) {
+    if (pt) return D == 128 ? launch_bwd<128, 2, true>(dO, q, k, v, p, s) : launch_bwd<64, 2, true>(dO, q, k, v, p, s);
+    return D == 128 ? launch_bwd<128, 2, false>(dO, q, k, v, p, s) : launch_bwd<64, 2, false>(dO, q, k, v, p, s);
+  }
+  if (pt) return D == 128 ? launch_bwd<128, 4, true>(dO, q, k, v, p, s) : launch_bwd<64, 4, true>(dO, q, k, v, p, s);
+  return D == 128 ? launch_bwd<128, 4, false>(dO, q, k, v, p, s) : launch_bwd<64, 4, false>(dO, q, k, v, p, s);
 }

@@ -50,7 +50,10 @@ struct AttnSmem {
 
 enum { BAR_Q = 0, BAR_KF = 1, BAR_VF = 3, BAR_KE = 5, BAR_VE = 7, BAR_SF = 9, BAR_SE = 11, BAR_PF = 13, BAR_PV = 14, BAR_MX = 15, BAR_N = 16 };
 
-template <int D, int NG>
+// PT: the probabilities go back to tensor memory (bf16, two per 32-bit column) and P V takes its A operand from
+// there, instead of a round trip through shared memory (a 32 KiB store, a proxy fence and a 32 KiB operand read per
+// block less on the shared-memory port, which the operand fetches of the MMAs already keep busy).
+template <int D, int NG, bool PT>
 __global__ void __launch_bounds__(att_threads(NG), 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
@@ -102,6 +105,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_o = tmem_base + 256;
+  const uint32_t tmem_p = tmem_base + 384;   // PT: P as packed bf16, 64 columns
 
   if (warp == 0) {
     if (lane == 0) {
@@ -189,9 +193,13 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #pragma unroll
         for (int k = 0; k < ATT_BN / 16; ++k) {
           // A = P: K-major, two 64-wide kv blocks; B = V: MN-major, 16 kv rows per step, 64-wide d blocks
-          const uint64_t da = make_smem_desc(sp + (k >> 2) * L::TILE + (k & 3) * 32, 16, 1024);
           const uint64_t db = make_smem_desc(sv + k * 2048, L::TILE, 1024);
-          umma_bf16_ss(tmem_o, da, db, idesc_pv, (j | k) != 0);
+          if constexpr (PT) {
+            umma_bf16_ts(tmem_o, tmem_p + k * 8, db, idesc_pv, (j | k) != 0);   // 16 kv = 8 packed columns per step
+          } else {
+            const uint64_t da = make_smem_desc(sp + (k >> 2) * L::TILE + (k & 3) * 32, 16, 1024);
+            umma_bf16_ss(tmem_o, da, db, idesc_pv, (j | k) != 0);
+          }
         }
         umma_commit(&bar[BAR_VE + s]);
         umma_commit(&bar[BAR_PV]);
@@ -281,19 +289,31 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
       }
       m_run = m_new;
-      // P -> shared memory, bf16, swizzled K-major: element (r, kv) lives in block kv/64 at
-      // r*128 + ((kv%64)/8 ^ (r%8))*16 + (kv%8)*2
+      if constexpr (PT) {
+        // P -> tensor memory: row r is lane r, kv columns (2c, 2c+1) share the 32-bit column c
 #pragma unroll
-      for (int c = 0; c < HALF / 8; ++c) {
-        uint4 v;
-        v.x = pack_bf16(sv[c * 8 + 0], sv[c * 8 + 1]);
-        v.y = pack_bf16(sv[c * 8 + 2], sv[c * 8 + 3]);
-        v.z = pack_bf16(sv[c * 8 + 4], sv[c * 8 + 5]);
-        v.w = pack_bf16(sv[c * 8 + 6], sv[c * 8 + 7]);
-        const int col = grp * HALF + c * 8;           // kv column of this chunk within the block
-        *reinterpret_cast<uint4*>(sp + (col >> 6) * L::TILE + r * 128 + ((((col & 63) >> 3) ^ (r & 7)) << 4)) = v;
+        for (int c = 0; c < HALF / 32; ++c) {
+          uint32_t w[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) w[i] = pack_bf16(sv[c * 32 + 2 * i], sv[c * 32 + 2 * i + 1]);
+          tmem_st_32x16(tmem_p + lane_addr + (grp * HALF + c * 32) / 2, w);
+        }
+        tc_wait_st();
+      } else {
+        // P -> shared memory, bf16, swizzled K-major: element (r, kv) lives in block kv/64 at
+        // r*128 + ((kv%64)/8 ^ (r%8))*16 + (kv%8)*2
+#pragma unroll
+        for (int c = 0; c < HALF / 8; ++c) {
+          uint4 v;
+          v.x = pack_bf16(sv[c * 8 + 0], sv[c * 8 + 1]);
+          v.y = pack_bf16(sv[c * 8 + 2], sv[c * 8 + 3]);
+          v.z = pack_bf16(sv[c * 8 + 4], sv[c * 8 + 5]);
+          v.w = pack_bf16(sv[c * 8 + 6], sv[c * 8 + 7]);
+          const int col = grp * HALF + c * 8;           // kv column of this chunk within the block
+          *reinterpret_cast<uint4*>(sp + (col >> 6) * L::TILE + r * 128 + ((((col & 63) >> 3) ^ (r & 7)) << 4)) = v;
+        }
+        fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's async proxy
       }
-      fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's async proxy
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar[BAR_PF]);
@@ -352,6 +372,17 @@ static int make_bshd_map(CUtensorMap* out, const void* base, int B, int S, int H
   return jpb_make_tensor_map(out, base, 2, 4, dims, strides, box, 1);
 }
 
+// 1: probabilities handed to the P V product through tensor memory; 0: through shared memory
+// (JAXPP_B200_ATTN_P_TMEM overrides the default)
+static int fwd_p_tmem() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("JAXPP_B200_ATTN_P_TMEM");
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v;
+}
+
 static int fwd_groups() {
   static int ng = 0;
   if (ng == 0) {
@@ -361,7 +392,7 @@ static int fwd_groups() {
   return ng;
 }
 
-template <int D, int NG>
+template <int D, int NG, bool PT>
 static int launch_attn_fwd(const void* q, const void* k, const void* v, const AttnParams& p, cudaStream_t stream) {
   using L = AttnSmem<D>;
   CUtensorMap mq, mk, mv;
@@ -371,7 +402,7 @@ static int launch_attn_fwd(const void* q, const void* k, const void* v, const At
   if (rc) return rc;
   rc = make_bshd_map(&mv, v, p.B, p.Sk, p.Hkv, D);
   if (rc) return rc;
-  auto kernel = attention_fwd_kernel<D, NG>;
+  auto kernel = attention_fwd_kernel<D, NG, PT>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
@@ -394,6 +425,11 @@ JPB_API int jpb_attention_fwd(const void* q, const void* k, const void* v, void*
   p.B = B; p.Sq = Sq; p.Sk = Sk; p.H = H; p.Hkv = Hkv; p.causal = causal; p.scale = scale;
   p.o = static_cast<__nv_bfloat16*>(o); p.lse = lse; p.status = jpb_status_device_ptr();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (fwd_groups() == 2) return D == 128 ? launch_attn_fwd<128, 2>(q, k, v, p, s) : launch_attn_fwd<64, 2>(q, k, v, p, s);
-  return D == 128 ? launch_attn_fwd<128, 4>(q, k, v, p, s) : launch_attn_fwd<64, 4>(q, k, v, p, s);
+  const bool pt = fwd_p_tmem() != 0;
+  if (fwd_groups() == 2) {
+    if (pt) return D == 128 ? launch_attn_fwd<128, 2, true>(q, k, v, p, s) : launch_attn_fwd<64, 2, true>(q, k, v, p, s);
+    return D == 128 ? launch_attn_fwd<128, 2, false>(q, k, v, p, s) : launch_attn_fwd<64, 2, false>(q, k, v, p, s);
+  }
+  if (pt) return D == 128 ? launch_attn_fwd<128, 4, true>(q, k, v, p, s) : launch_attn_fwd<64, 4, true>(q, k, v, p, s);
+  return D == 128 ? launch_attn_fwd<128, 4, false>(q, k, v, p, s) : launch_attn_fwd<64, 4, false>(q, k, v, p, s);
 }

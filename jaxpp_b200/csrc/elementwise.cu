@@ -835,6 +835,21 @@ JPB_API int jpb_embedding_bwd(int dt, const void* dy, const long long* ids, floa
   });
 }
 
+// Scatter-add of `dy` rows straight into an fp32 [vocab, d] table: with `zero_first` the table is cleared first
+// (it then holds this call's gradient), without it the call adds to what is there (a gradient accumulator).
+JPB_API int jpb_embedding_bwd_acc(int dt, const void* dy, const long long* ids, float* acc, long long n_tok, int d, int vocab,
+                                  int zero_first, void* stream) {
+  return dispatch_dtype(dt, [&](auto tag) {
+    using T = decltype(tag);
+    constexpr int VN = Vec<T>::N;
+    if (d % VN) return -int(JPB_ERR_BAD_ARGUMENT);
+    if (zero_first) cudaMemsetAsync(acc, 0, size_t(vocab) * d * sizeof(float), STREAM);
+    const size_t work = size_t(n_tok) * (d / VN);
+    embedding_bwd_kernel<T><<<ew_grid(work, 256), 256, 0, STREAM>>>((const T*)dy, (const int64_t*)ids, acc, n_tok, d, vocab);
+    return LAST_ERR;
+  });
+}
+
 JPB_API int jpb_ce_fwd(int dt, const void* logits, const long long* labels, float* loss, float* lse, int rows, int V,
                        void* stream) {
   return dispatch_dtype(dt, [&](auto tag) {

@@ -690,16 +690,18 @@ embedding = _define(
 )
 
 
-def _emb_bwd_ref(dy, ids, vocab):
+def _emb_bwd_ref(dy, ids, vocab, out_dtype=None):
     out = torch.zeros(vocab, dy.shape[-1], dtype=torch.float32, device=dy.device)
     out.index_add_(0, ids.reshape(-1), _f32(dy).reshape(-1, dy.shape[-1]))
-    return out.to(dy.dtype)
+    return out.to(out_dtype if out_dtype is not None else dy.dtype)
 
 
+# ``out_dtype`` float32 (what ``WGRAD_DTYPE`` asks for) returns the fp32 sum without a cast pass, and makes the op a
+# weight-gradient sink: inside a microbatch loop it adds straight into the accumulator (ops/sink.py)
 embedding_bwd = _define(
-    "embedding_bwd(Tensor dy, Tensor ids, int vocab) -> Tensor",
+    "embedding_bwd(Tensor dy, Tensor ids, int vocab, ScalarType? out_dtype=None) -> Tensor",
     _emb_bwd_ref,
-    lambda dy, ids, vocab: dy.new_empty(vocab, dy.shape[-1]),
+    lambda dy, ids, vocab, out_dtype=None: dy.new_empty(vocab, dy.shape[-1], dtype=out_dtype or dy.dtype),
     "embedding_bwd",
 )
 
@@ -710,7 +712,8 @@ def _emb_setup(ctx, inputs, output):
     ctx.vocab = table.shape[0]
 
 
-_autograd("embedding", lambda ctx, dy: (None, embedding_bwd(dy.contiguous(), ctx.saved_tensors[0], ctx.vocab)), _emb_setup)
+_autograd("embedding",
+          lambda ctx, dy: (None, embedding_bwd(dy.contiguous(), ctx.saved_tensors[0], ctx.vocab, WGRAD_DTYPE[0])), _emb_setup)
 
 
 # ======================================================================================

@@ -48,9 +48,73 @@ def timed(fn, iters: int, warmup: int = 3, flush: bool = True) -> float:
     return ts[len(ts) // 2]
 
 
+def suite(rows: int, hidden: int, iters: int, warmup: int, flush: bool):
+    """Every memory-bound kernel of the library once per iteration on inputs larger than L2, one JSON line each:
+    algorithmic bytes (what the op must read and write), CUDA-event time, GB/s and the fraction of the measured copy
+    bandwidth.  With ``--iters 1 --warmup 0`` every kernel launches once, which is the form to put under a profiler."""
+    from ..parallel import moe  # noqa: F401  (registers the router op)
+
+    _, bw_peak = _peaks()
+    bf = torch.bfloat16
+    R, H = rows, hidden
+    x, dy = torch.randn(R, H, device="cuda", dtype=bf), torch.randn(R, H, device="cuda", dtype=bf)
+    w, b = torch.randn(H, device="cuda", dtype=bf), torch.randn(H, device="cuda", dtype=bf)
+    _, rstd = native.rmsnorm(x, w, 1e-5)
+    _, mean, lrstd = native.layernorm(x, w, b, 1e-5)
+    gu = torch.randn(R, 2 * H, device="cuda", dtype=bf)
+    dyf = torch.randn(R, H, device="cuda", dtype=bf)
+    B, S, Hq, Hkv, D = max(1, R // 4096), 4096, 32, 32, 128
+    qkv = torch.randn(B, S, Hq + 2 * Hkv, D, device="cuda", dtype=bf)
+    pos = torch.arange(S, device="cuda", dtype=torch.float32)[:, None] * torch.rand(D // 2, device="cuda")[None, :]
+    cos, sin = pos.cos().contiguous(), pos.sin().contiguous()
+    q, k, v = native.qkv_split(qkv, cos, sin, Hq, Hkv)
+    V = 32000
+    Rl = max(1024, R // 4)
+    logits = torch.randn(Rl, V, device="cuda", dtype=bf)
+    labels = torch.randint(0, V, (Rl,), device="cuda")
+    _, lse = native.cross_entropy(logits, labels)
+    dloss = torch.ones(Rl, device="cuda")
+    table = torch.randn(V, H, device="cuda", dtype=bf)
+    ids = torch.randint(0, V, (R,), device="cuda")
+    n = R * H
+    pm, pg = torch.randn(n, device="cuda"), torch.randn(n, device="cuda")
+    m_, v_ = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    step = torch.ones((), dtype=torch.int64, device="cuda")
+    seed = torch.tensor(1234, dtype=torch.int64, device="cuda")
+    rl = torch.randn(R * 8, 8, device="cuda")
+    e2 = 2
+    cases = [
+        ("rmsnorm", 2 * n * e2, lambda: native.rmsnorm(x, w, 1e-5)),
+        ("rmsnorm_bwd", 3 * n * e2, lambda: native.rmsnorm_bwd(dy, x, w, rstd)),
+        ("rmsnorm_bwd_add", 4 * n * e2, lambda: native.rmsnorm_bwd_add(dy, x, w, rstd, dyf)),
+        ("layernorm", 2 * n * e2, lambda: native.layernorm(x, w, b, 1e-5)),
+        ("layernorm_bwd", 3 * n * e2, lambda: native.layernorm_bwd(dy, x, w, mean, lrstd)),
+        ("swiglu", 3 * n * e2, lambda: native.swiglu(gu)),
+        ("swiglu_bwd", 5 * n * e2, lambda: native.swiglu_bwd(dyf, gu)),
+        ("gelu", 2 * n * e2, lambda: native.gelu(x)),
+        ("gelu_bwd", 3 * n * e2, lambda: native.gelu_bwd(dy, x)),
+        ("qkv_split_rope", 2 * qkv.numel() * e2, lambda: native.qkv_split(qkv, cos, sin, Hq, Hkv)),
+        ("qkv_merge_rope", 2 * qkv.numel() * e2, lambda: native.qkv_merge(q, k, v, cos, sin)),
+        ("cross_entropy", logits.numel() * e2, lambda: native.cross_entropy(logits, labels)),
+        ("cross_entropy_bwd", 2 * logits.numel() * e2, lambda: native.cross_entropy_bwd(dloss, logits, labels, lse)),
+        ("embedding", 2 * n * e2, lambda: native.embedding(ids, table)),
+        ("embedding_bwd", n * e2 + V * H * (4 + 4 + e2), lambda: native.embedding_bwd(dy, ids, V)),
+        ("colsum", n * e2, lambda: native.colsum(dy)),
+        ("dropout", 2 * n * e2, lambda: native.dropout(x, 0.1, seed, 7)),
+        ("adamw", n * (4 * 4 + 3 * 4 + 2), lambda: native.adamw(pm, pg, m_, v_, step, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1.0, bf, None, False)),
+        ("router", rl.numel() * 4 * 2 + rl.shape[0] * 2 * 12, lambda: torch.ops.b200moe.router(rl, 2)),
+    ]
+    for name, nbytes, fn in cases:
+        ms = timed(fn, iters, warmup, flush)
+        print(json.dumps({"op": name, "rows": R, "hidden": H, "algorithmic_mb": round(nbytes / 1e6, 1), "ms": round(ms, 4),
+                          "gbs": round(nbytes / ms / 1e6, 1), "frac_of_measured_copy_bw": round(nbytes / ms / 1e6 / bw_peak, 3),
+                          "status": native.read_status()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "attn_fwd", "attn_bwd", "rmsnorm", "rmsnorm_bwd", "swiglu", "cross_entropy", "adamw"])
+    ap.add_argument("op", choices=["gemm", "gemm_batched", "attn_fwd", "attn_bwd", "rmsnorm", "rmsnorm_bwd", "swiglu", "cross_entropy",
+                                   "adamw", "suite"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -65,8 +129,11 @@ def main():
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--experts", type=int, default=4)
     a = ap.parse_args()
     native.load()
+    if a.op == "suite":
+        return suite(a.rows, a.hidden, a.iters, a.warmup, not a.no_flush)
     tf_peak, bw_peak = _peaks()
     bf = torch.bfloat16
     rnd = lambda *s: torch.randn(*s, device="cuda", dtype=bf)
@@ -83,6 +150,11 @@ def main():
         else:
             dy, x = rnd(M, N), rnd(M, K)
             fn = lambda: native.linear_wgrad(dy, x)
+    elif a.op == "gemm_batched":
+        E, M, N, K = a.experts, a.m, a.n, a.k
+        flops = 2.0 * E * M * N * K
+        xb, wb = rnd(E, M, K), rnd(E, N, K)
+        fn = lambda: native.linear_batched(xb, wb)
     elif a.op in ("attn_fwd", "attn_bwd"):
         B, S, H, D = a.batch, a.seq, a.heads, a.head_dim
         Hkv = a.kv_heads or H

@@ -421,18 +421,27 @@ def embedding(ids, table):
     return out
 
 
-def embedding_bwd(dy, ids, vocab):
+def embedding_bwd(dy, ids, vocab, out_dtype=None, out: Optional[torch.Tensor] = None, accumulate: bool = False):
+    """Gradient of the embedding table: rows of ``dy`` summed by token id.  ``out_dtype`` float32 returns the fp32 sum
+    itself (no cast pass); with ``out`` (fp32 [vocab, d]) the rows are added into it (``accumulate``) or it is
+    cleared first."""
     dy, ids = dy.contiguous(), ids.contiguous()
     d = dy.shape[-1]
-    acc = torch.empty(vocab, d, dtype=torch.float32, device=dy.device)
-    if dy.dtype == torch.float32:
-        _check(load().jpb_embedding_bwd(0, dy.data_ptr(), ids.data_ptr(), acc.data_ptr(), None, ids.numel(), d, vocab,
-                                        _stream()), "embedding_bwd", 1)
+    want = out_dtype or dy.dtype
+    if out is not None or want == torch.float32:
+        lib = load()
+        lib.jpb_embedding_bwd_acc.argtypes = [_c_int, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p]
+        acc = out if out is not None else torch.empty(vocab, d, dtype=torch.float32, device=dy.device)
+        if acc.dtype != torch.float32 or not acc.is_contiguous():
+            raise NativeError("embedding_bwd accumulates into a contiguous float32 table")
+        _check(lib.jpb_embedding_bwd_acc(_dt(dy), dy.data_ptr(), ids.data_ptr(), acc.data_ptr(), ids.numel(), d, vocab,
+                                         int(not accumulate), _stream()), "embedding_bwd", 1)
         return acc
-    out = torch.empty(vocab, d, dtype=dy.dtype, device=dy.device)
-    _check(load().jpb_embedding_bwd(_dt(dy), dy.data_ptr(), ids.data_ptr(), acc.data_ptr(), out.data_ptr(), ids.numel(), d,
+    acc = torch.empty(vocab, d, dtype=torch.float32, device=dy.device)
+    out_t = torch.empty(vocab, d, dtype=dy.dtype, device=dy.device)
+    _check(load().jpb_embedding_bwd(_dt(dy), dy.data_ptr(), ids.data_ptr(), acc.data_ptr(), out_t.data_ptr(), ids.numel(), d,
                                     vocab, _stream()), "embedding_bwd", 2)
-    return out
+    return out_t
 
 
 def cross_entropy(logits, labels):

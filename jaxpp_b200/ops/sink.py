@@ -17,7 +17,7 @@ from . import core as ops
 
 def sink_targets() -> tuple:
     """Op overloads whose result may be redirected into an accumulator."""
-    out = [torch.ops.b200.linear_wgrad.default]
+    out = [torch.ops.b200.linear_wgrad.default, torch.ops.b200.embedding_bwd.default]
     try:
         from ..parallel import tp  # noqa: F401  (registers the b200tp ops)
 
@@ -46,6 +46,12 @@ def accumulate(op, acc: torch.Tensor, *args, **kwargs) -> torch.Tensor:
         if (ops._use_native(dy) and acc.dtype == torch.float32 and acc.is_contiguous()
                 and _fits(acc, dy.shape[-1], x.shape[-1], out_dtype) and dy.dtype == torch.bfloat16):
             ops._native().linear_wgrad(dy, x, out=acc, accumulate=True)
+            return acc
+    elif op is torch.ops.b200.embedding_bwd.default:
+        dy, ids, vocab = args[0], args[1], args[2]
+        if (ops._use_native(dy) and acc.dtype == torch.float32 and acc.is_contiguous() and acc.dim() == 2
+                and acc.shape[0] == vocab and acc.shape[1] == dy.shape[-1]):
+            ops._native().embedding_bwd(dy, ids, vocab, out=acc, accumulate=True)   # scatter-add into the accumulator
             return acc
     elif op is torch.ops.b200tp.ag_wgrad.default:
         dy, x_shard, axis = args[0], args[1], args[2]

@@ -204,6 +204,15 @@ def test_embedding_and_cross_entropy(native, dtype):
     assert torch.equal(native.embedding(ids, table), table[ids])
     dy = rnd(4, 77, d, dtype=dtype, seed=1)
     close(native.embedding_bwd(dy, ids, vocab), ops._emb_bwd_ref(dy.float(), ids, vocab), **tol)
+    # the fp32 form (no cast pass) and the accumulating form that a microbatch loop's gradient sink uses
+    ref32 = ops._emb_bwd_ref(dy.float(), ids, vocab, torch.float32)
+    got32 = native.embedding_bwd(dy, ids, vocab, torch.float32)
+    assert got32.dtype == torch.float32
+    close(got32, ref32, rtol=1e-5, atol=1e-5)
+    acc = torch.full_like(ref32, 0.5)
+    assert native.embedding_bwd(dy, ids, vocab, out=acc, accumulate=True) is acc
+    native.embedding_bwd(dy, ids, vocab, out=acc, accumulate=True)
+    close(acc, 0.5 + 2 * ref32, rtol=1e-5, atol=1e-5)
     for V in (32000, 50257, 1000):
         logits = rnd(19, V, dtype=dtype, scale=3.0, seed=2)
         labels = torch.randint(0, V, (19,), device="cuda")
