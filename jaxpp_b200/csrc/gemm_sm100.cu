@@ -45,7 +45,35 @@ struct GemmParams {
   // end of a problem read rows of the next one; the epilogue masks them (and K must be a multiple of 64).
   int batch;
   int a_off, b_off;          // storage rows per problem of A and B
+  // Groups of unequal size inside equal-sized storage: the M rows of a problem (count_k == 0) or its K reduction
+  // rows (count_k == 1) are `segs` segments of `seg_rows` rows, and only the first counts[prob * segs + s] rows of
+  // segment s hold data (the others are zero).  Output tiles, or 64-row reduction blocks, without a live row are
+  // not loaded and not multiplied; an output tile without any is written as zeros (left alone when accumulating).
+  const int* counts;         // device memory, or nullptr: every row is live
+  int seg_rows, segs, count_k;
 };
+
+// Does [lo, hi) of problem `prob` contain a live row?  Every role of the CTA asks the same question about the same
+// ranges and gets the same answer (the counts do not change while the kernel runs), so they skip in step.
+__device__ __forceinline__ bool range_live(const GemmParams& p, int prob, int lo, int hi) {
+  const int* c = p.counts + prob * p.segs;
+  int q1 = (hi - 1) / p.seg_rows;
+  if (q1 >= p.segs) q1 = p.segs - 1;
+  for (int q = lo / p.seg_rows; q <= q1; ++q) {
+    const int s = q * p.seg_rows;
+    const int e = s + min(__ldg(c + q), p.seg_rows);
+    if (e > s && lo < e && hi > s) return true;
+  }
+  return false;
+}
+// Is output tile [m0, m0 + BM) of problem `prob` worth computing?
+__device__ __forceinline__ bool tile_live(const GemmParams& p, int prob, int m0) {
+  if (p.counts == nullptr) return true;
+  return p.count_k ? range_live(p, prob, 0, p.K) : range_live(p, prob, m0, m0 + BM);
+}
+__device__ __forceinline__ bool kblock_live(const GemmParams& p, int prob, int k0) {
+  return p.counts == nullptr || !p.count_k || range_live(p, prob, k0, k0 + BK);
+}
 
 // Tile rasterisation: groups of GROUP_M row blocks are walked column by column, so that the ~148 tiles in
 // flight at any time touch about GROUP_M row panels of A and 148/GROUP_M column panels of B — a working set that
@@ -118,7 +146,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         tile_coords(tile - prob * tiles_per_problem, p.tiles_m, p.tiles_n, m_blk, n_blk);
         const int m0 = m_blk * BM, n0 = n_blk * BN;
         const int a_row = prob * p.a_off, b_row = prob * p.b_off;  // storage-row offsets of this problem
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        if (!tile_live(p, prob, m0)) continue;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!kblock_live(p, prob, kb * BK)) continue;
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait_bounded(&empty[s], ph ^ 1, abort_flag, p.status)) { ok = false; break; }
@@ -144,6 +174,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &map_b, &full[s], n0 + j * 64, b_row + k0);
           }
+          ++it;
         }
       }
       if (!ok) {
@@ -165,13 +196,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       uint32_t it = 0;
       uint32_t tile_i = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int prob = tile / tiles_per_problem;
+        if (p.counts != nullptr) {
+          int m_blk, n_blk;
+          tile_coords(tile - prob * tiles_per_problem, p.tiles_m, p.tiles_n, m_blk, n_blk);
+          if (!tile_live(p, prob, m_blk * BM)) continue;
+        }
         const uint32_t acc = tile_i & 1;
         const uint32_t acc_ph = (tile_i >> 1) & 1;
         if (!mbar_wait_bounded(&acc_empty[acc], acc_ph ^ 1, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        bool fresh = true;  // the first product of a tile overwrites the accumulator
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!kblock_live(p, prob, kb * BK)) continue;
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait_bounded(&full[s], ph, abort_flag, p.status)) { ok = false; break; }
@@ -182,11 +221,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t da = A_MN ? make_smem_desc(sa + k * 2048, 8192, 1024) : make_smem_desc(sa + k * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, 8192, 1024) : make_smem_desc(sb + k * 32, 16, 1024);
-            umma_bf16_ss(d_tmem, da, db, idesc, (kb | k) != 0);
+            umma_bf16_ss(d_tmem, da, db, idesc, !(fresh && k == 0));
           }
+          fresh = false;
           umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
+          ++it;
         }
         if (ok) umma_commit(&acc_full[acc]);
+        ++tile_i;
       }
     }
   } else {
@@ -194,15 +236,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are visible to this warp
     uint32_t tile_i = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int m_blk, n_blk;
       const int prob = tile / tiles_per_problem;
       tile_coords(tile - prob * tiles_per_problem, p.tiles_m, p.tiles_n, m_blk, n_blk);
       const int m0 = m_blk * BM, n0 = n_blk * BN;
+      const bool live = tile_live(p, prob, m0);  // uniform across the CTA
+      if (!live && p.accumulate) continue;       // nothing to add
       const uint32_t acc = tile_i & 1;
       const uint32_t acc_ph = (tile_i >> 1) & 1;
-      if (!mbar_wait_bounded_warp(&acc_full[acc], acc_ph, abort_flag, p.status)) { ok = false; break; }
-      tc_fence_after();
+      if (live) {
+        if (!mbar_wait_bounded_warp(&acc_full[acc], acc_ph, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+      }
       const int row_in = m0 + quarter * 32 + lane;        // row within this problem
       const bool row_ok = row_in < p.M;
       const size_t row = size_t(prob) * p.M + row_in;     // row of the stacked output
@@ -211,8 +257,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int col0 = n0 + c * 32;
         if (col0 >= p.N) break;  // uniform across the warp
         uint32_t r[32];
-        tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN + c * 32, r);
-        tc_wait_ld();
+        if (live) {
+          tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN + c * 32, r);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;  // a tile without live rows is all zeros
+        }
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
@@ -261,9 +312,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
         }
       }
+      if (!live) continue;
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      ++tile_i;
     }
   }
 
@@ -375,9 +428,15 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams
 
 // Common entry: `batch` equal-sized problems stacked along the storage rows of A, B and D (batch == 1: one GEMM).
 static int gemm_entry(const void* A, const void* B, void* D, const void* bias, int batch, int M, int N, int K, int lda, int ldb,
-                      int ldd, int a_mn_major, int b_mn_major, int out_fp32, int accumulate, int bias_fp32, void* stream) {
+                      int ldd, int a_mn_major, int b_mn_major, int out_fp32, int accumulate, int bias_fp32, void* stream,
+                      const int* counts = nullptr, int seg_rows = 0, int segs = 0, int count_k = 0) {
   using namespace jpb;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
+  if (counts != nullptr) {
+    // segments must tile the counted dimension exactly; a bias would make dead tiles non-zero
+    if (seg_rows <= 0 || segs <= 0 || (long long)seg_rows * segs != (count_k ? K : M) || bias != nullptr || K % BK != 0)
+      return -JPB_ERR_BAD_ARGUMENT;
+  }
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
     return -JPB_ERR_BAD_ARGUMENT;
   if (accumulate && !out_fp32) return -JPB_ERR_BAD_ARGUMENT;
@@ -403,6 +462,7 @@ static int gemm_entry(const void* A, const void* B, void* D, const void* bias, i
   p.bias = bias; p.bias_fp32 = bias_fp32; p.D = D; p.status = jpb_status_device_ptr();
   p.tiles_m = (M + BM - 1) / BM;
   p.tiles_n = (N + BN - 1) / BN;
+  p.counts = counts; p.seg_rows = seg_rows; p.segs = segs; p.count_k = count_k;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (!a_mn_major && !b_mn_major) return launch<false, false>(ma, mb, p, s);
   if (!a_mn_major && b_mn_major) return launch<false, true>(ma, mb, p, s);
@@ -424,4 +484,18 @@ JPB_API int jpb_gemm_bf16(const void* A, const void* B, void* D, const void* bia
 JPB_API int jpb_gemm_bf16_batched(const void* A, const void* B, void* D, int batch, int M, int N, int K, int lda, int ldb,
                                   int ldd, int a_mn_major, int b_mn_major, int out_fp32, int accumulate, void* stream) {
   return gemm_entry(A, B, D, nullptr, batch, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, out_fp32, accumulate, 0, stream);
+}
+
+// Grouped GEMM whose groups differ in size (a mixture-of-experts layer after capacity routing: every expert has room
+// for the same number of slots, but fills only some).  Storage is that of jpb_gemm_bf16_batched; `counts` (device
+// memory, [batch, segs] int32) says how many rows at the start of each `seg_rows`-row segment hold data -- segments of
+// the M rows of each problem (count_k = 0: forward and input gradient), or of its K reduction rows (count_k = 1:
+// weight gradient).  The other rows must be zero.  Output tiles and 64-row reduction blocks without a live row cost no
+// memory traffic and no tensor-core time; the result equals that of jpb_gemm_bf16_batched.
+JPB_API int jpb_gemm_bf16_grouped(const void* A, const void* B, void* D, int batch, int M, int N, int K, int lda, int ldb,
+                                  int ldd, int a_mn_major, int b_mn_major, int out_fp32, int accumulate, const int* counts,
+                                  int seg_rows, int segs, int count_k, void* stream) {
+  if (counts == nullptr) return -JPB_ERR_BAD_ARGUMENT;
+  return gemm_entry(A, B, D, nullptr, batch, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, out_fp32, accumulate, 0, stream,
+                    counts, seg_rows, segs, count_k);
 }

@@ -171,35 +171,48 @@ def _wg_dtype(dy, out_dtype):
     return out_dtype if out_dtype is not None else dy.dtype
 
 
+# ``counts`` ([E, M / seg_rows] int32) describes groups of unequal size inside the equal-sized storage: the M rows of a
+# group are segments of ``seg_rows`` rows, and only the first counts[e, s] rows of segment s hold data; the caller
+# guarantees that the others are zero.  The results do not depend on it (zero rows give zero products), so the
+# references ignore it; the GPU kernels skip the tiles and reduction blocks that hold no data.
 linear_batched = _define(
-    "linear_batched(Tensor x, Tensor w) -> Tensor",
-    lambda x, w: torch.bmm(x, w.transpose(1, 2)),
-    lambda x, w: x.new_empty(x.shape[0], x.shape[1], w.shape[1]),
+    "linear_batched(Tensor x, Tensor w, Tensor? counts=None, int seg_rows=0) -> Tensor",
+    lambda x, w, counts=None, seg_rows=0: torch.bmm(x, w.transpose(1, 2)),
+    lambda x, w, counts=None, seg_rows=0: x.new_empty(x.shape[0], x.shape[1], w.shape[1]),
     "linear_batched",
 )
 linear_dgrad_batched = _define(
-    "linear_dgrad_batched(Tensor dy, Tensor w) -> Tensor",
-    lambda dy, w: torch.bmm(dy, w),
-    lambda dy, w: dy.new_empty(dy.shape[0], dy.shape[1], w.shape[2]),
+    "linear_dgrad_batched(Tensor dy, Tensor w, Tensor? counts=None, int seg_rows=0) -> Tensor",
+    lambda dy, w, counts=None, seg_rows=0: torch.bmm(dy, w),
+    lambda dy, w, counts=None, seg_rows=0: dy.new_empty(dy.shape[0], dy.shape[1], w.shape[2]),
     "linear_dgrad_batched",
 )
 linear_wgrad_batched = _define(
-    "linear_wgrad_batched(Tensor dy, Tensor x, ScalarType? out_dtype=None) -> Tensor",
-    lambda dy, x, out_dtype=None: torch.bmm(_f32(dy).transpose(1, 2), _f32(x)).to(_wg_dtype(dy, out_dtype)),
-    lambda dy, x, out_dtype=None: dy.new_empty(dy.shape[0], dy.shape[2], x.shape[2], dtype=_wg_dtype(dy, out_dtype)),
+    "linear_wgrad_batched(Tensor dy, Tensor x, ScalarType? out_dtype=None, Tensor? counts=None, int seg_rows=0) -> Tensor",
+    lambda dy, x, out_dtype=None, counts=None, seg_rows=0:
+        torch.bmm(_f32(dy).transpose(1, 2), _f32(x)).to(_wg_dtype(dy, out_dtype)),
+    lambda dy, x, out_dtype=None, counts=None, seg_rows=0:
+        dy.new_empty(dy.shape[0], dy.shape[2], x.shape[2], dtype=_wg_dtype(dy, out_dtype)),
     "linear_wgrad_batched",
 )
 
 
+def _linear_batched_setup(ctx, inputs, output):
+    x, w, counts, ctx.seg_rows = inputs
+    ctx.has_counts = counts is not None
+    ctx.save_for_backward(*([x, w] + ([counts] if ctx.has_counts else [])))
+
+
 def _linear_batched_bwd(ctx, dy):
-    x, w = ctx.saved_tensors
+    x, w = ctx.saved_tensors[:2]
+    counts = ctx.saved_tensors[2] if ctx.has_counts else None
     dy = dy.contiguous()
-    dx = linear_dgrad_batched(dy, w) if ctx.needs_input_grad[0] else None
-    dw = linear_wgrad_batched(dy, x, WGRAD_DTYPE[0]) if ctx.needs_input_grad[1] else None
-    return dx, dw
+    dx = linear_dgrad_batched(dy, w, counts, ctx.seg_rows) if ctx.needs_input_grad[0] else None
+    dw = linear_wgrad_batched(dy, x, WGRAD_DTYPE[0], counts, ctx.seg_rows) if ctx.needs_input_grad[1] else None
+    return dx, dw, None, None
 
 
-_autograd("linear_batched", _linear_batched_bwd, lambda ctx, inputs, output: ctx.save_for_backward(*inputs))
+_autograd("linear_batched", _linear_batched_bwd, _linear_batched_setup)
 
 
 # ======================================================================================

@@ -130,6 +130,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--experts", type=int, default=4)
+    ap.add_argument("--fill", type=float, default=1.0,
+                    help="gemm_batched: fraction of each group's rows that hold data (< 1: the unequal-group kernel, which "
+                         "skips the rest; the FLOP count stays that of the full storage, so the rate reads as 'effective')")
     a = ap.parse_args()
     native.load()
     if a.op == "suite":
@@ -154,7 +157,20 @@ def main():
         E, M, N, K = a.experts, a.m, a.n, a.k
         flops = 2.0 * E * M * N * K
         xb, wb = rnd(E, M, K), rnd(E, N, K)
-        fn = lambda: native.linear_batched(xb, wb)
+        if a.fill < 1.0:
+            live = int(M * a.fill)
+            xb[:, live:] = 0
+            counts = torch.full((E, 1), live, dtype=torch.int32, device="cuda")
+            dyb = rnd(E, M, N)
+            dyb[:, live:] = 0
+            if a.layout == "fwd":
+                fn = lambda: native.linear_batched(xb, wb, counts, M)
+            elif a.layout == "dgrad":
+                fn = lambda: native.linear_dgrad_batched(dyb, wb, counts, M)
+            else:
+                fn = lambda: native.linear_wgrad_batched(dyb, xb, torch.float32, counts, M)
+        else:
+            fn = lambda: native.linear_batched(xb, wb)
     elif a.op in ("attn_fwd", "attn_bwd"):
         B, S, H, D = a.batch, a.seq, a.heads, a.head_dim
         Hkv = a.kv_heads or H

@@ -181,8 +181,20 @@ def linear(x, w, bias):
     return out.view(*x.shape[:-1], N)
 
 
-def _gemm_batched(a, b, out, batch, M, N, K, a_mn, b_mn):
+def _counts_ok(counts, E) -> bool:
+    return (counts is not None and counts.dtype == torch.int32 and counts.dim() == 2 and counts.shape[0] == E
+            and counts.is_contiguous())
+
+
+def _gemm_batched(a, b, out, batch, M, N, K, a_mn, b_mn, counts=None, seg_rows=0, count_k=False):
     lib = load()
+    if counts is not None:
+        lib.jpb_gemm_bf16_grouped.argtypes = [_c_p, _c_p, _c_p] + [_c_int] * 11 + [_c_p] + [_c_int] * 3 + [_c_p]
+        rc = lib.jpb_gemm_bf16_grouped(a.data_ptr(), b.data_ptr(), out.data_ptr(), batch, M, N, K, a.stride(-2), b.stride(-2),
+                                       out.stride(-2), int(a_mn), int(b_mn), int(out.dtype == torch.float32), 0,
+                                       counts.data_ptr(), seg_rows, counts.shape[1], int(count_k), _stream())
+        _check(rc, "jpb_gemm_bf16_grouped")
+        return out
     lib.jpb_gemm_bf16_batched.argtypes = [_c_p, _c_p, _c_p] + [_c_int] * 11 + [_c_p]
     rc = lib.jpb_gemm_bf16_batched(a.data_ptr(), b.data_ptr(), out.data_ptr(), batch, M, N, K, a.stride(-2), b.stride(-2),
                                    out.stride(-2), int(a_mn), int(b_mn), int(out.dtype == torch.float32), 0, _stream())
@@ -194,34 +206,41 @@ def _batched_ok(*ts) -> bool:
     return all(t.dtype == torch.bfloat16 and t.dim() == 3 for t in ts)
 
 
-def linear_batched(x, w):
-    """x [E, M, K], w [E, N, K] -> [E, M, N]; one grouped launch when the reduction length allows it."""
+def linear_batched(x, w, counts=None, seg_rows=0):
+    """x [E, M, K], w [E, N, K] -> [E, M, N]; one grouped launch when the reduction length allows it.  ``counts``
+    ([E, M / seg_rows] int32): rows of data at the start of each ``seg_rows``-row segment of a group; the rest of
+    ``x`` is zero and the kernel neither loads nor multiplies tiles made of such rows only."""
     E, M, K = x.shape
     N = w.shape[1]
-    if not _batched_ok(x, w) or K % 64 or K % 8 or E == 1:
+    if not _batched_ok(x, w) or K % 64 or K % 8:
         return torch.stack([linear(x[e], w[e], None) for e in range(E)], 0)
     x, w = x.contiguous(), w.contiguous()
     out = torch.empty(E, M, N, dtype=torch.bfloat16, device=x.device)
+    if _counts_ok(counts, E) and seg_rows * counts.shape[1] == M:
+        return _gemm_batched(x, w, out, E, M, N, K, False, False, counts, seg_rows, False)
     return _gemm_batched(x, w, out, E, M, N, K, False, False)
 
 
-def linear_dgrad_batched(dy, w):
-    """dy [E, M, N], w [E, N, K] -> [E, M, K] (reduction over N)."""
+def linear_dgrad_batched(dy, w, counts=None, seg_rows=0):
+    """dy [E, M, N], w [E, N, K] -> [E, M, K] (reduction over N); ``counts`` as in :func:`linear_batched`."""
     E, M, N = dy.shape
     K = w.shape[2]
-    if not _batched_ok(dy, w) or N % 64 or K % 8 or E == 1:
+    if not _batched_ok(dy, w) or N % 64 or K % 8:
         return torch.stack([linear_dgrad(dy[e], w[e]) for e in range(E)], 0)
     dy, w = dy.contiguous(), w.contiguous()
     out = torch.empty(E, M, K, dtype=torch.bfloat16, device=dy.device)
+    if _counts_ok(counts, E) and seg_rows * counts.shape[1] == M:
+        return _gemm_batched(dy, w, out, E, M, K, N, False, True, counts, seg_rows, False)
     return _gemm_batched(dy, w, out, E, M, K, N, False, True)
 
 
-def linear_wgrad_batched(dy, x, out_dtype=None):
-    """dy [E, M, N], x [E, M, K] -> [E, N, K] (reduction over the M tokens of each group)."""
+def linear_wgrad_batched(dy, x, out_dtype=None, counts=None, seg_rows=0):
+    """dy [E, M, N], x [E, M, K] -> [E, N, K] (reduction over the M tokens of each group).  With ``counts`` the
+    reduction skips 64-row blocks that hold no data."""
     E, M, N = dy.shape
     K = x.shape[2]
     out_dtype = out_dtype or dy.dtype
-    if not _batched_ok(dy, x) or M % 64 or N % 8 or K % 8 or E == 1 or out_dtype not in (torch.bfloat16, torch.float32):
+    if not _batched_ok(dy, x) or M % 64 or N % 8 or K % 8 or out_dtype not in (torch.bfloat16, torch.float32):
         out = torch.empty(E, N, K, dtype=out_dtype, device=dy.device)
         for e in range(E):
             if out_dtype in (torch.bfloat16, torch.float32):
@@ -231,6 +250,8 @@ def linear_wgrad_batched(dy, x, out_dtype=None):
         return out
     dy, x = dy.contiguous(), x.contiguous()
     out = torch.empty(E, N, K, dtype=out_dtype, device=dy.device)
+    if _counts_ok(counts, E) and seg_rows * counts.shape[1] == M:
+        return _gemm_batched(dy, x, out, E, N, K, M, True, True, counts, seg_rows, True)
     return _gemm_batched(dy, x, out, E, N, K, M, True, True)
 
 

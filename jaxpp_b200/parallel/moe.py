@@ -253,13 +253,20 @@ def route(x: Tensor, w_router: Tensor, top_k: int):
 def slots_for(top_i: Tensor, n_experts: int, capacity: int):
     """Flat destination index (expert * C + position) of every (token, pick); dropped picks map to the dump
     row ``E * C``.  Position = how many earlier (token-major) picks chose the same expert."""
-    T, k = top_i.shape
+    dest, keep, _ = slots_and_counts(top_i, n_experts, capacity)
+    return dest, keep
+
+
+def slots_and_counts(top_i: Tensor, n_experts: int, capacity: int):
+    """:func:`slots_for` plus ``counts`` [E] int32: how many slots of each expert this device's tokens fill."""
     flat = top_i.reshape(-1)
     onehot = torch.nn.functional.one_hot(flat, n_experts)
-    pos = (onehot.cumsum(0) - 1).gather(1, flat[:, None]).squeeze(1)
+    running = onehot.cumsum(0)
+    pos = (running - 1).gather(1, flat[:, None]).squeeze(1)
     keep = pos < capacity
     dest = torch.where(keep, flat * capacity + pos, torch.full_like(flat, n_experts * capacity))
-    return dest, keep
+    counts = running[-1].clamp(max=capacity).to(torch.int32)
+    return dest, keep, counts
 
 
 def dispatch(x: Tensor, dest: Tensor, n_experts: int, capacity: int, top_k: int) -> Tensor:
@@ -279,12 +286,14 @@ def combine(y_buf: Tensor, dest: Tensor, weights: Tensor, top_k: int) -> Tensor:
     return (picked.float() * weights.unsqueeze(-1)).sum(1).to(y_buf.dtype)
 
 
-def expert_ffn(x: Tensor, w_up: Tensor, w_down: Tensor) -> Tensor:
-    """x: [E_l, M, d]; w_up: [E_l, 2F, d] ([gate | up]); w_down: [E_l, d, F].  Every local expert sees the same
-    number of slots, so each projection is one grouped tcgen05 GEMM over all local experts."""
+def expert_ffn(x: Tensor, w_up: Tensor, w_down: Tensor, counts: Tensor | None = None, seg_rows: int = 0) -> Tensor:
+    """x: [E_l, M, d]; w_up: [E_l, 2F, d] ([gate | up]); w_down: [E_l, d, F].  Every local expert has room for the
+    same number of slots, so each projection is one grouped tcgen05 GEMM over all local experts.  ``counts``
+    [E_l, M / seg_rows] says how many slots at the start of each ``seg_rows``-slot segment are filled (the others hold
+    zeros): the GEMMs of the forward and of both gradients skip the tiles made of empty slots."""
     E_l, M, d = x.shape
-    h = ops.swiglu(ops.linear_batched(x, w_up).view(E_l * M, -1))
-    return ops.linear_batched(h.view(E_l, M, -1), w_down)
+    h = ops.swiglu(ops.linear_batched(x, w_up, counts, seg_rows).view(E_l * M, -1))
+    return ops.linear_batched(h.view(E_l, M, -1), w_down, counts, seg_rows)
 
 
 def moe_ffn(x: Tensor, p: dict, n_experts: int, top_k: int, capacity_factor: float, ep: int, ep_axis: str):
@@ -292,15 +301,22 @@ def moe_ffn(x: Tensor, p: dict, n_experts: int, top_k: int, capacity_factor: flo
     T, d = x.shape
     capacity = int(-(-T * top_k * capacity_factor // n_experts))
     capacity = (capacity + 7) // 8 * 8
+    from ..utils import config
+
     top_i, weights, aux = route(x, p["router"], top_k)
-    dest, _ = slots_for(top_i, n_experts, capacity)
+    dest, _, counts = slots_and_counts(top_i, n_experts, capacity)
+    if not config.moe_skip_empty_slots.value:
+        counts = None
     if ep > 1:
         buf = torch.ops.b200moe.dispatch_a2a(x, dest, None, n_experts, capacity, top_k, ep_axis)   # [E_l, ep*C, d]
-        y = expert_ffn(buf, p["w_up"], p["w_down"])
+        if counts is not None:
+            # every rank tells the owner of each expert how many of its C slots it filled: [ep (source), E_l] -> [E_l, ep]
+            counts = torch.ops.b200moe.all_to_all(counts.view(ep, n_experts // ep), ep_axis).t().contiguous()
+        y = expert_ffn(buf, p["w_up"], p["w_down"], counts, capacity)
         out, _ = torch.ops.b200moe.combine_a2a(y, dest, weights.reshape(-1), n_experts, capacity, top_k, ep_axis, True)
         return out, aux
     buf = dispatch(x, dest, n_experts, capacity, top_k)                        # [E, C, d]
-    y = expert_ffn(buf, p["w_up"], p["w_down"])
+    y = expert_ffn(buf, p["w_up"], p["w_down"], None if counts is None else counts.view(n_experts, 1), capacity)
     return combine(y.reshape(n_experts, capacity, d), dest, weights, top_k), aux
 
 def _register_direct_calls():

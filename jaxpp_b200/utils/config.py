@@ -165,6 +165,8 @@ zb_defer_bytes = IntEnvVar("JAXPP_B200_ZB_DEFER_BYTES", -1)
 overlap_grad_reduce = BoolEnvVar("JAXPP_B200_OVERLAP_GRAD_REDUCE", True)
 # CTAs of a peer-memory collective that runs beside compute kernels (it shares the SMs with them).
 overlap_collective_ctas = IntEnvVar("JAXPP_B200_OVERLAP_CTAS", 32)
+# Expert GEMMs of a mixture-of-experts layer skip the tiles and reduction blocks made only of unused capacity slots.
+moe_skip_empty_slots = BoolEnvVar("JAXPP_B200_MOE_SKIP_EMPTY_SLOTS", True)
 # Seconds a rank may go without a heartbeat before the watchdog reports it.
 heartbeat_timeout_s = IntEnvVar("JAXPP_B200_HEARTBEAT_TIMEOUT", 30)
 # Wrap every task in an NVTX range named like the task (fwd_3__5, …) for timeline profilers.

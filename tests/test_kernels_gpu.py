@@ -162,6 +162,49 @@ def test_grouped_gemm_equal_groups(native, E, M, N, K):
     close(native.linear_wgrad_batched(dy, x), ref_w, rtol=2e-2, atol=3e-2 * M ** 0.5)
 
 
+@pytest.mark.parametrize("E,seg,segs,N,K", [(3, 200, 2, 320, 256), (2, 384, 1, 512, 128), (4, 80, 4, 256, 64)])
+def test_grouped_gemm_unequal_groups(native, E, seg, segs, N, K):
+    """Groups of different sizes inside equal-sized storage: each group's rows are ``segs`` segments of ``seg`` rows
+    with a filled prefix (given in ``counts``) and zeros behind it.  Skipping what holds no data must not change any
+    of the three products; entirely empty groups and segments, full ones and ones that end inside a tile are covered,
+    and the output of skipped tiles must be written (zeros), not left as it was."""
+    M = seg * segs
+    if M % 64:
+        M = None
+    g = torch.Generator().manual_seed(7)
+    counts = torch.randint(0, seg + 1, (E, segs), generator=g, dtype=torch.int32)
+    counts[0, 0] = seg          # a full segment
+    counts[-1] = 0              # a group without any data
+    if E > 2:
+        counts[1, -1] = 1       # a single row
+    live = (torch.arange(seg)[None, None, :] < counts[:, :, None]).reshape(E, seg * segs, 1).cuda()
+    counts = counts.cuda()
+    rows = seg * segs
+    x = rnd(E, rows, K, seed=51) * live
+    dy = rnd(E, rows, N, seed=52) * live
+    w = rnd(E, N, K, scale=0.2, seed=53)
+    # outputs are fresh allocations: leave NaNs in the block that the caching allocator hands out next
+    junk = torch.full((E, rows, max(N, K)), float("nan"), dtype=torch.bfloat16, device="cuda")
+    del junk
+    y = native.linear_batched(x, w, counts, seg)
+    assert torch.isfinite(y.float()).all()
+    close(y, torch.bmm(x.float(), w.float().transpose(1, 2)), rtol=2e-2, atol=2e-2 * K ** 0.5 * 0.2)
+    junk = torch.full((E, rows, max(N, K)), float("nan"), dtype=torch.bfloat16, device="cuda")
+    del junk
+    dx = native.linear_dgrad_batched(dy, w, counts, seg)
+    assert torch.isfinite(dx.float()).all()
+    close(dx, torch.bmm(dy.float(), w.float()), rtol=2e-2, atol=2e-2 * N ** 0.5 * 0.2)
+    if M is not None:
+        ref_w = torch.bmm(dy.float().transpose(1, 2), x.float())
+        junk = torch.full((E, N, K), float("nan"), dtype=torch.float32, device="cuda")
+        del junk
+        dw = native.linear_wgrad_batched(dy, x, torch.float32, counts, seg)
+        assert torch.isfinite(dw).all()
+        close(dw, ref_w, rtol=2e-2, atol=2e-2 * rows ** 0.5)
+        assert dw[-1].abs().max().item() == 0.0      # the empty group's gradient is exactly zero
+        close(native.linear_wgrad_batched(dy, x, None, counts, seg), ref_w, rtol=2e-2, atol=3e-2 * rows ** 0.5)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_router_kernel(native, dtype):
     from jaxpp_b200.parallel import moe
