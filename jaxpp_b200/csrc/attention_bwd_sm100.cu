@@ -31,17 +31,6 @@ __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[W]) {
   else tmem_ld_32x16(taddr, r);
 }
 
-// W consecutive bf16 values of row `lane` -> W / 2 packed 32-bit columns of TMEM (the layout of an A operand that
-// tcgen05.mma reads from tensor memory: element k of the row in column k / 2, even k in the low half)
-template <int W>
-__device__ __forceinline__ void tmem_st_packed(uint32_t taddr, const float (&v)[W]) {
-  uint32_t w[W / 2];
-#pragma unroll
-  for (int i = 0; i < W / 2; ++i) w[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
-  if constexpr (W == 32) tmem_st_32x16(taddr, w);
-  else tmem_st_32x8(taddr, w);
-}
-
 struct AttnBwdParams {
   int B, Sq, Sk, H, Hkv;
   int causal;
@@ -50,6 +39,8 @@ struct AttnBwdParams {
   const float* delta;  // [B,H,Sq], already multiplied by the softmax scale
   __nv_bfloat16 *dq, *dk, *dv;
   int* status;
+  int stats_smem;      // Sq is a multiple of 64 and lse / delta are 16-byte aligned: the dK/dV kernel's producer copies each
+                       // query block's 64 + 64 statistics into the operand stage (else the warps load them themselves)
 };
 
 // swizzled K-major store of 8 consecutive bf16 (one 16-byte chunk `cc` of row `r`) into a [rows x 64] tile
@@ -98,17 +89,27 @@ struct DkvSmem {
   // NS stages, each: Q (DB tiles) then dO (DB tiles).  A stage is reloaded only after the MMAs that read it have
   // completed, and a TMA load takes about as long as an iteration: with two stages the loop
   // "MMA done -> load -> S -> softmax -> MMA" spanned two iterations and set the pace; more stages hide it.
-  static constexpr int NS = 4;
+  static constexpr int NS = 3;
   static constexpr int OFF_Q = OFF_V + DB * KV_TILE;
   static constexpr int STAGE = 2 * DB * Q_TILE;
-  static constexpr int OFF_P = OFF_Q + NS * STAGE;        // P^T  [128 kv x 64 q]
-  static constexpr int OFF_DS = OFF_P + 128 * 128;        // dS^T [128 kv x 64 q]
-  static constexpr int OFF_BAR = OFF_DS + 128 * 128;
+  // P^T and dS^T, [128 kv x 64 q] bf16 each, in two buffers used by alternate iterations: the warps write the pair of
+  // iteration g while the tensor core still reads that of g-1, so the completion of those products (and the two
+  // barrier hops around it) is off the loop's critical path
+  static constexpr int PD_BYTES = 2 * 128 * 128;
+  static constexpr int OFF_P = OFF_Q + NS * STAGE;        // buffer i: P^T at OFF_P + i * PD_BYTES, dS^T 16 KiB behind it
+  static constexpr int OFF_STAT = OFF_P + 2 * PD_BYTES;   // per stage: lse * log2(e) and delta * scale of the 64 query rows
+  static constexpr int STAT_BYTES = 2 * 64 * 4;
+  static constexpr int OFF_BAR = OFF_STAT + NS * STAT_BYTES;
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
 };
 
-constexpr int BWD_NS = 4;  // stages of the streamed operand in both kernels
-enum { K1_KV = 0, K1_KVE = 1, K1_QF = 2, K1_QE = K1_QF + BWD_NS, K1_SF = K1_QE + BWD_NS, K1_SFREE, K1_PF, K1_PE, K1_N };
+// Stages of the streamed operand.  The dK/dV kernel gives one of its four to a second pair of P^T / dS^T buffers.
+constexpr int DKV_NS = 3, DQ_NS = 4;
+// S^T / dP^T live in two TMEM buffers (K1_SF / K1_SFREE come in pairs, indexed by the parity of the iteration): the
+// tensor core computes the pair of iteration g+2 while the warps work on g and g+1, so that the round trip
+// "S loaded -> next S issued -> S done" is off the loop's critical path.
+enum { K1_KV = 0, K1_KVE = 1, K1_QF = 2, K1_QE = K1_QF + DKV_NS, K1_SF = K1_QE + DKV_NS, K1_SFREE = K1_SF + 2, K1_PF = K1_SFREE + 2,
+       K1_PE = K1_PF + 2, K1_N = K1_PE + 2 };
 
 // Work distribution of the persistent dK/dV kernel.  A work item is a pair of kv blocks (j, n_kvb-1-j) of one
 // (batch, kv head): under a causal mask the two together see the same number of query blocks whatever j is, so
@@ -134,9 +135,7 @@ struct DkvTiles {
   }
 };
 
-// PT: P^T and dS^T go back to tensor memory as packed bf16 and the dV / dK products take their A operand from there,
-// instead of through shared memory (see the forward kernel).
-template <int D, int NG, bool PT>
+template <int D, int NG>
 __global__ void __launch_bounds__(bwd_threads(NG), 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                      const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -159,11 +158,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   if (threadIdx.x == 0) {
     mbar_init(&bar[K1_KV], 1);
     mbar_init(&bar[K1_KVE], 1);
-    for (int s = 0; s < BWD_NS; ++s) { mbar_init(&bar[K1_QF + s], 1); mbar_init(&bar[K1_QE + s], 1); }
-    mbar_init(&bar[K1_SF], 1);
-    mbar_init(&bar[K1_SFREE], 4 * NG);
-    mbar_init(&bar[K1_PF], 4 * NG);
-    mbar_init(&bar[K1_PE], 1);
+    for (int s = 0; s < DKV_NS; ++s) { mbar_init(&bar[K1_QF + s], 1); mbar_init(&bar[K1_QE + s], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&bar[K1_SF + i], 1); mbar_init(&bar[K1_SFREE + i], 4 * NG); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&bar[K1_PF + i], 4 * NG); mbar_init(&bar[K1_PE + i], 1); }
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_do); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v);
@@ -173,8 +170,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t t_s = tmem_base, t_dp = tmem_base + 64, t_dv = tmem_base + 128, t_dk = tmem_base + 128 + D;
-  const uint32_t t_p = tmem_base + 384, t_ds = tmem_base + 416;   // PT: [128 kv x 64 q] bf16 = 32 columns each
+  // columns: [S^T 64 | dP^T 64] x 2 buffers, then dV (D) and dK (D)
+  const uint32_t t_dv = tmem_base + 256, t_dk = tmem_base + 256 + D;
 
   // Every role walks the same tiles in the same order.  `g` counts the (kv block, q block) iterations of this
   // CTA over all its tiles and `tile_i` its non-empty tiles: the barrier phases follow these two counters, so the
@@ -202,12 +199,17 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           tma_load_4d(smem + L::OFF_V + d * L::KV_TILE, &map_v, &bar[K1_KV], d * 64, hk, jb * 128, b);
         }
         for (int t = 0; t < n_iter && ok; ++t, ++g) {
-          const int s = g % BWD_NS;
-          const uint32_t ph = (g / BWD_NS) & 1;
+          const int s = g % DKV_NS;
+          const uint32_t ph = (g / DKV_NS) & 1;
           const int h = hk * G + t / per_head;
           const int q0 = (i_start + t % per_head) * 64;
           if (!mbar_wait_bounded(&bar[K1_QE + s], ph ^ 1, abort_flag, p.status)) { ok = false; break; }
-          arm(K1_QF + s, ph, L::STAGE);
+          arm(K1_QF + s, ph, L::STAGE + (p.stats_smem ? L::STAT_BYTES : 0));
+          if (p.stats_smem) {
+            const size_t row = (size_t(b) * p.H + h) * p.Sq + q0;
+            bulk_load_1d(smem + L::OFF_STAT + s * L::STAT_BYTES, p.lse + row, 256, &bar[K1_QF + s]);
+            bulk_load_1d(smem + L::OFF_STAT + s * L::STAT_BYTES + 256, p.delta + row, 256, &bar[K1_QF + s]);
+          }
           uint8_t* st = smem + L::OFF_Q + s * L::STAGE;
 #pragma unroll
           for (int d = 0; d < L::DB; ++d) {
@@ -230,29 +232,36 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);   // [kv x q] = K-major x K-major
       constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);  // [kv x d] = K-major(P^T) x MN-major(dO / Q)
-      const uint32_t sk = smem_u32(smem + L::OFF_K), sv = smem_u32(smem + L::OFF_V);
-      const uint32_t sp = smem_u32(smem + L::OFF_P), sds = smem_u32(smem + L::OFF_DS);
+      // descriptor words that do not change from one MMA to the next are computed here, once (see SmemDesc)
+      const SmemDesc dk_ = make_smem_desc2(smem_u32(smem + L::OFF_K), 16, 1024);    // K, V, Q, dO, P^T, dS^T as K-major operands
+      const SmemDesc dv_ = make_smem_desc2(smem_u32(smem + L::OFF_V), 16, 1024);
+      const SmemDesc dq_ = make_smem_desc2(smem_u32(smem + L::OFF_Q), 16, 1024);
+      const SmemDesc dp_ = make_smem_desc2(smem_u32(smem + L::OFF_P), 16, 1024);
+      const SmemDesc dqm_ = make_smem_desc2(smem_u32(smem + L::OFF_Q), L::Q_TILE, 1024);   // Q / dO as MN-major operands
+      constexpr uint32_t STAGE16 = L::STAGE >> 4, DO16 = (L::DB * L::Q_TILE) >> 4, PD16 = L::PD_BYTES >> 4, DS16 = (128 * 128) >> 4;
       bool ok = true;
       auto issue_s = [&](uint32_t gg) -> bool {
-        const int s = gg % BWD_NS;
-        if (!mbar_wait_bounded(&bar[K1_QF + s], (gg / BWD_NS) & 1, abort_flag, p.status)) return false;
-        if (gg > 0 && !mbar_wait_bounded(&bar[K1_SFREE], (gg - 1) & 1, abort_flag, p.status)) return false;
+        const int s = gg % DKV_NS;
+        const uint32_t bf = gg & 1;
+        if (!mbar_wait_bounded(&bar[K1_QF + s], (gg / DKV_NS) & 1, abort_flag, p.status)) return false;
+        // the buffer's previous content (iteration gg - 2) has been read into registers
+        if (gg > 1 && !mbar_wait_bounded(&bar[K1_SFREE + bf], ((gg >> 1) - 1) & 1, abort_flag, p.status)) return false;
         tc_fence_after();
-        const uint32_t sq = smem_u32(smem + L::OFF_Q + s * L::STAGE);
-        const uint32_t sdo = sq + L::DB * L::Q_TILE;
+        const uint32_t t_s = tmem_base + bf * 128, t_dp = t_s + 64;
+        const uint32_t q_lo = dq_.lo + s * STAGE16, do_lo = q_lo + DO16;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t a_off = (k >> 2) * L::KV_TILE + (k & 3) * 32;
-          const uint32_t b_off = (k >> 2) * L::Q_TILE + (k & 3) * 32;
-          umma_bf16_ss(t_s, make_smem_desc(sk + a_off, 16, 1024), make_smem_desc(sq + b_off, 16, 1024), idesc_s, k != 0);
+          const uint32_t a_off = ((k >> 2) * L::KV_TILE + (k & 3) * 32) >> 4;
+          const uint32_t b_off = ((k >> 2) * L::Q_TILE + (k & 3) * 32) >> 4;
+          umma_bf16_ss2(t_s, dk_.lo + a_off, dk_.hi, q_lo + b_off, dq_.hi, idesc_s, k != 0);
         }
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t a_off = (k >> 2) * L::KV_TILE + (k & 3) * 32;
-          const uint32_t b_off = (k >> 2) * L::Q_TILE + (k & 3) * 32;
-          umma_bf16_ss(t_dp, make_smem_desc(sv + a_off, 16, 1024), make_smem_desc(sdo + b_off, 16, 1024), idesc_s, k != 0);
+          const uint32_t a_off = ((k >> 2) * L::KV_TILE + (k & 3) * 32) >> 4;
+          const uint32_t b_off = ((k >> 2) * L::Q_TILE + (k & 3) * 32) >> 4;
+          umma_bf16_ss2(t_dp, dv_.lo + a_off, dv_.hi, do_lo + b_off, dq_.hi, idesc_s, k != 0);
         }
-        umma_commit(&bar[K1_SF]);
+        umma_commit(&bar[K1_SF + bf]);
         return true;
       };
       uint32_t g = 0, tile_i = 0;
@@ -261,36 +270,36 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const int n_iter = per_head * G;
         if (n_iter <= 0) continue;
         if (!mbar_wait_bounded(&bar[K1_KV], tile_i & 1, abort_flag, p.status)) { ok = false; break; }
-        if (!issue_s(g)) { ok = false; break; }
-        if (n_iter == 1) umma_commit(&bar[K1_KVE]);
+        // S^T / dP^T run two iterations ahead of the products that consume P^T / dS^T
+        const uint32_t g0 = g;
+        int issued = 0;
+        auto issue_next = [&]() -> bool {
+          if (issued == n_iter) return true;
+          if (!issue_s(g0 + issued)) return false;
+          if (++issued == n_iter) umma_commit(&bar[K1_KVE]);  // the last S / dP of this tile: K and V may be replaced
+          return true;
+        };
+        if (!issue_next() || !issue_next()) { ok = false; break; }
         for (int t = 0; t < n_iter && ok; ++t, ++g) {
-          if (t + 1 < n_iter) {
-            if (!issue_s(g + 1)) { ok = false; break; }
-            if (t + 2 == n_iter) umma_commit(&bar[K1_KVE]);  // the last S / dP of this tile: K and V may be replaced
-          }
-          const int s = g % BWD_NS;
-          if (!mbar_wait_bounded(&bar[K1_PF], g & 1, abort_flag, p.status)) { ok = false; break; }
+          const int s = g % DKV_NS;
+          const uint32_t pb = g & 1;
+          if (!mbar_wait_bounded(&bar[K1_PF + pb], (g >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sq = smem_u32(smem + L::OFF_Q + s * L::STAGE);
-          const uint32_t sdo = sq + L::DB * L::Q_TILE;
+          const uint32_t p_lo = dp_.lo + pb * PD16, ds_lo = p_lo + DS16;
+          const uint32_t qm_lo = dqm_.lo + s * STAGE16, dom_lo = qm_lo + DO16;
+          const uint32_t acc = t != 0;
 #pragma unroll
-          for (int kk = 0; kk < 64 / 16; ++kk) {  // reduction over the 64 query rows
-            if constexpr (PT)
-              umma_bf16_ts(t_dv, t_p + kk * 8, make_smem_desc(sdo + kk * 2048, L::Q_TILE, 1024), idesc_acc, (t | kk) != 0);
-            else
-              umma_bf16_ss(t_dv, make_smem_desc(sp + kk * 32, 16, 1024), make_smem_desc(sdo + kk * 2048, L::Q_TILE, 1024),
-                           idesc_acc, (t | kk) != 0);
-          }
+          for (int kk = 0; kk < 64 / 16; ++kk)  // reduction over the 64 query rows
+            umma_bf16_ss2(t_dv, p_lo + kk * 2, dp_.hi, dom_lo + kk * 128, dqm_.hi, idesc_acc, kk ? 1u : acc);
 #pragma unroll
-          for (int kk = 0; kk < 64 / 16; ++kk) {
-            if constexpr (PT)
-              umma_bf16_ts(t_dk, t_ds + kk * 8, make_smem_desc(sq + kk * 2048, L::Q_TILE, 1024), idesc_acc, (t | kk) != 0);
-            else
-              umma_bf16_ss(t_dk, make_smem_desc(sds + kk * 32, 16, 1024), make_smem_desc(sq + kk * 2048, L::Q_TILE, 1024),
-                           idesc_acc, (t | kk) != 0);
-          }
+          for (int kk = 0; kk < 64 / 16; ++kk)
+            umma_bf16_ss2(t_dk, ds_lo + kk * 2, dp_.hi, qm_lo + kk * 128, dqm_.hi, idesc_acc, kk ? 1u : acc);
           umma_commit(&bar[K1_QE + s]);
-          umma_commit(&bar[K1_PE]);
+          umma_commit(&bar[K1_PE + pb]);
+          // S^T / dP^T of iteration t + 2 (their buffer was read at the start of iteration t).  Issued after the
+          // products above: with three operand stages its Q / dO may still be on their way, and a wait for them here
+          // delays nothing that the warps need before iteration t + 2.
+          if (!issue_next()) { ok = false; break; }
         }
         ++tile_i;
       }
@@ -334,7 +343,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         // tile-level test (warp-uniform): is every (kv row, query column) of this warp group's 128 x CW block visible?
         const bool full = q0 + CW - 1 < p.Sq && kv0 + 127 < p.Sk && (!p.causal || kv0 + 127 <= q0 + off) && (p.Sq & 3) == 0;
         float lq[CW], dl[CW];
-        if (full) {
+        if (p.stats_smem) {
+          // they come with the operand stage (read below, once S^T is there: that they have landed follows from it)
+        } else if (full) {
           const float4* l4 = reinterpret_cast<const float4*>(lse_q + q0);
           const float4* d4 = reinterpret_cast<const float4*>(dl_q + q0);
 #pragma unroll
@@ -351,20 +362,41 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             dl[i] = in ? __ldg(dl_q + q0 + i) : 0.f;
           }
         }
-        if (!mbar_wait_bounded_warp(&bar[K1_SF], g & 1, abort_flag, p.status)) { ok = false; break; }
+        // the statistics of the next iteration's columns: pull their lines into L1 now, so that the loads above hit it
+        // then (they sit on the loop's critical path: nothing else waits between two iterations of these warps)
+        if (!p.stats_smem && t + 1 < n_iter && lane < 4) {
+          const int hn = hk * G + (t + 1) / per_head;
+          const int qn = (i_start + (t + 1) % per_head) * 64;
+          if (qn + 64 <= p.Sq) {
+            const float* base = ((lane & 2) ? p.delta : p.lse) + (size_t(b) * p.H + hn) * p.Sq + qn + (lane & 1) * 32;
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(base));
+          }
+        }
+        const uint32_t bf = g & 1;
+        if (!mbar_wait_bounded_warp(&bar[K1_SF + bf], (g >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
         float sv[CW], dp[CW];
         {
           uint32_t a[CW], d2[CW];
-          tmem_ld_cols<CW>(t_s + lane_addr + cb, a);
-          tmem_ld_cols<CW>(t_dp + lane_addr + cb, d2);
+          tmem_ld_cols<CW>(tmem_base + bf * 128 + lane_addr + cb, a);
+          tmem_ld_cols<CW>(tmem_base + bf * 128 + 64 + lane_addr + cb, d2);
           tc_wait_ld();
 #pragma unroll
           for (int i = 0; i < CW; ++i) { sv[i] = __uint_as_float(a[i]); dp[i] = __uint_as_float(d2[i]); }
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bar[K1_SFREE]);
+        if (lane == 0) mbar_arrive(&bar[K1_SFREE + bf]);
+        if (p.stats_smem) {
+          // same address in every lane: one broadcast read per four values
+          const float4* st4 = reinterpret_cast<const float4*>(smem + L::OFF_STAT + (g % DKV_NS) * L::STAT_BYTES) + cb / 4;
+#pragma unroll
+          for (int i = 0; i < CW / 4; ++i) {
+            const float4 a = st4[i], c = st4[16 + i];
+            lq[4 * i] = a.x; lq[4 * i + 1] = a.y; lq[4 * i + 2] = a.z; lq[4 * i + 3] = a.w;
+            dl[4 * i] = c.x; dl[4 * i + 1] = c.y; dl[4 * i + 2] = c.z; dl[4 * i + 3] = c.w;
+          }
+        }
         if (full) {
 #pragma unroll
           for (int i = 0; i < CW; ++i) {
@@ -386,16 +418,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             dp[i] = ds;
           }
         }
-        if (g > 0) {  // P^T / dS^T of the previous iteration (possibly of the previous tile) have been consumed
-          if (!mbar_wait_bounded_warp(&bar[K1_PE], (g - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+        if (g > 1) {  // this buffer's previous content (iteration g - 2, possibly of the previous tile) has been consumed
+          if (!mbar_wait_bounded_warp(&bar[K1_PE + bf], ((g >> 1) - 1) & 1, abort_flag, p.status)) { ok = false; break; }
         }
-        if constexpr (PT) {
-          tmem_st_packed<CW>(t_p + lane_addr + cb / 2, sv);
-          tmem_st_packed<CW>(t_ds + lane_addr + cb / 2, dp);
-          tc_wait_st();
-        } else {
-          uint8_t* tp = smem + L::OFF_P;
-          uint8_t* tds = smem + L::OFF_DS;
+        {
+          uint8_t* tp = smem + L::OFF_P + bf * L::PD_BYTES;
+          uint8_t* tds = tp + 128 * 128;
 #pragma unroll
           for (int c = 0; c < CW / 8; ++c) {
             uint4 v, w;
@@ -410,12 +438,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bar[K1_PF]);
+        if (lane == 0) mbar_arrive(&bar[K1_PF + bf]);
       }
       if (!ok) break;
       // dK / dV of this tile: the accumulators are complete when the last iteration's MMAs are.  The next tile's
       // first accumulating MMA is issued only after these warps hand over its P^T / dS^T, i.e. after this read.
-      if (!mbar_wait_bounded_warp(&bar[K1_PE], (g - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+      if (!mbar_wait_bounded_warp(&bar[K1_PE + ((g - 1) & 1)], ((g - 1) >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
       tc_fence_after();
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
@@ -458,14 +486,15 @@ struct DqSmem {
   static constexpr int KV_TILE = 64 * 128;   // [64 kv x 64 d]
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_DO = OFF_Q + DB * Q_TILE;
-  static constexpr int OFF_KV = OFF_DO + DB * Q_TILE;   // BWD_NS stages, each: K (DB tiles) then V (DB tiles)
+  static constexpr int OFF_KV = OFF_DO + DB * Q_TILE;   // DQ_NS stages, each: K (DB tiles) then V (DB tiles)
   static constexpr int STAGE = 2 * DB * KV_TILE;
-  static constexpr int OFF_DS = OFF_KV + 4 * STAGE;     // dS [128 q x 64 kv]
-  static constexpr int OFF_BAR = OFF_DS + 128 * 128;
+  static constexpr int OFF_DS = OFF_KV + 4 * STAGE;     // dS [128 q x 64 kv], two buffers used by alternate iterations
+  static constexpr int OFF_BAR = OFF_DS + 2 * 128 * 128;
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
 };
 
-enum { K2_Q = 0, K2_QFREE = 1, K2_KF = 2, K2_KE = K2_KF + BWD_NS, K2_SF = K2_KE + BWD_NS, K2_SFREE, K2_DF, K2_DE, K2_N };
+enum { K2_Q = 0, K2_QFREE = 1, K2_KF = 2, K2_KE = K2_KF + DQ_NS, K2_SF = K2_KE + DQ_NS, K2_SFREE = K2_SF + 2, K2_DF = K2_SFREE + 2,
+       K2_DE = K2_DF + 2, K2_N = K2_DE + 2 };
 
 // Work distribution of the persistent dQ kernel: an item is a pair of query blocks (i, num_m-1-i) of one
 // (batch, head); under a causal mask the two together see the same number of kv blocks whatever i is.
@@ -489,7 +518,7 @@ struct DqTiles {
   }
 };
 
-template <int D, int NG, bool PT>
+template <int D, int NG>
 __global__ void __launch_bounds__(bwd_threads(NG), 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -512,11 +541,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   if (threadIdx.x == 0) {
     mbar_init(&bar[K2_Q], 1);
     mbar_init(&bar[K2_QFREE], 1);
-    for (int s = 0; s < BWD_NS; ++s) { mbar_init(&bar[K2_KF + s], 1); mbar_init(&bar[K2_KE + s], 1); }
-    mbar_init(&bar[K2_SF], 1);
-    mbar_init(&bar[K2_SFREE], 4 * NG);
-    mbar_init(&bar[K2_DF], 4 * NG);
-    mbar_init(&bar[K2_DE], 1);
+    for (int s = 0; s < DQ_NS; ++s) { mbar_init(&bar[K2_KF + s], 1); mbar_init(&bar[K2_KE + s], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&bar[K2_SF + i], 1); mbar_init(&bar[K2_SFREE + i], 4 * NG); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&bar[K2_DF + i], 4 * NG); mbar_init(&bar[K2_DE + i], 1); }
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_do); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v);
@@ -526,8 +553,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t t_s = tmem_base, t_dp = tmem_base + 64, t_dq = tmem_base + 128;
-  const uint32_t t_ds = tmem_base + 256;   // PT: dS [128 q x 64 kv] as packed bf16, 32 columns
+  const uint32_t t_dq = tmem_base + 256;   // after the two [S 64 | dP 64] buffers
 
   // As in the dK/dV kernel: every role walks the same tiles; `g` counts this CTA's (q block, kv block) iterations
   // over all its tiles and `tile_i` its tiles, and the barrier phases follow those two counters.
@@ -554,8 +580,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           tma_load_4d(smem + L::OFF_DO + d * L::Q_TILE, &map_do, &bar[K2_Q], d * 64, h, m_blk * 128, b);
         }
         for (int t = 0; t < n_iter && ok; ++t, ++g) {
-          const int s = g % BWD_NS;
-          const uint32_t ph = (g / BWD_NS) & 1;
+          const int s = g % DQ_NS;
+          const uint32_t ph = (g / DQ_NS) & 1;
           if (!mbar_wait_bounded(&bar[K2_KE + s], ph ^ 1, abort_flag, p.status)) { ok = false; break; }
           arm(K2_KF + s, ph, L::STAGE);
           uint8_t* st = smem + L::OFF_KV + s * L::STAGE;
@@ -581,13 +607,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);   // [q x kv]
       constexpr uint32_t idesc_dq = make_idesc_bf16(128, D, 0, 1);   // [q x d] = K-major(dS) x MN-major(K)
       const uint32_t sq = smem_u32(smem + L::OFF_Q), sdo = smem_u32(smem + L::OFF_DO);
-      const uint32_t sds = smem_u32(smem + L::OFF_DS);
+      const uint32_t sds0 = smem_u32(smem + L::OFF_DS);
       bool ok = true;
       auto issue_s = [&](uint32_t gg) -> bool {
-        const int s = gg % BWD_NS;
-        if (!mbar_wait_bounded(&bar[K2_KF + s], (gg / BWD_NS) & 1, abort_flag, p.status)) return false;
-        if (gg > 0 && !mbar_wait_bounded(&bar[K2_SFREE], (gg - 1) & 1, abort_flag, p.status)) return false;
+        const int s = gg % DQ_NS;
+        const uint32_t bf = gg & 1;
+        if (!mbar_wait_bounded(&bar[K2_KF + s], (gg / DQ_NS) & 1, abort_flag, p.status)) return false;
+        if (gg > 1 && !mbar_wait_bounded(&bar[K2_SFREE + bf], ((gg >> 1) - 1) & 1, abort_flag, p.status)) return false;
         tc_fence_after();
+        const uint32_t t_s = tmem_base + bf * 128, t_dp = t_s + 64;
         const uint32_t sk = smem_u32(smem + L::OFF_KV + s * L::STAGE);
         const uint32_t sv = sk + L::DB * L::KV_TILE;
 #pragma unroll
@@ -602,7 +630,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           const uint32_t b_off = (k >> 2) * L::KV_TILE + (k & 3) * 32;
           umma_bf16_ss(t_dp, make_smem_desc(sdo + a_off, 16, 1024), make_smem_desc(sv + b_off, 16, 1024), idesc_s, k != 0);
         }
-        umma_commit(&bar[K2_SF]);
+        umma_commit(&bar[K2_SF + bf]);
         return true;
       };
       uint32_t g = 0, tile_i = 0;
@@ -610,27 +638,30 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       for (int k = 0; ok && tiles.get(k, m_blk, h, b, n_iter); ++k) {
         if (n_iter <= 0) continue;
         if (!mbar_wait_bounded(&bar[K2_Q], tile_i & 1, abort_flag, p.status)) { ok = false; break; }
-        if (!issue_s(g)) { ok = false; break; }
-        if (n_iter == 1) umma_commit(&bar[K2_QFREE]);
+        // S / dP run two iterations ahead of the product that consumes dS
+        const uint32_t g0 = g;
+        int issued = 0;
+        auto issue_next = [&]() -> bool {
+          if (issued == n_iter) return true;
+          if (!issue_s(g0 + issued)) return false;
+          if (++issued == n_iter) umma_commit(&bar[K2_QFREE]);  // the last S / dP of this tile: Q and dO may be replaced
+          return true;
+        };
+        if (!issue_next() || !issue_next()) { ok = false; break; }
         for (int t = 0; t < n_iter && ok; ++t, ++g) {
-          if (t + 1 < n_iter) {
-            if (!issue_s(g + 1)) { ok = false; break; }
-            if (t + 2 == n_iter) umma_commit(&bar[K2_QFREE]);  // the last S / dP of this tile: Q and dO may be replaced
-          }
-          const int s = g % BWD_NS;
-          if (!mbar_wait_bounded(&bar[K2_DF], g & 1, abort_flag, p.status)) { ok = false; break; }
+          if (!issue_next()) { ok = false; break; }   // iteration t + 2: its buffer was read at the start of iteration t
+          const int s = g % DQ_NS;
+          const uint32_t pb = g & 1;
+          if (!mbar_wait_bounded(&bar[K2_DF + pb], (g >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
           tc_fence_after();
+          const uint32_t sds = sds0 + pb * 128 * 128;
           const uint32_t sk = smem_u32(smem + L::OFF_KV + s * L::STAGE);
 #pragma unroll
-          for (int kk = 0; kk < 64 / 16; ++kk) {  // reduction over the 64 kv rows
-            if constexpr (PT)
-              umma_bf16_ts(t_dq, t_ds + kk * 8, make_smem_desc(sk + kk * 2048, L::KV_TILE, 1024), idesc_dq, (t | kk) != 0);
-            else
-              umma_bf16_ss(t_dq, make_smem_desc(sds + kk * 32, 16, 1024), make_smem_desc(sk + kk * 2048, L::KV_TILE, 1024),
-                           idesc_dq, (t | kk) != 0);
-          }
+          for (int kk = 0; kk < 64 / 16; ++kk)  // reduction over the 64 kv rows
+            umma_bf16_ss(t_dq, make_smem_desc(sds + kk * 32, 16, 1024), make_smem_desc(sk + kk * 2048, L::KV_TILE, 1024),
+                         idesc_dq, (t | kk) != 0);
           umma_commit(&bar[K2_KE + s]);
-          umma_commit(&bar[K2_DE]);
+          umma_commit(&bar[K2_DE + pb]);
         }
         ++tile_i;
       }
@@ -656,20 +687,21 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const float lse_r = row_ok ? p.lse[(size_t(b) * p.H + h) * p.Sq + qi] : 0.f;
       const float dl_r = row_ok ? p.delta[(size_t(b) * p.H + h) * p.Sq + qi] : 0.f;
       for (int t = 0; t < n_iter && ok; ++t, ++g) {
-        if (!mbar_wait_bounded_warp(&bar[K2_SF], g & 1, abort_flag, p.status)) { ok = false; break; }
+        const uint32_t bf = g & 1;
+        if (!mbar_wait_bounded_warp(&bar[K2_SF + bf], (g >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
         float sv[CW], dp[CW];
         {
           uint32_t a[CW], d2[CW];
-          tmem_ld_cols<CW>(t_s + lane_addr + cb, a);
-          tmem_ld_cols<CW>(t_dp + lane_addr + cb, d2);
+          tmem_ld_cols<CW>(tmem_base + bf * 128 + lane_addr + cb, a);
+          tmem_ld_cols<CW>(tmem_base + bf * 128 + 64 + lane_addr + cb, d2);
           tc_wait_ld();
 #pragma unroll
           for (int i = 0; i < CW; ++i) { sv[i] = __uint_as_float(a[i]); dp[i] = __uint_as_float(d2[i]); }
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bar[K2_SFREE]);
+        if (lane == 0) mbar_arrive(&bar[K2_SFREE + bf]);
         // warp-uniform: every (query row, kv column) of this warp group's 128 x CW block visible?
         const int kv_first = t * 64 + cb;
         const bool full = m0 + 127 < p.Sq && kv_first + CW - 1 < p.Sk && (!p.causal || kv_first + CW - 1 <= m0 + off);
@@ -692,14 +724,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             dp[i] = ds;
           }
         }
-        if (g > 0) {  // dS of the previous iteration (possibly of the previous tile) has been consumed
-          if (!mbar_wait_bounded_warp(&bar[K2_DE], (g - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+        if (g > 1) {  // this buffer's previous content (iteration g - 2, possibly of the previous tile) has been consumed
+          if (!mbar_wait_bounded_warp(&bar[K2_DE + bf], ((g >> 1) - 1) & 1, abort_flag, p.status)) { ok = false; break; }
         }
-        if constexpr (PT) {
-          tmem_st_packed<CW>(t_ds + lane_addr + cb / 2, dp);
-          tc_wait_st();
-        } else {
-          uint8_t* tds = smem + L::OFF_DS;
+        {
+          uint8_t* tds = smem + L::OFF_DS + bf * 128 * 128;
 #pragma unroll
           for (int c = 0; c < CW / 8; ++c) {
             uint4 w;
@@ -711,12 +740,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bar[K2_DF]);
+        if (lane == 0) mbar_arrive(&bar[K2_DF + bf]);
       }
       if (!ok) break;
       // dQ of this tile; the next tile's first accumulating MMA needs a dS hand-over from these warps, which comes
       // after this read of the accumulator
-      if (!mbar_wait_bounded_warp(&bar[K2_DE], (g - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+      if (!mbar_wait_bounded_warp(&bar[K2_DE + ((g - 1) & 1)], ((g - 1) >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
       tc_fence_after();
       __nv_bfloat16* dst = p.dq + ((size_t(b) * p.Sq + qi) * p.H + h) * D;
 #pragma unroll
@@ -763,16 +792,7 @@ static int bwd_groups() {
   return ng;
 }
 
-static int bwd_p_tmem() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("JAXPP_B200_ATTN_P_TMEM");
-    v = (e && e[0] == '1') ? 1 : 0;
-  }
-  return v;
-}
-
-template <int D, int NG, bool PT>
+template <int D, int NG>
 static int launch_bwd(const void* dO, const void* q, const void* k, const void* v, const AttnBwdParams& p, cudaStream_t stream) {
   CUtensorMap mq64, mdo64, mk128, mv128, mq128, mdo128, mk64, mv64;
   int rc = 0;
@@ -785,8 +805,8 @@ static int launch_bwd(const void* dO, const void* q, const void* k, const void* 
   rc |= make_map_rows(&mk64, k, p.B, p.Sk, p.Hkv, D, 64);
   rc |= make_map_rows(&mv64, v, p.B, p.Sk, p.Hkv, D, 64);
   if (rc) return rc;
-  auto k1 = attn_bwd_dkdv_kernel<D, NG, PT>;
-  auto k2 = attn_bwd_dq_kernel<D, NG, PT>;
+  auto k1 = attn_bwd_dkdv_kernel<D, NG>;
+  auto k2 = attn_bwd_dq_kernel<D, NG>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvSmem<D>::TOTAL) != cudaSuccess) return -3;
@@ -837,11 +857,7 @@ JPB_API int jpb_attention_bwd(const void* dO, const void* q, const void* k, cons
   p.lse = lse2; p.delta = delta;
   p.dq = static_cast<__nv_bfloat16*>(dq); p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
   p.status = jpb_status_device_ptr();
-  const bool pt = bwd_p_tmem() != 0;
-  if (bwd_groups() == 2) {
-    if (pt) return D == 128 ? launch_bwd<128, 2, true>(dO, q, k, v, p, s) : launch_bwd<64, 2, true>(dO, q, k, v, p, s);
-    return D == 128 ? launch_bwd<128, 2, false>(dO, q, k, v, p, s) : launch_bwd<64, 2, false>(dO, q, k, v, p, s);
-  }
-  if (pt) return D == 128 ? launch_bwd<128, 4, true>(dO, q, k, v, p, s) : launch_bwd<64, 4, true>(dO, q, k, v, p, s);
-  return D == 128 ? launch_bwd<128, 4, false>(dO, q, k, v, p, s) : launch_bwd<64, 4, false>(dO, q, k, v, p, s);
+  p.stats_smem = (Sq % 64 == 0 && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0) ? 1 : 0;
+  if (bwd_groups() == 2) return D == 128 ? launch_bwd<128, 2>(dO, q, k, v, p, s) : launch_bwd<64, 2>(dO, q, k, v, p, s);
+  return D == 128 ? launch_bwd<128, 4>(dO, q, k, v, p, s) : launch_bwd<64, 4>(dO, q, k, v, p, s);
 }

@@ -48,11 +48,16 @@ struct AttnSmem {
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
 };
 
-enum { BAR_Q = 0, BAR_KF = 1, BAR_VF = 3, BAR_KE = 5, BAR_VE = 7, BAR_SF = 9, BAR_SE = 11, BAR_PF = 13, BAR_PV = 14, BAR_MX = 15, BAR_N = 16 };
+// BAR_PF / BAR_PV come in pairs indexed by the parity of the kv block (two P buffers in tensor memory)
+enum { BAR_Q = 0, BAR_KF = 1, BAR_VF = 3, BAR_KE = 5, BAR_VE = 7, BAR_SF = 9, BAR_SE = 11, BAR_PF = 13, BAR_PV = 15, BAR_MX = 17, BAR_N = 18 };
 
 // PT: the probabilities go back to tensor memory (bf16, two per 32-bit column) and P V takes its A operand from
 // there, instead of a round trip through shared memory (a 32 KiB store, a proxy fence and a 32 KiB operand read per
-// block less on the shared-memory port, which the operand fetches of the MMAs already keep busy).
+// block less on the shared-memory port, which the operand fetches of the MMAs already keep busy).  There are two such
+// P buffers, used by alternate blocks: the warps write P of block j while the tensor core may still be reading P of
+// block j-1, so "P handed over -> P V issued -> P V complete" (two barrier hops and the product itself, about as long
+// as everything else in an iteration) leaves the loop's critical path; the warps wait for P V of the previous block
+// only in the few iterations that rescale O.
 template <int D, int NG, bool PT>
 __global__ void __launch_bounds__(att_threads(NG), 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -87,8 +92,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       mbar_init(&bar[BAR_SF + s], 1);
       mbar_init(&bar[BAR_SE + s], 4 * NG);
     }
-    mbar_init(&bar[BAR_PF], 4 * NG);
-    mbar_init(&bar[BAR_PV], 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&bar[BAR_PF + s], 4 * NG); mbar_init(&bar[BAR_PV + s], 1); }
     mbar_init(&bar[BAR_MX], 4 * NG);   // all softmax warps meet here once per block (and once at the end)
     *abort_flag = 0;
     fence_barrier_init();
@@ -105,7 +109,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_o = tmem_base + 256;
-  const uint32_t tmem_p = tmem_base + 384;   // PT: P as packed bf16, 64 columns
+  const uint32_t tmem_p = tmem_base + 384;   // PT: P as packed bf16, two buffers of 64 columns
 
   if (warp == 0) {
     if (lane == 0) {
@@ -186,7 +190,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       for (int j = 0; j < n_blocks && ok; ++j) {
         if (j + 1 < n_blocks && !issue_s(j + 1)) { ok = false; break; }
         const int s = j & 1;
-        if (!mbar_wait_bounded(&bar[BAR_PF], j & 1, abort_flag, p.status)) { ok = false; break; }
+        if (!mbar_wait_bounded(&bar[BAR_PF + s], (j >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
         if (!mbar_wait_bounded(&bar[BAR_VF + s], (j >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sv = smem_u32(smem + L::OFF_V + s * L::KV_BYTES);
@@ -195,14 +199,14 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           // A = P: K-major, two 64-wide kv blocks; B = V: MN-major, 16 kv rows per step, 64-wide d blocks
           const uint64_t db = make_smem_desc(sv + k * 2048, L::TILE, 1024);
           if constexpr (PT) {
-            umma_bf16_ts(tmem_o, tmem_p + k * 8, db, idesc_pv, (j | k) != 0);   // 16 kv = 8 packed columns per step
+            umma_bf16_ts(tmem_o, tmem_p + s * 64 + k * 8, db, idesc_pv, (j | k) != 0);   // 16 kv = 8 packed columns per step
           } else {
             const uint64_t da = make_smem_desc(sp + (k >> 2) * L::TILE + (k & 3) * 32, 16, 1024);
             umma_bf16_ss(tmem_o, da, db, idesc_pv, (j | k) != 0);
           }
         }
         umma_commit(&bar[BAR_VE + s]);
-        umma_commit(&bar[BAR_PV]);
+        umma_commit(&bar[BAR_PV + s]);
       }
     }
   } else {
@@ -272,10 +276,14 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       }
       l_run = l_run * alpha + rs;
       if (j > 0) {
-        // PV of the previous block must be complete before O is rescaled and P is overwritten
-        if (!mbar_wait_bounded_warp(&bar[BAR_PV], (j - 1) & 1, abort_flag, p.status)) { ok = false; break; }
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, bump)) {
+        // P V of the previous block must be complete before O is rescaled -- and, without the second P buffer of the
+        // tensor-memory path, before P is overwritten
+        const bool rescale = __any_sync(0xffffffffu, bump);
+        if (!PT || rescale) {
+          if (!mbar_wait_bounded_warp(&bar[BAR_PV + ((j - 1) & 1)], ((j - 1) >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+          tc_fence_after();
+        }
+        if (rescale) {
 #pragma unroll
           for (int c = 0; c < OC / 16; ++c) {   // this group's part of the O columns, 16 at a time
             uint32_t t[16];
@@ -288,6 +296,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           tc_wait_st();
         }
       }
+      if (PT && j > 1) {   // this P buffer's previous content (block j - 2) has been consumed: long since, as a rule
+        if (!mbar_wait_bounded_warp(&bar[BAR_PV + s], ((j >> 1) - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+      }
       m_run = m_new;
       if constexpr (PT) {
         // P -> tensor memory: row r is lane r, kv columns (2c, 2c+1) share the 32-bit column c
@@ -296,7 +307,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           uint32_t w[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) w[i] = pack_bf16(sv[c * 32 + 2 * i], sv[c * 32 + 2 * i + 1]);
-          tmem_st_32x16(tmem_p + lane_addr + (grp * HALF + c * 32) / 2, w);
+          tmem_st_32x16(tmem_p + s * 64 + lane_addr + (grp * HALF + c * 32) / 2, w);
         }
         tc_wait_st();
       } else {
@@ -316,9 +327,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bar[BAR_PF]);
+      if (lane == 0) mbar_arrive(&bar[BAR_PF + s]);
     }
-    if (ok && mbar_wait_bounded_warp(&bar[BAR_PV], (n_blocks - 1) & 1, abort_flag, p.status)) {
+    if (ok && mbar_wait_bounded_warp(&bar[BAR_PV + ((n_blocks - 1) & 1)], ((n_blocks - 1) >> 1) & 1, abort_flag, p.status)) {
       tc_fence_after();
       // combine the partial row sums
       float* ssum = reinterpret_cast<float*>(smem + L::OFF_SUM);
@@ -372,13 +383,13 @@ static int make_bshd_map(CUtensorMap* out, const void* base, int B, int S, int H
   return jpb_make_tensor_map(out, base, 2, 4, dims, strides, box, 1);
 }
 
-// 1: probabilities handed to the P V product through tensor memory; 0: through shared memory
-// (JAXPP_B200_ATTN_P_TMEM overrides the default)
+// 1 (default, the faster one: 0.40 against 0.44 ms at B4 S4096 H16 D128): probabilities handed to the P V product
+// through tensor memory; 0: through shared memory.  JAXPP_B200_ATTN_P_TMEM overrides the default.
 static int fwd_p_tmem() {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("JAXPP_B200_ATTN_P_TMEM");
-    v = (e && e[0] == '1') ? 1 : 0;
+    v = (e && e[0] == '0') ? 0 : 1;
   }
   return v;
 }

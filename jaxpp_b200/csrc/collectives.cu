@@ -56,15 +56,19 @@ __device__ __forceinline__ uint4 ar_ld_v4(const void* p) {
 __device__ __forceinline__ bool ar_wait_all(const int* flags, int n_ranks, int rank, int epoch, int* status, int* smem_ok) {
   if (threadIdx.x == 0) {
     int ok = 1;
-    const uint64_t t0 = globaltimer_ns();
+    uint64_t t0 = 0;   // the clock is read every 256 polls only (a read costs about as much as a small all-reduce step)
     for (int q = 0; q < n_ranks && ok; ++q) {
       if (q == rank) continue;
       uint32_t spins = 0;
       while (ar_ld_acquire_sys(flags + q) < epoch) {
-        if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > wait_budget_ns()) {
-          report_status(status, JPB_ERR_PEER_TIMEOUT);
-          ok = 0;
-          break;
+        if ((++spins & 0xff) == 0) {
+          const uint64_t now = globaltimer_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > wait_budget_ns()) {
+            report_status(status, JPB_ERR_PEER_TIMEOUT);
+            ok = 0;
+            break;
+          }
         }
       }
     }

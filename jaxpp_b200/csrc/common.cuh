@@ -66,6 +66,20 @@ __device__ __forceinline__ void fence_barrier_init() {
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+// One lane of the (converged) warp, the same one every time.  The producer and MMA warps run their loops with all 32
+// lanes and put only the issuing instructions (TMA copies, tcgen05.mma, commits) under `if (elect_one())`: addresses,
+// descriptors and loop counters are then computed in warp-uniform code, where the compiler may keep them in uniform
+// registers -- the form those instructions take their operands in -- instead of converting them for every issue.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
@@ -91,14 +105,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // (JPB_ERR_PEER_TIMEOUT) instead of one of the internal waits that it starved.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                                   int* status, int code = JPB_ERR_WAIT_TIMEOUT) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  // The clock is read only every 1024 polls, the first time to start the interval: reading %globaltimer costs on the
+  // order of a thousand cycles, and a wait that blocks at all sits on the critical path of its loop (an up-front read
+  // per blocked wait made the attention kernels spend most of every iteration in it).
   uint32_t spins = 0;
+  uint64_t t0 = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3ff) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > 2 * wait_budget_ns()) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > 2 * wait_budget_ns()) {
         *abort_flag = 1;
         report_status(status, code);
         return false;
@@ -134,6 +152,13 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
+}
+// Untiled bulk copy global -> shared memory of this CTA (both addresses 16-byte aligned, size a multiple of 16 bytes),
+// completing on an mbarrier like the tensor copies.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
@@ -245,6 +270,46 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
   d |= 1ull << 46;  // descriptor version for sm_100
   d |= 2ull << 61;  // SWIZZLE_128B
   return d;
+}
+
+// The same descriptor as two 32-bit words.  One thread issues every MMA of a CTA, and each instruction it spends
+// between two MMAs delays the next one (its instructions depend on one another, so each costs several cycles): a
+// 64-bit descriptor assembled from scratch per MMA costs more issue time than a 128x64x16 product takes to execute.
+// With the words kept apart, the high word and the start word of each operand are computed once, outside the loops,
+// and stepping to the next 16 elements of K (or the next stage) is one 32-bit add on the low word: the start
+// address field holds (address >> 4) and shared-memory addresses leave its upper bits free, so the add cannot carry
+// into the leading-dimension field.
+struct SmemDesc {
+  uint32_t lo, hi;
+};
+__device__ __forceinline__ SmemDesc make_smem_desc2(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  SmemDesc d;
+  d.lo = ((smem_addr >> 4) & 0x3fff) | (((lbo_bytes >> 4) & 0x3fff) << 16);
+  d.hi = ((sbo_bytes >> 4) & 0x3fff) | (1u << 14) | (2u << 29);  // bit 46: descriptor version; bits 61-63: SWIZZLE_128B
+  return d;
+}
+// D[tmem] (+)= A[smem] * B[smem]; `a_lo` / `b_lo` are SmemDesc::lo plus (byte offset >> 4)
+__device__ __forceinline__ void umma_bf16_ss2(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                              uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void umma_bf16_ts2(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
 }
 
 // Instruction descriptor for kind::f16 with bf16 inputs and fp32 accumulation.

@@ -71,19 +71,44 @@ __device__ __forceinline__ bool tile_live(const GemmParams& p, int prob, int m0)
   if (p.counts == nullptr) return true;
   return p.count_k ? range_live(p, prob, 0, p.K) : range_live(p, prob, m0, m0 + BM);
 }
-__device__ __forceinline__ bool kblock_live(const GemmParams& p, int prob, int k0) {
-  return p.counts == nullptr || !p.count_k || range_live(p, prob, k0, k0 + BK);
-}
+// The 64-row reduction blocks of a problem that hold data, as a sequence of ranges [lo, hi): one range covering all
+// k blocks when the counts do not describe K; otherwise one per non-empty segment (a block shared by two segments is
+// visited once).  Every role walks the same sequence.  No division: this runs once per k block in the threads that
+// issue the copies and the MMAs.
+struct KRanges {
+  int q = 0, next = 0, seg_lo = 0;
+  __device__ __forceinline__ bool get(const GemmParams& p, int prob, int k_blocks, int& lo, int& hi) {
+    if (p.counts == nullptr || !p.count_k) {
+      if (q++ > 0) return false;
+      lo = 0; hi = k_blocks;
+      return true;
+    }
+    const int* c = p.counts + prob * p.segs;
+    for (; q < p.segs; ++q, seg_lo += p.seg_rows) {
+      const int n = min(__ldg(c + q), p.seg_rows);
+      if (n <= 0) continue;
+      lo = max(next, seg_lo / BK);
+      hi = min(k_blocks, (seg_lo + n + BK - 1) / BK);
+      if (lo >= hi) continue;
+      next = hi;
+      ++q; seg_lo += p.seg_rows;
+      return true;
+    }
+    return false;
+  }
+};
 
 // Tile rasterisation: groups of GROUP_M row blocks are walked column by column, so that the ~148 tiles in
-// flight at any time touch about GROUP_M row panels of A and 148/GROUP_M column panels of B — a working set that
+// flight at any time touch about GROUP_M row panels of A and 148/GROUP_M column panels of B -- a working set that
 // stays in L2 instead of re-streaming all of A for every column of tiles.
-constexpr int GROUP_M = 16;
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& m_blk, int& n_blk) {
-  const int per_group = GROUP_M * tiles_n;
+// With live-row counts the group is 15 blocks high: empty tiles sit at fixed row blocks, a CTA visits every 148th
+// tile, and a height that shares a factor with 148 would hand some CTAs twice as many empty tiles as others.
+constexpr int GROUP_M = 16, GROUP_M_COUNTS = 15;
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& m_blk, int& n_blk, int group_m = GROUP_M) {
+  const int per_group = group_m * tiles_n;
   const int group = tile / per_group;
-  const int first_m = group * GROUP_M;
-  const int gm = (tiles_m - first_m) < GROUP_M ? (tiles_m - first_m) : GROUP_M;
+  const int first_m = group * group_m;
+  const int gm = (tiles_m - first_m) < group_m ? (tiles_m - first_m) : group_m;
   const int in = tile - group * per_group;
   m_blk = first_m + in % gm;
   n_blk = in / gm;
@@ -108,6 +133,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int lane = threadIdx.x & 31;
   const int tiles_per_problem = p.tiles_m * p.tiles_n;
   const int num_tiles = tiles_per_problem * p.batch;
+  const int group_m = (p.counts != nullptr && !p.count_k) ? GROUP_M_COUNTS : GROUP_M;
   const int k_blocks = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -135,7 +161,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   if (warp == 0) {
     // ------------------------------- TMA producer --------------------------------------------
-    if (lane == 0) {
+    // (all lanes walk the loop; one elected lane issues: see elect_one)
+    {
       uint32_t it = 0;
       uint32_t armed = 0;       // bit s set <=> a copy into stage s may still be in flight
       uint32_t armed_phase = 0; // bit s = barrier phase of the latest copy issued into stage s
@@ -143,37 +170,41 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int m_blk, n_blk;
         const int prob = tile / tiles_per_problem;
-        tile_coords(tile - prob * tiles_per_problem, p.tiles_m, p.tiles_n, m_blk, n_blk);
+        tile_coords(tile - prob * tiles_per_problem, p.tiles_m, p.tiles_n, m_blk, n_blk, group_m);
         const int m0 = m_blk * BM, n0 = n_blk * BN;
         const int a_row = prob * p.a_off, b_row = prob * p.b_off;  // storage-row offsets of this problem
         if (!tile_live(p, prob, m0)) continue;
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!kblock_live(p, prob, kb * BK)) continue;
+        KRanges kr;
+        int kb_lo, kb_hi;
+        while (ok && kr.get(p, prob, k_blocks, kb_lo, kb_hi)) for (int kb = kb_lo; kb < kb_hi; ++kb) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait_bounded(&empty[s], ph ^ 1, abort_flag, p.status)) { ok = false; break; }
+          if (!mbar_wait_bounded_warp(&empty[s], ph ^ 1, abort_flag, p.status)) { ok = false; break; }
           uint8_t* sa = smem + s * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
-          mbar_expect_tx(&full[s], STAGE_BYTES);
           armed |= 1u << s;
           armed_phase = (armed_phase & ~(1u << s)) | (ph << s);
           const int k0 = kb * BK;
-          if (!A_MN) {
-            tma_load_2d(sa, &map_a, &full[s], k0, a_row + m0);         // box {64 k, 128 rows}
-          } else if (p.a_blocked) {
-            tma_load_3d(sa, &map_a, &full[s], 0, a_row + k0, m0 >> 6); // box {64 m, 64 k, 2 blocks}
-          } else {
+          if (elect_one()) {
+            mbar_expect_tx(&full[s], STAGE_BYTES);
+            if (!A_MN) {
+              tma_load_2d(sa, &map_a, &full[s], k0, a_row + m0);         // box {64 k, 128 rows}
+            } else if (p.a_blocked) {
+              tma_load_3d(sa, &map_a, &full[s], 0, a_row + k0, m0 >> 6); // box {64 m, 64 k, 2 blocks}
+            } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &map_a, &full[s], m0 + j * 64, a_row + k0);
-          }
-          if (!B_MN) {
-            tma_load_2d(sb, &map_b, &full[s], k0, b_row + n0);         // box {64 k, 256 rows}
-          } else if (p.b_blocked) {
-            tma_load_3d(sb, &map_b, &full[s], 0, b_row + k0, n0 >> 6); // box {64 n, 64 k, 4 blocks}
-          } else {
+              for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &map_a, &full[s], m0 + j * 64, a_row + k0);
+            }
+            if (!B_MN) {
+              tma_load_2d(sb, &map_b, &full[s], k0, b_row + n0);         // box {64 k, 256 rows}
+            } else if (p.b_blocked) {
+              tma_load_3d(sb, &map_b, &full[s], 0, b_row + k0, n0 >> 6); // box {64 n, 64 k, 4 blocks}
+            } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &map_b, &full[s], n0 + j * 64, b_row + k0);
+              for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &map_b, &full[s], n0 + j * 64, b_row + k0);
+            }
           }
+          __syncwarp();
           ++it;
         }
       }
@@ -191,7 +222,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer --------------------------------------------------
-    if (lane == 0) {
+    {
       constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
       uint32_t it = 0;
       uint32_t tile_i = 0;
@@ -200,34 +231,39 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int prob = tile / tiles_per_problem;
         if (p.counts != nullptr) {
           int m_blk, n_blk;
-          tile_coords(tile - prob * tiles_per_problem, p.tiles_m, p.tiles_n, m_blk, n_blk);
+          tile_coords(tile - prob * tiles_per_problem, p.tiles_m, p.tiles_n, m_blk, n_blk, group_m);
           if (!tile_live(p, prob, m_blk * BM)) continue;
         }
         const uint32_t acc = tile_i & 1;
         const uint32_t acc_ph = (tile_i >> 1) & 1;
-        if (!mbar_wait_bounded(&acc_empty[acc], acc_ph ^ 1, abort_flag, p.status)) { ok = false; break; }
+        if (!mbar_wait_bounded_warp(&acc_empty[acc], acc_ph ^ 1, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         bool fresh = true;  // the first product of a tile overwrites the accumulator
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!kblock_live(p, prob, kb * BK)) continue;
+        KRanges kr;
+        int kb_lo, kb_hi;
+        while (ok && kr.get(p, prob, k_blocks, kb_lo, kb_hi)) for (int kb = kb_lo; kb < kb_hi; ++kb) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait_bounded(&full[s], ph, abort_flag, p.status)) { ok = false; break; }
+          if (!mbar_wait_bounded_warp(&full[s], ph, abort_flag, p.status)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
           const uint32_t sb = sa + A_BYTES;
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t da = A_MN ? make_smem_desc(sa + k * 2048, 8192, 1024) : make_smem_desc(sa + k * 32, 16, 1024);
-            const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, 8192, 1024) : make_smem_desc(sb + k * 32, 16, 1024);
-            umma_bf16_ss(d_tmem, da, db, idesc, !(fresh && k == 0));
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint64_t da = A_MN ? make_smem_desc(sa + k * 2048, 8192, 1024) : make_smem_desc(sa + k * 32, 16, 1024);
+              const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, 8192, 1024) : make_smem_desc(sb + k * 32, 16, 1024);
+              umma_bf16_ss(d_tmem, da, db, idesc, !(fresh && k == 0));
+            }
+            umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
           }
+          __syncwarp();
           fresh = false;
-          umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
           ++it;
         }
-        if (ok) umma_commit(&acc_full[acc]);
+        if (ok && elect_one()) umma_commit(&acc_full[acc]);
+        __syncwarp();
         ++tile_i;
       }
     }
@@ -239,16 +275,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int m_blk, n_blk;
       const int prob = tile / tiles_per_problem;
-      tile_coords(tile - prob * tiles_per_problem, p.tiles_m, p.tiles_n, m_blk, n_blk);
+      tile_coords(tile - prob * tiles_per_problem, p.tiles_m, p.tiles_n, m_blk, n_blk, group_m);
       const int m0 = m_blk * BM, n0 = n_blk * BN;
-      const bool live = tile_live(p, prob, m0);  // uniform across the CTA
-      if (!live && p.accumulate) continue;       // nothing to add
+      if (!tile_live(p, prob, m0)) {  // uniform across the CTA: nothing was computed, the tile is all zeros
+        if (p.accumulate) continue;   // nothing to add
+        const int row_z = m0 + quarter * 32;   // this warp's 32 rows, one row at a time, lanes along the columns
+        const int n_end = min(n0 + BN, p.N);
+        for (int rr = 0; rr < 32 && row_z + rr < p.M; ++rr) {
+          const size_t row = size_t(prob) * p.M + row_z + rr;
+          if (p.out_fp32) {
+            float* d = static_cast<float*>(p.D) + row * p.ldd;
+            for (int c = n0 + lane; c < n_end; c += 32) d[c] = 0.f;
+          } else {
+            __nv_bfloat16* d = static_cast<__nv_bfloat16*>(p.D) + row * p.ldd;
+            for (int c = n0 + lane; c < n_end; c += 32) d[c] = __float2bfloat16_rn(0.f);
+          }
+        }
+        continue;
+      }
       const uint32_t acc = tile_i & 1;
       const uint32_t acc_ph = (tile_i >> 1) & 1;
-      if (live) {
-        if (!mbar_wait_bounded_warp(&acc_full[acc], acc_ph, abort_flag, p.status)) { ok = false; break; }
-        tc_fence_after();
-      }
+      if (!mbar_wait_bounded_warp(&acc_full[acc], acc_ph, abort_flag, p.status)) { ok = false; break; }
+      tc_fence_after();
       const int row_in = m0 + quarter * 32 + lane;        // row within this problem
       const bool row_ok = row_in < p.M;
       const size_t row = size_t(prob) * p.M + row_in;     // row of the stacked output
@@ -257,13 +305,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int col0 = n0 + c * 32;
         if (col0 >= p.N) break;  // uniform across the warp
         uint32_t r[32];
-        if (live) {
-          tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN + c * 32, r);
-          tc_wait_ld();
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = 0u;  // a tile without live rows is all zeros
-        }
+        tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN + c * 32, r);
+        tc_wait_ld();
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
@@ -312,7 +355,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
         }
       }
-      if (!live) continue;
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);

@@ -80,13 +80,17 @@ __device__ __forceinline__ void moe_signal_done(const MoeParams& p) {
 __device__ __forceinline__ bool moe_wait_peer(const MoeParams& p, int q, int lane) {
   int ok = 1;
   if (lane == 0) {
-    const uint64_t t0 = globaltimer_ns();
+    uint64_t t0 = 0;
     uint32_t spins = 0;
     while (moe_ld_acquire_sys(p.flags_local + q) < p.epoch) {
-      if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > wait_budget_ns()) {
-        report_status(p.status, JPB_ERR_PEER_TIMEOUT);
-        ok = 0;
-        break;
+      if ((++spins & 0xff) == 0) {
+        const uint64_t now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > wait_budget_ns()) {
+          report_status(p.status, JPB_ERR_PEER_TIMEOUT);
+          ok = 0;
+          break;
+        }
       }
     }
   }

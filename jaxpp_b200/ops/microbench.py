@@ -141,6 +141,7 @@ def main():
     bf = torch.bfloat16
     rnd = lambda *s: torch.randn(*s, device="cuda", dtype=bf)
     flops = bytes_ = 0
+    fn_equal = None   # gemm_batched --fill: the same data through the equal-group kernel, timed in the same process
     if a.op == "gemm":
         M, N, K = a.m, a.n, a.k
         flops = 2.0 * M * N * K
@@ -164,11 +165,12 @@ def main():
             dyb = rnd(E, M, N)
             dyb[:, live:] = 0
             if a.layout == "fwd":
-                fn = lambda: native.linear_batched(xb, wb, counts, M)
+                fn, fn_equal = (lambda: native.linear_batched(xb, wb, counts, M)), (lambda: native.linear_batched(xb, wb))
             elif a.layout == "dgrad":
-                fn = lambda: native.linear_dgrad_batched(dyb, wb, counts, M)
+                fn, fn_equal = (lambda: native.linear_dgrad_batched(dyb, wb, counts, M)), (lambda: native.linear_dgrad_batched(dyb, wb))
             else:
                 fn = lambda: native.linear_wgrad_batched(dyb, xb, torch.float32, counts, M)
+                fn_equal = lambda: native.linear_wgrad_batched(dyb, xb, torch.float32)
         else:
             fn = lambda: native.linear_batched(xb, wb)
     elif a.op in ("attn_fwd", "attn_bwd"):
@@ -206,6 +208,10 @@ def main():
     ms = timed(fn, a.iters, a.warmup, not a.no_flush)
     torch.cuda.synchronize()
     out = {"op": a.op, "ms": round(ms, 4), "status": native.read_status()}
+    if fn_equal is not None:
+        out["fill"] = a.fill
+        out["ms_equal_groups_same_data"] = round(timed(fn_equal, a.iters, a.warmup, not a.no_flush), 4)
+        out["ms_again"] = round(timed(fn, a.iters, a.warmup, not a.no_flush), 4)
     out.update({k: v for k, v in vars(a).items() if k in ("m", "n", "k", "layout", "batch", "seq", "heads", "head_dim", "rows", "hidden")})
     if flops:
         out["tflops"] = round(flops / ms / 1e9, 1)
