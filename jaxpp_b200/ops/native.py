@@ -186,6 +186,13 @@ def _counts_ok(counts, E) -> bool:
             and counts.is_contiguous())
 
 
+def _skip_rows() -> bool:
+    """Row counts are used by the forward / input-gradient grouped GEMMs only on request (see the flag's comment)."""
+    from ..utils import config
+
+    return config.moe_skip_empty_slots.value >= 2
+
+
 def _gemm_batched(a, b, out, batch, M, N, K, a_mn, b_mn, counts=None, seg_rows=0, count_k=False):
     lib = load()
     if counts is not None:
@@ -216,7 +223,7 @@ def linear_batched(x, w, counts=None, seg_rows=0):
         return torch.stack([linear(x[e], w[e], None) for e in range(E)], 0)
     x, w = x.contiguous(), w.contiguous()
     out = torch.empty(E, M, N, dtype=torch.bfloat16, device=x.device)
-    if _counts_ok(counts, E) and seg_rows * counts.shape[1] == M:
+    if _counts_ok(counts, E) and seg_rows * counts.shape[1] == M and _skip_rows():
         return _gemm_batched(x, w, out, E, M, N, K, False, False, counts, seg_rows, False)
     return _gemm_batched(x, w, out, E, M, N, K, False, False)
 
@@ -229,7 +236,7 @@ def linear_dgrad_batched(dy, w, counts=None, seg_rows=0):
         return torch.stack([linear_dgrad(dy[e], w[e]) for e in range(E)], 0)
     dy, w = dy.contiguous(), w.contiguous()
     out = torch.empty(E, M, K, dtype=torch.bfloat16, device=dy.device)
-    if _counts_ok(counts, E) and seg_rows * counts.shape[1] == M:
+    if _counts_ok(counts, E) and seg_rows * counts.shape[1] == M and _skip_rows():
         return _gemm_batched(dy, w, out, E, M, K, N, False, True, counts, seg_rows, False)
     return _gemm_batched(dy, w, out, E, M, K, N, False, True)
 

@@ -305,7 +305,7 @@ def moe_ffn(x: Tensor, p: dict, n_experts: int, top_k: int, capacity_factor: flo
 
     top_i, weights, aux = route(x, p["router"], top_k)
     dest, _, counts = slots_and_counts(top_i, n_experts, capacity)
-    if not config.moe_skip_empty_slots.value:
+    if config.moe_skip_empty_slots.value <= 0:
         counts = None
     if ep > 1:
         buf = torch.ops.b200moe.dispatch_a2a(x, dest, None, n_experts, capacity, top_k, ep_axis)   # [E_l, ep*C, d]
