@@ -300,6 +300,17 @@ def main():
     sync_all()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
     peak_mem = torch.cuda.max_memory_allocated() / 1e9 if cuda else 0.0
+    from jaxpp_b200.runtime import executor as _ex
+    if _ex.LIVE_REPORT:   # JAXPP_B200_TRACK_LIVE_BYTES=1: what the step's environment held at its fullest
+        rep = _ex.LIVE_REPORT[-1]
+        state_bytes = sum(t.untyped_storage().nbytes() for t in torch.utils._pytree.tree_leaves(state) if isinstance(t, torch.Tensor))
+        print(f"[live rank {rank}] peak {rep['bytes'] / 1e6:.1f} MB in {rep['n_values']} values before {rep['before']}; "
+              f"state {state_bytes / 1e6:.1f} MB; largest: "
+              + "; ".join(f"%{v} {sh} {dt} {b / 1e6:.2f}MB" for b, v, sh, dt in rep["largest"]), file=sys.stderr, flush=True)
+        if os.environ.get("JAXPP_B200_TRACK_LIVE_BYTES_SHAPES") == "1" and rank == 0:
+            import collections
+            cnt = collections.Counter((sh, dt) for b, v, sh, dt in rep["all"])
+            print("[live shapes] " + "; ".join(f"{sh} {dt} x{c}" for (sh, dt), c in cnt.most_common(30)), file=sys.stderr, flush=True)
 
     # ---- bubble and timeline: one extra step with per-task CUDA events ---------------------------------------------------
     compiled = jitted.lower(state, tok, lab)

@@ -295,10 +295,27 @@ def cluster_stages(region: Sequence[fx.Node], get_rank, mpmd_dim: int) -> tuple[
         put_yield(y, n + j)
 
     # ---- left-over nodes, pass 1: follow definitions -----------------------------------------
+    # A left-over node that the program runs after a backward marker belongs to the backward pass, whatever it reads:
+    # the re-run forward of a recomputed block of the FIRST stage depends on forward values and parameters only (no
+    # backward marker follows it, so it is in no marker's closure), and following its definitions alone would put it
+    # into the forward task -- which then runs the block twice and keeps every activation, the opposite of recompute.
+    # (Only nodes that backward computations read are held back like this: what merely post-processes a forward
+    # value after the markers -- the loss handed to the loop's output, say -- still follows its definitions.)
+    bwd_at = [(pos[y], n + j) for j, y in enumerate(bwd)]
+    needs_bwd: dict = {}    # reads, directly or not, a value of a backward cluster
+    for m in region:
+        needs_bwd[m] = (m in assign and assign[m] >= n) or any(needs_bwd.get(i, False) for i in m.all_input_nodes)
+    feeds_bwd: dict = {}    # is read, directly or not, by such a node
+    for m in reversed(region):
+        feeds_bwd[m] = any(needs_bwd.get(u, False) or feeds_bwd.get(u, False) for u in m.users if u in allowed)
     floating = []
     for m in region:
         if m in assign:
             continue
+        floor = None
+        for p_y, c_y in bwd_at:
+            if p_y < pos[m]:
+                floor = c_y
         if is_marker(m, "place_with") and m.args[1] in assign:
             c = assign[m.args[1]]
         elif m.meta.get("pp_passthrough"):
@@ -306,6 +323,8 @@ def cluster_stages(region: Sequence[fx.Node], get_rank, mpmd_dim: int) -> tuple[
         else:
             cs = [assign[i] for i in m.all_input_nodes if i in assign]
             c = max(cs) if cs else None
+            if floor is not None and (c is None or c < floor) and has_bwd and feeds_bwd[m] and not needs_bwd[m]:
+                c = floor
         if c is None:
             floating.append(m)
             continue

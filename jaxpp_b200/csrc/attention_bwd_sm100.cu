@@ -39,8 +39,6 @@ struct AttnBwdParams {
   const float* delta;  // [B,H,Sq], already multiplied by the softmax scale
   __nv_bfloat16 *dq, *dk, *dv;
   int* status;
-  int stats_smem;      // Sq is a multiple of 64 and lse / delta are 16-byte aligned: the dK/dV kernel's producer copies each
-                       // query block's 64 + 64 statistics into the operand stage (else the warps load them themselves)
 };
 
 // swizzled K-major store of 8 consecutive bf16 (one 16-byte chunk `cc` of row `r`) into a [rows x 64] tile
@@ -89,22 +87,17 @@ struct DkvSmem {
   // NS stages, each: Q (DB tiles) then dO (DB tiles).  A stage is reloaded only after the MMAs that read it have
   // completed, and a TMA load takes about as long as an iteration: with two stages the loop
   // "MMA done -> load -> S -> softmax -> MMA" spanned two iterations and set the pace; more stages hide it.
-  static constexpr int NS = 3;
+  static constexpr int NS = 4;
   static constexpr int OFF_Q = OFF_V + DB * KV_TILE;
   static constexpr int STAGE = 2 * DB * Q_TILE;
-  // P^T and dS^T, [128 kv x 64 q] bf16 each, in two buffers used by alternate iterations: the warps write the pair of
-  // iteration g while the tensor core still reads that of g-1, so the completion of those products (and the two
-  // barrier hops around it) is off the loop's critical path
-  static constexpr int PD_BYTES = 2 * 128 * 128;
-  static constexpr int OFF_P = OFF_Q + NS * STAGE;        // buffer i: P^T at OFF_P + i * PD_BYTES, dS^T 16 KiB behind it
-  static constexpr int OFF_STAT = OFF_P + 2 * PD_BYTES;   // per stage: lse * log2(e) and delta * scale of the 64 query rows
-  static constexpr int STAT_BYTES = 2 * 64 * 4;
-  static constexpr int OFF_BAR = OFF_STAT + NS * STAT_BYTES;
+  static constexpr int OFF_P = OFF_Q + NS * STAGE;        // P^T [128 kv x 64 q] bf16, dS^T 16 KiB behind it
+  static constexpr int OFF_BAR = OFF_P + 2 * 128 * 128;
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
 };
 
-// Stages of the streamed operand.  The dK/dV kernel gives one of its four to a second pair of P^T / dS^T buffers.
-constexpr int DKV_NS = 3, DQ_NS = 4;
+// Stages of the streamed operand (a stage is reloaded only after the MMAs that read it have completed, and a copy takes
+// about as long as an iteration: three stages, tried to make room for a second pair of P^T / dS^T buffers, cost 7 %).
+constexpr int DKV_NS = 4, DQ_NS = 4;
 // S^T / dP^T live in two TMEM buffers (K1_SF / K1_SFREE come in pairs, indexed by the parity of the iteration): the
 // tensor core computes the pair of iteration g+2 while the warps work on g and g+1, so that the round trip
 // "S loaded -> next S issued -> S done" is off the loop's critical path.
@@ -204,12 +197,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           const int h = hk * G + t / per_head;
           const int q0 = (i_start + t % per_head) * 64;
           if (!mbar_wait_bounded(&bar[K1_QE + s], ph ^ 1, abort_flag, p.status)) { ok = false; break; }
-          arm(K1_QF + s, ph, L::STAGE + (p.stats_smem ? L::STAT_BYTES : 0));
-          if (p.stats_smem) {
-            const size_t row = (size_t(b) * p.H + h) * p.Sq + q0;
-            bulk_load_1d(smem + L::OFF_STAT + s * L::STAT_BYTES, p.lse + row, 256, &bar[K1_QF + s]);
-            bulk_load_1d(smem + L::OFF_STAT + s * L::STAT_BYTES + 256, p.delta + row, 256, &bar[K1_QF + s]);
-          }
+          arm(K1_QF + s, ph, L::STAGE);
           uint8_t* st = smem + L::OFF_Q + s * L::STAGE;
 #pragma unroll
           for (int d = 0; d < L::DB; ++d) {
@@ -238,7 +226,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       const SmemDesc dq_ = make_smem_desc2(smem_u32(smem + L::OFF_Q), 16, 1024);
       const SmemDesc dp_ = make_smem_desc2(smem_u32(smem + L::OFF_P), 16, 1024);
       const SmemDesc dqm_ = make_smem_desc2(smem_u32(smem + L::OFF_Q), L::Q_TILE, 1024);   // Q / dO as MN-major operands
-      constexpr uint32_t STAGE16 = L::STAGE >> 4, DO16 = (L::DB * L::Q_TILE) >> 4, PD16 = L::PD_BYTES >> 4, DS16 = (128 * 128) >> 4;
+      constexpr uint32_t STAGE16 = L::STAGE >> 4, DO16 = (L::DB * L::Q_TILE) >> 4, DS16 = (128 * 128) >> 4;
       bool ok = true;
       auto issue_s = [&](uint32_t gg) -> bool {
         const int s = gg % DKV_NS;
@@ -285,7 +273,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           const uint32_t pb = g & 1;
           if (!mbar_wait_bounded(&bar[K1_PF + pb], (g >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t p_lo = dp_.lo + pb * PD16, ds_lo = p_lo + DS16;
+          const uint32_t p_lo = dp_.lo, ds_lo = p_lo + DS16;
           const uint32_t qm_lo = dqm_.lo + s * STAGE16, dom_lo = qm_lo + DO16;
           const uint32_t acc = t != 0;
 #pragma unroll
@@ -334,18 +322,17 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
         continue;
       }
-      for (int t = 0; t < n_iter && ok; ++t, ++g) {
+      // Per-column statistics (lse * log2 e, delta * scale; the same addresses in every lane).  Those of iteration t + 1 are
+      // requested right after the arithmetic of iteration t has consumed the current ones, into the same registers:
+      // their latency then overlaps the hand-over of P^T / dS^T and the wait for the next S^T instead of standing at
+      // the head of every iteration (520-610 cycles each, measured), and no extra registers are live.
+      float lq[CW], dl[CW];
+      auto load_stats = [&](int t) {
         const int h = hk * G + t / per_head;
         const int q0 = (i_start + t % per_head) * 64 + cb;
-        // per-column statistics of this block, fetched before the tensor core is done (same address in every lane)
         const float* lse_q = p.lse + (size_t(b) * p.H + h) * p.Sq;
         const float* dl_q = p.delta + (size_t(b) * p.H + h) * p.Sq;
-        // tile-level test (warp-uniform): is every (kv row, query column) of this warp group's 128 x CW block visible?
-        const bool full = q0 + CW - 1 < p.Sq && kv0 + 127 < p.Sk && (!p.causal || kv0 + 127 <= q0 + off) && (p.Sq & 3) == 0;
-        float lq[CW], dl[CW];
-        if (p.stats_smem) {
-          // they come with the operand stage (read below, once S^T is there: that they have landed follows from it)
-        } else if (full) {
+        if (q0 + CW - 1 < p.Sq && (p.Sq & 3) == 0) {
           const float4* l4 = reinterpret_cast<const float4*>(lse_q + q0);
           const float4* d4 = reinterpret_cast<const float4*>(dl_q + q0);
 #pragma unroll
@@ -362,16 +349,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             dl[i] = in ? __ldg(dl_q + q0 + i) : 0.f;
           }
         }
-        // the statistics of the next iteration's columns: pull their lines into L1 now, so that the loads above hit it
-        // then (they sit on the loop's critical path: nothing else waits between two iterations of these warps)
-        if (!p.stats_smem && t + 1 < n_iter && lane < 4) {
-          const int hn = hk * G + (t + 1) / per_head;
-          const int qn = (i_start + (t + 1) % per_head) * 64;
-          if (qn + 64 <= p.Sq) {
-            const float* base = ((lane & 2) ? p.delta : p.lse) + (size_t(b) * p.H + hn) * p.Sq + qn + (lane & 1) * 32;
-            asm volatile("prefetch.global.L1 [%0];" ::"l"(base));
-          }
-        }
+      };
+      load_stats(0);
+      for (int t = 0; t < n_iter && ok; ++t, ++g) {
+        const int q0 = (i_start + t % per_head) * 64 + cb;
+        // tile-level test (warp-uniform): is every (kv row, query column) of this warp group's 128 x CW block visible?
+        const bool full = q0 + CW - 1 < p.Sq && kv0 + 127 < p.Sk && (!p.causal || kv0 + 127 <= q0 + off);
         const uint32_t bf = g & 1;
         if (!mbar_wait_bounded_warp(&bar[K1_SF + bf], (g >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
@@ -387,16 +370,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar[K1_SFREE + bf]);
-        if (p.stats_smem) {
-          // same address in every lane: one broadcast read per four values
-          const float4* st4 = reinterpret_cast<const float4*>(smem + L::OFF_STAT + (g % DKV_NS) * L::STAT_BYTES) + cb / 4;
-#pragma unroll
-          for (int i = 0; i < CW / 4; ++i) {
-            const float4 a = st4[i], c = st4[16 + i];
-            lq[4 * i] = a.x; lq[4 * i + 1] = a.y; lq[4 * i + 2] = a.z; lq[4 * i + 3] = a.w;
-            dl[4 * i] = c.x; dl[4 * i + 1] = c.y; dl[4 * i + 2] = c.z; dl[4 * i + 3] = c.w;
-          }
-        }
         if (full) {
 #pragma unroll
           for (int i = 0; i < CW; ++i) {
@@ -418,11 +391,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             dp[i] = ds;
           }
         }
-        if (g > 1) {  // this buffer's previous content (iteration g - 2, possibly of the previous tile) has been consumed
-          if (!mbar_wait_bounded_warp(&bar[K1_PE + bf], ((g >> 1) - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+        if (t + 1 < n_iter) load_stats(t + 1);
+        if (g > 0) {  // P^T / dS^T of the previous iteration (possibly of the previous tile) have been consumed
+          if (!mbar_wait_bounded_warp(&bar[K1_PE + ((g - 1) & 1)], ((g - 1) >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
         }
         {
-          uint8_t* tp = smem + L::OFF_P + bf * L::PD_BYTES;
+          uint8_t* tp = smem + L::OFF_P;
           uint8_t* tds = tp + 128 * 128;
 #pragma unroll
           for (int c = 0; c < CW / 8; ++c) {
@@ -782,12 +756,13 @@ static int make_map_rows(CUtensorMap* out, const void* base, int B, int S, int H
   return jpb_make_tensor_map(out, base, 2, 4, dims, strides, box, 1);
 }
 
-// Softmax groups per CTA of the two backward kernels (2 or 4; JAXPP_B200_ATTN_BWD_GROUPS overrides the default).
+// Softmax groups per CTA of the two backward kernels: 2 (default; 3-5 % faster than 4 in every measurement: the loop is
+// paced by the operand fetches of the MMAs, not by the warps) or 4.  JAXPP_B200_ATTN_BWD_GROUPS overrides the default.
 static int bwd_groups() {
   static int ng = 0;
   if (ng == 0) {
     const char* e = getenv("JAXPP_B200_ATTN_BWD_GROUPS");
-    ng = (e && e[0] == '2') ? 2 : 4;
+    ng = (e && e[0] == '4') ? 4 : 2;
   }
   return ng;
 }
@@ -857,7 +832,6 @@ JPB_API int jpb_attention_bwd(const void* dO, const void* q, const void* k, cons
   p.lse = lse2; p.delta = delta;
   p.dq = static_cast<__nv_bfloat16*>(dq); p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
   p.status = jpb_status_device_ptr();
-  p.stats_smem = (Sq % 64 == 0 && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0) ? 1 : 0;
   if (bwd_groups() == 2) return D == 128 ? launch_bwd<128, 2>(dO, q, k, v, p, s) : launch_bwd<64, 2>(dO, q, k, v, p, s);
   return D == 128 ? launch_bwd<128, 4>(dO, q, k, v, p, s) : launch_bwd<64, 4>(dO, q, k, v, p, s);
 }

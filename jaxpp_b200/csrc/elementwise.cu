@@ -242,15 +242,35 @@ __global__ void __launch_bounds__(MAXT) norm_bwd_kernel(const T* __restrict__ dy
   }
 }
 
-// out[c] = sum_p partial[p * stride + c]   (p < nparts); one thread per column, coalesced over c
+// out[c] = sum_p partial[p * stride + c]   (p < nparts).  A CTA of 256 threads owns 32 columns: thread (cx, ry) adds up
+// rows ry, ry + 8, ... of column cx (four independent loads in flight, 128 contiguous bytes per warp and row), and the
+// eight row slices meet in shared memory.  One thread per column walking all rows, the earlier form, took as long as
+// half the norm-backward kernel that produces the partial sums.
 template <typename T>
 __global__ void reduce_partials_kernel(const float* __restrict__ partial, T* __restrict__ out, int nparts, int cols,
                                        size_t stride) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
-  float acc = 0.f;
-  for (int p = 0; p < nparts; ++p) acc += partial[size_t(p) * stride + c];
-  out[c] = from_f<T>(acc);
+  __shared__ float red[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  if (c < cols) {
+    int p = ry;
+    for (; p + 24 < nparts; p += 32) {
+      a0 += partial[size_t(p) * stride + c];
+      a1 += partial[size_t(p + 8) * stride + c];
+      a2 += partial[size_t(p + 16) * stride + c];
+      a3 += partial[size_t(p + 24) * stride + c];
+    }
+    for (; p < nparts; p += 8) a0 += partial[size_t(p) * stride + c];
+  }
+  red[ry][cx] = (a0 + a1) + (a2 + a3);
+  __syncthreads();
+  if (ry == 0 && c < cols) {
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc += red[i][cx];
+    out[c] = from_f<T>(acc);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -264,7 +284,19 @@ __global__ void colsum_partial_kernel(const T* __restrict__ x, float* __restrict
   float acc[VN];
 #pragma unroll
   for (int j = 0; j < VN; ++j) acc[j] = 0.f;
-  for (int r = blockIdx.y; r < rows; r += gridDim.y) {
+  int r = blockIdx.y;
+  for (; r + 3 * int(gridDim.y) < rows; r += 4 * gridDim.y) {   // four rows in flight per thread
+    Vec<T> x0, x1, x2, x3;
+    x0.load(x + size_t(r) * cols + v * VN);
+    x1.load(x + size_t(r + gridDim.y) * cols + v * VN);
+    x2.load(x + size_t(r + 2 * gridDim.y) * cols + v * VN);
+    x3.load(x + size_t(r + 3 * gridDim.y) * cols + v * VN);
+    float f0[VN], f1[VN], f2[VN], f3[VN];
+    x0.to_float(f0); x1.to_float(f1); x2.to_float(f2); x3.to_float(f3);
+#pragma unroll
+    for (int j = 0; j < VN; ++j) acc[j] += (f0[j] + f1[j]) + (f2[j] + f3[j]);
+  }
+  for (; r < rows; r += gridDim.y) {
     Vec<T> xv; xv.load(x + size_t(r) * cols + v * VN);
     float f[VN]; xv.to_float(f);
 #pragma unroll
@@ -693,9 +725,8 @@ static int norm_bwd_impl(int layer, int dt, const void* dy, const void* x, const
     } else {
       norm_bwd_kernel<T, false><<<grid, threads, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)w, nullptr, rstd, (T*)dx, scratch, rows, H, (const T*)add);
     }
-    const int rt = 256;
-    reduce_partials_kernel<T><<<(H + rt - 1) / rt, rt, 0, STREAM>>>(scratch, (T*)dw, grid, H, size_t(2) * H);
-    if (layer) reduce_partials_kernel<T><<<(H + rt - 1) / rt, rt, 0, STREAM>>>(scratch + H, (T*)db, grid, H, size_t(2) * H);
+    reduce_partials_kernel<T><<<(H + 31) / 32, 256, 0, STREAM>>>(scratch, (T*)dw, grid, H, size_t(2) * H);
+    if (layer) reduce_partials_kernel<T><<<(H + 31) / 32, 256, 0, STREAM>>>(scratch + H, (T*)db, grid, H, size_t(2) * H);
     return LAST_ERR;
   });
 }
@@ -713,7 +744,7 @@ JPB_API int jpb_norm_bwd_add(int layer, int dt, const void* dy, const void* x, c
 }
 
 JPB_API long long jpb_colsum_scratch_elems(int rows, int cols) {
-  const int parts = rows < 64 ? rows : 64;
+  const int parts = rows < 256 ? rows : 256;
   return (long long)parts * cols;
 }
 
@@ -722,11 +753,11 @@ JPB_API int jpb_colsum(int dt, const void* x, void* out, float* scratch, int row
     using T = decltype(tag);
     constexpr int VN = Vec<T>::N;
     if (cols % VN) return -int(JPB_ERR_BAD_ARGUMENT);
-    const int parts = rows < 64 ? rows : 64;
+    const int parts = rows < 256 ? rows : 256;
     const int threads = 128;
     dim3 grid((cols / VN + threads - 1) / threads, parts);
     colsum_partial_kernel<T><<<grid, threads, 0, STREAM>>>((const T*)x, scratch, rows, cols);
-    reduce_partials_kernel<T><<<(cols + 255) / 256, 256, 0, STREAM>>>(scratch, (T*)out, parts, cols, size_t(cols));
+    reduce_partials_kernel<T><<<(cols + 31) / 32, 256, 0, STREAM>>>(scratch, (T*)out, parts, cols, size_t(cols));
     return LAST_ERR;
   });
 }
@@ -935,7 +966,7 @@ JPB_API int jpb_rmsnorm_bwd_noalloc(int dtype, const void* dy, const void* x, co
     else
       norm_bwd_kernel<T, false><<<grid, threads, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)w, nullptr, rstd, (T*)dx,
                                                               scratch, rows, H);
-    reduce_partials_kernel<T><<<(H + 255) / 256, 256, 0, STREAM>>>(scratch, (T*)dw, grid, H, size_t(2) * H);
+    reduce_partials_kernel<T><<<(H + 31) / 32, 256, 0, STREAM>>>(scratch, (T*)dw, grid, H, size_t(2) * H);
     return LAST_ERR;
   });
 }

@@ -193,18 +193,18 @@ def _skip_rows() -> bool:
     return config.moe_skip_empty_slots.value >= 2
 
 
-def _gemm_batched(a, b, out, batch, M, N, K, a_mn, b_mn, counts=None, seg_rows=0, count_k=False):
+def _gemm_batched(a, b, out, batch, M, N, K, a_mn, b_mn, counts=None, seg_rows=0, count_k=False, accumulate=False):
     lib = load()
     if counts is not None:
         lib.jpb_gemm_bf16_grouped.argtypes = [_c_p, _c_p, _c_p] + [_c_int] * 11 + [_c_p] + [_c_int] * 3 + [_c_p]
         rc = lib.jpb_gemm_bf16_grouped(a.data_ptr(), b.data_ptr(), out.data_ptr(), batch, M, N, K, a.stride(-2), b.stride(-2),
-                                       out.stride(-2), int(a_mn), int(b_mn), int(out.dtype == torch.float32), 0,
+                                       out.stride(-2), int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate),
                                        counts.data_ptr(), seg_rows, counts.shape[1], int(count_k), _stream())
         _check(rc, "jpb_gemm_bf16_grouped")
         return out
     lib.jpb_gemm_bf16_batched.argtypes = [_c_p, _c_p, _c_p] + [_c_int] * 11 + [_c_p]
     rc = lib.jpb_gemm_bf16_batched(a.data_ptr(), b.data_ptr(), out.data_ptr(), batch, M, N, K, a.stride(-2), b.stride(-2),
-                                   out.stride(-2), int(a_mn), int(b_mn), int(out.dtype == torch.float32), 0, _stream())
+                                   out.stride(-2), int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate), _stream())
     _check(rc, "jpb_gemm_bf16_batched")
     return out
 
@@ -241,11 +241,18 @@ def linear_dgrad_batched(dy, w, counts=None, seg_rows=0):
     return _gemm_batched(dy, w, out, E, M, K, N, False, True)
 
 
-def linear_wgrad_batched(dy, x, out_dtype=None, counts=None, seg_rows=0):
+def linear_wgrad_batched(dy, x, out_dtype=None, counts=None, seg_rows=0, out=None, accumulate=False):
     """dy [E, M, N], x [E, M, K] -> [E, N, K] (reduction over the M tokens of each group).  With ``counts`` the
-    reduction skips 64-row blocks that hold no data."""
+    reduction skips 64-row blocks that hold no data.  ``out`` (fp32, contiguous) with ``accumulate``: the product is
+    added onto it in the GEMM's epilogue; None is returned when the shapes do not allow the grouped kernel."""
     E, M, N = dy.shape
     K = x.shape[2]
+    if out is not None:
+        if not _batched_ok(dy, x) or M % 64 or N % 8 or K % 8 or out.dtype != torch.float32 or not out.is_contiguous():
+            return None
+        dy, x = dy.contiguous(), x.contiguous()
+        use_counts = _counts_ok(counts, E) and seg_rows * counts.shape[1] == M
+        return _gemm_batched(dy, x, out, E, N, K, M, True, True, counts if use_counts else None, seg_rows, use_counts, accumulate)
     out_dtype = out_dtype or dy.dtype
     if not _batched_ok(dy, x) or M % 64 or N % 8 or K % 8 or out_dtype not in (torch.bfloat16, torch.float32):
         out = torch.empty(E, N, K, dtype=out_dtype, device=dy.device)

@@ -17,7 +17,7 @@ from . import core as ops
 
 def sink_targets() -> tuple:
     """Op overloads whose result may be redirected into an accumulator."""
-    out = [torch.ops.b200.linear_wgrad.default, torch.ops.b200.embedding_bwd.default]
+    out = [torch.ops.b200.linear_wgrad.default, torch.ops.b200.embedding_bwd.default, torch.ops.b200.linear_wgrad_batched.default]
     try:
         from ..parallel import tp  # noqa: F401  (registers the b200tp ops)
 
@@ -53,6 +53,15 @@ def accumulate(op, acc: torch.Tensor, *args, **kwargs) -> torch.Tensor:
                 and acc.shape[0] == vocab and acc.shape[1] == dy.shape[-1]):
             ops._native().embedding_bwd(dy, ids, vocab, out=acc, accumulate=True)   # scatter-add into the accumulator
             return acc
+    elif op is torch.ops.b200.linear_wgrad_batched.default:
+        # expert weight gradients: [E, N, K] per microbatch is the largest tensor a mixture-of-experts backward produces
+        dy, x = args[0], args[1]
+        counts = args[3] if len(args) > 3 else kwargs.get("counts")
+        seg_rows = args[4] if len(args) > 4 else kwargs.get("seg_rows", 0)
+        if (ops._use_native(dy) and acc.dtype == torch.float32 and acc.is_contiguous() and dy.dtype == torch.bfloat16
+                and acc.dim() == 3 and tuple(acc.shape) == (dy.shape[0], dy.shape[2], x.shape[2])):
+            if ops._native().linear_wgrad_batched(dy, x, None, counts, seg_rows, out=acc, accumulate=True) is not None:
+                return acc
     elif op is torch.ops.b200tp.ag_wgrad.default:
         dy, x_shard, axis = args[0], args[1], args[2]
         out_dtype = args[3] if len(args) > 3 else kwargs.get("out_dtype")

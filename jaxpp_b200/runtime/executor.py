@@ -11,6 +11,7 @@ src/jaxpp/jax_primitives.py:370-523, 776-859).
 from __future__ import annotations
 
 import contextlib
+import os
 import time
 from collections import defaultdict
 from typing import Any, Sequence
@@ -201,6 +202,24 @@ def _local_sum(state: RankState, ins: AllReduce, like_shape, like_dtype):
     return torch.zeros(like_shape, dtype=like_dtype, device=state.device)
 
 
+LIVE_REPORT: list = []   # filled when JAXPP_B200_TRACK_LIVE_BYTES=1: one dict per step of this process
+
+
+def _live_bytes(env: dict):
+    """Bytes of distinct storages referenced by the environment, and the values sorted by size."""
+    seen: dict[int, int] = {}
+    items = []
+    for vid, t in env.items():
+        if not isinstance(t, torch.Tensor):
+            continue
+        st = t.untyped_storage()
+        key = st.data_ptr()
+        if key not in seen:
+            seen[key] = st.nbytes()
+            items.append((st.nbytes(), vid, tuple(t.shape), str(t.dtype)))
+    return sum(seen.values()), sorted(items, reverse=True)
+
+
 def run_single_controller(prog: Program, inputs: Sequence[torch.Tensor | None], devices: Sequence[torch.device],
                           record_events: bool = False) -> tuple[list[RankState], list]:
     """Execute ``prog`` for all ranks in this process.  ``inputs[i]`` is the full flat input ``i`` (or
@@ -210,8 +229,15 @@ def run_single_controller(prog: Program, inputs: Sequence[torch.Tensor | None], 
         for r in ranks:
             states[r].env[vid] = x if x.device == devices[r] else x.to(devices[r])
     pending_collectives: dict[int, list] = defaultdict(list)
-    for ins in prog.instrs:
+    track = os.environ.get("JAXPP_B200_TRACK_LIVE_BYTES") == "1"
+    peak = {"bytes": 0}
+    for pos, ins in enumerate(prog.instrs):
         st = states[ins.rank]
+        if track and ins.rank == 0 and isinstance(ins, (RunTask, Delete)):
+            total, items = _live_bytes(st.env)
+            if total > peak["bytes"]:
+                peak = {"bytes": total, "before": f"{pos}: {getattr(ins, 'name', type(ins).__name__)}", "largest": items[:12],
+                        "all": items, "n_values": len(items), "rank": 0}
         if isinstance(ins, RunTask):
             st.run_task(ins)
         elif isinstance(ins, Slice):
@@ -242,6 +268,8 @@ def run_single_controller(prog: Program, inputs: Sequence[torch.Tensor | None], 
                 del pending_collectives[ins.cid]
         else:  # pragma: no cover
             raise NotImplementedError(type(ins))
+    if track:
+        LIVE_REPORT.append(peak)
     outs = []
     for o in prog.outputs:
         if o[0] == "c":
@@ -282,7 +310,20 @@ def run_multi_controller(prog: Program, rank: int, inputs: Sequence[torch.Tensor
                 raise ValueError(f"input %{vid} is required on pipeline rank {rank} but no local data was given")
             st.env[vid] = x
     comm.begin_step(st)
-    for ins in prog.for_rank(rank):
+    track = os.environ.get("JAXPP_B200_TRACK_LIVE_BYTES") == "1"
+    peak = {"bytes": 0}
+    for pos, ins in enumerate(prog.for_rank(rank)):
+        if track and isinstance(ins, (RunTask, Delete)):
+            total, items = _live_bytes(st.env)
+            if total > peak["bytes"]:
+                grew = total > 1.05 * peak["bytes"]
+                peak = {"bytes": total, "before": f"{pos}: {getattr(ins, 'name', type(ins).__name__)}", "largest": items[:12], "all": items,
+                        "n_values": len(items)}
+                if grew and device.type == "cuda" and total > 1e9:   # as it happens: a step that runs out of memory never reports
+                    import sys
+                    print(f"[live rank {rank}] env {total / 1e9:.1f} GB in {len(items)} values before {peak['before']}; allocator "
+                          f"{torch.cuda.memory_allocated(device) / 1e9:.1f} GB now, {torch.cuda.max_memory_allocated(device) / 1e9:.1f} GB max; "
+                          + "; ".join(f"%{v} {sh} {dt} {b / 1e9:.2f}GB" for b, v, sh, dt in items[:8]), file=sys.stderr, flush=True)
         if isinstance(ins, RunTask):
             if fault._PLAN[0] is not None:
                 fault.maybe_fail_task(rank, ins.name)
@@ -315,6 +356,9 @@ def run_multi_controller(prog: Program, rank: int, inputs: Sequence[torch.Tensor
         else:  # pragma: no cover
             raise NotImplementedError(type(ins))
     comm.end_step(st)
+    if track:
+        peak["rank"] = rank
+        LIVE_REPORT.append(peak)
     outs = []
     for o in prog.outputs:
         if o[0] == "c":

@@ -210,6 +210,14 @@ def _grouped_gemm_unequal_groups(native, E, seg, segs, N, K):
         close(dw, ref_w, rtol=2e-2, atol=2e-2 * rows ** 0.5)
         assert dw[-1].abs().max().item() == 0.0      # the empty group's gradient is exactly zero
         close(native.linear_wgrad_batched(dy, x, None, counts, seg), ref_w, rtol=2e-2, atol=3e-2 * rows ** 0.5)
+        # as a gradient sink: added onto an fp32 accumulator in the epilogue (empty groups leave it alone)
+        from jaxpp_b200.ops import sink
+
+        acc = torch.ones(E, N, K, dtype=torch.float32, device="cuda")
+        got = sink.accumulate(torch.ops.b200.linear_wgrad_batched.default, acc, dy, x, torch.float32, counts, seg)
+        assert got is acc
+        close(acc, 1.0 + ref_w, rtol=2e-2, atol=2e-2 * rows ** 0.5)
+        assert (acc[-1] == 1.0).all()
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

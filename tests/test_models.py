@@ -138,6 +138,13 @@ def test_activation_recompute_matches_and_moves_forward_ops_into_backward():
     # and the forward task hands fewer activations to the backward task
     fwd = lambda prog: next(i for i in prog.instrs if isinstance(i, RunTask) and i.name == "fwd_1__0")
     assert len(fwd(progs[1]).outs) < len(fwd(progs[0]).outs)
+    # the FIRST stage too: no backward marker follows its backward pass, and its re-run forward reads forward values
+    # only -- it must still run in the backward task, not a second time in the forward task
+    first_bwd = next(i.name for i in progs[0].instrs if isinstance(i, RunTask) and i.name.startswith("bwd") and "_0__0" in i.name)
+    assert n_attn(progs[0], "fwd_0__0") == n_attn(progs[1], "fwd_0__0") == 1
+    assert n_attn(progs[0], first_bwd) == 0 and n_attn(progs[1], first_bwd) == 1
+    fwd0 = lambda prog: next(i for i in prog.instrs if isinstance(i, RunTask) and i.name == "fwd_0__0")
+    assert len(fwd0(progs[1]).outs) < len(fwd0(progs[0]).outs)
 
 
 @pytest.mark.parametrize("family,schedule,tied", [
