@@ -260,12 +260,14 @@ def slots_for(top_i: Tensor, n_experts: int, capacity: int):
 def slots_and_counts(top_i: Tensor, n_experts: int, capacity: int):
     """:func:`slots_for` plus ``counts`` [E] int32: how many slots of each expert this device's tokens fill."""
     flat = top_i.reshape(-1)
-    onehot = torch.nn.functional.one_hot(flat, n_experts)
-    running = onehot.cumsum(0)
-    pos = (running - 1).gather(1, flat[:, None]).squeeze(1)
+    # running count of picks per expert, scanned along the CONTIGUOUS dimension of an [E, picks] int32 matrix: the same
+    # scan down the rows of a [picks, E] int64 one-hot matrix took 3.2 ms per call on the GPU (15 % of a Mixtral step)
+    onehot_t = (flat[None, :] == torch.arange(n_experts, device=flat.device, dtype=flat.dtype)[:, None]).to(torch.int32)
+    running = onehot_t.cumsum(1, dtype=torch.int32)                   # [E, picks]
+    pos = (running.gather(0, flat[None, :]).squeeze(0) - 1).to(flat.dtype)
     keep = pos < capacity
     dest = torch.where(keep, flat * capacity + pos, torch.full_like(flat, n_experts * capacity))
-    counts = running[-1].clamp(max=capacity).to(torch.int32)
+    counts = running[:, -1].clamp(max=capacity).to(torch.int32)
     return dest, keep, counts
 
 
