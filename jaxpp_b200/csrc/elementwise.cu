@@ -68,19 +68,35 @@ __global__ void norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w
   constexpr int VN = Vec<T>::N;
   __shared__ float scratch[64];
   const int nvec = H / VN;
+  // the next row is requested before this row's block reduction, so that loads stay in flight across the barriers
+  // and the stores (a CTA that loads, reduces and stores one row at a time keeps the memory system busy about a
+  // third of the time)
+  Vec<T> xv[NORM_MAX_VECS], xn[NORM_MAX_VECS];
+  if (blockIdx.x < rows) {
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_VECS; ++i) {
+      const int v = threadIdx.x + i * blockDim.x;
+      if (v < nvec) xv[i].load(x + size_t(blockIdx.x) * H + v * VN);
+    }
+  }
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const T* xr = x + size_t(row) * H;
-    Vec<T> xv[NORM_MAX_VECS];
     float s[2] = {0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < NORM_MAX_VECS; ++i) {
       const int v = threadIdx.x + i * blockDim.x;
       if (v < nvec) {
-        xv[i].load(xr + v * VN);
         float f[VN];
         xv[i].to_float(f);
 #pragma unroll
         for (int j = 0; j < VN; ++j) { s[0] += f[j]; s[1] += f[j] * f[j]; }
+      }
+    }
+    const int next = row + gridDim.x;
+    if (next < rows) {
+#pragma unroll
+      for (int i = 0; i < NORM_MAX_VECS; ++i) {
+        const int v = threadIdx.x + i * blockDim.x;
+        if (v < nvec) xn[i].load(x + size_t(next) * H + v * VN);
       }
     }
     block_sum<2>(s, scratch);
@@ -122,6 +138,8 @@ __global__ void norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w
         Vec<T> o; o.from_float(f); o.store(yr + v * VN);
       }
     }
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_VECS; ++i) xv[i] = xn[i];
   }
 }
 
@@ -204,6 +222,14 @@ __global__ void __launch_bounds__(MAXT) norm_bwd_kernel(const T* __restrict__ dy
         }
       }
     }
+    Vec<T> av[NORM_BWD_VECS];   // this row of `add`: requested before the barrier too
+    if (add != nullptr) {
+#pragma unroll
+      for (int i = 0; i < NORM_BWD_VECS; ++i) {
+        const int v = threadIdx.x + i * blockDim.x;
+        if (v < nvec) av[i].load(add + size_t(row) * H + v * VN);
+      }
+    }
     block_sum<2>(s, scratch);
     const float m_g = LAYER ? s[0] / H : 0.f;
     const float m_gx = s[1] / H;
@@ -216,9 +242,8 @@ __global__ void __launch_bounds__(MAXT) norm_bwd_kernel(const T* __restrict__ dy
         for (int j = 0; j < VN; ++j) o[j] = (g[i][j] - m_g - xh[i][j] * m_gx) * rstd;
         Vec<T> ov; ov.from_float(o);
         if (add != nullptr) {
-          Vec<T> av; av.load(add + size_t(row) * H + v * VN);
           float r[VN], a[VN];
-          ov.to_float(r); av.to_float(a);
+          ov.to_float(r); av[i].to_float(a);
 #pragma unroll
           for (int j = 0; j < VN; ++j) r[j] = __fadd_rn(r[j], a[j]);  // never contracted into the multiply above
           ov.from_float(r);

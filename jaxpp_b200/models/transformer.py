@@ -151,23 +151,23 @@ class ModelConfig:
 
 
 def stage_cost_model(cfg: "ModelConfig") -> tuple:
-    """``(attn_share, head_extra, first_extra)`` for :func:`balanced_stage_layers`: the share of a block's time spent in
-    its attention half, and the cost, in blocks, of the extra work of the output stage (final norm, output projection,
-    cross entropy) and of the first stage (embedding, token slicing, position tables).  From training FLOPs per token,
-    with three corrections taken from the per-task timeline of a step on 8 GPUs: attention-kernel FLOPs count twice (the
-    flash-attention kernels run at about half the rate of the GEMMs); the output projection costs 1.12x its FLOPs with
-    the single-GPU cross-entropy kernel and 1.7x under tensor parallelism (the vocabulary-parallel loss makes several
-    fp32 passes over the logits: 11.8 ms against 11.5 ms for a block, forward and backward); the first stage's extra
-    forward work is worth a third of a block (3.8 ms)."""
+    """``(attn_share, head_extra, first_extra)`` for :func:`balanced_stage_layers`, from training FLOPs per token: the
+    share of a block's time spent in its attention half, and the cost, in blocks, of the extra work of the output stage
+    (final norm, output projection, cross entropy) and of the first stage.  Attention-kernel FLOPs count twice (the
+    flash-attention kernels run at about half the rate of the GEMMs, per the per-op timings of a step) and the output
+    projection gets 12 % on top for the cross entropy's passes over the logits.  The per-op timings of a step on 8 GPUs
+    agree with this within what they can resolve (output projection + loss: 5.1 ms against 11.5 ms for a block, forward
+    and backward, i.e. 0.44; the first stage's embedding is below 0.05): the per-TASK times do not, because a task's
+    first kernel waits on the stream for the activation from the previous rank, which makes forward tasks of later
+    ranks look longer than their work."""
     d, hd = cfg.d_model, cfg.head_dim
     attn_w = d * (cfg.n_heads + 2 * cfg.n_kv_heads) * hd + cfg.n_heads * hd * d
     mlp_w = (3 if cfg.family in ("llama", "mixtral") else 2) * d * cfg.ffn * (cfg.top_k if cfg.n_experts else 1)
     attn_kernels = 2.0 * 3.5 * 4.0 * cfg.seq * cfg.n_heads * hd * (0.5 if cfg.causal else 1.0)
     attn_half = 6.0 * attn_w + attn_kernels
     block = attn_half + 6.0 * mlp_w
-    head = 6.0 * cfg.padded_vocab * d * (1.7 if cfg.tp > 1 else 1.12) if cfg.family != "encoder" else 0.0
-    first = 0.33 if cfg.family != "encoder" else 0.0
-    return attn_half / block, head / block, first
+    head = 6.0 * cfg.padded_vocab * d * 1.12 if cfg.family != "encoder" else 0.0
+    return attn_half / block, head / block, 0.0
 
 
 def rank_loads(sizes, stage_to_rank, n_ranks: int, attn_share: float, first_extra: float, last_extra: float) -> list:
