@@ -76,8 +76,13 @@ _EXPANDING_TARGETS = {aten._to_copy.default, aten.to.dtype, aten.add.Tensor, ate
                       aten.full_like.default}
 
 
+_ALIASES = (aten.detach.default, aten.alias.default)
+
+
 def _freeze(a):
     if isinstance(a, fx.Node):
+        while a.op == "call_function" and a.target in _ALIASES:   # an alias stands for its operand (tasks are functional)
+            a = a.args[0]
         return ("n", id(a))
     if isinstance(a, (list, tuple)):
         return (type(a).__name__,) + tuple(_freeze(x) for x in a)
@@ -97,12 +102,21 @@ def _freeze(a):
 def cse(graph: fx.Graph) -> int:
     """Common-subexpression elimination: a node that applies the same pure op to the same operands as an earlier one
     is replaced by it (the reference re-traces the step through a CSE trace before hoisting, src/jaxpp/licm.py:66-126).
-    Stage markers, loop markers, seeded random ops and ``get_attr`` nodes are left alone.  Returns the number of nodes
-    removed."""
+    Stage markers, loop markers, seeded random ops and ``get_attr`` nodes are left alone.  A node of the backward pass
+    is never replaced by one of the forward pass: the re-run forward of a recomputed block applies the same ops to the
+    same operands as the forward pass did, and merging the two would keep every activation alive until the backward
+    pass -- what recompute exists to avoid (JAX marks such blocks ``prevent_cse``; ``JAXPP_DISABLE_PREVENT_CSE`` lifts
+    the barrier here as it does in the reference, src/jaxpp/core.py:3043-3074).  Returns the number of nodes removed."""
     markers = set(prim.marker_targets().values())
     seen: dict = {}
     removed = 0
+    in_backward = False
+    barrier = not config.disable_prevent_cse.value
+    from_forward: set = set()
     for node in list(graph.nodes):
+        if node.op == "call_function" and is_marker(node, "yield") and node.args[2] == prim.BWD_CODE and not in_backward:
+            in_backward = True
+            from_forward = set(seen.values())
         if node.op != "call_function" or node.target in markers or is_nondeterministic(node):
             continue
         schema = getattr(node.target, "_schema", None)
@@ -110,7 +124,7 @@ def cse(graph: fx.Graph) -> int:
             continue
         key = (id(node.target), _freeze(node.args), _freeze(node.kwargs))
         first = seen.get(key)
-        if first is None:
+        if first is None or (barrier and in_backward and first in from_forward):
             seen[key] = node
             continue
         node.replace_all_uses_with(first)

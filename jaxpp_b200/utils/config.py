@@ -120,10 +120,9 @@ dump_dir = StrEnvVar("JAXPP_DUMP_DIR", "")
 # inf (the default) = sent buffers are only collected at the end of the step.
 transfer_done_delay = IntEnvVar("JAXPP_TRANSFER_DONE_DELAY", math.inf)  # type: ignore[arg-type]
 disable_schedule_task_fusion = BoolEnvVar("JAXPP_DISABLE_SCHEDULE_TASK_FUSION", False)
-disable_prevent_cse = BoolEnvVar(
-    "JAXPP_DISABLE_PREVENT_CSE", False,
-    no_effect="recomputed blocks are traced as ordinary ops of the backward task and no pass merges them with the "
-              "forward pass' ops across tasks, so there is no barrier to relax")
+# Common-subexpression elimination (JAXPP_ENABLE_LICM) never replaces an op of the backward pass by one of the forward pass,
+# which is what keeps a recomputed block recomputed; this flag lifts the barrier.
+disable_prevent_cse = BoolEnvVar("JAXPP_DISABLE_PREVENT_CSE", False)
 directional_communicators = BoolEnvVar(
     "JAXPP_DIRECTIONAL_COMMUNICATORS", False,
     no_effect="point-to-point transfers always use one communicator per direction of a pair of pipeline ranks: "

@@ -147,6 +147,37 @@ def test_activation_recompute_matches_and_moves_forward_ops_into_backward():
     assert len(fwd0(progs[1]).outs) < len(fwd0(progs[0]).outs)
 
 
+def test_cse_does_not_undo_activation_recompute_unless_asked():
+    """With common-subexpression elimination on, the re-run forward of a recomputed block equals the forward pass op for
+    op; merging them would hand every activation from the forward task to the backward task again."""
+    from jaxpp_b200.compiler.program import RunTask
+    from jaxpp_b200.utils import config
+
+    sched = jp.Std1F1B(2)
+    kw = dict(vocab=128, d_model=32, n_layers=2, n_heads=2, n_kv_heads=2, ffn=64, seq=16, n_stages=2, dtype=torch.float32)
+    g = torch.Generator().manual_seed(3)
+    tokens = torch.randint(0, 128, (2, 2, 16), generator=g)
+    labels = torch.randint(0, 128, (2, 2, 16), generator=g)
+    cfg = tf.ModelConfig("llama", recompute=True, **kw)
+
+    def n_fwd_outs(**flags):
+        step = lt.make_train_step(cfg, sched, lt.Hyper(lr=1e-2, inplace_update=False))
+        state = lt.init_state(cfg, sched, "cpu")
+        with config.enable_licm.set(flags.get("licm", False)), config.disable_prevent_cse.set(flags.get("lift", False)):
+            f = jp.mpmd_jit_with_loop(step, cpu_mesh(2))
+            prog = f.lower(state, tokens, labels).program
+            out = f(state, tokens, labels)
+        fwd0 = next(i for i in prog.instrs if isinstance(i, RunTask) and i.name == "fwd_0__0")
+        return len(fwd0.outs), out
+
+    plain, ref = n_fwd_outs()
+    kept, got = n_fwd_outs(licm=True)
+    lifted, got2 = n_fwd_outs(licm=True, lift=True)
+    assert kept <= plain < lifted
+    assert_trees_equal(pytree.tree_map(local, ref, is_leaf=lambda x: isinstance(x, jp.MpmdArray)), got, exact=True)
+    assert_trees_equal(pytree.tree_map(local, ref, is_leaf=lambda x: isinstance(x, jp.MpmdArray)), got2, exact=True)
+
+
 @pytest.mark.parametrize("family,schedule,tied", [
     ("llama", jp.Interleaved1F1B(4, 2), False), ("gpt2", jp.Std1F1B(2), True), ("llama", jp.ZeroBubble(2), False),
 ])

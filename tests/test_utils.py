@@ -269,7 +269,7 @@ def test_reference_flags_without_an_effect_here_say_so(caplog):
 
     inert = [v for v in vars(config).values() if isinstance(v, config.EnvVar) and v.no_effect]
     assert {v.env_key for v in inert} == {
-        "JAXPP_SHARE_DONATION", "JAXPP_ENABLE_LOCAL_PROPAGATION", "JAXPP_DISABLE_PREVENT_CSE",
+        "JAXPP_SHARE_DONATION", "JAXPP_ENABLE_LOCAL_PROPAGATION",
         "JAXPP_DIRECTIONAL_COMMUNICATORS", "JAXPP_DEBUG_SKIP_PROPAGATION", "JAXPP_FAST_INFER_SHARDINGS"}
     config._WARNED.clear()
     log = logging.getLogger("test_flags")
