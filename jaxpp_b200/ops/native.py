@@ -122,7 +122,12 @@ def set_wait_budget_ms(ms: float) -> None:
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """Raw handle of the current stream of the current device (the C getters: a ``torch.cuda.Stream`` object per launch
+    costs more than the rest of a small op's wrapper)."""
+    try:
+        return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice())
+    except AttributeError:  # pragma: no cover - a torch build without the private getters
+        return torch.cuda.current_stream().cuda_stream
 
 
 def _dt(t: torch.Tensor) -> int:
@@ -143,6 +148,11 @@ def _rows(t: torch.Tensor) -> int:
 
 # ---- GEMM ---------------------------------------------------------------------------------------------
 def _as_2d_bf16(t: torch.Tensor) -> torch.Tensor:
+    # the common case first (a contiguous bfloat16 matrix whose rows start on 16-byte boundaries): this function runs
+    # two or three times per GEMM, and in launch-bound configurations the Python in front of a kernel is the step time
+    if (t.dim() == 2 and t.dtype == torch.bfloat16 and t.is_contiguous() and not (t.shape[1] & 7)
+            and not (t.data_ptr() & 15)):
+        return t
     t2 = t.reshape(-1, t.shape[-1])
     if t2.dtype != torch.bfloat16:
         raise NativeError(f"the tcgen05 GEMM takes bfloat16 operands, got {t2.dtype}")
@@ -178,7 +188,7 @@ def linear(x, w, bias):
     N = w2.shape[0]
     out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
     gemm(x2, w2, M, N, K, False, False, out, bias.contiguous() if bias is not None else None)
-    return out.view(*x.shape[:-1], N)
+    return out if x.dim() == 2 else out.view(*x.shape[:-1], N)
 
 
 def _counts_ok(counts, E) -> bool:
@@ -276,7 +286,7 @@ def linear_dgrad(dy, w):
     Kout = w2.shape[1]
     out = torch.empty(M, Kout, dtype=torch.bfloat16, device=dy.device)
     gemm(dy2, w2, M, Kout, Nred, False, True, out)
-    return out.view(*dy.shape[:-1], Kout)
+    return out if dy.dim() == 2 else out.view(*dy.shape[:-1], Kout)
 
 
 def linear_wgrad(dy, x, out: Optional[torch.Tensor] = None, accumulate: bool = False):
