@@ -28,6 +28,35 @@ def test_slots_are_unique_and_capacity_bounded():
     assert (dest[e0[:C]] == torch.arange(C)).all()
 
 
+def test_slot_counts_and_grouped_linear_with_counts():
+    """The per-expert counts of filled slots (what lets the grouped GEMMs skip unused capacity) against a direct count,
+    and the grouped linear op with counts against the one without: zero rows give zero products, so results and
+    gradients must be identical (on CPU the counts are ignored; on the GPU they select the skipping kernels)."""
+    from jaxpp_b200.ops import core as ops
+
+    top_i = _routing(T=40, E=4, k=2, seed=3)
+    C = 16
+    dest, keep, counts = moe.slots_and_counts(top_i, 4, C)
+    flat = top_i.reshape(-1)
+    assert counts.dtype == torch.int32
+    assert counts.tolist() == [min(C, int((flat == e).sum())) for e in range(4)]
+    assert int(keep.sum()) == int(counts.sum())
+    d2, k2 = moe.slots_for(top_i, 4, C)
+    assert torch.equal(d2, dest) and torch.equal(k2, keep)
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(40, 8, generator=g)
+    buf = moe.dispatch(x, dest, 4, C, 2)                                  # [E, C, d], unused slots are zero
+    live = torch.arange(C)[None, :] < counts[:, None]
+    assert (buf[~live] == 0).all()
+    w = torch.randn(4, 6, 8, generator=g, requires_grad=True)
+    bx = buf.clone().requires_grad_(True)
+    y0 = ops.linear_batched(bx, w)
+    g0 = torch.autograd.grad(y0.square().sum(), [bx, w])
+    y1 = ops.linear_batched(bx, w, counts.view(4, 1), C)
+    g1 = torch.autograd.grad(y1.square().sum(), [bx, w])
+    assert torch.equal(y0, y1) and all(torch.equal(a, b) for a, b in zip(g0, g1))
+
+
 def test_fused_ops_match_index_ops_and_are_transposes():
     T, E, k, d, C = 24, 4, 2, 16, 8
     top_i = _routing(T, E, k, seed=1)

@@ -208,6 +208,35 @@ def test_collect_task_times_ms_records_every_task():
     assert nothing is None
 
 
+def test_live_bytes_tracker_reports_the_fullest_moment_of_a_step(monkeypatch):
+    """With JAXPP_B200_TRACK_LIVE_BYTES=1 the executor records, per step, the bytes of distinct storages a rank's
+    environment held at its fullest, which task came next and the largest values; without it nothing is recorded."""
+    import torch
+
+    import jaxpp_b200 as jp
+    from helpers import make_mlp_step, mlp_params
+    from jaxpp_b200.runtime import executor
+
+    mesh = jp.MpmdMesh.create({"mpmd": 2, "data": 1, "model": 1}, kind="cpu", multi_process=False)
+    f = jp.mpmd_jit_with_loop(make_mlp_step(2, jp.Std1F1B(2), 3), mesh)
+    params, batch = mlp_params(2, 8), torch.randn(3, 2, 8)
+    executor.LIVE_REPORT.clear()
+    f(params, batch)
+    assert not executor.LIVE_REPORT
+    monkeypatch.setenv("JAXPP_B200_TRACK_LIVE_BYTES", "1")
+    f(params, batch)
+    assert len(executor.LIVE_REPORT) == 1
+    rep = executor.LIVE_REPORT[-1]
+    sizes = [b for b, _vid, _shape, _dtype in rep["all"]]
+    assert rep["bytes"] == sum(sizes) > 0 and sizes == sorted(sizes, reverse=True) and rep["n_values"] == len(sizes)
+    assert rep["largest"] == rep["all"][:12] and ":" in rep["before"]
+    # aliases of one storage count once
+    t = torch.zeros(16)
+    total, items = executor._live_bytes({1: t, 2: t[:4], 3: torch.zeros(2)})
+    assert total == 16 * 4 + 2 * 4 and len(items) == 2
+    executor.LIVE_REPORT.clear()
+
+
 def test_memstats_and_sharding_mesh_helpers(capsys):
     """``print_memstats`` is silent unless enabled and brackets the body with labelled reports; shardings are
     re-pointed at another mesh with their specs unchanged (reference: utils.py:223-268)."""
