@@ -18,8 +18,8 @@ test-all: build
 lint:
 	$(PY) -m ruff check jaxpp_b200 tests examples bench.py
 
-docs:             ## the documentation is plain Markdown: README.md, DESIGN.md, docs/, examples/tutorial.md
-	@ls README.md DESIGN.md docs/*.md examples/tutorial.md
+docs:             ## the documentation is plain Markdown: the top-level README, docs/ and the tutorial under examples/
+	@ls README.md docs/*.md examples/tutorial.md
 
 bench:            ## headline benchmark on one GPU (use torch.distributed.run for more, see bench.py)
 	$(PY) bench.py --gpus 1

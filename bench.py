@@ -208,7 +208,7 @@ def main():
         cfg = dataclasses.replace(cfg, **over)
     if args.stage_layers != "equal" and n_stages > 1:
         if args.stage_layers == "auto":
-            attn_share, head_extra, first_extra = tf.stage_cost_model(cfg)   # calibrated on profiles/step_timeline_n8.txt
+            attn_share, head_extra, first_extra = tf.stage_cost_model(cfg)   # from FLOPs per token
             sizes = tf.balanced_stage_layers(cfg.n_layers, n_stages, schedule.get_mpmd_idx, pp, first_extra=first_extra,
                                              last_extra=head_extra, attn_share=attn_share,
                                              max_shift=max(1.0, min(3.0, head_extra)))
