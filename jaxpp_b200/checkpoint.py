@@ -18,7 +18,7 @@ from __future__ import annotations
 import json
 import os
 import shutil
-from typing import Any, Callable, Mapping
+from typing import Any, Mapping
 
 import numpy as np
 import torch

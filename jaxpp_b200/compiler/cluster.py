@@ -19,7 +19,7 @@ from torch import fx
 
 from .. import primitives as prim
 from ..types import TaskType
-from ..utils import config, logger
+from ..utils import config
 
 aten = torch.ops.aten
 

@@ -19,15 +19,12 @@ from __future__ import annotations
 
 import dataclasses
 import math
-import operator
 from collections import defaultdict
-from typing import Any
 
-import torch
 from torch import fx
 
 from .. import primitives as prim
-from ..schedules import BaseSchedule, FusedTask, Task, mk_task_name, preprocess_schedule_tasks
+from ..schedules import BaseSchedule, FusedTask, mk_task_name, preprocess_schedule_tasks
 from ..types import TaskType
 from ..utils import config, hbytes, log_elapsed_time, logger
 from . import cluster as cl

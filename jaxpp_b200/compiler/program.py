@@ -11,8 +11,7 @@ own id → tensor environment.
 from __future__ import annotations
 
 import dataclasses
-import json
-from typing import Any, Sequence
+from typing import Any
 
 import torch
 

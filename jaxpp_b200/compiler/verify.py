@@ -12,7 +12,7 @@ from __future__ import annotations
 
 from collections import defaultdict
 
-from .program import (Accum, AllGather, AllReduce, Delete, LoopIndex, Program, RunTask, SendDone, Slice, Transfer)
+from .program import (Accum, AllGather, AllReduce, Delete, LoopIndex, Program, RunTask, Slice, Transfer)
 
 
 class ProgramError(AssertionError):

@@ -8,7 +8,6 @@ from __future__ import annotations
 import dataclasses
 from typing import Callable
 
-import torch
 
 from . import api as jp
 from .models import transformer as tf

@@ -23,7 +23,7 @@ from .compiler.program import Program
 from .mesh import MpmdMesh, NamedSharding, PartitionSpec
 from .runtime.executor import run_multi_controller, run_single_controller
 from .schedules import BaseSchedule
-from .utils import config, log_elapsed_time, logger
+from .utils import config, logger
 
 
 @dataclasses.dataclass(frozen=True)

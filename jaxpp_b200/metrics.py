@@ -9,7 +9,6 @@ between stages, peak device memory.
 from __future__ import annotations
 
 import json
-import os
 import time
 from typing import Any
 

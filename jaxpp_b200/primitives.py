@@ -26,7 +26,6 @@ from typing import Any
 import torch
 from torch import Tensor
 
-from .types import TaskType
 
 _lib = torch.library.Library("pp", "DEF")
 

@@ -18,7 +18,7 @@ from typing import Any, Sequence
 
 import torch
 
-from ..compiler.program import (Accum, AllGather, AllReduce, Delete, Instr, LoopIndex, Program, RunTask, SendDone,
+from ..compiler.program import (Accum, AllGather, AllReduce, Delete, LoopIndex, Program, RunTask, SendDone,
                                 Slice, Transfer)
 from .. import fault
 from ..utils import config

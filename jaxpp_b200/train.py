@@ -11,11 +11,8 @@ from __future__ import annotations
 
 import argparse
 import dataclasses
-import os
-import sys
 
 import torch
-from torch.utils import _pytree as pytree
 
 
 def main(argv=None):

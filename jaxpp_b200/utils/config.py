@@ -11,7 +11,7 @@ from __future__ import annotations
 import contextlib
 import math
 import os
-from typing import Callable, Generic, Iterator, TypeVar
+from typing import Generic, Iterator, TypeVar
 
 T = TypeVar("T")
 _UNSET = object()
