@@ -46,6 +46,17 @@ class DistArray:
             if t is not None and tuple(t.shape) != want:
                 raise ValueError(f"shard on {d} has shape {tuple(t.shape)}, expected {want} for {sharding.spec}")
 
+    @classmethod
+    def _trusted(cls, shards: dict, sharding: NamedSharding, shape: tuple, dtype: torch.dtype) -> "DistArray":
+        """Constructor for callers that have checked the shard shapes once already (the compiled step wraps the same
+        outputs every step: thousands of arrays per step for a model with many parameters)."""
+        self = object.__new__(cls)
+        self.shards = shards
+        self.sharding = sharding
+        self.shape = shape
+        self.dtype = dtype
+        return self
+
     @property
     def mesh(self) -> Mesh:
         return self.sharding.mesh
@@ -166,6 +177,19 @@ class MpmdArray:
             assert all(g == want for g in got), (got, want)
         self._shape = tuple(int(s) for s in shape)
         self._dtype = dtype
+
+    @classmethod
+    def _trusted(cls, arrays: "OrderedDict[int, DistArray]", mpmd_sharding: MpmdSharding, idxs: tuple, shape: tuple,
+                 dtype: torch.dtype) -> "MpmdArray":
+        """Constructor without the consistency checks, for the compiled step's outputs (checked on its first call)."""
+        self = object.__new__(cls)
+        self._mpmd_sharding = mpmd_sharding
+        self._mpmd_mesh = mpmd_sharding.mpmd_mesh
+        self._mpmd_idxs = idxs
+        self._arrays = arrays
+        self._shape = shape
+        self._dtype = dtype
+        return self
 
     # -- metadata -------------------------------------------------------------------------------
     @property

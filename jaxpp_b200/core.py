@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import dataclasses
 import os
+from collections import OrderedDict
 from typing import Any, Callable, Sequence
 
 import torch
@@ -186,26 +187,45 @@ class CompiledMpmd:
                 pass   # a metadata-only array of another pipeline rank: nothing to release here
 
     def _wrap_outputs(self, outs):
+        """Flat program outputs -> the user's output tree of :class:`MpmdArray`.  What does not change from call to call
+        (shardings, global shapes, the sub-mesh and device of every local piece) is worked out on the first call, which
+        also builds the arrays through the checking constructors; later calls only attach the new tensors."""
         mesh = self.mesh
+        plan = getattr(self, "_wrap_plan", None)
         wrapped = []
-        for k, (o, val) in enumerate(zip(self.program.outputs, outs)):
-            if o[0] == "c":
+        if plan is None:
+            plan = []
+            low = mesh.lowering_mesh()
+            for k, (o, val) in enumerate(zip(self.program.outputs, outs)):
+                if o[0] == "c":
+                    wrapped.append(val)
+                    plan.append(None)
+                    continue
+                _, vid, ranks = o
+                spec = self.out_specs_flat[k]
+                info = self.program.values[vid]
+                sharding = MpmdSharding(mesh, frozenset(ranks), spec)
+                gshape = tuple(int(s * low.axis_size(sharding.spec.axes_of(d))) for d, s in enumerate(info.shape))
+                pieces = {}
+                for r in ranks:
+                    sub = mesh.unstack[r]
+                    dev = mesh.my_device if mesh.jax_mesh.is_multi_process else sub.flat_devices[0]
+                    pieces[r] = (dev, NamedSharding(sub, sharding.spec))
+                locals_ = [DistArray({pieces[r][0]: t}, pieces[r][1], gshape, info.dtype) for r, t in sorted(val.items())]
+                wrapped.append(MpmdArray(locals_, sharding, gshape, info.dtype))   # checks shapes, dtypes and specs
+                plan.append((sharding, tuple(sorted(sharding.mesh_ids)), gshape, info.dtype, pieces))
+            self._wrap_plan = plan
+            return pytree.tree_unflatten(wrapped, self.out_spec)
+        for entry, val in zip(plan, outs):
+            if entry is None:
                 wrapped.append(val)
                 continue
-            _, vid, ranks = o
-            spec = self.out_specs_flat[k]
-            info = self.program.values[vid]
-            sharding = MpmdSharding(mesh, frozenset(ranks), spec)
-            low = mesh.lowering_mesh()
-            gshape = tuple(
-                s * low.axis_size(sharding.spec.axes_of(d)) for d, s in enumerate(info.shape)
-            )
-            locals_ = []
-            for r, t in sorted(val.items()):
-                sub = mesh.unstack[r]
-                dev = mesh.my_device if mesh.jax_mesh.is_multi_process else sub.flat_devices[0]
-                locals_.append(DistArray({dev: t}, NamedSharding(sub, sharding.spec), gshape, info.dtype))
-            wrapped.append(MpmdArray(locals_, sharding, gshape, info.dtype))
+            sharding, idxs, gshape, dtype, pieces = entry
+            arrays = OrderedDict()
+            for r in sorted(val):
+                dev, named = pieces[r]
+                arrays[r] = DistArray._trusted({dev: val[r]}, named, gshape, dtype)
+            wrapped.append(MpmdArray._trusted(arrays, sharding, idxs, gshape, dtype))
         return pytree.tree_unflatten(wrapped, self.out_spec)
 
 
