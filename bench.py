@@ -209,6 +209,8 @@ def main():
     if args.stage_layers != "equal" and n_stages > 1:
         if args.stage_layers == "auto":
             attn_share, head_extra, first_extra = tf.stage_cost_model(cfg)   # from FLOPs per token
+            if tf.launch_bound(cfg, mb_local * cfg.seq):
+                attn_share, head_extra = 0.5, 0.1   # stages cost their number of kernels: the head is a dozen launches
             sizes = tf.balanced_stage_layers(cfg.n_layers, n_stages, schedule.get_mpmd_idx, pp, first_extra=first_extra,
                                              last_extra=head_extra, attn_share=attn_share,
                                              max_shift=max(1.0, min(3.0, head_extra)))

@@ -170,6 +170,20 @@ def stage_cost_model(cfg: "ModelConfig") -> tuple:
     return attn_half / block, head / block, 0.0
 
 
+def launch_bound(cfg: "ModelConfig", tokens_per_microbatch: int) -> bool:
+    """Is a block's GPU time below the time Python needs to launch its kernels?  A block is about 110 launches forward
+    and backward at 25-35 us of host time each (measured: 33 us per launch on a step of the GPT-2-XL shape with one
+    sequence per replica, where the GPUs ran at 0.11 of the GEMM peak and full clock); its GPU time is estimated from
+    its FLOPs at 1e15 FLOP/s.  In such a configuration a stage's cost is its NUMBER of kernels, not their work: the
+    output stage's extra is a dozen launches, not the FLOPs of the output projection."""
+    d, hd = cfg.d_model, cfg.head_dim
+    attn_w = d * (cfg.n_heads + 2 * cfg.n_kv_heads) * hd + cfg.n_heads * hd * d
+    mlp_w = (3 if cfg.family in ("llama", "mixtral") else 2) * d * cfg.ffn * (cfg.top_k if cfg.n_experts else 1)
+    gpu_ms = 6.0 * (attn_w + mlp_w) * tokens_per_microbatch / max(1, cfg.tp) / 1e15 * 1e3
+    host_ms = 110 * 0.030
+    return gpu_ms < host_ms
+
+
 def rank_loads(sizes, stage_to_rank, n_ranks: int, attn_share: float, first_extra: float, last_extra: float) -> list:
     """Work per pipeline rank, in blocks, of stages of ``sizes`` blocks (entries may end in .5) placed by
     ``stage_to_rank``.  The attention half of a block costs ``attn_share`` of a block; the first stage carries
