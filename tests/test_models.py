@@ -274,6 +274,20 @@ def test_stage_layers_validation_and_balancing():
     assert isinstance(s1["params"]["layers"]["001"]["wqkv"], jp.ShapeDtypeStruct)
 
 
+def test_launch_bound_configurations_are_told_apart():
+    """One GPT-2-XL sequence per replica makes kernels shorter than the Python that launches them (stages then cost
+    their number of kernels: equal stages); the large shapes are bound by the GPU (stages cost their FLOPs)."""
+    from jaxpp_b200 import configs
+
+    seen = {}
+    for name, per_rank in (("gpt2xl_pp2dp4", 1), ("llama7b_pp4tp2", 4), ("mixtral8x7b_pp2ep4", 2), ("llama70b_pp4tp2", 1)):
+        cfg = configs.get(name).model_config()
+        seen[name] = tf.launch_bound(cfg, per_rank * cfg.seq)
+    assert seen == {"gpt2xl_pp2dp4": True, "llama7b_pp4tp2": False, "mixtral8x7b_pp2ep4": False, "llama70b_pp4tp2": False}
+    attn_share, head_extra, first_extra = tf.stage_cost_model(configs.get("llama7b_pp4tp2").model_config())
+    assert 0.3 < attn_share < 0.6 and 0.4 < head_extra < 0.8 and first_extra == 0.0
+
+
 def test_zero_bubble_split_bounds_what_stays_alive_until_the_weight_gradient_half():
     """ZeroBubble with full recompute: the recomputed inputs and the activation gradients of every linear live from the
     activation-gradient task to the weight-gradient task.  ``JAXPP_B200_ZB_DEFER_BYTES`` bounds those bytes by running
