@@ -206,16 +206,8 @@ def main():
         if rc.ep > 1:
             over.update(n_experts=2 * rc.ep, capacity_factor=4.0)
         cfg = dataclasses.replace(cfg, **over)
-    if args.stage_layers != "equal" and n_stages > 1:
-        if args.stage_layers == "auto":
-            attn_share, head_extra, first_extra = tf.stage_cost_model(cfg)   # from FLOPs per token
-            if tf.launch_bound(cfg, mb_local * cfg.seq):
-                attn_share, head_extra = 0.5, 0.1   # stages cost their number of kernels: the head is a dozen launches
-            sizes = tf.balanced_stage_layers(cfg.n_layers, n_stages, schedule.get_mpmd_idx, pp, first_extra=first_extra,
-                                             last_extra=head_extra, attn_share=attn_share,
-                                             max_shift=max(1.0, min(3.0, head_extra)))
-        else:
-            sizes = tuple(float(x) for x in args.stage_layers.split(","))
+    sizes = configs.choose_stage_layers(cfg, schedule, pp, mb_local * cfg.seq, args.stage_layers)
+    if sizes is not None:
         cfg = dataclasses.replace(cfg, stage_layers=sizes)
     mesh = jp.MpmdMesh.create({"mpmd": pp, "data": dp, "model": tp}, kind="cuda" if cuda else "cpu", multi_process=world > 1)
     if world > 1:

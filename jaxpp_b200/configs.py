@@ -81,6 +81,22 @@ CONFIGS: dict[str, RunConfig] = {c.name: c for c in [
 ]}
 
 
+def choose_stage_layers(cfg: tf.ModelConfig, schedule, pp: int, tokens_per_microbatch: int, mode: str = "auto"):
+    """Stage sizes for ``cfg`` under ``schedule``: ``"equal"`` (None: the model's default), a comma-separated list of
+    sizes in blocks (multiples of 0.5), or ``"auto"``: the split that evens out the pipeline ranks' work, counted in
+    FLOPs -- or in kernels when the configuration is bound by launches (:func:`transformer.launch_bound`)."""
+    n_stages = cfg.n_stages
+    if mode == "equal" or n_stages <= 1:
+        return None
+    if mode != "auto":
+        return tuple(float(x) for x in mode.split(","))
+    attn_share, head_extra, first_extra = tf.stage_cost_model(cfg)
+    if tf.launch_bound(cfg, tokens_per_microbatch):
+        attn_share, head_extra = 0.5, 0.1   # stages cost their number of kernels: the head is a dozen launches
+    return tf.balanced_stage_layers(cfg.n_layers, n_stages, schedule.get_mpmd_idx, pp, first_extra=first_extra,
+                                    last_extra=head_extra, attn_share=attn_share, max_shift=max(1.0, min(3.0, head_extra)))
+
+
 def get(name: str) -> RunConfig:
     if name not in CONFIGS:
         raise KeyError(f"unknown configuration {name!r}; available: {sorted(CONFIGS)}")

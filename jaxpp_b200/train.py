@@ -35,6 +35,9 @@ def main(argv=None):
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--lr", type=float, default=3e-4)
     ap.add_argument("--clip-grad-norm", type=float, default=None, help="clip gradients to this global L2 norm")
+    ap.add_argument("--stage-layers", default="equal",
+                    help="blocks per pipeline stage: 'equal', 'auto' (even out the pipeline ranks' work) or a list such as "
+                         "4,4,4,4,4,4,4.5,3.5 (a stage may end between the attention half and the feed-forward half of a block)")
     ap.add_argument("--shard-optimizer", action="store_true",
                     help="keep master weights and Adam moments as 1/dp slices per data-parallel rank (ZeRO stage 1)")
     args = ap.parse_args(argv)
@@ -62,6 +65,9 @@ def main(argv=None):
         if not multi and (rc.tp > 1 or rc.dp > 1):
             raise SystemExit("tensor/data parallel configurations need one process per device")
         sched = rc.make_schedule()
+        sizes = configs.choose_stage_layers(cfg, sched, rc.pp, max(1, rc.microbatch // rc.dp) * cfg.seq, args.stage_layers)
+        if sizes is not None:
+            cfg = dataclasses.replace(cfg, stage_layers=sizes)
         device = mesh.my_device.torch_device if multi else torch.device(kind)
         my_pp = mesh.my_mpmd_axis_index if multi else None
         tp_rank = mesh.axis_index("model") if multi and rc.tp > 1 else 0

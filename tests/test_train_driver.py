@@ -39,3 +39,17 @@ def test_train_driver_with_sharded_optimizer_state(tmp_path):
     assert len(manifest["params/layers/000/wqkv"]["shards"]) == 1           # parameters stay replicated
     assert launch(base + ["--steps", "1", "--resume"], 8, env=env, timeout_s=300) == 0
     assert os.path.exists(os.path.join(ck, "step_00000002", "manifest.json"))
+
+
+def test_train_driver_with_unequal_half_block_stages(tmp_path):
+    """``--stage-layers`` with a stage boundary between the two halves of a block: the run checkpoints, and a run with
+    equal stages resumes from that checkpoint (parameters are stored by name, whichever rank owns them)."""
+    ck = str(tmp_path / "ckpt")
+    base = ["-m", "jaxpp_b200.train", "--config", "llama7b_pp2tp2", "--tiny", "--device", "cpu", "--ckpt-dir", ck,
+            "--ckpt-every", "1", "--lr", "0.01"]
+    env = {"CUDA_VISIBLE_DEVICES": "", "OMP_NUM_THREADS": "1",
+           "PYTHONPATH": os.path.dirname(os.path.dirname(os.path.abspath(__file__)))}
+    assert launch(base + ["--steps", "1", "--stage-layers", "1,1,1.5,0.5"], 4, env=env, timeout_s=300) == 0
+    assert os.path.exists(os.path.join(ck, "step_00000001", "manifest.json"))
+    assert launch(base + ["--steps", "1", "--resume"], 4, env=env, timeout_s=300) == 0
+    assert os.path.exists(os.path.join(ck, "step_00000002", "manifest.json"))
